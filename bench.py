@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the attention engine on the multi-stream serving workload.
+
+One step = the attention of one decode step for every synthesis stream a GPU serves:
+24 backbone + 6 residual-LM layers of single-token attention over each stream's own KV cache
+(append of the new row included), followed by one LocDiT CFG patch (10 CFM timesteps x 8 layers,
+2 branches x 9 tokens).  256 streams per GPU with KV lengths drawn uniformly from [128, 4096].
+Metric: patches per second (one patch per stream per step), whole job.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--kv-type f16]
+
+N > 1 is launched by torch.distributed.run, one rank per GPU; ranks share nothing on the data path
+(every stream lives on one GPU), so the only cross-rank traffic is the barrier and the max-reduce of
+the timings.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, HK, D = 16, 2, 64
+BASE_LAYERS, RES_LAYERS = 24, 6
+DIT_LAYERS, DIT_SEQ, CFM_STEPS = 8, 9, 10
+KV_LO, KV_HI = 128, 4096
+WORKLOAD = ("multi-stream serving: {s} streams/GPU, ragged KV U[128,4096], 24+6 LM layers single-token attention "
+            "(append included) + 1 LocDiT CFG patch (10 CFM steps x 8 layers x 2 branches x 9 tokens)")
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    p.add_argument("--streams", type=int, default=256, help="streams per GPU (weak) or in total (strong)")
+    p.add_argument("--kv-type", default="f16", choices=["f16", "q8_0"])
+    p.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    p.add_argument("--cpu-sample-streams", type=int, default=24)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def stream_lengths(n, rank=0):
+    return np.random.default_rng(12345 + rank).integers(KV_LO, KV_HI + 1, n).astype(np.int32)
+
+
+def lm_bytes_per_layer(lens, kv_type):
+    """Algorithmic bytes of one LM layer over all streams: K and V rows once, Q in, output out."""
+    row = 512.0 if kv_type == "f16" else 272.0
+    return float(np.sum(row * lens.astype(np.float64) + 8192.0))
+
+
+# ------------------------------------------------------------------ clocks
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower() == "active" for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ reference arm / CPU baseline
+
+def cpu_reference_throughput(n_streams, iters, kv_type):
+    """patches/s of the reference's own ggml CPU attention (unmodified, as shipped: native K/V type,
+    one graph of 30 single-token nodes per stream and one graph of 80 LocDiT nodes per patch, streams
+    served one after another as the reference server does) on a sample of the workload."""
+    from oracle import voxoracle as vo
+    if vo.RefGgml.available():
+        ref, kind = vo.RefGgml(), "reference"
+    else:
+        ref, kind = None, "port"
+    oracle = vo.Oracle()
+    cores = os.cpu_count() or 1
+    lens = stream_lengths(max(n_streams, 1))[:n_streams]
+    rng = np.random.default_rng(7)
+    L = BASE_LAYERS + RES_LAYERS
+    kvt = vo.F16 if kv_type == "f16" else vo.Q8_0
+    work = []
+    for n in lens:
+        q = rng.standard_normal((L, 1, H, 1, D)).astype(np.float32)
+        k = rng.standard_normal((L, 1, HK, int(n), D)).astype(np.float32)
+        v = rng.standard_normal((L, 1, HK, int(n), D)).astype(np.float32)
+        ks, vs = (k.astype(np.float16), v.astype(np.float16)) if kv_type == "f16" else (oracle.quantize_q8_0(k), oracle.quantize_q8_0(v))
+        work.append((q, ks, vs))
+    n_dit = CFM_STEPS * DIT_LAYERS
+    dq = rng.standard_normal((n_dit, 2, H, DIT_SEQ, D)).astype(np.float32)
+    dk = rng.standard_normal((n_dit, 2, HK, DIT_SEQ, D)).astype(np.float32)
+    dv = rng.standard_normal((n_dit, 2, HK, DIT_SEQ, D)).astype(np.float32)
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for q, ks, vs in work:
+            if ref is not None:
+                ref.attn(q, ks, vs, None, kv_type=kvt, n_threads=cores, n_layers=L)
+                ref.attn(dq, dk, dv, None, kv_type=vo.F32, n_threads=cores, n_layers=n_dit)
+            else:
+                for l in range(L):
+                    oracle.attn(q[l], ks[l], vs[l], kv_type=kvt, path=vo.PATH_AUTO, n_chunks=cores)
+                for l in range(n_dit):
+                    oracle.attn(dq[l], dk[l], dv[l], kv_type=vo.F32, path=vo.PATH_ROW)
+        return time.perf_counter() - t0
+
+    one_pass()
+    times = [one_pass() for _ in range(max(iters, 1))]
+    med = statistics.median(times)
+    return {"value": n_streams / med, "unit": "patches/s", "cores": cores if ref is not None else 1, "kind": kind,
+            "sample": f"{n_streams} streams of the workload (KV lengths {int(lens.min())}..{int(lens.max())}), "
+                      f"{L} decode layers + {n_dit} LocDiT calls each, median of {len(times)} passes, "
+                      f"ggml CPU backend {'(' + ref.isa + ', OpenMP)' if ref is not None else 'restated in C'}",
+            "ms_per_stream": med / n_streams * 1e3}
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    steps = max(args.steps, 1)
+    r = cpu_reference_throughput(args.cpu_sample_streams, min(steps, 5), args.kv_type)
+    line = {"impl": "reference", "metric": "patches/s", "value": r["value"], "unit": "patches/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_stream"] * args.cpu_sample_streams,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD.format(s=args.streams), "kv_type": args.kv_type,
+                       "note": "host cores only; the reference serves streams one at a time"},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": "patches/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ engine arm
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.import_package()
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    # streams of this rank
+    if args.scaling == "weak":
+        lens = stream_lengths(args.streams, rank)
+    else:
+        all_lens = stream_lengths(args.streams, 0)
+        owner = pkg.partition_streams(all_lens, world)
+        lens = all_lens[owner == rank]
+    S = len(lens)
+    total_steps = args.warmup + args.steps
+    max_len = ((KV_HI + 2 * (total_steps + 8) + 63) // 64) * 64
+    kv_type = pkg.F16 if args.kv_type == "f16" else pkg.Q8_0
+
+    eng = pkg.Engine(local)
+    group = pkg.Group(eng, n_streams=S, max_len=max_len, kv_type=kv_type, base_layers=BASE_LAYERS, res_layers=RES_LAYERS,
+                      n_heads=H, n_kv_heads=HK, locdit_layers=DIT_LAYERS, locdit_seq=DIT_SEQ, cfm_steps=CFM_STEPS)
+    group.set_kv_len(lens)
+    group.fill_synthetic(seed=rank)
+    shapes = group.buffer_shapes()
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    dev_t = {n: (torch.empty(s, device="cuda") if n.endswith("out") else torch.randn(s, device="cuda", generator=gen))
+             for n, s in shapes.items()}
+    stream = torch.cuda.current_stream()
+
+    # ---- device-resident throughput: K steps, CUDA events, barrier + sync on both sides
+    for _ in range(args.warmup):
+        group.step(dev_t, advance=True)
+    eng.sync_status()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    barrier()
+    l0 = eng.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        group.step(dev_t, advance=True)
+    e1.record(stream)
+    barrier()
+    eng.sync_status()
+    launches = eng.launches - l0
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clock_info = clocks.stop() if rank == 0 else None
+    ms_per_step = ms_total / args.steps
+    total_streams = sum_over_ranks(float(S))
+    value = total_streams / (ms_per_step * 1e-3)
+
+    # ---- roofline of the dominant kernel (split-KV decode): per-launch duration by CUDA events on the
+    #      launching stream, one (decode [+ merge]) launch pair per LM layer, lengths as they now stand
+    cur = group.kv_len()
+    kv_len_dev = torch.from_numpy(cur).cuda()
+    bound = int(cur.max())
+    q_all = dev_t["lm_q"]
+    durs = []
+    for rep in range(3):
+        for l in range(BASE_LAYERS + RES_LAYERS):
+            cache = group.cache(0 if l < BASE_LAYERS else 1)
+            layer = l if l < BASE_LAYERS else l - BASE_LAYERS
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            cache.decode(layer, q_all[l], kv_len_dev, bound, dst=dev_t["lm_out"][l])
+            b.record(stream)
+            durs.append((a, b))
+    torch.cuda.synchronize()
+    dec_ms = statistics.mean(a.elapsed_time(b) for a, b in durs[len(durs) // 3:])
+    layer_bytes = lm_bytes_per_layer(cur, args.kv_type)
+    achieved = layer_bytes / (dec_ms * 1e-3) / 1e9
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    roofline = {"bound": "hbm", "kernel": "decode_f16_kernel (+ decode_merge_kernel)" if args.kv_type == "f16" else "decode_q8_kernel (+ merge)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                "us_per_launch": dec_ms * 1e3, "algorithmic_bytes_per_launch": layer_bytes,
+                "frac_of_nominal_8000": achieved / 8000.0}
+
+    # ---- LocDiT: latency of one patch for one stream (10 launches), and launches per CFM timestep
+    q1 = torch.randn((CFM_STEPS, 1, DIT_LAYERS, 2, H, DIT_SEQ, D), device="cuda", generator=gen)
+    k1 = torch.randn((CFM_STEPS, 1, DIT_LAYERS, 2, HK, DIT_SEQ, D), device="cuda", generator=gen)
+    v1 = torch.randn((CFM_STEPS, 1, DIT_LAYERS, 2, HK, DIT_SEQ, D), device="cuda", generator=gen)
+    o1 = torch.empty((CFM_STEPS, 1, DIT_LAYERS, 2, DIT_SEQ, H, D), device="cuda")
+    for _ in range(3):
+        for t in range(CFM_STEPS):
+            eng.locdit_step(q1[t], k1[t], v1[t], dst=o1[t])
+    torch.cuda.synchronize()
+    lb = eng.launches
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    a.record(stream)
+    for _ in range(reps):
+        for t in range(CFM_STEPS):
+            eng.locdit_step(q1[t], k1[t], v1[t], dst=o1[t])
+    b.record(stream)
+    torch.cuda.synchronize()
+    locdit = {"us_per_patch_single_stream": a.elapsed_time(b) * 1e3 / reps,
+              "launches_per_cfm_step": (eng.launches - lb) / (reps * CFM_STEPS)}
+
+    # ---- end to end through the host-buffer entry point: pinned host inputs, H2D + launches + D2H per step
+    e2e = None
+    if not args.no_e2e:
+        host_t = {n: torch.empty(s, dtype=torch.float32).pin_memory() for n, s in shapes.items()}
+        for n, x in host_t.items():
+            if not n.endswith("out"):
+                x.copy_(dev_t[n])
+        h2d = group.step_bytes(0) + group.step_bytes(2)
+        d2h = group.step_bytes(1) + group.step_bytes(3)
+        e2e_steps = max(2, min(args.steps, 5))
+        group.step_host(host_t, advance=True)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            group.step_host(host_t, advance=True)
+        barrier()
+        dt = max_over_ranks(time.perf_counter() - t0)
+        e2e = {"value": total_streams * e2e_steps / dt, "unit": "patches/s", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            r = cpu_reference_throughput(args.cpu_sample_streams, 3, args.kv_type)
+            cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        except Exception as ex:  # the baseline is a report, it must not take the bench line down
+            cpu = {"value": None, "unit": "patches/s", "cores": 0, "kind": "unavailable", "sample": repr(ex)}
+
+    if rank == 0:
+        line = {"metric": "patches/s", "value": value, "unit": "patches/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
+                "vs_baseline": None, "dtype": "f16 K/V, f32 Q/out, f16 MMA with f32 accumulation" if args.kv_type == "f16"
+                else "q8_0 K/V, f32 Q/out, f16 MMA with f32 accumulation",
+                "data": "synthetic",
+                "config": {"workload": WORKLOAD.format(s=args.streams), "streams_total": int(total_streams), "kv_type": args.kv_type,
+                           "l2": "inputs larger than L2 (KV read per step >> 126 MB)", "append": "included"},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_info,
+                "locdit": locdit,
+                "decode": {"gb_per_s": achieved, "pct_of_measured_peak": 100 * achieved / peak, "pct_of_8000": 100 * achieved / 8000}}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

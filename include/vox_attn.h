@@ -1,0 +1,268 @@
+/* vox_attn.h — C ABI of the B200 (sm_100a) attention engine for VoxCPM.cpp.
+ *
+ * The engine implements the operator that VoxCPM.cpp reaches through
+ * ggml_flash_attn_ext (third_party/ggml/include/ggml.h:2311-2330, called from
+ * src/minicpm.cpp:708-710 for the backbone LM, the residual LM, LocEnc and LocDiT):
+ *
+ *     dst = softmax(scale * Q K^T + mask) V      with GQA broadcast of K/V heads
+ *
+ * plus the KV cache that feeds it (MiniCPMKVCache, include/voxcpm/minicpm.h:44-84) and the
+ * batched forms VoxCPM.cpp's loops need (one launch for many synthesis streams; one launch
+ * for all layers and both CFG branches of a LocDiT timestep).
+ *
+ * Conventions
+ *   - plain C, no CUDA or torch types: device pointers are void*, a CUDA stream is passed
+ *     as void* (cudaStream_t), NULL meaning the legacy default stream;
+ *   - tensors are described as ggml describes them: element type, ne[4] extents with
+ *     dim 0 fastest, nb[4] strides in BYTES (ggml.h:655-687);
+ *   - every function returns a vox_status; nothing aborts, nothing falls back to the CPU;
+ *   - all launches are asynchronous on the caller's stream; an engine (and everything
+ *     created from it) belongs to one device and may be used by one host thread at a time.
+ */
+#ifndef VOX_ATTN_H
+#define VOX_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    VOX_ATTN_OK                  = 0,
+    VOX_ATTN_INVALID_ARGUMENT    = 1, /* null pointer, bad extent/stride, out-of-range index   */
+    VOX_ATTN_UNSUPPORTED         = 2, /* valid for the reference operator, not built here       */
+    VOX_ATTN_WORKSPACE_TOO_SMALL = 3,
+    VOX_ATTN_CUDA_ERROR          = 4, /* a CUDA runtime/driver call failed; see error string    */
+    VOX_ATTN_TIMEOUT             = 5, /* a bounded device-side wait ran out (status word)       */
+    VOX_ATTN_OUT_OF_MEMORY       = 6
+} vox_status;
+
+/* numbered as ggml numbers them (ggml.h enum ggml_type) */
+typedef enum {
+    VOX_TYPE_F32  = 0,
+    VOX_TYPE_F16  = 1,
+    VOX_TYPE_Q8_0 = 8  /* 34-byte blocks: fp16 scale + 32 int8 (ggml-common.h:221-224) */
+} vox_type;
+
+/* mirrors the fields of ggml_tensor the operator reads (ggml.h:655-687) */
+typedef struct {
+    int32_t type;   /* vox_type */
+    int64_t ne[4];
+    size_t  nb[4];  /* bytes */
+    void *  data;   /* device pointer (host pointer for the *_host entry points) */
+} vox_tensor;
+
+/* replaces the argument list of ggml_flash_attn_ext (ggml.h:2322-2330):
+ *   q    [D, n_q,  H,  B] f32          k, v [D, n_kv, HK, B] f32 | f16 | q8_0, rows contiguous
+ *   mask data==NULL, or [n_kv, n_q, ne2, ne3] f16 contiguous, broadcast over heads/batch
+ *   dst  [D, H, n_q, B] f32  (permuted against q exactly as the reference result is)      */
+typedef struct {
+    vox_tensor q, k, v, mask, dst;
+    float      scale;
+    float      max_bias;      /* must be 0: ALiBi is never used by VoxCPM.cpp             */
+    float      logit_softcap; /* must be 0                                                  */
+    int32_t    has_sinks;     /* must be 0 (ggml_flash_attn_ext_add_sinks is never called)  */
+} vox_attn_args;
+
+typedef struct vox_engine   vox_engine;
+typedef struct vox_kv_cache vox_kv_cache;
+typedef struct vox_group    vox_group;
+
+/* ---------------------------------------------------------------- engine --------------- */
+
+/* Replaces backend selection in VoxCPMBackend (src/backend.cpp:146-205): binds to one CUDA
+ * device, fails with VOX_ATTN_UNSUPPORTED unless it is compute capability 10.x. */
+int  vox_engine_create(int device, vox_engine ** out);
+void vox_engine_destroy(vox_engine * e);
+
+/* Text of the last failure on the calling thread (replaces GGML_ASSERT / CUDA_CHECK abort
+ * messages, third_party/ggml/src/ggml-cuda/common.cuh CUDA_CHECK). */
+const char * vox_attn_last_error_string(void);
+const char * vox_attn_status_string(int status);
+
+/* Kernel launches issued through this engine so far (the launch-count metric). */
+uint64_t vox_engine_launch_count(const vox_engine * e);
+
+/* Synchronise `stream` and fold the device status word into a status: VOX_ATTN_TIMEOUT when
+ * a kernel's bounded wait gave up.  Replaces the ggml_status returned by
+ * ggml_backend_graph_compute (src/backend.cpp:564-570).  Clears the word. */
+int vox_engine_sync_status(vox_engine * e, void * stream);
+
+/* ---------------------------------------------------------------- generic operator ----- */
+
+/* Replaces ggml_cuda_flash_attn_ext_supported (third_party/ggml/src/ggml-cuda/fattn.cu:480-482).
+ * Pure host function: 1 if vox_attn_forward accepts these operands, else 0. */
+int vox_attn_supported(const vox_attn_args * a);
+
+/* Scratch bytes vox_attn_forward needs for these operands (replaces the pool allocations of
+ * launch_fattn, third_party/ggml/src/ggml-cuda/fattn-common.cuh:808-818). */
+size_t vox_attn_workspace_bytes(const vox_attn_args * a);
+
+/* Replaces ggml_cuda_flash_attn_ext (fattn.cu:460-478) / ggml_compute_forward_flash_attn_ext
+ * (third_party/ggml/src/ggml-cpu/ops.cpp:8838-8853).  Routes by shape: n_q==1 with f16 K/V ->
+ * split-KV decode kernel; causal f16 prefill -> tcgen05 kernel (see vox_attn_prefill); anything
+ * else the contract allows (any n_q/n_kv, f32/f16/q8_0 K/V, arbitrary f16 mask, strides) ->
+ * general kernel.  Never allocates. */
+int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes,
+                     void * stream);
+
+/* Same operator with HOST tensors: copies q/k/v/mask to the device, runs, copies dst back and
+ * synchronises.  Uses engine-owned staging buffers that grow on demand. */
+int vox_attn_forward_host(vox_engine * e, const vox_attn_args * a, void * stream);
+
+/* Causal prefill without a materialised mask (the mask MiniCPMModel::create_causal_mask builds,
+ * src/minicpm.cpp:602-620, is implied: key j visible to query i iff j <= i + n_kv - n_q).
+ * q [D, n_q, H, B] f32; k, v [D, n_kv, HK, B] f16; runs on tcgen05/TMEM. */
+int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes,
+                     void * stream);
+size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a);
+
+/* ---------------------------------------------------------------- KV cache ------------- */
+
+/* Replaces MiniCPMKVCache (src/minicpm.cpp:144-271).  Storage is f16 or q8_0 instead of the
+ * reference's F32 and holds many independent streams:
+ *   f16 : K and V as [layer][stream][kv_head][pos][64] halves
+ *   q8_0: K and V each as an int8 plane [layer][stream][kv_head][pos][64] plus a scale plane
+ *         [layer][stream][kv_head][pos][2] halves — the values of block_q8_0, re-packed so
+ *         that rows are 16-byte aligned for bulk copies.                                   */
+typedef struct {
+    int32_t n_layers, n_streams, n_kv_heads, head_dim /* 64 */, max_len, type /* F16 | Q8_0 */;
+} vox_kv_config;
+
+int  vox_kv_create(vox_engine * e, const vox_kv_config * cfg, vox_kv_cache ** out); /* MiniCPMKVCache::init  */
+void vox_kv_destroy(vox_kv_cache * c);
+int  vox_kv_clear(vox_kv_cache * c, int stream_id /* -1: all */, void * stream);    /* MiniCPMKVCache::clear */
+size_t vox_kv_bytes(const vox_kv_cache * c);                                        /* ::buffer_size         */
+
+/* Replaces ggml_cpy into get_k_batch/get_v_batch views (src/minicpm.cpp:684-685, 222-236) and
+ * the concat(past, cur) that follows (:696-701): rounds f32 rows to f16 (GGML_FP32_TO_FP16) or
+ * quantises them (quantize_row_q8_0_ref, third_party/ggml/src/ggml-quants.c:199-222) in place.
+ *   k, v      [D, HK, n_tok, n_streams] f32 on the device; strides in bytes
+ *   positions device array [n_streams]: first cache row written for each stream (NULL: `pos0`)
+ * Rows land at positions[s] .. positions[s]+n_tok-1 of every stream s < n_streams. */
+int vox_kv_append(vox_kv_cache * c, int layer, int n_streams, int n_tok, const int32_t * positions, int pos0,
+                  const float * k, const float * v, size_t nb_head, size_t nb_tok, size_t nb_stream,
+                  void * stream);
+
+/* Replaces MiniCPMKVCache::get_k / get_v (src/minicpm.cpp:200-212): describes the first
+ * seq_len rows of one stream's K and V for `layer` as operator tensors [64, seq_len, HK, 1].
+ * Only an f16 cache can be viewed as a ggml tensor; a q8_0 cache returns UNSUPPORTED (use
+ * vox_attn_decode, or vox_kv_export to get block_q8_0 rows). */
+int vox_kv_view(const vox_kv_cache * c, int layer, int stream_id, int seq_len, vox_tensor * k, vox_tensor * v);
+
+/* Host <-> cache in the reference's storage formats (f16 rows, or block_q8_0 rows of 68 bytes),
+ * rows ordered [kv_head][pos].  Replaces backend.tensor_get/tensor_set on raw_k_cache()
+ * (src/minicpm.cpp:252-271).  Synchronous. */
+int vox_kv_export(const vox_kv_cache * c, int layer, int stream_id, int n_pos, void * k_host, void * v_host);
+int vox_kv_import(vox_kv_cache * c, int layer, int stream_id, int n_pos, const void * k_host, const void * v_host);
+int vox_kv_copy_from(vox_kv_cache * dst, const vox_kv_cache * src, void * stream); /* ::copy_from */
+
+/* ---------------------------------------------------------------- decode --------------- */
+
+/* One-token attention for n_streams independent streams in one launch (+ a merge launch when
+ * the KV range is split).  Replaces the n_q==1 call made by MiniCPMModel::forward_step
+ * (src/minicpm.cpp:813-846) once per stream.
+ *   q        [D, 1, H, n_streams] f32 (strides q_nb_head, q_nb_stream in bytes)
+ *   kv_len   device array [n_streams]: rows of each stream that are visible (after append)
+ *   kv_bound host-known upper bound of every kv_len (sizes the grid; <= max_len)
+ *   dst      [D, H, 1, n_streams] f32, contiguous                                           */
+typedef struct {
+    const vox_kv_cache * cache;
+    int32_t         layer;
+    int32_t         n_streams;
+    int32_t         n_heads;
+    const int32_t * kv_len;
+    int32_t         kv_bound;
+    const float *   q;
+    size_t          q_nb_head, q_nb_stream;
+    float *         dst;
+    float           scale;
+} vox_decode_args;
+
+size_t vox_attn_decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);
+int    vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace, size_t workspace_bytes,
+                       void * stream);
+
+/* ---------------------------------------------------------------- LocDiT --------------- */
+
+/* All attention of ONE CFM timestep in ONE launch: every layer, both CFG branches, every head,
+ * for n_streams patches.  Replaces the 8 ggml_flash_attn_ext nodes (18 packed tokens +
+ * block-diagonal mask) that LocDiTModel::forward_cfg_pair_projected emits per evaluation
+ * (src/locdit.cpp:401-464, 63-130) inside UnifiedCFM::solve_euler (src/unified_cfm.cpp:88-149).
+ * Bidirectional, no mask, f32 in and out.
+ *   q   [D, seq, H,  2, n_layers, n_streams] f32 contiguous
+ *   k,v [D, seq, HK, 2, n_layers, n_streams] f32 contiguous
+ *   dst [D, H, seq, 2, n_layers, n_streams] f32 contiguous                                  */
+typedef struct {
+    int32_t       n_streams, n_layers, n_heads, n_kv_heads, seq /* <= 16 */, head_dim /* 64 */;
+    const float * q;
+    const float * k;
+    const float * v;
+    float *       dst;
+    float         scale;
+} vox_locdit_args;
+
+int vox_attn_locdit_step(vox_engine * e, const vox_locdit_args * a, void * stream);
+
+/* ---------------------------------------------------------------- stream groups -------- */
+
+/* A group is the set of synthesis streams one GPU serves: a backbone cache, a residual-LM
+ * cache, per-stream lengths, and the step that VoxCPMRuntime::decode (src/voxcpm.cpp:1027-1128)
+ * performs as far as attention is concerned: per layer append + decode attention for both LM
+ * stacks, then cfm_steps LocDiT launches for the patch. */
+typedef struct {
+    int32_t n_streams;
+    int32_t base_layers, res_layers;       /* 24, 6 */
+    int32_t n_heads, n_kv_heads, head_dim; /* 16, 2, 64 */
+    int32_t max_len;
+    int32_t kv_type;                       /* VOX_TYPE_F16 | VOX_TYPE_Q8_0 */
+    int32_t locdit_layers, locdit_seq, cfm_steps; /* 8, 9, 10 */
+} vox_group_config;
+
+/* Device (or, for vox_group_step_host, pinned host) buffers of one step.
+ *   lm_q      [D, 1, H,  S, L] f32   L = base_layers + res_layers, S = n_streams
+ *   lm_k_new  [D, HK, 1, S, L] f32   rows appended at position kv_len[s] before attending
+ *   lm_v_new  same
+ *   lm_out    [D, H, 1, S, L] f32
+ *   dit_q     [D, seq, H,  2, locdit_layers, S, cfm_steps] f32;  dit_k, dit_v with HK
+ *   dit_out   [D, H, seq, 2, locdit_layers, S, cfm_steps] f32                                */
+typedef struct {
+    const float * lm_q;
+    const float * lm_k_new;
+    const float * lm_v_new;
+    float *       lm_out;
+    const float * dit_q;
+    const float * dit_k;
+    const float * dit_v;
+    float *       dit_out;
+} vox_step_buffers;
+
+int  vox_group_create(vox_engine * e, const vox_group_config * cfg, vox_group ** out);
+void vox_group_destroy(vox_group * g);
+vox_kv_cache * vox_group_cache(vox_group * g, int stack /* 0 backbone, 1 residual */);
+/* Set every stream's current length (host array [n_streams]); synchronous. */
+int vox_group_set_kv_len(vox_group * g, const int32_t * kv_len);
+int vox_group_get_kv_len(const vox_group * g, int32_t * kv_len);
+/* Fill both caches' first kv_len[s] rows of every stream with N(0,1) values from a counter-based
+ * generator seeded with `seed` (synthetic prompt state for benchmarks). */
+int vox_group_fill_synthetic(vox_group * g, uint64_t seed, void * stream);
+size_t vox_group_step_bytes(const vox_group * g, int which /* 0 lm in, 1 lm out, 2 dit in, 3 dit out */);
+
+/* One decode step on device buffers.  advance != 0 appends the new rows and grows every stream
+ * by one position; advance == 0 attends to the current rows only (append excluded, lengths
+ * fixed).  Launches: 2 per LM layer with append (+1 merge when split), 1 per CFM step. */
+int vox_group_step(vox_group * g, const vox_step_buffers * dev, int advance, void * stream);
+/* The same step from pinned HOST buffers: H2D of the inputs, the launches, D2H of the outputs,
+ * overlapped on the group's own streams; returns after the outputs have landed. */
+int vox_group_step_host(vox_group * g, const vox_step_buffers * host, int advance);
+
+/* Longest-processing-time partition of streams over GPUs by KV length (pure host function):
+ * owner[s] in [0, n_gpus) such that the per-GPU sums of kv_len are balanced. */
+int vox_partition_streams(const int32_t * kv_len, int n_streams, int n_gpus, int32_t * owner);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VOX_ATTN_H */

@@ -1,0 +1,94 @@
+"""Seeded operand sets shared by the golden-fixture generator and the parity tests.
+
+Each case names shapes in the reference's terms (n_q query rows, n_kv cache rows, H query heads,
+HK key/value heads, batch B) plus the K/V storage type and the mask the reference's callers
+would build.  ``make_inputs`` regenerates the operands from the seed, so fixtures store outputs
+only (and a digest of the inputs, to detect generator drift).
+"""
+from __future__ import annotations
+
+import hashlib
+
+import numpy as np
+
+D = 64
+
+CASES = {
+    # config 1: backbone single-token decode, f16 cache (one layer per seed)
+    "decode_kv256_f16_l0": dict(B=1, n_q=1, n_kv=256, H=16, HK=2, kv="f16", mask=None, seed=0),
+    "decode_kv256_f16_l1": dict(B=1, n_q=1, n_kv=256, H=16, HK=2, kv="f16", mask=None, seed=1),
+    # config 4: long-form decode, both cache types, ragged lengths that are no tile multiple
+    "decode_kv1024_f16": dict(B=1, n_q=1, n_kv=1024, H=16, HK=2, kv="f16", mask=None, seed=2),
+    "decode_kv2048_b2_f16": dict(B=2, n_q=1, n_kv=2048, H=16, HK=2, kv="f16", mask=None, seed=3),
+    "decode_kv777_f16": dict(B=1, n_q=1, n_kv=777, H=16, HK=2, kv="f16", mask=None, seed=4),
+    "decode_kv256_q8": dict(B=1, n_q=1, n_kv=256, H=16, HK=2, kv="q8_0", mask=None, seed=5),
+    "decode_kv1000_q8": dict(B=1, n_q=1, n_kv=1000, H=16, HK=2, kv="q8_0", mask=None, seed=6),
+    "decode_kv1_f16": dict(B=1, n_q=1, n_kv=1, H=16, HK=2, kv="f16", mask=None, seed=7),
+    # config 2: causal prefill (reference mask from create_causal_mask)
+    "prefill72_causal_f16": dict(B=1, n_q=72, n_kv=72, H=16, HK=2, kv="f16", mask="causal", seed=8, q_f16=True),
+    "prefill128_gqa4_causal_f16": dict(B=2, n_q=128, n_kv=128, H=4, HK=1, kv="f16", mask="causal", seed=9, q_f16=True),
+    # config 3: LocDiT, batch form and the reference's packed 18-token form with block-diagonal mask
+    "locdit_2x9_f32": dict(B=2, n_q=9, n_kv=9, H=16, HK=2, kv="f32", mask=None, seed=10),
+    "locdit_packed18_f32": dict(B=1, n_q=18, n_kv=18, H=16, HK=2, kv="f32", mask="cfg_pair", seed=10),
+    # LocEnc patch: 5 tokens, no mask
+    "locenc_5_f32": dict(B=1, n_q=5, n_kv=5, H=16, HK=2, kv="f32", mask=None, seed=11),
+    # contract edges exercised by ggml's own op test grid (odd sizes, random block mask, q8_0 with n_q > 1)
+    "odd_nq3_kv113_f16_mask": dict(B=1, n_q=3, n_kv=113, H=16, HK=2, kv="f16", mask="random", seed=12),
+    "odd_nq33_kv75_q8_mask": dict(B=2, n_q=33, n_kv=75, H=8, HK=2, kv="q8_0", mask="random", seed=13),
+    "masked_row_f32": dict(B=1, n_q=4, n_kv=40, H=4, HK=4, kv="f32", mask="row_masked", seed=14),
+}
+
+
+def make_mask(case, oracle):
+    kind, n_q, n_kv = case["mask"], case["n_q"], case["n_kv"]
+    if kind is None:
+        return None
+    if kind == "causal":
+        return oracle.causal_mask(np.arange(n_kv - n_q, n_kv), n_kv)[None, None]
+    if kind == "cfg_pair":
+        return oracle.cfg_pair_mask(n_q // 2)[None, None]
+    rng = np.random.default_rng(1000 + case["seed"])
+    m = np.where(rng.random((1, 1, n_q, n_kv)) < 0.3, -np.inf, 0.0).astype(np.float16)
+    m[..., 0] = 0.0  # keep at least one key visible per row
+    if kind == "row_masked":
+        m[0, 0, 1, :] = -np.inf  # one query row sees nothing: the reference returns zeros for it
+    return m
+
+
+def make_inputs(case, oracle):
+    """Returns q [B,H,n_q,64] f32, k/v in the case's storage type, mask or None, and f32 views of
+    exactly the K/V values the stored type holds."""
+    rng = np.random.default_rng(case["seed"])
+    B, n_q, n_kv, H, HK = case["B"], case["n_q"], case["n_kv"], case["H"], case["HK"]
+    q = rng.standard_normal((B, H, n_q, D)).astype(np.float32)
+    k = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    if case.get("q_f16"):
+        q = q.astype(np.float16).astype(np.float32)
+    if case["kv"] == "f16":
+        ks, vs = k.astype(np.float16), v.astype(np.float16)
+        kf, vf = ks.astype(np.float32), vs.astype(np.float32)
+    elif case["kv"] == "q8_0":
+        ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+        kf, vf = oracle.dequantize_q8_0(ks), oracle.dequantize_q8_0(vs)
+    else:
+        ks, vs, kf, vf = k, v, k, v
+    return dict(q=q, k=ks, v=vs, kf=kf, vf=vf, mask=make_mask(case, oracle))
+
+
+def digest(inp) -> str:
+    h = hashlib.sha256()
+    for name in ("q", "k", "v"):
+        h.update(np.ascontiguousarray(inp[name]).tobytes())
+    if inp["mask"] is not None:
+        h.update(np.ascontiguousarray(inp["mask"]).tobytes())
+    return h.hexdigest()[:16]
+
+
+KV_TYPE = {"f32": 0, "f16": 1, "q8_0": 8}
+
+
+def rel_err(a, b) -> float:
+    """max-abs deviation over the RMS of the expected output: the parity metric."""
+    b64 = np.asarray(b, np.float64)
+    return float(np.abs(np.asarray(a, np.float64) - b64).max() / max(np.sqrt((b64 ** 2).mean()), 1e-30))

@@ -1,0 +1,149 @@
+"""CPU tests that pin the oracle: the C restatement against fixtures generated from the
+reference's own ggml CPU backend, and against that backend itself where it is present."""
+import numpy as np
+import pytest
+
+from cases import CASES, KV_TYPE, digest, make_inputs, rel_err
+
+# tolerance of the restatement against the reference's accurate path (both f32; they differ by
+# summation order and libm vs vectorised expf only)
+GATE_TOL = 2e-5
+# the as-shipped row path keeps an fp16 accumulator for f16 V: the order of the fp16 roundings
+# differs between the scalar restatement and the reference's SIMD code
+SHIPPED_TOL = {"f16": 5e-3, "q8_0": 2e-5, "f32": 2e-5}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_oracle_matches_golden_gate(name, oracle, vo, golden):
+    case = CASES[name]
+    inp = make_inputs(case, oracle)
+    assert digest(inp) == bytes(golden[name + "/digest"]).decode(), "input generator drifted from the fixtures"
+    gate = golden[name + "/gate"]
+    kt = KV_TYPE[case["kv"]]
+    exact = oracle.attn(inp["q"], inp["k"], inp["v"], inp["mask"], kv_type=kt, path=vo.PATH_ROW_F32)
+    assert rel_err(exact, gate) < GATE_TOL
+    tiled = oracle.attn(inp["q"], inp["k"], inp["v"], inp["mask"], kv_type=kt, path=vo.PATH_TILED)
+    assert rel_err(tiled, gate) < GATE_TOL
+    f64 = oracle.attn(inp["q"], inp["k"], inp["v"], inp["mask"], kv_type=kt, path=vo.PATH_F64)
+    assert rel_err(f64, gate) < GATE_TOL
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_oracle_matches_golden_as_shipped(name, oracle, vo, golden):
+    case = CASES[name]
+    inp = make_inputs(case, oracle)
+    key = name + "/shipped"
+    shipped = golden[key] if key in golden.files else golden[name + "/gate"]
+    kt = KV_TYPE[case["kv"]]
+    # one thread in the fixture => no split-KV: the shipped path is the row loop (or the tiled one)
+    path = vo.PATH_TILED if (case["n_q"] >= 64 and case["kv"] != "q8_0") else vo.PATH_ROW
+    mine = oracle.attn(inp["q"], inp["k"], inp["v"], inp["mask"], kv_type=kt, path=path)
+    assert rel_err(mine, shipped) < SHIPPED_TOL[case["kv"]]
+
+
+def test_storage_formats_bit_exact(oracle, golden):
+    x = golden["storage/x"]
+    assert np.array_equal(oracle.quantize_q8_0(x), golden["storage/q8_0"])
+    mine = np.array([oracle.lib.voxo_fp32_to_fp16(float(t)) for t in x.ravel()], np.uint16).reshape(x.shape)
+    assert np.array_equal(mine, golden["storage/f16"])
+    assert np.array_equal(oracle.kv_store(x, 1).view(np.uint16), golden["storage/f16"])
+    assert np.array_equal(oracle.kv_store(x, 8), golden["storage/q8_0"])
+    # dequantise(quantise(x)) stays within half a quantisation step of x, plus the f16 rounding of
+    # the block scale (relative 2^-11) carried by the largest quant (127)
+    back = oracle.dequantize_q8_0(golden["storage/q8_0"])
+    step = np.abs(x).reshape(64, 2, 32).max(-1, keepdims=True) / 127.0
+    bound = step * (0.5 + 127.0 * 2.0 ** -11) * 1.001 + 1e-12
+    normal = step >= 2.0 ** -14  # below that the f16 scale itself is subnormal and coarser
+    ok = (np.abs(back.reshape(64, 2, 32) - x.reshape(64, 2, 32)) <= bound) | ~normal
+    assert bool(ok.all())
+    assert int(normal.sum()) > 60
+
+
+def test_fp16_special_values(oracle):
+    cv = oracle.lib.voxo_fp32_to_fp16
+    assert cv(0.0) == 0 and cv(-0.0) == 0x8000
+    assert cv(65504.0) == 0x7BFF and cv(65519.0) == 0x7BFF and cv(65520.0) == 0x7C00
+    assert cv(float("inf")) == 0x7C00 and cv(float("-inf")) == 0xFC00
+    assert cv(-1.0e9) == 0xFC00  # the callers' -1e9 mask value becomes -inf in f16
+    assert cv(5.960464477539063e-08) == 1 and cv(2.9e-08) == 0  # subnormal edge, ties to even
+    for h in (0, 1, 0x3FF, 0x400, 0x3C00, 0x7BFF, 0x8001, 0xFBFF):
+        assert cv(oracle.lib.voxo_fp16_to_fp32(h)) == h
+
+
+def test_masks(oracle):
+    m = oracle.causal_mask(np.arange(4, 8), 8)  # 4 new tokens after 4 cached ones
+    assert m.shape == (4, 8)
+    for r in range(4):
+        assert np.all(m[r, : r + 5] == 0) and np.all(np.isneginf(m[r, r + 5:]))
+    assert np.signbit(m[0, 0])  # step(..)*-1e9 leaves -0 where visible, as the reference's graph does
+    c = oracle.cfg_pair_mask(9)
+    assert c.shape == (18, 18)
+    assert np.all(c[:9, :9] == 0) and np.all(c[9:, 9:] == 0) and np.all(np.isneginf(c[:9, 9:])) and np.all(np.isneginf(c[9:, :9]))
+
+
+def test_fully_masked_row_is_zero(oracle, vo):
+    case = CASES["masked_row_f32"]
+    inp = make_inputs(case, oracle)
+    for path in (vo.PATH_ROW, vo.PATH_ROW_F32, vo.PATH_TILED, vo.PATH_F64):
+        out = oracle.attn(inp["q"], inp["k"], inp["v"], inp["mask"], kv_type=0, path=path)
+        assert np.all(out[0, 1] == 0.0)
+        assert np.all(np.isfinite(out))
+
+
+def test_packed_cfg_pair_equals_batch_form(oracle, vo):
+    """The reference packs cond/uncond as 18 tokens with a block-diagonal mask; the engine treats the
+    branches as a batch of two 9-token sequences.  The two forms are the same arithmetic."""
+    a = make_inputs(CASES["locdit_2x9_f32"], oracle)
+    packed_q = np.concatenate([a["q"][0], a["q"][1]], axis=1)[None]
+    packed_k = np.concatenate([a["k"][0], a["k"][1]], axis=1)[None]
+    packed_v = np.concatenate([a["v"][0], a["v"][1]], axis=1)[None]
+    mask = oracle.cfg_pair_mask(9)[None, None]
+    batch = oracle.attn(a["q"], a["k"], a["v"], None, kv_type=0, path=vo.PATH_ROW)
+    packed = oracle.attn(packed_q, packed_k, packed_v, mask, kv_type=0, path=vo.PATH_ROW)
+    assert np.array_equal(packed[0, :9], batch[0]) and np.array_equal(packed[0, 9:], batch[1])
+
+
+def test_split_kv_merge_matches_single_pass(oracle, vo):
+    inp = make_inputs(CASES["decode_kv1024_f16"], oracle)
+    one = oracle.attn(inp["q"], inp["kf"], inp["vf"], None, kv_type=0, path=vo.PATH_ROW)
+    for n_chunks in (2, 7, 8, 64):
+        split = oracle.attn(inp["q"], inp["kf"], inp["vf"], None, kv_type=0, path=vo.PATH_SPLIT_KV, n_chunks=n_chunks)
+        assert rel_err(split, one) < 1e-5
+
+
+def test_oracle_rejects_what_the_reference_rejects(oracle):
+    q = np.zeros((1, 3, 1, 64), np.float32)
+    k = np.zeros((1, 2, 8, 64), np.float32)
+    with pytest.raises(ValueError):  # 3 query heads cannot broadcast over 2 kv heads
+        oracle.attn(q, k, k, kv_type=0)
+
+
+# ------------------------------------------------------------------ live comparison with the reference build
+
+@pytest.mark.parametrize("name", ["decode_kv256_f16_l0", "decode_kv1000_q8", "prefill72_causal_f16", "locdit_2x9_f32",
+                                  "odd_nq33_kv75_q8_mask"])
+def test_reference_build_reproduces_fixtures(name, ref, oracle, golden):
+    case = CASES[name]
+    inp = make_inputs(case, oracle)
+    gate = ref.attn(inp["q"], inp["kf"], inp["vf"], inp["mask"], kv_type=0, n_threads=1)
+    # same library, possibly another ISA variant than the one that wrote the fixture
+    assert rel_err(gate, golden[name + "/gate"]) < 1e-5
+
+
+def test_reference_tiled_path_agrees_with_f32_typed_path(ref, oracle):
+    """Gate A of the parity plan: f16 K/V with Q replicated to 64 rows runs the reference's tiled f32
+    path; its row 0 agrees with the F32-typed run (gate B') far inside the parity tolerance."""
+    inp = make_inputs(CASES["decode_kv1024_f16"], oracle)
+    q64 = np.repeat(inp["q"], 64, axis=2)
+    tiled = ref.attn(q64, inp["k"], inp["v"], None, kv_type=1, n_threads=2)[:, :1]
+    typed = ref.attn(inp["q"], inp["kf"], inp["vf"], None, kv_type=0, n_threads=1)
+    assert rel_err(tiled, typed) < 2e-5
+
+
+def test_reference_quantiser_matches_oracle(ref, oracle):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((257, 64)).astype(np.float32) * 3.0
+    assert np.array_equal(ref.quantize_q8_0(x), oracle.quantize_q8_0(x))
+    assert np.array_equal(ref.fp32_to_fp16(x).view(np.uint16), oracle.kv_store(x, 1).view(np.uint16))
+    blocks = oracle.quantize_q8_0(x)
+    assert np.array_equal(ref.dequantize_q8_0(blocks), oracle.dequantize_q8_0(blocks))

@@ -1,0 +1,177 @@
+// Shared declarations of the attention engine: status handling, the engine object, and
+// thin wrappers over the sm_100a PTX the kernels use (mbarrier, bulk-tensor copies,
+// ldmatrix, mma).  Every device-side wait in this code base goes through mbar_wait_bounded,
+// which gives up after a fixed number of polls and reports instead of spinning forever.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "vox_attn.h"
+
+namespace vox {
+
+// ------------------------------------------------------------------ host side
+
+void set_error(const char * fmt, ...);
+
+#define VOX_CUDA_TRY(expr)                                                                   \
+    do {                                                                                     \
+        cudaError_t err__ = (expr);                                                          \
+        if (err__ != cudaSuccess) {                                                          \
+            ::vox::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__, __LINE__); \
+            return VOX_ATTN_CUDA_ERROR;                                                      \
+        }                                                                                    \
+    } while (0)
+
+#define VOX_REQUIRE(cond, status, ...)          \
+    do {                                        \
+        if (!(cond)) {                          \
+            ::vox::set_error(__VA_ARGS__);      \
+            return (status);                    \
+        }                                       \
+    } while (0)
+
+constexpr int kHeadDim = 64;
+
+// bits of the device status word
+enum : int { kStatusTimeout = 1, kStatusBadState = 2 };
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace vox
+
+struct vox_engine {
+    int               device       = 0;
+    int               sm_count     = 0;
+    int *             status_host  = nullptr;  // pinned, mapped; kernels write through status_dev
+    int *             status_dev   = nullptr;
+    uint64_t          launches     = 0;
+    vox::encode_tiled_fn encode    = nullptr;
+    // staging for the *_host entry points
+    void *            stage_dev    = nullptr;
+    size_t            stage_bytes  = 0;
+    void *            stage_ws     = nullptr;
+    size_t            stage_ws_bytes = 0;
+};
+
+namespace vox {
+
+// 5-D tiled tensor map: dims/box in elements (dim 0 fastest), strides[i] = byte stride of dim i+1.
+int make_tensor_map(const vox_engine * e, CUtensorMap * out, void * base, CUtensorMapDataType dt, const uint64_t dims[5],
+                    const uint64_t strides[4], const uint32_t box[5], CUtensorMapSwizzle swizzle);
+
+inline int check_launch(vox_engine * e, const char * what) {
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        set_error("launch of %s failed: %s", what, cudaGetErrorString(err));
+        return VOX_ATTN_CUDA_ERROR;
+    }
+    e->launches += 1;
+    return VOX_ATTN_OK;
+}
+
+// ------------------------------------------------------------------ device side
+
+#ifdef __CUDACC__
+
+constexpr uint32_t kSpinLimit = 1u << 22;  // polls before a wait gives up (each poll may sleep)
+
+__device__ __forceinline__ uint32_t smem_u32(const void * p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Returns false when the phase did not complete within kSpinLimit polls.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap * map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap * map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t & r0, uint32_t & r1, uint32_t & r2, uint32_t & r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t & r0, uint32_t & r1, uint32_t & r2,
+                                                  uint32_t & r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// x ~= hi + lo with hi, lo representable in f16: carries ~22 bits of x through f16 MMAs
+__device__ __forceinline__ void split_hi_lo(float x, float & hi, float & lo) {
+    hi = __half2float(__float2half_rn(x));
+    lo = x - hi;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
+#endif  // __CUDACC__
+
+}  // namespace vox

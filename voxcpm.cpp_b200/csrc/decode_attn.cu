@@ -1,0 +1,378 @@
+// Split-KV decode attention (one query token per stream) for sm_100a.
+//
+// Replaces, for the n_q == 1 call of MiniCPMModel::forward_step (src/minicpm.cpp:813-846 ->
+// :708-710), what ggml's CPU backend does in ggml_compute_forward_flash_attn_ext_f16_one_chunk
+// plus ggml_flash_attn_ext_reduce_partials (third_party/ggml/src/ggml-cpu/ops.cpp:8109-8345,
+// 8637-8705) and what ggml-cuda does in flash_attn_ext_vec + flash_attn_combine_results
+// (third_party/ggml/src/ggml-cuda/fattn-vec.cuh:19-507, fattn-common.cuh:728-779).
+//
+// Design (HBM-bound kernel; the cache is read exactly once):
+//   grid  = (kv chunks, kv heads, streams); one CTA owns `chunk` consecutive cache rows of one
+//           kv head of one stream and serves all GQA query heads that share it, so each K/V
+//           byte is fetched once for the whole group;
+//   copy  = a producer warp streams 64-row K and V tiles into a 4-stage shared-memory ring with
+//           bulk-tensor copies (cp.async.bulk.tensor, 128-byte swizzle) signalled on mbarriers;
+//   math  = four consumer warps, 16 rows each.  Q (pre-scaled by scale*log2 e) is split as
+//           hi + lo in f16 and the two parts occupy rows 0-7 and 8-15 of the m16n8k16 A operand,
+//           so one MMA yields the hi and lo products and their sum carries ~22 bits of Q.  The
+//           same trick carries the softmax weights P through the P.V MMA.  Accumulation is f32;
+//   merge = warps are merged through shared memory; when the KV range was split across CTAs the
+//           (max, sum, acc[64]) partials go to the workspace and decode_merge_kernel folds them.
+// q8_0 K/V (int8 plane + scale plane) is dequantised in registers: int8 -> f16 is exact, the
+// per-block scales are applied in f32 to the per-block score accumulators (K) and folded into
+// the softmax weights (V), so Q is never quantised.
+#include "kv_cache.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+
+using namespace vox;
+
+namespace {
+
+constexpr int kStages        = 4;
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads       = (kConsumerWarps + 1) * 32;
+constexpr int kPartialStride = 66;  // max, sum, acc[64]
+
+struct DecodeParams {
+    const uint8_t * q;
+    size_t          q_nb_head, q_nb_stream;
+    const int32_t * kv_len;
+    int             kv_len_const;
+    float *         partial;
+    float *         dst;
+    int             n_heads, gqa, chunk, n_chunks, layer, max_len;
+    float           scale_log2;
+    int *           status;
+};
+
+__device__ __forceinline__ int stream_len(const DecodeParams & p, int stream) {
+    int len = p.kv_len ? p.kv_len[stream] : p.kv_len_const;
+    return max(0, min(len, p.max_len));
+}
+
+// ---------------------------------------------------------------------------------------------
+// f16 K/V
+// ---------------------------------------------------------------------------------------------
+constexpr int kStageBytesF16 = 2 * kKvTile * 128;  // K tile + V tile
+
+__global__ void __launch_bounds__(kThreads, 3)
+decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                  const DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[2 * kStages];
+    __shared__ int      abort_flag;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const int chunk_id = blockIdx.x, kvh = blockIdx.y, stream = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int len = stream_len(p, stream);
+    const int c0  = chunk_id * p.chunk;
+    if (c0 >= len) {
+        // nothing visible in this chunk; a stream with no visible rows at all yields zeros
+        if (len == 0 && chunk_id == 0 && warp < kConsumerWarps) {
+            for (int i = tid; i < p.gqa * kHeadDim; i += kConsumerWarps * 32)
+                p.dst[((size_t) stream * p.n_heads + (size_t) kvh * p.gqa) * kHeadDim + i] = 0.0f;
+        }
+        return;
+    }
+    const int c1      = min(c0 + p.chunk, len);
+    const int n_tiles = (c1 - c0 + kKvTile - 1) / kKvTile;
+
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]);
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kConsumerWarps);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i % kStages;
+                if (i >= kStages && !mbar_wait_bounded(empty0 + 8 * s, ((i / kStages) - 1) & 1)) {
+                    atomicOr(p.status, kStatusTimeout);
+                    atomicExch(&abort_flag, 1);
+                    break;
+                }
+                if (*reinterpret_cast<volatile int *>(&abort_flag)) break;
+                const uint32_t kb = smem_base + s * kStageBytesF16;
+                mbar_expect_tx(full0 + 8 * s, kStageBytesF16);
+                tma_load_5d(kb, &map_k, full0 + 8 * s, 0, c0 + i * kKvTile, kvh, stream, p.layer);
+                tma_load_5d(kb + kKvTile * 128, &map_v, full0 + 8 * s, 0, c0 + i * kKvTile, kvh, stream, p.layer);
+                issued = i + 1;
+            }
+            if (*reinterpret_cast<volatile int *>(&abort_flag)) {
+                // consumers gave up: let the copies already issued land before the CTA retires
+                for (int i = max(0, issued - kStages); i < issued; ++i)
+                    mbar_wait_bounded(full0 + 8 * (i % kStages), (i / kStages) & 1);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+
+    // Q fragments: rows 0-7 = hi part of the 8 heads of this group, rows 8-15 = lo part
+    uint32_t qa[4][4];
+    {
+        const int     head = kvh * p.gqa + min(g, p.gqa - 1);
+        const float * qrow = reinterpret_cast<const float *>(p.q + (size_t) stream * p.q_nb_stream + (size_t) head * p.q_nb_head);
+        const float   live = g < p.gqa ? p.scale_log2 : 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float2 x = *reinterpret_cast<const float2 *>(qrow + 16 * c + 2 * t);
+            const float2 y = *reinterpret_cast<const float2 *>(qrow + 16 * c + 8 + 2 * t);
+            float h0, l0, h1, l1, h2, l2, h3, l3;
+            split_hi_lo(x.x * live, h0, l0);
+            split_hi_lo(x.y * live, h1, l1);
+            split_hi_lo(y.x * live, h2, l2);
+            split_hi_lo(y.y * live, h3, l3);
+            qa[c][0] = pack_half2(h0, h1);
+            qa[c][1] = pack_half2(l0, l1);
+            qa[c][2] = pack_half2(h2, h3);
+            qa[c][3] = pack_half2(l2, l3);
+        }
+    }
+
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m = -INFINITY, l = 0.0f;
+    bool  ok = true;
+
+    // per-lane ldmatrix row/chunk selectors (see the fragment layouts of mma.m16n8k16)
+    const int k_row = 16 * warp + ((lane >> 4) << 3) + (lane & 7), k_chk = (lane >> 3) & 1;
+    const int v_row = 16 * warp + (((lane >> 3) & 1) << 3) + (lane & 7), v_chk = lane >> 4;
+
+    for (int i = 0; i < n_tiles; ++i) {
+        const int s = i % kStages;
+        if (!mbar_wait_bounded(full0 + 8 * s, (i / kStages) & 1)) {
+            atomicOr(p.status, kStatusTimeout);
+            atomicExch(&abort_flag, 1);
+            ok = false;
+            break;
+        }
+        const int p0 = c0 + i * kKvTile + 16 * warp;
+        if (p0 < c1) {
+            const uint32_t kb = smem_base + s * kStageBytesF16, vb = kb + kKvTile * 128;
+            float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(kb + k_row * 128 + (((2 * c + k_chk) ^ (k_row & 7)) << 4), b0, b1, b2, b3);
+                mma_16816(sc[0], qa[c], b0, b1);
+                mma_16816(sc[1], qa[c], b2, b3);
+            }
+            float sv[2][2];
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int pos = p0 + 8 * j + 2 * t + e;
+                    sv[j][e]      = pos < c1 ? sc[j][e] + sc[j][e + 2] : -INFINITY;
+                    tmax          = fmaxf(tmax, sv[j][e]);
+                }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float m_new = fmaxf(m, tmax);
+            const float alpha = m_new == -INFINITY ? 1.0f : exp2f(m - m_new);
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+            m                 = m_new;
+            uint32_t pa[4];
+            float    psum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float h0, l0, h1, l1;
+                split_hi_lo(exp2f(sv[j][0] - m_use), h0, l0);
+                split_hi_lo(exp2f(sv[j][1] - m_use), h1, l1);
+                pa[2 * j]     = pack_half2(h0, h1);
+                pa[2 * j + 1] = pack_half2(l0, l1);
+                psum += (h0 + l0) + (h1 + l1);
+            }
+            l = l * alpha + psum;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                o[n][0] *= alpha; o[n][1] *= alpha; o[n][2] *= alpha; o[n][3] *= alpha;
+            }
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(vb + v_row * 128 + (((2 * n2 + v_chk) ^ (v_row & 7)) << 4), b0, b1, b2, b3);
+                mma_16816(o[2 * n2], pa, b0, b1);
+                mma_16816(o[2 * n2 + 1], pa, b2, b3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+
+    // merge the four warps through shared memory (re-using the first stage once all tiles are consumed)
+    named_bar_sync(1, kConsumerWarps * 32);
+    if (!ok || *reinterpret_cast<volatile int *>(&abort_flag)) return;
+    float * scratch = reinterpret_cast<float *>(smem_gen);
+    {
+        float * mine = scratch + (warp * 8 + g) * kPartialStride;
+        if (t == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            mine[2 + 8 * n + 2 * t]     = o[n][0] + o[n][2];
+            mine[2 + 8 * n + 2 * t + 1] = o[n][1] + o[n][3];
+        }
+    }
+    named_bar_sync(1, kConsumerWarps * 32);
+    {
+        const int hh = tid >> 4, d0 = (tid & 15) * 4;  // 8 heads x 16 threads x 4 values
+        if (hh < p.gqa) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, scratch[(w * 8 + hh) * kPartialStride]);
+            float L = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                const float * src = scratch + (w * 8 + hh) * kPartialStride;
+                const float   f   = src[0] == -INFINITY ? 0.0f : exp2f(src[0] - M);
+                L += src[1] * f;
+#pragma unroll
+                for (int d = 0; d < 4; ++d) acc[d] += src[2 + d0 + d] * f;
+            }
+            const int head = kvh * p.gqa + hh;
+            if (p.n_chunks == 1) {
+                const float inv = L > 0.0f ? 1.0f / L : 0.0f;  // nothing visible -> zeros, as the reference
+                float4      r   = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+                *reinterpret_cast<float4 *>(p.dst + ((size_t) stream * p.n_heads + head) * kHeadDim + d0) = r;
+            } else {
+                float * dstp = p.partial + (((size_t) stream * p.n_heads + head) * p.n_chunks + chunk_id) * kPartialStride;
+                if ((tid & 15) == 0) { dstp[0] = M; dstp[1] = L; }
+#pragma unroll
+                for (int d = 0; d < 4; ++d) dstp[2 + d0 + d] = acc[d];
+            }
+        }
+    }
+}
+
+// Second pass of split-KV: fold the per-chunk (max, sum, acc) partials of one (stream, head).
+__global__ void __launch_bounds__(64) decode_merge_kernel(const DecodeParams p) {
+    const int head = blockIdx.x, stream = blockIdx.y, d = threadIdx.x;
+    const int len     = stream_len(p, stream);
+    const int n_valid = min(p.n_chunks, (len + p.chunk - 1) / p.chunk);
+    const float * src = p.partial + ((size_t) stream * p.n_heads + head) * p.n_chunks * kPartialStride;
+    float M = -INFINITY;
+    for (int c = 0; c < n_valid; ++c) M = fmaxf(M, src[c * kPartialStride]);
+    float L = 0.0f, acc = 0.0f;
+    for (int c = 0; c < n_valid; ++c) {
+        const float mc = src[c * kPartialStride];
+        const float f  = mc == -INFINITY ? 0.0f : exp2f(mc - M);
+        L += src[c * kPartialStride + 1] * f;
+        acc += src[c * kPartialStride + 2 + d] * f;
+    }
+    p.dst[((size_t) stream * p.n_heads + head) * kHeadDim + d] = L > 0.0f ? acc / L : 0.0f;
+}
+
+}  // namespace
+
+namespace vox {
+
+// Rows per CTA and CTAs per (stream, kv head): aims at several waves of 3 CTAs per SM so that the
+// ragged tail of a launch stays short, with chunks of at least one 64-row tile.
+void decode_plan(int n_streams, int n_kv_heads, int kv_bound, int * chunk, int * n_chunks) {
+    static const int forced = [] {
+        const char * s = getenv("VOX_DECODE_CHUNK");
+        return s ? atoi(s) : 0;
+    }();
+    const long long rows   = (long long) std::max(kv_bound, 1) * n_streams * n_kv_heads;
+    const long long target = 148LL * 3 * 6;
+    long long c = (rows + target - 1) / target;
+    c = ((c + kKvTile - 1) / kKvTile) * kKvTile;
+    c = std::max<long long>(4 * kKvTile, std::min<long long>(c, 512));  // short caches: one CTA, no merge launch
+    if (forced >= kKvTile) c = (forced / kKvTile) * kKvTile;
+    *chunk    = (int) c;
+    *n_chunks = std::max(1, (int) ((std::max(kv_bound, 1) + c - 1) / c));
+}
+
+size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound) {
+    int chunk, n_chunks;
+    decode_plan(n_streams, n_kv_heads, kv_bound, &chunk, &n_chunks);
+    return n_chunks <= 1 ? 0 : (size_t) n_streams * n_heads * n_chunks * kPartialStride * sizeof(float);
+}
+
+// K/V described by tensor maps (a cache layer, or caller tensors); q/dst/lengths by pointers.
+int launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorMap & map_v, int layer, int max_len,
+                      int n_streams, int n_heads, int n_kv_heads, const int32_t * kv_len, int kv_len_const, int kv_bound,
+                      const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst, float scale, void * workspace,
+                      size_t workspace_bytes, cudaStream_t stream) {
+    static bool attr_done = false;
+    const int   smem      = kStages * kStageBytesF16 + 1024;
+    if (!attr_done) {
+        VOX_CUDA_TRY(cudaFuncSetAttribute(decode_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done = true;
+    }
+    DecodeParams p;
+    p.q = reinterpret_cast<const uint8_t *>(q);
+    p.q_nb_head = q_nb_head; p.q_nb_stream = q_nb_stream;
+    p.kv_len = kv_len; p.kv_len_const = kv_len_const;
+    p.dst = dst; p.n_heads = n_heads; p.gqa = n_heads / n_kv_heads; p.layer = layer; p.max_len = max_len;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = e->status_dev;
+    decode_plan(n_streams, n_kv_heads, kv_bound, &p.chunk, &p.n_chunks);
+    const size_t need = decode_workspace_bytes(n_streams, n_heads, n_kv_heads, kv_bound);
+    VOX_REQUIRE(workspace_bytes >= need && (need == 0 || workspace != nullptr), VOX_ATTN_WORKSPACE_TOO_SMALL,
+                "decode needs %zu workspace bytes, got %zu", need, workspace_bytes);
+    p.partial = static_cast<float *>(workspace);
+    dim3 grid(p.n_chunks, n_kv_heads, n_streams);
+    decode_f16_kernel<<<grid, kThreads, smem, stream>>>(map_k, map_v, p);
+    int rc = check_launch(e, "decode_f16_kernel");
+    if (rc != VOX_ATTN_OK) return rc;
+    if (p.n_chunks > 1) {
+        decode_merge_kernel<<<dim3(n_heads, n_streams), 64, 0, stream>>>(p);
+        rc = check_launch(e, "decode_merge_kernel");
+    }
+    return rc;
+}
+
+}  // namespace vox
+
+extern "C" {
+
+size_t vox_attn_decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound) {
+    if (n_streams <= 0 || n_heads <= 0 || n_kv_heads <= 0) return 0;
+    return decode_workspace_bytes(n_streams, n_heads, n_kv_heads, kv_bound);
+}
+
+int vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace, size_t workspace_bytes, void * stream) {
+    VOX_REQUIRE(e && a && a->cache && a->q && a->dst, VOX_ATTN_INVALID_ARGUMENT, "vox_attn_decode: null argument");
+    const vox_kv_cache * c = a->cache;
+    VOX_REQUIRE(c->e == e, VOX_ATTN_INVALID_ARGUMENT, "cache belongs to another engine");
+    VOX_REQUIRE(a->layer >= 0 && a->layer < c->cfg.n_layers, VOX_ATTN_INVALID_ARGUMENT, "layer %d out of range", a->layer);
+    VOX_REQUIRE(a->n_streams > 0 && a->n_streams <= c->cfg.n_streams, VOX_ATTN_INVALID_ARGUMENT,
+                "n_streams %d out of range (cache holds %d)", a->n_streams, c->cfg.n_streams);
+    VOX_REQUIRE(a->n_heads > 0 && a->n_heads % c->cfg.n_kv_heads == 0, VOX_ATTN_INVALID_ARGUMENT,
+                "n_heads %d is not a multiple of n_kv_heads %d", a->n_heads, c->cfg.n_kv_heads);
+    VOX_REQUIRE(a->n_heads / c->cfg.n_kv_heads <= 8, VOX_ATTN_UNSUPPORTED, "GQA ratio above 8 is not supported");
+    VOX_REQUIRE(a->kv_len != nullptr, VOX_ATTN_INVALID_ARGUMENT, "kv_len is null");
+    VOX_REQUIRE(a->kv_bound >= 0 && a->kv_bound <= c->cfg.max_len, VOX_ATTN_INVALID_ARGUMENT,
+                "kv_bound %d exceeds the cache capacity %d", a->kv_bound, c->cfg.max_len);
+    VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->q) & 7) == 0 && a->q_nb_head % 8 == 0 && a->q_nb_stream % 8 == 0,
+                VOX_ATTN_INVALID_ARGUMENT, "q rows must be 8-byte aligned");
+    VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->dst) & 15) == 0, VOX_ATTN_INVALID_ARGUMENT, "dst must be 16-byte aligned");
+    VOX_REQUIRE(c->cfg.type == VOX_TYPE_F16, VOX_ATTN_UNSUPPORTED, "q8_0 decode is not built yet");
+    return launch_decode_f16(e, c->map_k, c->map_v, a->layer, c->cfg.max_len, a->n_streams, a->n_heads, c->cfg.n_kv_heads,
+                             a->kv_len, 0, a->kv_bound, a->q, a->q_nb_head, a->q_nb_stream, a->dst, a->scale, workspace,
+                             workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,129 @@
+// Engine object: device binding, status word, launch counter, tensor-map encoder.
+// Plays the part that VoxCPMBackend's CUDA initialisation (src/backend.cpp:146-205) and
+// ggml-cuda's per-context state play for the reference's attention path.
+#include "common.cuh"
+
+#include <cstring>
+#include <new>
+
+namespace vox {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char * fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int make_tensor_map(const vox_engine * e, CUtensorMap * out, void * base, CUtensorMapDataType dt, const uint64_t dims[5],
+                    const uint64_t strides[4], const uint32_t box[5], CUtensorMapSwizzle swizzle) {
+    VOX_REQUIRE(e && e->encode, VOX_ATTN_CUDA_ERROR, "tensor-map encoder unavailable");
+    VOX_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, VOX_ATTN_INVALID_ARGUMENT,
+                "base address must be 16-byte aligned for bulk-tensor copies");
+    cuuint64_t d[5], s[4];
+    cuuint32_t b[5], estr[5] = {1, 1, 1, 1, 1};
+    for (int i = 0; i < 5; ++i) { d[i] = dims[i]; b[i] = box[i]; }
+    for (int i = 0; i < 4; ++i) {
+        VOX_REQUIRE(strides[i] % 16 == 0, VOX_ATTN_INVALID_ARGUMENT,
+                    "stride %d (%llu bytes) must be a multiple of 16 bytes for bulk-tensor copies", i + 1,
+                    (unsigned long long) strides[i]);
+        s[i] = strides[i];
+    }
+    CUresult rc = e->encode(out, dt, 5, base, d, s, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    VOX_REQUIRE(rc == CUDA_SUCCESS, VOX_ATTN_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code %d", (int) rc);
+    return VOX_ATTN_OK;
+}
+
+}  // namespace vox
+
+using namespace vox;
+
+extern "C" {
+
+const char * vox_attn_last_error_string(void) { return g_error; }
+
+const char * vox_attn_status_string(int status) {
+    switch (status) {
+        case VOX_ATTN_OK: return "ok";
+        case VOX_ATTN_INVALID_ARGUMENT: return "invalid argument";
+        case VOX_ATTN_UNSUPPORTED: return "unsupported";
+        case VOX_ATTN_WORKSPACE_TOO_SMALL: return "workspace too small";
+        case VOX_ATTN_CUDA_ERROR: return "CUDA error";
+        case VOX_ATTN_TIMEOUT: return "device-side wait timed out";
+        case VOX_ATTN_OUT_OF_MEMORY: return "out of memory";
+        default: return "unknown status";
+    }
+}
+
+int vox_engine_create(int device, vox_engine ** out) {
+    VOX_REQUIRE(out != nullptr, VOX_ATTN_INVALID_ARGUMENT, "vox_engine_create: out is null");
+    *out = nullptr;
+    int n_dev = 0;
+    VOX_CUDA_TRY(cudaGetDeviceCount(&n_dev));
+    VOX_REQUIRE(device >= 0 && device < n_dev, VOX_ATTN_INVALID_ARGUMENT, "device %d out of range (%d devices)", device,
+                n_dev);
+    cudaDeviceProp prop;
+    VOX_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    VOX_REQUIRE(prop.major == 10, VOX_ATTN_UNSUPPORTED,
+                "device %d is compute capability %d.%d; this engine is built for sm_100a only", device, prop.major,
+                prop.minor);
+    VOX_CUDA_TRY(cudaSetDevice(device));
+
+    vox_engine * e = new (std::nothrow) vox_engine();
+    VOX_REQUIRE(e != nullptr, VOX_ATTN_OUT_OF_MEMORY, "out of host memory");
+    e->device   = device;
+    e->sm_count = prop.multiProcessorCount;
+
+    cudaError_t err = cudaHostAlloc(reinterpret_cast<void **>(&e->status_host), sizeof(int) * 4, cudaHostAllocMapped);
+    if (err == cudaSuccess) {
+        memset(e->status_host, 0, sizeof(int) * 4);
+        err = cudaHostGetDevicePointer(reinterpret_cast<void **>(&e->status_dev), e->status_host, 0);
+    }
+    if (err != cudaSuccess) {
+        set_error("status word allocation failed: %s", cudaGetErrorString(err));
+        delete e;
+        return VOX_ATTN_CUDA_ERROR;
+    }
+
+    void *                          fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (err != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+        set_error("cuTensorMapEncodeTiled not available from the driver");
+        cudaFreeHost(e->status_host);
+        delete e;
+        return VOX_ATTN_CUDA_ERROR;
+    }
+    e->encode = reinterpret_cast<encode_tiled_fn>(fn);
+    *out      = e;
+    return VOX_ATTN_OK;
+}
+
+void vox_engine_destroy(vox_engine * e) {
+    if (!e) return;
+    cudaSetDevice(e->device);
+    if (e->stage_dev) cudaFree(e->stage_dev);
+    if (e->stage_ws) cudaFree(e->stage_ws);
+    if (e->status_host) cudaFreeHost(e->status_host);
+    delete e;
+}
+
+uint64_t vox_engine_launch_count(const vox_engine * e) { return e ? e->launches : 0; }
+
+int vox_engine_sync_status(vox_engine * e, void * stream) {
+    VOX_REQUIRE(e != nullptr, VOX_ATTN_INVALID_ARGUMENT, "engine is null");
+    VOX_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    const int word = *reinterpret_cast<volatile int *>(e->status_host);
+    if (word != 0) {
+        *reinterpret_cast<volatile int *>(e->status_host) = 0;
+        set_error("device status word 0x%x: %s", word,
+                  (word & kStatusTimeout) ? "a bounded wait on a copy barrier ran out" : "kernel reported bad state");
+        return VOX_ATTN_TIMEOUT;
+    }
+    return VOX_ATTN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,44 @@
+// KV cache object shared by the cache, decode and stream-group translation units.
+#pragma once
+
+#include "common.cuh"
+
+constexpr int kKvTile = 64;  // cache rows moved per bulk-tensor copy
+
+struct vox_kv_cache {
+    vox_engine *  e = nullptr;
+    vox_kv_config cfg{};
+    // data planes: f16 rows (128 B) or int8 rows (64 B); [layer][stream][kv_head][pos][64]
+    uint8_t * k_data = nullptr;
+    uint8_t * v_data = nullptr;
+    size_t    nb_pos = 0, nb_head = 0, nb_stream = 0, nb_layer = 0;
+    // q8_0 only, scale planes: two halves per row; [layer][stream][kv_head][pos][2]
+    uint8_t * k_scale = nullptr;
+    uint8_t * v_scale = nullptr;
+    size_t    sb_pos = 0, sb_head = 0, sb_stream = 0, sb_layer = 0;
+    size_t    bytes  = 0;
+    // bulk-tensor descriptors, box = kKvTile rows
+    CUtensorMap map_k, map_v;    // data planes, 5-D (64, pos, head, stream, layer)
+    CUtensorMap map_ks, map_vs;  // scale planes, 5-D (2*pos halves, 1, head, stream, layer)
+};
+
+namespace vox {
+
+// Deterministic N(0,1) value number `idx` of stream `seed`: counter-based, so that any kernel
+// (cache fill, benchmarks) can regenerate the same synthetic state without storing it.
+__host__ __device__ inline float synth_normal(uint64_t seed, uint64_t idx) {
+    uint64_t z = seed * 0x9E3779B97F4A7C15ull + idx * 0xD1B54A32D192ED03ull + 0x632BE59BD9B4E019ull;
+    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull;
+    z ^= z >> 27; z *= 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    const uint32_t a = static_cast<uint32_t>(z), b = static_cast<uint32_t>(z >> 32);
+    const float u1 = (static_cast<float>(a >> 8) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
+    const float u2 = static_cast<float>(b >> 8) * (1.0f / 16777216.0f);           // [0, 1)
+#ifdef __CUDA_ARCH__
+    return sqrtf(-2.0f * __logf(u1)) * __cosf(6.2831853f * u2);
+#else
+    return sqrtf(-2.0f * logf(u1)) * cosf(6.2831853f * u2);
+#endif
+}
+
+}  // namespace vox

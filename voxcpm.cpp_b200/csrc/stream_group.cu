@@ -1,0 +1,333 @@
+// Stream groups: the synthesis streams one GPU serves and the attention part of one decode
+// step for all of them at once.
+//
+// Replaces, for attention, the per-stream loop of VoxCPMRuntime::decode
+// (src/voxcpm.cpp:1027-1128): there each stream rebuilds a ggml graph per position
+// (:485-544), runs 24 + 6 single-token attention nodes and one unrolled CFM solve with
+// 8 attention nodes per evaluation.  Here every LM layer is one append launch plus one decode
+// launch (plus a merge) for ALL streams of the group, and every CFM timestep is one launch.
+// Streams never exchange data, so several GPUs each run their own group with no collective;
+// vox_partition_streams assigns streams to GPUs.
+#include "kv_cache.cuh"
+
+#include <algorithm>
+#include <cstring>
+#include <new>
+#include <numeric>
+#include <vector>
+
+using namespace vox;
+
+namespace vox {
+int kv_fill_synthetic(vox_kv_cache * c, const int32_t * kv_len_dev, uint64_t seed, cudaStream_t stream);
+}
+
+struct vox_group {
+    vox_engine *     e = nullptr;
+    vox_group_config cfg{};
+    vox_kv_cache *   cache[2]  = {nullptr, nullptr};  // backbone, residual LM
+    int32_t *        kv_len_dev = nullptr;            // [n_streams] rows visible to attention
+    int32_t *        kv_pos_dev = nullptr;            // [n_streams] row the next append writes
+    std::vector<int32_t> kv_len_host;
+    int              kv_bound  = 0;
+    void *           workspace = nullptr;
+    size_t           workspace_bytes = 0;
+    // vox_group_step_host: device mirrors of the step buffers, two copy streams, events
+    uint8_t *        dev_buf   = nullptr;
+    size_t           dev_off[8] = {0};
+    cudaStream_t     st_compute = nullptr, st_copy = nullptr;
+    cudaEvent_t      ev_lm_in = nullptr, ev_dit_in[16] = {nullptr}, ev_lm_done = nullptr, ev_dit_done[16] = {nullptr};
+};
+
+namespace {
+
+__global__ void add_scalar_kernel(int32_t * a, int n, int delta, int cap) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = min(a[i] + delta, cap);
+}
+
+size_t lm_layers(const vox_group_config & c) { return (size_t) c.base_layers + c.res_layers; }
+
+size_t step_bytes(const vox_group_config & c, int which) {
+    const size_t S = c.n_streams, D = c.head_dim;
+    switch (which) {
+        case 0: return lm_layers(c) * S * (c.n_heads + 2 * (size_t) c.n_kv_heads) * D * 4;            // q + k_new + v_new
+        case 1: return lm_layers(c) * S * c.n_heads * D * 4;                                            // lm_out
+        case 2: return (size_t) c.cfm_steps * S * c.locdit_layers * 2 * c.locdit_seq * (c.n_heads + 2 * (size_t) c.n_kv_heads) * D * 4;
+        case 3: return (size_t) c.cfm_steps * S * c.locdit_layers * 2 * c.locdit_seq * c.n_heads * D * 4;
+        default: return 0;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int vox_group_create(vox_engine * e, const vox_group_config * cfg, vox_group ** out) {
+    VOX_REQUIRE(e && cfg && out, VOX_ATTN_INVALID_ARGUMENT, "vox_group_create: null argument");
+    *out = nullptr;
+    VOX_REQUIRE(cfg->n_streams > 0 && cfg->base_layers >= 0 && cfg->res_layers >= 0 && cfg->base_layers + cfg->res_layers > 0,
+                VOX_ATTN_INVALID_ARGUMENT, "bad stream/layer counts");
+    VOX_REQUIRE(cfg->head_dim == kHeadDim, VOX_ATTN_UNSUPPORTED, "head_dim %d not supported (64 only)", cfg->head_dim);
+    VOX_REQUIRE(cfg->n_heads > 0 && cfg->n_kv_heads > 0 && cfg->n_heads % cfg->n_kv_heads == 0 &&
+                    cfg->n_heads / cfg->n_kv_heads <= 8,
+                VOX_ATTN_UNSUPPORTED, "head counts %d/%d not supported", cfg->n_heads, cfg->n_kv_heads);
+    VOX_REQUIRE(cfg->cfm_steps >= 0 && cfg->cfm_steps <= 16, VOX_ATTN_UNSUPPORTED, "cfm_steps %d not supported (0..16)", cfg->cfm_steps);
+    VOX_REQUIRE(cfg->locdit_seq >= 1 && cfg->locdit_seq <= 16 && cfg->locdit_layers >= 0, VOX_ATTN_UNSUPPORTED, "LocDiT shape not supported");
+    VOX_CUDA_TRY(cudaSetDevice(e->device));
+
+    vox_group * g = new (std::nothrow) vox_group();
+    VOX_REQUIRE(g != nullptr, VOX_ATTN_OUT_OF_MEMORY, "out of host memory");
+    g->e = e;
+    g->cfg = *cfg;
+    g->kv_len_host.assign(cfg->n_streams, 0);
+    int rc = VOX_ATTN_OK;
+    const int layers[2] = {cfg->base_layers, cfg->res_layers};
+    for (int s = 0; s < 2 && rc == VOX_ATTN_OK; ++s) {
+        if (layers[s] == 0) continue;
+        vox_kv_config kc = {layers[s], cfg->n_streams, cfg->n_kv_heads, cfg->head_dim, cfg->max_len, cfg->kv_type};
+        rc = vox_kv_create(e, &kc, &g->cache[s]);
+    }
+    if (rc == VOX_ATTN_OK) {
+        g->workspace_bytes = vox_attn_decode_workspace_bytes(cfg->n_streams, cfg->n_heads, cfg->n_kv_heads, cfg->max_len);
+        // the plan may pick any chunk for smaller bounds: size for the finest split
+        g->workspace_bytes = std::max(g->workspace_bytes,
+                                      (size_t) cfg->n_streams * cfg->n_heads * ((cfg->max_len + 63) / 64) * 66 * sizeof(float));
+        cudaError_t err = cudaMalloc(&g->workspace, g->workspace_bytes);
+        if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&g->kv_len_dev), sizeof(int32_t) * 2 * cfg->n_streams);
+        if (err == cudaSuccess) err = cudaMemset(g->kv_len_dev, 0, sizeof(int32_t) * 2 * cfg->n_streams);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            set_error("group allocation failed: %s", cudaGetErrorString(err));
+            rc = VOX_ATTN_OUT_OF_MEMORY;
+        } else {
+            g->kv_pos_dev = g->kv_len_dev + cfg->n_streams;
+        }
+    }
+    if (rc != VOX_ATTN_OK) {
+        vox_group_destroy(g);
+        return rc;
+    }
+    *out = g;
+    return VOX_ATTN_OK;
+}
+
+void vox_group_destroy(vox_group * g) {
+    if (!g) return;
+    cudaSetDevice(g->e->device);
+    for (int s = 0; s < 2; ++s) vox_kv_destroy(g->cache[s]);
+    if (g->workspace) cudaFree(g->workspace);
+    if (g->kv_len_dev) cudaFree(g->kv_len_dev);
+    if (g->dev_buf) cudaFree(g->dev_buf);
+    if (g->st_compute) cudaStreamDestroy(g->st_compute);
+    if (g->st_copy) cudaStreamDestroy(g->st_copy);
+    if (g->ev_lm_in) cudaEventDestroy(g->ev_lm_in);
+    if (g->ev_lm_done) cudaEventDestroy(g->ev_lm_done);
+    for (int i = 0; i < 16; ++i) {
+        if (g->ev_dit_in[i]) cudaEventDestroy(g->ev_dit_in[i]);
+        if (g->ev_dit_done[i]) cudaEventDestroy(g->ev_dit_done[i]);
+    }
+    delete g;
+}
+
+vox_kv_cache * vox_group_cache(vox_group * g, int stack) { return (g && stack >= 0 && stack < 2) ? g->cache[stack] : nullptr; }
+
+int vox_group_set_kv_len(vox_group * g, const int32_t * kv_len) {
+    VOX_REQUIRE(g && kv_len, VOX_ATTN_INVALID_ARGUMENT, "null argument");
+    int bound = 0;
+    for (int s = 0; s < g->cfg.n_streams; ++s) {
+        VOX_REQUIRE(kv_len[s] >= 0 && kv_len[s] <= g->cfg.max_len, VOX_ATTN_INVALID_ARGUMENT,
+                    "kv_len[%d] = %d exceeds the capacity %d", s, kv_len[s], g->cfg.max_len);
+        bound = std::max(bound, kv_len[s]);
+    }
+    VOX_CUDA_TRY(cudaSetDevice(g->e->device));
+    VOX_CUDA_TRY(cudaMemcpy(g->kv_len_dev, kv_len, sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
+    VOX_CUDA_TRY(cudaMemcpy(g->kv_pos_dev, kv_len, sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
+    memcpy(g->kv_len_host.data(), kv_len, sizeof(int32_t) * g->cfg.n_streams);
+    g->kv_bound = bound;
+    return VOX_ATTN_OK;
+}
+
+int vox_group_get_kv_len(const vox_group * g, int32_t * kv_len) {
+    VOX_REQUIRE(g && kv_len, VOX_ATTN_INVALID_ARGUMENT, "null argument");
+    memcpy(kv_len, g->kv_len_host.data(), sizeof(int32_t) * g->cfg.n_streams);
+    return VOX_ATTN_OK;
+}
+
+int vox_group_fill_synthetic(vox_group * g, uint64_t seed, void * stream) {
+    VOX_REQUIRE(g != nullptr, VOX_ATTN_INVALID_ARGUMENT, "group is null");
+    for (int s = 0; s < 2; ++s) {
+        if (!g->cache[s]) continue;
+        int rc = kv_fill_synthetic(g->cache[s], g->kv_len_dev, seed + 7919u * s, static_cast<cudaStream_t>(stream));
+        if (rc != VOX_ATTN_OK) return rc;
+    }
+    return VOX_ATTN_OK;
+}
+
+size_t vox_group_step_bytes(const vox_group * g, int which) { return g ? step_bytes(g->cfg, which) : 0; }
+
+int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void * stream) {
+    VOX_REQUIRE(g && b, VOX_ATTN_INVALID_ARGUMENT, "null argument");
+    const vox_group_config & c = g->cfg;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t S = c.n_streams, D = c.head_dim;
+    const float  scale = 1.0f / sqrtf((float) c.head_dim);  // src/minicpm.cpp:708-710
+    const int    L = c.base_layers + c.res_layers;
+    if (L > 0) VOX_REQUIRE(b->lm_q && b->lm_out && (!advance || (b->lm_k_new && b->lm_v_new)), VOX_ATTN_INVALID_ARGUMENT, "LM step buffers are null");
+    if (advance) {
+        VOX_REQUIRE(g->kv_bound + 1 <= c.max_len, VOX_ATTN_INVALID_ARGUMENT, "a stream would outgrow the cache capacity %d", c.max_len);
+    }
+    const int bound = g->kv_bound + (advance ? 1 : 0);
+    if (advance) {  // the appended row becomes visible to this step's attention
+        add_scalar_kernel<<<(c.n_streams + 255) / 256, 256, 0, st>>>(g->kv_len_dev, c.n_streams, 1, c.max_len);
+        int rc = check_launch(g->e, "add_scalar_kernel");
+        if (rc != VOX_ATTN_OK) return rc;
+    }
+    for (int l = 0; l < L; ++l) {
+        const int      stack = l < c.base_layers ? 0 : 1;
+        const int      layer = stack == 0 ? l : l - c.base_layers;
+        vox_kv_cache * kc    = g->cache[stack];
+        if (advance) {
+            const float * kn = b->lm_k_new + (size_t) l * S * c.n_kv_heads * D;
+            const float * vn = b->lm_v_new + (size_t) l * S * c.n_kv_heads * D;
+            int rc = vox_kv_append(kc, layer, c.n_streams, 1, g->kv_pos_dev, 0, kn, vn, D * 4, (size_t) c.n_kv_heads * D * 4,
+                                   (size_t) c.n_kv_heads * D * 4, st);
+            if (rc != VOX_ATTN_OK) return rc;
+        }
+        vox_decode_args da;
+        da.cache = kc; da.layer = layer; da.n_streams = c.n_streams; da.n_heads = c.n_heads;
+        da.kv_len = g->kv_len_dev; da.kv_bound = bound;
+        da.q = b->lm_q + (size_t) l * S * c.n_heads * D;
+        da.q_nb_head = D * 4; da.q_nb_stream = (size_t) c.n_heads * D * 4;
+        da.dst = b->lm_out + (size_t) l * S * c.n_heads * D;
+        da.scale = scale;
+        int rc = vox_attn_decode(g->e, &da, g->workspace, g->workspace_bytes, stream);
+        if (rc != VOX_ATTN_OK) return rc;
+    }
+    if (advance) {  // next append position; kv_len was already advanced above
+        add_scalar_kernel<<<(c.n_streams + 255) / 256, 256, 0, st>>>(g->kv_pos_dev, c.n_streams, 1, c.max_len);
+        int rc = check_launch(g->e, "add_scalar_kernel");
+        if (rc != VOX_ATTN_OK) return rc;
+        for (auto & x : g->kv_len_host) x += 1;
+        g->kv_bound += 1;
+    }
+    if (c.cfm_steps > 0 && c.locdit_layers > 0) {
+        VOX_REQUIRE(b->dit_q && b->dit_k && b->dit_v && b->dit_out, VOX_ATTN_INVALID_ARGUMENT, "LocDiT step buffers are null");
+        const size_t q_step  = S * c.locdit_layers * 2 * c.locdit_seq * c.n_heads * D;
+        const size_t kv_step = S * c.locdit_layers * 2 * c.locdit_seq * c.n_kv_heads * D;
+        for (int t = 0; t < c.cfm_steps; ++t) {
+            vox_locdit_args la;
+            la.n_streams = c.n_streams; la.n_layers = c.locdit_layers; la.n_heads = c.n_heads; la.n_kv_heads = c.n_kv_heads;
+            la.seq = c.locdit_seq; la.head_dim = c.head_dim;
+            la.q = b->dit_q + t * q_step; la.k = b->dit_k + t * kv_step; la.v = b->dit_v + t * kv_step;
+            la.dst = b->dit_out + t * q_step; la.scale = scale;
+            int rc = vox_attn_locdit_step(g->e, &la, stream);
+            if (rc != VOX_ATTN_OK) return rc;
+        }
+    }
+    return VOX_ATTN_OK;
+}
+
+// Host-buffer form: inputs cross PCIe on a copy stream while the compute stream works on what has
+// already landed (LM inputs first, then one CFM timestep at a time); outputs go back the same way.
+int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) {
+    VOX_REQUIRE(g && h, VOX_ATTN_INVALID_ARGUMENT, "null argument");
+    const vox_group_config & c = g->cfg;
+    VOX_CUDA_TRY(cudaSetDevice(g->e->device));
+    const size_t S = c.n_streams, D = c.head_dim, L = lm_layers(c);
+    const size_t lm_q_b = L * S * c.n_heads * D * 4, lm_kv_b = L * S * c.n_kv_heads * D * 4;
+    const size_t dq_step = S * c.locdit_layers * 2 * c.locdit_seq * c.n_heads * D * 4;
+    const size_t dkv_step = S * c.locdit_layers * 2 * c.locdit_seq * c.n_kv_heads * D * 4;
+    const size_t T = c.cfm_steps;
+    if (!g->dev_buf) {
+        const size_t sizes[8] = {lm_q_b, lm_kv_b, lm_kv_b, lm_q_b, dq_step * T, dkv_step * T, dkv_step * T, dq_step * T};
+        size_t off = 0;
+        for (int i = 0; i < 8; ++i) { g->dev_off[i] = off; off += (sizes[i] + 255) & ~(size_t) 255; }
+        cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&g->dev_buf), std::max<size_t>(off, 256));
+        if (err != cudaSuccess) { cudaGetLastError(); set_error("step staging allocation of %zu bytes failed", off); return VOX_ATTN_OUT_OF_MEMORY; }
+        VOX_CUDA_TRY(cudaStreamCreateWithFlags(&g->st_compute, cudaStreamNonBlocking));
+        VOX_CUDA_TRY(cudaStreamCreateWithFlags(&g->st_copy, cudaStreamNonBlocking));
+        VOX_CUDA_TRY(cudaEventCreateWithFlags(&g->ev_lm_in, cudaEventDisableTiming));
+        VOX_CUDA_TRY(cudaEventCreateWithFlags(&g->ev_lm_done, cudaEventDisableTiming));
+        for (int i = 0; i < 16; ++i) {
+            VOX_CUDA_TRY(cudaEventCreateWithFlags(&g->ev_dit_in[i], cudaEventDisableTiming));
+            VOX_CUDA_TRY(cudaEventCreateWithFlags(&g->ev_dit_done[i], cudaEventDisableTiming));
+        }
+    }
+    uint8_t * d = g->dev_buf;
+    vox_step_buffers dev;
+    dev.lm_q = (const float *) (d + g->dev_off[0]); dev.lm_k_new = (const float *) (d + g->dev_off[1]);
+    dev.lm_v_new = (const float *) (d + g->dev_off[2]); dev.lm_out = (float *) (d + g->dev_off[3]);
+    dev.dit_q = (const float *) (d + g->dev_off[4]); dev.dit_k = (const float *) (d + g->dev_off[5]);
+    dev.dit_v = (const float *) (d + g->dev_off[6]); dev.dit_out = (float *) (d + g->dev_off[7]);
+
+    // inputs: LM first, then each CFM timestep
+    if (L > 0) {
+        VOX_CUDA_TRY(cudaMemcpyAsync((void *) dev.lm_q, h->lm_q, lm_q_b, cudaMemcpyHostToDevice, g->st_copy));
+        if (advance) {
+            VOX_CUDA_TRY(cudaMemcpyAsync((void *) dev.lm_k_new, h->lm_k_new, lm_kv_b, cudaMemcpyHostToDevice, g->st_copy));
+            VOX_CUDA_TRY(cudaMemcpyAsync((void *) dev.lm_v_new, h->lm_v_new, lm_kv_b, cudaMemcpyHostToDevice, g->st_copy));
+        }
+    }
+    VOX_CUDA_TRY(cudaEventRecord(g->ev_lm_in, g->st_copy));
+    for (size_t t = 0; t < T; ++t) {
+        VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) dev.dit_q + t * dq_step, (const uint8_t *) h->dit_q + t * dq_step, dq_step, cudaMemcpyHostToDevice, g->st_copy));
+        VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) dev.dit_k + t * dkv_step, (const uint8_t *) h->dit_k + t * dkv_step, dkv_step, cudaMemcpyHostToDevice, g->st_copy));
+        VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) dev.dit_v + t * dkv_step, (const uint8_t *) h->dit_v + t * dkv_step, dkv_step, cudaMemcpyHostToDevice, g->st_copy));
+        VOX_CUDA_TRY(cudaEventRecord(g->ev_dit_in[t], g->st_copy));
+    }
+    // compute: LM layers once their inputs are in, then each timestep as it lands
+    vox_group_config lm_only = c; lm_only.cfm_steps = 0;
+    vox_group_config saved = g->cfg;
+    VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_compute, g->ev_lm_in, 0));
+    g->cfg = lm_only;
+    int rc = vox_group_step(g, &dev, advance, g->st_compute);
+    g->cfg = saved;
+    if (rc != VOX_ATTN_OK) return rc;
+    VOX_CUDA_TRY(cudaEventRecord(g->ev_lm_done, g->st_compute));
+    const float scale = 1.0f / sqrtf((float) c.head_dim);
+    for (size_t t = 0; t < T && c.locdit_layers > 0; ++t) {
+        VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_compute, g->ev_dit_in[t], 0));
+        vox_locdit_args la;
+        la.n_streams = c.n_streams; la.n_layers = c.locdit_layers; la.n_heads = c.n_heads; la.n_kv_heads = c.n_kv_heads;
+        la.seq = c.locdit_seq; la.head_dim = c.head_dim; la.scale = scale;
+        la.q = (const float *) ((const uint8_t *) dev.dit_q + t * dq_step);
+        la.k = (const float *) ((const uint8_t *) dev.dit_k + t * dkv_step);
+        la.v = (const float *) ((const uint8_t *) dev.dit_v + t * dkv_step);
+        la.dst = (float *) ((uint8_t *) dev.dit_out + t * dq_step);
+        rc = vox_attn_locdit_step(g->e, &la, g->st_compute);
+        if (rc != VOX_ATTN_OK) return rc;
+        VOX_CUDA_TRY(cudaEventRecord(g->ev_dit_done[t], g->st_compute));
+    }
+    // outputs ride the copy stream behind the inputs (PCIe is full duplex; D2H overlaps later H2D)
+    if (L > 0) {
+        VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_copy, g->ev_lm_done, 0));
+        VOX_CUDA_TRY(cudaMemcpyAsync(h->lm_out, dev.lm_out, lm_q_b, cudaMemcpyDeviceToHost, g->st_copy));
+    }
+    for (size_t t = 0; t < T && c.locdit_layers > 0; ++t) {
+        VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_copy, g->ev_dit_done[t], 0));
+        VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) h->dit_out + t * dq_step, (const uint8_t *) dev.dit_out + t * dq_step, dq_step, cudaMemcpyDeviceToHost, g->st_copy));
+    }
+    VOX_CUDA_TRY(cudaStreamSynchronize(g->st_copy));
+    return vox_engine_sync_status(g->e, g->st_compute);
+}
+
+int vox_partition_streams(const int32_t * kv_len, int n_streams, int n_gpus, int32_t * owner) {
+    VOX_REQUIRE(kv_len && owner && n_streams >= 0 && n_gpus > 0, VOX_ATTN_INVALID_ARGUMENT, "bad partition arguments");
+    std::vector<int> order(n_streams);
+    std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return kv_len[a] > kv_len[b]; });
+    std::vector<long long> load(n_gpus, 0);
+    std::vector<int>       count(n_gpus, 0);
+    for (int s : order) {
+        int best = 0;
+        for (int gidx = 1; gidx < n_gpus; ++gidx)
+            if (load[gidx] < load[best] || (load[gidx] == load[best] && count[gidx] < count[best])) best = gidx;
+        owner[s] = best;
+        load[best] += std::max(kv_len[s], 0);
+        count[best] += 1;
+    }
+    return VOX_ATTN_OK;
+}
+
+}  // extern "C"
