@@ -231,12 +231,12 @@ def main():
     stream = torch.cuda.current_stream()
 
     # ---- device-resident throughput: K steps, CUDA events, barrier + sync on both sides
-    for _ in range(args.warmup):
-        group.step(dev_t, advance=True)
-    eng.sync_status()
     clocks = ClockSampler(local)
     if rank == 0:
         clocks.start()
+    for _ in range(args.warmup):
+        group.step(dev_t, advance=True)
+    eng.sync_status()
     barrier()
     l0 = eng.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -248,7 +248,6 @@ def main():
     eng.sync_status()
     launches = eng.launches - l0
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    clock_info = clocks.stop() if rank == 0 else None
     ms_per_step = ms_total / args.steps
     total_streams = sum_over_ranks(float(S))
     value = total_streams / (ms_per_step * 1e-3)
@@ -284,23 +283,21 @@ def main():
                 "frac_of_nominal_8000": achieved / 8000.0}
 
     # ---- LocDiT: latency of one patch for one stream (10 launches), and launches per CFM timestep
-    q1 = torch.randn((CFM_STEPS, 1, DIT_LAYERS, 2, H, DIT_SEQ, D), device="cuda", generator=gen)
-    k1 = torch.randn((CFM_STEPS, 1, DIT_LAYERS, 2, HK, DIT_SEQ, D), device="cuda", generator=gen)
-    v1 = torch.randn((CFM_STEPS, 1, DIT_LAYERS, 2, HK, DIT_SEQ, D), device="cuda", generator=gen)
-    o1 = torch.empty((CFM_STEPS, 1, DIT_LAYERS, 2, DIT_SEQ, H, D), device="cuda")
+    one = pkg.Group(eng, n_streams=1, max_len=64, kv_type=kv_type, base_layers=0, res_layers=0, n_heads=H, n_kv_heads=HK,
+                    locdit_layers=DIT_LAYERS, locdit_seq=DIT_SEQ, cfm_steps=CFM_STEPS)
+    one_t = {n: torch.randn(s, device="cuda", generator=gen) for n, s in one.buffer_shapes().items()}
     for _ in range(3):
-        for t in range(CFM_STEPS):
-            eng.locdit_step(q1[t], k1[t], v1[t], dst=o1[t])
+        one.step(one_t, advance=False)
     torch.cuda.synchronize()
     lb = eng.launches
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = 20
     a.record(stream)
     for _ in range(reps):
-        for t in range(CFM_STEPS):
-            eng.locdit_step(q1[t], k1[t], v1[t], dst=o1[t])
+        one.step(one_t, advance=False)  # the 10 CFM launches are issued back to back from C
     b.record(stream)
     torch.cuda.synchronize()
+    one.close()
     locdit = {"us_per_patch_single_stream": a.elapsed_time(b) * 1e3 / reps,
               "launches_per_cfm_step": (eng.launches - lb) / (reps * CFM_STEPS)}
 
@@ -324,6 +321,9 @@ def main():
         e2e = {"value": total_streams * e2e_steps / dt, "unit": "patches/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps}
 
+    # clocks were sampled from the first warm-up step to the last end-to-end step (GPU under load throughout)
+    clock_info = clocks.stop() if rank == 0 else None
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
@@ -335,11 +335,11 @@ def main():
     if rank == 0:
         line = {"metric": "patches/s", "value": value, "unit": "patches/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
-                "vs_baseline": None, "dtype": "f16 K/V, f32 Q/out, f16 MMA with f32 accumulation" if args.kv_type == "f16"
-                else "q8_0 K/V, f32 Q/out, f16 MMA with f32 accumulation",
-                "data": "synthetic",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD.format(s=args.streams), "streams_total": int(total_streams), "kv_type": args.kv_type,
-                           "l2": "inputs larger than L2 (KV read per step >> 126 MB)", "append": "included"},
+                           "l2": "inputs larger than L2 (KV read per step >> 126 MB)", "append": "included",
+                           "arithmetic": "f16 K/V (or q8_0), f32 Q and output, f16 tensor-core products with hi+lo split of Q and P, "
+                                         "f32 accumulation; LocDiT f32 throughout"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_info,
                 "locdit": locdit,
                 "decode": {"gb_per_s": achieved, "pct_of_measured_peak": 100 * achieved / peak, "pct_of_8000": 100 * achieved / 8000}}

@@ -290,9 +290,11 @@ def test_locdit_matches_reference_fixture(engine, oracle, golden):
     engine.sync_status()
     got = out.cpu().numpy()[0, 0]
     assert rel_err(got, golden["locdit_2x9_f32/gate"]) < TOL["f32"]
-    # and it equals the reference's packed 18-token form with the block-diagonal mask
-    packed = golden["locdit_packed18_f32/gate"]
-    assert rel_err(got[0], packed[0, :9]) < TOL["f32"] and rel_err(got[1], packed[0, 9:]) < TOL["f32"]
+    # and it equals the packed 18-token form with the block-diagonal mask that the reference builds
+    packed = [np.concatenate([inp[n][0], inp[n][1]], axis=1)[None] for n in ("q", "k", "v")]
+    mask = oracle.cfg_pair_mask(9)[None, None]
+    via_mask = engine.forward(dev(packed[0]), dev(packed[1]), dev(packed[2]), dev(mask)).cpu().numpy()
+    assert rel_err(got[0], via_mask[0, :9]) < 1e-5 and rel_err(got[1], via_mask[0, 9:]) < 1e-5
 
 
 @pytest.mark.parametrize("name", ["prefill72_causal_f16", "prefill128_gqa4_causal_f16"])

@@ -128,8 +128,10 @@ int validate(const vox_attn_args * a, bool need_data) {
                         (long long) k.ne[1], (long long) q.ne[1]);
             VOX_REQUIRE(m.ne[2] > 0 && m.ne[3] > 0 && q.ne[2] % m.ne[2] == 0 && q.ne[3] % m.ne[3] == 0,
                         VOX_ATTN_INVALID_ARGUMENT, "mask does not broadcast over heads/batch");
-            VOX_REQUIRE(m.nb[0] == 2 && m.nb[1] == (size_t) m.ne[0] * 2 && m.nb[2] == m.nb[1] * m.ne[1] &&
-                            m.nb[3] == m.nb[2] * m.ne[2],
+            // contiguity as ggml_is_contiguous sees it: strides of extent-1 axes do not matter
+            VOX_REQUIRE(m.nb[0] == 2 && (m.ne[1] == 1 || m.nb[1] == (size_t) m.ne[0] * 2) &&
+                            (m.ne[2] == 1 || m.nb[2] == (size_t) m.ne[0] * 2 * m.ne[1]) &&
+                            (m.ne[3] == 1 || m.nb[3] == (size_t) m.ne[0] * 2 * m.ne[1] * m.ne[2]),
                         VOX_ATTN_INVALID_ARGUMENT, "mask must be contiguous");
         }
     }
@@ -230,7 +232,7 @@ int vox_attn_forward_host(vox_engine * e, const vox_attn_args * a, void * stream
                 "null data pointer");
     VOX_CUDA_TRY(cudaSetDevice(e->device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // host tensors are repacked densely on the device: the strides below describe that copy
+    // each host tensor is copied as one span with its strides unchanged
     auto span = [](const vox_tensor & t) {
         size_t end = 0;
         const size_t e0 = t.type == VOX_TYPE_Q8_0 ? (size_t) (t.ne[0] / 32) * 34 : (size_t) t.ne[0] * t.nb[0];

@@ -66,8 +66,8 @@ extern "C" {
 int vox_group_create(vox_engine * e, const vox_group_config * cfg, vox_group ** out) {
     VOX_REQUIRE(e && cfg && out, VOX_ATTN_INVALID_ARGUMENT, "vox_group_create: null argument");
     *out = nullptr;
-    VOX_REQUIRE(cfg->n_streams > 0 && cfg->base_layers >= 0 && cfg->res_layers >= 0 && cfg->base_layers + cfg->res_layers > 0,
-                VOX_ATTN_INVALID_ARGUMENT, "bad stream/layer counts");
+    VOX_REQUIRE(cfg->n_streams > 0 && cfg->base_layers >= 0 && cfg->res_layers >= 0, VOX_ATTN_INVALID_ARGUMENT,
+                "bad stream/layer counts");
     VOX_REQUIRE(cfg->head_dim == kHeadDim, VOX_ATTN_UNSUPPORTED, "head_dim %d not supported (64 only)", cfg->head_dim);
     VOX_REQUIRE(cfg->n_heads > 0 && cfg->n_kv_heads > 0 && cfg->n_heads % cfg->n_kv_heads == 0 &&
                     cfg->n_heads / cfg->n_kv_heads <= 8,
