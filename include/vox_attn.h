@@ -185,6 +185,23 @@ size_t vox_attn_decode_workspace_bytes(int n_streams, int n_heads, int n_kv_head
 int    vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace, size_t workspace_bytes,
                        void * stream);
 
+/* vox_attn_decode for callers that cannot allocate device memory and so have no workspace to
+ * pass: a real-time audio thread that must stay out of the allocator, a host that gave all device
+ * memory to its own arena at start-up, a plugin that is handed nothing but its inputs and
+ * outputs.  It has no counterpart in the reference.  Same arguments and results as
+ * vox_attn_decode; the split-KV partials go to a 16 MiB array built into the library (each GPU
+ * that loads the library holds it until the process exits), and the call performs no allocation
+ * of any kind.
+ *   - A call whose partials would not fit (n_streams * n_heads * chunks * 264 bytes > 16 MiB;
+ *     ask vox_attn_decode_workspace_bytes) returns VOX_ATTN_WORKSPACE_TOO_SMALL and launches
+ *     nothing.
+ *   - The engine's device must be the current device.  The first call on a device looks up the
+ *     array's device address; make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it needs clearing between calls, but
+ *     two calls whose kernels overlap on the GPU (different streams) overwrite each other's
+ *     partials: keep calls on one stream, or order them yourself. */
+int    vox_attn_decode_static(vox_engine * e, const vox_decode_args * a, void * stream);
+
 /* ---------------------------------------------------------------- LocDiT --------------- */
 
 /* All attention of ONE CFM timestep in ONE launch: every layer, both CFG branches, every head,

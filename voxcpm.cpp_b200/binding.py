@@ -140,6 +140,7 @@ def lib() -> C.CDLL:
         "vox_kv_copy_from": (i32, [vp, vp, vp]),
         "vox_attn_decode_workspace_bytes": (sz, [i32, i32, i32, i32]),
         "vox_attn_decode": (i32, [vp, C.POINTER(DecodeArgs), vp, sz, vp]),
+        "vox_attn_decode_static": (i32, [vp, C.POINTER(DecodeArgs), vp]),
         "vox_attn_locdit_step": (i32, [vp, C.POINTER(LocditArgs), vp]),
         "vox_group_create": (i32, [vp, C.POINTER(GroupConfig), C.POINTER(vp)]),
         "vox_group_destroy": (None, [vp]),
@@ -344,6 +345,15 @@ class KVCache:
         a = DecodeArgs(self.h, layer, S, H, kv_len.data_ptr(), kv_bound, q.data_ptr(), q.stride(1) * 4, q.stride(0) * 4,
                        dst.data_ptr(), scale)
         _check(lib().vox_attn_decode(self.engine.h, C.byref(a), C.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(stream)))
+        return dst
+
+    def decode_static(self, layer, q, kv_len, kv_bound, dst, scale=0.125, stream=None):
+        """``vox_attn_decode_static``: the caller passes inputs and the output only; the split-KV
+        scratch is the array built into the library, so nothing is allocated by the call."""
+        S, H, D = q.shape
+        a = DecodeArgs(self.h, layer, S, H, kv_len.data_ptr(), kv_bound, q.data_ptr(), q.stride(1) * 4, q.stride(0) * 4,
+                       dst.data_ptr(), scale)
+        _check(lib().vox_attn_decode_static(self.engine.h, C.byref(a), _stream_ptr(stream)))
         return dst
 
 

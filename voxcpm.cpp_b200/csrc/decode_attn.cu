@@ -376,3 +376,47 @@ int vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Decode without any allocation: split-KV partials in a built-in device array
+// ---------------------------------------------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory at the point where they call
+// attention: a real-time audio thread that must not enter the allocator, a host that has handed
+// all device memory to its own arena up front, or a plugin that is only given input and output
+// buffers by its framework.  For them the partial results of the split-KV pass live in the array
+// below, which is part of the library image: every GPU that loads the library carries these
+// bytes until the process exits, whether or not the entry point is ever called.
+//
+// In host code `g_decode_scratch` is only a handle for the runtime, not a device address, so the
+// address is looked up with cudaGetSymbolAddress (once per device, with that device current) and
+// that pointer is what the kernels receive.
+constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB: e.g. 32 streams x 16 heads x 8192 rows, or 256 x 16 x 3800
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int  kMaxDevices = 64;
+unsigned char * g_scratch_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int vox_attn_decode_static(vox_engine * e, const vox_decode_args * a, void * stream) {
+    VOX_REQUIRE(e && a && a->cache, VOX_ATTN_INVALID_ARGUMENT, "vox_attn_decode_static: null argument");
+    int current = -1;
+    VOX_CUDA_TRY(cudaGetDevice(&current));
+    VOX_REQUIRE(current == e->device && current >= 0 && current < kMaxDevices, VOX_ATTN_INVALID_ARGUMENT,
+                "the engine's device %d must be the current device (current is %d)", e->device, current);
+    const size_t need = decode_workspace_bytes(a->n_streams, a->n_heads, a->cache->cfg.n_kv_heads, a->kv_bound);
+    VOX_REQUIRE(need <= kStaticScratchBytes, VOX_ATTN_WORKSPACE_TOO_SMALL,
+                "this call needs %zu bytes of split-KV scratch but the built-in array holds %zu; "
+                "use vox_attn_decode with a caller-provided workspace for this size",
+                need, kStaticScratchBytes);
+    if (g_scratch_ptr[current] == nullptr) {  // first call on this device: resolve the array's device address
+        void * ptr = nullptr;
+        VOX_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_scratch));
+        VOX_REQUIRE(ptr != nullptr, VOX_ATTN_CUDA_ERROR, "cudaGetSymbolAddress returned a null address");
+        g_scratch_ptr[current] = static_cast<unsigned char *>(ptr);
+    }
+    // Nothing in the array has to start at zero: every partial a merge reads was written by the
+    // decode kernel of the same call.  What the previous call left behind is simply overwritten.
+    return vox_attn_decode(e, a, g_scratch_ptr[current], kStaticScratchBytes, stream);
+}
