@@ -244,7 +244,8 @@ typedef struct {
  *   lm_v_new  same
  *   lm_out    [D, H, 1, S, L] f32
  *   dit_q     [D, seq, H,  2, locdit_layers, S, cfm_steps] f32;  dit_k, dit_v with HK
- *   dit_out   [D, H, seq, 2, locdit_layers, S, cfm_steps] f32                                */
+ *   dit_out   [D, H, seq, 2, locdit_layers, S, cfm_steps] f32
+ * vox_group_step skips the LM stacks when lm_q is NULL and the LocDiT patch when dit_q is NULL.  */
 typedef struct {
     const float * lm_q;
     const float * lm_k_new;

@@ -184,7 +184,7 @@ def _fill(cache, oracle, rng, lens, kv, layer=0):
     return ks, vs
 
 
-@pytest.mark.parametrize("kv", ["f16"])
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
 @pytest.mark.parametrize("lens", [[256], [1, 2, 63, 64, 65, 127, 128, 129, 130], [1024, 17, 2048, 700], [8192], [0, 5]])
 def test_decode_ragged_batch(kv, lens, engine, pkg, oracle, vo):
     rng = np.random.default_rng(len(lens) * 1000 + lens[0])
@@ -204,17 +204,35 @@ def test_decode_ragged_batch(kv, lens, engine, pkg, oracle, vo):
         assert rel_err(out[s], ref) < TOL[kv], f"stream {s} (kv_len {n})"
 
 
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
 @pytest.mark.parametrize("n_kv", list(range(1, 131, 7)) + [130])
-def test_decode_every_tail_length(n_kv, engine, pkg, oracle, vo):
+def test_decode_every_tail_length(n_kv, kv, engine, pkg, oracle, vo):
     """kv lengths 1..130 walk through every position of the 16-row warp slices and 64-row tiles."""
     rng = np.random.default_rng(n_kv)
-    cache = pkg.KVCache(engine, 1, 1, HK, 192, pkg.F16)
-    ks, vs = _fill(cache, oracle, rng, [n_kv], "f16")
+    cache = pkg.KVCache(engine, 1, 1, HK, 192, KV_TYPE[kv])
+    ks, vs = _fill(cache, oracle, rng, [n_kv], kv)
     q = rng.standard_normal((1, H, D)).astype(np.float32)
     out = cache.decode(0, dev(q), dev(np.array([n_kv], np.int32)), n_kv).cpu().numpy()
     engine.sync_status()
-    ref = oracle.attn(q[0][None, :, None, :], ks[0][None], vs[0][None], kv_type=vo.F16, path=vo.PATH_ROW_F32)[0, 0]
-    assert rel_err(out[0], ref) < TOL["f16"]
+    ref = oracle.attn(q[0][None, :, None, :], ks[0][None], vs[0][None], kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)[0, 0]
+    assert rel_err(out[0], ref) < TOL[kv]
+
+
+@pytest.mark.parametrize("name", ["decode_kv256_f16_l0", "decode_kv1024_f16", "decode_kv2048_b2_f16", "decode_kv777_f16",
+                                  "decode_kv256_q8", "decode_kv1000_q8", "decode_kv1_f16"])
+def test_cache_decode_matches_reference_fixture(name, engine, pkg, oracle, golden):
+    """The reference's stored K/V (f16 rows / block_q8_0 rows) imported into the cache, decoded by the
+    split-KV kernel, against the reference's accurate-path output."""
+    case = CASES[name]
+    inp = make_inputs(case, oracle)
+    B, n_kv = case["B"], case["n_kv"]
+    cache = pkg.KVCache(engine, 1, B, case["HK"], -(-n_kv // 64) * 64, KV_TYPE[case["kv"]])
+    for b in range(B):
+        cache.import_(0, b, inp["k"][b], inp["v"][b])
+    q = np.ascontiguousarray(inp["q"][:, :, 0, :])
+    out = cache.decode(0, dev(q), dev(np.full(B, n_kv, np.int32)), n_kv).cpu().numpy()
+    engine.sync_status()
+    assert rel_err(out, golden[name + "/gate"][:, 0]) < TOL[case["kv"]]
 
 
 def test_decode_ignores_stale_rows_beyond_kv_len(engine, pkg, oracle, vo):
@@ -320,7 +338,7 @@ def test_prefill_causal(B, L, engine, oracle, vo):
 
 # ------------------------------------------------------------------ stream groups
 
-@pytest.mark.parametrize("kv", ["f16"])
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
 def test_group_step_appends_then_attends(kv, engine, pkg, oracle, vo):
     import torch
     rng = np.random.default_rng(5)

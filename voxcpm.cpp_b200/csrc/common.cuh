@@ -38,6 +38,7 @@ void set_error(const char * fmt, ...);
     } while (0)
 
 constexpr int kHeadDim = 64;
+constexpr int kCounterSlots = 1 << 16;
 
 // bits of the device status word
 enum : int { kStatusTimeout = 1, kStatusBadState = 2 };
@@ -54,6 +55,8 @@ struct vox_engine {
     int *             status_host  = nullptr;  // pinned, mapped; kernels write through status_dev
     int *             status_dev   = nullptr;
     uint64_t          launches     = 0;
+    int *             counters_dev = nullptr;  // kCounterSlots zeroed ints: split-KV arrival tickets
+    uint32_t          attr_mask    = 0;      // kernels whose shared-memory attribute was set on this device
     vox::encode_tiled_fn encode    = nullptr;
     // staging for the *_host entry points
     void *            stage_dev    = nullptr;

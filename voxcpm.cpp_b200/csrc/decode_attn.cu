@@ -30,7 +30,6 @@ using namespace vox;
 
 namespace {
 
-constexpr int kStages        = 4;
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads       = (kConsumerWarps + 1) * 32;
 constexpr int kPartialStride = 66;  // max, sum, acc[64]
@@ -45,6 +44,7 @@ struct DecodeParams {
     int             n_heads, gqa, chunk, n_chunks, layer, max_len;
     float           scale_log2;
     int *           status;
+    int *           counters;  // non-null: the last CTA of a (stream, kv head) to finish folds the partials itself
 };
 
 __device__ __forceinline__ int stream_len(const DecodeParams & p, int stream) {
@@ -52,14 +52,40 @@ __device__ __forceinline__ int stream_len(const DecodeParams & p, int stream) {
     return max(0, min(len, p.max_len));
 }
 
-// ---------------------------------------------------------------------------------------------
-// f16 K/V
-// ---------------------------------------------------------------------------------------------
-constexpr int kStageBytesF16 = 2 * kKvTile * 128;  // K tile + V tile
+// Shared-memory ring: per stage one 64-row K tile and one 64-row V tile.
+//   f16 : 2 x 8 KB (128-byte rows, 128-byte swizzle)                       -> 16 KB, 4 stages
+//   q8_0: 2 x 4 KB int8 (64-byte rows, 64-byte swizzle) + 2 x 256 B scales -> 9 KB (1 KB aligned), 6 stages
+template <bool Q8> struct Ring {
+    static constexpr int kStages     = Q8 ? 6 : 4;
+    static constexpr int kDataBytes  = Q8 ? kKvTile * 64 : kKvTile * 128;
+    static constexpr int kStageBytes = Q8 ? 9 * 1024 : 2 * kDataBytes;
+    static constexpr int kTxBytes    = Q8 ? 2 * kDataBytes + 2 * kKvTile * 4 : 2 * kDataBytes;
+    static constexpr int kSmemBytes  = kStages * kStageBytes + 1024;
+};
 
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float half_lo(uint32_t x) { return __half2float(__ushort_as_half((unsigned short) (x & 0xffffu))); }
+__device__ __forceinline__ float half_hi(uint32_t x) { return __half2float(__ushort_as_half((unsigned short) (x >> 16))); }
+
+// four signed bytes -> two half2 registers holding the exact values.  A byte b is biased to b+128,
+// placed in the mantissa of 1024.0h (0x6400 | b+128 == 1024 + b + 128) and 1152 is subtracted.
+// `sel_a` / `sel_b` pick which two bytes go to each register (PRMT selectors, 4 = the 0x64 byte).
+__device__ __forceinline__ uint32_t s8_pair_to_half2(uint32_t biased, uint32_t selector) {
+    const uint32_t h  = __byte_perm(biased, 0x64646464u, selector);
+    const __half2  r  = __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half((unsigned short) 0x6480)));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+template <bool Q8>
 __global__ void __launch_bounds__(kThreads, 3)
-decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                  const DecodeParams p) {
+decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+              const __grid_constant__ CUtensorMap map_ks, const __grid_constant__ CUtensorMap map_vs, const DecodeParams p) {
+    using R = Ring<Q8>;
+    constexpr int kStages = R::kStages;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * kStages];
     __shared__ int      abort_flag;
@@ -105,10 +131,16 @@ decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     break;
                 }
                 if (*reinterpret_cast<volatile int *>(&abort_flag)) break;
-                const uint32_t kb = smem_base + s * kStageBytesF16;
-                mbar_expect_tx(full0 + 8 * s, kStageBytesF16);
-                tma_load_5d(kb, &map_k, full0 + 8 * s, 0, c0 + i * kKvTile, kvh, stream, p.layer);
-                tma_load_5d(kb + kKvTile * 128, &map_v, full0 + 8 * s, 0, c0 + i * kKvTile, kvh, stream, p.layer);
+                const uint32_t sb  = smem_base + s * R::kStageBytes;
+                const uint32_t bar = full0 + 8 * s;
+                const int      pos = c0 + i * kKvTile;
+                mbar_expect_tx(bar, R::kTxBytes);
+                tma_load_5d(sb, &map_k, bar, 0, pos, kvh, stream, p.layer);
+                tma_load_5d(sb + R::kDataBytes, &map_v, bar, 0, pos, kvh, stream, p.layer);
+                if constexpr (Q8) {
+                    tma_load_5d(sb + 2 * R::kDataBytes, &map_ks, bar, 2 * pos, 0, kvh, stream, p.layer);
+                    tma_load_5d(sb + 2 * R::kDataBytes + kKvTile * 4, &map_vs, bar, 2 * pos, 0, kvh, stream, p.layer);
+                }
                 issued = i + 1;
             }
             if (*reinterpret_cast<volatile int *>(&abort_flag)) {
@@ -123,7 +155,12 @@ decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     // ---------------------------------------------------------------------- consumers
     const int g = lane >> 2, t = lane & 3;
 
-    // Q fragments: rows 0-7 = hi part of the 8 heads of this group, rows 8-15 = lo part
+    // Q fragments of the four k-steps: rows 0-7 = hi part of the group's heads, rows 8-15 = lo part.
+    // The 64 head dimensions may be fed to the MMAs in any order as long as K uses the same one:
+    //   f16 : k-step c covers d = 16c .. 16c+15 in natural order (K fragments come from ldmatrix);
+    //   q8_0: k-step s covers the 8 bytes per lane that one 64-bit shared load returns,
+    //         d = 32*(s/2) + 8t + 4*(s%2) + {0,1,2,3}, so that k-steps 0,1 / 2,3 stay inside one
+    //         32-value quantisation block and the block scale can be applied to their accumulator.
     uint32_t qa[4][4];
     {
         const int     head = kvh * p.gqa + min(g, p.gqa - 1);
@@ -131,8 +168,10 @@ decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         const float   live = g < p.gqa ? p.scale_log2 : 0.0f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const float2 x = *reinterpret_cast<const float2 *>(qrow + 16 * c + 2 * t);
-            const float2 y = *reinterpret_cast<const float2 *>(qrow + 16 * c + 8 + 2 * t);
+            const int d0 = Q8 ? 32 * (c >> 1) + 8 * t + 4 * (c & 1) : 16 * c + 2 * t;
+            const int d1 = Q8 ? d0 + 2 : d0 + 8;
+            const float2 x = *reinterpret_cast<const float2 *>(qrow + d0);
+            const float2 y = *reinterpret_cast<const float2 *>(qrow + d1);
             float h0, l0, h1, l1, h2, l2, h3, l3;
             split_hi_lo(x.x * live, h0, l0);
             split_hi_lo(x.y * live, h1, l1);
@@ -165,23 +204,48 @@ decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         }
         const int p0 = c0 + i * kKvTile + 16 * warp;
         if (p0 < c1) {
-            const uint32_t kb = smem_base + s * kStageBytesF16, vb = kb + kKvTile * 128;
-            float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(kb + k_row * 128 + (((2 * c + k_chk) ^ (k_row & 7)) << 4), b0, b1, b2, b3);
-                mma_16816(sc[0], qa[c], b0, b1);
-                mma_16816(sc[1], qa[c], b2, b3);
-            }
+            const uint32_t kb = smem_base + s * R::kStageBytes, vb = kb + R::kDataBytes;
             float sv[2][2];
+            if constexpr (!Q8) {
+                float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(kb + k_row * 128 + (((2 * c + k_chk) ^ (k_row & 7)) << 4), b0, b1, b2, b3);
+                    mma_16816(sc[0], qa[c], b0, b1);
+                    mma_16816(sc[1], qa[c], b2, b3);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    sv[j][0] = sc[j][0] + sc[j][2];
+                    sv[j][1] = sc[j][1] + sc[j][3];
+                }
+            } else {
+                const uint32_t ksc = kb + 2 * R::kDataBytes;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int row = 16 * warp + 8 * j + g;
+                    float     sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // one accumulator per 32-value block
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        const uint2 raw = lds64(kb + row * 64 + (((2 * b + (t >> 1)) ^ ((row >> 1) & 3)) << 4) + ((t & 1) << 3));
+                        const uint32_t x0 = raw.x ^ 0x80808080u, x1 = raw.y ^ 0x80808080u;
+                        mma_16816(sc[b], qa[2 * b], s8_pair_to_half2(x0, 0x4140), s8_pair_to_half2(x0, 0x4342));
+                        mma_16816(sc[b], qa[2 * b + 1], s8_pair_to_half2(x1, 0x4140), s8_pair_to_half2(x1, 0x4342));
+                    }
+                    // scales of positions 8j+2t and 8j+2t+1, both blocks: four consecutive halves
+                    const uint2 ds = lds64(ksc + (16 * warp + 8 * j + 2 * t) * 4);
+                    sv[j][0] = (sc[0][0] + sc[0][2]) * half_lo(ds.x) + (sc[1][0] + sc[1][2]) * half_hi(ds.x);
+                    sv[j][1] = (sc[0][1] + sc[0][3]) * half_lo(ds.y) + (sc[1][1] + sc[1][3]) * half_hi(ds.y);
+                }
+            }
             float tmax = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int pos = p0 + 8 * j + 2 * t + e;
-                    sv[j][e]      = pos < c1 ? sc[j][e] + sc[j][e + 2] : -INFINITY;
+                    sv[j][e]      = pos < c1 ? sv[j][e] : -INFINITY;
                     tmax          = fmaxf(tmax, sv[j][e]);
                 }
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
@@ -190,28 +254,66 @@ decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             const float alpha = m_new == -INFINITY ? 1.0f : exp2f(m - m_new);
             const float m_use = m_new == -INFINITY ? 0.0f : m_new;
             m                 = m_new;
-            uint32_t pa[4];
-            float    psum = 0.0f;
+            float pr[2][2];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                float h0, l0, h1, l1;
-                split_hi_lo(exp2f(sv[j][0] - m_use), h0, l0);
-                split_hi_lo(exp2f(sv[j][1] - m_use), h1, l1);
-                pa[2 * j]     = pack_half2(h0, h1);
-                pa[2 * j + 1] = pack_half2(l0, l1);
-                psum += (h0 + l0) + (h1 + l1);
+                pr[j][0] = exp2f(sv[j][0] - m_use);
+                pr[j][1] = exp2f(sv[j][1] - m_use);
             }
-            l = l * alpha + psum;
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 o[n][0] *= alpha; o[n][1] *= alpha; o[n][2] *= alpha; o[n][3] *= alpha;
             }
+            if constexpr (!Q8) {
+                uint32_t pa[4];
+                float    psum = 0.0f;
 #pragma unroll
-            for (int n2 = 0; n2 < 4; ++n2) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(vb + v_row * 128 + (((2 * n2 + v_chk) ^ (v_row & 7)) << 4), b0, b1, b2, b3);
-                mma_16816(o[2 * n2], pa, b0, b1);
-                mma_16816(o[2 * n2 + 1], pa, b2, b3);
+                for (int j = 0; j < 2; ++j) {
+                    float h0, l0, h1, l1;
+                    split_hi_lo(pr[j][0], h0, l0);
+                    split_hi_lo(pr[j][1], h1, l1);
+                    pa[2 * j]     = pack_half2(h0, h1);
+                    pa[2 * j + 1] = pack_half2(l0, l1);
+                    psum += (h0 + l0) + (h1 + l1);
+                }
+                l = l * alpha + psum;
+#pragma unroll
+                for (int n2 = 0; n2 < 4; ++n2) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(vb + v_row * 128 + (((2 * n2 + v_chk) ^ (v_row & 7)) << 4), b0, b1, b2, b3);
+                    mma_16816(o[2 * n2], pa, b0, b1);
+                    mma_16816(o[2 * n2 + 1], pa, b2, b3);
+                }
+            } else {
+                l = l * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
+                // V scales are folded into the weights: one A operand per 32-wide block of output columns
+                const uint32_t vsc = kb + 2 * R::kDataBytes + kKvTile * 4;
+                uint32_t       pa[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint2 ds = lds64(vsc + (16 * warp + 8 * j + 2 * t) * 4);
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        float h0, l0, h1, l1;
+                        split_hi_lo(pr[j][0] * (b ? half_hi(ds.x) : half_lo(ds.x)), h0, l0);
+                        split_hi_lo(pr[j][1] * (b ? half_hi(ds.y) : half_lo(ds.y)), h1, l1);
+                        pa[b][2 * j]     = pack_half2(h0, h1);
+                        pa[b][2 * j + 1] = pack_half2(l0, l1);
+                    }
+                }
+                // ldmatrix.trans on 16-bit units keeps byte pairs together: a register holds
+                // V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1] of one 16-column chunk, i.e. the B
+                // fragments of an "even columns" tile (bytes 0,2) and an "odd columns" tile (bytes 1,3).
+#pragma unroll
+                for (int cp = 0; cp < 2; ++cp) {
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4_trans(vb + v_row * 64 + (((2 * cp + v_chk) ^ ((v_row >> 1) & 3)) << 4), r0, r1, r2, r3);
+                    r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+                    mma_16816(o[4 * cp + 0], pa[cp], s8_pair_to_half2(r0, 0x4240), s8_pair_to_half2(r1, 0x4240));
+                    mma_16816(o[4 * cp + 1], pa[cp], s8_pair_to_half2(r0, 0x4341), s8_pair_to_half2(r1, 0x4341));
+                    mma_16816(o[4 * cp + 2], pa[cp], s8_pair_to_half2(r2, 0x4240), s8_pair_to_half2(r3, 0x4240));
+                    mma_16816(o[4 * cp + 3], pa[cp], s8_pair_to_half2(r2, 0x4341), s8_pair_to_half2(r3, 0x4341));
+                }
             }
         }
         __syncwarp();
@@ -230,8 +332,13 @@ decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         if (t == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
-            mine[2 + 8 * n + 2 * t]     = o[n][0] + o[n][2];
-            mine[2 + 8 * n + 2 * t + 1] = o[n][1] + o[n][3];
+            // output column of accumulator registers 0/2 and 1/3 of tile n
+            //   f16 : tile n = columns 8n .. 8n+7, this lane holds 8n+2t and 8n+2t+1
+            //   q8_0: tile n = chunk n/2 (16 columns), parity n%2: this lane holds 16(n/2)+4t+(n%2) and +2
+            const int da = Q8 ? 16 * (n >> 1) + 4 * t + (n & 1) : 8 * n + 2 * t;
+            const int db = Q8 ? da + 2 : da + 1;
+            mine[2 + da] = o[n][0] + o[n][2];
+            mine[2 + db] = o[n][1] + o[n][3];
         }
     }
     named_bar_sync(1, kConsumerWarps * 32);
@@ -263,9 +370,49 @@ decode_f16_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
         }
     }
+    if (p.n_chunks == 1 || p.counters == nullptr) return;
+
+    // Second pass without a second launch: every CTA of this (stream, kv head) takes a ticket after
+    // publishing its partials; the one that draws the last ticket folds them all and resets the counter.
+    __threadfence();
+    named_bar_sync(1, kConsumerWarps * 32);
+    const int n_valid = min(p.n_chunks, (len + p.chunk - 1) / p.chunk);
+    if (tid == 0) {
+        int * ctr = p.counters + stream * gridDim.y + kvh;
+        const int ticket = atomicAdd(ctr, 1);
+        const int last   = ticket == n_valid - 1;
+        if (last) *ctr = 0;
+        abort_flag = last ? 2 : 0;  // the shared flag doubles as the broadcast slot: 2 = this CTA merges
+    }
+    named_bar_sync(1, kConsumerWarps * 32);
+    if (*reinterpret_cast<volatile int *>(&abort_flag) != 2) return;
+    __threadfence();
+    {
+        const int hh = tid >> 4, d0 = (tid & 15) * 4;
+        if (hh < p.gqa) {
+            const int     head = kvh * p.gqa + hh;
+            const float * src  = p.partial + ((size_t) stream * p.n_heads + head) * p.n_chunks * kPartialStride;
+            float M = -INFINITY;
+            for (int c = 0; c < n_valid; ++c) M = fmaxf(M, __ldcg(src + c * kPartialStride));
+            float L = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int c = 0; c < n_valid; ++c) {
+                const float * pc = src + c * kPartialStride;
+                const float   mc = __ldcg(pc);
+                const float   f  = mc == -INFINITY ? 0.0f : exp2f(mc - M);
+                L += __ldcg(pc + 1) * f;
+                const float2 lo = __ldcg(reinterpret_cast<const float2 *>(pc + 2 + d0));
+                const float2 hi = __ldcg(reinterpret_cast<const float2 *>(pc + 4 + d0));
+                acc[0] += lo.x * f; acc[1] += lo.y * f; acc[2] += hi.x * f; acc[3] += hi.y * f;
+            }
+            const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+            *reinterpret_cast<float4 *>(p.dst + ((size_t) stream * p.n_heads + head) * kHeadDim + d0) =
+                make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+        }
+    }
 }
 
-// Second pass of split-KV: fold the per-chunk (max, sum, acc) partials of one (stream, head).
+// Second pass of split-KV as a kernel of its own: used when a launch has more (stream, kv head)
+// pairs than the engine has ticket counters.
 __global__ void __launch_bounds__(64) decode_merge_kernel(const DecodeParams p) {
     const int head = blockIdx.x, stream = blockIdx.y, d = threadIdx.x;
     const int len     = stream_len(p, stream);
@@ -311,15 +458,17 @@ size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv
 }
 
 // K/V described by tensor maps (a cache layer, or caller tensors); q/dst/lengths by pointers.
-int launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorMap & map_v, int layer, int max_len,
-                      int n_streams, int n_heads, int n_kv_heads, const int32_t * kv_len, int kv_len_const, int kv_bound,
-                      const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst, float scale, void * workspace,
-                      size_t workspace_bytes, cudaStream_t stream) {
-    static bool attr_done = false;
-    const int   smem      = kStages * kStageBytesF16 + 1024;
-    if (!attr_done) {
-        VOX_CUDA_TRY(cudaFuncSetAttribute(decode_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done = true;
+// map_ks / map_vs are the scale planes of a q8_0 cache (null for f16).
+int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUtensorMap & map_v, const CUtensorMap * map_ks,
+                  const CUtensorMap * map_vs, int layer, int max_len, int n_streams, int n_heads, int n_kv_heads,
+                  const int32_t * kv_len, int kv_len_const, int kv_bound, const float * q, size_t q_nb_head,
+                  size_t q_nb_stream, float * dst, float scale, void * workspace, size_t workspace_bytes,
+                  cudaStream_t stream) {
+    const uint32_t bit = q8 ? (1u << 9) : (1u << 8);
+    if (!(e->attr_mask & bit)) {
+        if (q8) VOX_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring<true>::kSmemBytes));
+        else    VOX_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring<false>::kSmemBytes));
+        e->attr_mask |= bit;
     }
     DecodeParams p;
     p.q = reinterpret_cast<const uint8_t *>(q);
@@ -333,15 +482,26 @@ int launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorM
     VOX_REQUIRE(workspace_bytes >= need && (need == 0 || workspace != nullptr), VOX_ATTN_WORKSPACE_TOO_SMALL,
                 "decode needs %zu workspace bytes, got %zu", need, workspace_bytes);
     p.partial = static_cast<float *>(workspace);
+    // fused second pass needs one ticket counter per (stream, kv head); larger launches use the merge kernel
+    p.counters = (long long) n_streams * n_kv_heads <= kCounterSlots ? e->counters_dev : nullptr;
     dim3 grid(p.n_chunks, n_kv_heads, n_streams);
-    decode_f16_kernel<<<grid, kThreads, smem, stream>>>(map_k, map_v, p);
-    int rc = check_launch(e, "decode_f16_kernel");
+    if (q8) decode_kernel<true><<<grid, kThreads, Ring<true>::kSmemBytes, stream>>>(map_k, map_v, *map_ks, *map_vs, p);
+    else    decode_kernel<false><<<grid, kThreads, Ring<false>::kSmemBytes, stream>>>(map_k, map_v, map_k, map_v, p);
+    int rc = check_launch(e, q8 ? "decode_kernel<q8_0>" : "decode_kernel<f16>");
     if (rc != VOX_ATTN_OK) return rc;
-    if (p.n_chunks > 1) {
+    if (p.n_chunks > 1 && p.counters == nullptr) {
         decode_merge_kernel<<<dim3(n_heads, n_streams), 64, 0, stream>>>(p);
         rc = check_launch(e, "decode_merge_kernel");
     }
     return rc;
+}
+
+int launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorMap & map_v, int layer, int max_len,
+                      int n_streams, int n_heads, int n_kv_heads, const int32_t * kv_len, int kv_len_const, int kv_bound,
+                      const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst, float scale, void * workspace,
+                      size_t workspace_bytes, cudaStream_t stream) {
+    return launch_decode(e, false, map_k, map_v, nullptr, nullptr, layer, max_len, n_streams, n_heads, n_kv_heads, kv_len,
+                         kv_len_const, kv_bound, q, q_nb_head, q_nb_stream, dst, scale, workspace, workspace_bytes, stream);
 }
 
 }  // namespace vox
@@ -369,10 +529,9 @@ int vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace,
     VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->q) & 7) == 0 && a->q_nb_head % 8 == 0 && a->q_nb_stream % 8 == 0,
                 VOX_ATTN_INVALID_ARGUMENT, "q rows must be 8-byte aligned");
     VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->dst) & 15) == 0, VOX_ATTN_INVALID_ARGUMENT, "dst must be 16-byte aligned");
-    VOX_REQUIRE(c->cfg.type == VOX_TYPE_F16, VOX_ATTN_UNSUPPORTED, "q8_0 decode is not built yet");
-    return launch_decode_f16(e, c->map_k, c->map_v, a->layer, c->cfg.max_len, a->n_streams, a->n_heads, c->cfg.n_kv_heads,
-                             a->kv_len, 0, a->kv_bound, a->q, a->q_nb_head, a->q_nb_stream, a->dst, a->scale, workspace,
-                             workspace_bytes, static_cast<cudaStream_t>(stream));
+    return launch_decode(e, c->cfg.type == VOX_TYPE_Q8_0, c->map_k, c->map_v, &c->map_ks, &c->map_vs, a->layer, c->cfg.max_len, a->n_streams, a->n_heads, c->cfg.n_kv_heads,
+                         a->kv_len, 0, a->kv_bound, a->q, a->q_nb_head, a->q_nb_stream, a->dst, a->scale, workspace,
+                         workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -98,6 +98,16 @@ int vox_engine_create(int device, vox_engine ** out) {
         return VOX_ATTN_CUDA_ERROR;
     }
     e->encode = reinterpret_cast<encode_tiled_fn>(fn);
+    err = cudaMalloc(reinterpret_cast<void **>(&e->counters_dev), sizeof(int) * kCounterSlots);
+    if (err == cudaSuccess) err = cudaMemset(e->counters_dev, 0, sizeof(int) * kCounterSlots);
+    if (err != cudaSuccess) {
+        set_error("ticket counter allocation failed: %s", cudaGetErrorString(err));
+        cudaGetLastError();
+        if (e->counters_dev) cudaFree(e->counters_dev);
+        cudaFreeHost(e->status_host);
+        delete e;
+        return VOX_ATTN_OUT_OF_MEMORY;
+    }
     *out      = e;
     return VOX_ATTN_OK;
 }
@@ -107,6 +117,7 @@ void vox_engine_destroy(vox_engine * e) {
     cudaSetDevice(e->device);
     if (e->stage_dev) cudaFree(e->stage_dev);
     if (e->stage_ws) cudaFree(e->stage_ws);
+    if (e->counters_dev) cudaFree(e->counters_dev);
     if (e->status_host) cudaFreeHost(e->status_host);
     delete e;
 }
@@ -119,6 +130,7 @@ int vox_engine_sync_status(vox_engine * e, void * stream) {
     const int word = *reinterpret_cast<volatile int *>(e->status_host);
     if (word != 0) {
         *reinterpret_cast<volatile int *>(e->status_host) = 0;
+        cudaMemset(e->counters_dev, 0, sizeof(int) * kCounterSlots);  // a kernel that gave up may have left tickets behind
         set_error("device status word 0x%x: %s", word,
                   (word & kStatusTimeout) ? "a bounded wait on a copy barrier ran out" : "kernel reported bad state");
         return VOX_ATTN_TIMEOUT;

@@ -172,8 +172,10 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t S = c.n_streams, D = c.head_dim;
     const float  scale = 1.0f / sqrtf((float) c.head_dim);  // src/minicpm.cpp:708-710
-    const int    L = c.base_layers + c.res_layers;
-    if (L > 0) VOX_REQUIRE(b->lm_q && b->lm_out && (!advance || (b->lm_k_new && b->lm_v_new)), VOX_ATTN_INVALID_ARGUMENT, "LM step buffers are null");
+    // a null lm_q skips the LM stacks, a null dit_q skips the LocDiT patch (partial steps for profiling)
+    const int    L = b->lm_q ? c.base_layers + c.res_layers : 0;
+    VOX_REQUIRE(L > 0 || !advance, VOX_ATTN_INVALID_ARGUMENT, "advance needs the LM step buffers");
+    if (L > 0) VOX_REQUIRE(b->lm_out && (!advance || (b->lm_k_new && b->lm_v_new)), VOX_ATTN_INVALID_ARGUMENT, "LM step buffers are null");
     if (advance) {
         VOX_REQUIRE(g->kv_bound + 1 <= c.max_len, VOX_ATTN_INVALID_ARGUMENT, "a stream would outgrow the cache capacity %d", c.max_len);
     }
@@ -211,8 +213,8 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         for (auto & x : g->kv_len_host) x += 1;
         g->kv_bound += 1;
     }
-    if (c.cfm_steps > 0 && c.locdit_layers > 0) {
-        VOX_REQUIRE(b->dit_q && b->dit_k && b->dit_v && b->dit_out, VOX_ATTN_INVALID_ARGUMENT, "LocDiT step buffers are null");
+    if (c.cfm_steps > 0 && c.locdit_layers > 0 && b->dit_q) {
+        VOX_REQUIRE(b->dit_k && b->dit_v && b->dit_out, VOX_ATTN_INVALID_ARGUMENT, "LocDiT step buffers are null");
         const size_t q_step  = S * c.locdit_layers * 2 * c.locdit_seq * c.n_heads * D;
         const size_t kv_step = S * c.locdit_layers * 2 * c.locdit_seq * c.n_kv_heads * D;
         for (int t = 0; t < c.cfm_steps; ++t) {
