@@ -49,6 +49,9 @@ def parse():
     p.add_argument("--cpu-sample-streams", type=int, default=24)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--prefill-shapes", default="512x1,512x8", help="LxB list for --workload prefill")
+    p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1"],
+                   help="serving = the headline line; the others time one more configuration each on one GPU")
     return p.parse_args()
 
 
@@ -167,6 +170,79 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------ other configurations (one GPU)
+
+def aux_workload(args, pkg, torch):
+    """Times the other configurations: causal prefill (512 tokens, 24 layers, batch 1 and 8), the long-form decode
+    sweep (KV 1k-8k, batch 1 and 32, f16 and q8_0, 24+6 layers) and single-stream decode at KV 256 (24 layers).
+    Launch sequences are issued from C (stream groups) or replayed from a CUDA graph, so host launch cost is not
+    what is measured.  L2 is scrubbed between repetitions for the "cold" figures."""
+    eng = pkg.Engine(torch.cuda.current_device())
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    hbm, tens = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    stream = torch.cuda.current_stream()
+    scrub = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")  # > 126 MB L2
+
+    def timed(fn, reps, cold):
+        fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(reps):
+            if cold:
+                scrub.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / reps  # ms
+
+    out = {"workload": args.workload, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tens}, "results": []}
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    if args.workload == "prefill":
+        layers = BASE_LAYERS
+        for L, B in [(int(x.split("x")[0]), int(x.split("x")[1])) for x in args.prefill_shapes.split(",")]:
+            q = torch.randn((layers, B, H, L, D), device="cuda", generator=gen).half().float()
+            k = torch.randn((layers, B, HK, L, D), device="cuda", generator=gen).half()
+            v = torch.randn((layers, B, HK, L, D), device="cuda", generator=gen).half()
+            o = torch.empty((layers, B, L, H, D), device="cuda")
+            for l in range(layers):  # warm-up outside capture (attribute set-up, descriptors)
+                eng.prefill(q[l], k[l], v[l], dst=o[l])
+            eng.sync_status()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for l in range(layers):
+                    eng.prefill(q[l], k[l], v[l], dst=o[l])
+            ms = timed(graph.replay, 20, cold=False)
+            flops = layers * B * 4.0 * H * D * L * (L + 1) / 2
+            out["results"].append({"config": f"prefill L={L} B={B} x {layers} layers", "ms": ms, "us_per_layer": ms * 1e3 / layers,
+                                   "tflops_causal_useful": flops / (ms * 1e-3) / 1e12,
+                                   "frac_of_measured_bf16_peak": flops / (ms * 1e-3) / 1e12 / tens})
+    else:
+        combos = [(256, 1, "f16", 24, 0)] if args.workload == "decode_c1" else \
+            [(L, B, t, BASE_LAYERS, RES_LAYERS) for t in ("f16", "q8_0") for B in (1, 32) for L in (1024, 2048, 4096, 8192)]
+        for L, B, t, nb, nr in combos:
+            g = pkg.Group(eng, n_streams=B, max_len=L, kv_type=pkg.F16 if t == "f16" else pkg.Q8_0, base_layers=nb, res_layers=nr,
+                          n_heads=H, n_kv_heads=HK, locdit_layers=0, cfm_steps=0)
+            lens = np.full(B, L, np.int32)
+            g.set_kv_len(lens)
+            g.fill_synthetic(seed=L + B)
+            shapes = g.buffer_shapes()
+            bufs = {n: torch.randn(s, device="cuda", generator=gen) for n, s in shapes.items() if n.startswith("lm_")}
+            step = lambda: g.step(bufs, advance=False)
+            nbytes = (nb + nr) * lm_bytes_per_layer(lens, t)
+            warm, cold = timed(step, 20, cold=False), timed(step, 10, cold=True)
+            eng.sync_status()
+            out["results"].append({"config": f"decode kv={L} B={B} {t} x {nb + nr} layers", "bytes": nbytes,
+                                   "warm_us_per_layer": warm * 1e3 / (nb + nr), "cold_us_per_layer": cold * 1e3 / (nb + nr),
+                                   "warm_gb_s": nbytes / (warm * 1e-3) / 1e9, "cold_gb_s": nbytes / (cold * 1e-3) / 1e9,
+                                   "cold_frac_of_measured_hbm": nbytes / (cold * 1e-3) / 1e9 / hbm,
+                                   "cold_frac_of_8000": nbytes / (cold * 1e-3) / 1e9 / 8000.0})
+            g.close()
+    return out
+
+
 # ------------------------------------------------------------------ engine arm
 
 def main():
@@ -206,6 +282,11 @@ def main():
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
+
+    if args.workload != "serving":
+        if rank == 0:
+            print(json.dumps(aux_workload(args, pkg, torch)))
+        return
 
     # streams of this rank
     if args.scaling == "weak":

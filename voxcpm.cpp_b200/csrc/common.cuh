@@ -85,7 +85,7 @@ inline int check_launch(vox_engine * e, const char * what) {
 
 #ifdef __CUDACC__
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // polls before a wait gives up (each poll may sleep)
+constexpr long long kWaitCycles = 4000000000LL;  // SM clock cycles before a wait gives up (~2 s at 1.9 GHz)
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -117,13 +117,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Returns false when the phase did not complete within kSpinLimit polls.
+// Returns false when the phase did not complete in time.  try_wait already parks the thread in
+// hardware for a short while, so the loop polls back to back (waking late costs more than polling);
+// every 1024 failed polls the elapsed clock is checked against kWaitCycles (about two seconds).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) __nanosleep(64);
+        if ((i & 1023u) == 0 && clock64() - t0 > kWaitCycles) return false;
     }
-    return false;
 }
 
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap * map, uint32_t bar, int c0, int c1, int c2,

@@ -6,19 +6,24 @@
 // On the CPU this is ggml's tiled path (third_party/ggml/src/ggml-cpu/ops.cpp:8347-8633); ggml-cuda
 // would run the mma.sync kernel flash_attn_ext_f16 (fattn-mma-f16.cuh:1459-1628).
 //
-// One CTA = 128 query rows of one head.  Six warps:
-//   warps 0-3  softmax: thread r owns query row r = TMEM lane r.  Per 128-key tile it reads the
-//              scores S from TMEM (tcgen05.ld), takes the row maximum, writes P = 2^(c*(S - max)) as
-//              f16 into shared memory in the 128-byte-swizzled K-major layout the tensor core reads,
-//              then adds the tile's P.V (read back from TMEM) into its f32 output row in registers
-//              with the usual running-max rescale.
-//   warp 4     producer: one lane issues cp.async.bulk.tensor copies of 128-row K and V tiles into a
-//              two-stage ring.
-//   warp 5     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128): S = Q.K^T (N=128, 4 k-steps)
-//              into TMEM columns 0-127 and O_tile = P.V (N=64, 8 k-steps, V read MN-major straight from
-//              the row-major tile) into columns 128-191; completion is signalled with tcgen05.commit.
+// One CTA = 128 query rows of one head.  Ten warps:
+//   warps 0-7  softmax: two threads per query row (row r = TMEM lane r).  Warps 0-3 own score columns
+//              0-63 and output columns 0-31, warps 4-7 the other halves.  Per 128-key tile a thread
+//              reads its scores from TMEM (tcgen05.ld), the pair agrees on the row maximum through shared
+//              memory, each writes P = 2^(c*S - max) as f16 into shared memory in the 128-byte-swizzled
+//              K-major layout the tensor core reads.  The output row and the row sums accumulate in TMEM
+//              over all tiles (no per-tile read-back); they are rescaled in place only when the running
+//              maximum jumps by more than 2^8, and read once at the end.
+//   warp 8     producer: one lane issues cp.async.bulk.tensor copies of 128-row K tiles (two-stage ring)
+//              and V tiles (one buffer, refilled as soon as the previous P.V has retired).
+//   warp 9     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128): S = Q.K^T (N=128, 4 k-steps)
+//              into TMEM columns 0-127, O_tile = P.V (N=64, 8 k-steps, V read MN-major straight from the
+//              row-major tile) into columns 128-191, and P.1 (N=16, a tile of ones) into columns 192-207,
+//              which yields the row sums of exactly the rounded weights the tensor core used.
+//              Completion is signalled with tcgen05.commit.
 // Q arrives as f32 and is rounded to f16 once per CTA (exact when it already holds f16 values);
-// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.
+// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  100 KB of shared memory and
+// 256 TMEM columns per CTA: two CTAs share an SM, one computing softmax while the other waits on copies.
 // Every wait is bounded; on expiry the status word is set and all roles fall through to the common
 // exit, where the TMEM columns are released.
 #include "common.cuh"
@@ -35,10 +40,12 @@ namespace {
 
 constexpr int kTile      = 128;            // query rows per CTA and keys per tile
 constexpr int kTileBytes = kTile * 128;    // one [128][64] f16 tile
-constexpr int kKvStages  = 2;
-constexpr int kThreadsPf = 6 * 32;
-constexpr int kTmemCols  = 256;            // S: columns 0-127, O tile: 128-191
-constexpr int kSmemPf    = kTileBytes * (1 + 2 * kKvStages + 2) + 1024;  // Q, K/V ring, P (two 64-key halves)
+constexpr int kKStages   = 2;              // K tiles are prefetched two ahead, V one ahead
+constexpr int kSoftmaxThreads = 256;
+constexpr int kThreadsPf = kSoftmaxThreads + 64;
+constexpr int kTmemCols  = 256;            // S: columns 0-127, O tile: 128-191, row sums: 192-207
+constexpr int kOnesBytes = 4096;           // a [16][128] f16 tile of ones (any layout: every element is 1)
+constexpr int kSmemPf    = kTileBytes * (1 + kKStages + 1 + 2) + kOnesBytes + 1024;  // Q, K ring, V, P (two 64-key halves), ones
 
 struct PrefillParams {
     const uint8_t * q;
@@ -88,6 +95,60 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 64 consecutive columns: two loads in flight, one wait
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[32 * h + 0]), "=r"(r[32 * h + 1]), "=r"(r[32 * h + 2]), "=r"(r[32 * h + 3]), "=r"(r[32 * h + 4]), "=r"(r[32 * h + 5]),
+              "=r"(r[32 * h + 6]), "=r"(r[32 * h + 7]), "=r"(r[32 * h + 8]), "=r"(r[32 * h + 9]), "=r"(r[32 * h + 10]), "=r"(r[32 * h + 11]),
+              "=r"(r[32 * h + 12]), "=r"(r[32 * h + 13]), "=r"(r[32 * h + 14]), "=r"(r[32 * h + 15]), "=r"(r[32 * h + 16]), "=r"(r[32 * h + 17]),
+              "=r"(r[32 * h + 18]), "=r"(r[32 * h + 19]), "=r"(r[32 * h + 20]), "=r"(r[32 * h + 21]), "=r"(r[32 * h + 22]), "=r"(r[32 * h + 23]),
+              "=r"(r[32 * h + 24]), "=r"(r[32 * h + 25]), "=r"(r[32 * h + 26]), "=r"(r[32 * h + 27]), "=r"(r[32 * h + 28]), "=r"(r[32 * h + 29]),
+              "=r"(r[32 * h + 30]), "=r"(r[32 * h + 31])
+            : "r"(taddr + 32 * h)
+            : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float x) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(x)) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    return __uint_as_float(r);
+}
+
+// 2^x on the special-function unit (one MUFU instruction; arguments here are <= 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // Shared-memory matrix descriptor (64-bit) of a 128-byte-swizzled tile whose 8-row groups are 1024
 // bytes apart: start address, leading/stride byte offsets (>> 4), descriptor version 1, layout type 2.
@@ -106,16 +167,18 @@ constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
     return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (kTile >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(kThreadsPf, 1)
+__global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[2 * kKvStages + 6];
+    __shared__ uint64_t bars[2 * kKStages + 8];
+    __shared__ float    half_max[2][2][kTile];  // [tile parity][column half][row]
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sKV = smem_base + kTileBytes, sP = sKV + 2 * kKvStages * kTileBytes;
+    const uint32_t sQ = smem_base, sK0 = smem_base + kTileBytes, sV = sK0 + kKStages * kTileBytes, sP = sV + kTileBytes,
+                   sOnes = sP + 2 * kTileBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // heavier (later) query tiles first so that the causal triangle drains evenly
@@ -126,24 +189,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     const int last_row = min(q0 + kTile, p.n_q) - 1;
     const int n_tiles  = min((p.n_kv + kTile - 1) / kTile, (last_row + p.causal_offset) / kTile + 1);
 
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kKvStages]);
-    const uint32_t bQ = smem_u32(&bars[2 * kKvStages]), bSready = bQ + 8, bSfree = bQ + 16, bPready = bQ + 24, bPVdone = bQ + 32,
-                   bOfree = bQ + 40;
+    const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = smem_u32(&bars[kKStages]);
+    const uint32_t bQ = smem_u32(&bars[2 * kKStages]), bSready = bQ + 8, bSfree = bQ + 16, bPready = bQ + 24, bPVdone = bQ + 32,
+                   bOfree = bQ + 40, vfull = bQ + 48, vempty = bQ + 56;
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < kKvStages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
+        for (int s = 0; s < kKStages; ++s) {
+            mbar_init(kfull0 + 8 * s, 1);
+            mbar_init(kempty0 + 8 * s, 1);
         }
-        mbar_init(bQ, 128);
+        mbar_init(vfull, 1);
+        mbar_init(vempty, 1);
+        mbar_init(bQ, kSoftmaxThreads / 32);  // one arrival per softmax warp
         mbar_init(bSready, 1);
-        mbar_init(bSfree, 128);
-        mbar_init(bPready, 128);
+        mbar_init(bSfree, kSoftmaxThreads / 32);
+        mbar_init(bPready, kSoftmaxThreads / 32);
         mbar_init(bPVdone, 1);
-        mbar_init(bOfree, 128);
         fence_mbar_init();
     }
-    if (warp == 5) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    if (warp == 9) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -155,57 +219,71 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     };
     auto aborted = [&]() { return *reinterpret_cast<volatile int *>(&abort_flag) != 0; };
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             for (int j = 0; j < n_tiles && !aborted(); ++j) {
-                const int s = j % kKvStages;
-                if (j >= kKvStages && !mbar_wait_bounded(empty0 + 8 * s, ((j / kKvStages) - 1) & 1)) { give_up(); break; }
-                const uint32_t dst = sKV + s * 2 * kTileBytes;
-                mbar_expect_tx(full0 + 8 * s, 2 * kTileBytes);
-                tma_load_5d(dst, &map_k, full0 + 8 * s, 0, j * kTile, kvh, batch, 0);
-                tma_load_5d(dst + kTileBytes, &map_v, full0 + 8 * s, 0, j * kTile, kvh, batch, 0);
+                const int s = j % kKStages;
+                if (j >= kKStages && !mbar_wait_bounded(kempty0 + 8 * s, ((j / kKStages) - 1) & 1)) { give_up(); break; }
+                mbar_expect_tx(kfull0 + 8 * s, kTileBytes);
+                tma_load_5d(sK0 + s * kTileBytes, &map_k, kfull0 + 8 * s, 0, j * kTile, kvh, batch, 0);
+                if (j >= 1 && !mbar_wait_bounded(vempty, (j - 1) & 1)) { give_up(); break; }
+                mbar_expect_tx(vfull, kTileBytes);
+                tma_load_5d(sV, &map_v, vfull, 0, j * kTile, kvh, batch, 0);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc_f16(kTile, false), idesc_pv = idesc_f16(kHeadDim, true);
+            constexpr uint32_t idesc_qk = idesc_f16(kTile, false), idesc_pv = idesc_f16(kHeadDim, true), idesc_sum = idesc_f16(16, false);
             bool ok = mbar_wait_bounded(bQ, 0);
             if (!ok) give_up();
-            for (int j = 0; j < n_tiles && ok && !aborted(); ++j) {
-                const int      s  = j % kKvStages;
-                const uint32_t sK = sKV + s * 2 * kTileBytes, sV = sK + kTileBytes;
-                if (!mbar_wait_bounded(full0 + 8 * s, (j / kKvStages) & 1)) { give_up(); break; }
-                if (j > 0 && !mbar_wait_bounded(bSfree, (j - 1) & 1)) { give_up(); break; }
+            // S = Q K^T of tile j: four k-steps of 16 along head_dim, 32 bytes each inside the swizzle atom.
+            // It is issued as soon as the softmax threads have taken S of tile j-1 out of TMEM, i.e. while
+            // they are still busy with the exponentials of tile j-1.
+            auto issue_qk = [&](int j) {
+                const int      s  = j % kKStages;
+                const uint32_t sK = sK0 + s * kTileBytes;
+                if (!mbar_wait_bounded(kfull0 + 8 * s, (j / kKStages) & 1)) return false;
+                if (j > 0 && !mbar_wait_bounded(bSfree, (j - 1) & 1)) return false;
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 4; ++k)  // S = Q K^T: four k-steps of 16 along head_dim, 32 bytes each inside the swizzle atom
+                for (int k = 0; k < 4; ++k)
                     tc_mma_f16(tmem, smem_desc_sw128(sQ + 32 * k), smem_desc_sw128(sK + 32 * k), idesc_qk, k > 0);
                 tc_commit(bSready);
+                tc_commit(kempty0 + 8 * s);  // the K tile may be refilled once Q.K^T has retired
+                return true;
+            };
+            if (ok && !issue_qk(0)) { give_up(); ok = false; }
+            for (int j = 0; j < n_tiles && ok && !aborted(); ++j) {
+                if (j + 1 < n_tiles && !issue_qk(j + 1)) { give_up(); break; }
+                if (!mbar_wait_bounded(vfull, j & 1)) { give_up(); break; }
                 if (!mbar_wait_bounded(bPready, j & 1)) { give_up(); break; }
-                if (j > 0 && !mbar_wait_bounded(bOfree, (j - 1) & 1)) { give_up(); break; }
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 8; ++k)  // O_tile = P V: eight k-steps of 16 keys; P half-tiles of 64 keys, V rows 16 at a time
-                    tc_mma_f16(tmem + kTile, smem_desc_sw128(sP + (k >> 2) * kTileBytes + 32 * (k & 3)),
-                               smem_desc_sw128(sV + 2048 * k), idesc_pv, k > 0);
+                for (int k = 0; k < 8; ++k) {  // eight k-steps of 16 keys; P half-tiles of 64 keys, V rows 16 at a time
+                    const uint64_t pd = smem_desc_sw128(sP + (k >> 2) * kTileBytes + 32 * (k & 3));
+                    tc_mma_f16(tmem + kTile, pd, smem_desc_sw128(sV + 2048 * k), idesc_pv, j > 0 || k > 0);     // O += P V
+                    tc_mma_f16(tmem + kTile + kHeadDim, pd, smem_desc_sw128(sOnes), idesc_sum, j > 0 || k > 0);  // row sums += P 1
+                }
                 tc_commit(bPVdone);
-                tc_commit(empty0 + 8 * s);
+                tc_commit(vempty);
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax warps: thread = query row
-        const int  row   = tid;  // 0..127 == TMEM lane
+        // ------------------------------------------------------------------ softmax warps: two threads per query row
+        const int  row   = 32 * (warp & 3) + lane;  // == TMEM lane; a warp may only touch lanes 32*(warp%4)..+31
+        const int  half  = warp >> 2;               // 0: score columns 0-63 / output columns 0-31, 1: the rest
         const int  qpos  = q0 + row;
         const bool live  = qpos < p.n_q;
         {
-            // Q row -> f16, written as eight 16-byte chunks at their swizzled places
+            // this thread's half of the Q row -> f16, four 16-byte chunks at their swizzled places; and the ones tile
             uint8_t * dstrow = smem_gen + row * 128;
             const float * src = reinterpret_cast<const float *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) head * p.q_nb2 +
                                                                 (size_t) batch * p.q_nb3);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int u = 0; u < 4; ++u) {
+                const int c = 4 * half + u;
                 uint4 w = make_uint4(0, 0, 0, 0);
                 if (live) {
                     const float2 a = *reinterpret_cast<const float2 *>(src + 8 * c), b = *reinterpret_cast<const float2 *>(src + 8 * c + 2);
@@ -214,89 +292,101 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
                 *reinterpret_cast<uint4 *>(dstrow + ((c ^ (row & 7)) << 4)) = w;
             }
+            const uint32_t one2 = 0x3C003C00u;
+            *reinterpret_cast<uint4 *>(smem_gen + (sOnes - smem_base) + tid * 16) = make_uint4(one2, one2, one2, one2);
             fence_proxy_async_smem();
-            mbar_arrive(bQ);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bQ);
         }
-        const uint32_t t_row = tmem + ((uint32_t) (warp * 32) << 16);  // this warp's lane quarter
-        const int      limit = min(qpos + p.causal_offset, p.n_kv - 1);  // last key this row may see
-        float acc[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f;
-        bool  ok = true;
-        for (int j = 0; j < n_tiles && ok && !aborted(); ++j) {
-            if (!mbar_wait_bounded(bSready, j & 1)) { give_up(); break; }
+        const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);  // this warp's lane quarter
+        const int      limit = min(qpos + p.causal_offset, p.n_kv - 1);      // last key this row may see
+        // The output row and the row sum accumulate in TMEM across all key tiles, both scaled by
+        // 2^(-m_ref): their ratio does not depend on m_ref, so the reference maximum only has to keep
+        // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
+        // tile's maximum exceeds it by more than 2^8, which after the first tile is rare.
+        float m_ref = -INFINITY;
+        bool  ok    = true;
+        for (int j = 0; j < n_tiles && !aborted(); ++j) {
+            if (!mbar_wait_bounded(bSready, j & 1)) { give_up(); ok = false; break; }
             tc_fence_after();
-            const int  k0     = j * kTile;
-            const bool masked = k0 + kTile - 1 > min(q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: any row of the tile may be cut
-            float v[32];
-            // pass 1: row maximum of this tile
+            const int  k0     = j * kTile + 64 * half;  // first key of this thread's columns
+            const bool masked = j * kTile + kTile - 1 > min(q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
+            float v[64];
+            tmem_ld64(t_row + 64 * half, v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bSfree);  // S is in registers: the next tile's Q.K^T may overwrite it
             float tmax = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(t_row + 32 * c, v);
+            if (masked) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float x = (masked && k0 + 32 * c + i > limit) ? -INFINITY : v[i];
-                    tmax = fmaxf(tmax, x);
-                }
+                for (int i = 0; i < 64; ++i) v[i] = k0 + i > limit ? -INFINITY : v[i];
             }
-            const float m_new = fmaxf(m, tmax * p.scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            const float alpha = m == -INFINITY ? 0.0f : exp2f(m - m_use);
-            m = m_new;
-            // pass 2: P = 2^(c*S - max), f16, into the two 64-key halves of the P tile
-            float psum = 0.0f;
-            uint8_t * prow = smem_gen + (sP - smem_base) + row * 128;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(t_row + 32 * c, v);
-                uint32_t h[16];
+            {
+                float t0 = v[0], t1 = v[1], t2 = v[2], t3 = v[3];  // four chains instead of one 64-deep dependency
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float x0 = (masked && k0 + 32 * c + i > limit) ? 0.0f : exp2f(fmaf(v[i], p.scale_log2, -m_use));
-                    const float x1 = (masked && k0 + 32 * c + i + 1 > limit) ? 0.0f : exp2f(fmaf(v[i + 1], p.scale_log2, -m_use));
-                    const __half2 hh = __floats2half2_rn(x0, x1);
-                    h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-                    const float2 back = __half22float2(hh);
-                    psum += back.x + back.y;  // the sum of the weights the tensor core will actually use
+                for (int i = 4; i < 64; i += 4) {
+                    t0 = fmaxf(t0, v[i]); t1 = fmaxf(t1, v[i + 1]); t2 = fmaxf(t2, v[i + 2]); t3 = fmaxf(t3, v[i + 3]);
                 }
-                uint8_t * half_tile = prow + (c >> 1) * kTileBytes;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int chunk = (c & 1) * 4 + u;
-                    *reinterpret_cast<uint4 *>(half_tile + ((chunk ^ (row & 7)) << 4)) = make_uint4(h[4 * u], h[4 * u + 1], h[4 * u + 2], h[4 * u + 3]);
-                }
+                tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
             }
-            tc_fence_before();
-            mbar_arrive(bSfree);  // S may be overwritten by the next tile's Q.K^T
+            half_max[j & 1][half][row] = tmax;
+            named_bar_sync(1, kSoftmaxThreads);
+            tmax = fmaxf(tmax, half_max[j & 1][half ^ 1][row]) * p.scale_log2;
+            // the previous tile's P.V must have retired before P is overwritten (and before O is touched)
+            if (j > 0 && !mbar_wait_bounded(bPVdone, (j - 1) & 1)) { give_up(); ok = false; break; }
+            // tcgen05.ld/st are warp-collective: the decision to rescale is taken per warp (any lane), and lanes
+            // that do not need it take part with a factor of 1
+            const bool raise = j > 0 && tmax > m_ref + 8.0f;
+            if (j == 0) {
+                m_ref = tmax;  // key 0 is visible to every row: finite
+            } else if (__any_sync(0xffffffffu, raise)) {
+                tc_fence_after();
+                const float f = raise ? ex2_approx(m_ref - tmax) : 1.0f;
+                if (raise) m_ref = tmax;
+                float o[32];
+                tmem_ld32(t_row + kTile + 32 * half, o);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] *= f;
+                tmem_st32(t_row + kTile + 32 * half, o);
+                if (half == 0) tmem_st1(t_row + kTile + kHeadDim, tmem_ld1(t_row + kTile + kHeadDim) * f);
+                tc_fence_before();
+            }
+            // P = 2^(c*S - m_ref), f16, into this thread's 64-key half of the P tile, 8 keys (16 bytes) at a time
+            uint8_t * prow = smem_gen + (sP - smem_base) + half * kTileBytes + row * 128;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                uint32_t h[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    h[i] = pack_half2(ex2_approx(fmaf(v[8 * u + 2 * i], p.scale_log2, -m_ref)),
+                                      ex2_approx(fmaf(v[8 * u + 2 * i + 1], p.scale_log2, -m_ref)));
+                *reinterpret_cast<uint4 *>(prow + ((u ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
             fence_proxy_async_smem();
-            mbar_arrive(bPready);  // P is visible to the tensor core
-            l = l * alpha + psum;
-            if (!mbar_wait_bounded(bPVdone, j & 1)) { give_up(); break; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                tmem_ld32(t_row + kTile + 32 * c, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[32 * c + i] = fmaf(acc[32 * c + i], alpha, v[i]);
-            }
-            tc_fence_before();
-            mbar_arrive(bOfree);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bPready);  // this warp's part of P is visible to the tensor core
         }
-        if (live && !aborted()) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            float4 * out = reinterpret_cast<float4 *>(p.dst + (((size_t) batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim);
+        if (ok && !aborted() && !mbar_wait_bounded(bPVdone, (n_tiles - 1) & 1)) { give_up(); ok = false; }
+        if (ok && !aborted()) {
+            // warp-collective TMEM reads by every lane; only rows that exist are stored
+            tc_fence_after();
+            const float l = tmem_ld1(t_row + kTile + kHeadDim);  // sum of exactly the rounded weights the tensor core used
+            float o[32];
+            tmem_ld32(t_row + kTile + 32 * half, o);
+            if (live) {
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                float4 * out = reinterpret_cast<float4 *>(p.dst + (((size_t) batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim + 32 * half);
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                out[i] = make_float4(acc[4 * i] * inv, acc[4 * i + 1] * inv, acc[4 * i + 2] * inv, acc[4 * i + 3] * inv);
+                for (int i = 0; i < 8; ++i)
+                    out[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+            }
         }
     }
 
     // common exit: tensor-core work has been waited for by the softmax warps; release TMEM
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
