@@ -11,6 +11,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <utility>
 
 #include "vox_attn.h"
 
@@ -71,6 +72,24 @@ namespace vox {
 int make_tensor_map(const vox_engine * e, CUtensorMap * out, void * base, CUtensorMapDataType dt, const uint64_t dims[5],
                     const uint64_t strides[4], const uint32_t box[5], CUtensorMapSwizzle swizzle);
 
+// Launch with programmatic dependent launch: the grid may be scheduled while the previous kernel of the
+// stream is still draining, and its threads block in pdl_wait() until that kernel has completed and its
+// writes are visible.  Every kernel launched this way calls pdl_wait() before its first global access.
+// VOX_NO_PDL=1 in the environment turns the attribute off.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);  // errors surface through check_launch
+}
+
 inline int check_launch(vox_engine * e, const char * what) {
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
@@ -86,6 +105,10 @@ inline int check_launch(vox_engine * e, const char * what) {
 #ifdef __CUDACC__
 
 constexpr long long kWaitCycles = 4000000000LL;  // SM clock cycles before a wait gives up (~2 s at 1.9 GHz)
+
+// programmatic dependent launch: wait for the preceding kernel of the stream / let the next one be scheduled
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -126,6 +149,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 0 && clock64() - t0 > kWaitCycles) return false;
+    }
+}
+
+// Same contract, polling with the non-blocking test_wait: lowest wake-up latency, for the few
+// threads whose wait sits on a kernel's critical path.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((i & 4095u) == 0 && clock64() - t0 > kWaitCycles) return false;
     }
 }
 

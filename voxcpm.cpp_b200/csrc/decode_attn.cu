@@ -95,6 +95,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
     const int chunk_id = blockIdx.x, kvh = blockIdx.y, stream = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_wait();  // the append of this layer (and the length update before it) must have landed
+    pdl_launch_dependents();
     const int len = stream_len(p, stream);
     const int c0  = chunk_id * p.chunk;
     if (c0 >= len) {
@@ -415,6 +417,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 // pairs than the engine has ticket counters.
 __global__ void __launch_bounds__(64) decode_merge_kernel(const DecodeParams p) {
     const int head = blockIdx.x, stream = blockIdx.y, d = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
     const int len     = stream_len(p, stream);
     const int n_valid = min(p.n_chunks, (len + p.chunk - 1) / p.chunk);
     const float * src = p.partial + ((size_t) stream * p.n_heads + head) * p.n_chunks * kPartialStride;
@@ -485,12 +489,12 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     // fused second pass needs one ticket counter per (stream, kv head); larger launches use the merge kernel
     p.counters = (long long) n_streams * n_kv_heads <= kCounterSlots ? e->counters_dev : nullptr;
     dim3 grid(p.n_chunks, n_kv_heads, n_streams);
-    if (q8) decode_kernel<true><<<grid, kThreads, Ring<true>::kSmemBytes, stream>>>(map_k, map_v, *map_ks, *map_vs, p);
-    else    decode_kernel<false><<<grid, kThreads, Ring<false>::kSmemBytes, stream>>>(map_k, map_v, map_k, map_v, p);
+    if (q8) launch_pdl(decode_kernel<true>, grid, dim3(kThreads), Ring<true>::kSmemBytes, stream, map_k, map_v, *map_ks, *map_vs, p);
+    else    launch_pdl(decode_kernel<false>, grid, dim3(kThreads), Ring<false>::kSmemBytes, stream, map_k, map_v, map_k, map_v, p);
     int rc = check_launch(e, q8 ? "decode_kernel<q8_0>" : "decode_kernel<f16>");
     if (rc != VOX_ATTN_OK) return rc;
     if (p.n_chunks > 1 && p.counters == nullptr) {
-        decode_merge_kernel<<<dim3(n_heads, n_streams), 64, 0, stream>>>(p);
+        launch_pdl(decode_merge_kernel, dim3(n_heads, n_streams), dim3(64), 0, stream, p);
         rc = check_launch(e, "decode_merge_kernel");
     }
     return rc;

@@ -3,6 +3,7 @@
 // ggml-cuda's per-context state play for the reference's attention path.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -15,6 +16,14 @@ void set_error(const char * fmt, ...) {
     va_start(ap, fmt);
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
     va_end(ap);
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char * s = getenv("VOX_NO_PDL");
+        return !(s && s[0] == '1');
+    }();
+    return on;
 }
 
 int make_tensor_map(const vox_engine * e, CUtensorMap * out, void * base, CUtensorMapDataType dt, const uint64_t dims[5],

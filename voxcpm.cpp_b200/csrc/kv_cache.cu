@@ -55,6 +55,8 @@ __global__ void kv_append_kernel(CacheView c, int layer, int n_streams, int n_to
                                  int * status) {
     const int warps_per_block = blockDim.x >> 5;
     const int lane            = threadIdx.x & 31;
+    pdl_wait();  // positions come from the kernel before; earlier readers of these cache rows are done
+    pdl_launch_dependents();
     const long long n_rows    = (long long) n_streams * n_tok * c.n_kv_heads;
     for (long long row = (long long) blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < n_rows;
          row += (long long) gridDim.x * warps_per_block) {
@@ -241,9 +243,8 @@ int vox_kv_append(vox_kv_cache * c, int layer, int n_streams, int n_tok, const i
                 VOX_ATTN_INVALID_ARGUMENT, "new K/V rows must be 8-byte aligned");
     const long long rows = (long long) n_streams * n_tok * c->cfg.n_kv_heads;
     const int blocks     = (int) std::min<long long>((rows + 7) / 8, (long long) c->e->sm_count * 8);
-    kv_append_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(view_of(c), layer, n_streams, n_tok, positions,
-                                                                           pos0, k, v, nb_head, nb_tok, nb_stream,
-                                                                           c->e->status_dev);
+    launch_pdl(kv_append_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), view_of(c), layer, n_streams, n_tok,
+               positions, pos0, k, v, nb_head, nb_tok, nb_stream, c->e->status_dev);
     return check_launch(c->e, "kv_append_kernel");
 }
 

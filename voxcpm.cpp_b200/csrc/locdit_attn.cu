@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(kMaxWarp * 32) locdit_attn_kernel(const Locdit
     const int stage_floats = (2 * seq + n_rows) * kRowPad;
     __half *  kv16         = reinterpret_cast<__half *>(smem_f + 2 * stage_floats);  // [Khi][Klo][Vhi][Vlo], 16 x kHalfPad each
     const int q_vecs = n_rows * 16, kv_vecs = seq * 16;  // float4 per tile
+    pdl_wait();
+    pdl_launch_dependents();
 
     auto issue_loads = [&](int grp, int buf) {
         float *   st   = smem_f + buf * stage_floats;
@@ -246,6 +248,6 @@ extern "C" int vox_attn_locdit_step(vox_engine * e, const vox_locdit_args * a, v
     }
     const int per_sm = (int) std::max<size_t>(1, std::min<size_t>(6, (220 * 1024) / (smem + 1024)));
     const int blocks = (int) std::min<long long>(groups, (long long) e->sm_count * per_sm);
-    locdit_attn_kernel<<<blocks, kMaxWarp * 32, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    launch_pdl(locdit_attn_kernel, dim3(blocks), dim3(kMaxWarp * 32), smem, static_cast<cudaStream_t>(stream), p);
     return check_launch(e, "locdit_attn_kernel");
 }

@@ -14,8 +14,9 @@
 //              K-major layout the tensor core reads.  The output row and the row sums accumulate in TMEM
 //              over all tiles (no per-tile read-back); they are rescaled in place only when the running
 //              maximum jumps by more than 2^8, and read once at the end.
-//   warp 8     producer: one lane issues cp.async.bulk.tensor copies of 128-row K tiles (two-stage ring)
-//              and V tiles (one buffer, refilled as soon as the previous P.V has retired).
+//   warp 8     producer: one lane issues cp.async.bulk.tensor copies of 128-row K tiles (one buffer,
+//              refilled as soon as Q.K^T has retired, i.e. while the softmax of that tile runs) and V tiles
+//              (two-stage ring).
 //   warp 9     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128): S = Q.K^T (N=128, 4 k-steps)
 //              into TMEM columns 0-127, O_tile = P.V (N=64, 8 k-steps, V read MN-major straight from the
 //              row-major tile) into columns 128-191, and P.1 (N=16, a tile of ones) into columns 192-207,
@@ -40,12 +41,12 @@ namespace {
 
 constexpr int kTile      = 128;            // query rows per CTA and keys per tile
 constexpr int kTileBytes = kTile * 128;    // one [128][64] f16 tile
-constexpr int kKStages   = 2;              // K tiles are prefetched two ahead, V one ahead
+constexpr int kVStages   = 2;              // V tiles are prefetched two ahead; K has one buffer, refilled when Q.K^T retires
 constexpr int kSoftmaxThreads = 256;
 constexpr int kThreadsPf = kSoftmaxThreads + 64;
 constexpr int kTmemCols  = 256;            // S: columns 0-127, O tile: 128-191, row sums: 192-207
 constexpr int kOnesBytes = 4096;           // a [16][128] f16 tile of ones (any layout: every element is 1)
-constexpr int kSmemPf    = kTileBytes * (1 + kKStages + 1 + 2) + kOnesBytes + 1024;  // Q, K ring, V, P (two 64-key halves), ones
+constexpr int kSmemPf    = kTileBytes * (1 + 1 + kVStages + 2) + kOnesBytes + 1024;  // Q, K, V ring, P (two 64-key halves), ones
 
 struct PrefillParams {
     const uint8_t * q;
@@ -170,14 +171,14 @@ constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
 __global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[2 * kKStages + 8];
+    __shared__ uint64_t bars[2 * kVStages + 8];
     __shared__ float    half_max[2][2][kTile];  // [tile parity][column half][row]
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sK0 = smem_base + kTileBytes, sV = sK0 + kKStages * kTileBytes, sP = sV + kTileBytes,
+    const uint32_t sQ = smem_base, sK = smem_base + kTileBytes, sV0 = sK + kTileBytes, sP = sV0 + kVStages * kTileBytes,
                    sOnes = sP + 2 * kTileBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -189,17 +190,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     const int last_row = min(q0 + kTile, p.n_q) - 1;
     const int n_tiles  = min((p.n_kv + kTile - 1) / kTile, (last_row + p.causal_offset) / kTile + 1);
 
-    const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = smem_u32(&bars[kKStages]);
-    const uint32_t bQ = smem_u32(&bars[2 * kKStages]), bSready = bQ + 8, bSfree = bQ + 16, bPready = bQ + 24, bPVdone = bQ + 32,
-                   bOfree = bQ + 40, vfull = bQ + 48, vempty = bQ + 56;
+    const uint32_t vfull0 = smem_u32(&bars[0]), vempty0 = smem_u32(&bars[kVStages]);
+    const uint32_t bQ = smem_u32(&bars[2 * kVStages]), bSready = bQ + 8, bSfree = bQ + 16, bPready = bQ + 24, bPVdone = bQ + 32,
+                   kfull = bQ + 48, kempty = bQ + 56;
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < kKStages; ++s) {
-            mbar_init(kfull0 + 8 * s, 1);
-            mbar_init(kempty0 + 8 * s, 1);
+        for (int s = 0; s < kVStages; ++s) {
+            mbar_init(vfull0 + 8 * s, 1);
+            mbar_init(vempty0 + 8 * s, 1);
         }
-        mbar_init(vfull, 1);
-        mbar_init(vempty, 1);
+        mbar_init(kfull, 1);
+        mbar_init(kempty, 1);
         mbar_init(bQ, kSoftmaxThreads / 32);  // one arrival per softmax warp
         mbar_init(bSready, 1);
         mbar_init(bSfree, kSoftmaxThreads / 32);
@@ -211,6 +212,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();  // barriers and TMEM are set up while the previous kernel drains; Q, K, V are read after this
+    pdl_launch_dependents();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&tmem_base_slot);
 
     auto give_up = [&]() {
@@ -222,43 +225,45 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
             for (int j = 0; j < n_tiles && !aborted(); ++j) {
-                const int s = j % kKStages;
-                if (j >= kKStages && !mbar_wait_bounded(kempty0 + 8 * s, ((j / kKStages) - 1) & 1)) { give_up(); break; }
-                mbar_expect_tx(kfull0 + 8 * s, kTileBytes);
-                tma_load_5d(sK0 + s * kTileBytes, &map_k, kfull0 + 8 * s, 0, j * kTile, kvh, batch, 0);
-                if (j >= 1 && !mbar_wait_bounded(vempty, (j - 1) & 1)) { give_up(); break; }
-                mbar_expect_tx(vfull, kTileBytes);
-                tma_load_5d(sV, &map_v, vfull, 0, j * kTile, kvh, batch, 0);
+                const int s = j % kVStages;
+                if (j >= 1 && !mbar_wait_spin(kempty, (j - 1) & 1)) { give_up(); break; }
+                mbar_expect_tx(kfull, kTileBytes);
+                tma_load_5d(sK, &map_k, kfull, 0, j * kTile, kvh, batch, 0);
+                if (j >= kVStages && !mbar_wait_spin(vempty0 + 8 * s, ((j / kVStages) - 1) & 1)) { give_up(); break; }
+                mbar_expect_tx(vfull0 + 8 * s, kTileBytes);
+                tma_load_5d(sV0 + s * kTileBytes, &map_v, vfull0 + 8 * s, 0, j * kTile, kvh, batch, 0);
             }
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_f16(kTile, false), idesc_pv = idesc_f16(kHeadDim, true), idesc_sum = idesc_f16(16, false);
-            bool ok = mbar_wait_bounded(bQ, 0);
+            bool ok = mbar_wait_spin(bQ, 0);
             if (!ok) give_up();
             // S = Q K^T of tile j: four k-steps of 16 along head_dim, 32 bytes each inside the swizzle atom.
             // It is issued as soon as the softmax threads have taken S of tile j-1 out of TMEM, i.e. while
             // they are still busy with the exponentials of tile j-1.
             auto issue_qk = [&](int j) {
-                const int      s  = j % kKStages;
-                const uint32_t sK = sK0 + s * kTileBytes;
-                if (!mbar_wait_bounded(kfull0 + 8 * s, (j / kKStages) & 1)) return false;
-                if (j > 0 && !mbar_wait_bounded(bSfree, (j - 1) & 1)) return false;
+                if (!mbar_wait_spin(kfull, j & 1)) return false;
+                if (j > 0 && !mbar_wait_spin(bSfree, (j - 1) & 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     tc_mma_f16(tmem, smem_desc_sw128(sQ + 32 * k), smem_desc_sw128(sK + 32 * k), idesc_qk, k > 0);
                 tc_commit(bSready);
-                tc_commit(kempty0 + 8 * s);  // the K tile may be refilled once Q.K^T has retired
+                tc_commit(kempty);  // the K tile may be refilled once Q.K^T has retired
                 return true;
             };
             if (ok && !issue_qk(0)) { give_up(); ok = false; }
             for (int j = 0; j < n_tiles && ok && !aborted(); ++j) {
                 if (j + 1 < n_tiles && !issue_qk(j + 1)) { give_up(); break; }
-                if (!mbar_wait_bounded(vfull, j & 1)) { give_up(); break; }
-                if (!mbar_wait_bounded(bPready, j & 1)) { give_up(); break; }
+                const int      s  = j % kVStages;
+                const uint32_t sV = sV0 + s * kTileBytes;
+                if (!mbar_wait_spin(vfull0 + 8 * s, (j / kVStages) & 1)) { give_up(); break; }
+                if (!mbar_wait_spin(bPready, j & 1)) { give_up(); break; }
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {  // eight k-steps of 16 keys; P half-tiles of 64 keys, V rows 16 at a time
@@ -267,7 +272,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     tc_mma_f16(tmem + kTile + kHeadDim, pd, smem_desc_sw128(sOnes), idesc_sum, j > 0 || k > 0);  // row sums += P 1
                 }
                 tc_commit(bPVdone);
-                tc_commit(vempty);
+                tc_commit(vempty0 + 8 * s);
             }
         }
     } else {
@@ -307,7 +312,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         float m_ref = -INFINITY;
         bool  ok    = true;
         for (int j = 0; j < n_tiles && !aborted(); ++j) {
-            if (!mbar_wait_bounded(bSready, j & 1)) { give_up(); ok = false; break; }
+            if (!mbar_wait_spin(bSready, j & 1)) { give_up(); ok = false; break; }
             tc_fence_after();
             const int  k0     = j * kTile + 64 * half;  // first key of this thread's columns
             const bool masked = j * kTile + kTile - 1 > min(q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
@@ -333,7 +338,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             named_bar_sync(1, kSoftmaxThreads);
             tmax = fmaxf(tmax, half_max[j & 1][half ^ 1][row]) * p.scale_log2;
             // the previous tile's P.V must have retired before P is overwritten (and before O is touched)
-            if (j > 0 && !mbar_wait_bounded(bPVdone, (j - 1) & 1)) { give_up(); ok = false; break; }
+            if (j > 0 && !mbar_wait_spin(bPVdone, (j - 1) & 1)) { give_up(); ok = false; break; }
             // tcgen05.ld/st are warp-collective: the decision to rescale is taken per warp (any lane), and lanes
             // that do not need it take part with a factor of 1
             const bool raise = j > 0 && tmax > m_ref + 8.0f;
@@ -366,7 +371,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(bPready);  // this warp's part of P is visible to the tensor core
         }
-        if (ok && !aborted() && !mbar_wait_bounded(bPVdone, (n_tiles - 1) & 1)) { give_up(); ok = false; }
+        if (ok && !aborted() && !mbar_wait_spin(bPVdone, (n_tiles - 1) & 1)) { give_up(); ok = false; }
         if (ok && !aborted()) {
             // warp-collective TMEM reads by every lane; only rows that exist are stored
             tc_fence_after();
@@ -451,7 +456,7 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.status = e->status_dev;
     dim3 grid((p.n_q + kTile - 1) / kTile, p.n_heads, (unsigned) a->q.ne[3]);
-    prefill_tc_kernel<<<grid, kThreadsPf, kSmemPf, st>>>(mk, mv, p);
+    launch_pdl(prefill_tc_kernel, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
     return check_launch(e, "prefill_tc_kernel");
 }
 

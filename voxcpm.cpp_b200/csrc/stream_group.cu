@@ -43,6 +43,8 @@ namespace {
 
 __global__ void add_scalar_kernel(int32_t * a, int n, int delta, int cap) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
     if (i < n) a[i] = min(a[i] + delta, cap);
 }
 
@@ -181,7 +183,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
     }
     const int bound = g->kv_bound + (advance ? 1 : 0);
     if (advance) {  // the appended row becomes visible to this step's attention
-        add_scalar_kernel<<<(c.n_streams + 255) / 256, 256, 0, st>>>(g->kv_len_dev, c.n_streams, 1, c.max_len);
+        launch_pdl(add_scalar_kernel, dim3((c.n_streams + 255) / 256), dim3(256), 0, st, g->kv_len_dev, c.n_streams, 1, c.max_len);
         int rc = check_launch(g->e, "add_scalar_kernel");
         if (rc != VOX_ATTN_OK) return rc;
     }
@@ -207,7 +209,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         if (rc != VOX_ATTN_OK) return rc;
     }
     if (advance) {  // next append position; kv_len was already advanced above
-        add_scalar_kernel<<<(c.n_streams + 255) / 256, 256, 0, st>>>(g->kv_pos_dev, c.n_streams, 1, c.max_len);
+        launch_pdl(add_scalar_kernel, dim3((c.n_streams + 255) / 256), dim3(256), 0, st, g->kv_pos_dev, c.n_streams, 1, c.max_len);
         int rc = check_launch(g->e, "add_scalar_kernel");
         if (rc != VOX_ATTN_OK) return rc;
         for (auto & x : g->kv_len_host) x += 1;
