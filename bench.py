@@ -59,6 +59,47 @@ def stream_lengths(n, rank=0):
     return np.random.default_rng(12345 + rank).integers(KV_LO, KV_HI + 1, n).astype(np.int32)
 
 
+def streams_of_rank(scaling, n_streams, rank, world, partition):
+    """KV lengths of the streams one rank serves.  weak: every rank draws its own `n_streams`; strong: one
+    draw of `n_streams` is split over the ranks by `partition` (longest-processing-time on KV length).
+    Streams never move between ranks and nothing is exchanged on the data path."""
+    if scaling == "weak":
+        return stream_lengths(n_streams, rank)
+    all_lens = stream_lengths(n_streams, 0)
+    owner = partition(all_lens, world)
+    return all_lens[owner == rank]
+
+
+class Ranks:
+    """The only cross-rank traffic of the benchmark: a barrier and max / sum of a scalar (timings, stream
+    counts).  Works on any initialised process group (NCCL on GPUs, gloo in the CPU tests)."""
+
+    def __init__(self, world, device):
+        self.world, self.device = world, device
+
+    def _reduce(self, x, op):
+        if self.world == 1:
+            return x
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([x], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def max(self, x):
+        import torch.distributed as dist
+        return self._reduce(x, dist.ReduceOp.MAX)
+
+    def sum(self, x):
+        import torch.distributed as dist
+        return self._reduce(x, dist.ReduceOp.SUM)
+
+
 def lm_bytes_per_layer(lens, kv_type):
     """Algorithmic bytes of one LM layer over all streams: K and V rows once, Q in, output out."""
     row = 512.0 if kv_type == "f16" else 272.0
@@ -263,38 +304,20 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ranks = Ranks(world, "cuda")
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        ranks.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def sum_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+    max_over_ranks, sum_over_ranks = ranks.max, ranks.sum
 
     if args.workload != "serving":
         if rank == 0:
             print(json.dumps(aux_workload(args, pkg, torch)))
         return
 
-    # streams of this rank
-    if args.scaling == "weak":
-        lens = stream_lengths(args.streams, rank)
-    else:
-        all_lens = stream_lengths(args.streams, 0)
-        owner = pkg.partition_streams(all_lens, world)
-        lens = all_lens[owner == rank]
+    lens = streams_of_rank(args.scaling, args.streams, rank, world, pkg.partition_streams)
     S = len(lens)
     total_steps = args.warmup + args.steps
     max_len = ((KV_HI + 2 * (total_steps + 8) + 63) // 64) * 64

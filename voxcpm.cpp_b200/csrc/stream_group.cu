@@ -35,7 +35,7 @@ struct vox_group {
     // vox_group_step_host: device mirrors of the step buffers, two copy streams, events
     uint8_t *        dev_buf   = nullptr;
     size_t           dev_off[8] = {0};
-    cudaStream_t     st_compute = nullptr, st_copy = nullptr;
+    cudaStream_t     st_compute = nullptr, st_copy = nullptr, st_back = nullptr;  // launches, host-to-device, device-to-host
     cudaEvent_t      ev_lm_in = nullptr, ev_dit_in[16] = {nullptr}, ev_lm_done = nullptr, ev_dit_done[16] = {nullptr};
 };
 
@@ -123,6 +123,7 @@ void vox_group_destroy(vox_group * g) {
     if (g->dev_buf) cudaFree(g->dev_buf);
     if (g->st_compute) cudaStreamDestroy(g->st_compute);
     if (g->st_copy) cudaStreamDestroy(g->st_copy);
+    if (g->st_back) cudaStreamDestroy(g->st_back);
     if (g->ev_lm_in) cudaEventDestroy(g->ev_lm_in);
     if (g->ev_lm_done) cudaEventDestroy(g->ev_lm_done);
     for (int i = 0; i < 16; ++i) {
@@ -232,8 +233,9 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
     return VOX_ATTN_OK;
 }
 
-// Host-buffer form: inputs cross PCIe on a copy stream while the compute stream works on what has
-// already landed (LM inputs first, then one CFM timestep at a time); outputs go back the same way.
+// Host-buffer form: inputs cross PCIe on one copy stream while the compute stream works on what has
+// already landed (LM inputs first, then one CFM timestep at a time); outputs return on a second copy
+// stream as each part finishes, so both directions of the link are busy at once.
 int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) {
     VOX_REQUIRE(g && h, VOX_ATTN_INVALID_ARGUMENT, "null argument");
     const vox_group_config & c = g->cfg;
@@ -251,6 +253,7 @@ int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) 
         if (err != cudaSuccess) { cudaGetLastError(); set_error("step staging allocation of %zu bytes failed", off); return VOX_ATTN_OUT_OF_MEMORY; }
         VOX_CUDA_TRY(cudaStreamCreateWithFlags(&g->st_compute, cudaStreamNonBlocking));
         VOX_CUDA_TRY(cudaStreamCreateWithFlags(&g->st_copy, cudaStreamNonBlocking));
+        VOX_CUDA_TRY(cudaStreamCreateWithFlags(&g->st_back, cudaStreamNonBlocking));
         VOX_CUDA_TRY(cudaEventCreateWithFlags(&g->ev_lm_in, cudaEventDisableTiming));
         VOX_CUDA_TRY(cudaEventCreateWithFlags(&g->ev_lm_done, cudaEventDisableTiming));
         for (int i = 0; i < 16; ++i) {
@@ -303,16 +306,16 @@ int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) 
         if (rc != VOX_ATTN_OK) return rc;
         VOX_CUDA_TRY(cudaEventRecord(g->ev_dit_done[t], g->st_compute));
     }
-    // outputs ride the copy stream behind the inputs (PCIe is full duplex; D2H overlaps later H2D)
+    // outputs go back on a stream of their own: PCIe is full duplex, so they overlap the inputs still arriving
     if (L > 0) {
-        VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_copy, g->ev_lm_done, 0));
-        VOX_CUDA_TRY(cudaMemcpyAsync(h->lm_out, dev.lm_out, lm_q_b, cudaMemcpyDeviceToHost, g->st_copy));
+        VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_back, g->ev_lm_done, 0));
+        VOX_CUDA_TRY(cudaMemcpyAsync(h->lm_out, dev.lm_out, lm_q_b, cudaMemcpyDeviceToHost, g->st_back));
     }
     for (size_t t = 0; t < T && c.locdit_layers > 0; ++t) {
-        VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_copy, g->ev_dit_done[t], 0));
-        VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) h->dit_out + t * dq_step, (const uint8_t *) dev.dit_out + t * dq_step, dq_step, cudaMemcpyDeviceToHost, g->st_copy));
+        VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_back, g->ev_dit_done[t], 0));
+        VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) h->dit_out + t * dq_step, (const uint8_t *) dev.dit_out + t * dq_step, dq_step, cudaMemcpyDeviceToHost, g->st_back));
     }
-    VOX_CUDA_TRY(cudaStreamSynchronize(g->st_copy));
+    VOX_CUDA_TRY(cudaStreamSynchronize(g->st_back));
     return vox_engine_sync_status(g->e, g->st_compute);
 }
 
