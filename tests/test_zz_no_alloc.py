@@ -61,7 +61,7 @@ def rel(a, b):
 
 def test_static_scratch_refuses_oversized_calls(engine, pkg):
     import torch
-    S, cap = 256, 8192  # 256 streams x 16 heads x 16 chunks x 264 B = 17.3 MB > 16 MiB
+    S, cap = 512, 8192  # 512 streams x 16 heads x 8 chunks x 264 B = 17.3 MB > 16 MiB
     need = pkg.lib().vox_attn_decode_workspace_bytes(S, H, HK, cap)
     assert need > (16 << 20)
     cache = pkg.KVCache(engine, 1, S, HK, cap, pkg.F16)

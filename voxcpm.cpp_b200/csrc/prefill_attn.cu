@@ -6,7 +6,10 @@
 // On the CPU this is ggml's tiled path (third_party/ggml/src/ggml-cpu/ops.cpp:8347-8633); ggml-cuda
 // would run the mma.sync kernel flash_attn_ext_f16 (fattn-mma-f16.cuh:1459-1628).
 //
-// One CTA = 128 query rows of one head.  Ten warps:
+// A work item = 128 query rows of one head of one sequence.  CTAs are persistent (two per SM) and walk
+// a heaviest-first item list in snake order; barriers, TMEM and the tile of ones are set up once, and the
+// next item's Q rows are fetched while the current item's last P.V retires and its output is written.
+// Ten warps:
 //   warps 0-7  softmax: two threads per query row (row r = TMEM lane r).  Warps 0-3 own score columns
 //              0-63 and output columns 0-31, warps 4-7 the other halves.  Per 128-key tile a thread
 //              reads its scores from TMEM (tcgen05.ld), the pair agrees on the row maximum through shared
@@ -53,6 +56,7 @@ struct PrefillParams {
     size_t          q_nb1, q_nb2, q_nb3;
     float *         dst;
     int             n_q, n_kv, n_heads, gqa, causal_offset;
+    int             n_batch, n_qtiles, n_items;
     float           scale_log2;
     int *           status;
 };
@@ -168,6 +172,40 @@ constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
     return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (kTile >> 4) << 24);
 }
 
+// Rare path of the softmax warps, kept out of line so that its 32 registers do not weigh on the tile loop:
+// multiply this thread's 32 output columns (and, for the first column half, the row sum) in TMEM by f.
+__device__ __noinline__ void rescale_accumulators(uint32_t t_row, int half, float f) {
+    tc_fence_after();
+    float o[32];
+    tmem_ld32(t_row + kTile + 32 * half, o);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] *= f;
+    tmem_st32(t_row + kTile + 32 * half, o);
+    if (half == 0) tmem_st1(t_row + kTile + kHeadDim, tmem_ld1(t_row + kTile + kHeadDim) * f);
+    tc_fence_before();
+}
+
+// One unit of work: 128 query rows (tile `qtile`) of one head of one sequence.  Items are numbered
+// heaviest first (late query tiles see more keys); CTA c of G takes items c, 2G-1-c, 2G+c, ... so that
+// a heavy first item is followed by a light one.
+struct WorkItem {
+    int qtile, head, batch, n_tiles, q0;
+};
+__device__ __forceinline__ bool work_item(const PrefillParams & p, int round, WorkItem & w) {
+    const int G = gridDim.x, c = blockIdx.x;
+    const int idx = round * G + ((round & 1) ? G - 1 - c : c);
+    if (idx >= p.n_items) return false;
+    const int per_tile = p.n_heads * p.n_batch;
+    const int rest     = idx % per_tile;
+    w.qtile = p.n_qtiles - 1 - idx / per_tile;
+    w.head  = rest % p.n_heads;
+    w.batch = rest / p.n_heads;
+    w.q0    = w.qtile * kTile;
+    const int last_row = min(w.q0 + kTile, p.n_q) - 1;
+    w.n_tiles = min((p.n_kv + kTile - 1) / kTile, (last_row + p.causal_offset) / kTile + 1);
+    return true;
+}
+
 __global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -182,13 +220,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                    sOnes = sP + 2 * kTileBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // heavier (later) query tiles first so that the causal triangle drains evenly
-    const int n_qtiles = (p.n_q + kTile - 1) / kTile;
-    const int qtile = n_qtiles - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-    const int kvh   = head / p.gqa;
-    const int q0    = qtile * kTile;
-    const int last_row = min(q0 + kTile, p.n_q) - 1;
-    const int n_tiles  = min((p.n_kv + kTile - 1) / kTile, (last_row + p.causal_offset) / kTile + 1);
 
     const uint32_t vfull0 = smem_u32(&bars[0]), vempty0 = smem_u32(&bars[kVStages]);
     const uint32_t bQ = smem_u32(&bars[2 * kVStages]), bSready = bQ + 8, bSfree = bQ + 16, bPready = bQ + 24, bPVdone = bQ + 32,
@@ -222,33 +253,40 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     };
     auto aborted = [&]() { return *reinterpret_cast<volatile int *>(&abort_flag) != 0; };
 
+    // The CTA is persistent: every role walks the same item sequence; T counts key tiles over all items
+    // and fixes the phase of every barrier (one K copy, one S, one P and one P.V per tile).
     if (warp == 8) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
-            for (int j = 0; j < n_tiles && !aborted(); ++j) {
-                const int s = j % kVStages;
-                if (j >= 1 && !mbar_wait_spin(kempty, (j - 1) & 1)) { give_up(); break; }
-                mbar_expect_tx(kfull, kTileBytes);
-                tma_load_5d(sK, &map_k, kfull, 0, j * kTile, kvh, batch, 0);
-                if (j >= kVStages && !mbar_wait_spin(vempty0 + 8 * s, ((j / kVStages) - 1) & 1)) { give_up(); break; }
-                mbar_expect_tx(vfull0 + 8 * s, kTileBytes);
-                tma_load_5d(sV0 + s * kTileBytes, &map_v, vfull0 + 8 * s, 0, j * kTile, kvh, batch, 0);
+            WorkItem w;
+            int      T  = 0;
+            bool     ok = true;
+            for (int round = 0; ok && work_item(p, round, w); ++round) {
+                const int kvh = w.head / p.gqa;
+                for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
+                    const int s = T % kVStages;
+                    if (T >= 1 && !mbar_wait_spin(kempty, (T - 1) & 1)) { give_up(); ok = false; break; }
+                    mbar_expect_tx(kfull, kTileBytes);
+                    tma_load_5d(sK, &map_k, kfull, 0, j * kTile, kvh, w.batch, 0);
+                    if (T >= kVStages && !mbar_wait_spin(vempty0 + 8 * s, ((T / kVStages) - 1) & 1)) { give_up(); ok = false; break; }
+                    mbar_expect_tx(vfull0 + 8 * s, kTileBytes);
+                    tma_load_5d(sV0 + s * kTileBytes, &map_v, vfull0 + 8 * s, 0, j * kTile, kvh, w.batch, 0);
+                }
+                if (aborted()) break;
             }
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_f16(kTile, false), idesc_pv = idesc_f16(kHeadDim, true), idesc_sum = idesc_f16(16, false);
-            bool ok = mbar_wait_spin(bQ, 0);
-            if (!ok) give_up();
-            // S = Q K^T of tile j: four k-steps of 16 along head_dim, 32 bytes each inside the swizzle atom.
-            // It is issued as soon as the softmax threads have taken S of tile j-1 out of TMEM, i.e. while
-            // they are still busy with the exponentials of tile j-1.
-            auto issue_qk = [&](int j) {
-                if (!mbar_wait_spin(kfull, j & 1)) return false;
-                if (j > 0 && !mbar_wait_spin(bSfree, (j - 1) & 1)) return false;
+            // S = Q K^T of global tile T: four k-steps of 16 along head_dim, 32 bytes each inside the swizzle atom.
+            // It is issued as soon as the softmax threads have taken S of tile T-1 out of TMEM, i.e. while
+            // they are still busy with the exponentials of tile T-1.
+            auto issue_qk = [&](int T) {
+                if (!mbar_wait_spin(kfull, T & 1)) return false;
+                if (T > 0 && !mbar_wait_spin(bSfree, (T - 1) & 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
@@ -257,134 +295,180 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 tc_commit(kempty);  // the K tile may be refilled once Q.K^T has retired
                 return true;
             };
-            if (ok && !issue_qk(0)) { give_up(); ok = false; }
-            for (int j = 0; j < n_tiles && ok && !aborted(); ++j) {
-                if (j + 1 < n_tiles && !issue_qk(j + 1)) { give_up(); break; }
-                const int      s  = j % kVStages;
-                const uint32_t sV = sV0 + s * kTileBytes;
-                if (!mbar_wait_spin(vfull0 + 8 * s, (j / kVStages) & 1)) { give_up(); break; }
-                if (!mbar_wait_spin(bPready, j & 1)) { give_up(); break; }
-                tc_fence_after();
+            WorkItem w;
+            int      T  = 0;
+            bool     ok = true;
+            for (int round = 0; ok && work_item(p, round, w); ++round) {
+                // the first Q.K^T of an item needs the item's Q tile; later ones were issued one tile ahead
+                if (!mbar_wait_spin(bQ, round & 1) || !issue_qk(T)) { give_up(); break; }
+                for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
+                    if (j + 1 < w.n_tiles && !issue_qk(T + 1)) { give_up(); ok = false; break; }
+                    const int      s  = T % kVStages;
+                    const uint32_t sV = sV0 + s * kTileBytes;
+                    if (!mbar_wait_spin(vfull0 + 8 * s, (T / kVStages) & 1)) { give_up(); ok = false; break; }
+                    if (!mbar_wait_spin(bPready, T & 1)) { give_up(); ok = false; break; }
+                    tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {  // eight k-steps of 16 keys; P half-tiles of 64 keys, V rows 16 at a time
-                    const uint64_t pd = smem_desc_sw128(sP + (k >> 2) * kTileBytes + 32 * (k & 3));
-                    tc_mma_f16(tmem + kTile, pd, smem_desc_sw128(sV + 2048 * k), idesc_pv, j > 0 || k > 0);     // O += P V
-                    tc_mma_f16(tmem + kTile + kHeadDim, pd, smem_desc_sw128(sOnes), idesc_sum, j > 0 || k > 0);  // row sums += P 1
+                    for (int k = 0; k < 8; ++k) {  // eight k-steps of 16 keys; P half-tiles of 64 keys, V rows 16 at a time
+                        const uint64_t pd = smem_desc_sw128(sP + (k >> 2) * kTileBytes + 32 * (k & 3));
+                        tc_mma_f16(tmem + kTile, pd, smem_desc_sw128(sV + 2048 * k), idesc_pv, j > 0 || k > 0);     // O += P V
+                        tc_mma_f16(tmem + kTile + kHeadDim, pd, smem_desc_sw128(sOnes), idesc_sum, j > 0 || k > 0);  // row sums += P 1
+                    }
+                    tc_commit(bPVdone);
+                    tc_commit(vempty0 + 8 * s);
                 }
-                tc_commit(bPVdone);
-                tc_commit(vempty0 + 8 * s);
+                if (aborted()) break;
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax warps: two threads per query row
-        const int  row   = 32 * (warp & 3) + lane;  // == TMEM lane; a warp may only touch lanes 32*(warp%4)..+31
-        const int  half  = warp >> 2;               // 0: score columns 0-63 / output columns 0-31, 1: the rest
-        const int  qpos  = q0 + row;
-        const bool live  = qpos < p.n_q;
-        {
-            // this thread's half of the Q row -> f16, four 16-byte chunks at their swizzled places; and the ones tile
-            uint8_t * dstrow = smem_gen + row * 128;
-            const float * src = reinterpret_cast<const float *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) head * p.q_nb2 +
-                                                                (size_t) batch * p.q_nb3);
+        const int row  = 32 * (warp & 3) + lane;  // == TMEM lane; a warp may only touch lanes 32*(warp%4)..+31
+        const int half = warp >> 2;               // 0: score columns 0-63 / output columns 0-31, 1: the rest
+        const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);  // this warp's lane quarter
+        uint8_t * const q_dst = smem_gen + row * 128;
+        uint8_t * const p_dst = smem_gen + (sP - smem_base) + half * kTileBytes + row * 128;
+
+        // this thread's half of a Q row: f32 from memory, f16 into four 16-byte chunks at their swizzled places
+        auto load_q = [&](const WorkItem & w, float4 (&qv)[8]) {
+            const int qpos = w.q0 + row;
+            if (qpos < p.n_q) {
+                const float4 * src = reinterpret_cast<const float4 *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) w.head * p.q_nb2 +
+                                                                      (size_t) w.batch * p.q_nb3) + 8 * half;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) qv[i] = src[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
+        auto store_q = [&](const float4 (&qv)[8], int round) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int c = 4 * half + u;
-                uint4 w = make_uint4(0, 0, 0, 0);
-                if (live) {
-                    const float2 a = *reinterpret_cast<const float2 *>(src + 8 * c), b = *reinterpret_cast<const float2 *>(src + 8 * c + 2);
-                    const float2 cc = *reinterpret_cast<const float2 *>(src + 8 * c + 4), d = *reinterpret_cast<const float2 *>(src + 8 * c + 6);
-                    w = make_uint4(pack_half2(a.x, a.y), pack_half2(b.x, b.y), pack_half2(cc.x, cc.y), pack_half2(d.x, d.y));
-                }
-                *reinterpret_cast<uint4 *>(dstrow + ((c ^ (row & 7)) << 4)) = w;
+                *reinterpret_cast<uint4 *>(q_dst + ((c ^ (row & 7)) << 4)) =
+                    make_uint4(pack_half2(qv[2 * u].x, qv[2 * u].y), pack_half2(qv[2 * u].z, qv[2 * u].w),
+                               pack_half2(qv[2 * u + 1].x, qv[2 * u + 1].y), pack_half2(qv[2 * u + 1].z, qv[2 * u + 1].w));
             }
-            const uint32_t one2 = 0x3C003C00u;
-            *reinterpret_cast<uint4 *>(smem_gen + (sOnes - smem_base) + tid * 16) = make_uint4(one2, one2, one2, one2);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(bQ);
+            (void) round;
+        };
+
+        WorkItem w, wn;
+        bool     have = work_item(p, 0, w);
+        {
+            const uint32_t one2 = 0x3C003C00u;
+            *reinterpret_cast<uint4 *>(smem_gen + (sOnes - smem_base) + tid * 16) = make_uint4(one2, one2, one2, one2);
+            if (have) {
+                float4 qv[8];
+                load_q(w, qv);
+                store_q(qv, 0);
+            }
         }
-        const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);  // this warp's lane quarter
-        const int      limit = min(qpos + p.causal_offset, p.n_kv - 1);      // last key this row may see
-        // The output row and the row sum accumulate in TMEM across all key tiles, both scaled by
-        // 2^(-m_ref): their ratio does not depend on m_ref, so the reference maximum only has to keep
-        // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
-        // tile's maximum exceeds it by more than 2^8, which after the first tile is rare.
-        float m_ref = -INFINITY;
-        bool  ok    = true;
-        for (int j = 0; j < n_tiles && !aborted(); ++j) {
-            if (!mbar_wait_spin(bSready, j & 1)) { give_up(); ok = false; break; }
-            tc_fence_after();
-            const int  k0     = j * kTile + 64 * half;  // first key of this thread's columns
-            const bool masked = j * kTile + kTile - 1 > min(q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
-            float v[64];
-            tmem_ld64(t_row + 64 * half, v);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bSfree);  // S is in registers: the next tile's Q.K^T may overwrite it
-            float tmax = -INFINITY;
-            if (masked) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) v[i] = k0 + i > limit ? -INFINITY : v[i];
-            }
-            {
-                float t0 = v[0], t1 = v[1], t2 = v[2], t3 = v[3];  // four chains instead of one 64-deep dependency
-#pragma unroll
-                for (int i = 4; i < 64; i += 4) {
-                    t0 = fmaxf(t0, v[i]); t1 = fmaxf(t1, v[i + 1]); t2 = fmaxf(t2, v[i + 2]); t3 = fmaxf(t3, v[i + 3]);
-                }
-                tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
-            }
-            half_max[j & 1][half][row] = tmax;
-            named_bar_sync(1, kSoftmaxThreads);
-            tmax = fmaxf(tmax, half_max[j & 1][half ^ 1][row]) * p.scale_log2;
-            // the previous tile's P.V must have retired before P is overwritten (and before O is touched)
-            if (j > 0 && !mbar_wait_spin(bPVdone, (j - 1) & 1)) { give_up(); ok = false; break; }
-            // tcgen05.ld/st are warp-collective: the decision to rescale is taken per warp (any lane), and lanes
-            // that do not need it take part with a factor of 1
-            const bool raise = j > 0 && tmax > m_ref + 8.0f;
-            if (j == 0) {
-                m_ref = tmax;  // key 0 is visible to every row: finite
-            } else if (__any_sync(0xffffffffu, raise)) {
+        int  T  = 0;
+        bool ok = true;
+        for (int round = 0; have && ok; ++round) {
+            const int  qpos  = w.q0 + row;
+            const bool live  = qpos < p.n_q;
+            const int  limit = min(qpos + p.causal_offset, p.n_kv - 1);  // last key this row may see
+            // The output row and the row sum accumulate in TMEM across all key tiles, both scaled by
+            // 2^(-m_ref): their ratio does not depend on m_ref, so the reference maximum only has to keep
+            // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
+            // tile's maximum exceeds it by more than 2^8, which after the first tile is rare.
+            float m_ref = -INFINITY;
+            for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
+                if (!mbar_wait_bounded(bSready, T & 1)) { give_up(); ok = false; break; }
                 tc_fence_after();
-                const float f = raise ? ex2_approx(m_ref - tmax) : 1.0f;
-                if (raise) m_ref = tmax;
-                float o[32];
-                tmem_ld32(t_row + kTile + 32 * half, o);
+                const int  k0     = j * kTile + 64 * half;  // first key of this thread's columns
+                const bool masked = j * kTile + kTile - 1 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
+                // pass 1: maximum over this thread's 64 columns (two 32-column reads), then over the row through
+                // shared memory.  S is read from TMEM again in pass 2 instead of being kept: 64 more live registers
+                // would spill at two CTAs per SM.
+                float v[32];
+                float tmax = -INFINITY;
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    tmem_ld32(t_row + 64 * half + 32 * c, v);
+                    if (masked) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] *= f;
-                tmem_st32(t_row + kTile + 32 * half, o);
-                if (half == 0) tmem_st1(t_row + kTile + kHeadDim, tmem_ld1(t_row + kTile + kHeadDim) * f);
-                tc_fence_before();
+                        for (int i = 0; i < 32; ++i) v[i] = k0 + 32 * c + i > limit ? -INFINITY : v[i];
+                    }
+                    float t0 = v[0], t1 = v[1], t2 = v[2], t3 = v[3];  // four chains instead of one long dependency
+#pragma unroll
+                    for (int i = 4; i < 32; i += 4) {
+                        t0 = fmaxf(t0, v[i]); t1 = fmaxf(t1, v[i + 1]); t2 = fmaxf(t2, v[i + 2]); t3 = fmaxf(t3, v[i + 3]);
+                    }
+                    tmax = fmaxf(tmax, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
+                }
+                half_max[T & 1][half][row] = tmax;
+                named_bar_sync(1, kSoftmaxThreads);
+                tmax = fmaxf(tmax, half_max[T & 1][half ^ 1][row]) * p.scale_log2;
+                // the previous tile's P.V must have retired before P is overwritten (and before O is touched);
+                // at the first tile of an item that wait was done when the previous item was read out
+                if (j > 0 && !mbar_wait_bounded(bPVdone, (T - 1) & 1)) { give_up(); ok = false; break; }
+                // tcgen05.ld/st are warp-collective: the decision to rescale is taken per warp (any lane), and lanes
+                // that do not need it take part with a factor of 1
+                const bool raise = j > 0 && tmax > m_ref + 8.0f;
+                if (j == 0) {
+                    m_ref = tmax;  // key 0 is visible to every row: finite
+                } else if (__any_sync(0xffffffffu, raise)) {
+                    const float f = raise ? ex2_approx(m_ref - tmax) : 1.0f;
+                    if (raise) m_ref = tmax;
+                    rescale_accumulators(t_row, half, f);
+                }
+                // pass 2: P = 2^(c*S - m_ref), f16, into this thread's 64-key half of the P tile, 8 keys (16 bytes) at a time
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    tmem_ld32(t_row + 64 * half + 32 * c, v);
+                    if (c == 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bSfree);  // S has been read for the last time: the next Q.K^T may overwrite it
+                    }
+                    if (masked) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = k0 + 32 * c + i > limit ? -INFINITY : v[i];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            h[i] = pack_half2(ex2_approx(fmaf(v[8 * u + 2 * i], p.scale_log2, -m_ref)),
+                                              ex2_approx(fmaf(v[8 * u + 2 * i + 1], p.scale_log2, -m_ref)));
+                        *reinterpret_cast<uint4 *>(p_dst + (((4 * c + u) ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bPready);  // this warp's part of P is visible to the tensor core
             }
-            // P = 2^(c*S - m_ref), f16, into this thread's 64-key half of the P tile, 8 keys (16 bytes) at a time
-            uint8_t * prow = smem_gen + (sP - smem_base) + half * kTileBytes + row * 128;
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                uint32_t h[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    h[i] = pack_half2(ex2_approx(fmaf(v[8 * u + 2 * i], p.scale_log2, -m_ref)),
-                                      ex2_approx(fmaf(v[8 * u + 2 * i + 1], p.scale_log2, -m_ref)));
-                *reinterpret_cast<uint4 *>(prow + ((u ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bPready);  // this warp's part of P is visible to the tensor core
-        }
-        if (ok && !aborted() && !mbar_wait_spin(bPVdone, (n_tiles - 1) & 1)) { give_up(); ok = false; }
-        if (ok && !aborted()) {
+            if (!ok || aborted()) break;
+            // item done: read the result out once the last P.V has retired, then bring in the next item's Q rows
+            const bool have_next = work_item(p, round + 1, wn);
+            if (!mbar_wait_bounded(bPVdone, (T - 1) & 1)) { give_up(); break; }
             // warp-collective TMEM reads by every lane; only rows that exist are stored
             tc_fence_after();
             const float l = tmem_ld1(t_row + kTile + kHeadDim);  // sum of exactly the rounded weights the tensor core used
             float o[32];
             tmem_ld32(t_row + kTile + 32 * half, o);
+            tc_fence_before();
             if (live) {
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                float4 * out = reinterpret_cast<float4 *>(p.dst + (((size_t) batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim + 32 * half);
+                float4 * out = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + w.head) * kHeadDim + 32 * half);
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
                     out[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
             }
+            // every Q.K^T of this item has retired (its last S was consumed above), so the Q tile may be replaced
+            if (have_next) {
+                float4 qv[8];
+                load_q(wn, qv);
+                store_q(qv, round + 1);
+            }
+            have = have_next;
+            w    = wn;
         }
     }
 
@@ -402,6 +486,8 @@ bool tc_route_ok(const vox_attn_args * a) {
     if (k.type != VOX_TYPE_F16 || v.type != VOX_TYPE_F16) return false;
     if (k.ne[2] != v.ne[2] || k.ne[3] != v.ne[3]) return false;
     if (a->q.ne[1] < 1 || k.ne[1] < 1) return false;
+    // Q rows are read with 16-byte loads
+    if ((reinterpret_cast<uintptr_t>(a->q.data) & 15) != 0 || a->q.nb[1] % 16 || a->q.nb[2] % 16 || a->q.nb[3] % 16) return false;
     for (const vox_tensor * t : {&k, &v}) {
         if ((reinterpret_cast<uintptr_t>(t->data) & 15) != 0) return false;
         if (t->nb[1] % 16 || t->nb[2] % 16 || t->nb[3] % 16) return false;
@@ -455,7 +541,13 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     p.gqa = (int) (a->q.ne[2] / a->k.ne[2]); p.causal_offset = offset;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.status = e->status_dev;
-    dim3 grid((p.n_q + kTile - 1) / kTile, p.n_heads, (unsigned) a->q.ne[3]);
+    p.n_batch  = (int) a->q.ne[3];
+    p.n_qtiles = (p.n_q + kTile - 1) / kTile;
+    const long long items = (long long) p.n_qtiles * p.n_heads * p.n_batch;
+    VOX_REQUIRE(items < (1LL << 30), VOX_ATTN_INVALID_ARGUMENT, "too many query tiles");
+    p.n_items = (int) items;
+    // persistent CTAs, two per SM (100 KB of shared memory and 256 TMEM columns each)
+    dim3 grid((unsigned) std::min<long long>(items, 2LL * e->sm_count));
     launch_pdl(prefill_tc_kernel, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
     return check_launch(e, "prefill_tc_kernel");
 }
