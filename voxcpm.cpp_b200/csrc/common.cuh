@@ -1,7 +1,8 @@
 // Shared declarations of the attention engine: status handling, the engine object, and
 // thin wrappers over the sm_100a PTX the kernels use (mbarrier, bulk-tensor copies,
-// ldmatrix, mma).  Every device-side wait in this code base goes through mbar_wait_bounded,
-// which gives up after a fixed number of polls and reports instead of spinning forever.
+// ldmatrix, mma).  Every device-side wait in this code base goes through mbar_wait_bounded or
+// mbar_wait_spin, which compare the SM clock with a limit every 1024 polls, give up when it is
+// exceeded and report through the engine's status word instead of spinning forever.
 #pragma once
 
 #include <cuda.h>

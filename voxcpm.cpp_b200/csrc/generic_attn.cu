@@ -19,7 +19,6 @@ int    launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtens
                          int kv_bound, const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst, float scale,
                          void * workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);
-bool   prefill_route_ok(const vox_attn_args * a);
 }  // namespace vox
 
 namespace {
