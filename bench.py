@@ -414,8 +414,9 @@ def main():
         for n, x in host_t.items():
             if not n.endswith("out"):
                 x.copy_(dev_t[n])
-        h2d = group.step_bytes(0) + group.step_bytes(2)
-        d2h = group.step_bytes(1) + group.step_bytes(3)
+        # bytes copied per step by all ranks together (each rank feeds its own GPU over its own PCIe link)
+        h2d = sum_over_ranks(float(group.step_bytes(0) + group.step_bytes(2)))
+        d2h = sum_over_ranks(float(group.step_bytes(1) + group.step_bytes(3)))
         e2e_steps = max(2, min(args.steps, 5))
         group.step_host(host_t, advance=True)
         barrier()
