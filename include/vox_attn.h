@@ -167,7 +167,22 @@ int vox_kv_copy_from(vox_kv_cache * dst, const vox_kv_cache * src, void * stream
  *   q        [D, 1, H, n_streams] f32 (strides q_nb_head, q_nb_stream in bytes)
  *   kv_len   device array [n_streams]: rows of each stream that are visible (after append)
  *   kv_bound host-known upper bound of every kv_len (sizes the grid; <= max_len)
- *   dst      [D, H, 1, n_streams] f32, contiguous                                           */
+ *   dst      [D, H, 1, n_streams] f32, contiguous
+ *   k_new, v_new  optional (both or neither), [D, HK, n_streams] f32 with strides new_nb_head,
+ *            new_nb_stream in bytes: the token's own K/V rows.  The reference stores them with
+ *            ggml_cpy just before the attention node (src/minicpm.cpp:684-701); given here, the
+ *            decode launch does that store itself: stream s's row goes to position kv_len[s]-1
+ *            (converted exactly as vox_kv_append converts it) and takes part in this call's
+ *            attention, so no append launch is needed.  A stream whose kv_len exceeds the cache
+ *            capacity writes nothing and raises the engine's status (vox_engine_sync_status).
+ *            The cache is written: do not run two such calls on one layer concurrently.
+ *   flags    VOX_DECODE_CACHE_STABLE: a promise that neither kv_len nor any cache row this call reads
+ *            was written by the kernel launched just before it on the same stream (q, k_new and
+ *            v_new may have been).  True for the layers of a model, where a projection GEMM
+ *            precedes attention and the cache rows are at least one step old.  The launch then
+ *            requests its first K/V tiles before its programmatic-dependency wait, i.e. while the
+ *            previous kernel drains.                                                           */
+#define VOX_DECODE_CACHE_STABLE 1u
 typedef struct {
     const vox_kv_cache * cache;
     int32_t         layer;
@@ -179,6 +194,10 @@ typedef struct {
     size_t          q_nb_head, q_nb_stream;
     float *         dst;
     float           scale;
+    const float *   k_new;
+    const float *   v_new;
+    size_t          new_nb_head, new_nb_stream;
+    uint32_t        flags;
 } vox_decode_args;
 
 size_t vox_attn_decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);

@@ -266,6 +266,71 @@ def test_decode_gqa_ratios_and_large_logits(engine, pkg, oracle, vo):
             assert rel_err(out[s], outs[s]) < TOL["f16"], (heads, kvh, s)
 
 
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+def test_decode_stores_the_arriving_row_itself(kv, engine, pkg, oracle, vo):
+    """k_new / v_new given to the decode call: same cache bytes and same output bits as append followed by
+    decode, with the arriving row on every kind of boundary (first row, tile edges, a chunk of its own)."""
+    lens = [1, 2, 16, 17, 64, 65, 128, 512, 513, 1024, 1025, 1537, 2047, 2048, 700]  # lengths including the new row
+    rng = np.random.default_rng(77)
+    S, cap = len(lens), 2048
+    two = [pkg.KVCache(engine, 2, S, HK, cap, KV_TYPE[kv]) for _ in range(2)]
+    past = []
+    for s, n in enumerate(lens):
+        k = rng.standard_normal((HK, n - 1, D)).astype(np.float32)
+        v = rng.standard_normal((HK, n - 1, D)).astype(np.float32)
+        sk, sv = oracle.kv_store(k, KV_TYPE[kv]), oracle.kv_store(v, KV_TYPE[kv])
+        past.append((sk, sv))
+        if n > 1:
+            for c in two:
+                c.import_(1, s, sk, sv)
+    q = rng.standard_normal((S, H, D)).astype(np.float32)
+    k_new = (rng.standard_normal((S, HK, D)) * 2).astype(np.float32)
+    v_new = (rng.standard_normal((S, HK, D)) * 2).astype(np.float32)
+    k_new[3, 0, 32:] = 0.0  # an all-zero q8_0 block
+    kv_len = dev(np.array(lens, np.int32))
+    # separately: append at position len-1, then attend
+    two[0].append(1, dev(k_new[:, None]), dev(v_new[:, None]), positions=dev(np.array(lens, np.int32) - 1))
+    want = two[0].decode(1, dev(q), kv_len, max(lens))
+    # in one launch
+    before = engine.launches
+    got = two[1].decode(1, dev(q), kv_len, max(lens), k_new=dev(k_new), v_new=dev(v_new))
+    engine.sync_status()
+    assert engine.launches - before == 1
+    import torch
+    assert torch.equal(got, want)
+    # the same call with the promise that lengths and cache are older than the previous kernel (tiles are then
+    # requested before the dependency wait): same row stored again, same bits out
+    again = two[1].decode(1, dev(q), kv_len, max(lens), k_new=dev(k_new), v_new=dev(v_new), cache_stable=True)
+    engine.sync_status()
+    assert torch.equal(again, want)
+    out = got.cpu().numpy()
+    for s, n in enumerate(lens):
+        a, b = two[0].export(1, s, cap), two[1].export(1, s, cap)
+        assert np.array_equal(a[0].view(np.uint8), b[0].view(np.uint8)) and np.array_equal(a[1].view(np.uint8), b[1].view(np.uint8))
+        assert np.array_equal(b[0][:, n - 1].view(np.uint8), oracle.kv_store(k_new[s][:, None], KV_TYPE[kv])[:, 0].view(np.uint8))
+        ref = oracle.attn(q[s][None, :, None, :], b[0][None, :, :n], b[1][None, :, :n], kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)[0, 0]
+        assert rel_err(out[s], ref) < TOL[kv], f"stream {s} (kv_len {n})"
+    # the other layer was not touched
+    assert not two[1].export(0, 0, cap)[0].view(np.uint8).any()
+
+
+def test_decode_with_arriving_row_reports_a_stream_beyond_capacity(engine, pkg):
+    import torch
+    cache = pkg.KVCache(engine, 1, 2, HK, 64, pkg.F16)
+    q = torch.zeros((2, H, D), device="cuda")
+    rows = torch.ones((2, HK, D), device="cuda")
+    cache.decode(0, q, dev(np.array([65, 3], np.int32)), 64, k_new=rows, v_new=rows)  # stream 0 claims 65 rows of 64
+    with pytest.raises(pkg.VoxError) as e:
+        engine.sync_status()
+    assert e.value.status_name == "TIMEOUT" and "bad state" in str(e.value)
+    k0, _ = cache.export(0, 0, 64)
+    assert not k0.view(np.uint8).any()  # nothing was written for the stream that does not fit
+    k1, _ = cache.export(0, 1, 64)
+    assert np.all(k1[:, 2].astype(np.float32) == 1.0)
+    with pytest.raises(pkg.VoxError):
+        cache.decode(0, q, dev(np.array([1, 1], np.int32)), 1, k_new=rows)  # v_new missing
+
+
 def test_decode_refuses_bad_arguments(engine, pkg):
     import torch
     cache = pkg.KVCache(engine, 1, 2, HK, 128, pkg.F16)
@@ -355,8 +420,9 @@ def test_group_step_appends_then_attends(kv, engine, pkg, oracle, vo):
     before = engine.launches
     g.step(t, advance=True)
     engine.sync_status()
-    # per LM layer: append + decode (no merge at these lengths); 2 length bumps; one launch per CFM timestep
-    assert engine.launches - before == 3 * 2 + 2 + 2
+    # per LM layer one decode launch that also stores the new row (no merge at these lengths); one length
+    # bump; one launch per CFM timestep
+    assert engine.launches - before == 3 + 1 + 2
     assert np.array_equal(g.kv_len(), lens + 1)
     lm_out = t["lm_out"].cpu().numpy()
     for l in range(3):

@@ -72,7 +72,8 @@ class KVConfig(C.Structure):
 class DecodeArgs(C.Structure):
     _fields_ = [("cache", C.c_void_p), ("layer", C.c_int32), ("n_streams", C.c_int32), ("n_heads", C.c_int32),
                 ("kv_len", C.c_void_p), ("kv_bound", C.c_int32), ("q", C.c_void_p), ("q_nb_head", C.c_size_t),
-                ("q_nb_stream", C.c_size_t), ("dst", C.c_void_p), ("scale", C.c_float)]
+                ("q_nb_stream", C.c_size_t), ("dst", C.c_void_p), ("scale", C.c_float), ("k_new", C.c_void_p),
+                ("v_new", C.c_void_p), ("new_nb_head", C.c_size_t), ("new_nb_stream", C.c_size_t), ("flags", C.c_uint32)]
 
 
 class LocditArgs(C.Structure):
@@ -334,8 +335,11 @@ class KVCache:
     def copy_from(self, other: "KVCache", stream=None):
         _check(lib().vox_kv_copy_from(self.h, other.h, _stream_ptr(stream)))
 
-    def decode(self, layer, q, kv_len, kv_bound, scale=0.125, stream=None, dst=None):
-        """q [n_streams, H, 64] f32, kv_len int32 device [n_streams] -> [n_streams, H, 64]."""
+    def decode(self, layer, q, kv_len, kv_bound, scale=0.125, stream=None, dst=None, k_new=None, v_new=None, cache_stable=False):
+        """q [n_streams, H, 64] f32, kv_len int32 device [n_streams] -> [n_streams, H, 64].
+
+        ``k_new`` / ``v_new`` [n_streams, HK, 64] f32: the token's own rows, stored at position
+        ``kv_len - 1`` by the same launch (no separate append)."""
         import torch
         S, H, D = q.shape
         if dst is None:
@@ -344,6 +348,12 @@ class KVCache:
         ws = self.engine.workspace(ws_bytes)
         a = DecodeArgs(self.h, layer, S, H, kv_len.data_ptr(), kv_bound, q.data_ptr(), q.stride(1) * 4, q.stride(0) * 4,
                        dst.data_ptr(), scale)
+        a.flags = 1 if cache_stable else 0
+        if k_new is not None or v_new is not None:
+            a.k_new = k_new.data_ptr() if k_new is not None else None
+            a.v_new = v_new.data_ptr() if v_new is not None else None
+            ref = k_new if k_new is not None else v_new
+            a.new_nb_head, a.new_nb_stream = ref.stride(1) * 4, ref.stride(0) * 4
         _check(lib().vox_attn_decode(self.engine.h, C.byref(a), C.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(stream)))
         return dst
 

@@ -46,6 +46,20 @@ struct DecodeParams {
     float           scale_log2;
     int *           status;
     int *           counters;  // non-null: the last CTA of a (stream, kv head) to finish folds the partials itself
+    // Fused append (k_new non-null): kv_len[stream] counts the row that arrives with this call; the CTA
+    // whose chunk holds position kv_len-1 converts it, stores it into the cache and uses it.
+    const uint8_t * k_new;
+    const uint8_t * v_new;
+    size_t          new_nb_head, new_nb_stream;
+    uint8_t *       k_rows;    // data planes of this layer
+    uint8_t *       v_rows;
+    uint8_t *       k_scales;  // scale planes of this layer (q8_0)
+    uint8_t *       v_scales;
+    size_t          nb_pos, nb_head, nb_stream, sb_pos, sb_head, sb_stream;
+    // Non-zero: the lengths and the cache rows this launch reads were not written by the kernel just before
+    // it on the stream (only Q and the arriving row were), so the first tiles are requested before the
+    // programmatic-dependency wait, while that kernel is still draining.
+    int             early;
 };
 
 __device__ __forceinline__ int stream_len(const DecodeParams & p, int stream) {
@@ -82,6 +96,32 @@ __device__ __forceinline__ uint32_t s8_pair_to_half2(uint32_t biased, uint32_t s
     return *reinterpret_cast<const uint32_t *>(&r);
 }
 
+// The row that arrives with this call, stored by the producer warp (lane l holds elements 2l, 2l+1 of K
+// and of V; converted exactly as kv_append_kernel converts them) before it requests the tile that
+// contains the row: the bulk copy then delivers the new row like any other.  The proxy fence orders
+// these generic-proxy stores before the async-proxy read of the copy issued after the warp barrier.
+template <bool Q8>
+__device__ __forceinline__ void store_arriving_row(float2 kk, float2 vv, uint8_t * k_dst, uint8_t * v_dst, uint8_t * ks_dst,
+                                                   uint8_t * vs_dst, int lane) {
+    if constexpr (!Q8) {
+        *reinterpret_cast<uint32_t *>(k_dst + lane * 4) = pack_half2(kk.x, kk.y);
+        *reinterpret_cast<uint32_t *>(v_dst + lane * 4) = pack_half2(vv.x, vv.y);
+    } else {
+        char2 qk, qv;
+        float dk, dv;
+        q8_0_quantize_pair(kk.x, kk.y, qk, dk);
+        q8_0_quantize_pair(vv.x, vv.y, qv, dv);
+        *reinterpret_cast<char2 *>(k_dst + lane * 2) = qk;
+        *reinterpret_cast<char2 *>(v_dst + lane * 2) = qv;
+        if ((lane & 15) == 0) {
+            *reinterpret_cast<__half *>(ks_dst + (lane >> 4) * 2) = __float2half_rn(dk);
+            *reinterpret_cast<__half *>(vs_dst + (lane >> 4) * 2) = __float2half_rn(dv);
+        }
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __syncwarp();
+}
+
 template <bool Q8>
 __global__ void __launch_bounds__(kThreads, Ring<Q8>::kCtasPerSm)
 decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -97,21 +137,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
     const int chunk_id = blockIdx.x, kvh = blockIdx.y, stream = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    pdl_wait();  // the append of this layer (and the length update before it) must have landed
-    pdl_launch_dependents();
-    const int len = stream_len(p, stream);
-    const int c0  = chunk_id * p.chunk;
-    if (c0 >= len) {
-        // nothing visible in this chunk; a stream with no visible rows at all yields zeros
-        if (len == 0 && chunk_id == 0 && warp < kConsumerWarps) {
-            for (int i = tid; i < p.gqa * kHeadDim; i += kConsumerWarps * 32)
-                p.dst[((size_t) stream * p.n_heads + (size_t) kvh * p.gqa) * kHeadDim + i] = 0.0f;
-        }
-        return;
-    }
-    const int c1      = min(c0 + p.chunk, len);
-    const int n_tiles = (c1 - c0 + kKvTile - 1) / kKvTile;
 
+    // set-up that reads nothing the previous kernel of the stream wrote: done while that kernel drains
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]);
     if (tid == 0) {
         abort_flag = 0;
@@ -121,43 +148,112 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         }
         fence_mbar_init();
     }
+    if (tid == kConsumerWarps * 32) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+        if constexpr (Q8) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_ks)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_vs)) : "memory");
+        }
+    }
     __syncthreads();
+    // Dependency wait.  Every thread passes it before it triggers the launch of the next kernel, and the
+    // CTAs of chunk 0 always pass it, so a kernel that starts early can rely on everything before its
+    // predecessor being complete.
+    if (!p.early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+    const int len = stream_len(p, stream);
+    const int c0  = chunk_id * p.chunk;
+    if (c0 >= len) {
+        if (chunk_id == 0) {
+            if (p.early) {
+                pdl_wait();
+                pdl_launch_dependents();
+            }
+            // a stream with no visible rows at all yields zeros
+            if (warp < kConsumerWarps) {
+                for (int i = tid; i < p.gqa * kHeadDim; i += kConsumerWarps * 32)
+                    p.dst[((size_t) stream * p.n_heads + (size_t) kvh * p.gqa) * kHeadDim + i] = 0.0f;
+            }
+        }
+        return;  // nothing visible in this chunk
+    }
+    const int c1      = min(c0 + p.chunk, len);
+    const int n_tiles = (c1 - c0 + kKvTile - 1) / kKvTile;
+    // fused append: this CTA holds the arriving row iff its chunk ends at the stream's length
+    bool appends = false;
+    if (p.k_new != nullptr && c1 == len) {
+        appends = p.kv_len[stream] <= p.max_len;
+        if (!appends && tid == 0) atomicOr(p.status, kStatusBadState);  // the stream has outgrown its rows: nothing is written
+    }
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer
+        int  issued  = 0;
+        auto request = [&](int i) {  // lane 0: the copies of tile i; false when the CTA is giving up
+            const int s = i % kStages;
+            if (i >= kStages && !mbar_wait_bounded(empty0 + 8 * s, ((i / kStages) - 1) & 1)) {
+                atomicOr(p.status, kStatusTimeout);
+                atomicExch(&abort_flag, 1);
+                return false;
+            }
+            if (*reinterpret_cast<volatile int *>(&abort_flag)) return false;
+            const uint32_t sb  = smem_base + s * R::kStageBytes;
+            const uint32_t bar = full0 + 8 * s;
+            const int      pos = c0 + i * kKvTile;
+            mbar_expect_tx(bar, R::kTxBytes);
+            tma_load_5d(sb, &map_k, bar, 0, pos, kvh, stream, p.layer);
+            tma_load_5d(sb + R::kDataBytes, &map_v, bar, 0, pos, kvh, stream, p.layer);
+            if constexpr (Q8) {
+                tma_load_5d(sb + 2 * R::kDataBytes, &map_ks, bar, 2 * pos, 0, kvh, stream, p.layer);
+                tma_load_5d(sb + 2 * R::kDataBytes + kKvTile * 4, &map_vs, bar, 2 * pos, 0, kvh, stream, p.layer);
+            }
+            issued = i + 1;
+            return true;
+        };
+        const int n_before = appends ? n_tiles - 1 : n_tiles;  // the arriving row lies in the last tile
+        int       next     = 0;
+        if (p.early) {  // fill the ring while the previous kernel drains
+            if (lane == 0) {
+                for (; next < min(n_before, kStages); ++next)
+                    if (!request(next)) break;
+            }
+            pdl_wait();
+            pdl_launch_dependents();
+        }
+        float2 kk = make_float2(0.f, 0.f), vv = kk;
+        if (appends) {  // fetched now, stored just before the tile that holds the row is requested
+            const size_t src = (size_t) stream * p.new_nb_stream + (size_t) kvh * p.new_nb_head + lane * 8;
+            kk = *reinterpret_cast<const float2 *>(p.k_new + src);
+            vv = *reinterpret_cast<const float2 *>(p.v_new + src);
+        }
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < n_tiles; ++i) {
-                const int s = i % kStages;
-                if (i >= kStages && !mbar_wait_bounded(empty0 + 8 * s, ((i / kStages) - 1) & 1)) {
-                    atomicOr(p.status, kStatusTimeout);
-                    atomicExch(&abort_flag, 1);
-                    break;
-                }
-                if (*reinterpret_cast<volatile int *>(&abort_flag)) break;
-                const uint32_t sb  = smem_base + s * R::kStageBytes;
-                const uint32_t bar = full0 + 8 * s;
-                const int      pos = c0 + i * kKvTile;
-                mbar_expect_tx(bar, R::kTxBytes);
-                tma_load_5d(sb, &map_k, bar, 0, pos, kvh, stream, p.layer);
-                tma_load_5d(sb + R::kDataBytes, &map_v, bar, 0, pos, kvh, stream, p.layer);
-                if constexpr (Q8) {
-                    tma_load_5d(sb + 2 * R::kDataBytes, &map_ks, bar, 2 * pos, 0, kvh, stream, p.layer);
-                    tma_load_5d(sb + 2 * R::kDataBytes + kKvTile * 4, &map_vs, bar, 2 * pos, 0, kvh, stream, p.layer);
-                }
-                issued = i + 1;
-            }
-            if (*reinterpret_cast<volatile int *>(&abort_flag)) {
-                // consumers gave up: let the copies already issued land before the CTA retires
-                for (int i = max(0, issued - kStages); i < issued; ++i)
-                    mbar_wait_bounded(full0 + 8 * (i % kStages), (i / kStages) & 1);
-            }
+            for (int i = next; i < n_before; ++i)
+                if (!request(i)) break;
+        }
+        if (appends) {
+            __syncwarp();
+            const size_t off  = (size_t) stream * p.nb_stream + (size_t) kvh * p.nb_head + (size_t) (len - 1) * p.nb_pos;
+            const size_t soff = (size_t) stream * p.sb_stream + (size_t) kvh * p.sb_head + (size_t) (len - 1) * p.sb_pos;
+            store_arriving_row<Q8>(kk, vv, p.k_rows + off, p.v_rows + off, p.k_scales + soff, p.v_scales + soff, lane);
+            if (lane == 0 && issued == n_before) request(n_tiles - 1);
+        }
+        if (lane == 0 && *reinterpret_cast<volatile int *>(&abort_flag)) {
+            // consumers gave up: let the copies already issued land before the CTA retires
+            for (int i = max(0, issued - kStages); i < issued; ++i)
+                mbar_wait_bounded(full0 + 8 * (i % kStages), (i / kStages) & 1);
         }
         return;
     }
 
     // ---------------------------------------------------------------------- consumers
     const int g = lane >> 2, t = lane & 3;
+    if (p.early) {  // Q is written by the kernel before this one
+        pdl_wait();
+        pdl_launch_dependents();
+    }
 
     // Q fragments of the four k-steps: rows 0-7 = hi part of the group's heads, rows 8-15 = lo part.
     // The 64 head dimensions may be fed to the MMAs in any order as long as K uses the same one:
@@ -445,29 +541,43 @@ __global__ void __launch_bounds__(64) decode_merge_kernel(const DecodeParams p) 
 namespace vox {
 
 // Rows per CTA and CTAs per (stream, kv head).  A CTA is a copy pipeline that needs a few tiles to fill
-// and pays a fixed cost at its end (warp merge, partial write, ticket), so chunks are long: about 1.5
-// CTAs per SM when the launch is small, never below 512 rows (short caches: one CTA, no second pass) and
-// at most 1024 (measured on 256 ragged streams: 768..4096 rows per CTA are within 3 % of each other,
-// 256 rows cost 40 %).
-void decode_plan(int n_streams, int n_kv_heads, int kv_bound, int * chunk, int * n_chunks) {
-    static const int forced = [] {
-        const char * s = getenv("VOX_DECODE_CHUNK");
-        return s ? atoi(s) : 0;
-    }();
-    const long long rows   = (long long) std::max(kv_bound, 1) * n_streams * n_kv_heads;
-    const long long target = 148LL * 3 / 2;
-    long long c = (rows + target - 1) / target;
-    c = ((c + kKvTile - 1) / kKvTile) * kKvTile;
-    c = std::max<long long>(8 * kKvTile, std::min<long long>(c, 1024));
+// and pays a fixed cost at its end (warp merge, partial write, ticket), so chunks are long:
+//   - at most 1024 rows per CTA (measured on 256 ragged streams: 768..4096 rows are within 3 % of each
+//     other, 256 rows cost 40 %): with many (stream, kv head) pairs that alone gives several waves of CTAs;
+//   - with few pairs, more CTAs per pair until the launch has about 1.5 CTAs per SM for f16 and 3.5 for
+//     q8_0 (its arithmetic chain is longer and four of its CTAs fit an SM), but never below 256 rows per
+//     CTA nor above 8 CTAs per pair (16 when there are only a handful of pairs): every further CTA adds a
+//     partial to write, fence and fold.  Measured per layer, one stream: 8.0 -> 6.7 us at 1024 rows with
+//     4 x 256 instead of 2 x 512;
+//   - a launch that would need between 1 and 1.5 waves is cut back to one wave if chunks stay within 2048
+//     rows (32 streams at 8192 rows: 34 -> 30 us with 6 x 1408 instead of 8 x 1024; 512 CTAs do not fit
+//     the 444 resident slots);
+//   - every chunk of a launch gets the same number of rows (a short last chunk leaves its CTA idle while
+//     the others still stream: 640+640+640+128 measured 5 % slower than 4 x 512 at 2048 rows).
+void decode_plan(bool q8, int n_streams, int n_kv_heads, int kv_bound, int * chunk, int * n_chunks) {
+    const char *    env    = getenv("VOX_DECODE_CHUNK");  // tuning aid: rows per CTA, overrides the plan
+    const int       forced = env ? atoi(env) : 0;
+    const long long kv     = std::max(kv_bound, 1);
+    const long long pairs  = (long long) n_streams * n_kv_heads;
+    const long long target = q8 ? 512 : 222;
+    const long long slots  = 148LL * (q8 ? Ring<true>::kCtasPerSm : Ring<false>::kCtasPerSm);
+    auto            cdiv   = [](long long a, long long b) { return (a + b - 1) / b; };
+    const long long most   = std::min(cdiv(kv, 256), std::max(8LL, std::min(16LL, 32 / pairs)));
+    long long       n      = std::max(cdiv(kv, 1024), std::min(cdiv(target, pairs), most));
+    if (pairs * n > slots && 2 * pairs * n < 3 * slots && slots / pairs >= std::max(4LL, cdiv(kv, 2048))) n = slots / pairs;
+    long long c = cdiv(cdiv(kv, n), kKvTile) * kKvTile;
     if (forced >= kKvTile) c = (forced / kKvTile) * kKvTile;
     *chunk    = (int) c;
-    *n_chunks = std::max(1, (int) ((std::max(kv_bound, 1) + c - 1) / c));
+    *n_chunks = (int) cdiv(kv, c);
 }
 
+// Workspace for either cache type (the caller of the size query does not say which): the larger split.
 size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound) {
-    int chunk, n_chunks;
-    decode_plan(n_streams, n_kv_heads, kv_bound, &chunk, &n_chunks);
-    return n_chunks <= 1 ? 0 : (size_t) n_streams * n_heads * n_chunks * kPartialStride * sizeof(float);
+    int chunk, n_f16, n_q8;
+    decode_plan(false, n_streams, n_kv_heads, kv_bound, &chunk, &n_f16);
+    decode_plan(true, n_streams, n_kv_heads, kv_bound, &chunk, &n_q8);
+    const int n = std::max(n_f16, n_q8);
+    return n <= 1 ? 0 : (size_t) n_streams * n_heads * n * kPartialStride * sizeof(float);
 }
 
 // K/V described by tensor maps (a cache layer, or caller tensors); q/dst/lengths by pointers.
@@ -476,7 +586,8 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
                   const CUtensorMap * map_vs, int layer, int max_len, int n_streams, int n_heads, int n_kv_heads,
                   const int32_t * kv_len, int kv_len_const, int kv_bound, const float * q, size_t q_nb_head,
                   size_t q_nb_stream, float * dst, float scale, void * workspace, size_t workspace_bytes,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const vox_kv_cache * append_to = nullptr, const float * k_new = nullptr,
+                  const float * v_new = nullptr, size_t new_nb_head = 0, size_t new_nb_stream = 0, bool early = false) {
     const uint32_t bit = q8 ? (1u << 9) : (1u << 8);
     if (!(e->attr_mask & bit)) {
         if (q8) VOX_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring<true>::kSmemBytes));
@@ -490,8 +601,27 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     p.dst = dst; p.n_heads = n_heads; p.gqa = n_heads / n_kv_heads; p.layer = layer; p.max_len = max_len;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = e->status_dev;
-    decode_plan(n_streams, n_kv_heads, kv_bound, &p.chunk, &p.n_chunks);
-    const size_t need = decode_workspace_bytes(n_streams, n_heads, n_kv_heads, kv_bound);
+    p.early = early ? 1 : 0;
+    p.k_new = p.v_new = nullptr;
+    p.new_nb_head = p.new_nb_stream = 0;
+    p.k_rows = p.v_rows = p.k_scales = p.v_scales = nullptr;
+    p.nb_pos = p.nb_head = p.nb_stream = p.sb_pos = p.sb_head = p.sb_stream = 0;
+    if (append_to != nullptr) {
+        const vox_kv_cache * c = append_to;
+        p.k_new = reinterpret_cast<const uint8_t *>(k_new);
+        p.v_new = reinterpret_cast<const uint8_t *>(v_new);
+        p.new_nb_head = new_nb_head; p.new_nb_stream = new_nb_stream;
+        p.k_rows = c->k_data + (size_t) layer * c->nb_layer;
+        p.v_rows = c->v_data + (size_t) layer * c->nb_layer;
+        p.nb_pos = c->nb_pos; p.nb_head = c->nb_head; p.nb_stream = c->nb_stream;
+        if (q8) {
+            p.k_scales = c->k_scale + (size_t) layer * c->sb_layer;
+            p.v_scales = c->v_scale + (size_t) layer * c->sb_layer;
+            p.sb_pos = c->sb_pos; p.sb_head = c->sb_head; p.sb_stream = c->sb_stream;
+        }
+    }
+    decode_plan(q8, n_streams, n_kv_heads, kv_bound, &p.chunk, &p.n_chunks);
+    const size_t need = p.n_chunks <= 1 ? 0 : (size_t) n_streams * n_heads * p.n_chunks * kPartialStride * sizeof(float);
     VOX_REQUIRE(workspace_bytes >= need && (need == 0 || workspace != nullptr), VOX_ATTN_WORKSPACE_TOO_SMALL,
                 "decode needs %zu workspace bytes, got %zu", need, workspace_bytes);
     p.partial = static_cast<float *>(workspace);
@@ -542,9 +672,18 @@ int vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace,
     VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->q) & 7) == 0 && a->q_nb_head % 8 == 0 && a->q_nb_stream % 8 == 0,
                 VOX_ATTN_INVALID_ARGUMENT, "q rows must be 8-byte aligned");
     VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->dst) & 15) == 0, VOX_ATTN_INVALID_ARGUMENT, "dst must be 16-byte aligned");
+    const bool appends = a->k_new != nullptr || a->v_new != nullptr;
+    if (appends) {
+        VOX_REQUIRE(a->k_new && a->v_new, VOX_ATTN_INVALID_ARGUMENT, "k_new and v_new must be given together");
+        VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->k_new) & 7) == 0 && (reinterpret_cast<uintptr_t>(a->v_new) & 7) == 0 &&
+                        a->new_nb_head % 8 == 0 && a->new_nb_stream % 8 == 0,
+                    VOX_ATTN_INVALID_ARGUMENT, "k_new / v_new rows must be 8-byte aligned");
+        VOX_REQUIRE(a->kv_bound >= 1, VOX_ATTN_INVALID_ARGUMENT, "kv_bound counts the arriving row: it cannot be 0 with k_new");
+    }
     return launch_decode(e, c->cfg.type == VOX_TYPE_Q8_0, c->map_k, c->map_v, &c->map_ks, &c->map_vs, a->layer, c->cfg.max_len, a->n_streams, a->n_heads, c->cfg.n_kv_heads,
                          a->kv_len, 0, a->kv_bound, a->q, a->q_nb_head, a->q_nb_stream, a->dst, a->scale, workspace,
-                         workspace_bytes, static_cast<cudaStream_t>(stream));
+                         workspace_bytes, static_cast<cudaStream_t>(stream), appends ? c : nullptr, a->k_new, a->v_new,
+                         a->new_nb_head, a->new_nb_stream, (a->flags & VOX_DECODE_CACHE_STABLE) != 0);
 }
 
 }  // extern "C"

@@ -32,15 +32,9 @@ __device__ __forceinline__ void write_row(const CacheView & c, uint8_t * data, u
     if (c.type == VOX_TYPE_F16) {
         *reinterpret_cast<__half2 *>(data + off + lane * 4) = __floats2half2_rn(x0, x1);
     } else {
-        float amax = fmaxf(fabsf(x0), fabsf(x1));
-#pragma unroll
-        for (int m = 1; m < 16; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-        const float d  = amax / 127.0f;
-        const float id = d != 0.0f ? 1.0f / d : 0.0f;
-        const int   q0 = (int) roundf(x0 * id), q1 = (int) roundf(x1 * id);
         char2 q;
-        q.x = (signed char) q0;
-        q.y = (signed char) q1;
+        float d;
+        q8_0_quantize_pair(x0, x1, q, d);
         *reinterpret_cast<char2 *>(data + off + lane * 2) = q;
         if ((lane & 15) == 0) {
             const size_t soff = (size_t) layer * c.sb_layer + (size_t) stream * c.sb_stream + (size_t) head * c.sb_head +

@@ -41,4 +41,19 @@ __host__ __device__ inline float synth_normal(uint64_t seed, uint64_t idx) {
 #endif
 }
 
+#ifdef __CUDACC__
+// q8_0 of one 32-value block held by a half-warp, two values per lane: the arithmetic of
+// quantize_row_q8_0_ref (third_party/ggml/src/ggml-quants.c:199-222): d = amax/127, id = d ? 1/d : 0,
+// q = roundf(x*id).  All 32 lanes of the warp must call it (the two half-warps are two blocks).
+__device__ __forceinline__ void q8_0_quantize_pair(float x0, float x1, char2 & q, float & d) {
+    float amax = fmaxf(fabsf(x0), fabsf(x1));
+#pragma unroll
+    for (int m = 1; m < 16; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    d = amax / 127.0f;
+    const float id = d != 0.0f ? 1.0f / d : 0.0f;
+    q.x = (signed char) (int) roundf(x0 * id);
+    q.y = (signed char) (int) roundf(x1 * id);
+}
+#endif
+
 }  // namespace vox

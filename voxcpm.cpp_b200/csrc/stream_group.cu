@@ -27,7 +27,6 @@ struct vox_group {
     vox_group_config cfg{};
     vox_kv_cache *   cache[2]  = {nullptr, nullptr};  // backbone, residual LM
     int32_t *        kv_len_dev = nullptr;            // [n_streams] rows visible to attention
-    int32_t *        kv_pos_dev = nullptr;            // [n_streams] row the next append writes
     std::vector<int32_t> kv_len_host;
     int              kv_bound  = 0;
     void *           workspace = nullptr;
@@ -96,14 +95,12 @@ int vox_group_create(vox_engine * e, const vox_group_config * cfg, vox_group ** 
         g->workspace_bytes = std::max(g->workspace_bytes,
                                       (size_t) cfg->n_streams * cfg->n_heads * ((cfg->max_len + 63) / 64) * 66 * sizeof(float));
         cudaError_t err = cudaMalloc(&g->workspace, g->workspace_bytes);
-        if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&g->kv_len_dev), sizeof(int32_t) * 2 * cfg->n_streams);
-        if (err == cudaSuccess) err = cudaMemset(g->kv_len_dev, 0, sizeof(int32_t) * 2 * cfg->n_streams);
+        if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&g->kv_len_dev), sizeof(int32_t) * cfg->n_streams);
+        if (err == cudaSuccess) err = cudaMemset(g->kv_len_dev, 0, sizeof(int32_t) * cfg->n_streams);
         if (err != cudaSuccess) {
             cudaGetLastError();
             set_error("group allocation failed: %s", cudaGetErrorString(err));
             rc = VOX_ATTN_OUT_OF_MEMORY;
-        } else {
-            g->kv_pos_dev = g->kv_len_dev + cfg->n_streams;
         }
     }
     if (rc != VOX_ATTN_OK) {
@@ -145,7 +142,6 @@ int vox_group_set_kv_len(vox_group * g, const int32_t * kv_len) {
     }
     VOX_CUDA_TRY(cudaSetDevice(g->e->device));
     VOX_CUDA_TRY(cudaMemcpy(g->kv_len_dev, kv_len, sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
-    VOX_CUDA_TRY(cudaMemcpy(g->kv_pos_dev, kv_len, sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
     memcpy(g->kv_len_host.data(), kv_len, sizeof(int32_t) * g->cfg.n_streams);
     g->kv_bound = bound;
     return VOX_ATTN_OK;
@@ -192,14 +188,17 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         const int      stack = l < c.base_layers ? 0 : 1;
         const int      layer = stack == 0 ? l : l - c.base_layers;
         vox_kv_cache * kc    = g->cache[stack];
-        if (advance) {
-            const float * kn = b->lm_k_new + (size_t) l * S * c.n_kv_heads * D;
-            const float * vn = b->lm_v_new + (size_t) l * S * c.n_kv_heads * D;
-            int rc = vox_kv_append(kc, layer, c.n_streams, 1, g->kv_pos_dev, 0, kn, vn, D * 4, (size_t) c.n_kv_heads * D * 4,
-                                   (size_t) c.n_kv_heads * D * 4, st);
-            if (rc != VOX_ATTN_OK) return rc;
-        }
         vox_decode_args da;
+        da.k_new = da.v_new = nullptr;
+        da.new_nb_head = da.new_nb_stream = 0;
+        // from the second layer on, the kernel before this one is the previous layer's decode: it wrote
+        // neither the lengths nor this layer's rows (layer 0 follows the length update)
+        da.flags = l > 0 ? VOX_DECODE_CACHE_STABLE : 0u;
+        if (advance) {  // the token's K/V rows are stored by the decode launch itself (position kv_len-1)
+            da.k_new = b->lm_k_new + (size_t) l * S * c.n_kv_heads * D;
+            da.v_new = b->lm_v_new + (size_t) l * S * c.n_kv_heads * D;
+            da.new_nb_head = D * 4; da.new_nb_stream = (size_t) c.n_kv_heads * D * 4;
+        }
         da.cache = kc; da.layer = layer; da.n_streams = c.n_streams; da.n_heads = c.n_heads;
         da.kv_len = g->kv_len_dev; da.kv_bound = bound;
         da.q = b->lm_q + (size_t) l * S * c.n_heads * D;
@@ -209,10 +208,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         int rc = vox_attn_decode(g->e, &da, g->workspace, g->workspace_bytes, stream);
         if (rc != VOX_ATTN_OK) return rc;
     }
-    if (advance) {  // next append position; kv_len was already advanced above
-        launch_pdl(add_scalar_kernel, dim3((c.n_streams + 255) / 256), dim3(256), 0, st, g->kv_pos_dev, c.n_streams, 1, c.max_len);
-        int rc = check_launch(g->e, "add_scalar_kernel");
-        if (rc != VOX_ATTN_OK) return rc;
+    if (advance) {
         for (auto & x : g->kv_len_host) x += 1;
         g->kv_bound += 1;
     }
