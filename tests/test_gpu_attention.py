@@ -401,6 +401,39 @@ def test_prefill_causal(B, L, engine, oracle, vo):
     assert rel_err(out.cpu().numpy(), ref) < TOL["f16"]
 
 
+def test_prefill_rising_logits_move_the_reference_maximum(engine, oracle, vo):
+    """Scores that keep growing along the key axis (by far more than 2^8 per tile): the running reference of
+    the kernel has to be raised inside tiles, in every block position, and the accumulated output rescaled."""
+    rng = np.random.default_rng(11)
+    B, L = 1, 300
+    ramp = (np.arange(L, dtype=np.float32) / L * 15.0)[None, None, :, None]
+    q = np.full((B, H, L, D), 0.5, np.float32) + rng.standard_normal((B, H, L, D)).astype(np.float16).astype(np.float32) * 0.05
+    q = q.astype(np.float16).astype(np.float32)
+    k = (ramp * np.ones((B, HK, L, D), np.float32) + rng.standard_normal((B, HK, L, D)).astype(np.float32) * 0.1).astype(np.float16)
+    v = rng.standard_normal((B, HK, L, D)).astype(np.float16)
+    out = engine.prefill(dev(q), dev(k), dev(v))
+    engine.sync_status()
+    mask = oracle.causal_mask(np.arange(L), L)[None, None]
+    ref = oracle.attn(q, k, v, mask, kv_type=vo.F16, path=vo.PATH_TILED)
+    assert np.all(np.isfinite(out.cpu().numpy()))
+    assert rel_err(out.cpu().numpy(), ref) < TOL["f16"]
+
+
+@pytest.mark.parametrize("n_q, n_kv", [(200, 328), (130, 207), (64, 512), (1, 300)])
+def test_prefill_with_past(n_q, n_kv, engine, oracle, vo):
+    """A chunk of n_q new tokens attending over n_kv - n_q cached ones and, causally, itself."""
+    rng = np.random.default_rng(n_q * 7 + n_kv)
+    B = 2
+    q = rng.standard_normal((B, H, n_q, D)).astype(np.float16).astype(np.float32)
+    k = rng.standard_normal((B, HK, n_kv, D)).astype(np.float16)
+    v = rng.standard_normal((B, HK, n_kv, D)).astype(np.float16)
+    out = engine.prefill(dev(q), dev(k), dev(v))
+    engine.sync_status()
+    mask = oracle.causal_mask(np.arange(n_kv - n_q, n_kv), n_kv)[None, None]
+    ref = oracle.attn(q, k, v, mask, kv_type=vo.F16, path=vo.PATH_TILED)
+    assert rel_err(out.cpu().numpy(), ref) < TOL["f16"]
+
+
 # ------------------------------------------------------------------ stream groups
 
 @pytest.mark.parametrize("kv", ["f16", "q8_0"])

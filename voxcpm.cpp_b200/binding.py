@@ -93,7 +93,8 @@ class StepBuffers(C.Structure):
 
 
 def library_path() -> str:
-    return os.path.join(HERE, "libvoxattn.so")
+    """The in-tree build, or another build of the same sources named by VOX_ATTN_LIBRARY (developer aid)."""
+    return os.environ.get("VOX_ATTN_LIBRARY") or os.path.join(HERE, "libvoxattn.so")
 
 
 def declared_symbols() -> list[str]:

@@ -6,30 +6,33 @@
 // On the CPU this is ggml's tiled path (third_party/ggml/src/ggml-cpu/ops.cpp:8347-8633); ggml-cuda
 // would run the mma.sync kernel flash_attn_ext_f16 (fattn-mma-f16.cuh:1459-1628).
 //
-// A work item = 128 query rows of one head of one sequence.  CTAs are persistent (two per SM) and walk
-// a heaviest-first item list in snake order; barriers, TMEM and the tile of ones are set up once, and the
-// next item's Q rows are fetched while the current item's last P.V retires and its output is written.
-// Ten warps:
-//   warps 0-7  softmax: two threads per query row (row r = TMEM lane r).  Warps 0-3 own score columns
-//              0-63 and output columns 0-31, warps 4-7 the other halves.  Per 128-key tile a thread
-//              reads its scores from TMEM (tcgen05.ld), the pair agrees on the row maximum through shared
-//              memory, each writes P = 2^(c*S - max) as f16 into shared memory in the 128-byte-swizzled
-//              K-major layout the tensor core reads.  The output row and the row sums accumulate in TMEM
-//              over all tiles (no per-tile read-back); they are rescaled in place only when the running
-//              maximum jumps by more than 2^8, and read once at the end.
-//   warp 8     producer: one lane issues cp.async.bulk.tensor copies of 128-row K tiles (one buffer,
-//              refilled as soon as Q.K^T has retired, i.e. while the softmax of that tile runs) and V tiles
-//              (two-stage ring).
-//   warp 9     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128): S = Q.K^T (N=128, 4 k-steps)
-//              into TMEM columns 0-127, O_tile = P.V (N=64, 8 k-steps, V read MN-major straight from the
-//              row-major tile) into columns 128-191, and P.1 (N=16, a tile of ones) into columns 192-207,
-//              which yields the row sums of exactly the rounded weights the tensor core used.
-//              Completion is signalled with tcgen05.commit.
-// Q arrives as f32 and is rounded to f16 once per CTA (exact when it already holds f16 values);
-// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  100 KB of shared memory and
-// 256 TMEM columns per CTA: two CTAs share an SM, one computing softmax while the other waits on copies.
-// Every wait is bounded; on expiry the status word is set and all roles fall through to the common
-// exit, where the TMEM columns are released.
+// A work item = 128 query rows of one head of one sequence, walked over 64-key tiles.  CTAs are persistent
+// (two per SM) and take items from a heaviest-first list in snake order; barriers, TMEM and the tile of ones
+// are set up once.  Six warps:
+//   warps 0-3  softmax: one thread per query row (row r = TMEM lane r).  Per tile a thread reads its 64 scores
+//              from TMEM (tcgen05.ld), takes their maximum, and writes P = 2^(c*S - m_ref) as packed f16 back into
+//              TMEM (tcgen05.st) over the first half of the scores it has just read: the tensor core takes the
+//              weights from there as the A operand of P.V, so they never pass through shared memory.  On the
+//              diagonal tile a warp skips the 32-column blocks none of its rows can see.  The output row and the
+//              row sums accumulate in TMEM over all tiles (no per-tile read-back); they are rescaled in place only
+//              when a tile's maximum exceeds the reference m_ref by more than 2^8, and read once at the end.
+//   warp 4     producer: one lane issues cp.async.bulk.tensor copies of 64-row K and V tiles into four-stage rings.
+//   warp 5     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128).  S = Q.K^T (N=64, 4 k-steps, both
+//              operands in shared memory) goes to one of two score buffers in TMEM (tile T uses buffer T % 2), so
+//              the scores of tile T+1 are computed while the softmax of tile T runs.  O += P.V and the row sums
+//              come from ONE instruction per 16 keys (N=80, 4 k-steps): P from TMEM, V read MN-major straight
+//              from its row-major tile, and a tile of ones addressed as columns 64-79 of every V tile, which
+//              yields the sums of exactly the rounded weights the tensor core used.  The tensor pipe executes in
+//              issue order, so Q.K^T of tile T+2, issued behind P.V of tile T, overwrites that tile's weights only
+//              once they have been used.  Completion is signalled with tcgen05.commit (two per tile).
+// Measured costs that shaped this: a tcgen05.mma costs its issuing thread 45-70 cycles whatever its shape, so
+// instructions are few and wide (the sums ride along with P.V); the per-tile chain scores -> weights -> P.V ->
+// next scores was 2.5x the softmax time until the scores were double-buffered; and a parity wait cannot see
+// two completed phases, so every barrier here completes at most once between two looks of its waiters.
+// Q arrives as f32 and is rounded to f16 once per item (exact when it already holds f16 values);
+// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  89 KB of shared memory and
+// 256 TMEM columns per CTA.  Every wait is bounded; on expiry the status word is set and all roles fall
+// through to the common exit, where the TMEM columns are released.
 #include "common.cuh"
 
 #include <algorithm>
@@ -42,14 +45,40 @@ int launch_generic(vox_engine * e, const vox_attn_args * a, int causal_offset, c
 
 namespace {
 
-constexpr int kTile      = 128;            // query rows per CTA and keys per tile
-constexpr int kTileBytes = kTile * 128;    // one [128][64] f16 tile
-constexpr int kVStages   = 2;              // V tiles are prefetched two ahead; K has one buffer, refilled when Q.K^T retires
-constexpr int kSoftmaxThreads = 256;
+// Developer aid, off unless the file is compiled with -DVOX_PREFILL_PROFILE: per-role cycle counters
+// (SM clock, summed over CTAs with atomics) that vox_debug_prefill_profile copies out.
+#ifdef VOX_PREFILL_PROFILE
+__device__ unsigned long long g_prof[32];
+__device__ long long g_trace[4][64];  // CTA 0, first 64 tiles: scores seen, weights signalled, weights seen, MMAs issued
+#define PROF_TRACE(k, T) do { if (blockIdx.x == 0 && (T) < 64) g_trace[k][T] = clock64(); } while (0)
+#define PROF_VARS long long pf_t = 0, pf_acc[12] = {0}
+#define PROF_START() pf_t = clock64()
+#define PROF_STOP(i) do { const long long pf_n = clock64(); pf_acc[i] += pf_n - pf_t; pf_t = pf_n; } while (0)
+#define PROF_COUNT(i, n) pf_acc[i] += (n)
+#define PROF_FLUSH(base, n) do { for (int pf_i = 0; pf_i < (n); ++pf_i) atomicAdd(&g_prof[(base) + pf_i], (unsigned long long) pf_acc[pf_i]); } while (0)
+#else
+#define PROF_VARS
+#define PROF_START()
+#define PROF_STOP(i)
+#define PROF_COUNT(i, n)
+#define PROF_FLUSH(base, n)
+#define PROF_TRACE(k, T)
+#endif
+
+constexpr int kTile      = 128;            // query rows per item
+constexpr int kKeys      = 64;             // keys per tile
+constexpr int kQBytes    = kTile * 128;    // the item's [128][64] f16 Q tile
+constexpr int kKvBytes   = kKeys * 128;    // one [64][64] f16 K or V tile
+constexpr int kStages    = 4;              // K ring and V ring
+constexpr int kSoftmaxThreads = 128;
 constexpr int kThreadsPf = kSoftmaxThreads + 64;
-constexpr int kTmemCols  = 256;            // S: columns 0-127, O tile: 128-191, row sums: 192-207
-constexpr int kOnesBytes = 4096;           // a [16][128] f16 tile of ones (any layout: every element is 1)
-constexpr int kSmemPf    = kTileBytes * (1 + 1 + kVStages + 2) + kOnesBytes + 1024;  // Q, K, V ring, P (two 64-key halves), ones
+// TMEM columns: two score buffers (tile T uses buffer T % 2; its weights, packed f16, replace the first 32
+// columns of its scores) and the output row with its row sum
+constexpr int kTmemCols  = 256;
+constexpr int kSCol      = 0;              // S: 2 x 64 columns
+constexpr int kOCol      = 128;            // O: 64 columns, row sums: 16 columns behind them
+constexpr int kOnesBytes = kKvBytes;       // a tile of ones, addressed as columns 64-79 of every V tile (any layout: every element is 1)
+constexpr int kSmemPf    = kQBytes + 2 * kStages * kKvBytes + kOnesBytes + 1024;  // Q, K ring, V ring, ones
 
 struct PrefillParams {
     const uint8_t * q;
@@ -83,9 +112,17 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// 32 consecutive f32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
+// A operand (the f16 weights) read from TMEM: 8 columns per k-step of 16 keys
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane; the registers are valid after tmem_wait_ld
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t * r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -96,30 +133,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-// 64 consecutive columns: two loads in flight, one wait
-__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
-    uint32_t r[64];
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Pins a register behind the volatile statements before it (the wait above), so that no use of a loaded
+// value can be scheduled ahead of the wait that makes it valid.
+__device__ __forceinline__ void pin(uint32_t & r) { asm volatile("" : "+r"(r)); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    tmem_ld32_nowait(taddr, r);
+    tmem_wait_ld();
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(r[32 * h + 0]), "=r"(r[32 * h + 1]), "=r"(r[32 * h + 2]), "=r"(r[32 * h + 3]), "=r"(r[32 * h + 4]), "=r"(r[32 * h + 5]),
-              "=r"(r[32 * h + 6]), "=r"(r[32 * h + 7]), "=r"(r[32 * h + 8]), "=r"(r[32 * h + 9]), "=r"(r[32 * h + 10]), "=r"(r[32 * h + 11]),
-              "=r"(r[32 * h + 12]), "=r"(r[32 * h + 13]), "=r"(r[32 * h + 14]), "=r"(r[32 * h + 15]), "=r"(r[32 * h + 16]), "=r"(r[32 * h + 17]),
-              "=r"(r[32 * h + 18]), "=r"(r[32 * h + 19]), "=r"(r[32 * h + 20]), "=r"(r[32 * h + 21]), "=r"(r[32 * h + 22]), "=r"(r[32 * h + 23]),
-              "=r"(r[32 * h + 24]), "=r"(r[32 * h + 25]), "=r"(r[32 * h + 26]), "=r"(r[32 * h + 27]), "=r"(r[32 * h + 28]), "=r"(r[32 * h + 29]),
-              "=r"(r[32 * h + 30]), "=r"(r[32 * h + 31])
-            : "r"(taddr + 32 * h)
-            : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 32; ++i) {
+        pin(r[i]);
+        v[i] = __uint_as_float(r[i]);
+    }
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
@@ -135,17 +163,32 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
           "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
           "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
         : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    tmem_wait_st();
+}
+// 16 columns (32 packed f16 weights); completion is awaited by the caller (tmem_wait_st)
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
 __device__ __forceinline__ void tmem_st1(uint32_t taddr, float x) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(x)) : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    tmem_wait_st();
 }
 __device__ __forceinline__ float tmem_ld1(uint32_t taddr) {
     uint32_t r;
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    tmem_wait_ld();
+    pin(r);
     return __uint_as_float(r);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
 
 // 2^x on the special-function unit (one MUFU instruction; arguments here are <= 0)
@@ -167,21 +210,33 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
+// The same for an MN-major operand wider than one 64-element swizzle atom: `next_atom` is the byte distance
+// from this atom to the one holding elements 64.. of every row (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr, uint32_t next_atom) {
+    uint64_t d = smem_desc_sw128(addr);
+    d &= ~((uint64_t) 0x3FFF << 16);
+    d |= (uint64_t) ((next_atom >> 4) & 0x3FFF) << 16;
+    return d;
+}
+
 // Instruction descriptor, kind::f16: f32 accumulate, f16 A and B, M = 128.
 constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
     return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (kTile >> 4) << 24);
 }
 
-// Rare path of the softmax warps, kept out of line so that its 32 registers do not weigh on the tile loop:
-// multiply this thread's 32 output columns (and, for the first column half, the row sum) in TMEM by f.
-__device__ __noinline__ void rescale_accumulators(uint32_t t_row, int half, float f) {
+// Rare path of the softmax warps, kept out of line so that its registers do not weigh on the tile loop:
+// multiply this thread's output row and row sum in TMEM by f.
+__device__ __noinline__ void rescale_accumulators(uint32_t t_row, float f) {
     tc_fence_after();
-    float o[32];
-    tmem_ld32(t_row + kTile + 32 * half, o);
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+        float o[32];
+        tmem_ld32(t_row + kOCol + 32 * h, o);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] *= f;
-    tmem_st32(t_row + kTile + 32 * half, o);
-    if (half == 0) tmem_st1(t_row + kTile + kHeadDim, tmem_ld1(t_row + kTile + kHeadDim) * f);
+        for (int i = 0; i < 32; ++i) o[i] *= f;
+        tmem_st32(t_row + kOCol + 32 * h, o);
+    }
+    tmem_st1(t_row + kOCol + kHeadDim, tmem_ld1(t_row + kOCol + kHeadDim) * f);
     tc_fence_before();
 }
 
@@ -202,44 +257,51 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
     w.batch = rest / p.n_heads;
     w.q0    = w.qtile * kTile;
     const int last_row = min(w.q0 + kTile, p.n_q) - 1;
-    w.n_tiles = min((p.n_kv + kTile - 1) / kTile, (last_row + p.causal_offset) / kTile + 1);
+    w.n_tiles = min((p.n_kv + kKeys - 1) / kKeys, (last_row + p.causal_offset) / kKeys + 1);
     return true;
 }
 
 __global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[2 * kVStages + 8];
-    __shared__ float    half_max[2][2][kTile];  // [tile parity][column half][row]
+    __shared__ uint64_t bars[4 * kStages + 5];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sK = smem_base + kTileBytes, sV0 = sK + kTileBytes, sP = sV0 + kVStages * kTileBytes,
-                   sOnes = sP + 2 * kTileBytes;
+    const uint32_t sQ = smem_base, sK0 = sQ + kQBytes, sV0 = sK0 + kStages * kKvBytes, sOnes = sV0 + kStages * kKvBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    const uint32_t vfull0 = smem_u32(&bars[0]), vempty0 = smem_u32(&bars[kVStages]);
-    const uint32_t bQ = smem_u32(&bars[2 * kVStages]), bSready = bQ + 8, bSfree = bQ + 16, bPready = bQ + 24, bPVdone = bQ + 32,
-                   kfull = bQ + 48, kempty = bQ + 56;
+    // per-tile barriers: K/V ring (stage T % 4; "K stage free" is signalled when Q.K^T of the tile has retired and
+    // is also what the softmax warps wait on for the scores; "V stage free" is signalled when P.V has retired and
+    // is also what tells them that the accumulators are at rest), weights ready (buffer T % 2);
+    // the softmax warps may be two tiles ahead of the MMA thread (the scores of tile T+1 exist before it has
+    // looked at the weights of tile T), so "weights ready" is one barrier per buffer: a single one could complete
+    // two phases unobserved, and a parity wait cannot tell that from none;
+    // per-item barriers: Q in place, output complete, output read
+    const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = kfull0 + 8 * kStages, vfull0 = kempty0 + 8 * kStages,
+                   vempty0 = vfull0 + 8 * kStages, bP0 = vempty0 + 8 * kStages, bQ = bP0 + 16, bO = bQ + 8, bOfree = bO + 8;
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < kVStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(kfull0 + 8 * s, 1);
+            mbar_init(kempty0 + 8 * s, 1);
             mbar_init(vfull0 + 8 * s, 1);
             mbar_init(vempty0 + 8 * s, 1);
         }
-        mbar_init(kfull, 1);
-        mbar_init(kempty, 1);
-        mbar_init(bQ, kSoftmaxThreads / 32);  // one arrival per softmax warp
-        mbar_init(bSready, 1);
-        mbar_init(bSfree, kSoftmaxThreads / 32);
-        mbar_init(bPready, kSoftmaxThreads / 32);
-        mbar_init(bPVdone, 1);
+        for (int s = 0; s < 2; ++s) mbar_init(bP0 + 8 * s, kSoftmaxThreads / 32);  // one arrival per softmax warp
+        mbar_init(bQ, kSoftmaxThreads / 32);
+        mbar_init(bO, 1);
+        mbar_init(bOfree, kSoftmaxThreads / 32);
         fence_mbar_init();
     }
-    if (warp == 9) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    if (warp == 5) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    if (tid == kSoftmaxThreads) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -254,228 +316,295 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     auto aborted = [&]() { return *reinterpret_cast<volatile int *>(&abort_flag) != 0; };
 
     // The CTA is persistent: every role walks the same item sequence; T counts key tiles over all items
-    // and fixes the phase of every barrier (one K copy, one S, one P and one P.V per tile).
-    if (warp == 8) {
+    // and fixes the phase of every per-tile barrier; `round` fixes the phase of the per-item ones.
+    if (warp == 4) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
             WorkItem w;
             int      T  = 0;
             bool     ok = true;
+            PROF_VARS;
+            PROF_START();
             for (int round = 0; ok && work_item(p, round, w); ++round) {
                 const int kvh = w.head / p.gqa;
                 for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                    const int s = T % kVStages;
-                    if (T >= 1 && !mbar_wait_spin(kempty, (T - 1) & 1)) { give_up(); ok = false; break; }
-                    mbar_expect_tx(kfull, kTileBytes);
-                    tma_load_5d(sK, &map_k, kfull, 0, j * kTile, kvh, w.batch, 0);
-                    if (T >= kVStages && !mbar_wait_spin(vempty0 + 8 * s, ((T / kVStages) - 1) & 1)) { give_up(); ok = false; break; }
-                    mbar_expect_tx(vfull0 + 8 * s, kTileBytes);
-                    tma_load_5d(sV0 + s * kTileBytes, &map_v, vfull0 + 8 * s, 0, j * kTile, kvh, w.batch, 0);
+                    const int      st = T % kStages;
+                    const uint32_t ph = ((T / kStages) - 1) & 1;
+                    PROF_STOP(0);
+                    if (T >= kStages && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                    PROF_STOP(1);
+                    mbar_expect_tx(kfull0 + 8 * st, kKvBytes);
+                    tma_load_5d(sK0 + st * kKvBytes, &map_k, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
+                    PROF_STOP(0);
+                    if (T >= kStages && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                    PROF_STOP(2);
+                    mbar_expect_tx(vfull0 + 8 * st, kKvBytes);
+                    tma_load_5d(sV0 + st * kKvBytes, &map_v, vfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
                 }
                 if (aborted()) break;
             }
+            PROF_STOP(0);
+            PROF_FLUSH(0, 3);  // 0 issue, 1 wait K stage free, 2 wait V stage free
         }
-    } else if (warp == 9) {
+    } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc_f16(kTile, false), idesc_pv = idesc_f16(kHeadDim, true), idesc_sum = idesc_f16(16, false);
-            // S = Q K^T of global tile T: four k-steps of 16 along head_dim, 32 bytes each inside the swizzle atom.
-            // It is issued as soon as the softmax threads have taken S of tile T-1 out of TMEM, i.e. while
-            // they are still busy with the exponentials of tile T-1.
+            constexpr uint32_t idesc_qk = idesc_f16(kKeys, false), idesc_pv = idesc_f16(kHeadDim + 16, true);
+            // Descriptors are built once; a ring stage is selected by adding its distance to the address field
+            // (and, for V, taking it off the distance to the tile of ones).
+            uint64_t dQ[4], dK[4], dV[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                dQ[k] = smem_desc_sw128(sQ + 32 * k);
+                dK[k] = smem_desc_sw128(sK0 + 32 * k);
+                dV[k] = smem_desc_sw128_mn(sV0 + 2048 * k, sOnes - sV0);
+            }
+            constexpr uint64_t kStage  = kKvBytes >> 4;
+            constexpr uint64_t kVStage = kStage - (kStage << 16);
+            PROF_VARS;
+            // S = Q K^T of global tile T into score buffer T % 2: four k-steps of 16 along head_dim, 32 bytes each
+            // inside the swizzle atom.  The buffer last held the weights of tile T-2; the tensor pipe executes in
+            // issue order, so issuing this behind P.V of tile T-2 is all the protection they need.
             auto issue_qk = [&](int T) {
-                if (!mbar_wait_spin(kfull, T & 1)) return false;
-                if (T > 0 && !mbar_wait_spin(bSfree, (T - 1) & 1)) return false;
+                const int st = T % kStages, sb = T & 1;
+                PROF_STOP(0);
+                if (!mbar_wait_bounded(kfull0 + 8 * st, (T / kStages) & 1)) return false;
+                PROF_STOP(1);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    tc_mma_f16(tmem, smem_desc_sw128(sQ + 32 * k), smem_desc_sw128(sK + 32 * k), idesc_qk, k > 0);
-                tc_commit(bSready);
-                tc_commit(kempty);  // the K tile may be refilled once Q.K^T has retired
+                for (int k = 0; k < 4; ++k) tc_mma_f16(tmem + kSCol + kKeys * sb, dQ[k], dK[k] + st * kStage, idesc_qk, k > 0);
+                tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
                 return true;
             };
             WorkItem w;
             int      T  = 0;
             bool     ok = true;
+            PROF_START();
             for (int round = 0; ok && work_item(p, round, w); ++round) {
-                // the first Q.K^T of an item needs the item's Q tile; later ones were issued one tile ahead
-                if (!mbar_wait_spin(bQ, round & 1) || !issue_qk(T)) { give_up(); break; }
+                // the item's Q tile is in place: scores of its first two tiles
+                PROF_STOP(0);
+                if (!mbar_wait_bounded(bQ, round & 1)) { give_up(); break; }
+                PROF_STOP(2);
+                if (!issue_qk(T) || (w.n_tiles > 1 && !issue_qk(T + 1))) { give_up(); break; }
+                // the previous item's result has been read out of TMEM: its columns may be overwritten
+                if (round > 0 && !mbar_wait_bounded(bOfree, (round - 1) & 1)) { give_up(); break; }
                 for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                    if (j + 1 < w.n_tiles && !issue_qk(T + 1)) { give_up(); ok = false; break; }
-                    const int      s  = T % kVStages;
-                    const uint32_t sV = sV0 + s * kTileBytes;
-                    if (!mbar_wait_spin(vfull0 + 8 * s, (T / kVStages) & 1)) { give_up(); ok = false; break; }
-                    if (!mbar_wait_spin(bPready, T & 1)) { give_up(); ok = false; break; }
+                    const int st = T % kStages;
+                    PROF_STOP(0);
+                    if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kStages) & 1)) { give_up(); ok = false; break; }
+                    PROF_STOP(3);
+                    if (!mbar_wait_bounded(bP0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
+                    PROF_STOP(4);
+                    PROF_TRACE(2, T);
                     tc_fence_after();
+                    // O += P V and row sums += P 1 in one instruction per 16 keys: N = 80, columns 64-79 of the B
+                    // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, at the start of
+                    // the tile's score buffer.
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {  // eight k-steps of 16 keys; P half-tiles of 64 keys, V rows 16 at a time
-                        const uint64_t pd = smem_desc_sw128(sP + (k >> 2) * kTileBytes + 32 * (k & 3));
-                        tc_mma_f16(tmem + kTile, pd, smem_desc_sw128(sV + 2048 * k), idesc_pv, j > 0 || k > 0);     // O += P V
-                        tc_mma_f16(tmem + kTile + kHeadDim, pd, smem_desc_sw128(sOnes), idesc_sum, j > 0 || k > 0);  // row sums += P 1
-                    }
-                    tc_commit(bPVdone);
-                    tc_commit(vempty0 + 8 * s);
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dV[k] + st * kVStage, idesc_pv, j > 0 || k > 0);
+                    tc_commit(vempty0 + 8 * st);  // P.V has retired: the V stage may be refilled, the accumulators are at rest
+                    if (j + 1 == w.n_tiles) tc_commit(bO);  // the item's output is complete
+                    // scores two tiles ahead, into the buffer whose weights P.V has just been told to read
+                    if (j + 2 < w.n_tiles && !issue_qk(T + 2)) { give_up(); ok = false; break; }
+                    PROF_TRACE(3, T);
                 }
                 if (aborted()) break;
             }
+            PROF_STOP(0);
+            PROF_FLUSH(4, 5);  // 4 issue, 5 wait K tile, 6 wait Q / score buffer, 7 wait V tile, 8 wait P
         }
     } else {
-        // ------------------------------------------------------------------ softmax warps: two threads per query row
-        const int row  = 32 * (warp & 3) + lane;  // == TMEM lane; a warp may only touch lanes 32*(warp%4)..+31
-        const int half = warp >> 2;               // 0: score columns 0-63 / output columns 0-31, 1: the rest
-        const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);  // this warp's lane quarter
+        // ------------------------------------------------------------------ softmax warps: one thread per query row
+        const int      row   = tid;                                    // == TMEM lane; warp w may only touch lanes 32w..32w+31
+        const uint32_t t_row = tmem + ((uint32_t) (32 * warp) << 16);  // this warp's lane quarter
         uint8_t * const q_dst = smem_gen + row * 128;
-        uint8_t * const p_dst = smem_gen + (sP - smem_base) + half * kTileBytes + row * 128;
 
-        // this thread's half of a Q row: f32 from memory, f16 into four 16-byte chunks at their swizzled places
-        auto load_q = [&](const WorkItem & w, float4 (&qv)[8]) {
+        // this thread's Q row: f32 from memory, f16 into eight 16-byte chunks at their swizzled places
+        auto load_q = [&](const WorkItem & w, float4 (&qv)[16]) {
             const int qpos = w.q0 + row;
             if (qpos < p.n_q) {
                 const float4 * src = reinterpret_cast<const float4 *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) w.head * p.q_nb2 +
-                                                                      (size_t) w.batch * p.q_nb3) + 8 * half;
+                                                                      (size_t) w.batch * p.q_nb3);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) qv[i] = src[i];
+                for (int i = 0; i < 16; ++i) qv[i] = src[i];
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < 16; ++i) qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         };
-        auto store_q = [&](const float4 (&qv)[8], int round) {
+        auto store_q = [&](const float4 (&qv)[16]) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int c = 4 * half + u;
+            for (int c = 0; c < 8; ++c) {
                 *reinterpret_cast<uint4 *>(q_dst + ((c ^ (row & 7)) << 4)) =
-                    make_uint4(pack_half2(qv[2 * u].x, qv[2 * u].y), pack_half2(qv[2 * u].z, qv[2 * u].w),
-                               pack_half2(qv[2 * u + 1].x, qv[2 * u + 1].y), pack_half2(qv[2 * u + 1].z, qv[2 * u + 1].w));
+                    make_uint4(pack_half2(qv[2 * c].x, qv[2 * c].y), pack_half2(qv[2 * c].z, qv[2 * c].w),
+                               pack_half2(qv[2 * c + 1].x, qv[2 * c + 1].y), pack_half2(qv[2 * c + 1].z, qv[2 * c + 1].w));
             }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(bQ);
-            (void) round;
         };
 
         WorkItem w, wn;
         bool     have = work_item(p, 0, w);
         {
             const uint32_t one2 = 0x3C003C00u;
-            *reinterpret_cast<uint4 *>(smem_gen + (sOnes - smem_base) + tid * 16) = make_uint4(one2, one2, one2, one2);
+            for (int i = tid; i < kOnesBytes / 16; i += kSoftmaxThreads)
+                *reinterpret_cast<uint4 *>(smem_gen + (sOnes - smem_base) + i * 16) = make_uint4(one2, one2, one2, one2);
             if (have) {
-                float4 qv[8];
+                float4 qv[16];
                 load_q(w, qv);
-                store_q(qv, 0);
+                store_q(qv);
             }
         }
         int  T  = 0;
         bool ok = true;
+        PROF_VARS;
+        PROF_START();
         for (int round = 0; have && ok; ++round) {
             const int  qpos  = w.q0 + row;
             const bool live  = qpos < p.n_q;
             const int  limit = min(qpos + p.causal_offset, p.n_kv - 1);  // last key this row may see
+            // last key any row of this warp may see (rows beyond n_q compute on zeros and are not stored)
+            const int  warp_limit = min(w.q0 + 32 * warp + 31 + p.causal_offset, p.n_kv - 1);
             // The output row and the row sum accumulate in TMEM across all key tiles, both scaled by
             // 2^(-m_ref): their ratio does not depend on m_ref, so the reference maximum only has to keep
             // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
-            // tile's maximum exceeds it by more than 2^8, which after the first tile is rare.
+            // block's maximum exceeds it by more than 2^8, which after the first tile is rare.
             float m_ref = -INFINITY;
             for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                if (!mbar_wait_bounded(bSready, T & 1)) { give_up(); ok = false; break; }
+                const int sb = T & 1;
+                PROF_STOP(0);
+                if (!mbar_wait_bounded(kempty0 + 8 * (T % kStages), (T / kStages) & 1)) { give_up(); ok = false; break; }
+                PROF_STOP(1);
+                PROF_COUNT(7, 1);
+                if (tid == 0) PROF_TRACE(0, T);
                 tc_fence_after();
-                const int  k0     = j * kTile + 64 * half;  // first key of this thread's columns
-                const bool masked = j * kTile + kTile - 1 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
-                // pass 1: maximum over this thread's 64 columns (two 32-column reads), then over the row through
-                // shared memory.  S is read from TMEM again in pass 2 instead of being kept: 64 more live registers
-                // would spill at two CTAs per SM.
-                float v[32];
-                float tmax = -INFINITY;
-#pragma unroll 1
+                const uint32_t t_s    = t_row + kSCol + kKeys * sb;
+                const int      k0     = j * kKeys;
+                const bool     masked = k0 + kKeys - 1 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
+                // 32-column blocks with at least one key some row of this warp sees (warp-uniform)
+                const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
+                uint32_t       r[64];
+#pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    tmem_ld32(t_row + 64 * half + 32 * c, v);
-                    if (masked) {
+                    if (c < n_live) {
+                        tmem_ld32_nowait(t_s + 32 * c, r + 32 * c);
+                    } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = k0 + 32 * c + i > limit ? -INFINITY : v[i];
+                        for (int i = 0; i < 32; ++i) r[32 * c + i] = 0xff800000u;  // -inf: no weight
                     }
-                    float t0 = v[0], t1 = v[1], t2 = v[2], t3 = v[3];  // four chains instead of one long dependency
-#pragma unroll
-                    for (int i = 4; i < 32; i += 4) {
-                        t0 = fmaxf(t0, v[i]); t1 = fmaxf(t1, v[i + 1]); t2 = fmaxf(t2, v[i + 2]); t3 = fmaxf(t3, v[i + 3]);
-                    }
-                    tmax = fmaxf(tmax, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
                 }
-                half_max[T & 1][half][row] = tmax;
-                named_bar_sync(1, kSoftmaxThreads);
-                tmax = fmaxf(tmax, half_max[T & 1][half ^ 1][row]) * p.scale_log2;
-                // the previous tile's P.V must have retired before P is overwritten (and before O is touched);
-                // at the first tile of an item that wait was done when the previous item was read out
-                if (j > 0 && !mbar_wait_bounded(bPVdone, (T - 1) & 1)) { give_up(); ok = false; break; }
-                // tcgen05.ld/st are warp-collective: the decision to rescale is taken per warp (any lane), and lanes
-                // that do not need it take part with a factor of 1
-                const bool raise = j > 0 && tmax > m_ref + 8.0f;
+                tmem_wait_ld();
+                PROF_STOP(10);
+#pragma unroll
+                for (int i = 0; i < 64; ++i) pin(r[i]);
+                if (masked) {  // only the tiles the causal diagonal or the end of the keys cuts through
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (k0 + i > limit) r[i] = 0xff800000u;
+                }
+                float cmax;
+                {
+                    float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 64; i += 4) {
+                        t0 = max3(t0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                        t1 = max3(t1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                    }
+                    cmax = fmaxf(t0, t1) * p.scale_log2;
+                }
+                PROF_STOP(11);
+                // The weights are written only after the whole tile has been looked at, so a raise of the
+                // reference needs no second pass.  tcgen05.ld/st are warp-collective: the decision to rescale is
+                // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.
                 if (j == 0) {
-                    m_ref = tmax;  // key 0 is visible to every row: finite
-                } else if (__any_sync(0xffffffffu, raise)) {
-                    const float f = raise ? ex2_approx(m_ref - tmax) : 1.0f;
-                    if (raise) m_ref = tmax;
-                    rescale_accumulators(t_row, half, f);
+                    m_ref = cmax;  // key 0 is visible to every row: finite
+                } else {
+                    const bool raise = cmax > m_ref + 8.0f;
+                    if (__any_sync(0xffffffffu, raise)) {
+                        const float f = raise ? ex2_approx(m_ref - cmax) : 1.0f;
+                        if (raise) m_ref = cmax;
+                        // the accumulators are at rest once P.V of the previous tile has retired
+                        if (!mbar_wait_bounded(vempty0 + 8 * ((T - 1) % kStages), ((T - 1) / kStages) & 1)) { give_up(); ok = false; break; }
+                        rescale_accumulators(t_row, f);
+                    }
                 }
-                // pass 2: P = 2^(c*S - m_ref), f16, into this thread's 64-key half of the P tile, 8 keys (16 bytes) at a time
-#pragma unroll 1
+#ifndef VOX_PREFILL_NOSOFTMAX
+                // P = 2^(c*S - m_ref) as packed f16 over the first half of the scores just read
+#pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    tmem_ld32(t_row + 64 * half + 32 * c, v);
-                    if (c == 1) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bSfree);  // S has been read for the last time: the next Q.K^T may overwrite it
-                    }
-                    if (masked) {
+                    uint32_t h[16];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = k0 + 32 * c + i > limit ? -INFINITY : v[i];
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        uint32_t h[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            h[i] = pack_half2(ex2_approx(fmaf(v[8 * u + 2 * i], p.scale_log2, -m_ref)),
-                                              ex2_approx(fmaf(v[8 * u + 2 * i + 1], p.scale_log2, -m_ref)));
-                        *reinterpret_cast<uint4 *>(p_dst + (((4 * c + u) ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                    }
+                    for (int i = 0; i < 16; ++i)
+#ifdef VOX_PREFILL_NOEXP  // experiment: everything but the exponentials
+                        h[i] = pack_half2(fmaf(__uint_as_float(r[32 * c + 2 * i]), p.scale_log2, -m_ref),
+                                          fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), p.scale_log2, -m_ref));
+#else
+                        h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i]), p.scale_log2, -m_ref)),
+                                          ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), p.scale_log2, -m_ref)));
+#endif
+                    tmem_st16_nowait(t_s + 16 * c, h);
                 }
-                fence_proxy_async_smem();
+#endif
+                PROF_STOP(2);
+                tmem_wait_st();
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bPready);  // this warp's part of P is visible to the tensor core
+                if (lane == 0) mbar_arrive(bP0 + 8 * sb);  // this warp's rows of P are in TMEM
+                if (tid == 0) PROF_TRACE(1, T);
+                PROF_STOP(3);
             }
             if (!ok || aborted()) break;
-            // item done: read the result out once the last P.V has retired, then bring in the next item's Q rows
+            // item done.  Every Q.K^T of this item retired before its last scores were read, so the next item's Q
+            // tile goes in first (its first Q.K^T then runs while this item's result is read out); the output
+            // columns are handed back to the tensor core once they have been read.
             const bool have_next = work_item(p, round + 1, wn);
-            if (!mbar_wait_bounded(bPVdone, (T - 1) & 1)) { give_up(); break; }
+            if (have_next) {
+                float4 qv[16];
+                load_q(wn, qv);
+                store_q(qv);
+            }
+            PROF_STOP(6);
+            if (!mbar_wait_bounded(bO, round & 1)) { give_up(); break; }
+            PROF_STOP(4);
             // warp-collective TMEM reads by every lane; only rows that exist are stored
             tc_fence_after();
-            const float l = tmem_ld1(t_row + kTile + kHeadDim);  // sum of exactly the rounded weights the tensor core used
-            float o[32];
-            tmem_ld32(t_row + kTile + 32 * half, o);
-            tc_fence_before();
-            if (live) {
-                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                float4 * out = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + w.head) * kHeadDim + 32 * half);
+            const float l   = tmem_ld1(t_row + kOCol + kHeadDim);  // sum of exactly the rounded weights the tensor core used
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float4 *    out = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + w.head) * kHeadDim);
+            float       o[64];
+            {
+                uint32_t r[64];
+                tmem_ld32_nowait(t_row + kOCol, r);
+                tmem_ld32_nowait(t_row + kOCol + 32, r + 32);
+                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    out[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+                for (int i = 0; i < 64; ++i) {
+                    pin(r[i]);
+                    o[i] = __uint_as_float(r[i]) * inv;
+                }
             }
-            // every Q.K^T of this item has retired (its last S was consumed above), so the Q tile may be replaced
-            if (have_next) {
-                float4 qv[8];
-                load_q(wn, qv);
-                store_q(qv, round + 1);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bOfree);
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) out[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
             }
+            PROF_STOP(5);
+            PROF_COUNT(9, 1);
             have = have_next;
             w    = wn;
         }
+        // 0 other, 1 wait S, 2 softmax blocks, 3 store wait + signal, 4 wait O, 5 read-out, 6 next Q, 7 tiles, 8 passes, 9 items
+        if (lane == 0) PROF_FLUSH(9 + 0, 12);  // 10 wait for a block of scores, 11 block maximum
     }
 
     // common exit: tensor-core work has been waited for by the softmax warps; release TMEM
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
@@ -499,6 +628,20 @@ bool tc_route_ok(const vox_attn_args * a) {
 
 extern "C" {
 
+#ifdef VOX_PREFILL_PROFILE
+int vox_debug_prefill_trace(long long * out) {
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 4 * 64) != cudaSuccess;
+}
+int vox_debug_prefill_profile(unsigned long long * out, int reset) {
+    if (out && cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+    if (reset) {
+        unsigned long long zero[32] = {0};
+        if (cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#endif
+
 size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a) {
     (void) a;
     return 0;
@@ -520,7 +663,7 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
 
     CUtensorMap    mk, mv;
     const uint64_t dims[5] = {64, (uint64_t) a->k.ne[1], (uint64_t) a->k.ne[2], (uint64_t) a->k.ne[3], 1};
-    const uint32_t box[5]  = {64, kTile, 1, 1, 1};
+    const uint32_t box[5]  = {64, kKeys, 1, 1, 1};
     const vox_tensor * ts[2] = {&a->k, &a->v};
     CUtensorMap *      ms[2] = {&mk, &mv};
     for (int i = 0; i < 2; ++i) {
