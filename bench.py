@@ -380,10 +380,10 @@ def main():
         peak, peak_src = 6650.0, "fallback"
     roofline = {"bound": "hbm", "kernel": f"decode_kernel<{args.kv_type}> (split-KV, partials folded by the last CTA of each stream and kv head)",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                # DRAM bytes per launch: one ncu capture of a 32-stream launch read 1.012x (f16) / 1.010x (q8_0) the
+                # DRAM bytes per launch: ncu captures of the 256-stream launch read 1.041x (f16) / 1.043x (q8_0) the
                 # algorithmic bytes (the ncu summaries kept under profiles/); traffic grows with the streams' KV bytes
-                "traffic": layer_bytes * (1.012 if args.kv_type == "f16" else 1.010),
-                "traffic_source": "ncu capture of a 32-stream launch, scaled by algorithmic bytes",
+                "traffic": layer_bytes * (1.041 if args.kv_type == "f16" else 1.043),
+                "traffic_source": "ncu capture of the 256-stream launch (DRAM bytes / algorithmic bytes), applied to this launch's algorithmic bytes",
                 "peak_source": peak_src,
                 "us_per_launch": dec_ms * 1e3, "algorithmic_bytes_per_launch": layer_bytes,
                 "frac_of_nominal_8000": achieved / 8000.0}
