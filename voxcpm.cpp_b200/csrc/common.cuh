@@ -216,6 +216,14 @@ __device__ __forceinline__ void split_hi_lo(float x, float & hi, float & lo) {
     lo = x - hi;
 }
 
+// 2^x on the special-function unit: one MUFU instruction, relative error 2^-22, results below 2^-126 flushed
+// to zero (exp2f adds range handling for arguments the kernels here never produce)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
 }

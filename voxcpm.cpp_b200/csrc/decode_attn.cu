@@ -351,14 +351,14 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
             const float m_new = fmaxf(m, tmax);
-            const float alpha = m_new == -INFINITY ? 1.0f : exp2f(m - m_new);
+            const float alpha = m_new == -INFINITY ? 1.0f : ex2_approx(m - m_new);
             const float m_use = m_new == -INFINITY ? 0.0f : m_new;
             m                 = m_new;
             float pr[2][2];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                pr[j][0] = exp2f(sv[j][0] - m_use);
-                pr[j][1] = exp2f(sv[j][1] - m_use);
+                pr[j][0] = ex2_approx(sv[j][0] - m_use);
+                pr[j][1] = ex2_approx(sv[j][1] - m_use);
             }
             if (__any_sync(0xffffffffu, alpha != 1.0f)) {  // after the first tiles the running maxima rarely move
 #pragma unroll

@@ -191,13 +191,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
-// 2^x on the special-function unit (one MUFU instruction; arguments here are <= 0)
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 // Shared-memory matrix descriptor (64-bit) of a 128-byte-swizzled tile whose 8-row groups are 1024
 // bytes apart: start address, leading/stride byte offsets (>> 4), descriptor version 1, layout type 2.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
