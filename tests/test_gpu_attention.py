@@ -69,6 +69,66 @@ def test_forward_with_strided_views(engine, oracle, vo):
     assert rel_err(out.cpu().numpy(), ref) < TOL["f16"]
 
 
+def _ggml_grid():
+    """The head-size-64 slice of the reference's own operator test (test_flash_attn_ext,
+    third_party/ggml/tests/test-backend-ops.cpp:8286-8329): 4 KV heads, GQA ratio nr2, batch nr3, kv, n_q = nb,
+    with and without mask, every K/V type this engine stores."""
+    for mask in (True, False):
+        for nr3 in (1, 3):
+            for nr2 in (1, 4):
+                for kv in (113, 512, 1024):
+                    if nr2 != 1 and kv != 512:
+                        continue
+                    for nb in (1, 3, 32, 75):
+                        for kv_type in ("f32", "f16", "q8_0"):
+                            yield pytest.param(mask, nr3, nr2, kv, nb, kv_type, id=f"mask{int(mask)}-nr3_{nr3}-nr2_{nr2}-kv{kv}-nb{nb}-{kv_type}")
+
+
+def _kq_mask(rng, n_kv, n_q, ne3):
+    """init_tensor_kq_mask of the same file (:152-193): uniform values, and 20 % of the 128x64 blocks set to
+    -inf or 0 at random places."""
+    m = rng.uniform(-1.0, 1.0, (ne3, 1, n_q, n_kv)).astype(np.float32)
+    for _ in range(int(0.2 * m.size / (128 * 64))):
+        p3, p1, p0 = rng.integers(ne3), rng.integers(n_q), rng.integers(n_kv)
+        m[p3, 0, p1:p1 + 64, p0:p0 + 128] = -np.inf if rng.integers(2) else 0.0
+    return m.astype(np.float16)
+
+
+@pytest.mark.parametrize("mask, nr3, nr2, kv, nb, kv_type", list(_ggml_grid()))
+def test_forward_on_the_reference_test_grid(mask, nr3, nr2, kv, nb, kv_type, engine, oracle, vo):
+    """Same shapes, value ranges, mask construction and K/V-as-cache-view layout as the reference's backend test, which
+    accepts a backend at NMSE <= 5e-4 against its CPU op; here both that metric and this engine's own tolerance apply,
+    against the accurate path of the CPU algorithm."""
+    import torch
+    import zlib
+    rng = np.random.default_rng(zlib.crc32(f"{mask}-{nr3}-{nr2}-{kv}-{nb}-{kv_type}".encode()))
+    HKg, Hg = 4, 4 * nr2
+    q = rng.uniform(-1, 1, (nr3, Hg, nb, D)).astype(np.float32)
+    k = rng.uniform(-1, 1, (nr3, HKg, kv, D)).astype(np.float32)
+    v = rng.uniform(-1, 1, (nr3, HKg, kv, D)).astype(np.float32)
+    if kv_type == "f16":
+        ks, vs = k.astype(np.float16), v.astype(np.float16)
+    elif kv_type == "q8_0":
+        ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+    else:
+        ks, vs = k, v
+    m = _kq_mask(rng, kv, nb, nr3) if mask else None
+    # K and V are views of tensors twice as long, as in the reference test ("usually a view of the cache")
+    def as_view(x):
+        t = dev(x)
+        big = torch.zeros((t.shape[0], t.shape[1], 2 * t.shape[2], t.shape[3]), dtype=t.dtype, device="cuda")
+        big[:, :, :t.shape[2]] = t
+        return big[:, :, :t.shape[2]]
+    out = engine.forward(dev(q), as_view(ks), as_view(vs), dev(m) if m is not None else None)
+    engine.sync_status()
+    out = out.cpu().numpy()
+    ref = oracle.attn(q, ks, vs, m, kv_type=KV_TYPE[kv_type], path=vo.PATH_ROW_F32)
+    assert np.all(np.isfinite(out))
+    nmse = float(((out.astype(np.float64) - ref) ** 2).sum() / max((ref.astype(np.float64) ** 2).sum(), 1e-30))
+    assert nmse <= 5e-4
+    assert rel_err(out, ref) < TOL[kv_type]
+
+
 def test_forward_refuses_bad_operands(engine, pkg):
     import torch
     q = torch.zeros((1, H, 1, D), device="cuda")
