@@ -49,6 +49,8 @@ def parse():
     p.add_argument("--cpu-sample-streams", type=int, default=24)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--rope", action="store_true",
+                   help="hand Q and the new K rows over before the rotary embedding: one cos/sin table per step, rotation inside the decode launches")
     p.add_argument("--prefill-shapes", default="512x1,512x8", help="LxB list for --workload prefill")
     p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1"],
                    help="serving = the headline line; the others time one more configuration each on one GPU")
@@ -328,6 +330,8 @@ def main():
                       n_heads=H, n_kv_heads=HK, locdit_layers=DIT_LAYERS, locdit_seq=DIT_SEQ, cfm_steps=CFM_STEPS)
     group.set_kv_len(lens)
     group.fill_synthetic(seed=rank)
+    if args.rope:  # llama.rope.freq_base of the reference's GGUF defaults, per-frequency factors as LongRoPE ships them
+        group.set_rope(freq_base=10000.0, attn_factor=1.0, freq_factors=np.linspace(1.0, 4.0, 32, dtype=np.float32))
     shapes = group.buffer_shapes()
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
     dev_t = {n: (torch.empty(s, device="cuda") if n.endswith("out") else torch.randn(s, device="cuda", generator=gen))
@@ -445,6 +449,7 @@ def main():
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD.format(s=args.streams), "streams_total": int(total_streams), "kv_type": args.kv_type,
                            "l2": "inputs larger than L2 (KV read per step >> 126 MB)", "append": "included",
+                           "rope": "rotary embedding of Q and the new K rows inside the decode launches" if args.rope else "applied by the caller",
                            "arithmetic": "f16 K/V (or q8_0), f32 Q and output, f16 tensor-core products with hi+lo split of Q and P, "
                                          "f32 accumulation; LocDiT f32 throughout"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_info,

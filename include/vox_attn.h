@@ -90,6 +90,13 @@ uint64_t vox_engine_launch_count(const vox_engine * e);
  * ggml_backend_graph_compute (src/backend.cpp:564-570).  Clears the word. */
 int vox_engine_sync_status(vox_engine * e, void * stream);
 
+/* Failure-path self-test without a fault: launches one thread that waits, for at most limit_cycles SM
+ * clock cycles (<= 2e9), on a barrier nothing ever arrives at.  The wait gives up the way every bounded
+ * wait of the engine's kernels does: it raises the device status word and the kernel returns normally.
+ * The next vox_engine_sync_status reports VOX_ATTN_TIMEOUT and the context stays usable.  (The reference
+ * has no counterpart: a stuck ggml-cuda kernel ends in the driver's watchdog or not at all.) */
+int vox_engine_selftest_wait(vox_engine * e, long long limit_cycles, void * stream);
+
 /* ---------------------------------------------------------------- generic operator ----- */
 
 /* Replaces ggml_cuda_flash_attn_ext_supported (third_party/ggml/src/ggml-cuda/fattn.cu:480-482).
@@ -159,6 +166,28 @@ int vox_kv_export(const vox_kv_cache * c, int layer, int stream_id, int n_pos, v
 int vox_kv_import(vox_kv_cache * c, int layer, int stream_id, int n_pos, const void * k_host, const void * v_host);
 int vox_kv_copy_from(vox_kv_cache * dst, const vox_kv_cache * src, void * stream); /* ::copy_from */
 
+/* ---------------------------------------------------------------- rotary embedding ------ */
+
+/* Rotary position embedding of the decode step.  MiniCPMModel::apply_rope (src/minicpm.cpp:582-600)
+ * issues ggml_rope_ext (GGML_ROPE_TYPE_NEOX, n_dims = 64, freq_scale 1, ext_factor 0) on Q and on K
+ * in every layer, each time rebuilding the cos/sin cache of the token's position.  Here the table is
+ * built once per step and the decode launch rotates Q and the arriving K row itself.
+ *   freq_base     llama.rope.freq_base
+ *   attn_factor   1, or the magnitude factor apply_rope derives beyond the original context
+ *   freq_factors  device pointer to 32 floats (rope_short_factor / rope_long_factor), or NULL    */
+typedef struct {
+    float         freq_base;
+    float         attn_factor;
+    const float * freq_factors;
+} vox_rope_config;
+
+/* table[s][i] = (cos, sin)(theta_i / freq_factors[i]) * attn_factor for stream s at position
+ * positions[s] + pos_offset, i < 32; theta_0 = position, theta_{i+1} = theta_i * freq_base^(-2/64)
+ * (ggml_rope_cache_init).  positions is a device array; table is device memory of
+ * n_streams * 64 floats.  One launch. */
+int vox_rope_table(vox_engine * e, const vox_rope_config * cfg, const int32_t * positions, int pos_offset,
+                   int n_streams, float * table, void * stream);
+
 /* ---------------------------------------------------------------- decode --------------- */
 
 /* One-token attention for n_streams independent streams in one launch (+ a merge launch when
@@ -176,6 +205,10 @@ int vox_kv_copy_from(vox_kv_cache * dst, const vox_kv_cache * src, void * stream
  *            attention, so no append launch is needed.  A stream whose kv_len exceeds the cache
  *            capacity writes nothing and raises the engine's status (vox_engine_sync_status).
  *            The cache is written: do not run two such calls on one layer concurrently.
+ *   rope_table  optional: the table vox_rope_table built for these streams' positions
+ *            (kv_len - 1).  q and k_new are then the projections BEFORE the rotary embedding
+ *            and the launch rotates them (element i with element i + 32) as it reads them;
+ *            v_new is stored as it is.  NULL: q and k_new are already rotated.
  *   flags    VOX_DECODE_CACHE_STABLE: a promise that neither kv_len nor any cache row this call reads
  *            was written by the kernel launched just before it on the same stream (q, k_new and
  *            v_new may have been).  True for the layers of a model, where a projection GEMM
@@ -198,6 +231,7 @@ typedef struct {
     const float *   v_new;
     size_t          new_nb_head, new_nb_stream;
     uint32_t        flags;
+    const float *   rope_table;
 } vox_decode_args;
 
 size_t vox_attn_decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);
@@ -286,10 +320,16 @@ int vox_group_get_kv_len(const vox_group * g, int32_t * kv_len);
  * generator seeded with `seed` (synthetic prompt state for benchmarks). */
 int vox_group_fill_synthetic(vox_group * g, uint64_t seed, void * stream);
 size_t vox_group_step_bytes(const vox_group * g, int which /* 0 lm in, 1 lm out, 2 dit in, 3 dit out */);
+/* Rotary embedding inside the step: with a configuration set, lm_q and lm_k_new of vox_step_buffers are the
+ * projections BEFORE apply_rope (src/minicpm.cpp:582-600); each step builds one cos/sin table for the
+ * streams' positions (one launch) and every layer's decode launch rotates Q and the arriving K row.
+ * freq_factors_host: 32 floats on the host (copied), or NULL.  cfg == NULL switches it off again. */
+int vox_group_set_rope(vox_group * g, const vox_rope_config * cfg, const float * freq_factors_host);
 
-/* One decode step on device buffers.  advance != 0 appends the new rows and grows every stream
- * by one position; advance == 0 attends to the current rows only (append excluded, lengths
- * fixed).  Launches: 2 per LM layer with append (+1 merge when split), 1 per CFM step. */
+/* One decode step on device buffers.  advance != 0 stores the new rows and grows every stream
+ * by one position; advance == 0 attends to the current rows only (lengths fixed).
+ * Launches: one per LM layer (it stores the arriving row and folds the split-KV partials itself), one
+ * length update, one rotary table when set, one per CFM step. */
 int vox_group_step(vox_group * g, const vox_step_buffers * dev, int advance, void * stream);
 /* The same step from pinned HOST buffers: H2D of the inputs, the launches, D2H of the outputs,
  * overlapped on the group's own streams; returns after the outputs have landed. */

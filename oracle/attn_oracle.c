@@ -484,3 +484,34 @@ int voxo_flash_attn_ext(const voxo_tensor * q, const voxo_tensor * k, const voxo
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------ rotary embedding */
+
+void voxo_rope_table(const int32_t * pos, int64_t n_pos, int n_dims, float freq_base, float attn_factor,
+                     const float * freq_factors, float * table) {
+    const float theta_scale = powf(freq_base, -2.0f / n_dims); /* ops.cpp:5778 */
+    for (int64_t p = 0; p < n_pos; ++p) {
+        float theta = (float) pos[p]; /* theta_base = position (ops.cpp: cache init per token) */
+        for (int i0 = 0; i0 < n_dims; i0 += 2) {
+            const float ff = freq_factors ? freq_factors[i0 / 2] : 1.0f;
+            const float th = 1.0f * (theta / ff); /* rope_yarn with freq_scale 1 and ext_factor 0 */
+            table[(p * (n_dims / 2) + i0 / 2) * 2 + 0] = cosf(th) * attn_factor;
+            table[(p * (n_dims / 2) + i0 / 2) * 2 + 1] = sinf(th) * attn_factor;
+            theta *= theta_scale;
+        }
+    }
+}
+
+void voxo_rope_neox(float * x, int64_t n_rows, int n_dims, const float * table, const int32_t * pos_index) {
+    const int half = n_dims / 2;
+    for (int64_t r = 0; r < n_rows; ++r) {
+        const float * tb  = table + (int64_t) pos_index[r] * half * 2;
+        float *       row = x + r * n_dims;
+        for (int i = 0; i < half; ++i) {
+            const float c = tb[2 * i], s = tb[2 * i + 1];
+            const float x0 = row[i], x1 = row[i + half];
+            row[i]        = x0 * c - x1 * s;
+            row[i + half] = x0 * s + x1 * c;
+        }
+    }
+}

@@ -72,6 +72,20 @@ void voxo_cfg_pair_mask(int seq, uint16_t * mask);
  * (src/minicpm.cpp:684-685). */
 void voxo_kv_store(const float * x, int64_t n_rows, int64_t D, int type, void * dst);
 
+/* Rotary position embedding as MiniCPMModel::apply_rope asks for it (src/minicpm.cpp:582-600:
+ * ggml_rope_ext, GGML_ROPE_TYPE_NEOX, freq_scale 1, ext_factor 0, optional per-frequency
+ * factors, attn_factor on cos and sin).
+ *   voxo_rope_table: table[p][i] = (cos, sin) of theta_i / ff_i, times attn_factor, for
+ *     n_pos positions and i < n_dims/2, with theta_0 = pos and theta_{i+1} = theta_i *
+ *     powf(freq_base, -2/n_dims) (ggml_rope_cache_init, rope_yarn:
+ *     third_party/ggml/src/ggml-cpu/ops.cpp:5596-5629, theta_scale at :5778).
+ *   voxo_rope_neox: rotates n_rows rows of n_dims floats in place, pairing element i with
+ *     element i + n_dims/2 (rotate_pairs, ops.cpp:5701-5718); row r uses the table entry of
+ *     position index pos_index[r]. */
+void voxo_rope_table(const int32_t * pos, int64_t n_pos, int n_dims, float freq_base, float attn_factor,
+                     const float * freq_factors, float * table);
+void voxo_rope_neox(float * x, int64_t n_rows, int n_dims, const float * table, const int32_t * pos_index);
+
 #ifdef __cplusplus
 }
 #endif

@@ -118,4 +118,41 @@ int voxref_attn(int n_layers, const float * q, const void * k, const void * v, c
     return rc;
 }
 
+// ggml_rope_ext exactly as MiniCPMModel::apply_rope issues it (src/minicpm.cpp:582-600): NEOX pairing,
+// n_dims = D, freq_scale 1, ext_factor 0, beta_fast 32, beta_slow 1.
+//   x            : [D, n_heads, n_tok] f32, contiguous (the projection layout)
+//   positions    : n_tok int32
+//   freq_factors : NULL or D/2 floats
+//   out          : same shape as x
+int voxref_rope(const float * x, int64_t D, int64_t n_heads, int64_t n_tok, const int32_t * positions,
+                const float * freq_factors, int n_ctx_orig, float freq_base, float attn_factor, int n_threads, float * out) {
+    ggml_init_params ip = {
+        /*.mem_size   =*/ ggml_tensor_overhead() * 8 + ggml_graph_overhead_custom(16, false) + 4096,
+        /*.mem_buffer =*/ nullptr,
+        /*.no_alloc   =*/ true,
+    };
+    ggml_context * ctx = ggml_init(ip);
+    if (!ctx) return 2;
+    ggml_tensor * tx = ggml_new_tensor_3d(ctx, GGML_TYPE_F32, D, n_heads, n_tok);
+    ggml_tensor * tp = ggml_new_tensor_1d(ctx, GGML_TYPE_I32, n_tok);
+    ggml_tensor * tf = nullptr;
+    tx->data = (void *) x;
+    tp->data = (void *) positions;
+    if (freq_factors) {
+        tf = ggml_new_tensor_1d(ctx, GGML_TYPE_F32, D / 2);
+        tf->data = (void *) freq_factors;
+    }
+    ggml_tensor * to = ggml_rope_ext(ctx, tx, tp, tf, (int) D, GGML_ROPE_TYPE_NEOX, n_ctx_orig, freq_base, 1.0f, 0.0f,
+                                     attn_factor, 32.0f, 1.0f);
+    to->data = out;
+    ggml_cgraph * gf = ggml_new_graph_custom(ctx, 16, false);
+    ggml_build_forward_expand(gf, to);
+    ggml_cplan plan = ggml_graph_plan(gf, n_threads, nullptr);
+    std::vector<uint8_t> work(plan.work_size + 64);
+    plan.work_data = work.data();
+    const int rc = ggml_graph_compute(gf, &plan) == GGML_STATUS_SUCCESS ? 0 : 3;
+    ggml_free(ctx);
+    return rc;
+}
+
 }  // extern "C"

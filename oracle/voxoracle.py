@@ -99,6 +99,30 @@ class Oracle:
         self.lib.voxo_kv_store(_ptr(x), ctypes.c_int64(x.size // D), ctypes.c_int64(D), kv_type, _ptr(out))
         return out.view(np.float16) if kv_type == F16 else out
 
+    def rope_table(self, positions, freq_base=10000.0, attn_factor=1.0, freq_factors=None, n_dims=64) -> np.ndarray:
+        """(cos, sin) table [n_pos, n_dims/2, 2] of the reference's rotary embedding."""
+        pos = np.ascontiguousarray(positions, np.int32)
+        ff = None if freq_factors is None else np.ascontiguousarray(freq_factors, np.float32)
+        out = np.zeros((len(pos), n_dims // 2, 2), np.float32)
+        self.lib.voxo_rope_table(_ptr(pos), ctypes.c_int64(len(pos)), int(n_dims), ctypes.c_float(freq_base),
+                                 ctypes.c_float(attn_factor), _ptr(ff), _ptr(out))
+        return out
+
+    def rope(self, x, table, pos_index=None) -> np.ndarray:
+        """NEOX rotation of rows x[..., n_dims]; row r uses table[pos_index[r]] (default: x.shape[0]
+        leading index, i.e. x is [n_pos, ..., n_dims])."""
+        x = np.array(x, np.float32, order="C")
+        n_dims = x.shape[-1]
+        rows = x.reshape(-1, n_dims)
+        if pos_index is None:
+            per = rows.shape[0] // x.shape[0]
+            pos_index = np.repeat(np.arange(x.shape[0], dtype=np.int32), per)
+        pos_index = np.ascontiguousarray(pos_index, np.int32)
+        assert len(pos_index) == rows.shape[0]
+        self.lib.voxo_rope_neox(_ptr(rows), ctypes.c_int64(rows.shape[0]), int(n_dims), _ptr(np.ascontiguousarray(table, np.float32)),
+                                _ptr(pos_index))
+        return rows.reshape(x.shape)
+
     def causal_mask(self, positions, total_len: int) -> np.ndarray:
         pos = np.ascontiguousarray(positions, np.int32)
         out = np.zeros((len(pos), total_len), np.uint16)
@@ -177,6 +201,20 @@ class RefGgml:
         out = np.zeros(x.shape, np.uint16)
         self.lib.voxref_fp32_to_fp16(_ptr(x), _ptr(out), ctypes.c_int64(x.size))
         return out.view(np.float16)
+
+    def rope(self, x, positions, freq_base=10000.0, attn_factor=1.0, freq_factors=None, n_ctx_orig=32768, n_threads=1):
+        """ggml_rope_ext (NEOX) on x [n_tok, n_heads, D] f32 with one position per token."""
+        x = np.ascontiguousarray(x, np.float32)
+        n_tok, n_heads, D = x.shape
+        pos = np.ascontiguousarray(positions, np.int32)
+        ff = None if freq_factors is None else np.ascontiguousarray(freq_factors, np.float32)
+        out = np.zeros_like(x)
+        i64 = ctypes.c_int64
+        rc = self.lib.voxref_rope(_ptr(x), i64(D), i64(n_heads), i64(n_tok), _ptr(pos), _ptr(ff), int(n_ctx_orig),
+                                  ctypes.c_float(freq_base), ctypes.c_float(attn_factor), int(n_threads), _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"reference harness failed (code {rc})")
+        return out
 
     def attn(self, q, k, v, mask=None, scale=0.125, kv_type=F16, n_threads=1, iters=1, use_ref=False,
              n_layers=1, return_ms=False):

@@ -76,6 +76,24 @@ def make_inputs(case, oracle):
     return dict(q=q, k=ks, v=vs, kf=kf, vf=vf, mask=make_mask(case, oracle))
 
 
+# Rotary embedding: (tokens, heads) of 64-wide rows at the listed positions; "long" uses per-frequency factors
+# and the magnitude factor apply_rope derives for sequences beyond the original context.
+ROPE_CASES = {
+    "rope_plain": dict(seed=30, n_heads=16, freq_base=10000.0, attn_factor=1.0, factors=False, n_ctx_orig=32768,
+                       positions=[0, 1, 2, 63, 64, 255, 1000, 4095]),
+    "rope_long": dict(seed=31, n_heads=2, freq_base=1000000.0, attn_factor=1.1893, factors=True, n_ctx_orig=4096,
+                      positions=[0, 7, 511, 4096, 8191, 20000, 32767]),
+}
+
+
+def rope_inputs(args):
+    rng = np.random.default_rng(args["seed"])
+    pos = np.array(args["positions"], np.int32)
+    x = rng.standard_normal((len(pos), args["n_heads"], D)).astype(np.float32)
+    ff = (1.0 + 3.0 * rng.random(D // 2)).astype(np.float32) if args["factors"] else None
+    return x, pos, ff
+
+
 def digest(inp) -> str:
     h = hashlib.sha256()
     for name in ("q", "k", "v"):

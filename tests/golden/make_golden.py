@@ -26,7 +26,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(HERE))
 
 from oracle import voxoracle as vo  # noqa: E402
-from cases import CASES, KV_TYPE, digest, make_inputs  # noqa: E402
+from cases import CASES, KV_TYPE, ROPE_CASES, digest, make_inputs, rope_inputs  # noqa: E402
 
 
 def main():
@@ -50,6 +50,13 @@ def main():
     out["storage/x"] = x
     out["storage/q8_0"] = ref.quantize_q8_0(x)
     out["storage/f16"] = ref.fp32_to_fp16(x).view(np.uint16)
+    # rotary embedding as apply_rope issues it (src/minicpm.cpp:582-600): plain, and with per-frequency factors
+    # and a magnitude factor (the long-context setting); inputs are regenerated from the seed by the tests
+    for name, args in ROPE_CASES.items():
+        x, pos, ff = rope_inputs(args)
+        out[name + "/out"] = ref.rope(x, pos, freq_base=args["freq_base"], attn_factor=args["attn_factor"], freq_factors=ff,
+                                      n_ctx_orig=args["n_ctx_orig"])
+        print(f"{name:32s} rope of {x.shape}")
     path = os.path.join(HERE, "attn_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {os.path.getsize(path) / 1024:.0f} KiB")

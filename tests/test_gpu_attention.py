@@ -146,6 +146,26 @@ def test_forward_refuses_bad_operands(engine, pkg):
     assert e.value.status_name == "UNSUPPORTED"
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_engine_keeps_working(engine, pkg, oracle, vo):
+    """Failure detection without a fault: a kernel waits (about a millisecond) on a barrier nothing arrives at, gives
+    up the way every bounded wait of the engine does, and the host reads that as a status; the context is intact."""
+    engine.sync_status()
+    engine.selftest_wait(limit_cycles=2_000_000)
+    with pytest.raises(pkg.VoxError) as e:
+        engine.sync_status()
+    assert e.value.status_name == "TIMEOUT" and "bounded wait" in str(e.value)
+    engine.sync_status()  # the word was cleared by the report
+    rng = np.random.default_rng(2)
+    q = rng.standard_normal((1, H, 1, D)).astype(np.float32)
+    k = rng.standard_normal((1, HK, 300, D)).astype(np.float16)
+    v = rng.standard_normal((1, HK, 300, D)).astype(np.float16)
+    out = engine.forward(dev(q), dev(k), dev(v))
+    engine.sync_status()
+    assert rel_err(out.cpu().numpy(), oracle.attn(q, k, v, kv_type=vo.F16, path=vo.PATH_ROW_F32)) < TOL["f16"]
+    with pytest.raises(pkg.VoxError):
+        engine.selftest_wait(limit_cycles=10 ** 12)  # limits above a second are refused
+
+
 # ------------------------------------------------------------------ KV cache
 
 @pytest.mark.parametrize("kv", ["f16", "q8_0"])
@@ -391,6 +411,60 @@ def test_decode_with_arriving_row_reports_a_stream_beyond_capacity(engine, pkg):
         cache.decode(0, q, dev(np.array([1, 1], np.int32)), 1, k_new=rows)  # v_new missing
 
 
+def test_rope_table_matches_the_reference_angles(engine, oracle):
+    pos = np.array([0, 1, 2, 63, 255, 1000, 4095, 8191, 32767], np.int32)
+    rng = np.random.default_rng(4)
+    ff = (1.0 + 3.0 * rng.random(32)).astype(np.float32)
+    for args in (dict(freq_base=10000.0, attn_factor=1.0, freq_factors=None),
+                 dict(freq_base=1000000.0, attn_factor=1.1893, freq_factors=ff)):
+        got = engine.rope_table(dev(pos + 1), pos_offset=-1, freq_base=args["freq_base"], attn_factor=args["attn_factor"],
+                                freq_factors=dev(ff) if args["freq_factors"] is not None else None)
+        engine.sync_status()
+        want = oracle.rope_table(pos, **args)
+        # same f32 angle (built by the same chain of multiplications); cosf/sinf of the device and of the host's libm
+        # may differ in the last place
+        assert np.abs(got.cpu().numpy() - want).max() <= 4e-7 * args["attn_factor"]
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+def test_decode_rotates_q_and_the_arriving_row(kv, engine, pkg, oracle, vo):
+    """q and k_new handed over BEFORE the rotary embedding, with the step's cos/sin table: the cache must hold the
+    rotated K row (bit for bit what the reference's rope + cpy store, given the same table) and the output must be the
+    attention of the rotated query."""
+    lens = [1, 17, 64, 65, 300, 512, 513, 1025, 2048]
+    rng = np.random.default_rng(91)
+    S, cap = len(lens), 2048
+    cache = pkg.KVCache(engine, 1, S, HK, cap, KV_TYPE[kv])
+    for s, n in enumerate(lens):
+        if n > 1:
+            k = rng.standard_normal((HK, n - 1, D)).astype(np.float32)
+            v = rng.standard_normal((HK, n - 1, D)).astype(np.float32)
+            cache.import_(0, s, oracle.kv_store(k, KV_TYPE[kv]), oracle.kv_store(v, KV_TYPE[kv]))
+    q = rng.standard_normal((S, H, D)).astype(np.float32)
+    k_new = rng.standard_normal((S, HK, D)).astype(np.float32)
+    v_new = rng.standard_normal((S, HK, D)).astype(np.float32)
+    ff = (1.0 + rng.random(32)).astype(np.float32)
+    pos = np.array(lens, np.int32) - 1
+    table = oracle.rope_table(pos, freq_base=1000000.0, attn_factor=1.05, freq_factors=ff)
+    out = cache.decode(0, dev(q), dev(np.array(lens, np.int32)), max(lens), k_new=dev(k_new), v_new=dev(v_new), rope_table=dev(table))
+    engine.sync_status()
+    out = out.cpu().numpy()
+    q_rot, k_rot = oracle.rope(q, table), oracle.rope(k_new, table)
+    for s, n in enumerate(lens):
+        ke, ve = cache.export(0, s, n)
+        assert np.array_equal(ke[:, n - 1].view(np.uint8), oracle.kv_store(k_rot[s][:, None], KV_TYPE[kv])[:, 0].view(np.uint8))
+        assert np.array_equal(ve[:, n - 1].view(np.uint8), oracle.kv_store(v_new[s][:, None], KV_TYPE[kv])[:, 0].view(np.uint8))
+        ref = oracle.attn(q_rot[s][None, :, None, :], ke[None], ve[None], kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)[0, 0]
+        assert rel_err(out[s], ref) < TOL[kv], f"stream {s} (kv_len {n})"
+    # the device-built table gives the same result within the tolerance (angles may differ in the last place)
+    cache2 = pkg.KVCache(engine, 1, S, HK, cap, KV_TYPE[kv])
+    cache2.copy_from(cache)
+    t_dev = engine.rope_table(dev(np.array(lens, np.int32)), pos_offset=-1, freq_base=1000000.0, attn_factor=1.05, freq_factors=dev(ff))
+    out2 = cache2.decode(0, dev(q), dev(np.array(lens, np.int32)), max(lens), k_new=dev(k_new), v_new=dev(v_new), rope_table=t_dev)
+    engine.sync_status()
+    assert rel_err(out2.cpu().numpy(), out) < 1e-4
+
+
 def test_decode_refuses_bad_arguments(engine, pkg):
     import torch
     cache = pkg.KVCache(engine, 1, 2, HK, 128, pkg.F16)
@@ -540,6 +614,37 @@ def test_group_step_appends_then_attends(kv, engine, pkg, oracle, vo):
     g.step(t2, advance=False)
     engine.sync_status()
     assert np.array_equal(g.kv_len(), lens + 1)
+
+
+def test_group_step_with_rotary_embedding(engine, pkg, oracle, vo):
+    rng = np.random.default_rng(15)
+    S = 4
+    g = pkg.Group(engine, n_streams=S, max_len=1024, kv_type=pkg.F16, base_layers=2, res_layers=1, cfm_steps=0, locdit_layers=0)
+    lens = np.array([5, 64, 700, 1000], np.int32)
+    g.set_kv_len(lens)
+    g.fill_synthetic(seed=3)
+    ff = (1.0 + rng.random(32)).astype(np.float32)
+    g.set_rope(freq_base=10000.0, attn_factor=1.0, freq_factors=ff)
+    shapes = g.buffer_shapes()
+    host = {n: rng.standard_normal(s).astype(np.float32) for n, s in shapes.items() if n.startswith("lm_") and not n.endswith("out")}
+    import torch
+    t = {n: dev(x) for n, x in host.items()}
+    t["lm_out"] = torch.zeros(shapes["lm_out"], device="cuda")
+    before = engine.launches
+    g.step(t, advance=True)
+    engine.sync_status()
+    assert engine.launches - before == 3 + 1 + 1  # decode per layer, length update, one rotary table for the step
+    table = oracle.rope_table(lens, freq_base=10000.0, attn_factor=1.0, freq_factors=ff)  # positions = old lengths
+    lm_out = t["lm_out"].cpu().numpy()
+    for l in range(3):
+        cache = g.cache(0 if l < 2 else 1)
+        layer = l if l < 2 else 0
+        q_rot, k_rot = oracle.rope(host["lm_q"][l], table), oracle.rope(host["lm_k_new"][l], table)
+        for s in range(S):
+            ke, ve = cache.export(layer, s, int(lens[s]) + 1)
+            assert np.abs(ke[:, -1].astype(np.float32) - k_rot[s]).max() < 4e-3  # f16 storage of the rotated row
+            ref = oracle.attn(q_rot[s][None, :, None, :], ke[None], ve[None], kv_type=vo.F16, path=vo.PATH_ROW_F32)[0, 0]
+            assert rel_err(lm_out[l, s], ref) < TOL["f16"]
 
 
 def test_group_step_host_equals_device_step(engine, pkg):

@@ -3,7 +3,7 @@ reference's own ggml CPU backend, and against that backend itself where it is pr
 import numpy as np
 import pytest
 
-from cases import CASES, KV_TYPE, digest, make_inputs, rel_err
+from cases import CASES, KV_TYPE, ROPE_CASES, digest, make_inputs, rel_err, rope_inputs
 
 # tolerance of the restatement against the reference's accurate path (both f32; they differ by
 # summation order and libm vs vectorised expf only)
@@ -39,6 +39,22 @@ def test_oracle_matches_golden_as_shipped(name, oracle, vo, golden):
     path = vo.PATH_TILED if (case["n_q"] >= 64 and case["kv"] != "q8_0") else vo.PATH_ROW
     mine = oracle.attn(inp["q"], inp["k"], inp["v"], inp["mask"], kv_type=kt, path=path)
     assert rel_err(mine, shipped) < SHIPPED_TOL[case["kv"]]
+
+
+@pytest.mark.parametrize("name", sorted(ROPE_CASES))
+def test_rope_restatement_matches_the_reference_fixture(name, oracle, golden):
+    """cos/sin table + NEOX rotation against ggml_rope_ext as apply_rope calls it.  Both are f32; the reference build
+    may fuse x0*cos - x1*sin into an FMA, the restatement does not: one unit in the last place."""
+    args = ROPE_CASES[name]
+    x, pos, ff = rope_inputs(args)
+    table = oracle.rope_table(pos, freq_base=args["freq_base"], attn_factor=args["attn_factor"], freq_factors=ff)
+    got = oracle.rope(x, table)
+    want = golden[name + "/out"]
+    assert np.abs(got - want).max() <= 1e-6 * max(1.0, float(np.abs(want).max()))
+    # a rotation scaled by attn_factor: row norms are preserved up to that factor
+    assert np.allclose(np.linalg.norm(got, axis=-1), np.linalg.norm(x, axis=-1) * args["attn_factor"], rtol=1e-5)
+    # position 0 is the identity (times the factor)
+    assert np.allclose(got[0], x[0] * np.float32(args["attn_factor"]), rtol=1e-6, atol=1e-7)
 
 
 def test_storage_formats_bit_exact(oracle, golden):
@@ -138,6 +154,16 @@ def test_reference_tiled_path_agrees_with_f32_typed_path(ref, oracle):
     tiled = ref.attn(q64, inp["k"], inp["v"], None, kv_type=1, n_threads=2)[:, :1]
     typed = ref.attn(inp["q"], inp["kf"], inp["vf"], None, kv_type=0, n_threads=1)
     assert rel_err(tiled, typed) < 2e-5
+
+
+def test_reference_rope_matches_oracle(ref, oracle):
+    rng = np.random.default_rng(6)
+    pos = np.array([0, 3, 100, 2047, 4096, 30000], np.int32)
+    x = rng.standard_normal((len(pos), 2, 64)).astype(np.float32)
+    ff = (1.0 + rng.random(32)).astype(np.float32)
+    want = ref.rope(x, pos, freq_base=500000.0, attn_factor=1.1, freq_factors=ff, n_ctx_orig=4096, n_threads=2)
+    got = oracle.rope(x, oracle.rope_table(pos, freq_base=500000.0, attn_factor=1.1, freq_factors=ff))
+    assert np.abs(got - want).max() <= 1e-6 * float(np.abs(want).max())
 
 
 def test_reference_quantiser_matches_oracle(ref, oracle):

@@ -73,7 +73,12 @@ class DecodeArgs(C.Structure):
     _fields_ = [("cache", C.c_void_p), ("layer", C.c_int32), ("n_streams", C.c_int32), ("n_heads", C.c_int32),
                 ("kv_len", C.c_void_p), ("kv_bound", C.c_int32), ("q", C.c_void_p), ("q_nb_head", C.c_size_t),
                 ("q_nb_stream", C.c_size_t), ("dst", C.c_void_p), ("scale", C.c_float), ("k_new", C.c_void_p),
-                ("v_new", C.c_void_p), ("new_nb_head", C.c_size_t), ("new_nb_stream", C.c_size_t), ("flags", C.c_uint32)]
+                ("v_new", C.c_void_p), ("new_nb_head", C.c_size_t), ("new_nb_stream", C.c_size_t), ("flags", C.c_uint32),
+                ("rope_table", C.c_void_p)]
+
+
+class RopeConfig(C.Structure):
+    _fields_ = [("freq_base", C.c_float), ("attn_factor", C.c_float), ("freq_factors", C.c_void_p)]
 
 
 class LocditArgs(C.Structure):
@@ -125,6 +130,9 @@ def lib() -> C.CDLL:
         "vox_attn_status_string": (C.c_char_p, [i32]),
         "vox_engine_launch_count": (C.c_uint64, [vp]),
         "vox_engine_sync_status": (i32, [vp, vp]),
+        "vox_engine_selftest_wait": (i32, [vp, C.c_longlong, vp]),
+        "vox_rope_table": (i32, [vp, C.POINTER(RopeConfig), vp, i32, i32, vp, vp]),
+        "vox_group_set_rope": (i32, [vp, C.POINTER(RopeConfig), vp]),
         "vox_attn_supported": (i32, [C.POINTER(AttnArgs)]),
         "vox_attn_workspace_bytes": (sz, [C.POINTER(AttnArgs)]),
         "vox_attn_forward": (i32, [vp, C.POINTER(AttnArgs), vp, sz, vp]),
@@ -213,6 +221,19 @@ class Engine:
 
     def sync_status(self, stream=None):
         _check(lib().vox_engine_sync_status(self.h, _stream_ptr(stream)))
+
+    def rope_table(self, positions, freq_base=10000.0, attn_factor=1.0, freq_factors=None, pos_offset=0, stream=None):
+        """``vox_rope_table``: positions int32 device [n] -> (cos, sin) table [n, 32, 2] f32 on the device."""
+        import torch
+        n = positions.numel()
+        table = torch.empty((n, 32, 2), dtype=torch.float32, device=positions.device)
+        cfg = RopeConfig(freq_base, attn_factor, freq_factors.data_ptr() if freq_factors is not None else None)
+        _check(lib().vox_rope_table(self.h, C.byref(cfg), positions.data_ptr(), pos_offset, n, table.data_ptr(), _stream_ptr(stream)))
+        return table
+
+    def selftest_wait(self, limit_cycles=2_000_000, stream=None):
+        """Launches the wait that nothing satisfies; the next ``sync_status`` raises TIMEOUT."""
+        _check(lib().vox_engine_selftest_wait(self.h, limit_cycles, _stream_ptr(stream)))
 
     def workspace(self, nbytes: int):
         import torch
@@ -336,7 +357,8 @@ class KVCache:
     def copy_from(self, other: "KVCache", stream=None):
         _check(lib().vox_kv_copy_from(self.h, other.h, _stream_ptr(stream)))
 
-    def decode(self, layer, q, kv_len, kv_bound, scale=0.125, stream=None, dst=None, k_new=None, v_new=None, cache_stable=False):
+    def decode(self, layer, q, kv_len, kv_bound, scale=0.125, stream=None, dst=None, k_new=None, v_new=None, cache_stable=False,
+               rope_table=None):
         """q [n_streams, H, 64] f32, kv_len int32 device [n_streams] -> [n_streams, H, 64].
 
         ``k_new`` / ``v_new`` [n_streams, HK, 64] f32: the token's own rows, stored at position
@@ -350,6 +372,7 @@ class KVCache:
         a = DecodeArgs(self.h, layer, S, H, kv_len.data_ptr(), kv_bound, q.data_ptr(), q.stride(1) * 4, q.stride(0) * 4,
                        dst.data_ptr(), scale)
         a.flags = 1 if cache_stable else 0
+        a.rope_table = rope_table.data_ptr() if rope_table is not None else None
         if k_new is not None or v_new is not None:
             a.k_new = k_new.data_ptr() if k_new is not None else None
             a.v_new = v_new.data_ptr() if v_new is not None else None
@@ -396,6 +419,14 @@ class Group:
         layers = c.base_layers if stack == 0 else c.res_layers
         return KVCache(self.engine, layers, c.n_streams, c.n_kv_heads, c.max_len, c.kv_type,
                        handle=lib().vox_group_cache(self.h, stack))
+
+    def set_rope(self, freq_base=10000.0, attn_factor=1.0, freq_factors=None):
+        """Rotary embedding inside the step (``vox_group_set_rope``); ``freq_factors``: 32 floats on the host."""
+        import numpy as np
+        cfg = RopeConfig(freq_base, attn_factor, None)
+        ff = None if freq_factors is None else np.ascontiguousarray(freq_factors, np.float32)
+        assert ff is None or ff.shape == (32,)
+        _check(lib().vox_group_set_rope(self.h, C.byref(cfg), None if ff is None else ff.ctypes.data_as(C.c_void_p)))
 
     def set_kv_len(self, kv_len):
         import numpy as np

@@ -144,12 +144,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Returns false when the phase did not complete in time.  try_wait already parks the thread in
 // hardware for a short while, so the loop polls back to back (waking late costs more than polling);
 // every 1024 failed polls the elapsed clock is checked against kWaitCycles (about two seconds).
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 0 && clock64() - t0 > kWaitCycles) return false;
+        if ((i & 1023u) == 0 && clock64() - t0 > limit) return false;
     }
 }
 

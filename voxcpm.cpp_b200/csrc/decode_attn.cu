@@ -60,6 +60,9 @@ struct DecodeParams {
     // it on the stream (only Q and the arriving row were), so the first tiles are requested before the
     // programmatic-dependency wait, while that kernel is still draining.
     int             early;
+    // Non-null: [stream][32] (cos, sin) pairs; Q and the arriving K row are rotated as they are read
+    // (element i with element i + 32: the reference's ggml_rope_ext, GGML_ROPE_TYPE_NEOX).
+    const float2 *  rope;
 };
 
 __device__ __forceinline__ int stream_len(const DecodeParams & p, int stream) {
@@ -228,6 +231,20 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             const size_t src = (size_t) stream * p.new_nb_stream + (size_t) kvh * p.new_nb_head + lane * 8;
             kk = *reinterpret_cast<const float2 *>(p.k_new + src);
             vv = *reinterpret_cast<const float2 *>(p.v_new + src);
+            if (p.rope != nullptr) {
+                // lane l holds elements 2l, 2l+1; their partners (32 further, or 32 back) sit in lane l ^ 16.
+                // Separate multiplies and adds, in the operand order of the reference's rotate_pairs.
+                const float2 * tb = p.rope + (size_t) stream * (kHeadDim / 2) + 2 * (lane & 15);
+                const float2   r0 = tb[0], r1 = tb[1];
+                const float    ox = __shfl_xor_sync(0xffffffffu, kk.x, 16), oy = __shfl_xor_sync(0xffffffffu, kk.y, 16);
+                if (lane < 16) {  // x0 = mine, x1 = partner: x0*cos - x1*sin
+                    kk.x = __fsub_rn(__fmul_rn(kk.x, r0.x), __fmul_rn(ox, r0.y));
+                    kk.y = __fsub_rn(__fmul_rn(kk.y, r1.x), __fmul_rn(oy, r1.y));
+                } else {          // x0 = partner, x1 = mine: x0*sin + x1*cos
+                    kk.x = __fadd_rn(__fmul_rn(ox, r0.y), __fmul_rn(kk.x, r0.x));
+                    kk.y = __fadd_rn(__fmul_rn(oy, r1.y), __fmul_rn(kk.y, r1.x));
+                }
+            }
         }
         if (lane == 0) {
             for (int i = next; i < n_before; ++i)
@@ -266,17 +283,38 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int     head = kvh * p.gqa + min(g, p.gqa - 1);
         const float * qrow = reinterpret_cast<const float *>(p.q + (size_t) stream * p.q_nb_stream + (size_t) head * p.q_nb_head);
         const float   live = g < p.gqa ? p.scale_log2 : 0.0f;
+        float xs[4][4];  // k-step c: elements d0, d0+1, d1, d1+1
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int d0 = Q8 ? 32 * (c >> 1) + 8 * t + 4 * (c & 1) : 16 * c + 2 * t;
             const int d1 = Q8 ? d0 + 2 : d0 + 8;
             const float2 x = *reinterpret_cast<const float2 *>(qrow + d0);
             const float2 y = *reinterpret_cast<const float2 *>(qrow + d1);
+            xs[c][0] = x.x; xs[c][1] = x.y; xs[c][2] = y.x; xs[c][3] = y.y;
+        }
+        if (p.rope != nullptr) {
+            // in both orders k-steps c and c+2 hold each other's partners (d and d + 32)
+            const float2 * tb = p.rope + (size_t) stream * (kHeadDim / 2);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int d0 = Q8 ? 8 * t + 4 * c : 16 * c + 2 * t;
+                const int d1 = Q8 ? d0 + 2 : d0 + 8;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 r  = tb[(e < 2 ? d0 : d1) + (e & 1)];
+                    const float  x0 = xs[c][e], x1 = xs[c + 2][e];
+                    xs[c][e]     = __fsub_rn(__fmul_rn(x0, r.x), __fmul_rn(x1, r.y));
+                    xs[c + 2][e] = __fadd_rn(__fmul_rn(x0, r.y), __fmul_rn(x1, r.x));
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
             float h0, l0, h1, l1, h2, l2, h3, l3;
-            split_hi_lo(x.x * live, h0, l0);
-            split_hi_lo(x.y * live, h1, l1);
-            split_hi_lo(y.x * live, h2, l2);
-            split_hi_lo(y.y * live, h3, l3);
+            split_hi_lo(xs[c][0] * live, h0, l0);
+            split_hi_lo(xs[c][1] * live, h1, l1);
+            split_hi_lo(xs[c][2] * live, h2, l2);
+            split_hi_lo(xs[c][3] * live, h3, l3);
             qa[c][0] = pack_half2(h0, h1);
             qa[c][1] = pack_half2(l0, l1);
             qa[c][2] = pack_half2(h2, h3);
@@ -587,7 +625,8 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
                   const int32_t * kv_len, int kv_len_const, int kv_bound, const float * q, size_t q_nb_head,
                   size_t q_nb_stream, float * dst, float scale, void * workspace, size_t workspace_bytes,
                   cudaStream_t stream, const vox_kv_cache * append_to = nullptr, const float * k_new = nullptr,
-                  const float * v_new = nullptr, size_t new_nb_head = 0, size_t new_nb_stream = 0, bool early = false) {
+                  const float * v_new = nullptr, size_t new_nb_head = 0, size_t new_nb_stream = 0, bool early = false,
+                  const float * rope_table = nullptr) {
     const uint32_t bit = q8 ? (1u << 9) : (1u << 8);
     if (!(e->attr_mask & bit)) {
         if (q8) VOX_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring<true>::kSmemBytes));
@@ -602,6 +641,7 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = e->status_dev;
     p.early = early ? 1 : 0;
+    p.rope  = reinterpret_cast<const float2 *>(rope_table);
     p.k_new = p.v_new = nullptr;
     p.new_nb_head = p.new_nb_stream = 0;
     p.k_rows = p.v_rows = p.k_scales = p.v_scales = nullptr;
@@ -680,10 +720,11 @@ int vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace,
                     VOX_ATTN_INVALID_ARGUMENT, "k_new / v_new rows must be 8-byte aligned");
         VOX_REQUIRE(a->kv_bound >= 1, VOX_ATTN_INVALID_ARGUMENT, "kv_bound counts the arriving row: it cannot be 0 with k_new");
     }
+    VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->rope_table) & 7) == 0, VOX_ATTN_INVALID_ARGUMENT, "rope_table must be 8-byte aligned");
     return launch_decode(e, c->cfg.type == VOX_TYPE_Q8_0, c->map_k, c->map_v, &c->map_ks, &c->map_vs, a->layer, c->cfg.max_len, a->n_streams, a->n_heads, c->cfg.n_kv_heads,
                          a->kv_len, 0, a->kv_bound, a->q, a->q_nb_head, a->q_nb_stream, a->dst, a->scale, workspace,
                          workspace_bytes, static_cast<cudaStream_t>(stream), appends ? c : nullptr, a->k_new, a->v_new,
-                         a->new_nb_head, a->new_nb_stream, (a->flags & VOX_DECODE_CACHE_STABLE) != 0);
+                         a->new_nb_head, a->new_nb_stream, (a->flags & VOX_DECODE_CACHE_STABLE) != 0, a->rope_table);
 }
 
 }  // extern "C"

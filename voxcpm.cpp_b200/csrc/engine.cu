@@ -50,6 +50,22 @@ int make_tensor_map(const vox_engine * e, CUtensorMap * out, void * base, CUtens
 
 using namespace vox;
 
+namespace {
+
+// The path every kernel takes when a copy or a peer never shows up, exercised on purpose: one thread waits,
+// with the given limit, on a barrier that nothing arrives at, gives up, raises the status word and returns.
+__global__ void wait_that_runs_out_kernel(int * status, long long limit_cycles) {
+    __shared__ uint64_t bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+        if (!mbar_wait_bounded(b, 0, limit_cycles)) atomicOr(status, kStatusTimeout);
+    }
+}
+
+}  // namespace
+
 extern "C" {
 
 const char * vox_attn_last_error_string(void) { return g_error; }
@@ -132,6 +148,15 @@ void vox_engine_destroy(vox_engine * e) {
 }
 
 uint64_t vox_engine_launch_count(const vox_engine * e) { return e ? e->launches : 0; }
+
+int vox_engine_selftest_wait(vox_engine * e, long long limit_cycles, void * stream) {
+    VOX_REQUIRE(e != nullptr, VOX_ATTN_INVALID_ARGUMENT, "engine is null");
+    VOX_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000LL, VOX_ATTN_INVALID_ARGUMENT,
+                "limit_cycles must be in (0, 2e9] (about a second at most)");
+    VOX_CUDA_TRY(cudaSetDevice(e->device));
+    wait_that_runs_out_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(e->status_dev, limit_cycles);
+    return check_launch(e, "wait_that_runs_out_kernel");
+}
 
 int vox_engine_sync_status(vox_engine * e, void * stream) {
     VOX_REQUIRE(e != nullptr, VOX_ATTN_INVALID_ARGUMENT, "engine is null");

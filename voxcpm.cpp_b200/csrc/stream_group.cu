@@ -31,6 +31,11 @@ struct vox_group {
     int              kv_bound  = 0;
     void *           workspace = nullptr;
     size_t           workspace_bytes = 0;
+    // rotary embedding inside the step (vox_group_set_rope): one table per step, applied by every layer's decode
+    bool             rope_on = false;
+    vox_rope_config  rope{};
+    float *          rope_factors = nullptr;          // device copy of the 32 per-frequency factors
+    float *          rope_table   = nullptr;          // [n_streams][32][2]
     // vox_group_step_host: device mirrors of the step buffers, two copy streams, events
     uint8_t *        dev_buf   = nullptr;
     size_t           dev_off[8] = {0};
@@ -117,6 +122,8 @@ void vox_group_destroy(vox_group * g) {
     for (int s = 0; s < 2; ++s) vox_kv_destroy(g->cache[s]);
     if (g->workspace) cudaFree(g->workspace);
     if (g->kv_len_dev) cudaFree(g->kv_len_dev);
+    if (g->rope_factors) cudaFree(g->rope_factors);
+    if (g->rope_table) cudaFree(g->rope_table);
     if (g->dev_buf) cudaFree(g->dev_buf);
     if (g->st_compute) cudaStreamDestroy(g->st_compute);
     if (g->st_copy) cudaStreamDestroy(g->st_copy);
@@ -163,6 +170,26 @@ int vox_group_fill_synthetic(vox_group * g, uint64_t seed, void * stream) {
     return VOX_ATTN_OK;
 }
 
+int vox_group_set_rope(vox_group * g, const vox_rope_config * cfg, const float * freq_factors_host) {
+    VOX_REQUIRE(g != nullptr, VOX_ATTN_INVALID_ARGUMENT, "null group");
+    if (cfg == nullptr) {  // back to "the caller rotates"
+        g->rope_on = false;
+        return VOX_ATTN_OK;
+    }
+    VOX_REQUIRE(cfg->freq_base > 0.0f, VOX_ATTN_INVALID_ARGUMENT, "freq_base must be positive");
+    VOX_CUDA_TRY(cudaSetDevice(g->e->device));
+    if (!g->rope_table) VOX_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&g->rope_table), sizeof(float) * 64 * g->cfg.n_streams));
+    g->rope = *cfg;
+    g->rope.freq_factors = nullptr;
+    if (freq_factors_host != nullptr) {
+        if (!g->rope_factors) VOX_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&g->rope_factors), sizeof(float) * 32));
+        VOX_CUDA_TRY(cudaMemcpy(g->rope_factors, freq_factors_host, sizeof(float) * 32, cudaMemcpyHostToDevice));
+        g->rope.freq_factors = g->rope_factors;
+    }
+    g->rope_on = true;
+    return VOX_ATTN_OK;
+}
+
 size_t vox_group_step_bytes(const vox_group * g, int which) { return g ? step_bytes(g->cfg, which) : 0; }
 
 int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void * stream) {
@@ -184,6 +211,10 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         int rc = check_launch(g->e, "add_scalar_kernel");
         if (rc != VOX_ATTN_OK) return rc;
     }
+    if (L > 0 && g->rope_on) {  // the angles of this step's positions (kv_len - 1), once for all layers
+        int rc = vox_rope_table(g->e, &g->rope, g->kv_len_dev, -1, c.n_streams, g->rope_table, stream);
+        if (rc != VOX_ATTN_OK) return rc;
+    }
     for (int l = 0; l < L; ++l) {
         const int      stack = l < c.base_layers ? 0 : 1;
         const int      layer = stack == 0 ? l : l - c.base_layers;
@@ -194,6 +225,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         // from the second layer on, the kernel before this one is the previous layer's decode: it wrote
         // neither the lengths nor this layer's rows (layer 0 follows the length update)
         da.flags = l > 0 ? VOX_DECODE_CACHE_STABLE : 0u;
+        da.rope_table = g->rope_on ? g->rope_table : nullptr;
         if (advance) {  // the token's K/V rows are stored by the decode launch itself (position kv_len-1)
             da.k_new = b->lm_k_new + (size_t) l * S * c.n_kv_heads * D;
             da.v_new = b->lm_v_new + (size_t) l * S * c.n_kv_heads * D;
