@@ -277,7 +277,20 @@ def aux_workload(args, pkg, torch):
             nbytes = (nb + nr) * lm_bytes_per_layer(lens, t)
             warm, cold = timed(step, 20, cold=False), timed(step, 10, cold=True)
             eng.sync_status()
+            # the same launch sequence captured once and replayed (vox_group_set_bound makes it position-independent):
+            # for a single stream the host's launch rate, not the GPU, bounds a step issued call by call
+            graph_us = None
+            if B == 1:
+                side = torch.cuda.Stream()
+                graph = torch.cuda.CUDAGraph()
+                g.set_bound(L)
+                with torch.cuda.stream(side):
+                    with torch.cuda.graph(graph, stream=side):
+                        g.step(bufs, advance=False, stream=side)
+                graph_us = timed(graph.replay, 20, cold=False) * 1e3 / (nb + nr)
+                eng.sync_status()
             out["results"].append({"config": f"decode kv={L} B={B} {t} x {nb + nr} layers", "bytes": nbytes,
+                                   "graph_replay_us_per_layer": graph_us,
                                    "warm_us_per_layer": warm * 1e3 / (nb + nr), "cold_us_per_layer": cold * 1e3 / (nb + nr),
                                    "warm_gb_s": nbytes / (warm * 1e-3) / 1e9, "cold_gb_s": nbytes / (cold * 1e-3) / 1e9,
                                    "cold_frac_of_measured_hbm": nbytes / (cold * 1e-3) / 1e9 / hbm,

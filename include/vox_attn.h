@@ -326,6 +326,17 @@ size_t vox_group_step_bytes(const vox_group * g, int which /* 0 lm in, 1 lm out,
  * freq_factors_host: 32 floats on the host (copied), or NULL.  cfg == NULL switches it off again. */
 int vox_group_set_rope(vox_group * g, const vox_rope_config * cfg, const float * freq_factors_host);
 
+/* Position-independent step (the reference rebuilds and re-reserves its step graph at every position,
+ * src/voxcpm.cpp:485-513).  Lengths live on the device and are advanced there, so the launch sequence of
+ * vox_group_step depends on the position only through the sizes of its grids.  vox_group_set_bound fixes
+ * those to "lengths up to kv_bound" (0: back to the exact longest stream): a step can then be captured
+ * into a CUDA graph (cudaStreamBeginCapture on the stream handed to vox_group_step; the programmatic
+ * dependencies between the launches are captured with them) and replayed for every position until a stream
+ * reaches the bound.  A captured step records launches only; after each replay of an advancing step call
+ * vox_group_advance(g, 1) so that the host copy of the lengths follows the device. */
+int vox_group_set_bound(vox_group * g, int kv_bound);
+int vox_group_advance(vox_group * g, int steps);
+
 /* One decode step on device buffers.  advance != 0 stores the new rows and grows every stream
  * by one position; advance == 0 attends to the current rows only (lengths fixed).
  * Launches: one per LM layer (it stores the arriving row and folds the split-KV partials itself), one

@@ -647,6 +647,56 @@ def test_group_step_with_rotary_embedding(engine, pkg, oracle, vo):
             assert rel_err(lm_out[l, s], ref) < TOL["f16"]
 
 
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+def test_captured_step_replays_for_every_position(kv, engine, pkg):
+    """One CUDA graph of an advancing step, replayed: same outputs, same cache rows and same lengths as issuing the step
+    anew at every position."""
+    import torch
+    S, steps = 3, 5
+    lens = np.array([60, 250, 1000], np.int32)
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    groups = []
+    for _ in range(2):
+        g = pkg.Group(engine, n_streams=S, max_len=1024 + 64, kv_type=KV_TYPE[kv], base_layers=2, res_layers=1, cfm_steps=2, locdit_layers=2)
+        g.set_kv_len(lens)
+        g.fill_synthetic(seed=9)
+        g.set_rope(freq_base=10000.0)
+        g.set_bound(1024 + 64)  # both runs size their grids for the capacity, so both split the KV range alike
+        groups.append(g)
+    shapes = groups[0].buffer_shapes()
+    inputs = [{n: torch.randn(s, device="cuda", generator=gen) for n, s in shapes.items() if not n.endswith("out")} for _ in range(steps)]
+    # reference run: a fresh launch sequence per position
+    want = []
+    for i in range(steps):
+        t = dict(inputs[i], lm_out=torch.zeros(shapes["lm_out"], device="cuda"), dit_out=torch.zeros(shapes["dit_out"], device="cuda"))
+        groups[0].step(t, advance=True)
+        want.append((t["lm_out"].clone(), t["dit_out"].clone()))
+    engine.sync_status()
+    # captured run: static buffers, one graph, bound = capacity
+    g = groups[1]
+    static = {n: torch.zeros(s, device="cuda") for n, s in shapes.items()}
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            g.step(static, advance=True, stream=side)
+    assert np.array_equal(g.kv_len(), lens)  # capturing moved nothing
+    for i in range(steps):
+        for n, x in inputs[i].items():
+            static[n].copy_(x)
+        graph.replay()
+        g.advance(1)
+        torch.cuda.synchronize()
+        assert torch.equal(static["lm_out"], want[i][0]) and torch.equal(static["dit_out"], want[i][1]), f"position {i}"
+    engine.sync_status()
+    assert np.array_equal(g.kv_len(), lens + steps) and np.array_equal(groups[0].kv_len(), lens + steps)
+    for stack in (0, 1):
+        a, b = groups[0].cache(stack).export(0, 2, 1010), g.cache(stack).export(0, 2, 1010)
+        assert np.array_equal(a[0].view(np.uint8), b[0].view(np.uint8)) and np.array_equal(a[1].view(np.uint8), b[1].view(np.uint8))
+    with pytest.raises(pkg.VoxError):
+        g.set_bound(10)  # below the longest stream
+
+
 def test_group_step_host_equals_device_step(engine, pkg):
     import torch
     rng = np.random.default_rng(6)

@@ -133,6 +133,8 @@ def lib() -> C.CDLL:
         "vox_engine_selftest_wait": (i32, [vp, C.c_longlong, vp]),
         "vox_rope_table": (i32, [vp, C.POINTER(RopeConfig), vp, i32, i32, vp, vp]),
         "vox_group_set_rope": (i32, [vp, C.POINTER(RopeConfig), vp]),
+        "vox_group_set_bound": (i32, [vp, i32]),
+        "vox_group_advance": (i32, [vp, i32]),
         "vox_attn_supported": (i32, [C.POINTER(AttnArgs)]),
         "vox_attn_workspace_bytes": (sz, [C.POINTER(AttnArgs)]),
         "vox_attn_forward": (i32, [vp, C.POINTER(AttnArgs), vp, sz, vp]),
@@ -419,6 +421,14 @@ class Group:
         layers = c.base_layers if stack == 0 else c.res_layers
         return KVCache(self.engine, layers, c.n_streams, c.n_kv_heads, c.max_len, c.kv_type,
                        handle=lib().vox_group_cache(self.h, stack))
+
+    def set_bound(self, kv_bound: int):
+        """Size every grid for lengths up to ``kv_bound`` (0: exact), so that a step can be captured and replayed."""
+        _check(lib().vox_group_set_bound(self.h, int(kv_bound)))
+
+    def advance(self, steps: int = 1):
+        """Host bookkeeping after ``steps`` replays of a captured advancing step."""
+        _check(lib().vox_group_advance(self.h, int(steps)))
 
     def set_rope(self, freq_base=10000.0, attn_factor=1.0, freq_factors=None):
         """Rotary embedding inside the step (``vox_group_set_rope``); ``freq_factors``: 32 floats on the host."""

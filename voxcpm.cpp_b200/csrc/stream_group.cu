@@ -28,7 +28,8 @@ struct vox_group {
     vox_kv_cache *   cache[2]  = {nullptr, nullptr};  // backbone, residual LM
     int32_t *        kv_len_dev = nullptr;            // [n_streams] rows visible to attention
     std::vector<int32_t> kv_len_host;
-    int              kv_bound  = 0;
+    int              kv_bound  = 0;                   // longest stream (host copy)
+    int              grid_bound = 0;                  // vox_group_set_bound: grids are sized for this length instead (0: exact)
     void *           workspace = nullptr;
     size_t           workspace_bytes = 0;
     // rotary embedding inside the step (vox_group_set_rope): one table per step, applied by every layer's decode
@@ -170,6 +171,23 @@ int vox_group_fill_synthetic(vox_group * g, uint64_t seed, void * stream) {
     return VOX_ATTN_OK;
 }
 
+int vox_group_set_bound(vox_group * g, int kv_bound) {
+    VOX_REQUIRE(g != nullptr, VOX_ATTN_INVALID_ARGUMENT, "null group");
+    VOX_REQUIRE(kv_bound == 0 || (kv_bound >= g->kv_bound && kv_bound <= g->cfg.max_len), VOX_ATTN_INVALID_ARGUMENT,
+                "bound %d must lie between the longest stream (%d) and the capacity (%d), or be 0", kv_bound, g->kv_bound, g->cfg.max_len);
+    g->grid_bound = kv_bound;
+    return VOX_ATTN_OK;
+}
+
+int vox_group_advance(vox_group * g, int steps) {
+    VOX_REQUIRE(g != nullptr && steps >= 0, VOX_ATTN_INVALID_ARGUMENT, "bad argument");
+    const int limit = g->grid_bound > 0 ? g->grid_bound : g->cfg.max_len;
+    VOX_REQUIRE(g->kv_bound + steps <= limit, VOX_ATTN_INVALID_ARGUMENT, "%d more rows would exceed %d", steps, limit);
+    for (auto & x : g->kv_len_host) x += steps;
+    g->kv_bound += steps;
+    return VOX_ATTN_OK;
+}
+
 int vox_group_set_rope(vox_group * g, const vox_rope_config * cfg, const float * freq_factors_host) {
     VOX_REQUIRE(g != nullptr, VOX_ATTN_INVALID_ARGUMENT, "null group");
     if (cfg == nullptr) {  // back to "the caller rotates"
@@ -205,7 +223,15 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
     if (advance) {
         VOX_REQUIRE(g->kv_bound + 1 <= c.max_len, VOX_ATTN_INVALID_ARGUMENT, "a stream would outgrow the cache capacity %d", c.max_len);
     }
-    const int bound = g->kv_bound + (advance ? 1 : 0);
+    const int longest = g->kv_bound + (advance ? 1 : 0);
+    VOX_REQUIRE(g->grid_bound == 0 || longest <= g->grid_bound, VOX_ATTN_INVALID_ARGUMENT,
+                "a stream of %d rows exceeds the bound %d set with vox_group_set_bound", longest, g->grid_bound);
+    const int bound = g->grid_bound > 0 ? g->grid_bound : longest;
+    // A step that is being captured into a CUDA graph only records launches: the lengths on the device move when
+    // the graph is replayed, and the host copy is moved by vox_group_advance after each replay.
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    VOX_CUDA_TRY(cudaStreamIsCapturing(st, &capture));
+    const bool capturing = capture != cudaStreamCaptureStatusNone;
     if (advance) {  // the appended row becomes visible to this step's attention
         launch_pdl(add_scalar_kernel, dim3((c.n_streams + 255) / 256), dim3(256), 0, st, g->kv_len_dev, c.n_streams, 1, c.max_len);
         int rc = check_launch(g->e, "add_scalar_kernel");
@@ -240,7 +266,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         int rc = vox_attn_decode(g->e, &da, g->workspace, g->workspace_bytes, stream);
         if (rc != VOX_ATTN_OK) return rc;
     }
-    if (advance) {
+    if (advance && !capturing) {
         for (auto & x : g->kv_len_host) x += 1;
         g->kv_bound += 1;
     }
