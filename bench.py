@@ -62,11 +62,12 @@ def stream_lengths(n, rank=0):
 
 
 def streams_of_rank(scaling, n_streams, rank, world, partition):
-    """KV lengths of the streams one rank serves.  weak: every rank draws its own `n_streams`; strong: one
+    """KV lengths of the streams one rank serves.  weak: every rank serves `n_streams` streams with the same
+    multiset of ragged lengths (the per-GPU work is what is held fixed), in an order of its own; strong: one
     draw of `n_streams` is split over the ranks by `partition` (longest-processing-time on KV length).
     Streams never move between ranks and nothing is exchanged on the data path."""
     if scaling == "weak":
-        return stream_lengths(n_streams, rank)
+        return np.random.default_rng(777 + rank).permutation(stream_lengths(n_streams, 0))
     all_lens = stream_lengths(n_streams, 0)
     owner = partition(all_lens, world)
     return all_lens[owner == rank]
@@ -462,6 +463,8 @@ def main():
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD.format(s=args.streams), "streams_total": int(total_streams), "kv_type": args.kv_type,
                            "l2": "inputs larger than L2 (KV read per step >> 126 MB)", "append": "included",
+                           "placement": "weak: every GPU serves the same multiset of ragged lengths" if args.scaling == "weak"
+                           else "strong: one population split over the GPUs by KV rows (longest-processing-time)",
                            "rope": "rotary embedding of Q and the new K rows inside the decode launches" if args.rope else "applied by the caller",
                            "arithmetic": "f16 K/V (or q8_0), f32 Q and output, f16 tensor-core products with hi+lo split of Q and P, "
                                          "f32 accumulation; LocDiT f32 throughout"},

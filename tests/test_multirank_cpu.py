@@ -56,9 +56,10 @@ def test_two_ranks_share_nothing_but_scalars(scaling, tmp_path):
     assert slowest == 3.0  # max over ranks, not rank 0's own value
     assert total_rows == sum(x.sum() for x in lens) and heaviest == max(x.sum() for x in lens)
     if scaling == "weak":
-        # every rank serves its own 256 streams, drawn independently
+        # every rank serves its own 256 streams: the same multiset of lengths (fixed work per GPU), its own order
         assert total_streams == 512 and all(len(x) == 256 for x in lens)
-        assert not np.array_equal(lens[0], lens[1])
+        assert not np.array_equal(lens[0], lens[1]) and np.array_equal(np.sort(lens[0]), np.sort(lens[1]))
+        assert np.array_equal(np.sort(lens[0]), np.sort(bench.stream_lengths(256, 0)))
     else:
         # one population of 256 streams, split without loss or duplication and balanced by KV rows
         assert total_streams == 256
