@@ -421,9 +421,26 @@ def main():
         one.step(one_t, advance=False)  # the 10 CFM launches are issued back to back from C
     b.record(stream)
     torch.cuda.synchronize()
+    issued_us = a.elapsed_time(b) * 1e3 / reps
+    launches_per_step = (eng.launches - lb) / (reps * CFM_STEPS)
+    # the same ten launches captured once and replayed: what a server that holds the step as a graph sees (issued
+    # call by call, a single stream is bound by the host's launch rate, which differs from box to box)
+    side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            one.step(one_t, advance=False, stream=side)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    a.record(stream)
+    for _ in range(reps):
+        graph.replay()
+    b.record(stream)
+    torch.cuda.synchronize()
+    replayed_us = a.elapsed_time(b) * 1e3 / reps
     one.close()
-    locdit = {"us_per_patch_single_stream": a.elapsed_time(b) * 1e3 / reps,
-              "launches_per_cfm_step": (eng.launches - lb) / (reps * CFM_STEPS)}
+    locdit = {"us_per_patch_single_stream": issued_us, "us_per_patch_single_stream_graph_replay": replayed_us,
+              "launches_per_cfm_step": launches_per_step}
 
     # ---- end to end through the host-buffer entry point: pinned host inputs, H2D + launches + D2H per step
     e2e = None
