@@ -118,3 +118,37 @@ def test_partition_streams_balances_kv_bytes(pkg):
         assert loads.max() / loads.mean() < 1.01          # byte load within 1 % of even
         assert counts.max() - counts.min() <= 256 // n // 4
     assert list(pkg.partition_streams(np.array([], np.int32), 4)) == []
+
+
+def test_header_is_plain_c_and_links_against_the_library(pkg, tmp_path):
+    """The boundary is a C ABI: the header must compile as C (no C++ in it) and a C program that names every
+    declared entry point must link against the shared library (what a cgo / FFI binding of the reference's host
+    language would do).  The program only calls host-side queries: no GPU is needed."""
+    import os
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    names = pkg.declared_symbols()
+    src = tmp_path / "abi.c"
+    src.write_text(
+        '#include "vox_attn.h"\n#include <stdio.h>\n'
+        "typedef void (*entry_point)(void);\n"
+        "static const entry_point table[] = {" + ", ".join(f"(entry_point) {n}" for n in names) + "};\n"
+        "int main(void) {\n"
+        "    vox_attn_args a = {0};\n"
+        "    int32_t len[4] = {4000, 100, 2000, 2100}, owner[4];\n"
+        "    if (vox_attn_supported(&a)) return 1;                       /* zero shapes are refused */\n"
+        "    if (vox_partition_streams(len, 4, 2, owner) != VOX_ATTN_OK) return 2;\n"
+        "    if (owner[0] == owner[2] && owner[0] == owner[3]) return 3;  /* the long stream does not share with both */\n"
+        "    if (vox_attn_decode_workspace_bytes(256, 16, 2, 4096) == 0) return 4;\n"
+        '    printf("%d symbols, status 0 = %s\\n", (int) (sizeof(table) / sizeof(table[0])), vox_attn_status_string(0));\n'
+        "    return 0;\n}\n")
+    exe = tmp_path / "abi"
+    lib_dir = os.path.dirname(pkg.library_path())
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(root, "include"), str(src), "-o", str(exe),
+                    "-L", lib_dir, "-l:libvoxattn.so", f"-Wl,-rpath,{lib_dir}"], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    assert out.startswith(f"{len(names)} symbols")
