@@ -209,6 +209,9 @@ int vox_rope_table(vox_engine * e, const vox_rope_config * cfg, const int32_t * 
  *            (kv_len - 1).  q and k_new are then the projections BEFORE the rotary embedding
  *            and the launch rotates them (element i with element i + 32) as it reads them;
  *            v_new is stored as it is.  NULL: q and k_new are already rotated.
+ *   stream_order  optional device array, a permutation of [0, n_streams): the order in which the
+ *            launch takes the streams up.  Longest first lets a launch end on short streams
+ *            instead of long ones (vox_group_* keeps such an order); results do not depend on it.
  *   flags    VOX_DECODE_CACHE_STABLE: a promise that neither kv_len nor any cache row this call reads
  *            was written by the kernel launched just before it on the same stream (q, k_new and
  *            v_new may have been).  True for the layers of a model, where a projection GEMM
@@ -232,6 +235,7 @@ typedef struct {
     size_t          new_nb_head, new_nb_stream;
     uint32_t        flags;
     const float *   rope_table;
+    const int32_t * stream_order;
 } vox_decode_args;
 
 size_t vox_attn_decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);

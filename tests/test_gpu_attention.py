@@ -380,7 +380,9 @@ def test_decode_stores_the_arriving_row_itself(kv, engine, pkg, oracle, vo):
     assert torch.equal(got, want)
     # the same call with the promise that lengths and cache are older than the previous kernel (tiles are then
     # requested before the dependency wait): same row stored again, same bits out
-    again = two[1].decode(1, dev(q), kv_len, max(lens), k_new=dev(k_new), v_new=dev(v_new), cache_stable=True)
+    # ... and with the streams taken up longest first instead of in index order
+    order = np.argsort(-np.array(lens), kind="stable").astype(np.int32)
+    again = two[1].decode(1, dev(q), kv_len, max(lens), k_new=dev(k_new), v_new=dev(v_new), cache_stable=True, stream_order=dev(order))
     engine.sync_status()
     assert torch.equal(again, want)
     out = got.cpu().numpy()

@@ -74,7 +74,7 @@ class DecodeArgs(C.Structure):
                 ("kv_len", C.c_void_p), ("kv_bound", C.c_int32), ("q", C.c_void_p), ("q_nb_head", C.c_size_t),
                 ("q_nb_stream", C.c_size_t), ("dst", C.c_void_p), ("scale", C.c_float), ("k_new", C.c_void_p),
                 ("v_new", C.c_void_p), ("new_nb_head", C.c_size_t), ("new_nb_stream", C.c_size_t), ("flags", C.c_uint32),
-                ("rope_table", C.c_void_p)]
+                ("rope_table", C.c_void_p), ("stream_order", C.c_void_p)]
 
 
 class RopeConfig(C.Structure):
@@ -360,7 +360,7 @@ class KVCache:
         _check(lib().vox_kv_copy_from(self.h, other.h, _stream_ptr(stream)))
 
     def decode(self, layer, q, kv_len, kv_bound, scale=0.125, stream=None, dst=None, k_new=None, v_new=None, cache_stable=False,
-               rope_table=None):
+               rope_table=None, stream_order=None):
         """q [n_streams, H, 64] f32, kv_len int32 device [n_streams] -> [n_streams, H, 64].
 
         ``k_new`` / ``v_new`` [n_streams, HK, 64] f32: the token's own rows, stored at position
@@ -375,6 +375,7 @@ class KVCache:
                        dst.data_ptr(), scale)
         a.flags = 1 if cache_stable else 0
         a.rope_table = rope_table.data_ptr() if rope_table is not None else None
+        a.stream_order = stream_order.data_ptr() if stream_order is not None else None
         if k_new is not None or v_new is not None:
             a.k_new = k_new.data_ptr() if k_new is not None else None
             a.v_new = v_new.data_ptr() if v_new is not None else None

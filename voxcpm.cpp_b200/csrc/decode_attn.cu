@@ -63,6 +63,8 @@ struct DecodeParams {
     // Non-null: [stream][32] (cos, sin) pairs; Q and the arriving K row are rotated as they are read
     // (element i with element i + 32: the reference's ggml_rope_ext, GGML_ROPE_TYPE_NEOX).
     const float2 *  rope;
+    // Non-null: a permutation of the streams; CTA z works on stream order[z] (longest first shortens a launch's tail)
+    const int32_t * order;
 };
 
 __device__ __forceinline__ int stream_len(const DecodeParams & p, int stream) {
@@ -140,7 +142,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const int chunk_id = blockIdx.x, kvh = blockIdx.y, stream = blockIdx.z;
+    // CTAs are handed out x first, z last, so the chunks of one (stream, kv head) start together and read neighbouring
+    // memory (handing out all first chunks, then all second chunks, ... measured 9 % slower for f16: 54.1 against 49.7 us).
+    // With `order` the streams are taken longest first, so that the last CTAs to start are short ones.
+    const int chunk_id = blockIdx.x, kvh = blockIdx.y, stream = p.order ? p.order[blockIdx.z] : blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // set-up that reads nothing the previous kernel of the stream wrote: done while that kernel drains
@@ -343,7 +348,11 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             break;
         }
         const int p0 = c0 + i * kKvTile + 16 * warp;
+#ifdef VOX_DECODE_NOMATH  // experiment: the copy structure alone
+        if (false) {
+#else
         if (p0 < c1) {
+#endif
             const uint32_t kb = smem_base + s * R::kStageBytes, vb = kb + R::kDataBytes;
             float sv[2][2];
             if constexpr (!Q8) {
@@ -628,7 +637,7 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
                   size_t q_nb_stream, float * dst, float scale, void * workspace, size_t workspace_bytes,
                   cudaStream_t stream, const vox_kv_cache * append_to = nullptr, const float * k_new = nullptr,
                   const float * v_new = nullptr, size_t new_nb_head = 0, size_t new_nb_stream = 0, bool early = false,
-                  const float * rope_table = nullptr) {
+                  const float * rope_table = nullptr, const int32_t * order = nullptr) {
     const uint32_t bit = q8 ? (1u << 9) : (1u << 8);
     if (!(e->attr_mask & bit)) {
         if (q8) VOX_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring<true>::kSmemBytes));
@@ -644,6 +653,7 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     p.status = e->status_dev;
     p.early = early ? 1 : 0;
     p.rope  = reinterpret_cast<const float2 *>(rope_table);
+    p.order = order;
     p.k_new = p.v_new = nullptr;
     p.new_nb_head = p.new_nb_stream = 0;
     p.k_rows = p.v_rows = p.k_scales = p.v_scales = nullptr;
@@ -726,7 +736,7 @@ int vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspace,
     return launch_decode(e, c->cfg.type == VOX_TYPE_Q8_0, c->map_k, c->map_v, &c->map_ks, &c->map_vs, a->layer, c->cfg.max_len, a->n_streams, a->n_heads, c->cfg.n_kv_heads,
                          a->kv_len, 0, a->kv_bound, a->q, a->q_nb_head, a->q_nb_stream, a->dst, a->scale, workspace,
                          workspace_bytes, static_cast<cudaStream_t>(stream), appends ? c : nullptr, a->k_new, a->v_new,
-                         a->new_nb_head, a->new_nb_stream, (a->flags & VOX_DECODE_CACHE_STABLE) != 0, a->rope_table);
+                         a->new_nb_head, a->new_nb_stream, (a->flags & VOX_DECODE_CACHE_STABLE) != 0, a->rope_table, a->stream_order);
 }
 
 }  // extern "C"

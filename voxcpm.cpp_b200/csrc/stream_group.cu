@@ -32,6 +32,7 @@ struct vox_group {
     int              grid_bound = 0;                  // vox_group_set_bound: grids are sized for this length instead (0: exact)
     void *           workspace = nullptr;
     size_t           workspace_bytes = 0;
+    int32_t *        order_dev = nullptr;             // streams by descending length (all grow together: set once)
     // rotary embedding inside the step (vox_group_set_rope): one table per step, applied by every layer's decode
     bool             rope_on = false;
     vox_rope_config  rope{};
@@ -123,6 +124,7 @@ void vox_group_destroy(vox_group * g) {
     for (int s = 0; s < 2; ++s) vox_kv_destroy(g->cache[s]);
     if (g->workspace) cudaFree(g->workspace);
     if (g->kv_len_dev) cudaFree(g->kv_len_dev);
+    if (g->order_dev) cudaFree(g->order_dev);
     if (g->rope_factors) cudaFree(g->rope_factors);
     if (g->rope_table) cudaFree(g->rope_table);
     if (g->dev_buf) cudaFree(g->dev_buf);
@@ -152,6 +154,13 @@ int vox_group_set_kv_len(vox_group * g, const int32_t * kv_len) {
     VOX_CUDA_TRY(cudaMemcpy(g->kv_len_dev, kv_len, sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
     memcpy(g->kv_len_host.data(), kv_len, sizeof(int32_t) * g->cfg.n_streams);
     g->kv_bound = bound;
+    // longest stream first: a decode launch then ends on short streams (every stream grows by one row per step, so
+    // the order holds until the lengths are set again)
+    std::vector<int32_t> order(g->cfg.n_streams);
+    for (int s = 0; s < g->cfg.n_streams; ++s) order[s] = s;
+    std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return kv_len[a] > kv_len[b]; });
+    if (!g->order_dev) VOX_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&g->order_dev), sizeof(int32_t) * g->cfg.n_streams));
+    VOX_CUDA_TRY(cudaMemcpy(g->order_dev, order.data(), sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
     return VOX_ATTN_OK;
 }
 
@@ -252,6 +261,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         // neither the lengths nor this layer's rows (layer 0 follows the length update)
         da.flags = l > 0 ? VOX_DECODE_CACHE_STABLE : 0u;
         da.rope_table = g->rope_on ? g->rope_table : nullptr;
+        da.stream_order = g->order_dev;
         if (advance) {  // the token's K/V rows are stored by the decode launch itself (position kv_len-1)
             da.k_new = b->lm_k_new + (size_t) l * S * c.n_kv_heads * D;
             da.v_new = b->lm_v_new + (size_t) l * S * c.n_kv_heads * D;
