@@ -78,7 +78,7 @@ __device__ __forceinline__ int stream_len(const DecodeParams & p, int stream) {
 template <bool Q8> struct Ring {
     static constexpr int kStages     = Q8 ? 5 : 4;
     // q8_0 tiles are half the bytes and its arithmetic chain is longer: one more CTA hides it.  Measured per 256-stream
-    // launch: 4 CTAs x 96 registers x 5 stages 45.6 us; 5 x 72 x 4: 48.1 us; 3 x 105 x 6: 48.2 us.
+    // launch (one tile per pass): 4 CTAs x 96 registers x 5 stages 45.6 us; 5 x 72 x 4: 48.1 us; 3 x 105 x 6: 48.2 us.
     static constexpr int kCtasPerSm  = Q8 ? 4 : 3;
     static constexpr int kDataBytes  = Q8 ? kKvTile * 64 : kKvTile * 128;
     static constexpr int kStageBytes = Q8 ? 9 * 1024 : 2 * kDataBytes;
@@ -339,76 +339,102 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     const int k_row = 16 * warp + ((lane >> 4) << 3) + (lane & 7), k_chk = (lane >> 3) & 1;
     const int v_row = 16 * warp + (((lane >> 3) & 1) << 3) + (lane & 7), v_chk = lane >> 4;
 
-    for (int i = 0; i < n_tiles; ++i) {
-        const int s = i % kStages;
-        if (!mbar_wait_bounded(full0 + 8 * s, (i / kStages) & 1)) {
-            atomicOr(p.status, kStatusTimeout);
-            atomicExch(&abort_flag, 1);
-            ok = false;
-            break;
+    // Tiles per pass of a consumer warp.  q8_0 takes two (its 16 rows of each): the byte unpacking and the per-block
+    // scales make its dependency chains long, and two independent tiles in one pass give the scheduler something to
+    // overlap them with; max, rescale decision and row sum are then taken once per 32 rows.  Measured per 256-stream
+    // launch: at 3 CTAs per SM (115 registers) 48.2 -> 45.4 us; at 4 CTAs per SM (96 registers, the configuration
+    // used) 43.9 -> 43.8 us: with that register budget the compiler cannot keep both chains in flight.
+    constexpr int U = Q8 ? 2 : 1;
+    for (int i = 0; i < n_tiles && ok; i += U) {
+        int  st[U], p0[U];
+        bool have[U], act[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            have[u] = i + u < n_tiles;
+            st[u]   = (i + u) % kStages;
+            p0[u]   = c0 + (i + u) * kKvTile + 16 * warp;
+            act[u]  = have[u] && p0[u] < c1;
+            if (have[u] && !mbar_wait_bounded(full0 + 8 * st[u], ((i + u) / kStages) & 1)) {
+                atomicOr(p.status, kStatusTimeout);
+                atomicExch(&abort_flag, 1);
+                ok = false;
+            }
         }
-        const int p0 = c0 + i * kKvTile + 16 * warp;
+        if (!ok) break;
 #ifdef VOX_DECODE_NOMATH  // experiment: the copy structure alone
         if (false) {
 #else
-        if (p0 < c1) {
+        if (act[0]) {
 #endif
-            const uint32_t kb = smem_base + s * R::kStageBytes, vb = kb + R::kDataBytes;
-            float sv[2][2];
-            if constexpr (!Q8) {
-                float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float sv[U][2][2];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(kb + k_row * 128 + (((2 * c + k_chk) ^ (k_row & 7)) << 4), b0, b1, b2, b3);
-                    mma_16816(sc[0], qa[c], b0, b1);
-                    mma_16816(sc[1], qa[c], b2, b3);
+            for (int u = 0; u < U; ++u) {
+                const uint32_t kb = smem_base + st[u] * R::kStageBytes;
+                if (!act[u]) {
+                    sv[u][0][0] = sv[u][0][1] = sv[u][1][0] = sv[u][1][1] = -INFINITY;
+                    continue;
                 }
+                if constexpr (!Q8) {
+                    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    sv[j][0] = sc[j][0] + sc[j][2];
-                    sv[j][1] = sc[j][1] + sc[j][3];
-                }
-            } else {
-                const uint32_t ksc = kb + 2 * R::kDataBytes;
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int row = 16 * warp + 8 * j + g;
-                    float     sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // one accumulator per 32-value block
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        const uint2 raw = lds64(kb + row * 64 + (((2 * b + (t >> 1)) ^ ((row >> 1) & 3)) << 4) + ((t & 1) << 3));
-                        const uint32_t x0 = raw.x ^ 0x80808080u, x1 = raw.y ^ 0x80808080u;
-                        mma_16816(sc[b], qa[2 * b], s8_pair_to_half2(x0, 0x4140), s8_pair_to_half2(x0, 0x4342));
-                        mma_16816(sc[b], qa[2 * b + 1], s8_pair_to_half2(x1, 0x4140), s8_pair_to_half2(x1, 0x4342));
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(kb + k_row * 128 + (((2 * c + k_chk) ^ (k_row & 7)) << 4), b0, b1, b2, b3);
+                        mma_16816(sc[0], qa[c], b0, b1);
+                        mma_16816(sc[1], qa[c], b2, b3);
                     }
-                    // scales of positions 8j+2t and 8j+2t+1, both blocks: four consecutive halves
-                    const uint2 ds = lds64(ksc + (16 * warp + 8 * j + 2 * t) * 4);
-                    sv[j][0] = (sc[0][0] + sc[0][2]) * half_lo(ds.x) + (sc[1][0] + sc[1][2]) * half_hi(ds.x);
-                    sv[j][1] = (sc[0][1] + sc[0][3]) * half_lo(ds.y) + (sc[1][1] + sc[1][3]) * half_hi(ds.y);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        sv[u][j][0] = sc[j][0] + sc[j][2];
+                        sv[u][j][1] = sc[j][1] + sc[j][3];
+                    }
+                } else {
+                    const uint32_t ksc = kb + 2 * R::kDataBytes;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int row = 16 * warp + 8 * j + g;
+                        float     sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // one accumulator per 32-value block
+#pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            const uint2 raw = lds64(kb + row * 64 + (((2 * b + (t >> 1)) ^ ((row >> 1) & 3)) << 4) + ((t & 1) << 3));
+                            const uint32_t x0 = raw.x ^ 0x80808080u, x1 = raw.y ^ 0x80808080u;
+                            mma_16816(sc[b], qa[2 * b], s8_pair_to_half2(x0, 0x4140), s8_pair_to_half2(x0, 0x4342));
+                            mma_16816(sc[b], qa[2 * b + 1], s8_pair_to_half2(x1, 0x4140), s8_pair_to_half2(x1, 0x4342));
+                        }
+                        // scales of positions 8j+2t and 8j+2t+1, both blocks: four consecutive halves
+                        const uint2 ds = lds64(ksc + (16 * warp + 8 * j + 2 * t) * 4);
+                        sv[u][j][0] = (sc[0][0] + sc[0][2]) * half_lo(ds.x) + (sc[1][0] + sc[1][2]) * half_hi(ds.x);
+                        sv[u][j][1] = (sc[0][1] + sc[0][3]) * half_lo(ds.y) + (sc[1][1] + sc[1][3]) * half_hi(ds.y);
+                    }
                 }
             }
             float tmax = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
+            for (int u = 0; u < U; ++u)
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int pos = p0 + 8 * j + 2 * t + e;
-                    sv[j][e]      = pos < c1 ? sv[j][e] : -INFINITY;
-                    tmax          = fmaxf(tmax, sv[j][e]);
-                }
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int pos = p0[u] + 8 * j + 2 * t + e;
+                        sv[u][j][e]   = pos < c1 ? sv[u][j][e] : -INFINITY;
+                        tmax          = fmaxf(tmax, sv[u][j][e]);
+                    }
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
             const float m_new = fmaxf(m, tmax);
             const float alpha = m_new == -INFINITY ? 1.0f : ex2_approx(m - m_new);
             const float m_use = m_new == -INFINITY ? 0.0f : m_new;
             m                 = m_new;
-            float pr[2][2];
+            float pr[U][2][2];
+            float psum_q8 = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                pr[j][0] = ex2_approx(sv[j][0] - m_use);
-                pr[j][1] = ex2_approx(sv[j][1] - m_use);
-            }
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    pr[u][j][0] = ex2_approx(sv[u][j][0] - m_use);
+                    pr[u][j][1] = ex2_approx(sv[u][j][1] - m_use);
+                    psum_q8 += pr[u][j][0] + pr[u][j][1];
+                }
             if (__any_sync(0xffffffffu, alpha != 1.0f)) {  // after the first tiles the running maxima rarely move
 #pragma unroll
                 for (int n = 0; n < 8; ++n) {
@@ -416,13 +442,14 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 }
             }
             if constexpr (!Q8) {
-                uint32_t pa[4];
-                float    psum = 0.0f;
+                const uint32_t vb = smem_base + st[0] * R::kStageBytes + R::kDataBytes;
+                uint32_t       pa[4];
+                float          psum = 0.0f;
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     float h0, l0, h1, l1;
-                    split_hi_lo(pr[j][0], h0, l0);
-                    split_hi_lo(pr[j][1], h1, l1);
+                    split_hi_lo(pr[0][j][0], h0, l0);
+                    split_hi_lo(pr[0][j][1], h1, l1);
                     pa[2 * j]     = pack_half2(h0, h1);
                     pa[2 * j + 1] = pack_half2(l0, l1);
                     psum += (h0 + l0) + (h1 + l1);
@@ -436,39 +463,46 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                     mma_16816(o[2 * n2 + 1], pa, b2, b3);
                 }
             } else {
-                l = l * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
-                // V scales are folded into the weights: one A operand per 32-wide block of output columns
-                const uint32_t vsc = kb + 2 * R::kDataBytes + kKvTile * 4;
-                uint32_t       pa[2][4];
+                l = l * alpha + psum_q8;
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const uint2 ds = lds64(vsc + (16 * warp + 8 * j + 2 * t) * 4);
+                for (int u = 0; u < U; ++u) {
+                    if (!act[u]) continue;
+                    const uint32_t kb = smem_base + st[u] * R::kStageBytes, vb = kb + R::kDataBytes;
+                    // V scales are folded into the weights: one A operand per 32-wide block of output columns
+                    const uint32_t vsc = kb + 2 * R::kDataBytes + kKvTile * 4;
+                    uint32_t       pa[2][4];
 #pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        // weights times V scale rounded to f16 once (2^-12 relative, far inside the q8_0
-                        // tolerance): the lo rows of the A operand stay zero
-                        pa[b][2 * j]     = pack_half2(pr[j][0] * (b ? half_hi(ds.x) : half_lo(ds.x)),
-                                                      pr[j][1] * (b ? half_hi(ds.y) : half_lo(ds.y)));
-                        pa[b][2 * j + 1] = 0u;
+                    for (int j = 0; j < 2; ++j) {
+                        const uint2 ds = lds64(vsc + (16 * warp + 8 * j + 2 * t) * 4);
+#pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            // weights times V scale rounded to f16 once (2^-12 relative, far inside the q8_0
+                            // tolerance): the lo rows of the A operand stay zero
+                            pa[b][2 * j]     = pack_half2(pr[u][j][0] * (b ? half_hi(ds.x) : half_lo(ds.x)),
+                                                          pr[u][j][1] * (b ? half_hi(ds.y) : half_lo(ds.y)));
+                            pa[b][2 * j + 1] = 0u;
+                        }
                     }
-                }
-                // ldmatrix.trans on 16-bit units keeps byte pairs together: a register holds
-                // V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1] of one 16-column chunk, i.e. the B
-                // fragments of an "even columns" tile (bytes 0,2) and an "odd columns" tile (bytes 1,3).
+                    // ldmatrix.trans on 16-bit units keeps byte pairs together: a register holds
+                    // V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1] of one 16-column chunk, i.e. the B
+                    // fragments of an "even columns" tile (bytes 0,2) and an "odd columns" tile (bytes 1,3).
 #pragma unroll
-                for (int cp = 0; cp < 2; ++cp) {
-                    uint32_t r0, r1, r2, r3;
-                    ldmatrix_x4_trans(vb + v_row * 64 + (((2 * cp + v_chk) ^ ((v_row >> 1) & 3)) << 4), r0, r1, r2, r3);
-                    r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-                    mma_16816(o[4 * cp + 0], pa[cp], s8_pair_to_half2(r0, 0x4240), s8_pair_to_half2(r1, 0x4240));
-                    mma_16816(o[4 * cp + 1], pa[cp], s8_pair_to_half2(r0, 0x4341), s8_pair_to_half2(r1, 0x4341));
-                    mma_16816(o[4 * cp + 2], pa[cp], s8_pair_to_half2(r2, 0x4240), s8_pair_to_half2(r3, 0x4240));
-                    mma_16816(o[4 * cp + 3], pa[cp], s8_pair_to_half2(r2, 0x4341), s8_pair_to_half2(r3, 0x4341));
+                    for (int cp = 0; cp < 2; ++cp) {
+                        uint32_t r0, r1, r2, r3;
+                        ldmatrix_x4_trans(vb + v_row * 64 + (((2 * cp + v_chk) ^ ((v_row >> 1) & 3)) << 4), r0, r1, r2, r3);
+                        r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+                        mma_16816(o[4 * cp + 0], pa[cp], s8_pair_to_half2(r0, 0x4240), s8_pair_to_half2(r1, 0x4240));
+                        mma_16816(o[4 * cp + 1], pa[cp], s8_pair_to_half2(r0, 0x4341), s8_pair_to_half2(r1, 0x4341));
+                        mma_16816(o[4 * cp + 2], pa[cp], s8_pair_to_half2(r2, 0x4240), s8_pair_to_half2(r3, 0x4240));
+                        mma_16816(o[4 * cp + 3], pa[cp], s8_pair_to_half2(r2, 0x4341), s8_pair_to_half2(r3, 0x4341));
+                    }
                 }
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (have[u] && lane == 0) mbar_arrive(empty0 + 8 * st[u]);
     }
 
     l += __shfl_xor_sync(0xffffffffu, l, 1);
