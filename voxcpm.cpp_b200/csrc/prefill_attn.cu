@@ -523,23 +523,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         rescale_accumulators(t_row, f);
                     }
                 }
-#ifndef VOX_PREFILL_NOSOFTMAX
                 // P = 2^(c*S - m_ref) as packed f16 over the first half of the scores just read
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     uint32_t h[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-#ifdef VOX_PREFILL_NOEXP  // experiment: everything but the exponentials
-                        h[i] = pack_half2(fmaf(__uint_as_float(r[32 * c + 2 * i]), p.scale_log2, -m_ref),
-                                          fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), p.scale_log2, -m_ref));
-#else
                         h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i]), p.scale_log2, -m_ref)),
                                           ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), p.scale_log2, -m_ref)));
-#endif
                     tmem_st16_nowait(t_s + 16 * c, h);
                 }
-#endif
                 PROF_STOP(2);
                 tmem_wait_st();
                 tc_fence_before();
