@@ -1,0 +1,122 @@
+"""Parity at the benchmark's full sizes, through properties that do not need the CPU oracle to finish the whole job:
+attention weights sum to one (a constant V comes back unchanged), the output is linear in V, rows past a stream's
+length and keys past the causal diagonal have no influence, and a sample of streams / rows is checked against the
+oracle.  Sizes: 256 ragged streams with KV lengths in [128, 4096] (one layer of the serving step), causal prefill of
+512 tokens x batch 8, the LocDiT patch of 256 streams."""
+import numpy as np
+import pytest
+
+from cases import KV_TYPE, rel_err
+
+pytestmark = pytest.mark.gpu
+
+H, HK, D = 16, 2, 64
+TOL = {"f16": 2e-3, "q8_0": 1e-2, "f32": 2e-3}
+
+
+def dev(x):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def _grid_values(shape, gen, device="cuda"):
+    """Values k/8 with |k| <= 24: sums and doubles of them are exact in f16, so linearity can be checked tightly."""
+    import torch
+    return (torch.randint(-24, 25, shape, generator=gen, device=device).float() / 8.0)
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+def test_decode_256_ragged_streams(kv, engine, pkg, oracle, vo):
+    import torch
+    S, cap = 256, 4096
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    lens = np.random.default_rng(12345).integers(128, cap + 1, S).astype(np.int32)
+    kv_len = dev(lens)
+    caches = [pkg.KVCache(engine, 1, S, HK, cap, KV_TYPE[kv]) for _ in range(3)]  # V1, V2, V1 + V2 over the same K
+    k = torch.randn((S, cap, HK, D), device="cuda", generator=gen)
+    v1, v2 = _grid_values((S, cap, HK, D), gen), _grid_values((S, cap, HK, D), gen)
+    if kv == "q8_0":  # one nonzero magnitude per 32-value block keeps the quantised values exact: +-m or 0
+        one = torch.ones((), device="cuda")
+        sign1, sign2 = torch.where(v1 >= 0, one, -one), torch.where(v2 >= 0, one, -one)
+        mag = (torch.randint(1, 9, (S, cap, HK, 2), generator=gen, device="cuda").float() / 8.0).repeat_interleave(32, dim=-1)
+        v1, v2 = sign1 * mag, sign2 * mag  # sums are 0 or +-2m: exact again
+    for c, v in zip(caches, (v1, v2, v1 + v2)):
+        c.append(0, k, v, pos0=0)
+    # rows beyond each stream's length hold finite garbage that must not matter: overwrite them in one cache only
+    noisy = pkg.KVCache(engine, 1, S, HK, cap, KV_TYPE[kv])
+    mask = (torch.arange(cap, device="cuda")[None, :] >= kv_len[:, None]).float()[:, :, None, None]
+    noisy.append(0, k + mask * 7.0, v1 + mask * 100.0, pos0=0)
+    q = torch.randn((S, H, D), device="cuda", generator=gen)
+    out = [c.decode(0, q, kv_len, cap) for c in caches]
+    out_noisy = noisy.decode(0, q, kv_len, cap)
+    engine.sync_status()
+    assert all(torch.isfinite(o).all() for o in out)
+    assert torch.equal(out_noisy, out[0])  # bit for bit: nothing past the length is read into the result
+    # linearity in V (exact inputs; what remains is the rounding of the weights and of the accumulation)
+    rms = out[2].pow(2).mean().sqrt().item()
+    assert (out[0] + out[1] - out[2]).abs().max().item() / rms < TOL[kv] / 4
+    # a V that is the same row everywhere comes back as that row: the weights sum to one
+    const = pkg.KVCache(engine, 1, S, HK, cap, KV_TYPE[kv])
+    row = torch.tensor(np.linspace(-2.0, 2.0, D, dtype=np.float32)).cuda().half().float()
+    if kv == "q8_0":
+        row = torch.where(torch.arange(D, device="cuda") % 2 == 0, torch.tensor(1.5, device="cuda"), torch.tensor(-1.5, device="cuda"))
+    const.append(0, k, row.expand(S, cap, HK, D).contiguous(), pos0=0)
+    out_c = const.decode(0, q, kv_len, cap)
+    engine.sync_status()
+    assert (out_c - row).abs().max().item() < 2e-3 * float(row.abs().max())
+    # a sample of streams against the oracle (shortest, longest, and a few in between)
+    order = np.argsort(lens)
+    for s in [int(order[0]), int(order[-1]), int(order[S // 2]), 7, 200]:
+        ke, ve = caches[0].export(0, s, int(lens[s]))
+        ref = oracle.attn(q[s].cpu().numpy()[None, :, None, :], ke[None], ve[None], kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)[0, 0]
+        assert rel_err(out[0][s].cpu().numpy(), ref) < TOL[kv], f"stream {s} (kv_len {lens[s]})"
+
+
+def test_prefill_512_tokens_batch_8(engine, oracle, vo):
+    import torch
+    B, L = 8, 512
+    gen = torch.Generator(device="cuda").manual_seed(22)
+    q = torch.randn((B, H, L, D), device="cuda", generator=gen).half().float()
+    k = torch.randn((B, HK, L, D), device="cuda", generator=gen).half()
+    v1, v2 = _grid_values((B, HK, L, D), gen).half(), _grid_values((B, HK, L, D), gen).half()
+    o1, o2, o12 = (engine.prefill(q, k, v).clone() for v in (v1, v2, v1 + v2))
+    engine.sync_status()
+    rms = o12.pow(2).mean().sqrt().item()
+    assert (o1 + o2 - o12).abs().max().item() / rms < TOL["f16"]  # linear in V (the weights are f16 in each run)
+    # causality: what lies after a row cannot reach it.  Perturb the last 200 keys and values: rows < 312 keep their bits.
+    k2, v3 = k.clone(), v1.clone()
+    k2[:, :, 312:] += 3.0
+    v3[:, :, 312:] = 50.0
+    o_p = engine.prefill(q, k2, v3)
+    engine.sync_status()
+    assert torch.equal(o_p[:, :312], o1[:, :312]) and not torch.equal(o_p[:, 312:], o1[:, 312:])
+    # constant V comes back unchanged
+    row = torch.tensor(np.linspace(-2.0, 2.0, D, dtype=np.float32)).cuda().half()
+    o_c = engine.prefill(q, k, row.expand(B, HK, L, D).contiguous())
+    engine.sync_status()
+    assert (o_c - row.float()).abs().max().item() < 2e-3 * 2.0
+    # two whole sequences against the oracle (its tiled path, as the reference runs this shape)
+    mask = oracle.causal_mask(np.arange(L), L)[None, None]
+    for b in (0, B - 1):
+        ref = oracle.attn(q[b:b + 1].cpu().numpy(), k[b:b + 1].cpu().numpy(), v1[b:b + 1].cpu().numpy(), mask, kv_type=vo.F16, path=vo.PATH_TILED)
+        assert rel_err(o1[b:b + 1].cpu().numpy(), ref) < TOL["f16"]
+
+
+def test_locdit_patch_of_256_streams(engine, oracle, vo):
+    import torch
+    S, L, seq = 256, 8, 9
+    gen = torch.Generator(device="cuda").manual_seed(23)
+    q = torch.randn((S, L, 2, H, seq, D), device="cuda", generator=gen)
+    k = torch.randn((S, L, 2, HK, seq, D), device="cuda", generator=gen)
+    v1, v2 = _grid_values((S, L, 2, HK, seq, D), gen), _grid_values((S, L, 2, HK, seq, D), gen)
+    o1, o2, o12 = (engine.locdit_step(q, k, v).clone() for v in (v1, v2, v1 + v2))
+    engine.sync_status()
+    rms = o12.pow(2).mean().sqrt().item()
+    assert (o1 + o2 - o12).abs().max().item() / rms < 1e-5  # f32 throughout (hi + lo products)
+    row = torch.tensor(np.linspace(-2.0, 2.0, D, dtype=np.float32)).cuda()
+    o_c = engine.locdit_step(q, k, row.expand(S, L, 2, HK, seq, D).contiguous())
+    engine.sync_status()
+    assert (o_c - row).abs().max().item() < 1e-5
+    for s, l in [(0, 0), (255, 7), (100, 3)]:
+        ref = oracle.attn(q[s, l].cpu().numpy(), k[s, l].cpu().numpy(), v1[s, l].cpu().numpy(), kv_type=vo.F32, path=vo.PATH_ROW_F32)
+        assert rel_err(o1[s, l].cpu().numpy(), ref) < TOL["f32"]
