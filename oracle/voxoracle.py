@@ -22,11 +22,14 @@ F32, F16, Q8_0 = 0, 1, 8
 PATH_AUTO, PATH_ROW, PATH_ROW_F32, PATH_TILED, PATH_F64, PATH_SPLIT_KV = 0, 1, 2, 3, 4, 5
 
 
+REFERENCE_DIR = os.environ.get("VOX_REFERENCE_DIR", "/root/reference")  # checkout of the reference project, if any
+
+
 def build(ref: bool = True) -> None:
     """Compile the C restatement, and the reference library when its sources are present."""
     subprocess.run(["make", "-C", HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
-    if ref and os.path.exists("/root/reference/third_party/ggml/src/ggml.c"):
-        subprocess.run(["make", "-C", HERE, "-j8", "ref"], check=True, stdout=subprocess.DEVNULL)
+    if ref and os.path.exists(os.path.join(REFERENCE_DIR, "third_party/ggml/src/ggml.c")):
+        subprocess.run(["make", "-C", HERE, "-j8", "ref", f"REF={REFERENCE_DIR}"], check=True, stdout=subprocess.DEVNULL)
 
 
 def _ptr(a):
