@@ -67,3 +67,23 @@ def test_two_ranks_share_nothing_but_scalars(scaling, tmp_path):
         assert np.array_equal(everything, np.sort(bench.stream_lengths(256, 0)))
         loads = np.array([x.sum() for x in lens], np.float64)
         assert loads.max() / loads.mean() < 1.01
+
+
+def test_reference_arm_prints_one_contract_line(tmp_path):
+    """`bench.py --impl reference` needs no GPU: one JSON line on stdout with the keys the benchmark contract names."""
+    import json
+    import subprocess
+
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                        "--cpu-sample-streams", "2"], capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [x for x in r.stdout.splitlines() if x.strip()]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
+        assert key in line, key
+    assert line["impl"] == "reference" and line["metric"] == "patches/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert "workload" in line["config"] and "model" not in line["config"]
