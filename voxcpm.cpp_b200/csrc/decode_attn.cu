@@ -344,7 +344,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     // overlap them with; max, rescale decision and row sum are then taken once per 32 rows.  Measured per 256-stream
     // launch: at 3 CTAs per SM (115 registers) 48.2 -> 45.4 us; at 4 CTAs per SM (96 registers, the configuration
     // used) 43.9 -> 43.8 us: with that register budget the compiler cannot keep both chains in flight.
-    constexpr int U = Q8 ? 2 : 1;
+    constexpr int U = Q8 ? 2 : 1;  // f16 with two tiles per pass measured 50.6 against 49.9 us: it holds two stages at a time
     for (int i = 0; i < n_tiles && ok; i += U) {
         int  st[U], p0[U];
         bool have[U], act[U];
@@ -442,26 +442,30 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 }
             }
             if constexpr (!Q8) {
-                const uint32_t vb = smem_base + st[0] * R::kStageBytes + R::kDataBytes;
-                uint32_t       pa[4];
-                float          psum = 0.0f;
+                float psum = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    float h0, l0, h1, l1;
-                    split_hi_lo(pr[0][j][0], h0, l0);
-                    split_hi_lo(pr[0][j][1], h1, l1);
-                    pa[2 * j]     = pack_half2(h0, h1);
-                    pa[2 * j + 1] = pack_half2(l0, l1);
-                    psum += (h0 + l0) + (h1 + l1);
+                for (int u = 0; u < U; ++u) {
+                    if (!act[u]) continue;
+                    const uint32_t vb = smem_base + st[u] * R::kStageBytes + R::kDataBytes;
+                    uint32_t       pa[4];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float h0, l0, h1, l1;
+                        split_hi_lo(pr[u][j][0], h0, l0);
+                        split_hi_lo(pr[u][j][1], h1, l1);
+                        pa[2 * j]     = pack_half2(h0, h1);
+                        pa[2 * j + 1] = pack_half2(l0, l1);
+                        psum += (h0 + l0) + (h1 + l1);
+                    }
+#pragma unroll
+                    for (int n2 = 0; n2 < 4; ++n2) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4_trans(vb + v_row * 128 + (((2 * n2 + v_chk) ^ (v_row & 7)) << 4), b0, b1, b2, b3);
+                        mma_16816(o[2 * n2], pa, b0, b1);
+                        mma_16816(o[2 * n2 + 1], pa, b2, b3);
+                    }
                 }
                 l = l * alpha + psum;
-#pragma unroll
-                for (int n2 = 0; n2 < 4; ++n2) {
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4_trans(vb + v_row * 128 + (((2 * n2 + v_chk) ^ (v_row & 7)) << 4), b0, b1, b2, b3);
-                    mma_16816(o[2 * n2], pa, b0, b1);
-                    mma_16816(o[2 * n2 + 1], pa, b2, b3);
-                }
             } else {
                 l = l * alpha + psum_q8;
 #pragma unroll
