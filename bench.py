@@ -61,6 +61,31 @@ def stream_lengths(n, rank=0):
     return np.random.default_rng(12345 + rank).integers(KV_LO, KV_HI + 1, n).astype(np.int32)
 
 
+def bind_to_gpu_numa_node(torch, device_index):
+    """Keep this process (and the pinned host buffers it allocates afterwards) on the NUMA node of its GPU: with one
+    process per GPU the host-buffer entry point otherwise sends half of its traffic across the socket link.  Returns
+    the node, or None when the platform does not say (containers often hide it): then nothing is changed."""
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        base = f"/sys/bus/pci/devices/{bdf}"
+        node = int(open(base + "/numa_node").read().strip())
+        cpus = open(base + "/local_cpulist").read().strip()
+        if node < 0 or not cpus:
+            return None
+        ids = set()
+        for part in cpus.split(","):
+            lo, _, hi = part.partition("-")
+            ids.update(range(int(lo), int(hi or lo) + 1))
+        allowed = ids & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 def streams_of_rank(scaling, n_streams, rank, world, partition):
     """KV lengths of the streams one rank serves.  weak: every rank serves `n_streams` streams with the same
     multiset of ragged lengths (the per-GPU work is what is held fixed), in an order of its own; strong: one
@@ -317,6 +342,7 @@ def main():
     pkg = entry.import_package()
 
     torch.cuda.set_device(local)
+    numa_node = bind_to_gpu_numa_node(torch, local) if world > 1 else None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -480,6 +506,7 @@ def main():
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD.format(s=args.streams), "streams_total": int(total_streams), "kv_type": args.kv_type,
                            "l2": "inputs larger than L2 (KV read per step >> 126 MB)", "append": "included",
+                           "host_numa_node": numa_node,
                            "placement": "weak: every GPU serves the same multiset of ragged lengths" if args.scaling == "weak"
                            else "strong: one population split over the GPUs by KV rows (longest-processing-time)",
                            "rope": "rotary embedding of Q and the new K rows inside the decode launches" if args.rope else "applied by the caller",
