@@ -10,7 +10,7 @@
 //   grid  = (kv chunks, kv heads, streams); one CTA owns `chunk` consecutive cache rows of one
 //           kv head of one stream and serves all GQA query heads that share it, so each K/V
 //           byte is fetched once for the whole group;
-//   copy  = a producer warp streams 64-row K and V tiles into a 4-stage shared-memory ring with
+//   copy  = a producer warp streams 64-row K and V tiles into a shared-memory ring (4 stages for f16, 6 for q8_0) with
 //           bulk-tensor copies (cp.async.bulk.tensor, 128-byte swizzle) signalled on mbarriers;
 //   math  = four consumer warps, 16 rows each.  Q (pre-scaled by scale*log2 e) is split as
 //           hi + lo in f16 and the two parts occupy rows 0-7 and 8-15 of the m16n8k16 A operand,

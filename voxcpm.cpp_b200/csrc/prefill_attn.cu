@@ -8,31 +8,37 @@
 //
 // A work item = 128 query rows of one head of one sequence, walked over 64-key tiles.  CTAs are persistent
 // (two per SM) and take items from a heaviest-first list in snake order; barriers, TMEM and the tile of ones
-// are set up once.  Six warps:
+// are set up once.  Twelve warps in three warpgroups, which trade registers after launch (setmaxnreg: the launch
+// allots 80 per thread, the softmax group takes 144, the others keep 40 and 56):
 //   warps 0-3  softmax: one thread per query row (row r = TMEM lane r).  Per tile a thread reads its 64 scores
 //              from TMEM (tcgen05.ld), takes their maximum, and writes P = 2^(c*S - m_ref) as packed f16 back into
 //              TMEM (tcgen05.st) over the first half of the scores it has just read: the tensor core takes the
 //              weights from there as the A operand of P.V, so they never pass through shared memory.  On the
 //              diagonal tile a warp skips the 32-column blocks none of its rows can see.  The output row and the
 //              row sums accumulate in TMEM over all tiles (no per-tile read-back); they are rescaled in place only
-//              when a tile's maximum exceeds the reference m_ref by more than 2^8, and read once at the end.
+//              when a tile's maximum exceeds the reference m_ref by more than 2^8.  These warps do nothing else:
+//              from the last tile of an item they go straight to the first tile of the next.
 //   warp 4     producer: one lane issues cp.async.bulk.tensor copies of 64-row K and V tiles into four-stage rings.
 //   warp 5     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128).  S = Q.K^T (N=64, 4 k-steps, both
-//              operands in shared memory) goes to one of two score buffers in TMEM (tile T uses buffer T % 2), so
-//              the scores of tile T+1 are computed while the softmax of tile T runs.  O += P.V and the row sums
-//              come from ONE instruction per 16 keys (N=80, 4 k-steps): P from TMEM, V read MN-major straight
-//              from its row-major tile, and a tile of ones addressed as columns 64-79 of every V tile, which
-//              yields the sums of exactly the rounded weights the tensor core used.  The tensor pipe executes in
-//              issue order, so Q.K^T of tile T+2, issued behind P.V of tile T, overwrites that tile's weights only
-//              once they have been used.  Completion is signalled with tcgen05.commit (two per tile).
+//              operands in shared memory) goes to one of two score buffers in TMEM (tile T uses buffer T % 2) and
+//              runs two tiles ahead of P.V, across item boundaries, so the scores of tile T+1 are computed while the
+//              softmax of tile T runs.  O += P.V and the row sums come from ONE instruction per 16 keys (N=80,
+//              4 k-steps): P from TMEM, V read MN-major straight from its row-major tile, and a tile of ones
+//              addressed as columns 64-79 of every V tile, which yields the sums of exactly the rounded weights the
+//              tensor core used.  The tensor pipe executes in issue order, so Q.K^T of tile T+2, issued behind P.V
+//              of tile T, overwrites that tile's weights only once they have been used.  Completion is signalled
+//              with tcgen05.commit (two per tile).  (Warps 6-7 only fill the warpgroup.)
+//   warps 8-11 in/out: one thread per query row again.  They keep the Q tiles of the next two items in shared
+//              memory (f32 from memory, rounded to f16 once, exact when it already holds f16 values) and read each
+//              finished output row out of TMEM, normalise and store it, handing the columns back to the issuer.
 // Measured costs that shaped this: a tcgen05.mma costs its issuing thread 45-70 cycles whatever its shape, so
 // instructions are few and wide (the sums ride along with P.V); the per-tile chain scores -> weights -> P.V ->
 // next scores was 2.5x the softmax time until the scores were double-buffered; and a parity wait cannot see
 // two completed phases, so every barrier here completes at most once between two looks of its waiters.
-// Q arrives as f32 and is rounded to f16 once per item (exact when it already holds f16 values);
-// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  89 KB of shared memory and
-// 256 TMEM columns per CTA.  Every wait is bounded; on expiry the status word is set and all roles fall
-// through to the common exit, where the TMEM columns are released.
+// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  105 KB of shared memory,
+// 256 TMEM columns and half the register file per CTA.  Every wait on a barrier is bounded; on expiry the status
+// word is set and all roles fall through to the common exit, where the TMEM columns are released.  The register
+// trade cannot block: what the softmax group takes is exactly what the other two give up (static_assert below).
 #include "common.cuh"
 
 #include <algorithm>
@@ -71,14 +77,20 @@ constexpr int kQBytes    = kTile * 128;    // the item's [128][64] f16 Q tile
 constexpr int kKvBytes   = kKeys * 128;    // one [64][64] f16 K or V tile
 constexpr int kStages    = 4;              // K ring and V ring
 constexpr int kSoftmaxThreads = 128;
-constexpr int kThreadsPf = kSoftmaxThreads + 64;
+constexpr int kIoThreads = 128;
+constexpr int kThreadsPf = 384;            // softmax warpgroup, control warpgroup (producer, issuer, two idle warps), in/out warpgroup
+constexpr int kQBufs     = 2;              // Q tiles of two consecutive items
+// Registers per thread after the warpgroups have traded (setmaxnreg).  What one group takes must have been given
+// up by the others of the same CTA: the launch allots 80 x 384 (two CTAs per SM), so the three figures sum to 240.
+constexpr int kRegsSoftmax = 144, kRegsControl = 40, kRegsIo = 56;
+static_assert(kRegsSoftmax + kRegsControl + kRegsIo == 3 * 80, "the CTA's registers are conserved");
 // TMEM columns: two score buffers (tile T uses buffer T % 2; its weights, packed f16, replace the first 32
 // columns of its scores) and the output row with its row sum
 constexpr int kTmemCols  = 256;
 constexpr int kSCol      = 0;              // S: 2 x 64 columns
 constexpr int kOCol      = 128;            // O: 64 columns, row sums: 16 columns behind them
 constexpr int kOnesBytes = kKvBytes;       // a tile of ones, addressed as columns 64-79 of every V tile (any layout: every element is 1)
-constexpr int kSmemPf    = kQBytes + 2 * kStages * kKvBytes + kOnesBytes + 1024;  // Q, K ring, V ring, ones
+constexpr int kSmemPf    = kQBufs * kQBytes + 2 * kStages * kKvBytes + kOnesBytes + 1024;  // Q x 2, K ring, V ring, ones
 
 struct PrefillParams {
     const uint8_t * q;
@@ -121,6 +133,11 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Warpgroups trade registers after launch: every warp of a group of four executes the same one.
+template <int N>
+__device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void regs_give() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 // 32 consecutive 32-bit columns of this thread's TMEM lane; the registers are valid after tmem_wait_ld
 __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t * r) {
     asm volatile(
@@ -257,13 +274,13 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
 __global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[4 * kStages + 5];
+    __shared__ uint64_t bars[4 * kStages + 6];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sK0 = sQ + kQBytes, sV0 = sK0 + kStages * kKvBytes, sOnes = sV0 + kStages * kKvBytes;
+    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBytes, sV0 = sK0 + kStages * kKvBytes, sOnes = sV0 + kStages * kKvBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -273,9 +290,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     // the softmax warps may be two tiles ahead of the MMA thread (the scores of tile T+1 exist before it has
     // looked at the weights of tile T), so "weights ready" is one barrier per buffer: a single one could complete
     // two phases unobserved, and a parity wait cannot tell that from none;
-    // per-item barriers: Q in place, output complete, output read
+    // per-item barriers: Q in place (one per Q buffer, for the same reason), output complete, output read
     const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = kfull0 + 8 * kStages, vfull0 = kempty0 + 8 * kStages,
-                   vempty0 = vfull0 + 8 * kStages, bP0 = vempty0 + 8 * kStages, bQ = bP0 + 16, bO = bQ + 8, bOfree = bO + 8;
+                   vempty0 = vfull0 + 8 * kStages, bP0 = vempty0 + 8 * kStages, bQ0 = bP0 + 16, bO = bQ0 + 16, bOfree = bO + 8;
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
@@ -285,9 +302,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             mbar_init(vempty0 + 8 * s, 1);
         }
         for (int s = 0; s < 2; ++s) mbar_init(bP0 + 8 * s, kSoftmaxThreads / 32);  // one arrival per softmax warp
-        mbar_init(bQ, kSoftmaxThreads / 32);
+        for (int s = 0; s < kQBufs; ++s) mbar_init(bQ0 + 8 * s, kIoThreads / 32);  // one arrival per in/out warp
         mbar_init(bO, 1);
-        mbar_init(bOfree, kSoftmaxThreads / 32);
+        mbar_init(bOfree, kIoThreads / 32);
         fence_mbar_init();
     }
     if (warp == 5) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -310,153 +327,195 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     // The CTA is persistent: every role walks the same item sequence; T counts key tiles over all items
     // and fixes the phase of every per-tile barrier; `round` fixes the phase of the per-item ones.
-    if (warp == 4) {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            WorkItem w;
-            int      T  = 0;
-            bool     ok = true;
-            PROF_VARS;
-            PROF_START();
-            for (int round = 0; ok && work_item(p, round, w); ++round) {
-                const int kvh = w.head / p.gqa;
-                for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                    const int      st = T % kStages;
-                    const uint32_t ph = ((T / kStages) - 1) & 1;
-                    PROF_STOP(0);
-                    if (T >= kStages && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
-                    PROF_STOP(1);
-                    mbar_expect_tx(kfull0 + 8 * st, kKvBytes);
-                    tma_load_5d(sK0 + st * kKvBytes, &map_k, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
-                    PROF_STOP(0);
-                    if (T >= kStages && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
-                    PROF_STOP(2);
-                    mbar_expect_tx(vfull0 + 8 * st, kKvBytes);
-                    tma_load_5d(sV0 + st * kKvBytes, &map_v, vfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
-                }
-                if (aborted()) break;
-            }
-            PROF_STOP(0);
-            PROF_FLUSH(0, 3);  // 0 issue, 1 wait K stage free, 2 wait V stage free
+    if (warp >= 8) {
+        // ------------------------------------------------------------------ in/out warps: Q tiles in, results out
+        // One thread per query row, as in the softmax warps (warp 8+i may touch TMEM lanes 32i..32i+31).  They keep
+        // the Q tiles of the next two items in shared memory and read each finished output out of TMEM, so that the
+        // softmax warps go from the last tile of one item straight to the first tile of the next.
+        regs_give<kRegsIo>();
+        const int      row   = tid - (kThreadsPf - kIoThreads);
+        const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);
+        {
+            const uint32_t one2 = 0x3C003C00u;
+            for (int i = row; i < kOnesBytes / 16; i += kIoThreads)
+                *reinterpret_cast<uint4 *>(smem_gen + (sOnes - smem_base) + i * 16) = make_uint4(one2, one2, one2, one2);
         }
-    } else if (warp == 5) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc_f16(kKeys, false), idesc_pv = idesc_f16(kHeadDim + 16, true);
-            // Descriptors are built once; a ring stage is selected by adding its distance to the address field
-            // (and, for V, taking it off the distance to the tile of ones).
-            uint64_t dQ[4], dK[4], dV[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                dQ[k] = smem_desc_sw128(sQ + 32 * k);
-                dK[k] = smem_desc_sw128(sK0 + 32 * k);
-                dV[k] = smem_desc_sw128_mn(sV0 + 2048 * k, sOnes - sV0);
-            }
-            constexpr uint64_t kStage  = kKvBytes >> 4;
-            constexpr uint64_t kVStage = kStage - (kStage << 16);
-            PROF_VARS;
-            // S = Q K^T of global tile T into score buffer T % 2: four k-steps of 16 along head_dim, 32 bytes each
-            // inside the swizzle atom.  The buffer last held the weights of tile T-2; the tensor pipe executes in
-            // issue order, so issuing this behind P.V of tile T-2 is all the protection they need.
-            auto issue_qk = [&](int T) {
-                const int st = T % kStages, sb = T & 1;
-                PROF_STOP(0);
-                if (!mbar_wait_bounded(kfull0 + 8 * st, (T / kStages) & 1)) return false;
-                PROF_STOP(1);
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < 4; ++k) tc_mma_f16(tmem + kSCol + kKeys * sb, dQ[k], dK[k] + st * kStage, idesc_qk, k > 0);
-                tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
-                return true;
-            };
-            WorkItem w;
-            int      T  = 0;
-            bool     ok = true;
-            PROF_START();
-            for (int round = 0; ok && work_item(p, round, w); ++round) {
-                // the item's Q tile is in place: scores of its first two tiles
-                PROF_STOP(0);
-                if (!mbar_wait_bounded(bQ, round & 1)) { give_up(); break; }
-                PROF_STOP(2);
-                if (!issue_qk(T) || (w.n_tiles > 1 && !issue_qk(T + 1))) { give_up(); break; }
-                // the previous item's result has been read out of TMEM: its columns may be overwritten
-                if (round > 0 && !mbar_wait_bounded(bOfree, (round - 1) & 1)) { give_up(); break; }
-                for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                    const int st = T % kStages;
-                    PROF_STOP(0);
-                    if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kStages) & 1)) { give_up(); ok = false; break; }
-                    PROF_STOP(3);
-                    if (!mbar_wait_bounded(bP0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
-                    PROF_STOP(4);
-                    PROF_TRACE(2, T);
-                    tc_fence_after();
-                    // O += P V and row sums += P 1 in one instruction per 16 keys: N = 80, columns 64-79 of the B
-                    // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, at the start of
-                    // the tile's score buffer.
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dV[k] + st * kVStage, idesc_pv, j > 0 || k > 0);
-                    tc_commit(vempty0 + 8 * st);  // P.V has retired: the V stage may be refilled, the accumulators are at rest
-                    if (j + 1 == w.n_tiles) tc_commit(bO);  // the item's output is complete
-                    // scores two tiles ahead, into the buffer whose weights P.V has just been told to read
-                    if (j + 2 < w.n_tiles && !issue_qk(T + 2)) { give_up(); ok = false; break; }
-                    PROF_TRACE(3, T);
-                }
-                if (aborted()) break;
-            }
-            PROF_STOP(0);
-            PROF_FLUSH(4, 5);  // 4 issue, 5 wait K tile, 6 wait Q / score buffer, 7 wait V tile, 8 wait P
-        }
-    } else {
-        // ------------------------------------------------------------------ softmax warps: one thread per query row
-        const int      row   = tid;                                    // == TMEM lane; warp w may only touch lanes 32w..32w+31
-        const uint32_t t_row = tmem + ((uint32_t) (32 * warp) << 16);  // this warp's lane quarter
-        uint8_t * const q_dst = smem_gen + row * 128;
-
         // this thread's Q row: f32 from memory, f16 into eight 16-byte chunks at their swizzled places
-        auto load_q = [&](const WorkItem & w, float4 (&qv)[16]) {
-            const int qpos = w.q0 + row;
-            if (qpos < p.n_q) {
-                const float4 * src = reinterpret_cast<const float4 *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) w.head * p.q_nb2 +
-                                                                      (size_t) w.batch * p.q_nb3);
+        auto load_q = [&](const WorkItem & w, int buf) {
+            uint8_t * const q_dst = smem_gen + buf * kQBytes + row * 128;
+            const int       qpos  = w.q0 + row;
+            const float4 *  src   = reinterpret_cast<const float4 *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) w.head * p.q_nb2 +
+                                                                  (size_t) w.batch * p.q_nb3);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) qv[i] = src[i];
-            } else {
+            for (int h = 0; h < 2; ++h) {
+                float4 qv[8];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        };
-        auto store_q = [&](const float4 (&qv)[16]) {
+                for (int i = 0; i < 8; ++i) qv[i] = qpos < p.n_q ? src[8 * h + i] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                *reinterpret_cast<uint4 *>(q_dst + ((c ^ (row & 7)) << 4)) =
-                    make_uint4(pack_half2(qv[2 * c].x, qv[2 * c].y), pack_half2(qv[2 * c].z, qv[2 * c].w),
-                               pack_half2(qv[2 * c + 1].x, qv[2 * c + 1].y), pack_half2(qv[2 * c + 1].z, qv[2 * c + 1].w));
+                for (int c = 0; c < 4; ++c) {
+                    *reinterpret_cast<uint4 *>(q_dst + (((4 * h + c) ^ (row & 7)) << 4)) =
+                        make_uint4(pack_half2(qv[2 * c].x, qv[2 * c].y), pack_half2(qv[2 * c].z, qv[2 * c].w),
+                                   pack_half2(qv[2 * c + 1].x, qv[2 * c + 1].y), pack_half2(qv[2 * c + 1].z, qv[2 * c + 1].w));
+                }
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bQ);
+            if (lane == 0) mbar_arrive(bQ0 + 8 * buf);
         };
-
         WorkItem w, wn;
-        bool     have = work_item(p, 0, w);
-        {
-            const uint32_t one2 = 0x3C003C00u;
-            for (int i = tid; i < kOnesBytes / 16; i += kSoftmaxThreads)
-                *reinterpret_cast<uint4 *>(smem_gen + (sOnes - smem_base) + i * 16) = make_uint4(one2, one2, one2, one2);
-            if (have) {
-                float4 qv[16];
-                load_q(w, qv);
-                store_q(qv);
+        for (int r = 0; r < kQBufs; ++r)
+            if (work_item(p, r, wn)) load_q(wn, r);
+        for (int round = 0; work_item(p, round, w) && !aborted(); ++round) {
+            if (!mbar_wait_bounded(bO, round & 1)) { give_up(); break; }
+            tc_fence_after();
+            const int   qpos = w.q0 + row;
+            const bool  live = qpos < p.n_q;
+            const float l    = tmem_ld1(t_row + kOCol + kHeadDim);  // sum of exactly the rounded weights the tensor core used
+            const float inv  = l > 0.0f ? 1.0f / l : 0.0f;
+            float4 *    out  = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + w.head) * kHeadDim);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t r[32];
+                tmem_ld32_nowait(t_row + kOCol + 32 * h, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) pin(r[i]);
+                if (h == 1) {  // both halves are in registers: the columns go back to the tensor core
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bOfree);
+                }
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        out[8 * h + i] = make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
+                                                     __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+                }
+            }
+            // every Q.K^T of this item retired before its output was complete: its Q buffer takes the item after next
+            if (work_item(p, round + kQBufs, wn)) load_q(wn, round % kQBufs);
+        }
+    } else if (warp >= 4) {
+        regs_give<kRegsControl>();
+        if (warp == 4) {
+            // -------------------------------------------------------------- producer
+            if (lane == 0) {
+                WorkItem w;
+                int      T  = 0;
+                bool     ok = true;
+                PROF_VARS;
+                PROF_START();
+                for (int round = 0; ok && work_item(p, round, w); ++round) {
+                    const int kvh = w.head / p.gqa;
+                    for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
+                        const int      st = T % kStages;
+                        const uint32_t ph = ((T / kStages) - 1) & 1;
+                        PROF_STOP(0);
+                        if (T >= kStages && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        PROF_STOP(1);
+                        mbar_expect_tx(kfull0 + 8 * st, kKvBytes);
+                        tma_load_5d(sK0 + st * kKvBytes, &map_k, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
+                        PROF_STOP(0);
+                        if (T >= kStages && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        PROF_STOP(2);
+                        mbar_expect_tx(vfull0 + 8 * st, kKvBytes);
+                        tma_load_5d(sV0 + st * kKvBytes, &map_v, vfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
+                    }
+                    if (aborted()) break;
+                }
+                PROF_STOP(0);
+                PROF_FLUSH(0, 3);  // 0 issue, 1 wait K stage free, 2 wait V stage free
+            }
+        } else if (warp == 5) {
+            // -------------------------------------------------------------- MMA issuer
+            if (lane == 0) {
+                constexpr uint32_t idesc_qk = idesc_f16(kKeys, false), idesc_pv = idesc_f16(kHeadDim + 16, true);
+                // Descriptors are built once (the thread lives on 40 registers); a k-step, a ring stage or a Q buffer is
+                // selected by adding its distance to the address field (for V, a stage's distance also comes off the
+                // distance to the tile of ones).
+                const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK0), dV = smem_desc_sw128_mn(sV0, sOnes - sV0);
+                constexpr uint64_t kStepQK = 32 >> 4, kStepV = 2048 >> 4;  // 16 of head_dim inside the swizzle atom; 16 keys
+                constexpr uint64_t kStage  = kKvBytes >> 4;
+                constexpr uint64_t kVStage = kStage - (kStage << 16);
+                constexpr uint64_t kQBuf   = kQBytes >> 4;
+                PROF_VARS;
+                // Q.K^T runs two tiles ahead of P.V, across item boundaries: `q` walks the same item sequence as the
+                // P.V loop below.  S of global tile Tq goes into score buffer Tq % 2: four k-steps of 16 along
+                // head_dim, 32 bytes each inside the swizzle atom.  The buffer last held the weights of tile Tq-2; the
+                // tensor pipe executes in issue order, so issuing this behind P.V of tile Tq-2 is all the protection
+                // they need.
+                WorkItem wq;
+                int      rq = 0, jq = 0, Tq = 0;
+                bool     have_q = work_item(p, 0, wq);
+                auto issue_qk = [&]() {
+                    if (!have_q) return true;
+                    PROF_STOP(0);
+                    if (jq == 0 && !mbar_wait_bounded(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) return false;  // the item's Q tile is in place
+                    PROF_STOP(2);
+                    const int st = Tq % kStages, sb = Tq & 1;
+                    if (!mbar_wait_bounded(kfull0 + 8 * st, (Tq / kStages) & 1)) return false;
+                    PROF_STOP(1);
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, k > 0);
+                    tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
+                    ++Tq;
+                    if (++jq == wq.n_tiles) {
+                        jq     = 0;
+                        have_q = work_item(p, ++rq, wq);
+                    }
+                    return true;
+                };
+                WorkItem w;
+                int      T  = 0;
+                bool     ok = true;
+                PROF_START();
+                if (!issue_qk() || !issue_qk()) { give_up(); ok = false; }
+                for (int round = 0; ok && work_item(p, round, w); ++round) {
+                    for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
+                        const int st = T % kStages;
+                        PROF_STOP(0);
+                        if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kStages) & 1)) { give_up(); ok = false; break; }
+                        PROF_STOP(3);
+                        if (!mbar_wait_bounded(bP0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
+                        PROF_STOP(4);
+                        // the previous item's result has been read out of TMEM: its columns may be overwritten
+                        if (j == 0 && round > 0 && !mbar_wait_bounded(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
+                        PROF_STOP(2);
+                        PROF_TRACE(2, T);
+                        tc_fence_after();
+                        // O += P V and row sums += P 1 in one instruction per 16 keys: N = 80, columns 64-79 of the B
+                        // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, at the start of
+                        // the tile's score buffer.
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, j > 0 || k > 0);
+                        tc_commit(vempty0 + 8 * st);  // P.V has retired: the V stage may be refilled, the accumulators are at rest
+                        if (j + 1 == w.n_tiles) tc_commit(bO);  // the item's output is complete
+                        // scores two tiles ahead, into the buffer whose weights P.V has just been told to read
+                        if (!issue_qk()) { give_up(); ok = false; break; }
+                        PROF_TRACE(3, T);
+                    }
+                    if (aborted()) break;
+                }
+                PROF_STOP(0);
+                PROF_FLUSH(4, 5);  // 4 issue, 5 wait K tile, 6 wait Q / output read, 7 wait V tile, 8 wait P
             }
         }
-        int  T  = 0;
-        bool ok = true;
+    } else {
+        // ------------------------------------------------------------------ softmax warps: one thread per query row
+        regs_take<kRegsSoftmax>();
+        const int      row   = tid;                                    // == TMEM lane; warp w may only touch lanes 32w..32w+31
+        const uint32_t t_row = tmem + ((uint32_t) (32 * warp) << 16);  // this warp's lane quarter
+
+        WorkItem w;
+        int      T  = 0;
+        bool     ok = true;
         PROF_VARS;
         PROF_START();
-        for (int round = 0; have && ok; ++round) {
+        for (int round = 0; ok && work_item(p, round, w); ++round) {
             const int  qpos  = w.q0 + row;
-            const bool live  = qpos < p.n_q;
             const int  limit = min(qpos + p.causal_offset, p.n_kv - 1);  // last key this row may see
             // last key any row of this warp may see (rows beyond n_q compute on zeros and are not stored)
             const int  warp_limit = min(w.q0 + 32 * warp + 31 + p.causal_offset, p.n_kv - 1);
@@ -542,52 +601,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_STOP(3);
             }
             if (!ok || aborted()) break;
-            // item done.  Every Q.K^T of this item retired before its last scores were read, so the next item's Q
-            // tile goes in first (its first Q.K^T then runs while this item's result is read out); the output
-            // columns are handed back to the tensor core once they have been read.
-            const bool have_next = work_item(p, round + 1, wn);
-            if (have_next) {
-                float4 qv[16];
-                load_q(wn, qv);
-                store_q(qv);
-            }
-            PROF_STOP(6);
-            if (!mbar_wait_bounded(bO, round & 1)) { give_up(); break; }
-            PROF_STOP(4);
-            // warp-collective TMEM reads by every lane; only rows that exist are stored
-            tc_fence_after();
-            const float l   = tmem_ld1(t_row + kOCol + kHeadDim);  // sum of exactly the rounded weights the tensor core used
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            float4 *    out = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + w.head) * kHeadDim);
-            float       o[64];
-            {
-                uint32_t r[64];
-                tmem_ld32_nowait(t_row + kOCol, r);
-                tmem_ld32_nowait(t_row + kOCol + 32, r + 32);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    pin(r[i]);
-                    o[i] = __uint_as_float(r[i]) * inv;
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bOfree);
-            if (live) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) out[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-            }
-            PROF_STOP(5);
             PROF_COUNT(9, 1);
-            have = have_next;
-            w    = wn;
         }
-        // 0 other, 1 wait S, 2 softmax blocks, 3 store wait + signal, 4 wait O, 5 read-out, 6 next Q, 7 tiles, 8 passes, 9 items
-        if (lane == 0) PROF_FLUSH(9 + 0, 12);  // 10 wait for a block of scores, 11 block maximum
+        // 0 other, 1 wait S, 2 softmax blocks, 3 store wait + signal, 7 tiles, 9 items, 10 wait for the scores' load, 11 tile maximum
+        if (lane == 0) PROF_FLUSH(9 + 0, 12);
     }
 
-    // common exit: tensor-core work has been waited for by the softmax warps; release TMEM
+    // common exit: every role has left its loop; release TMEM
     tc_fence_before();
     __syncthreads();
     if (warp == 5) {
@@ -675,7 +695,7 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     const long long items = (long long) p.n_qtiles * p.n_heads * p.n_batch;
     VOX_REQUIRE(items < (1LL << 30), VOX_ATTN_INVALID_ARGUMENT, "too many query tiles");
     p.n_items = (int) items;
-    // persistent CTAs, two per SM (100 KB of shared memory and 256 TMEM columns each)
+    // persistent CTAs, two per SM (105 KB of shared memory, 256 TMEM columns and half the register file each)
     dim3 grid((unsigned) std::min<long long>(items, 2LL * e->sm_count));
     launch_pdl(prefill_tc_kernel, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
     return check_launch(e, "prefill_tc_kernel");
