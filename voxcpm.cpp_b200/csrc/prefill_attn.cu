@@ -11,9 +11,11 @@
 // are set up once.  Twelve warps in three warpgroups, which trade registers after launch (setmaxnreg: the launch
 // allots 80 per thread, the softmax group takes 144, the others keep 40 and 56):
 //   warps 0-3  softmax: one thread per query row (row r = TMEM lane r).  Per tile a thread reads its 64 scores
-//              from TMEM (tcgen05.ld), takes their maximum, and writes P = 2^(c*S - m_ref) as packed f16 back into
-//              TMEM (tcgen05.st) over the first half of the scores it has just read: the tensor core takes the
-//              weights from there as the A operand of P.V, so they never pass through shared memory.  On the
+//              from TMEM (tcgen05.ld), takes their maximum, and writes P = 2^(c*S - m_ref) back into TMEM
+//              (tcgen05.st) over the scores it has just read, as two packed-f16 tiles hi + lo (~21 bits: one f16 per
+//              weight measured 2.3e-3 to 5e-3 of the output RMS on random sequences of 512 to 4096 tokens, outside
+//              the 2e-3 parity bound; hi + lo measures under 6e-5): the tensor core takes the weights from there
+//              as the A operand of P.V, so they never pass through shared memory.  On the
 //              diagonal tile a warp skips the 32-column blocks none of its rows can see.  The output row and the
 //              row sums accumulate in TMEM over all tiles (no per-tile read-back); they are rescaled in place only
 //              when a tile's maximum exceeds the reference m_ref by more than 2^8.  These warps do nothing else:
@@ -22,8 +24,8 @@
 //   warp 5     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128).  S = Q.K^T (N=64, 4 k-steps, both
 //              operands in shared memory) goes to one of two score buffers in TMEM (tile T uses buffer T % 2) and
 //              runs two tiles ahead of P.V, across item boundaries, so the scores of tile T+1 are computed while the
-//              softmax of tile T runs.  O += P.V and the row sums come from ONE instruction per 16 keys (N=80,
-//              4 k-steps): P from TMEM, V read MN-major straight from its row-major tile, and a tile of ones
+//              softmax of tile T runs.  O += P.V and the row sums come from ONE instruction per 16 keys and weight
+//              part (N=80, 4 k-steps for hi, 4 for lo): P from TMEM, V read MN-major straight from its row-major tile, and a tile of ones
 //              addressed as columns 64-79 of every V tile, which yields the sums of exactly the rounded weights the
 //              tensor core used.  The tensor pipe executes in issue order, so Q.K^T of tile T+2, issued behind P.V
 //              of tile T, overwrites that tile's weights only once they have been used.  Completion is signalled
@@ -42,6 +44,7 @@
 #include "common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 using namespace vox;
 
@@ -191,6 +194,13 @@ __device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t 
           "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+// 8 columns (16 packed f16 weights)
+__device__ __forceinline__ void tmem_st8_nowait(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st1(uint32_t taddr, float x) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(x)) : "memory");
     tmem_wait_st();
@@ -271,6 +281,8 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
     return true;
 }
 
+// kSplitP: the weights go to the tensor core as hi + lo (two f16 parts, ~21 bits) instead of one f16 (11 bits).
+template <bool kSplitP>
 __global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -491,6 +503,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, j > 0 || k > 0);
+                        if (kSplitP) {  // the low parts of the same weights, behind the high parts in the score buffer
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 32 + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, 1);
+                        }
                         tc_commit(vempty0 + 8 * st);  // P.V has retired: the V stage may be refilled, the accumulators are at rest
                         if (j + 1 == w.n_tiles) tc_commit(bO);  // the item's output is complete
                         // scores two tiles ahead, into the buffer whose weights P.V has just been told to read
@@ -582,15 +599,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         rescale_accumulators(t_row, f);
                     }
                 }
-                // P = 2^(c*S - m_ref) as packed f16 over the first half of the scores just read
+                if (kSplitP) {
+                    // P = 2^(c*S - m_ref) as hi + lo, two packed f16 tiles over the scores just read (hi: columns 0-31,
+                    // lo: columns 32-63).  hi keeps the top 11 bits of the f32 weight (a mask: exact in f16 for every
+                    // weight above 2^-14, and the weights that matter are >= 1 for the row's largest), lo is the
+                    // exact remainder rounded to f16: together ~21 bits, so that the result does not depend on how
+                    // the rounding errors of a few large weights happen to fall against the spread of V.
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t h[16];
+                    for (int g = 0; g < 4; ++g) {
+                        uint32_t hi[8], lo[8];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i]), p.scale_log2, -m_ref)),
-                                          ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), p.scale_log2, -m_ref)));
-                    tmem_st16_nowait(t_s + 16 * c, h);
+                        for (int i = 0; i < 8; ++i) {
+                            const float p0 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), p.scale_log2, -m_ref));
+                            const float p1 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), p.scale_log2, -m_ref));
+                            const float h0 = __uint_as_float(__float_as_uint(p0) & 0xFFFFE000u);
+                            const float h1 = __uint_as_float(__float_as_uint(p1) & 0xFFFFE000u);
+                            hi[i] = pack_half2(h0, h1);
+                            lo[i] = pack_half2(p0 - h0, p1 - h1);
+                        }
+                        tmem_st8_nowait(t_s + 8 * g, hi);
+                        tmem_st8_nowait(t_s + 32 + 8 * g, lo);
+                    }
+                } else {
+                    // P = 2^(c*S - m_ref) as packed f16 over the first half of the scores just read
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t h[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i]), p.scale_log2, -m_ref)),
+                                              ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), p.scale_log2, -m_ref)));
+                        tmem_st16_nowait(t_s + 16 * c, h);
+                    }
                 }
                 PROF_STOP(2);
                 tmem_wait_st();
@@ -679,9 +719,14 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
         if (rc != VOX_ATTN_OK) return rc;
     }
     if (!(e->attr_mask & (1u << 12))) {
-        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPf));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPf));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPf));
         e->attr_mask |= 1u << 12;
     }
+    // Experiment hook: VOX_PREFILL_WEIGHTS=f16 sends the weights as one f16 part (faster; on long sequences of
+    // random data the result then misses the 2e-3 parity bound: 2.6e-3 at 640 keys).  The product path splits them.
+    const char * weights_env = std::getenv("VOX_PREFILL_WEIGHTS");
+    const bool   split_p     = !(weights_env && weights_env[0] == 'f');
     PrefillParams p;
     p.q = static_cast<const uint8_t *>(a->q.data);
     p.q_nb1 = a->q.nb[1]; p.q_nb2 = a->q.nb[2]; p.q_nb3 = a->q.nb[3];
@@ -697,7 +742,8 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     p.n_items = (int) items;
     // persistent CTAs, two per SM (105 KB of shared memory, 256 TMEM columns and half the register file each)
     dim3 grid((unsigned) std::min<long long>(items, 2LL * e->sm_count));
-    launch_pdl(prefill_tc_kernel, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
+    if (split_p) launch_pdl(prefill_tc_kernel<true>, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
+    else launch_pdl(prefill_tc_kernel<false>, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
     return check_launch(e, "prefill_tc_kernel");
 }
 
