@@ -52,6 +52,7 @@ def parse():
     p.add_argument("--rope", action="store_true",
                    help="hand Q and the new K rows over before the rotary embedding: one cos/sin table per step, rotation inside the decode launches")
     p.add_argument("--prefill-shapes", default="512x1,512x8", help="LxB list for --workload prefill")
+    p.add_argument("--prefill-kv", default="f16", choices=["f16", "q8_0"], help="K/V operand type for --workload prefill")
     p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1"],
                    help="serving = the headline line; the others time one more configuration each on one GPU")
     return p.parse_args()
@@ -241,6 +242,16 @@ def run_reference_arm(args, rank, world):
 
 # ------------------------------------------------------------------ other configurations (one GPU)
 
+def q8_0_blocks(x):
+    """ggml q8_0 blocks of a device tensor whose last dimension is a multiple of 32: per block an f16 scale
+    d = amax / 127 and 32 int8 values round(x / d), 34 bytes (synthetic benchmark input only)."""
+    import torch
+    blocks = x.reshape(*x.shape[:-1], x.shape[-1] // 32, 32)
+    d = blocks.abs().amax(dim=-1, keepdim=True) / 127.0
+    qv = torch.where(d > 0, blocks / torch.where(d > 0, d, torch.ones_like(d)), torch.zeros_like(blocks)).round().clamp(-127, 127).to(torch.int8)
+    packed = torch.cat([d.half().view(torch.uint8), qv.view(torch.uint8)], dim=-1)
+    return packed.reshape(*x.shape[:-1], x.shape[-1] // 32 * 34).contiguous()
+
 def aux_workload(args, pkg, torch):
     """Times the other configurations: causal prefill (512 tokens, 24 layers, batch 1 and 8), the long-form decode
     sweep (KV 1k-8k, batch 1 and 32, f16 and q8_0, 24+6 layers) and single-stream decode at KV 256 (24 layers).
@@ -275,6 +286,8 @@ def aux_workload(args, pkg, torch):
             q = torch.randn((layers, B, H, L, D), device="cuda", generator=gen).half().float()
             k = torch.randn((layers, B, HK, L, D), device="cuda", generator=gen).half()
             v = torch.randn((layers, B, HK, L, D), device="cuda", generator=gen).half()
+            if args.prefill_kv == "q8_0":
+                k, v = q8_0_blocks(k.float()), q8_0_blocks(v.float())
             o = torch.empty((layers, B, L, H, D), device="cuda")
             for l in range(layers):  # warm-up outside capture (attribute set-up, descriptors)
                 eng.prefill(q[l], k[l], v[l], dst=o[l])
@@ -285,7 +298,7 @@ def aux_workload(args, pkg, torch):
                     eng.prefill(q[l], k[l], v[l], dst=o[l])
             ms = timed(graph.replay, 20, cold=False)
             flops = layers * B * 4.0 * H * D * L * (L + 1) / 2
-            out["results"].append({"config": f"prefill L={L} B={B} x {layers} layers", "ms": ms, "us_per_layer": ms * 1e3 / layers,
+            out["results"].append({"config": f"prefill L={L} B={B} x {layers} layers, {args.prefill_kv} K/V", "ms": ms, "us_per_layer": ms * 1e3 / layers,
                                    "tflops_causal_useful": flops / (ms * 1e-3) / 1e12,
                                    "frac_of_measured_bf16_peak": flops / (ms * 1e-3) / 1e12 / tens})
     else:

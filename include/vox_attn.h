@@ -121,7 +121,9 @@ int vox_attn_forward_host(vox_engine * e, const vox_attn_args * a, void * stream
 
 /* Causal prefill without a materialised mask (the mask MiniCPMModel::create_causal_mask builds,
  * src/minicpm.cpp:602-620, is implied: key j visible to query i iff j <= i + n_kv - n_q).
- * q [D, n_q, H, B] f32; k, v [D, n_kv, HK, B] f16; runs on tcgen05/TMEM. */
+ * q [D, n_q, H, B] f32; k, v [D, n_kv, HK, B] f16, or q8_0 when a workspace of
+ * vox_attn_prefill_workspace_bytes is passed (the blocks are expanded to f16 there first): runs on
+ * tcgen05/TMEM.  f32 K/V, unaligned strides, and q8_0 K/V without a workspace take the general kernel. */
 int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes,
                      void * stream);
 size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a);

@@ -132,6 +132,43 @@ def test_prefill_long_random_sequences(B, L, past, engine, oracle, vo):
         assert rel_err(out[b:b + 1].cpu().numpy(), o_ref) < TOL["f16"]
 
 
+@pytest.mark.parametrize("B, L, past", [(3, 300, 20), (8, 512, 0)])
+def test_prefill_over_a_q8_0_cache(B, L, past, engine, oracle, vo):
+    """Causal prefill whose K/V operands are q8_0 (a quantised cache): the blocks are expanded to f16 in the caller's
+    workspace and the tensor-core kernel runs on those.  Checked in full against an f32 softmax over exactly the values
+    the blocks hold, and one sequence against the oracle's accurate path; tolerance 1e-2 of the output RMS.  Without a
+    workspace the general kernel takes the call and gives the same result within the tolerance."""
+    import ctypes
+    import torch
+    from voxcpm_cpp_b200 import binding
+    rng = np.random.default_rng(31)
+    q = rng.standard_normal((B, H, L, D)).astype(np.float16).astype(np.float32)
+    k = rng.standard_normal((B, HK, past + L, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, past + L, D)).astype(np.float32)
+    kq, vq = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+    kf, vf = oracle.dequantize_q8_0(kq), oracle.dequantize_q8_0(vq)
+    qd, kd, vd = dev(q), dev(kq), dev(vq)
+    out = engine.prefill(qd, kd, vd)
+    engine.sync_status()
+    a = binding.attn_args(qd, kd, vd, out, None, 0.125)
+    assert binding.lib().vox_attn_prefill_workspace_bytes(ctypes.byref(a)) >= 2 * B * HK * (past + L) * D * 2
+    kk, vv = dev(kf).repeat_interleave(H // HK, dim=1), dev(vf).repeat_interleave(H // HK, dim=1)
+    s = torch.einsum("bhqd,bhkd->bhqk", qd, kk) * 0.125
+    visible = torch.arange(past + L, device="cuda")[None, :] <= (torch.arange(L, device="cuda")[:, None] + past)
+    ref = torch.einsum("bhqk,bhkd->bqhd", torch.softmax(s.masked_fill(~visible, float("-inf")), dim=-1), vv)
+    rms = ref.pow(2).mean().sqrt().item()
+    assert (out - ref).abs().max().item() / rms < TOL["q8_0"]
+    mask = oracle.causal_mask(np.arange(past, past + L), past + L)[None, None]
+    o_ref = oracle.attn(q[B - 1:], kq[B - 1:], vq[B - 1:], mask, kv_type=vo.Q8_0, path=vo.PATH_ROW_F32)
+    assert rel_err(out[B - 1:].cpu().numpy(), o_ref) < TOL["q8_0"]
+    # no workspace: the general kernel
+    out2 = torch.empty_like(out)
+    a2 = binding.attn_args(qd, kd, vd, out2, None, 0.125)
+    assert binding.lib().vox_attn_prefill(engine.h, ctypes.byref(a2), ctypes.c_void_p(0), 0, None) == 0
+    engine.sync_status()
+    assert (out2 - ref).abs().max().item() / rms < TOL["q8_0"]
+
+
 def test_locdit_patch_of_256_streams(engine, oracle, vo):
     import torch
     S, L, seq = 256, 8, 9

@@ -93,7 +93,13 @@ constexpr int kTmemCols  = 256;
 constexpr int kSCol      = 0;              // S: 2 x 64 columns
 constexpr int kOCol      = 128;            // O: 64 columns, row sums: 16 columns behind them
 constexpr int kOnesBytes = kKvBytes;       // a tile of ones, addressed as columns 64-79 of every V tile (any layout: every element is 1)
-constexpr int kSmemPf    = kQBufs * kQBytes + 2 * kStages * kKvBytes + kOnesBytes + 1024;  // Q x 2, K ring, V ring, ones
+// With kVLo (K/V expanded from q8_0) a K or V stage holds two tiles, the f16 values and what their rounding left over, and
+// the rings are two stages deep, so that two CTAs still fit on an SM.
+constexpr int stages_of(bool v_lo) { return v_lo ? 2 : kStages; }
+constexpr int v_stage_bytes(bool v_lo) { return v_lo ? 2 * kKvBytes : kKvBytes; }
+constexpr int smem_pf(bool v_lo) {  // Q x 2, K ring, V ring, ones
+    return kQBufs * kQBytes + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + 1024;
+}
 
 struct PrefillParams {
     const uint8_t * q;
@@ -282,9 +288,13 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
 }
 
 // kSplitP: the weights go to the tensor core as hi + lo (two f16 parts, ~21 bits) instead of one f16 (11 bits).
-template <bool kSplitP>
+// kVLo: K and V come as two f16 tiles each, value + remainder (q8_0 blocks expanded exactly); the remainders take a
+// second Q.K^T pass and a third P.V pass.
+template <bool kSplitP, bool kVLo>
 __global__ void __launch_bounds__(kThreadsPf, 2)
-prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                  const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo, const PrefillParams p) {
+    constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo);
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[4 * kStages + 6];
     __shared__ uint32_t tmem_base_slot;
@@ -292,7 +302,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBytes, sV0 = sK0 + kStages * kKvBytes, sOnes = sV0 + kStages * kKvBytes;
+    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBytes, sV0 = sK0 + kSt * kVBytes, sOnes = sV0 + kSt * kVBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -323,6 +333,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     if (tid == kSoftmaxThreads) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+        if (kVLo) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_klo)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_vlo)) : "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -420,18 +434,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 for (int round = 0; ok && work_item(p, round, w); ++round) {
                     const int kvh = w.head / p.gqa;
                     for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                        const int      st = T % kStages;
-                        const uint32_t ph = ((T / kStages) - 1) & 1;
+                        const int      st = T % kSt;
+                        const uint32_t ph = ((T / kSt) - 1) & 1;
                         PROF_STOP(0);
-                        if (T >= kStages && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        if (T >= kSt && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
                         PROF_STOP(1);
-                        mbar_expect_tx(kfull0 + 8 * st, kKvBytes);
-                        tma_load_5d(sK0 + st * kKvBytes, &map_k, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
+                        mbar_expect_tx(kfull0 + 8 * st, kVBytes);
+                        tma_load_5d(sK0 + st * kVBytes, &map_k, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
+                        if (kVLo) tma_load_5d(sK0 + st * kVBytes + kKvBytes, &map_klo, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
                         PROF_STOP(0);
-                        if (T >= kStages && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        if (T >= kSt && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
                         PROF_STOP(2);
-                        mbar_expect_tx(vfull0 + 8 * st, kKvBytes);
-                        tma_load_5d(sV0 + st * kKvBytes, &map_v, vfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
+                        mbar_expect_tx(vfull0 + 8 * st, kVBytes);
+                        tma_load_5d(sV0 + st * kVBytes, &map_v, vfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
+                        if (kVLo) tma_load_5d(sV0 + st * kVBytes + kKvBytes, &map_vlo, vfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
                     }
                     if (aborted()) break;
                 }
@@ -447,8 +463,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // distance to the tile of ones).
                 const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK0), dV = smem_desc_sw128_mn(sV0, sOnes - sV0);
                 constexpr uint64_t kStepQK = 32 >> 4, kStepV = 2048 >> 4;  // 16 of head_dim inside the swizzle atom; 16 keys
-                constexpr uint64_t kStage  = kKvBytes >> 4;
-                constexpr uint64_t kVStage = kStage - (kStage << 16);
+                constexpr uint64_t kVStep  = kVBytes >> 4;
+                constexpr uint64_t kStage  = kVStep;  // K stages are as large as V stages
+                const uint64_t     dKlo    = smem_desc_sw128(sK0 + kKvBytes);
+                constexpr uint64_t kVStage = kVStep - (kVStep << 16);
+                // the remainder tile of a V stage: 64 columns, no tile of ones behind it
+                const uint64_t     dVlo     = smem_desc_sw128_mn(sV0 + kKvBytes, 16);
+                constexpr uint32_t idesc_lo = idesc_f16(kHeadDim, true);
                 constexpr uint64_t kQBuf   = kQBytes >> 4;
                 PROF_VARS;
                 // Q.K^T runs two tiles ahead of P.V, across item boundaries: `q` walks the same item sequence as the
@@ -464,13 +485,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     PROF_STOP(0);
                     if (jq == 0 && !mbar_wait_bounded(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) return false;  // the item's Q tile is in place
                     PROF_STOP(2);
-                    const int st = Tq % kStages, sb = Tq & 1;
-                    if (!mbar_wait_bounded(kfull0 + 8 * st, (Tq / kStages) & 1)) return false;
+                    const int st = Tq % kSt, sb = Tq & 1;
+                    if (!mbar_wait_bounded(kfull0 + 8 * st, (Tq / kSt) & 1)) return false;
                     PROF_STOP(1);
                     tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, k > 0);
+                    if (kVLo) {  // what rounding K to f16 left over
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + k * kStepQK, dKlo + st * kStage + k * kStepQK, idesc_qk, 1);
+                    }
                     tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
                     ++Tq;
                     if (++jq == wq.n_tiles) {
@@ -486,9 +512,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 if (!issue_qk() || !issue_qk()) { give_up(); ok = false; }
                 for (int round = 0; ok && work_item(p, round, w); ++round) {
                     for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                        const int st = T % kStages;
+                        const int st = T % kSt;
                         PROF_STOP(0);
-                        if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kStages) & 1)) { give_up(); ok = false; break; }
+                        if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kSt) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(3);
                         if (!mbar_wait_bounded(bP0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(4);
@@ -507,6 +533,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                             for (int k = 0; k < 4; ++k)
                                 tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 32 + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, 1);
+                        }
+                        if (kVLo) {  // what rounding V to f16 left over, against the high parts of the weights
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dVlo + st * kVStep + k * kStepV, idesc_lo, 1);
                         }
                         tc_commit(vempty0 + 8 * st);  // P.V has retired: the V stage may be refilled, the accumulators are at rest
                         if (j + 1 == w.n_tiles) tc_commit(bO);  // the item's output is complete
@@ -544,7 +575,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
                 const int sb = T & 1;
                 PROF_STOP(0);
-                if (!mbar_wait_bounded(kempty0 + 8 * (T % kStages), (T / kStages) & 1)) { give_up(); ok = false; break; }
+                if (!mbar_wait_bounded(kempty0 + 8 * (T % kSt), (T / kSt) & 1)) { give_up(); ok = false; break; }
                 PROF_STOP(1);
                 PROF_COUNT(7, 1);
                 if (tid == 0) PROF_TRACE(0, T);
@@ -595,7 +626,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         const float f = raise ? ex2_approx(m_ref - cmax) : 1.0f;
                         if (raise) m_ref = cmax;
                         // the accumulators are at rest once P.V of the previous tile has retired
-                        if (!mbar_wait_bounded(vempty0 + 8 * ((T - 1) % kStages), ((T - 1) / kStages) & 1)) { give_up(); ok = false; break; }
+                        if (!mbar_wait_bounded(vempty0 + 8 * ((T - 1) % kSt), ((T - 1) / kSt) & 1)) { give_up(); ok = false; break; }
                         rescale_accumulators(t_row, f);
                     }
                 }
@@ -656,6 +687,66 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     }
 }
 
+// q8_0 K/V (34-byte blocks: f16 scale + 32 int8, third_party/ggml/src/ggml-common.h:221-224) are expanded once
+// per call into f16 tiles in the caller's workspace, [B][HK][n_kv][64] contiguous, and the tensor-core kernel runs
+// on those.  One thread per block of 32 values: d * q is exact in f32 (11 + 7 bits) and rounded to f16 once.
+struct DequantParams {
+    const uint8_t * src[2];
+    __half *        dst[2];
+    __half *        rest[2];  // what rounding to f16 leaves over (exact: d * q has at most 18 significant bits)
+    size_t          nb1[2], nb2[2], nb3[2];
+    int             n_kv, n_kvh, n_batch;
+};
+__global__ void __launch_bounds__(256) q8_0_to_f16_kernel(const DequantParams p) {
+    const long long n_blocks = 2LL * p.n_kv * p.n_kvh * p.n_batch;  // two blocks per 64-wide row
+    const bool      is_v     = blockIdx.y != 0;                     // 0: K, 1: V
+    const uint8_t * src      = is_v ? p.src[1] : p.src[0];
+    __half *        dst      = is_v ? p.dst[1] : p.dst[0];
+    const size_t    nb1 = is_v ? p.nb1[1] : p.nb1[0], nb2 = is_v ? p.nb2[1] : p.nb2[0], nb3 = is_v ? p.nb3[1] : p.nb3[0];
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks; i += (long long) gridDim.x * blockDim.x) {
+        const int       blk = (int) (i & 1);
+        const long long row = i >> 1;
+        const int       pos = (int) (row % p.n_kv);
+        const int       kvh = (int) ((row / p.n_kv) % p.n_kvh);
+        const int       b   = (int) (row / ((long long) p.n_kv * p.n_kvh));
+        const uint16_t * s  = reinterpret_cast<const uint16_t *>(src + (size_t) pos * nb1 + (size_t) kvh * nb2 + (size_t) b * nb3 +
+                                                                 (size_t) blk * 34);
+        const float d = __half2float(__ushort_as_half(s[0]));
+        uint32_t    out[16], rest[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint16_t two = s[1 + j];
+            const float    x0 = d * (float) (signed char) (two & 0xff), x1 = d * (float) (signed char) (two >> 8);
+            const __half2  h  = __floats2half2_rn(x0, x1);
+            out[j]  = *reinterpret_cast<const uint32_t *>(&h);
+            rest[j] = pack_half2(x0 - __low2float(h), x1 - __high2float(h));
+        }
+        uint4 * o = reinterpret_cast<uint4 *>(dst + (size_t) row * 64 + (size_t) blk * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+        uint4 * r = reinterpret_cast<uint4 *>((is_v ? p.rest[1] : p.rest[0]) + (size_t) row * 64 + (size_t) blk * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] = make_uint4(rest[4 * j], rest[4 * j + 1], rest[4 * j + 2], rest[4 * j + 3]);
+    }
+}
+
+size_t q8_scratch_bytes(const vox_attn_args * a) {  // one tensor, rounded up so that the second one stays aligned
+    const size_t bytes = (size_t) a->k.ne[1] * (size_t) a->k.ne[2] * (size_t) a->k.ne[3] * 128;
+    return (bytes + 255) & ~(size_t) 255;
+}
+
+// q8_0 K and V of equal shape, whole blocks, rows at even addresses (the blocks are read as 16-bit words)
+bool q8_route_ok(const vox_attn_args * a) {
+    const vox_tensor &k = a->k, &v = a->v;
+    if (k.type != VOX_TYPE_Q8_0 || v.type != VOX_TYPE_Q8_0) return false;
+    if (k.ne[1] != v.ne[1] || k.ne[2] != v.ne[2] || k.ne[3] != v.ne[3]) return false;
+    if (a->q.ne[1] < 1 || k.ne[1] < 1) return false;
+    if ((reinterpret_cast<uintptr_t>(a->q.data) & 15) != 0 || a->q.nb[1] % 16 || a->q.nb[2] % 16 || a->q.nb[3] % 16) return false;
+    for (const vox_tensor * t : {&k, &v})
+        if ((reinterpret_cast<uintptr_t>(t->data) & 1) != 0 || t->nb[1] % 2 || t->nb[2] % 2 || t->nb[3] % 2) return false;
+    return true;
+}
+
 bool tc_route_ok(const vox_attn_args * a) {
     const vox_tensor &k = a->k, &v = a->v;
     if (k.type != VOX_TYPE_F16 || v.type != VOX_TYPE_F16) return false;
@@ -689,13 +780,11 @@ int vox_debug_prefill_profile(unsigned long long * out, int reset) {
 #endif
 
 size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a) {
-    (void) a;
-    return 0;
+    if (!a || !vox_attn_supported(a) || a->mask.data != nullptr) return 0;
+    return q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;  // K, V, and what rounding each to f16 leaves over
 }
 
 int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, void * stream) {
-    (void) workspace;
-    (void) workspace_bytes;
     VOX_REQUIRE(e && a, VOX_ATTN_INVALID_ARGUMENT, "vox_attn_prefill: null argument");
     VOX_REQUIRE(a->mask.data == nullptr, VOX_ATTN_INVALID_ARGUMENT,
                 "vox_attn_prefill implies the causal mask; pass mask.data == NULL (use vox_attn_forward for explicit masks)");
@@ -705,22 +794,58 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
                 (long long) a->q.ne[1]);
     const int    offset = (int) (a->k.ne[1] - a->q.ne[1]);
     cudaStream_t st     = static_cast<cudaStream_t>(stream);
-    if (!tc_route_ok(a)) return launch_generic(e, a, offset, st);  // f32 / q8_0 K/V or unaligned strides
+    // q8_0 K/V: expanded to f16 in the workspace first (without one of the size vox_attn_prefill_workspace_bytes
+    // names, the general kernel takes the call, as it does for f32 K/V and unaligned strides)
+    vox_tensor kf = a->k, vf = a->v;
+    bool       v_lo = false;
+    __half *   lo_data[2] = {nullptr, nullptr};
+    if (q8_route_ok(a) && workspace != nullptr && workspace_bytes >= 4 * q8_scratch_bytes(a) &&
+        (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) {
+        DequantParams dp;
+        const size_t  one = q8_scratch_bytes(a);
+        vox_tensor *  fs[2] = {&kf, &vf};
+        const vox_tensor * qs[2] = {&a->k, &a->v};
+        for (int i = 0; i < 2; ++i) {
+            dp.src[i] = static_cast<const uint8_t *>(qs[i]->data);
+            dp.dst[i] = reinterpret_cast<__half *>(static_cast<uint8_t *>(workspace) + i * one);
+            dp.nb1[i] = qs[i]->nb[1]; dp.nb2[i] = qs[i]->nb[2]; dp.nb3[i] = qs[i]->nb[3];
+            fs[i]->type  = VOX_TYPE_F16;
+            fs[i]->data  = dp.dst[i];
+            fs[i]->nb[0] = 2;
+            fs[i]->nb[1] = 128;
+            fs[i]->nb[2] = (size_t) a->k.ne[1] * 128;
+            fs[i]->nb[3] = (size_t) a->k.ne[1] * (size_t) a->k.ne[2] * 128;
+        }
+        for (int i = 0; i < 2; ++i) dp.rest[i] = lo_data[i] = reinterpret_cast<__half *>(static_cast<uint8_t *>(workspace) + (2 + i) * one);
+        v_lo = true;
+        dp.n_kv = (int) a->k.ne[1]; dp.n_kvh = (int) a->k.ne[2]; dp.n_batch = (int) a->k.ne[3];
+        const long long n_blocks = 2LL * dp.n_kv * dp.n_kvh * dp.n_batch;
+        const unsigned  gx = (unsigned) std::min<long long>((n_blocks + 255) / 256, 8LL * e->sm_count);
+        q8_0_to_f16_kernel<<<dim3(gx, 2), 256, 0, st>>>(dp);
+        int rc = check_launch(e, "q8_0_to_f16_kernel");
+        if (rc != VOX_ATTN_OK) return rc;
+    } else if (!tc_route_ok(a)) {
+        return launch_generic(e, a, offset, st);
+    }
 
-    CUtensorMap    mk, mv;
+    CUtensorMap    mk, mv, mklo, mvlo;
     const uint64_t dims[5] = {64, (uint64_t) a->k.ne[1], (uint64_t) a->k.ne[2], (uint64_t) a->k.ne[3], 1};
     const uint32_t box[5]  = {64, kKeys, 1, 1, 1};
-    const vox_tensor * ts[2] = {&a->k, &a->v};
-    CUtensorMap *      ms[2] = {&mk, &mv};
-    for (int i = 0; i < 2; ++i) {
+    vox_tensor     kl = kf, vl = vf;  // the remainders: same shape and strides as the expanded tensors
+    if (v_lo) { kl.data = lo_data[0]; vl.data = lo_data[1]; }
+    const vox_tensor * ts[4] = {&kf, &vf, &kl, &vl};
+    CUtensorMap *      ms[4] = {&mk, &mv, &mklo, &mvlo};
+    for (int i = 0; i < (v_lo ? 4 : 2); ++i) {
         const uint64_t strides[4] = {ts[i]->nb[1], ts[i]->nb[2], ts[i]->nb[3],
                                      std::max<uint64_t>(ts[i]->nb[3] * (uint64_t) ts[i]->ne[3], 16)};
         int rc = make_tensor_map(e, ms[i], ts[i]->data, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != VOX_ATTN_OK) return rc;
     }
+    if (!v_lo) { mklo = mk; mvlo = mv; }  // not read
     if (!(e->attr_mask & (1u << 12))) {
-        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPf));
-        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPf));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(true)));
         e->attr_mask |= 1u << 12;
     }
     // Experiment hook: VOX_PREFILL_WEIGHTS=f16 sends the weights as one f16 part (faster; on long sequences of
@@ -742,8 +867,9 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     p.n_items = (int) items;
     // persistent CTAs, two per SM (105 KB of shared memory, 256 TMEM columns and half the register file each)
     dim3 grid((unsigned) std::min<long long>(items, 2LL * e->sm_count));
-    if (split_p) launch_pdl(prefill_tc_kernel<true>, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
-    else launch_pdl(prefill_tc_kernel<false>, grid, dim3(kThreadsPf), kSmemPf, st, mk, mv, p);
+    if (v_lo) launch_pdl(prefill_tc_kernel<true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
+    else if (split_p) launch_pdl(prefill_tc_kernel<true, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
+    else launch_pdl(prefill_tc_kernel<false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
     return check_launch(e, "prefill_tc_kernel");
 }
 
