@@ -169,6 +169,52 @@ def test_prefill_over_a_q8_0_cache(B, L, past, engine, oracle, vo):
     assert (out2 - ref).abs().max().item() / rms < TOL["q8_0"]
 
 
+@pytest.mark.parametrize("kv, B, n_q, n_kv, planes", [("f16", 2, 512, 512, 1), ("f16", 2, 200, 320, 2), ("q8_0", 1, 256, 384, 1)])
+def test_forward_with_an_explicit_mask_on_the_tensor_core_kernel(kv, B, n_q, n_kv, planes, engine, oracle, vo):
+    """The operator as the reference calls it for prefill, mask tensor included (src/minicpm.cpp:708-710): from 128
+    queries and keys on, vox_attn_forward sends f16 / q8_0 K/V with an additive f16 mask to the tcgen05 kernel, which
+    reads the mask instead of implying it.  Masks here: the reference's causal one; a random one with finite biases,
+    30 % of the keys hidden, one row that sees nothing (its output is zero) and one that sees its first key only in the
+    last tile, broadcast over heads from two planes.  Checked in full against an f32 softmax, one sequence against the
+    oracle, and the causal case against the implied-mask entry point."""
+    import torch
+    rng = np.random.default_rng(41)
+    q = rng.standard_normal((B, H, n_q, D)).astype(np.float16).astype(np.float32)
+    k = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    if kv == "q8_0":
+        ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+        kf, vf = oracle.dequantize_q8_0(ks), oracle.dequantize_q8_0(vs)
+    else:
+        ks, vs = k.astype(np.float16), v.astype(np.float16)
+        kf, vf = ks.astype(np.float32), vs.astype(np.float32)
+    if n_q == n_kv:
+        mask = np.array(np.broadcast_to(oracle.causal_mask(np.arange(n_kv), n_kv)[None, None], (1, planes, n_q, n_kv)))
+    else:
+        mask = np.where(rng.random((1, planes, n_q, n_kv)) < 0.3, -np.inf, rng.integers(-8, 1, (1, planes, n_q, n_kv)) / 4.0).astype(np.float16)
+        mask[..., 0] = 0.0
+        mask[0, 0, 5, :] = -np.inf                 # sees nothing
+        mask[0, planes - 1, 130, :n_kv - 3] = -np.inf  # first visible key in the last tile
+    qd, kd, vd, md = dev(q), dev(ks), dev(vs), dev(mask)
+    out = engine.forward(qd, kd, vd, md)
+    engine.sync_status()
+    kk, vv = dev(kf).repeat_interleave(H // HK, dim=1), dev(vf).repeat_interleave(H // HK, dim=1)
+    m_full = md.float().repeat(1, H // planes, 1, 1)  # head h reads plane h % planes
+    s = torch.einsum("bhqd,bhkd->bhqk", qd, kk) * 0.125 + m_full
+    ref = torch.einsum("bhqk,bhkd->bqhd", torch.nan_to_num(torch.softmax(s, dim=-1), nan=0.0), vv)
+    rms = ref.pow(2).mean().sqrt().item()
+    assert torch.isfinite(out).all()
+    assert (out - ref).abs().max().item() / rms < (2e-4 if kv == "f16" else 1e-3)
+    if n_q != n_kv:
+        assert out[0, 5, 0].abs().max().item() == 0.0 and out[0, 5, planes].abs().max().item() == 0.0
+    o_ref = oracle.attn(q[:1], ks[:1], vs[:1], mask, kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)
+    assert rel_err(out[:1].cpu().numpy(), o_ref) < TOL[kv]
+    if n_q == n_kv:
+        implied = engine.prefill(qd, kd, vd)
+        engine.sync_status()
+        assert (out - implied).abs().max().item() / rms < 1e-4
+
+
 def test_locdit_patch_of_256_streams(engine, oracle, vo):
     import torch
     S, L, seq = 256, 8, 9

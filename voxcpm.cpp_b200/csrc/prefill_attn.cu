@@ -50,6 +50,10 @@ using namespace vox;
 
 namespace vox {
 int launch_generic(vox_engine * e, const vox_attn_args * a, int causal_offset, cudaStream_t stream);
+// the tensor-core kernel with an explicit additive mask (called by vox_attn_forward)
+bool   prefill_mask_route_ok(const vox_attn_args * a);
+size_t prefill_mask_workspace_bytes(const vox_attn_args * a);
+int    launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 }
 
 namespace {
@@ -109,6 +113,11 @@ struct PrefillParams {
     int             n_batch, n_qtiles, n_items;
     float           scale_log2;
     int *           status;
+    // additive f16 mask (kMask kernels): rows of n_kv values, planes broadcast over heads and sequences
+    const uint8_t * mask;
+    size_t          m_nb1, m_nb2, m_nb3;
+    int             m_ne2, m_ne3;
+    float           scale;
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
@@ -290,7 +299,9 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
 // kSplitP: the weights go to the tensor core as hi + lo (two f16 parts, ~21 bits) instead of one f16 (11 bits).
 // kVLo: K and V come as two f16 tiles each, value + remainder (q8_0 blocks expanded exactly); the remainders take a
 // second Q.K^T pass and a third P.V pass.
-template <bool kSplitP, bool kVLo>
+// kMask: an additive f16 mask is read instead of implying the causal one; every key tile is walked, a row may see no
+// key at all (its output is zero, third_party/ggml/src/ggml-cpu/ops.cpp:8333).
+template <bool kSplitP, bool kVLo, bool kMask>
 __global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo, const PrefillParams p) {
@@ -572,8 +583,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
             // block's maximum exceeds it by more than 2^8, which after the first tile is rare.
             float m_ref = -INFINITY;
+            // this row of the mask (rows past n_q are computed on zeros and not stored: they borrow the last row)
+            const uint8_t * mrow = nullptr;
+            if (kMask)
+                mrow = p.mask + (size_t) min(qpos, p.n_q - 1) * p.m_nb1 + (size_t) (w.head % p.m_ne2) * p.m_nb2 +
+                       (size_t) (w.batch % p.m_ne3) * p.m_nb3;
+            // the scores are multiplied by `mul` on their way into the exponent: with a mask they have been put into
+            // natural units (scale * S + mask) first
+            const float mul = kMask ? 1.4426950408889634f : p.scale_log2;
             for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
                 const int sb = T & 1;
+                const int k0 = j * kKeys;
+                uint4     mv[8];
+                if (kMask) {  // requested before the wait for the scores; chunks of 8 keys lie wholly inside or outside n_kv
+                    const uint4 * mp = reinterpret_cast<const uint4 *>(mrow + (size_t) k0 * 2);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) mv[c] = k0 + 8 * c < p.n_kv ? __ldg(mp + c) : make_uint4(0u, 0u, 0u, 0u);
+                }
                 PROF_STOP(0);
                 if (!mbar_wait_bounded(kempty0 + 8 * (T % kSt), (T / kSt) & 1)) { give_up(); ok = false; break; }
                 PROF_STOP(1);
@@ -581,7 +607,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 if (tid == 0) PROF_TRACE(0, T);
                 tc_fence_after();
                 const uint32_t t_s    = t_row + kSCol + kKeys * sb;
-                const int      k0     = j * kKeys;
                 const bool     masked = k0 + kKeys - 1 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
                 // 32-column blocks with at least one key some row of this warp sees (warp-uniform)
                 const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
@@ -599,6 +624,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_STOP(10);
 #pragma unroll
                 for (int i = 0; i < 64; ++i) pin(r[i]);
+                if (kMask) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint32_t w4[4] = {mv[c].x, mv[c].y, mv[c].z, mv[c].w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 m2 = __half22float2(*reinterpret_cast<const __half2 *>(&w4[i]));
+                            r[8 * c + 2 * i]     = __float_as_uint(fmaf(__uint_as_float(r[8 * c + 2 * i]), p.scale, m2.x));
+                            r[8 * c + 2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(r[8 * c + 2 * i + 1]), p.scale, m2.y));
+                        }
+                    }
+                }
                 if (masked) {  // only the tiles the causal diagonal or the end of the keys cuts through
 #pragma unroll
                     for (int i = 0; i < 64; ++i)
@@ -612,14 +649,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         t0 = max3(t0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
                         t1 = max3(t1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
                     }
-                    cmax = fmaxf(t0, t1) * p.scale_log2;
+                    cmax = fmaxf(t0, t1) * mul;
                 }
                 PROF_STOP(11);
                 // The weights are written only after the whole tile has been looked at, so a raise of the
                 // reference needs no second pass.  tcgen05.ld/st are warp-collective: the decision to rescale is
                 // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.
+                // With a mask a row may have seen no key yet: its reference stays -inf (any finite maximum then
+                // raises it, with a factor of 0 for accumulators that hold 0) and its weights are 2^(-inf - 0) = 0.
                 if (j == 0) {
-                    m_ref = cmax;  // key 0 is visible to every row: finite
+                    m_ref = cmax;  // without a mask key 0 is visible to every row: finite
                 } else {
                     const bool raise = cmax > m_ref + 8.0f;
                     if (__any_sync(0xffffffffu, raise)) {
@@ -630,6 +669,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         rescale_accumulators(t_row, f);
                     }
                 }
+                const float m_sub = kMask && m_ref == -INFINITY ? 0.0f : m_ref;
                 if (kSplitP) {
                     // P = 2^(c*S - m_ref) as hi + lo, two packed f16 tiles over the scores just read (hi: columns 0-31,
                     // lo: columns 32-63).  hi keeps the top 11 bits of the f32 weight (a mask: exact in f16 for every
@@ -641,8 +681,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         uint32_t hi[8], lo[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            const float p0 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), p.scale_log2, -m_ref));
-                            const float p1 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), p.scale_log2, -m_ref));
+                            const float p0 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), mul, -m_sub));
+                            const float p1 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), mul, -m_sub));
                             const float h0 = __uint_as_float(__float_as_uint(p0) & 0xFFFFE000u);
                             const float h1 = __uint_as_float(__float_as_uint(p1) & 0xFFFFE000u);
                             hi[i] = pack_half2(h0, h1);
@@ -658,8 +698,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         uint32_t h[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i]), p.scale_log2, -m_ref)),
-                                              ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), p.scale_log2, -m_ref)));
+                            h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i]), mul, -m_sub)),
+                                              ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), mul, -m_sub)));
                         tmem_st16_nowait(t_s + 16 * c, h);
                     }
                 }
@@ -761,39 +801,10 @@ bool tc_route_ok(const vox_attn_args * a) {
     return true;
 }
 
-}  // namespace
-
-extern "C" {
-
-#ifdef VOX_PREFILL_PROFILE
-int vox_debug_prefill_trace(long long * out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 4 * 64) != cudaSuccess;
-}
-int vox_debug_prefill_profile(unsigned long long * out, int reset) {
-    if (out && cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
-    if (reset) {
-        unsigned long long zero[32] = {0};
-        if (cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) != cudaSuccess) return 1;
-    }
-    return 0;
-}
-#endif
-
-size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a) {
-    if (!a || !vox_attn_supported(a) || a->mask.data != nullptr) return 0;
-    return q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;  // K, V, and what rounding each to f16 leaves over
-}
-
-int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, void * stream) {
-    VOX_REQUIRE(e && a, VOX_ATTN_INVALID_ARGUMENT, "vox_attn_prefill: null argument");
-    VOX_REQUIRE(a->mask.data == nullptr, VOX_ATTN_INVALID_ARGUMENT,
-                "vox_attn_prefill implies the causal mask; pass mask.data == NULL (use vox_attn_forward for explicit masks)");
-    VOX_REQUIRE(vox_attn_supported(a), VOX_ATTN_INVALID_ARGUMENT, "%s", vox_attn_last_error_string());
-    VOX_REQUIRE(a->q.data && a->k.data && a->v.data && a->dst.data, VOX_ATTN_INVALID_ARGUMENT, "null data pointer");
-    VOX_REQUIRE(a->k.ne[1] >= a->q.ne[1], VOX_ATTN_INVALID_ARGUMENT, "n_kv %lld < n_q %lld", (long long) a->k.ne[1],
-                (long long) a->q.ne[1]);
-    const int    offset = (int) (a->k.ne[1] - a->q.ne[1]);
-    cudaStream_t st     = static_cast<cudaStream_t>(stream);
+// Host side of the tensor-core kernel: `with_mask` false implies the causal mask at `offset` (n_kv - n_q), true reads
+// a->mask.  q8_0 K/V are expanded into the workspace first; operands the kernel cannot take go to the general kernel.
+int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t st, bool with_mask) {
+    const int offset = with_mask ? (int) a->k.ne[1] : (int) (a->k.ne[1] - a->q.ne[1]);
     // q8_0 K/V: expanded to f16 in the workspace first (without one of the size vox_attn_prefill_workspace_bytes
     // names, the general kernel takes the call, as it does for f32 K/V and unaligned strides)
     vox_tensor kf = a->k, vf = a->v;
@@ -825,7 +836,7 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
         int rc = check_launch(e, "q8_0_to_f16_kernel");
         if (rc != VOX_ATTN_OK) return rc;
     } else if (!tc_route_ok(a)) {
-        return launch_generic(e, a, offset, st);
+        return launch_generic(e, a, with_mask ? -1 : offset, st);
     }
 
     CUtensorMap    mk, mv, mklo, mvlo;
@@ -843,9 +854,11 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     }
     if (!v_lo) { mklo = mk; mvlo = mv; }  // not read
     if (!(e->attr_mask & (1u << 12))) {
-        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
-        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
-        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(true)));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(true)));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
+        VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(true)));
         e->attr_mask |= 1u << 12;
     }
     // Experiment hook: VOX_PREFILL_WEIGHTS=f16 sends the weights as one f16 part (faster; on long sequences of
@@ -859,7 +872,11 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     p.n_q = (int) a->q.ne[1]; p.n_kv = (int) a->k.ne[1]; p.n_heads = (int) a->q.ne[2];
     p.gqa = (int) (a->q.ne[2] / a->k.ne[2]); p.causal_offset = offset;
     p.scale_log2 = a->scale * 1.4426950408889634f;
+    p.scale  = a->scale;
     p.status = e->status_dev;
+    p.mask   = with_mask ? static_cast<const uint8_t *>(a->mask.data) : nullptr;
+    p.m_nb1 = a->mask.nb[1]; p.m_nb2 = a->mask.nb[2]; p.m_nb3 = a->mask.nb[3];
+    p.m_ne2 = with_mask ? (int) a->mask.ne[2] : 1; p.m_ne3 = with_mask ? (int) a->mask.ne[3] : 1;
     p.n_batch  = (int) a->q.ne[3];
     p.n_qtiles = (p.n_q + kTile - 1) / kTile;
     const long long items = (long long) p.n_qtiles * p.n_heads * p.n_batch;
@@ -867,10 +884,65 @@ int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, 
     p.n_items = (int) items;
     // persistent CTAs, two per SM (105 KB of shared memory, 256 TMEM columns and half the register file each)
     dim3 grid((unsigned) std::min<long long>(items, 2LL * e->sm_count));
-    if (v_lo) launch_pdl(prefill_tc_kernel<true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
-    else if (split_p) launch_pdl(prefill_tc_kernel<true, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
-    else launch_pdl(prefill_tc_kernel<false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
+    if (with_mask && v_lo) launch_pdl(prefill_tc_kernel<true, true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
+    else if (with_mask) launch_pdl(prefill_tc_kernel<true, false, true>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
+    else if (v_lo) launch_pdl(prefill_tc_kernel<true, true, false>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
+    else if (split_p) launch_pdl(prefill_tc_kernel<true, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
+    else launch_pdl(prefill_tc_kernel<false, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
     return check_launch(e, "prefill_tc_kernel");
+}
+
+}  // namespace
+
+namespace vox {
+
+// An explicit mask goes to the tensor-core kernel when the problem is large enough to fill its 128-row items, the
+// mask rows can be read in 16-byte pieces that lie wholly inside or outside n_kv, and K/V are f16 (or q8_0).
+bool prefill_mask_route_ok(const vox_attn_args * a) {
+    const vox_tensor & m = a->mask;
+    if (m.data == nullptr || a->q.ne[1] < kTile || a->k.ne[1] < kTile || a->k.ne[1] % 8) return false;
+    if ((reinterpret_cast<uintptr_t>(m.data) & 15) != 0 || m.nb[1] % 16 || m.nb[2] % 16 || m.nb[3] % 16) return false;
+    return tc_route_ok(a) || q8_route_ok(a);
+}
+size_t prefill_mask_workspace_bytes(const vox_attn_args * a) {
+    return prefill_mask_route_ok(a) && q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;
+}
+int launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream) {
+    return run_tc(e, a, workspace, workspace_bytes, stream, true);
+}
+
+}  // namespace vox
+
+extern "C" {
+
+#ifdef VOX_PREFILL_PROFILE
+int vox_debug_prefill_trace(long long * out) {
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 4 * 64) != cudaSuccess;
+}
+int vox_debug_prefill_profile(unsigned long long * out, int reset) {
+    if (out && cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+    if (reset) {
+        unsigned long long zero[32] = {0};
+        if (cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#endif
+
+size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a) {
+    if (!a || !vox_attn_supported(a) || a->mask.data != nullptr) return 0;
+    return q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;  // K, V, and what rounding each to f16 leaves over
+}
+
+int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, void * stream) {
+    VOX_REQUIRE(e && a, VOX_ATTN_INVALID_ARGUMENT, "vox_attn_prefill: null argument");
+    VOX_REQUIRE(a->mask.data == nullptr, VOX_ATTN_INVALID_ARGUMENT,
+                "vox_attn_prefill implies the causal mask; pass mask.data == NULL (use vox_attn_forward for explicit masks)");
+    VOX_REQUIRE(vox_attn_supported(a), VOX_ATTN_INVALID_ARGUMENT, "%s", vox_attn_last_error_string());
+    VOX_REQUIRE(a->q.data && a->k.data && a->v.data && a->dst.data, VOX_ATTN_INVALID_ARGUMENT, "null data pointer");
+    VOX_REQUIRE(a->k.ne[1] >= a->q.ne[1], VOX_ATTN_INVALID_ARGUMENT, "n_kv %lld < n_q %lld", (long long) a->k.ne[1],
+                (long long) a->q.ne[1]);
+    return run_tc(e, a, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), false);
 }
 
 }  // extern "C"
