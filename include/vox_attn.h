@@ -109,11 +109,11 @@ size_t vox_attn_workspace_bytes(const vox_attn_args * a);
 
 /* Replaces ggml_cuda_flash_attn_ext (fattn.cu:460-478) / ggml_compute_forward_flash_attn_ext
  * (third_party/ggml/src/ggml-cpu/ops.cpp:8838-8853).  Routes by shape: n_q==1 with f16 K/V ->
- * split-KV decode kernel; 128 or more queries and keys with f16 / q8_0 K/V and a mask (the
+ * split-KV decode kernel; 128 or more queries and keys with a mask (the
  * reference's prefill call, src/minicpm.cpp:708-710, with the tensor create_causal_mask built, or
  * any other additive f16 mask whose rows start on 16-byte boundaries, n_kv a multiple of 8) ->
  * tcgen05 kernel, which reads the mask (see vox_attn_prefill for the form that implies it; q8_0
- * needs the workspace vox_attn_workspace_bytes names); anything else the contract allows (any
+ * and f32 K/V need the workspace vox_attn_workspace_bytes names); anything else the contract allows (any
  * n_q/n_kv, f32/f16/q8_0 K/V, arbitrary f16 mask, strides) -> general kernel.  Never allocates. */
 int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes,
                      void * stream);
@@ -124,9 +124,10 @@ int vox_attn_forward_host(vox_engine * e, const vox_attn_args * a, void * stream
 
 /* Causal prefill without a materialised mask (the mask MiniCPMModel::create_causal_mask builds,
  * src/minicpm.cpp:602-620, is implied: key j visible to query i iff j <= i + n_kv - n_q).
- * q [D, n_q, H, B] f32; k, v [D, n_kv, HK, B] f16, or q8_0 when a workspace of
- * vox_attn_prefill_workspace_bytes is passed (the blocks are expanded to f16 there first): runs on
- * tcgen05/TMEM.  f32 K/V, unaligned strides, and q8_0 K/V without a workspace take the general kernel. */
+ * q [D, n_q, H, B] f32; k, v [D, n_kv, HK, B] f16, or q8_0 / f32 when a workspace of
+ * vox_attn_prefill_workspace_bytes is passed (they are expanded there into f16 value + remainder
+ * tiles first): runs on tcgen05/TMEM.  Unaligned strides, and q8_0 / f32 K/V without a workspace,
+ * take the general kernel. */
 int vox_attn_prefill(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes,
                      void * stream);
 size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a);

@@ -101,8 +101,10 @@ constexpr int kOnesBytes = kKvBytes;       // a tile of ones, addressed as colum
 // the rings are two stages deep, so that two CTAs still fit on an SM.
 constexpr int stages_of(bool v_lo) { return v_lo ? 2 : kStages; }
 constexpr int v_stage_bytes(bool v_lo) { return v_lo ? 2 * kKvBytes : kKvBytes; }
+// ... and a Q buffer holds the f16 tile and the remainder tile as well (then one CTA fits per SM)
+constexpr int q_buf_bytes(bool v_lo) { return v_lo ? 2 * kQBytes : kQBytes; }
 constexpr int smem_pf(bool v_lo) {  // Q x 2, K ring, V ring, ones
-    return kQBufs * kQBytes + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + 1024;
+    return kQBufs * q_buf_bytes(v_lo) + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + 1024;
 }
 
 struct PrefillParams {
@@ -297,15 +299,16 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
 }
 
 // kSplitP: the weights go to the tensor core as hi + lo (two f16 parts, ~21 bits) instead of one f16 (11 bits).
-// kVLo: K and V come as two f16 tiles each, value + remainder (q8_0 blocks expanded exactly); the remainders take a
-// second Q.K^T pass and a third P.V pass.
+// kVLo: K and V come as two f16 tiles each, value + remainder (q8_0 blocks expanded exactly), and Q is kept as value +
+// remainder too (the reference's accurate path for such operands keeps Q in f32); the remainders take a second and
+// third Q.K^T pass and a third P.V pass.
 // kMask: an additive f16 mask is read instead of implying the causal one; every key tile is walked, a row may see no
 // key at all (its output is zero, third_party/ggml/src/ggml-cpu/ops.cpp:8333).
 template <bool kSplitP, bool kVLo, bool kMask>
 __global__ void __launch_bounds__(kThreadsPf, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo, const PrefillParams p) {
-    constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo);
+    constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo), kQBufBytes = q_buf_bytes(kVLo);
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[4 * kStages + 6];
     __shared__ uint32_t tmem_base_slot;
@@ -313,7 +316,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBytes, sV0 = sK0 + kSt * kVBytes, sOnes = sV0 + kSt * kVBytes;
+    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBufBytes, sV0 = sK0 + kSt * kVBytes, sOnes = sV0 + kSt * kVBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -379,7 +382,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         }
         // this thread's Q row: f32 from memory, f16 into eight 16-byte chunks at their swizzled places
         auto load_q = [&](const WorkItem & w, int buf) {
-            uint8_t * const q_dst = smem_gen + buf * kQBytes + row * 128;
+            uint8_t * const q_dst = smem_gen + buf * kQBufBytes + row * 128;
             const int       qpos  = w.q0 + row;
             const float4 *  src   = reinterpret_cast<const float4 *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) w.head * p.q_nb2 +
                                                                   (size_t) w.batch * p.q_nb3);
@@ -390,9 +393,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 for (int i = 0; i < 8; ++i) qv[i] = qpos < p.n_q ? src[8 * h + i] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    *reinterpret_cast<uint4 *>(q_dst + (((4 * h + c) ^ (row & 7)) << 4)) =
-                        make_uint4(pack_half2(qv[2 * c].x, qv[2 * c].y), pack_half2(qv[2 * c].z, qv[2 * c].w),
-                                   pack_half2(qv[2 * c + 1].x, qv[2 * c + 1].y), pack_half2(qv[2 * c + 1].z, qv[2 * c + 1].w));
+                    const float    x[8] = {qv[2 * c].x, qv[2 * c].y, qv[2 * c].z, qv[2 * c].w, qv[2 * c + 1].x, qv[2 * c + 1].y, qv[2 * c + 1].z, qv[2 * c + 1].w};
+                    uint32_t       hi[4], lo[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __half2 h2 = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+                        hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+                        lo[i] = pack_half2(x[2 * i] - __low2float(h2), x[2 * i + 1] - __high2float(h2));
+                    }
+                    const int at = ((4 * h + c) ^ (row & 7)) << 4;
+                    *reinterpret_cast<uint4 *>(q_dst + at) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    // what the rounding left over: a second tile, for operands whose reference path keeps Q in f32
+                    if (kVLo) *reinterpret_cast<uint4 *>(q_dst + kQBytes + at) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
             }
             fence_proxy_async_smem();
@@ -481,7 +493,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // the remainder tile of a V stage: 64 columns, no tile of ones behind it
                 const uint64_t     dVlo     = smem_desc_sw128_mn(sV0 + kKvBytes, 16);
                 constexpr uint32_t idesc_lo = idesc_f16(kHeadDim, true);
-                constexpr uint64_t kQBuf   = kQBytes >> 4;
+                constexpr uint64_t kQBuf   = kQBufBytes >> 4;
+                constexpr uint64_t kQLo    = kQBytes >> 4;  // from a Q tile to its remainder tile
                 PROF_VARS;
                 // Q.K^T runs two tiles ahead of P.V, across item boundaries: `q` walks the same item sequence as the
                 // P.V loop below.  S of global tile Tq goes into score buffer Tq % 2: four k-steps of 16 along
@@ -507,6 +520,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + k * kStepQK, dKlo + st * kStage + k * kStepQK, idesc_qk, 1);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)  // and what rounding Q to f16 left over
+                            tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + kQLo + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, 1);
                     }
                     tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
                     ++Tq;
@@ -727,15 +743,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     }
 }
 
-// q8_0 K/V (34-byte blocks: f16 scale + 32 int8, third_party/ggml/src/ggml-common.h:221-224) are expanded once
-// per call into f16 tiles in the caller's workspace, [B][HK][n_kv][64] contiguous, and the tensor-core kernel runs
-// on those.  One thread per block of 32 values: d * q is exact in f32 (11 + 7 bits) and rounded to f16 once.
+// q8_0 K/V (34-byte blocks: f16 scale + 32 int8, third_party/ggml/src/ggml-common.h:221-224) and f32 K/V are expanded
+// once per call into f16 tiles in the caller's workspace, [B][HK][n_kv][64] contiguous, and the tensor-core kernel
+// runs on those.  One thread per 32 values; each value becomes an f16 and the f16 of what that rounding left over
+// (exact for q8_0: d * q has at most 18 significant bits; 22 of 24 bits for f32).
 struct DequantParams {
     const uint8_t * src[2];
     __half *        dst[2];
     __half *        rest[2];  // what rounding to f16 leaves over (exact: d * q has at most 18 significant bits)
     size_t          nb1[2], nb2[2], nb3[2];
     int             n_kv, n_kvh, n_batch;
+    int             f32;  // source rows are 64 floats instead of two q8_0 blocks
 };
 __global__ void __launch_bounds__(256) q8_0_to_f16_kernel(const DequantParams p) {
     const long long n_blocks = 2LL * p.n_kv * p.n_kvh * p.n_batch;  // two blocks per 64-wide row
@@ -749,17 +767,30 @@ __global__ void __launch_bounds__(256) q8_0_to_f16_kernel(const DequantParams p)
         const int       pos = (int) (row % p.n_kv);
         const int       kvh = (int) ((row / p.n_kv) % p.n_kvh);
         const int       b   = (int) (row / ((long long) p.n_kv * p.n_kvh));
-        const uint16_t * s  = reinterpret_cast<const uint16_t *>(src + (size_t) pos * nb1 + (size_t) kvh * nb2 + (size_t) b * nb3 +
-                                                                 (size_t) blk * 34);
-        const float d = __half2float(__ushort_as_half(s[0]));
-        uint32_t    out[16], rest[16];
+        const uint8_t * at = src + (size_t) pos * nb1 + (size_t) kvh * nb2 + (size_t) b * nb3;
+        uint32_t        out[16], rest[16];
+        if (p.f32) {
+            const float4 * s = reinterpret_cast<const float4 *>(at + (size_t) blk * 128);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const uint16_t two = s[1 + j];
-            const float    x0 = d * (float) (signed char) (two & 0xff), x1 = d * (float) (signed char) (two >> 8);
-            const __half2  h  = __floats2half2_rn(x0, x1);
-            out[j]  = *reinterpret_cast<const uint32_t *>(&h);
-            rest[j] = pack_half2(x0 - __low2float(h), x1 - __high2float(h));
+            for (int j = 0; j < 8; ++j) {
+                const float4  x  = s[j];
+                const __half2 h0 = __floats2half2_rn(x.x, x.y), h1 = __floats2half2_rn(x.z, x.w);
+                out[2 * j]      = *reinterpret_cast<const uint32_t *>(&h0);
+                out[2 * j + 1]  = *reinterpret_cast<const uint32_t *>(&h1);
+                rest[2 * j]     = pack_half2(x.x - __low2float(h0), x.y - __high2float(h0));
+                rest[2 * j + 1] = pack_half2(x.z - __low2float(h1), x.w - __high2float(h1));
+            }
+        } else {
+            const uint16_t * s = reinterpret_cast<const uint16_t *>(at + (size_t) blk * 34);
+            const float      d = __half2float(__ushort_as_half(s[0]));
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint16_t two = s[1 + j];
+                const float    x0 = d * (float) (signed char) (two & 0xff), x1 = d * (float) (signed char) (two >> 8);
+                const __half2  h  = __floats2half2_rn(x0, x1);
+                out[j]  = *reinterpret_cast<const uint32_t *>(&h);
+                rest[j] = pack_half2(x0 - __low2float(h), x1 - __high2float(h));
+            }
         }
         uint4 * o = reinterpret_cast<uint4 *>(dst + (size_t) row * 64 + (size_t) blk * 32);
 #pragma unroll
@@ -775,15 +806,18 @@ size_t q8_scratch_bytes(const vox_attn_args * a) {  // one tensor, rounded up so
     return (bytes + 255) & ~(size_t) 255;
 }
 
-// q8_0 K and V of equal shape, whole blocks, rows at even addresses (the blocks are read as 16-bit words)
+// K and V to expand: both q8_0 (whole blocks, rows at even addresses: the blocks are read as 16-bit words) or both
+// f32 (rows read in 16-byte pieces), of equal shape
 bool q8_route_ok(const vox_attn_args * a) {
     const vox_tensor &k = a->k, &v = a->v;
-    if (k.type != VOX_TYPE_Q8_0 || v.type != VOX_TYPE_Q8_0) return false;
+    if (k.type != v.type || (k.type != VOX_TYPE_Q8_0 && k.type != VOX_TYPE_F32)) return false;
     if (k.ne[1] != v.ne[1] || k.ne[2] != v.ne[2] || k.ne[3] != v.ne[3]) return false;
     if (a->q.ne[1] < 1 || k.ne[1] < 1) return false;
     if ((reinterpret_cast<uintptr_t>(a->q.data) & 15) != 0 || a->q.nb[1] % 16 || a->q.nb[2] % 16 || a->q.nb[3] % 16) return false;
+    const uintptr_t unit = k.type == VOX_TYPE_F32 ? 16 : 2;
     for (const vox_tensor * t : {&k, &v})
-        if ((reinterpret_cast<uintptr_t>(t->data) & 1) != 0 || t->nb[1] % 2 || t->nb[2] % 2 || t->nb[3] % 2) return false;
+        if (reinterpret_cast<uintptr_t>(t->data) % unit || t->nb[1] % unit || t->nb[2] % unit || t->nb[3] % unit) return false;
+    if (k.type == VOX_TYPE_F32 && (k.nb[0] != 4 || v.nb[0] != 4)) return false;
     return true;
 }
 
@@ -830,6 +864,7 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
         for (int i = 0; i < 2; ++i) dp.rest[i] = lo_data[i] = reinterpret_cast<__half *>(static_cast<uint8_t *>(workspace) + (2 + i) * one);
         v_lo = true;
         dp.n_kv = (int) a->k.ne[1]; dp.n_kvh = (int) a->k.ne[2]; dp.n_batch = (int) a->k.ne[3];
+        dp.f32  = a->k.type == VOX_TYPE_F32;
         const long long n_blocks = 2LL * dp.n_kv * dp.n_kvh * dp.n_batch;
         const unsigned  gx = (unsigned) std::min<long long>((n_blocks + 255) / 256, 8LL * e->sm_count);
         q8_0_to_f16_kernel<<<dim3(gx, 2), 256, 0, st>>>(dp);
@@ -882,8 +917,9 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     const long long items = (long long) p.n_qtiles * p.n_heads * p.n_batch;
     VOX_REQUIRE(items < (1LL << 30), VOX_ATTN_INVALID_ARGUMENT, "too many query tiles");
     p.n_items = (int) items;
-    // persistent CTAs, two per SM (105 KB of shared memory, 256 TMEM columns and half the register file each)
-    dim3 grid((unsigned) std::min<long long>(items, 2LL * e->sm_count));
+    // persistent CTAs, two per SM (105 KB of shared memory, 256 TMEM columns and half the register file each); one
+    // per SM when K/V were expanded (137 KB: every operand tile comes with its remainder tile)
+    dim3 grid((unsigned) std::min<long long>(items, (v_lo ? 1LL : 2LL) * e->sm_count));
     if (with_mask && v_lo) launch_pdl(prefill_tc_kernel<true, true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
     else if (with_mask) launch_pdl(prefill_tc_kernel<true, false, true>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
     else if (v_lo) launch_pdl(prefill_tc_kernel<true, true, false>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
