@@ -22,6 +22,7 @@ size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv
 // the tcgen05 prefill kernel reading an explicit mask (prefill_attn.cu)
 bool   prefill_mask_route_ok(const vox_attn_args * a);
 size_t prefill_mask_workspace_bytes(const vox_attn_args * a);
+size_t prefill_mask_workspace_min(const vox_attn_args * a);
 int    launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 }  // namespace vox
 
@@ -225,8 +226,8 @@ int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, 
                                  a->q.nb[3], (float *) a->dst.data, a->scale, workspace, workspace_bytes, st);
     }
     // large masked problems over f16 / q8_0 K/V: the tensor-core kernel reads the mask (q8_0 needs the workspace)
-    if (prefill_mask_route_ok(a) && workspace_bytes >= prefill_mask_workspace_bytes(a) &&
-        (prefill_mask_workspace_bytes(a) == 0 || workspace != nullptr))
+    if (prefill_mask_route_ok(a) && workspace_bytes >= prefill_mask_workspace_min(a) &&
+        (prefill_mask_workspace_min(a) == 0 || workspace != nullptr))
         return launch_prefill_mask(e, a, workspace, workspace_bytes, st);
     return launch_generic(e, a, -1, st);
 }

@@ -53,6 +53,7 @@ int launch_generic(vox_engine * e, const vox_attn_args * a, int causal_offset, c
 // the tensor-core kernel with an explicit additive mask (called by vox_attn_forward)
 bool   prefill_mask_route_ok(const vox_attn_args * a);
 size_t prefill_mask_workspace_bytes(const vox_attn_args * a);
+size_t prefill_mask_workspace_min(const vox_attn_args * a);
 int    launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 }
 
@@ -120,6 +121,8 @@ struct PrefillParams {
     size_t          m_nb1, m_nb2, m_nb3;
     int             m_ne2, m_ne3;
     float           scale;
+    // per (mask plane, query tile): bit j set when key tile j holds a finite mask value for some row (NULL: not known)
+    const unsigned long long * tile_live;
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
@@ -281,7 +284,8 @@ __device__ __noinline__ void rescale_accumulators(uint32_t t_row, float f) {
 // heaviest first (late query tiles see more keys); CTA c of G takes items c, 2G-1-c, 2G+c, ... so that
 // a heavy first item is followed by a light one.
 struct WorkItem {
-    int qtile, head, batch, n_tiles, q0;
+    int                qtile, head, batch, n_tiles, q0;
+    unsigned long long live;  // key tiles to walk, as bits (at most 64 when some are left out)
 };
 __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, WorkItem & w) {
     const int G = gridDim.x, c = blockIdx.x;
@@ -295,7 +299,20 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
     w.q0    = w.qtile * kTile;
     const int last_row = min(w.q0 + kTile, p.n_q) - 1;
     w.n_tiles = min((p.n_kv + kKeys - 1) / kKeys, (last_row + p.causal_offset) / kKeys + 1);
+    w.live    = ~0ull;
+    if (p.tile_live != nullptr) {  // only set for n_tiles <= 64; a tile where the mask hides every key from every row is left out
+        const unsigned long long seen =
+            p.tile_live[((size_t) (w.batch % p.m_ne3) * p.m_ne2 + (w.head % p.m_ne2)) * p.n_qtiles + w.qtile];
+        w.live = seen != 0 ? seen : 1ull;  // an item that sees nothing still walks one tile: its rows come out as zeros
+    }
     return true;
+}
+
+// Walks the key tiles of an item that are to be computed: j is the first live tile at or after `from`, or n_tiles.
+__device__ __forceinline__ int next_live(const WorkItem & w, int from) {
+    if (w.live == ~0ull) return from;
+    const unsigned long long rest = from < 64 ? w.live >> from : 0ull;
+    return rest ? from + __ffsll((long long) rest) - 1 : w.n_tiles;
 }
 
 // kSplitP: the weights go to the tensor core as hi + lo (two f16 parts, ~21 bits) instead of one f16 (11 bits).
@@ -305,7 +322,7 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
 // kMask: an additive f16 mask is read instead of implying the causal one; every key tile is walked, a row may see no
 // key at all (its output is zero, third_party/ggml/src/ggml-cpu/ops.cpp:8333).
 template <bool kSplitP, bool kVLo, bool kMask>
-__global__ void __launch_bounds__(kThreadsPf, 2)
+__global__ void __launch_bounds__(kThreadsPf, kVLo ? 1 : 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo, const PrefillParams p) {
     constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo), kQBufBytes = q_buf_bytes(kVLo);
@@ -372,7 +389,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         // One thread per query row, as in the softmax warps (warp 8+i may touch TMEM lanes 32i..32i+31).  They keep
         // the Q tiles of the next two items in shared memory and read each finished output out of TMEM, so that the
         // softmax warps go from the last tile of one item straight to the first tile of the next.
-        regs_give<kRegsIo>();
+        if (!kVLo) regs_give<kRegsIo>();  // one CTA per SM with kVLo: the launch allots every thread enough
         const int      row   = tid - (kThreadsPf - kIoThreads);
         const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);
         {
@@ -445,7 +462,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (work_item(p, round + kQBufs, wn)) load_q(wn, round % kQBufs);
         }
     } else if (warp >= 4) {
-        regs_give<kRegsControl>();
+        if (!kVLo) regs_give<kRegsControl>();
         if (warp == 4) {
             // -------------------------------------------------------------- producer
             if (lane == 0) {
@@ -456,7 +473,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_START();
                 for (int round = 0; ok && work_item(p, round, w); ++round) {
                     const int kvh = w.head / p.gqa;
-                    for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
+                    for (int j = next_live(w, 0); j < w.n_tiles && !aborted(); j = next_live(w, j + 1), ++T) {
                         const int      st = T % kSt;
                         const uint32_t ph = ((T / kSt) - 1) & 1;
                         PROF_STOP(0);
@@ -503,11 +520,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // they need.
                 WorkItem wq;
                 int      rq = 0, jq = 0, Tq = 0;
-                bool     have_q = work_item(p, 0, wq);
+                bool     have_q = work_item(p, 0, wq), first_q = true;
+                if (have_q) jq = next_live(wq, 0);
                 auto issue_qk = [&]() {
                     if (!have_q) return true;
                     PROF_STOP(0);
-                    if (jq == 0 && !mbar_wait_bounded(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) return false;  // the item's Q tile is in place
+                    if (first_q && !mbar_wait_bounded(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) return false;  // the item's Q tile is in place
+                    first_q = false;
                     PROF_STOP(2);
                     const int st = Tq % kSt, sb = Tq & 1;
                     if (!mbar_wait_bounded(kfull0 + 8 * st, (Tq / kSt) & 1)) return false;
@@ -526,9 +545,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
                     ++Tq;
-                    if (++jq == wq.n_tiles) {
-                        jq     = 0;
-                        have_q = work_item(p, ++rq, wq);
+                    jq = next_live(wq, jq + 1);
+                    if (jq >= wq.n_tiles) {
+                        first_q = true;
+                        have_q  = work_item(p, ++rq, wq);
+                        if (have_q) jq = next_live(wq, 0);
                     }
                     return true;
                 };
@@ -538,15 +559,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_START();
                 if (!issue_qk() || !issue_qk()) { give_up(); ok = false; }
                 for (int round = 0; ok && work_item(p, round, w); ++round) {
-                    for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
-                        const int st = T % kSt;
+                    const int j_first = next_live(w, 0);
+                    for (int j = j_first; j < w.n_tiles && !aborted(); ++T) {
+                        const int st     = T % kSt;
+                        const int j_next = next_live(w, j + 1);
                         PROF_STOP(0);
                         if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kSt) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(3);
                         if (!mbar_wait_bounded(bP0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(4);
                         // the previous item's result has been read out of TMEM: its columns may be overwritten
-                        if (j == 0 && round > 0 && !mbar_wait_bounded(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
+                        if (j == j_first && round > 0 && !mbar_wait_bounded(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(2);
                         PROF_TRACE(2, T);
                         tc_fence_after();
@@ -555,7 +578,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         // the tile's score buffer.
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, j > 0 || k > 0);
+                            tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, j != j_first || k > 0);
                         if (kSplitP) {  // the low parts of the same weights, behind the high parts in the score buffer
 #pragma unroll
                             for (int k = 0; k < 4; ++k)
@@ -567,10 +590,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                                 tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dVlo + st * kVStep + k * kStepV, idesc_lo, 1);
                         }
                         tc_commit(vempty0 + 8 * st);  // P.V has retired: the V stage may be refilled, the accumulators are at rest
-                        if (j + 1 == w.n_tiles) tc_commit(bO);  // the item's output is complete
+                        if (j_next >= w.n_tiles) tc_commit(bO);  // the item's output is complete
                         // scores two tiles ahead, into the buffer whose weights P.V has just been told to read
                         if (!issue_qk()) { give_up(); ok = false; break; }
                         PROF_TRACE(3, T);
+                        j = j_next;
                     }
                     if (aborted()) break;
                 }
@@ -580,7 +604,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         }
     } else {
         // ------------------------------------------------------------------ softmax warps: one thread per query row
-        regs_take<kRegsSoftmax>();
+        if (!kVLo) regs_take<kRegsSoftmax>();
         const int      row   = tid;                                    // == TMEM lane; warp w may only touch lanes 32w..32w+31
         const uint32_t t_row = tmem + ((uint32_t) (32 * warp) << 16);  // this warp's lane quarter
 
@@ -607,7 +631,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             // the scores are multiplied by `mul` on their way into the exponent: with a mask they have been put into
             // natural units (scale * S + mask) first
             const float mul = kMask ? 1.4426950408889634f : p.scale_log2;
-            for (int j = 0; j < w.n_tiles && !aborted(); ++j, ++T) {
+            const int j_first = next_live(w, 0);
+            for (int j = j_first; j < w.n_tiles && !aborted(); j = next_live(w, j + 1), ++T) {
                 const int sb = T & 1;
                 const int k0 = j * kKeys;
                 uint4     mv[8];
@@ -673,7 +698,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.
                 // With a mask a row may have seen no key yet: its reference stays -inf (any finite maximum then
                 // raises it, with a factor of 0 for accumulators that hold 0) and its weights are 2^(-inf - 0) = 0.
-                if (j == 0) {
+                if (j == j_first) {
                     m_ref = cmax;  // without a mask key 0 is visible to every row: finite
                 } else {
                     const bool raise = cmax > m_ref + 8.0f;
@@ -835,10 +860,64 @@ bool tc_route_ok(const vox_attn_args * a) {
     return true;
 }
 
+// Which key tiles of which query tiles the mask leaves anything of: one 64-bit word per (mask plane, query tile), bit j
+// set when some row of the tile has a mask value other than -inf among keys 64j..64j+63.  The tensor-core kernel
+// leaves the other tiles out (with the reference's causal mask tensor that is half of them).  Grid: (key tiles,
+// query tiles, planes), one thread per row, into words cleared beforehand (one CTA per query tile walking all its key
+// tiles needs no clearing but measured slower: 95.6 against 73.2 us per layer at 2048 tokens x 2).
+__global__ void __launch_bounds__(kTile) mask_tiles_kernel(const uint8_t * mask, size_t nb1, size_t nb2, size_t nb3, int ne2, int n_q,
+                                                           int n_kv, unsigned long long * live) {
+    const int row = blockIdx.y * kTile + threadIdx.x, k0 = blockIdx.x * kKeys;
+    const int i2 = blockIdx.z % ne2, i3 = blockIdx.z / ne2;
+    int       any = 0;
+    if (row < n_q) {
+        const uint4 * m = reinterpret_cast<const uint4 *>(mask + (size_t) row * nb1 + (size_t) i2 * nb2 + (size_t) i3 * nb3 + (size_t) k0 * 2);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (k0 + 8 * c < n_kv) {  // n_kv is a multiple of 8: a piece lies wholly inside or outside
+                const uint4    x    = __ldg(m + c);
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) any |= (w[i] & 0xffffu) != 0xfc00u || (w[i] >> 16) != 0xfc00u;
+            }
+        }
+    }
+    if (__syncthreads_or(any) && threadIdx.x == 0)
+        atomicOr(live + (size_t) blockIdx.z * gridDim.y + blockIdx.y, 1ull << blockIdx.x);
+}
+
+// bytes of those words (0 when there are more than 64 key tiles: then every tile is walked)
+size_t mask_tiles_bytes(const vox_attn_args * a) {
+    const long long n_ktiles = (a->k.ne[1] + kKeys - 1) / kKeys, n_qtiles = (a->q.ne[1] + kTile - 1) / kTile;
+    if (a->mask.data == nullptr || n_ktiles > 64) return 0;
+    return ((size_t) (a->mask.ne[2] * a->mask.ne[3] * n_qtiles * 8) + 255) & ~(size_t) 255;
+}
+
 // Host side of the tensor-core kernel: `with_mask` false implies the causal mask at `offset` (n_kv - n_q), true reads
 // a->mask.  q8_0 K/V are expanded into the workspace first; operands the kernel cannot take go to the general kernel.
 int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t st, bool with_mask) {
     const int offset = with_mask ? (int) a->k.ne[1] : (int) (a->k.ne[1] - a->q.ne[1]);
+    // workspace: the live-tile words of the mask first (when it has room for them), then the expanded K/V
+    const unsigned long long * tile_live = nullptr;
+    if (with_mask && workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) {
+        const size_t words = mask_tiles_bytes(a);
+        const size_t rest  = q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;
+        // worth its launch from a few thousand tiles on (512 tokens x 1 sequence is 512 tiles: not worth it)
+        const long long tiles = ((a->k.ne[1] + kKeys - 1) / kKeys) * ((a->q.ne[1] + kTile - 1) / kTile) * a->q.ne[2] * a->q.ne[3];
+        if (words > 0 && workspace_bytes >= words + rest && tiles >= 2048) {
+            unsigned long long * live = static_cast<unsigned long long *>(workspace);
+            VOX_CUDA_TRY(cudaMemsetAsync(live, 0, words, st));
+            const dim3 grid((unsigned) ((a->k.ne[1] + kKeys - 1) / kKeys), (unsigned) ((a->q.ne[1] + kTile - 1) / kTile),
+                            (unsigned) (a->mask.ne[2] * a->mask.ne[3]));
+            mask_tiles_kernel<<<grid, kTile, 0, st>>>(static_cast<const uint8_t *>(a->mask.data), a->mask.nb[1], a->mask.nb[2], a->mask.nb[3],
+                                                      (int) a->mask.ne[2], (int) a->q.ne[1], (int) a->k.ne[1], live);
+            int rc = check_launch(e, "mask_tiles_kernel");
+            if (rc != VOX_ATTN_OK) return rc;
+            tile_live       = live;
+            workspace       = static_cast<uint8_t *>(workspace) + words;
+            workspace_bytes -= words;
+        }
+    }
     // q8_0 K/V: expanded to f16 in the workspace first (without one of the size vox_attn_prefill_workspace_bytes
     // names, the general kernel takes the call, as it does for f32 K/V and unaligned strides)
     vox_tensor kf = a->k, vf = a->v;
@@ -912,6 +991,7 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     p.mask   = with_mask ? static_cast<const uint8_t *>(a->mask.data) : nullptr;
     p.m_nb1 = a->mask.nb[1]; p.m_nb2 = a->mask.nb[2]; p.m_nb3 = a->mask.nb[3];
     p.m_ne2 = with_mask ? (int) a->mask.ne[2] : 1; p.m_ne3 = with_mask ? (int) a->mask.ne[3] : 1;
+    p.tile_live = tile_live;
     p.n_batch  = (int) a->q.ne[3];
     p.n_qtiles = (p.n_q + kTile - 1) / kTile;
     const long long items = (long long) p.n_qtiles * p.n_heads * p.n_batch;
@@ -941,6 +1021,11 @@ bool prefill_mask_route_ok(const vox_attn_args * a) {
     return tc_route_ok(a) || q8_route_ok(a);
 }
 size_t prefill_mask_workspace_bytes(const vox_attn_args * a) {
+    if (!prefill_mask_route_ok(a)) return 0;
+    return mask_tiles_bytes(a) + (q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0);
+}
+// what the route cannot do without: room for the expanded K/V (the live-tile words are optional)
+size_t prefill_mask_workspace_min(const vox_attn_args * a) {
     return prefill_mask_route_ok(a) && q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;
 }
 int launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream) {
