@@ -53,6 +53,8 @@ def parse():
                    help="hand Q and the new K rows over before the rotary embedding: one cos/sin table per step, rotation inside the decode launches")
     p.add_argument("--prefill-shapes", default="512x1,512x8", help="LxB list for --workload prefill")
     p.add_argument("--prefill-kv", default="f16", choices=["f16", "q8_0"], help="K/V operand type for --workload prefill")
+    p.add_argument("--prefill-mask", action="store_true",
+                   help="--workload prefill through vox_attn_forward with the causal mask as a tensor, as the reference's call site passes it")
     p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1"],
                    help="serving = the headline line; the others time one more configuration each on one GPU")
     return p.parse_args()
@@ -289,16 +291,22 @@ def aux_workload(args, pkg, torch):
             if args.prefill_kv == "q8_0":
                 k, v = q8_0_blocks(k.float()), q8_0_blocks(v.float())
             o = torch.empty((layers, B, L, H, D), device="cuda")
+            if args.prefill_mask:
+                hidden = torch.arange(L, device="cuda")[None, :] > torch.arange(L, device="cuda")[:, None]
+                mask = torch.zeros((1, 1, L, L), device="cuda", dtype=torch.float16).masked_fill(hidden, float("-inf"))
+                call = lambda l: eng.forward(q[l], k[l], v[l], mask, dst=o[l])
+            else:
+                call = lambda l: eng.prefill(q[l], k[l], v[l], dst=o[l])
             for l in range(layers):  # warm-up outside capture (attribute set-up, descriptors)
-                eng.prefill(q[l], k[l], v[l], dst=o[l])
+                call(l)
             eng.sync_status()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 for l in range(layers):
-                    eng.prefill(q[l], k[l], v[l], dst=o[l])
+                    call(l)
             ms = timed(graph.replay, 20, cold=False)
             flops = layers * B * 4.0 * H * D * L * (L + 1) / 2
-            out["results"].append({"config": f"prefill L={L} B={B} x {layers} layers, {args.prefill_kv} K/V", "ms": ms, "us_per_layer": ms * 1e3 / layers,
+            out["results"].append({"config": f"prefill L={L} B={B} x {layers} layers, {args.prefill_kv} K/V" + (", mask tensor" if args.prefill_mask else ""), "ms": ms, "us_per_layer": ms * 1e3 / layers,
                                    "tflops_causal_useful": flops / (ms * 1e-3) / 1e12,
                                    "frac_of_measured_bf16_peak": flops / (ms * 1e-3) / 1e12 / tens})
     else:
