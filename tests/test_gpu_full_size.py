@@ -220,6 +220,34 @@ def test_forward_with_an_explicit_mask_on_the_tensor_core_kernel(kv, B, n_q, n_k
         assert (out - implied).abs().max().item() / rms < 1e-4
 
 
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+def test_forward_without_a_mask_on_the_tensor_core_kernel(kv, engine, oracle, vo):
+    """No mask and 128 or more queries and keys (every query sees every key): vox_attn_forward uses the tcgen05 kernel.
+    300 queries over 456 keys, 2 sequences; in full against an f32 softmax, one sequence against the oracle."""
+    import torch
+    B, n_q, n_kv = 2, 300, 456
+    rng = np.random.default_rng(43)
+    q = rng.standard_normal((B, H, n_q, D)).astype(np.float32)
+    k = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    if kv == "q8_0":
+        ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+        kf, vf = oracle.dequantize_q8_0(ks), oracle.dequantize_q8_0(vs)
+    else:
+        q = q.astype(np.float16).astype(np.float32)
+        ks, vs = k.astype(np.float16), v.astype(np.float16)
+        kf, vf = ks.astype(np.float32), vs.astype(np.float32)
+    qd = dev(q)
+    out = engine.forward(qd, dev(ks), dev(vs))
+    engine.sync_status()
+    kk, vv = dev(kf).repeat_interleave(H // HK, dim=1), dev(vf).repeat_interleave(H // HK, dim=1)
+    s = torch.einsum("bhqd,bhkd->bhqk", qd, kk) * 0.125
+    ref = torch.einsum("bhqk,bhkd->bqhd", torch.softmax(s, dim=-1), vv)
+    assert (out - ref).abs().max().item() / ref.pow(2).mean().sqrt().item() < 2e-4
+    o_ref = oracle.attn(q[:1], ks[:1], vs[:1], None, kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)
+    assert rel_err(out[:1].cpu().numpy(), o_ref) < TOL[kv]
+
+
 def test_locdit_patch_of_256_streams(engine, oracle, vo):
     import torch
     S, L, seq = 256, 8, 9

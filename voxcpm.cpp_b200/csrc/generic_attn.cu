@@ -24,6 +24,9 @@ bool   prefill_mask_route_ok(const vox_attn_args * a);
 size_t prefill_mask_workspace_bytes(const vox_attn_args * a);
 size_t prefill_mask_workspace_min(const vox_attn_args * a);
 int    launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
+bool   prefill_full_route_ok(const vox_attn_args * a);
+size_t prefill_full_workspace_bytes(const vox_attn_args * a);
+int    launch_prefill_full(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 }  // namespace vox
 
 namespace {
@@ -198,7 +201,7 @@ size_t vox_attn_workspace_bytes(const vox_attn_args * a) {
     if (validate(a, false) != VOX_ATTN_OK) return 0;
     if (a->q.ne[1] == 1 && a->k.type == VOX_TYPE_F16 && a->v.type == VOX_TYPE_F16 && a->mask.data == nullptr)
         return decode_workspace_bytes((int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2], (int) a->k.ne[1]);
-    return prefill_mask_workspace_bytes(a);
+    return a->mask.data ? prefill_mask_workspace_bytes(a) : prefill_full_workspace_bytes(a);
 }
 
 int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, void * stream) {
@@ -229,6 +232,9 @@ int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, 
     if (prefill_mask_route_ok(a) && workspace_bytes >= prefill_mask_workspace_min(a) &&
         (prefill_mask_workspace_min(a) == 0 || workspace != nullptr))
         return launch_prefill_mask(e, a, workspace, workspace_bytes, st);
+    if (prefill_full_route_ok(a) && workspace_bytes >= prefill_full_workspace_bytes(a) &&
+        (prefill_full_workspace_bytes(a) == 0 || workspace != nullptr))
+        return launch_prefill_full(e, a, workspace, workspace_bytes, st);
     return launch_generic(e, a, -1, st);
 }
 

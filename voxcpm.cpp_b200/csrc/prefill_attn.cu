@@ -55,6 +55,9 @@ bool   prefill_mask_route_ok(const vox_attn_args * a);
 size_t prefill_mask_workspace_bytes(const vox_attn_args * a);
 size_t prefill_mask_workspace_min(const vox_attn_args * a);
 int    launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
+bool   prefill_full_route_ok(const vox_attn_args * a);
+size_t prefill_full_workspace_bytes(const vox_attn_args * a);
+int    launch_prefill_full(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 }
 
 namespace {
@@ -893,10 +896,12 @@ size_t mask_tiles_bytes(const vox_attn_args * a) {
     return ((size_t) (a->mask.ne[2] * a->mask.ne[3] * n_qtiles * 8) + 255) & ~(size_t) 255;
 }
 
-// Host side of the tensor-core kernel: `with_mask` false implies the causal mask at `offset` (n_kv - n_q), true reads
-// a->mask.  q8_0 K/V are expanded into the workspace first; operands the kernel cannot take go to the general kernel.
-int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t st, bool with_mask) {
-    const int offset = with_mask ? (int) a->k.ne[1] : (int) (a->k.ne[1] - a->q.ne[1]);
+// Host side of the tensor-core kernel: `with_mask` false implies the causal mask at `offset` (n_kv - n_q) or, with
+// `causal` false, no mask at all; true reads a->mask.  q8_0 K/V are expanded into the workspace first; operands the kernel cannot take go to the general kernel.
+int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t st, bool with_mask,
+           bool causal = true) {
+    // every key visible (before the mask, if there is one) is a causal offset of n_kv
+    const int offset = with_mask || !causal ? (int) a->k.ne[1] : (int) (a->k.ne[1] - a->q.ne[1]);
     // workspace: the live-tile words of the mask first (when it has room for them), then the expanded K/V
     const unsigned long long * tile_live = nullptr;
     if (with_mask && workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) {
@@ -950,7 +955,7 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
         int rc = check_launch(e, "q8_0_to_f16_kernel");
         if (rc != VOX_ATTN_OK) return rc;
     } else if (!tc_route_ok(a)) {
-        return launch_generic(e, a, with_mask ? -1 : offset, st);
+        return launch_generic(e, a, with_mask || !causal ? -1 : offset, st);
     }
 
     CUtensorMap    mk, mv, mklo, mvlo;
@@ -1030,6 +1035,16 @@ size_t prefill_mask_workspace_min(const vox_attn_args * a) {
 }
 int launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream) {
     return run_tc(e, a, workspace, workspace_bytes, stream, true);
+}
+// no mask, every key visible to every query: the same kernel from 128 queries and keys on
+bool prefill_full_route_ok(const vox_attn_args * a) {
+    return a->mask.data == nullptr && a->q.ne[1] >= kTile && a->k.ne[1] >= kTile && (tc_route_ok(a) || q8_route_ok(a));
+}
+size_t prefill_full_workspace_bytes(const vox_attn_args * a) {
+    return prefill_full_route_ok(a) && q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;
+}
+int launch_prefill_full(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream) {
+    return run_tc(e, a, workspace, workspace_bytes, stream, false, false);
 }
 
 }  // namespace vox
