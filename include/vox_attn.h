@@ -108,8 +108,9 @@ int vox_attn_supported(const vox_attn_args * a);
 size_t vox_attn_workspace_bytes(const vox_attn_args * a);
 
 /* Replaces ggml_cuda_flash_attn_ext (fattn.cu:460-478) / ggml_compute_forward_flash_attn_ext
- * (third_party/ggml/src/ggml-cpu/ops.cpp:8838-8853).  Routes by shape: n_q==1 with f16 K/V ->
- * split-KV decode kernel; 128 or more queries and keys with a mask (the
+ * (third_party/ggml/src/ggml-cpu/ops.cpp:8838-8853).  Routes by shape: n_q==1 with f16 K/V, or
+ * q8_0 K/V and the workspace vox_attn_workspace_bytes names (the blocks are taken apart into planes
+ * there) -> split-KV decode kernel; 128 or more queries and keys with a mask (the
  * reference's prefill call, src/minicpm.cpp:708-710, with the tensor create_causal_mask built, or
  * any other additive f16 mask whose rows start on 16-byte boundaries, n_kv a multiple of 8) ->
  * tcgen05 kernel, which reads the mask (see vox_attn_prefill for the form that implies it; q8_0

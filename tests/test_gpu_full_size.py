@@ -248,6 +248,29 @@ def test_forward_without_a_mask_on_the_tensor_core_kernel(kv, engine, oracle, vo
     assert rel_err(out[:1].cpu().numpy(), o_ref) < TOL[kv]
 
 
+def test_single_token_forward_over_q8_0_blocks(engine, oracle, vo):
+    """The operator at n_q = 1 on a caller's own q8_0 tensors (ggml's 34-byte blocks, here as views of a longer cache,
+    4100 of 4608 rows, 3 sequences): the blocks are taken apart into planes in the workspace and the q8_0 split-KV decode
+    kernel runs on them.  Against an f32 softmax over exactly the values the blocks hold, and against the oracle."""
+    import torch
+    B, n_kv, cap = 3, 4100, 4608
+    rng = np.random.default_rng(47)
+    q = rng.standard_normal((B, H, 1, D)).astype(np.float32)
+    k = rng.standard_normal((B, HK, cap, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, cap, D)).astype(np.float32)
+    ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+    kf, vf = oracle.dequantize_q8_0(ks)[:, :, :n_kv], oracle.dequantize_q8_0(vs)[:, :, :n_kv]
+    qd, kd, vd = dev(q), dev(ks)[:, :, :n_kv], dev(vs)[:, :, :n_kv]  # views: rows keep the stride of the longer cache
+    out = engine.forward(qd, kd, vd)
+    engine.sync_status()
+    kk, vv = dev(kf).repeat_interleave(H // HK, dim=1), dev(vf).repeat_interleave(H // HK, dim=1)
+    s = torch.einsum("bhqd,bhkd->bhqk", qd, kk) * 0.125
+    ref = torch.einsum("bhqk,bhkd->bqhd", torch.softmax(s, dim=-1), vv)
+    assert (out - ref).abs().max().item() / ref.pow(2).mean().sqrt().item() < 2e-3
+    o_ref = oracle.attn(q[:1], ks[:1, :, :n_kv], vs[:1, :, :n_kv], None, kv_type=vo.Q8_0, path=vo.PATH_ROW_F32)
+    assert rel_err(out[:1].cpu().numpy(), o_ref) < TOL["q8_0"]
+
+
 def test_locdit_patch_of_256_streams(engine, oracle, vo):
     import torch
     S, L, seq = 256, 8, 9

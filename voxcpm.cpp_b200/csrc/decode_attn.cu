@@ -738,6 +738,114 @@ int launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorM
                          kv_len_const, kv_bound, q, q_nb_head, q_nb_stream, dst, scale, workspace, workspace_bytes, stream);
 }
 
+// ---- single-token calls over q8_0 K/V in ggml's block layout (the operator called on a caller's own quantised
+// cache, third_party/ggml/src/ggml-common.h:221-224): the blocks are taken apart into the planes the q8_0 decode
+// kernel reads (int8 rows of 64 bytes, two f16 scales per row), in the workspace, and that kernel runs on them.
+// Nothing is re-quantised: the result is what the cache object gives for the same blocks.
+
+struct RepackParams {
+    const uint8_t * src[2];
+    size_t          nb1[2], nb2[2], nb3[2];
+    uint8_t *       rows[2];    // [B][HK][n_pad][64] int8
+    uint8_t *       scales[2];  // [B][HK][n_pad][2] f16
+    int             n_kv, n_pad, n_kvh, n_batch;
+};
+__global__ void __launch_bounds__(256) q8_0_blocks_to_planes_kernel(const RepackParams p) {
+    const long long n_blocks = 2LL * p.n_pad * p.n_kvh * p.n_batch;
+    const bool      is_v     = blockIdx.y != 0;
+    const uint8_t * src      = is_v ? p.src[1] : p.src[0];
+    uint8_t *       rows     = is_v ? p.rows[1] : p.rows[0];
+    uint8_t *       scales   = is_v ? p.scales[1] : p.scales[0];
+    const size_t    nb1 = is_v ? p.nb1[1] : p.nb1[0], nb2 = is_v ? p.nb2[1] : p.nb2[0], nb3 = is_v ? p.nb3[1] : p.nb3[0];
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks; i += (long long) gridDim.x * blockDim.x) {
+        const int       blk = (int) (i & 1);
+        const long long row = i >> 1;
+        const int       pos = (int) (row % p.n_pad);
+        const int       kvh = (int) ((row / p.n_pad) % p.n_kvh);
+        const int       b   = (int) (row / ((long long) p.n_pad * p.n_kvh));
+        uint32_t        q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        uint16_t        d    = 0;  // rows past n_kv (up to the next multiple of the tile) hold zeros
+        if (pos < p.n_kv) {
+            const uint16_t * s = reinterpret_cast<const uint16_t *>(src + (size_t) pos * nb1 + (size_t) kvh * nb2 + (size_t) b * nb3 +
+                                                                    (size_t) blk * 34);
+            d = s[0];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = (uint32_t) s[1 + 2 * j] | ((uint32_t) s[2 + 2 * j] << 16);
+        }
+        uint4 * o = reinterpret_cast<uint4 *>(rows + (size_t) row * 64 + (size_t) blk * 32);
+        o[0] = make_uint4(q[0], q[1], q[2], q[3]);
+        o[1] = make_uint4(q[4], q[5], q[6], q[7]);
+        reinterpret_cast<uint16_t *>(scales)[row * 2 + blk] = d;
+    }
+}
+
+static size_t q8_planes_bytes(const vox_attn_args * a, int * n_pad_out) {
+    const int n_pad = (int) ((a->k.ne[1] + kKvTile - 1) / kKvTile * kKvTile);
+    if (n_pad_out) *n_pad_out = n_pad;
+    const size_t rows = (size_t) n_pad * a->k.ne[2] * a->k.ne[3];
+    return 2 * (rows * 64 + rows * 4);  // K and V: int8 rows + scale pairs (both multiples of 256 bytes)
+}
+
+bool decode_q8_blocks_route_ok(const vox_attn_args * a) {
+    const vox_tensor &q = a->q, &k = a->k, &v = a->v;
+    if (q.ne[1] != 1 || a->mask.data != nullptr) return false;
+    if (k.type != VOX_TYPE_Q8_0 || v.type != VOX_TYPE_Q8_0) return false;
+    if (k.ne[1] < 1 || k.ne[1] != v.ne[1] || k.ne[2] != v.ne[2] || k.ne[3] != v.ne[3] || q.ne[2] / k.ne[2] > 8) return false;
+    for (const vox_tensor * t : {&k, &v})
+        if ((reinterpret_cast<uintptr_t>(t->data) & 1) != 0 || t->nb[1] % 2 || t->nb[2] % 2 || t->nb[3] % 2) return false;
+    return true;
+}
+
+size_t decode_q8_blocks_workspace_bytes(const vox_attn_args * a) {
+    if (!decode_q8_blocks_route_ok(a)) return 0;
+    const size_t partials = decode_workspace_bytes((int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2], (int) a->k.ne[1]);
+    return ((partials + 255) & ~(size_t) 255) + q8_planes_bytes(a, nullptr);
+}
+
+int launch_decode_q8_blocks(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t st) {
+    int          n_pad = 0;
+    const size_t planes = q8_planes_bytes(a, &n_pad);
+    const int    B = (int) a->q.ne[3], HK = (int) a->k.ne[2], n_kv = (int) a->k.ne[1];
+    const size_t partials = (decode_workspace_bytes(B, (int) a->q.ne[2], HK, n_kv) + 255) & ~(size_t) 255;
+    VOX_REQUIRE(workspace != nullptr && workspace_bytes >= partials + planes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+                VOX_ATTN_WORKSPACE_TOO_SMALL, "q8_0 decode needs %zu workspace bytes, got %zu", partials + planes, workspace_bytes);
+    uint8_t *    base = static_cast<uint8_t *>(workspace) + partials;
+    const size_t rows = (size_t) n_pad * HK * B;
+    RepackParams rp;
+    const vox_tensor * ts[2] = {&a->k, &a->v};
+    for (int i = 0; i < 2; ++i) {
+        rp.src[i] = static_cast<const uint8_t *>(ts[i]->data);
+        rp.nb1[i] = ts[i]->nb[1]; rp.nb2[i] = ts[i]->nb[2]; rp.nb3[i] = ts[i]->nb[3];
+        rp.rows[i]   = base + i * rows * 64;
+        rp.scales[i] = base + 2 * rows * 64 + i * rows * 4;
+    }
+    rp.n_kv = n_kv; rp.n_pad = n_pad; rp.n_kvh = HK; rp.n_batch = B;
+    const long long n_blocks = 2LL * (long long) rows;
+    const unsigned  gx = (unsigned) std::min<long long>((n_blocks + 255) / 256, 8LL * e->sm_count);
+    q8_0_blocks_to_planes_kernel<<<dim3(gx, 2), 256, 0, st>>>(rp);
+    int rc = check_launch(e, "q8_0_blocks_to_planes_kernel");
+    if (rc != VOX_ATTN_OK) return rc;
+    // the planes described as one cache layer of n_pad rows (the same descriptors vox_kv_create builds)
+    CUtensorMap    mk, mv, mks, mvs;
+    const uint64_t dims[5]     = {64, (uint64_t) n_pad, (uint64_t) HK, (uint64_t) B, 1};
+    const uint64_t strides[4]  = {64, (uint64_t) 64 * n_pad, (uint64_t) 64 * n_pad * HK, (uint64_t) 64 * n_pad * HK * B};
+    const uint32_t box[5]      = {64, kKvTile, 1, 1, 1};
+    const uint64_t sdims[5]    = {(uint64_t) n_pad * 2, 1, (uint64_t) HK, (uint64_t) B, 1};
+    const uint64_t sstrides[4] = {(uint64_t) 4 * n_pad, (uint64_t) 4 * n_pad, (uint64_t) 4 * n_pad * HK, (uint64_t) 4 * n_pad * HK * B};
+    const uint32_t sbox[5]     = {2 * kKvTile, 1, 1, 1, 1};
+    CUtensorMap * ms[2] = {&mk, &mv};
+    CUtensorMap * ss[2] = {&mks, &mvs};
+    for (int i = 0; i < 2; ++i) {
+        rc = make_tensor_map(e, ms[i], rp.rows[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc == VOX_ATTN_OK)
+            rc = make_tensor_map(e, ss[i], rp.scales[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, sdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != VOX_ATTN_OK) return rc;
+    }
+    return launch_decode(e, true, mk, mv, &mks, &mvs, 0, n_pad, B, (int) a->q.ne[2], HK, nullptr, n_kv, n_kv,
+                         static_cast<const float *>(a->q.data), a->q.nb[2], a->q.nb[3], static_cast<float *>(a->dst.data), a->scale,
+                         workspace, partials, st);
+}
+
 }  // namespace vox
 
 extern "C" {

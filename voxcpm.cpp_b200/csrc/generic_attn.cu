@@ -19,6 +19,10 @@ int    launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtens
                          int kv_bound, const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst, float scale,
                          void * workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);
+// single-token calls over q8_0 K/V in block layout: taken apart into planes in the workspace (decode_attn.cu)
+bool   decode_q8_blocks_route_ok(const vox_attn_args * a);
+size_t decode_q8_blocks_workspace_bytes(const vox_attn_args * a);
+int    launch_decode_q8_blocks(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 // the tcgen05 prefill kernel reading an explicit mask (prefill_attn.cu)
 bool   prefill_mask_route_ok(const vox_attn_args * a);
 size_t prefill_mask_workspace_bytes(const vox_attn_args * a);
@@ -201,6 +205,7 @@ size_t vox_attn_workspace_bytes(const vox_attn_args * a) {
     if (validate(a, false) != VOX_ATTN_OK) return 0;
     if (a->q.ne[1] == 1 && a->k.type == VOX_TYPE_F16 && a->v.type == VOX_TYPE_F16 && a->mask.data == nullptr)
         return decode_workspace_bytes((int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2], (int) a->k.ne[1]);
+    if (decode_q8_blocks_route_ok(a)) return decode_q8_blocks_workspace_bytes(a);
     return a->mask.data ? prefill_mask_workspace_bytes(a) : prefill_full_workspace_bytes(a);
 }
 
@@ -228,6 +233,8 @@ int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, 
                                  nullptr, (int) a->k.ne[1], (int) a->k.ne[1], (const float *) a->q.data, a->q.nb[2],
                                  a->q.nb[3], (float *) a->dst.data, a->scale, workspace, workspace_bytes, st);
     }
+    if (decode_q8_blocks_route_ok(a) && workspace != nullptr && workspace_bytes >= decode_q8_blocks_workspace_bytes(a))
+        return launch_decode_q8_blocks(e, a, workspace, workspace_bytes, st);
     // large masked problems over f16 / q8_0 K/V: the tensor-core kernel reads the mask (q8_0 needs the workspace)
     if (prefill_mask_route_ok(a) && workspace_bytes >= prefill_mask_workspace_min(a) &&
         (prefill_mask_workspace_min(a) == 0 || workspace != nullptr))
