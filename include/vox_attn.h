@@ -110,12 +110,12 @@ size_t vox_attn_workspace_bytes(const vox_attn_args * a);
 /* Replaces ggml_cuda_flash_attn_ext (fattn.cu:460-478) / ggml_compute_forward_flash_attn_ext
  * (third_party/ggml/src/ggml-cpu/ops.cpp:8838-8853).  Routes by shape: n_q==1 with f16 K/V, or
  * q8_0 K/V and the workspace vox_attn_workspace_bytes names (the blocks are taken apart into planes
- * there) -> split-KV decode kernel; 128 or more queries and keys with a mask (the
+ * there) -> split-KV decode kernel; 32 or more keys with a mask (the
  * reference's prefill call, src/minicpm.cpp:708-710, with the tensor create_causal_mask built, or
  * any other additive f16 mask whose rows start on 16-byte boundaries, n_kv a multiple of 8) ->
  * tcgen05 kernel, which reads the mask (see vox_attn_prefill for the form that implies it; q8_0
- * and f32 K/V need the workspace vox_attn_workspace_bytes names), and so do 128 or more queries and
- * keys without a mask; anything else the contract allows (any
+ * and f32 K/V need the workspace vox_attn_workspace_bytes names), and so do two or more queries
+ * over 32 or more keys without a mask; anything else the contract allows (any
  * n_q/n_kv, f32/f16/q8_0 K/V, arbitrary f16 mask, strides) -> general kernel.  Never allocates. */
 int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes,
                      void * stream);

@@ -172,8 +172,8 @@ def test_prefill_over_a_q8_0_cache(B, L, past, engine, oracle, vo):
 @pytest.mark.parametrize("kv, B, n_q, n_kv, planes", [("f16", 2, 512, 512, 1), ("f16", 2, 200, 320, 2), ("q8_0", 1, 256, 384, 1),
                                                       ("f32", 2, 300, 424, 1)])
 def test_forward_with_an_explicit_mask_on_the_tensor_core_kernel(kv, B, n_q, n_kv, planes, engine, oracle, vo):
-    """The operator as the reference calls it for prefill, mask tensor included (src/minicpm.cpp:708-710): from 128
-    queries and keys on, vox_attn_forward sends f16 / q8_0 K/V with an additive f16 mask to the tcgen05 kernel, which
+    """The operator as the reference calls it for prefill, mask tensor included (src/minicpm.cpp:708-710): from 32
+    keys on, vox_attn_forward sends f16 / q8_0 K/V with an additive f16 mask to the tcgen05 kernel, which
     reads the mask instead of implying it.  Masks here: the reference's causal one; a random one with finite biases,
     30 % of the keys hidden, one row that sees nothing (its output is zero) and one that sees its first key only in the
     last tile, broadcast over heads from two planes.  Checked in full against an f32 softmax, one sequence against the
@@ -222,7 +222,7 @@ def test_forward_with_an_explicit_mask_on_the_tensor_core_kernel(kv, B, n_q, n_k
 
 @pytest.mark.parametrize("kv", ["f16", "q8_0"])
 def test_forward_without_a_mask_on_the_tensor_core_kernel(kv, engine, oracle, vo):
-    """No mask and 128 or more queries and keys (every query sees every key): vox_attn_forward uses the tcgen05 kernel.
+    """No mask, two or more queries and 32 or more keys (every query sees every key): vox_attn_forward uses the tcgen05 kernel.
     300 queries over 456 keys, 2 sequences; in full against an f32 softmax, one sequence against the oracle."""
     import torch
     B, n_q, n_kv = 2, 300, 456
@@ -269,6 +269,35 @@ def test_single_token_forward_over_q8_0_blocks(engine, oracle, vo):
     assert (out - ref).abs().max().item() / ref.pow(2).mean().sqrt().item() < 2e-3
     o_ref = oracle.attn(q[:1], ks[:1, :, :n_kv], vs[:1, :, :n_kv], None, kv_type=vo.Q8_0, path=vo.PATH_ROW_F32)
     assert rel_err(out[:1].cpu().numpy(), o_ref) < TOL["q8_0"]
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+def test_a_chunk_of_queries_against_a_long_cache(kv, engine, oracle, vo):
+    """40 new tokens after 4056 cached ones, with the causal mask as a tensor (a prompt fed in chunks): few rows of the
+    kernel's 128-row tile are in use, every key tile is.  In full against an f32 softmax, and against the oracle."""
+    import torch
+    B, n_q, n_kv = 2, 40, 4096
+    rng = np.random.default_rng(53)
+    q = rng.standard_normal((B, H, n_q, D)).astype(np.float32)
+    k = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    if kv == "q8_0":
+        ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+        kf, vf = oracle.dequantize_q8_0(ks), oracle.dequantize_q8_0(vs)
+    else:
+        q = q.astype(np.float16).astype(np.float32)
+        ks, vs = k.astype(np.float16), v.astype(np.float16)
+        kf, vf = ks.astype(np.float32), vs.astype(np.float32)
+    mask = np.array(oracle.causal_mask(np.arange(n_kv - n_q, n_kv), n_kv)[None, None])
+    qd, md = dev(q), dev(mask)
+    out = engine.forward(qd, dev(ks), dev(vs), md)
+    engine.sync_status()
+    kk, vv = dev(kf).repeat_interleave(H // HK, dim=1), dev(vf).repeat_interleave(H // HK, dim=1)
+    s = torch.einsum("bhqd,bhkd->bhqk", qd, kk) * 0.125 + md.float()
+    ref = torch.einsum("bhqk,bhkd->bqhd", torch.softmax(s, dim=-1), vv)
+    assert (out - ref).abs().max().item() / ref.pow(2).mean().sqrt().item() < 2e-4
+    o_ref = oracle.attn(q[:1], ks[:1], vs[:1], mask, kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)
+    assert rel_err(out[:1].cpu().numpy(), o_ref) < TOL[kv]
 
 
 def test_locdit_patch_of_256_streams(engine, oracle, vo):

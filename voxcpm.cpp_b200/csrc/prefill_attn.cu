@@ -1017,11 +1017,17 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
 
 namespace vox {
 
-// An explicit mask goes to the tensor-core kernel when the problem is large enough to fill its 128-row items, the
+// The general kernel spreads its work over (query, head) pairs only and walks the keys one after another: 276 us for
+// 16 queries over 512 keys, 2.2 ms for 32 over 4096 (a chunk of a prompt against a long cache), where the tensor-core
+// kernel, with most rows of its 128-row tile idle, takes 10.7 and 68.5 us.  So the general kernel keeps only the
+// short-key problems (LocEnc's 5 tokens, LocDiT's 9 or 18).
+constexpr int kMinKeys = 32;
+
+// An explicit mask goes to the tensor-core kernel when there are enough keys, the
 // mask rows can be read in 16-byte pieces that lie wholly inside or outside n_kv, and K/V are f16 (or q8_0).
 bool prefill_mask_route_ok(const vox_attn_args * a) {
     const vox_tensor & m = a->mask;
-    if (m.data == nullptr || a->q.ne[1] < kTile || a->k.ne[1] < kTile || a->k.ne[1] % 8) return false;
+    if (m.data == nullptr || a->q.ne[1] < 1 || a->k.ne[1] < kMinKeys || a->k.ne[1] % 8) return false;
     if ((reinterpret_cast<uintptr_t>(m.data) & 15) != 0 || m.nb[1] % 16 || m.nb[2] % 16 || m.nb[3] % 16) return false;
     return tc_route_ok(a) || q8_route_ok(a);
 }
@@ -1036,9 +1042,9 @@ size_t prefill_mask_workspace_min(const vox_attn_args * a) {
 int launch_prefill_mask(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream) {
     return run_tc(e, a, workspace, workspace_bytes, stream, true);
 }
-// no mask, every key visible to every query: the same kernel from 128 queries and keys on
+// no mask, every key visible to every query (single-token calls have the decode kernel)
 bool prefill_full_route_ok(const vox_attn_args * a) {
-    return a->mask.data == nullptr && a->q.ne[1] >= kTile && a->k.ne[1] >= kTile && (tc_route_ok(a) || q8_route_ok(a));
+    return a->mask.data == nullptr && a->q.ne[1] >= 2 && a->k.ne[1] >= kMinKeys && (tc_route_ok(a) || q8_route_ok(a));
 }
 size_t prefill_full_workspace_bytes(const vox_attn_args * a) {
     return prefill_full_route_ok(a) && q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;
