@@ -41,6 +41,15 @@
 // 256 TMEM columns and half the register file per CTA.  Every wait on a barrier is bounded; on expiry the status
 // word is set and all roles fall through to the common exit, where the TMEM columns are released.  The register
 // trade cannot block: what the softmax group takes is exactly what the other two give up (static_assert below).
+//
+// Three forms of the kernel share this code (template parameters):
+//   kSplitP  the weights as hi + lo (the product path; a single f16 is kept for comparison);
+//   kMask    an additive f16 mask tensor is read instead of implying the causal one: this is what vox_attn_forward
+//            uses for the reference's own prefill call and for any other masked call with 32 or more keys.  A small
+//            kernel first notes which key tiles the mask leaves anything of, and every role walks only those;
+//   kVLo     K/V that are not f16 (q8_0 blocks, f32) are expanded by a small kernel into an f16 value tile and an f16
+//            remainder tile each, Q is kept as value + remainder too, and the remainders take extra Q.K^T and P.V
+//            passes (24 tcgen05.mma per tile instead of 12; one CTA per SM), so that nothing is lost to f16 rounding.
 #include "common.cuh"
 
 #include <algorithm>
