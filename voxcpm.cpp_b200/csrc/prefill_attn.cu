@@ -173,33 +173,35 @@ template <int N>
 __device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N>
 __device__ __forceinline__ void regs_give() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-// 32 consecutive 32-bit columns of this thread's TMEM lane; the registers are valid after tmem_wait_ld
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t * r) {
+// TMEM loads complete asynchronously: the registers are valid only after tcgen05.wait::ld.  Load and wait are ONE asm
+// statement here, so that the compiler can never place a copy or a spill of a destination register between the two.
+// 32 consecutive 32-bit columns of this thread's TMEM lane:
+__device__ __forceinline__ void tmem_ld32_sync(uint32_t taddr, uint32_t * r) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 64 consecutive columns (two loads in flight, one wait)
+__device__ __forceinline__ void tmem_ld64_sync(uint32_t taddr, uint32_t * r) {
+    asm volatile(
+        "{\n\t.reg .b32 second;\n\t"
+        "add.u32 second, %64, 32;\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [second];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n\t}"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// Pins a register behind the volatile statements before it (the wait above), so that no use of a loaded
-// value can be scheduled ahead of the wait that makes it valid.
-__device__ __forceinline__ void pin(uint32_t & r) { asm volatile("" : "+r"(r)); }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
-    tmem_ld32_nowait(taddr, r);
-    tmem_wait_ld();
+    tmem_ld32_sync(taddr, r);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        pin(r[i]);
-        v[i] = __uint_as_float(r[i]);
-    }
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
@@ -239,9 +241,7 @@ __device__ __forceinline__ void tmem_st1(uint32_t taddr, float x) {
 }
 __device__ __forceinline__ float tmem_ld1(uint32_t taddr) {
     uint32_t r;
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
-    tmem_wait_ld();
-    pin(r);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n\ttcgen05.wait::ld.sync.aligned;" : "=r"(r) : "r"(taddr) : "memory");
     return __uint_as_float(r);
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -454,10 +454,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 uint32_t r[32];
-                tmem_ld32_nowait(t_row + kOCol + 32 * h, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) pin(r[i]);
+                tmem_ld32_sync(t_row + kOCol + 32 * h, r);
                 if (h == 1) {  // both halves are in registers: the columns go back to the tensor core
                     tc_fence_before();
                     __syncwarp();
@@ -664,19 +661,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // 32-column blocks with at least one key some row of this warp sees (warp-uniform)
                 const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
                 uint32_t       r[64];
+                if (n_live == 2) {
+                    tmem_ld64_sync(t_s, r);
+                } else {
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    if (c < n_live) {
-                        tmem_ld32_nowait(t_s + 32 * c, r + 32 * c);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r[32 * c + i] = 0xff800000u;  // -inf: no weight
-                    }
+                    for (int i = 0; i < 64; ++i) r[i] = 0xff800000u;  // -inf: no weight
+                    if (n_live == 1) tmem_ld32_sync(t_s, r);
                 }
-                tmem_wait_ld();
                 PROF_STOP(10);
-#pragma unroll
-                for (int i = 0; i < 64; ++i) pin(r[i]);
                 if (kMask) {
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
