@@ -299,6 +299,7 @@ struct WorkItem {
     int                qtile, head, batch, n_tiles, q0;
     unsigned long long live;  // key tiles to walk, as bits (at most 64 when some are left out)
 };
+template <bool kMask>
 __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, WorkItem & w) {
     const int G = gridDim.x, c = blockIdx.x;
     const int idx = round * G + ((round & 1) ? G - 1 - c : c);
@@ -312,7 +313,7 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
     const int last_row = min(w.q0 + kTile, p.n_q) - 1;
     w.n_tiles = min((p.n_kv + kKeys - 1) / kKeys, (last_row + p.causal_offset) / kKeys + 1);
     w.live    = ~0ull;
-    if (p.tile_live != nullptr) {  // only set for n_tiles <= 64; a tile where the mask hides every key from every row is left out
+    if (kMask && p.tile_live != nullptr) {  // only set for n_tiles <= 64; a tile where the mask hides every key from every row is left out
         const unsigned long long seen =
             p.tile_live[((size_t) (w.batch % p.m_ne3) * p.m_ne2 + (w.head % p.m_ne2)) * p.n_qtiles + w.qtile];
         w.live = seen != 0 ? seen : 1ull;  // an item that sees nothing still walks one tile: its rows come out as zeros
@@ -321,8 +322,10 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
 }
 
 // Walks the key tiles of an item that are to be computed: j is the first live tile at or after `from`, or n_tiles.
+// Only the mask-reading form leaves tiles out: for the others this is the identity at compile time.
+template <bool kMask>
 __device__ __forceinline__ int next_live(const WorkItem & w, int from) {
-    if (w.live == ~0ull) return from;
+    if (!kMask || w.live == ~0ull) return from;
     const unsigned long long rest = from < 64 ? w.live >> from : 0ull;
     return rest ? from + __ffsll((long long) rest) - 1 : w.n_tiles;
 }
@@ -442,8 +445,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         };
         WorkItem w, wn;
         for (int r = 0; r < kQBufs; ++r)
-            if (work_item(p, r, wn)) load_q(wn, r);
-        for (int round = 0; work_item(p, round, w) && !aborted(); ++round) {
+            if (work_item<kMask>(p, r, wn)) load_q(wn, r);
+        for (int round = 0; work_item<kMask>(p, round, w) && !aborted(); ++round) {
             if (!mbar_wait_bounded(bO, round & 1)) { give_up(); break; }
             tc_fence_after();
             const int   qpos = w.q0 + row;
@@ -468,7 +471,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
             }
             // every Q.K^T of this item retired before its output was complete: its Q buffer takes the item after next
-            if (work_item(p, round + kQBufs, wn)) load_q(wn, round % kQBufs);
+            if (work_item<kMask>(p, round + kQBufs, wn)) load_q(wn, round % kQBufs);
         }
     } else if (warp >= 4) {
         if (!kVLo) regs_give<kRegsControl>();
@@ -480,9 +483,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 bool     ok = true;
                 PROF_VARS;
                 PROF_START();
-                for (int round = 0; ok && work_item(p, round, w); ++round) {
+                for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
                     const int kvh = w.head / p.gqa;
-                    for (int j = next_live(w, 0); j < w.n_tiles && !aborted(); j = next_live(w, j + 1), ++T) {
+                    for (int j = next_live<kMask>(w, 0); j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1), ++T) {
                         const int      st = T % kSt;
                         const uint32_t ph = ((T / kSt) - 1) & 1;
                         PROF_STOP(0);
@@ -529,8 +532,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // they need.
                 WorkItem wq;
                 int      rq = 0, jq = 0, Tq = 0;
-                bool     have_q = work_item(p, 0, wq), first_q = true;
-                if (have_q) jq = next_live(wq, 0);
+                bool     have_q = work_item<kMask>(p, 0, wq), first_q = true;
+                if (have_q) jq = next_live<kMask>(wq, 0);
                 auto issue_qk = [&]() {
                     if (!have_q) return true;
                     PROF_STOP(0);
@@ -554,11 +557,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
                     ++Tq;
-                    jq = next_live(wq, jq + 1);
+                    jq = next_live<kMask>(wq, jq + 1);
                     if (jq >= wq.n_tiles) {
                         first_q = true;
-                        have_q  = work_item(p, ++rq, wq);
-                        if (have_q) jq = next_live(wq, 0);
+                        have_q  = work_item<kMask>(p, ++rq, wq);
+                        if (have_q) jq = next_live<kMask>(wq, 0);
                     }
                     return true;
                 };
@@ -567,11 +570,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 bool     ok = true;
                 PROF_START();
                 if (!issue_qk() || !issue_qk()) { give_up(); ok = false; }
-                for (int round = 0; ok && work_item(p, round, w); ++round) {
-                    const int j_first = next_live(w, 0);
+                for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
+                    const int j_first = next_live<kMask>(w, 0);
                     for (int j = j_first; j < w.n_tiles && !aborted(); ++T) {
                         const int st     = T % kSt;
-                        const int j_next = next_live(w, j + 1);
+                        const int j_next = next_live<kMask>(w, j + 1);
                         PROF_STOP(0);
                         if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kSt) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(3);
@@ -622,7 +625,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         bool     ok = true;
         PROF_VARS;
         PROF_START();
-        for (int round = 0; ok && work_item(p, round, w); ++round) {
+        for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
             const int  qpos  = w.q0 + row;
             const int  limit = min(qpos + p.causal_offset, p.n_kv - 1);  // last key this row may see
             // last key any row of this warp may see (rows beyond n_q compute on zeros and are not stored)
@@ -640,8 +643,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             // the scores are multiplied by `mul` on their way into the exponent: with a mask they have been put into
             // natural units (scale * S + mask) first
             const float mul = kMask ? 1.4426950408889634f : p.scale_log2;
-            const int j_first = next_live(w, 0);
-            for (int j = j_first; j < w.n_tiles && !aborted(); j = next_live(w, j + 1), ++T) {
+            const int j_first = next_live<kMask>(w, 0);
+            for (int j = j_first; j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1), ++T) {
                 const int sb = T & 1;
                 const int k0 = j * kKeys;
                 uint4     mv[8];
