@@ -36,7 +36,10 @@ typedef enum {
     VOX_ATTN_WORKSPACE_TOO_SMALL = 3,
     VOX_ATTN_CUDA_ERROR          = 4, /* a CUDA runtime/driver call failed; see error string    */
     VOX_ATTN_TIMEOUT             = 5, /* a bounded device-side wait ran out (status word)       */
-    VOX_ATTN_OUT_OF_MEMORY       = 6
+    VOX_ATTN_OUT_OF_MEMORY       = 6,
+    VOX_ATTN_DEVICE_STATE        = 7  /* a kernel found device-side state that does not fit the call: a
+                                         stream's kv_len beyond its cache rows (status word); the row was
+                                         not stored                                                     */
 } vox_status;
 
 /* numbered as ggml numbers them (ggml.h enum ggml_type) */
@@ -301,6 +304,11 @@ typedef struct {
     int32_t max_len;
     int32_t kv_type;                       /* VOX_TYPE_F16 | VOX_TYPE_Q8_0 */
     int32_t locdit_layers, locdit_seq, cfm_steps; /* 8, 9, 10 */
+    /* Timesteps at the start of a patch that evaluate no network: UnifiedCFM::solve_euler with
+     * cfg-zero-star sets dphi_dt = 0 for step <= max(1, 0.04 * (n_steps + 1)) (src/unified_cfm.cpp:107-116),
+     * i.e. 1 of 10.  Those steps issue no launch, move no data in vox_group_step_host and leave their
+     * slice of dit_out untouched.  0: every timestep evaluates the network. */
+    int32_t cfm_zero_init_steps;
 } vox_group_config;
 
 /* Device (or, for vox_group_step_host, pinned host) buffers of one step.

@@ -22,7 +22,8 @@ F32, F16, Q8_0 = 0, 1, 8
 PATH_AUTO, PATH_ROW, PATH_ROW_F32, PATH_TILED, PATH_F64, PATH_SPLIT_KV = 0, 1, 2, 3, 4, 5
 
 
-REFERENCE_DIR = os.environ.get("VOX_REFERENCE_DIR", "/root/reference")  # checkout of the reference project, if any
+# checkout of the reference project, if any: VOX_REFERENCE_DIR, or a directory named "reference" beside this repository
+REFERENCE_DIR = os.environ.get("VOX_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def build(ref: bool = True) -> None:
@@ -30,6 +31,8 @@ def build(ref: bool = True) -> None:
     subprocess.run(["make", "-C", HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
     if ref and os.path.exists(os.path.join(REFERENCE_DIR, "third_party/ggml/src/ggml.c")):
         subprocess.run(["make", "-C", HERE, "-j8", "ref", f"REF={REFERENCE_DIR}"], check=True, stdout=subprocess.DEVNULL)
+        # a graph node built with the reference's ggml.h, run through include/vox_attn_ggml.h (needs the engine library)
+        subprocess.run(["make", "-C", HERE, "probe", f"REF={REFERENCE_DIR}"], check=True, stdout=subprocess.DEVNULL)
 
 
 def _ptr(a):

@@ -86,19 +86,26 @@ def test_mask_must_be_contiguous_f16_and_broadcastable(pkg, L):
 
 
 def test_workspace_sizing(pkg, L):
-    # a short cache fits one chunk per (stream, kv head): no partials, no workspace
-    assert L.vox_attn_decode_workspace_bytes(1, 16, 2, 64) == 0
+    # two partial slots (8 heads x 66 floats each) per CTA of the launch: one CTA for a short cache ...
+    slot = 8 * 66 * 4
+    assert L.vox_attn_decode_workspace_bytes(1, 16, 2, 64) == 2 * slot
+    # ... a run of at least 4 tiles per CTA while the launch is small (2 pairs x 16 tiles) ...
+    assert L.vox_attn_decode_workspace_bytes(1, 16, 2, 1024) == 2 * 8 * slot
+    # ... and never more than one wave of CTAs (4 per SM on 148 SMs), whatever the streams and their lengths
     big = L.vox_attn_decode_workspace_bytes(32, 16, 2, 8192)
-    assert big > 0 and big % (66 * 4) == 0
+    assert big == 2 * 4 * 148 * slot
+    assert L.vox_attn_decode_workspace_bytes(4096, 16, 2, 65536) == big
     assert L.vox_attn_workspace_bytes(C.byref(_args(pkg, n_kv=8192, B=32))) == big
     assert L.vox_attn_workspace_bytes(C.byref(_args(pkg, n_q=9, n_kv=9, kv_type=0))) == 0
-    assert L.vox_attn_decode_workspace_bytes(0, 16, 2, 64) == 0
+    for bad in [(0, 16, 2, 64), (-1, 16, 2, 64), (1, 0, 2, 64), (1, 16, 0, 64), (1, 15, 2, 64)]:
+        assert L.vox_attn_decode_workspace_bytes(*bad) == 0
 
 
 def test_entry_points_reject_null_without_a_gpu(L):
     assert L.vox_engine_create(0, None) == 1
     assert L.vox_attn_forward(None, None, None, 0, None) == 1
     assert L.vox_attn_decode(None, None, None, 0, None) == 1
+    assert L.vox_attn_decode_static(None, None, None) == 1
     assert L.vox_attn_locdit_step(None, None, None) == 1
     assert L.vox_kv_create(None, None, None) == 1
     assert L.vox_group_create(None, None, None) == 1

@@ -380,11 +380,15 @@ def test_decode_stores_the_arriving_row_itself(kv, engine, pkg, oracle, vo):
     assert torch.equal(got, want)
     # the same call with the promise that lengths and cache are older than the previous kernel (tiles are then
     # requested before the dependency wait): same row stored again, same bits out
-    # ... and with the streams taken up longest first instead of in index order
+    again = two[1].decode(1, dev(q), kv_len, max(lens), k_new=dev(k_new), v_new=dev(v_new), cache_stable=True)
+    engine.sync_status()
+    assert torch.equal(again, want)
+    # ... and with the streams listed longest first instead of in index order: the work list is then cut at other
+    # places, so the partial sums are folded in another order (the same values up to f32 rounding)
     order = np.argsort(-np.array(lens), kind="stable").astype(np.int32)
     again = two[1].decode(1, dev(q), kv_len, max(lens), k_new=dev(k_new), v_new=dev(v_new), cache_stable=True, stream_order=dev(order))
     engine.sync_status()
-    assert torch.equal(again, want)
+    assert rel_err(again.cpu().numpy(), want.cpu().numpy()) < TOL[kv] / 50
     out = got.cpu().numpy()
     for s, n in enumerate(lens):
         a, b = two[0].export(1, s, cap), two[1].export(1, s, cap)
@@ -404,7 +408,7 @@ def test_decode_with_arriving_row_reports_a_stream_beyond_capacity(engine, pkg):
     cache.decode(0, q, dev(np.array([65, 3], np.int32)), 64, k_new=rows, v_new=rows)  # stream 0 claims 65 rows of 64
     with pytest.raises(pkg.VoxError) as e:
         engine.sync_status()
-    assert e.value.status_name == "TIMEOUT" and "bad state" in str(e.value)
+    assert e.value.status_name == "DEVICE_STATE" and "longer than its cache rows" in str(e.value)
     k0, _ = cache.export(0, 0, 64)
     assert not k0.view(np.uint8).any()  # nothing was written for the stream that does not fit
     k1, _ = cache.export(0, 1, 64)
@@ -735,3 +739,133 @@ def test_group_refuses_to_outgrow_capacity(engine, pkg):
     assert e.value.status_name == "INVALID_ARGUMENT"
     with pytest.raises(pkg.VoxError):
         g.set_kv_len(np.array([65, 3], np.int32))
+
+
+# Distance of the engine's f16 / q8_0 cache from the reference's F32 cache (src/minicpm.cpp:182-183 stores F32 rows
+# and attends over them unrounded), max-abs over the RMS of the output, on N(0,1) rows.  f16 storage stays inside
+# the 2e-3 parity bound; q8_0 storage cannot (the reference's own q8_0 K/V type is as far from its F32 cache): what
+# is asserted for it is the bound that the storage format itself implies, and the measured figure is printed.
+STORAGE_BOUND = {"f16": 2e-3, "q8_0": 8e-2}
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+@pytest.mark.parametrize("n_kv", [1024, 4096])
+def test_cache_storage_against_the_reference_f32_cache(kv, n_kv, engine, pkg, oracle, vo, capsys):
+    """f32 K/V rows go in through vox_kv_append (all but the last) and through the decode launch's own store (the last,
+    k_new / v_new); the result is compared with the reference's attention over the ORIGINAL f32 rows, i.e. with what
+    MiniCPMKVCache's F32 storage would have given."""
+    import torch
+    rng = np.random.default_rng(n_kv + len(kv))
+    k = rng.standard_normal((1, n_kv, HK, D)).astype(np.float32)
+    v = rng.standard_normal((1, n_kv, HK, D)).astype(np.float32)
+    q = rng.standard_normal((1, H, D)).astype(np.float32)
+    cache = pkg.KVCache(engine, 1, 1, HK, n_kv, KV_TYPE[kv])
+    cache.append(0, dev(k[:, :-1]), dev(v[:, :-1]), pos0=0)
+    out = cache.decode(0, dev(q), dev(np.array([n_kv], np.int32)), n_kv, k_new=dev(k[:, -1]), v_new=dev(v[:, -1]))
+    engine.sync_status()
+    kf, vf = k[0].transpose(1, 0, 2)[None], v[0].transpose(1, 0, 2)[None]  # [1, HK, n_kv, D]
+    ref = oracle.attn(q[0][None, :, None, :], np.ascontiguousarray(kf), np.ascontiguousarray(vf), kv_type=vo.F32, path=vo.PATH_ROW_F32)[0, 0]
+    err = rel_err(out.cpu().numpy()[0], ref)
+    with capsys.disabled():
+        print(f"\n[storage deviation] {kv} cache, {n_kv} rows, against the reference's F32 cache: {err:.2e} of the output RMS")
+    assert err < STORAGE_BOUND[kv]
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+def test_two_caches_decode_on_two_streams_at_once(kv, engine, pkg):
+    """Two caches of one engine (backbone and residual stacks, say) decoding on two CUDA streams with their own
+    workspaces: the split-KV tickets belong to each cache's layer, so the launches may overlap on the GPU and give the
+    same bits as when they run one after the other."""
+    import torch
+    lens = [4096, 300, 2048, 1500, 64, 3000]
+    S = len(lens)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    caches, qs = [], []
+    for i in range(2):
+        c = pkg.KVCache(engine, 1, S, HK, 4096, KV_TYPE[kv])
+        c.append(0, torch.randn((S, 4096, HK, D), device="cuda", generator=gen), torch.randn((S, 4096, HK, D), device="cuda", generator=gen), pos0=0)
+        caches.append(c)
+        qs.append(torch.randn((S, H, D), device="cuda", generator=gen))
+    kv_len = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    need = pkg.lib().vox_attn_decode_workspace_bytes(S, H, HK, 4096)
+    ws = [torch.empty(need, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    serial = [torch.empty((S, H, D), device="cuda") for _ in range(2)]
+    both = [torch.empty((S, H, D), device="cuda") for _ in range(2)]
+
+    def call(i, dst, stream):
+        a = caches[i]._decode_args(0, qs[i], kv_len, 4096, dst, 0.125, None, None, False, None, None)
+        rc = pkg.lib().vox_attn_decode(engine.h, C.byref(a), C.c_void_p(ws[i].data_ptr()), need, C.c_void_p(stream.cuda_stream))
+        assert rc == 0
+
+    main = torch.cuda.current_stream()
+    for i in range(2):
+        call(i, serial[i], main)
+        torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for rep in range(20):  # many pairs of launches: some of them overlap
+        for i in range(2):
+            streams[i].wait_stream(main)
+            call(i, both[i], streams[i])
+    for s in streams:
+        s.synchronize()
+    engine.sync_status()
+    for i in range(2):
+        assert torch.equal(both[i], serial[i])
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+@pytest.mark.parametrize("n_kv, planes", [(700, 1), (2049, 16), (64, 2)])
+def test_single_token_forward_with_a_mask(kv, n_kv, planes, engine, oracle, vo):
+    """n_q == 1 with an additive mask (third_party/ggml/src/ggml-cpu/ops.cpp:8233-8237): the split-KV decode kernel adds
+    the mask row of each head's plane to its scores.  Random finite biases, 30 % of the keys hidden, one (batch, plane)
+    that sees nothing at all (zeros), an odd number of keys."""
+    B = 3
+    rng = np.random.default_rng(n_kv + planes)
+    q = rng.standard_normal((B, H, 1, D)).astype(np.float32)
+    k = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, n_kv, D)).astype(np.float32)
+    if kv == "q8_0":
+        ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+    else:
+        ks, vs = k.astype(np.float16), v.astype(np.float16)
+    mask = np.where(rng.random((B, planes, 1, n_kv)) < 0.3, -np.inf, rng.integers(-8, 1, (B, planes, 1, n_kv)) / 4.0).astype(np.float16)
+    mask[..., 0] = 0.0
+    mask[1, planes - 1, 0, :] = -np.inf
+    launches = engine.launches
+    out = engine.forward(dev(q), dev(ks), dev(vs), dev(mask))
+    engine.sync_status()
+    assert engine.launches - launches == (2 if kv == "q8_0" else 1)  # decode kernel (after the block repack for q8_0), not the general one
+    out = out.cpu().numpy()
+    ref = oracle.attn(q, ks, vs, mask, kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)
+    assert rel_err(out, ref) < TOL[kv]
+    heads_of_last_plane = [h for h in range(H) if h % planes == planes - 1]
+    assert np.all(out[1, 0, heads_of_last_plane] == 0.0)
+
+
+def test_replay_past_the_capacity_is_reported(engine, pkg):
+    """A captured step replayed once more than the cache has rows for: the host check of vox_group_advance comes after
+    the replay, so it is the decode launch that notices (the stream's length is beyond its rows), stores nothing for it
+    and raises the status word; the engine reports DEVICE_STATE and keeps working."""
+    import torch
+    g = pkg.Group(engine, n_streams=2, max_len=128, kv_type=pkg.F16, base_layers=1, res_layers=0, locdit_layers=0, cfm_steps=0)
+    g.set_kv_len(np.array([126, 5], np.int32))
+    g.set_bound(128)
+    bufs = {n: torch.randn(s, device="cuda") for n, s in g.buffer_shapes().items() if n.startswith("lm_")}
+    side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    g.step(bufs, advance=False)  # attributes and descriptors outside the capture
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            g.step(bufs, advance=True, stream=side)
+    for _ in range(2):  # rows 127 and 128: both fit
+        graph.replay()
+        g.advance(1)
+    engine.sync_status()
+    graph.replay()     # row 129 of 128
+    with pytest.raises(pkg.VoxError) as e:
+        engine.sync_status()
+    assert e.value.status_name == "DEVICE_STATE"
+    with pytest.raises(pkg.VoxError):
+        g.advance(1)   # and the host bookkeeping refuses to follow
+    engine.sync_status()
+    g.close()

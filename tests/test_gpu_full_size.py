@@ -318,3 +318,73 @@ def test_locdit_patch_of_256_streams(engine, oracle, vo):
     for s, l in [(0, 0), (255, 7), (100, 3)]:
         ref = oracle.attn(q[s, l].cpu().numpy(), k[s, l].cpu().numpy(), v1[s, l].cpu().numpy(), kv_type=vo.F32, path=vo.PATH_ROW_F32)
         assert rel_err(o1[s, l].cpu().numpy(), ref) < TOL["f32"]
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8_0"])
+@pytest.mark.parametrize("n_kv", [2048, 8192])
+def test_decode_sweep_batch_32(kv, n_kv, engine, pkg, oracle, vo):
+    """The long-form decode sweep at batch 32 (32 streams of equal length, 2048 and 8192 rows, both cache types): the
+    shapes whose launch is one full wave of CTAs with runs that start and end inside (stream, kv head) pairs.  Rows go
+    in through the engine's append, a sample of streams (first, last, two in the middle) is exported as stored and
+    checked against the oracle's accurate path; every stream is checked for finiteness and, with a constant V in
+    a second layer, for weights that sum to one."""
+    import torch
+    S = 32
+    gen = torch.Generator(device="cuda").manual_seed(n_kv + (7 if kv == "q8_0" else 0))
+    cache = pkg.KVCache(engine, 2, S, HK, n_kv, KV_TYPE[kv])
+    k = torch.randn((S, n_kv, HK, D), device="cuda", generator=gen)
+    v = torch.randn((S, n_kv, HK, D), device="cuda", generator=gen)
+    cache.append(0, k, v, pos0=0)
+    cache.append(1, k, torch.full_like(v, 0.75), pos0=0)
+    q = torch.randn((S, H, D), device="cuda", generator=gen)
+    kv_len = torch.full((S,), n_kv, dtype=torch.int32, device="cuda")
+    out = cache.decode(0, q, kv_len, n_kv)
+    flat = cache.decode(1, q, kv_len, n_kv)
+    engine.sync_status()
+    assert torch.isfinite(out).all()
+    assert (flat - 0.75).abs().max().item() < 2e-3  # 0.75 is exact in f16 and q8_0: the weights sum to one
+    out, qh = out.cpu().numpy(), q.cpu().numpy()
+    for s in (0, 11, 20, S - 1):
+        ks, vs = cache.export(0, s, n_kv)
+        ref = oracle.attn(qh[s][None, :, None, :], ks[None], vs[None], kv_type=KV_TYPE[kv], path=vo.PATH_ROW_F32)[0, 0]
+        assert rel_err(out[s], ref) < TOL[kv], f"stream {s}"
+
+
+@pytest.mark.parametrize("form", ["q8_0", "mask"])
+def test_prefill_many_items_per_cta_with_a_partial_last_tile(form, engine, oracle, vo):
+    """Four or more work items per persistent CTA, in the two forms of the tensor-core kernel whose Q tiles and score
+    buffers are handed back and forth most often: q8_0 operands (value + remainder tiles, one CTA per SM: 13 x 16 x 3 =
+    624 items on 148 CTAs) and an explicit mask (two CTAs per SM: 25 x 16 x 3 = 1200 items on 296).  300 tokens: the
+    last query tile holds 44 rows and the last key tile 44 keys.  Checked in full against an f32 softmax over the
+    values the operands hold."""
+    import torch
+    L = 300
+    B = 13 if form == "q8_0" else 25
+    rng = np.random.default_rng(77)
+    q = rng.standard_normal((B, H, L, D)).astype(np.float32)
+    k = rng.standard_normal((B, HK, L, D)).astype(np.float32)
+    v = rng.standard_normal((B, HK, L, D)).astype(np.float32)
+    causal = oracle.causal_mask(np.arange(L), L)[None, None]
+    if form == "q8_0":
+        ks, vs = oracle.quantize_q8_0(k), oracle.quantize_q8_0(v)
+        kf, vf = oracle.dequantize_q8_0(ks), oracle.dequantize_q8_0(vs)
+        out = engine.prefill(dev(q), dev(ks), dev(vs))
+        tol = 2e-4
+    else:
+        q = q.astype(np.float16).astype(np.float32)
+        ks, vs = k.astype(np.float16), v.astype(np.float16)
+        kf, vf = ks.astype(np.float32), vs.astype(np.float32)
+        out = engine.forward(dev(q), dev(ks), dev(vs), dev(causal))
+        tol = 2e-4
+    engine.sync_status()
+    qd = dev(q)
+    kk, vv = dev(kf).repeat_interleave(H // HK, dim=1), dev(vf).repeat_interleave(H // HK, dim=1)
+    s = torch.einsum("bhqd,bhkd->bhqk", qd, kk) * 0.125 + dev(causal).float()
+    ref = torch.einsum("bhqk,bhkd->bqhd", torch.softmax(s, dim=-1), vv)
+    rms = ref.pow(2).mean().sqrt().item()
+    assert torch.isfinite(out).all()
+    err = (out - ref).abs().max().item() / rms
+    assert err < tol, f"{form}: {err:.2e}"
+    b = B - 1
+    o_ref = oracle.attn(q[b:b + 1], ks[b:b + 1], vs[b:b + 1], causal, kv_type=vo.Q8_0 if form == "q8_0" else vo.F16, path=vo.PATH_ROW_F32)
+    assert rel_err(out[b:b + 1].cpu().numpy(), o_ref) < TOL["f16"]

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(HERE)
 F32, F16, Q8_0 = 0, 1, 8
 
 STATUS = {0: "OK", 1: "INVALID_ARGUMENT", 2: "UNSUPPORTED", 3: "WORKSPACE_TOO_SMALL", 4: "CUDA_ERROR", 5: "TIMEOUT",
-          6: "OUT_OF_MEMORY"}
+          6: "OUT_OF_MEMORY", 7: "DEVICE_STATE"}
 
 
 class VoxError(RuntimeError):
@@ -90,7 +90,8 @@ class LocditArgs(C.Structure):
 class GroupConfig(C.Structure):
     _fields_ = [("n_streams", C.c_int32), ("base_layers", C.c_int32), ("res_layers", C.c_int32), ("n_heads", C.c_int32),
                 ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("max_len", C.c_int32), ("kv_type", C.c_int32),
-                ("locdit_layers", C.c_int32), ("locdit_seq", C.c_int32), ("cfm_steps", C.c_int32)]
+                ("locdit_layers", C.c_int32), ("locdit_seq", C.c_int32), ("cfm_steps", C.c_int32),
+                ("cfm_zero_init_steps", C.c_int32)]
 
 
 class StepBuffers(C.Structure):
@@ -359,6 +360,20 @@ class KVCache:
     def copy_from(self, other: "KVCache", stream=None):
         _check(lib().vox_kv_copy_from(self.h, other.h, _stream_ptr(stream)))
 
+    def _decode_args(self, layer, q, kv_len, kv_bound, dst, scale, k_new, v_new, cache_stable, rope_table, stream_order):
+        S, H, D = q.shape
+        a = DecodeArgs(self.h, layer, S, H, kv_len.data_ptr(), kv_bound, q.data_ptr(), q.stride(1) * 4, q.stride(0) * 4,
+                       dst.data_ptr(), scale)
+        a.flags = 1 if cache_stable else 0
+        a.rope_table = rope_table.data_ptr() if rope_table is not None else None
+        a.stream_order = stream_order.data_ptr() if stream_order is not None else None
+        if k_new is not None or v_new is not None:
+            a.k_new = k_new.data_ptr() if k_new is not None else None
+            a.v_new = v_new.data_ptr() if v_new is not None else None
+            ref = k_new if k_new is not None else v_new
+            a.new_nb_head, a.new_nb_stream = ref.stride(1) * 4, ref.stride(0) * 4
+        return a
+
     def decode(self, layer, q, kv_len, kv_bound, scale=0.125, stream=None, dst=None, k_new=None, v_new=None, cache_stable=False,
                rope_table=None, stream_order=None):
         """q [n_streams, H, 64] f32, kv_len int32 device [n_streams] -> [n_streams, H, 64].
@@ -371,25 +386,14 @@ class KVCache:
             dst = torch.empty((S, H, D), dtype=torch.float32, device=q.device)
         ws_bytes = lib().vox_attn_decode_workspace_bytes(S, H, self.cfg.n_kv_heads, kv_bound)
         ws = self.engine.workspace(ws_bytes)
-        a = DecodeArgs(self.h, layer, S, H, kv_len.data_ptr(), kv_bound, q.data_ptr(), q.stride(1) * 4, q.stride(0) * 4,
-                       dst.data_ptr(), scale)
-        a.flags = 1 if cache_stable else 0
-        a.rope_table = rope_table.data_ptr() if rope_table is not None else None
-        a.stream_order = stream_order.data_ptr() if stream_order is not None else None
-        if k_new is not None or v_new is not None:
-            a.k_new = k_new.data_ptr() if k_new is not None else None
-            a.v_new = v_new.data_ptr() if v_new is not None else None
-            ref = k_new if k_new is not None else v_new
-            a.new_nb_head, a.new_nb_stream = ref.stride(1) * 4, ref.stride(0) * 4
+        a = self._decode_args(layer, q, kv_len, kv_bound, dst, scale, k_new, v_new, cache_stable, rope_table, stream_order)
         _check(lib().vox_attn_decode(self.engine.h, C.byref(a), C.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(stream)))
         return dst
 
-    def decode_static(self, layer, q, kv_len, kv_bound, dst, scale=0.125, stream=None):
+    def decode_static(self, layer, q, kv_len, kv_bound, dst, scale=0.125, stream=None, k_new=None, v_new=None, rope_table=None):
         """``vox_attn_decode_static``: the caller passes inputs and the output only; the split-KV
         scratch is the array built into the library, so nothing is allocated by the call."""
-        S, H, D = q.shape
-        a = DecodeArgs(self.h, layer, S, H, kv_len.data_ptr(), kv_bound, q.data_ptr(), q.stride(1) * 4, q.stride(0) * 4,
-                       dst.data_ptr(), scale)
+        a = self._decode_args(layer, q, kv_len, kv_bound, dst, scale, k_new, v_new, False, rope_table, None)
         _check(lib().vox_attn_decode_static(self.engine.h, C.byref(a), _stream_ptr(stream)))
         return dst
 
@@ -398,10 +402,10 @@ class Group:
     """``vox_group``: all streams one GPU serves, and the attention of one decode step."""
 
     def __init__(self, engine: Engine, n_streams, max_len=4096, kv_type=F16, base_layers=24, res_layers=6, n_heads=16,
-                 n_kv_heads=2, locdit_layers=8, locdit_seq=9, cfm_steps=10):
+                 n_kv_heads=2, locdit_layers=8, locdit_seq=9, cfm_steps=10, cfm_zero_init_steps=0):
         self.engine = engine
         self.cfg = GroupConfig(n_streams, base_layers, res_layers, n_heads, n_kv_heads, 64, max_len, kv_type,
-                               locdit_layers, locdit_seq, cfm_steps)
+                               locdit_layers, locdit_seq, cfm_steps, cfm_zero_init_steps)
         h = C.c_void_p()
         _check(lib().vox_group_create(engine.h, C.byref(self.cfg), C.byref(h)))
         self.h = h

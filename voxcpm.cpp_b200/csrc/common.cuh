@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <utility>
+#include <vector>
 
 #include "vox_attn.h"
 
@@ -40,7 +41,8 @@ void set_error(const char * fmt, ...);
     } while (0)
 
 constexpr int kHeadDim = 64;
-constexpr int kCounterSlots = 1 << 16;
+constexpr int kCounterSlots = 1 << 16;  // engine-owned split-KV tickets (operator calls on the caller's own tensors)
+constexpr int kDecodeMaxSms = 148;      // a decode grid never spans more SMs than this (bounds its workspace)
 
 // bits of the device status word
 enum : int { kStatusTimeout = 1, kStatusBadState = 2 };
@@ -51,6 +53,8 @@ typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32
 
 }  // namespace vox
 
+struct vox_kv_cache;
+
 struct vox_engine {
     int               device       = 0;
     int               sm_count     = 0;
@@ -59,6 +63,10 @@ struct vox_engine {
     uint64_t          launches     = 0;
     int *             counters_dev = nullptr;  // kCounterSlots zeroed ints: split-KV arrival tickets
     uint32_t          attr_mask    = 0;      // kernels whose shared-memory attribute was set on this device
+    // developer settings, read from the environment once, when the engine is created
+    int               decode_wave[2] = {0, 0};  // VOX_DECODE_WAVE / VOX_DECODE_WAVE_Q8: CTAs per SM of a decode grid (0: all that fit)
+    int               prefill_single_f16 = 0;   // VOX_PREFILL_WEIGHTS=f16: softmax weights as one f16 (comparison only)
+    std::vector<vox_kv_cache *> caches;         // caches created from this engine (their ticket counters are reset after a failure)
     vox::encode_tiled_fn encode    = nullptr;
     // staging for the *_host entry points
     void *            stage_dev    = nullptr;

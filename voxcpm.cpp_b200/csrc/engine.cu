@@ -18,13 +18,17 @@ void set_error(const char * fmt, ...) {
     va_end(ap);
 }
 
-bool pdl_enabled() {
-    static const bool on = [] {
-        const char * s = getenv("VOX_NO_PDL");
-        return !(s && s[0] == '1');
-    }();
-    return on;
+// Developer settings come from the environment exactly once per process (the first engine created reads them);
+// nothing on a launch path calls getenv.
+static int env_int(const char * name) {
+    const char * s = getenv(name);
+    return s ? atoi(s) : 0;
 }
+static bool g_pdl_on = true;
+
+bool pdl_enabled() { return g_pdl_on; }
+
+void reset_ticket_counters(vox_engine * e, cudaStream_t stream);
 
 int make_tensor_map(const vox_engine * e, CUtensorMap * out, void * base, CUtensorMapDataType dt, const uint64_t dims[5],
                     const uint64_t strides[4], const uint32_t box[5], CUtensorMapSwizzle swizzle) {
@@ -79,6 +83,7 @@ const char * vox_attn_status_string(int status) {
         case VOX_ATTN_CUDA_ERROR: return "CUDA error";
         case VOX_ATTN_TIMEOUT: return "device-side wait timed out";
         case VOX_ATTN_OUT_OF_MEMORY: return "out of memory";
+        case VOX_ATTN_DEVICE_STATE: return "device-side state does not fit the call";
         default: return "unknown status";
     }
 }
@@ -101,6 +106,14 @@ int vox_engine_create(int device, vox_engine ** out) {
     VOX_REQUIRE(e != nullptr, VOX_ATTN_OUT_OF_MEMORY, "out of host memory");
     e->device   = device;
     e->sm_count = prop.multiProcessorCount;
+    {
+        const char * s = getenv("VOX_NO_PDL");
+        g_pdl_on = !(s && s[0] == '1');
+        e->decode_wave[0] = env_int("VOX_DECODE_WAVE");
+        e->decode_wave[1] = env_int("VOX_DECODE_WAVE_Q8");
+        const char * w = getenv("VOX_PREFILL_WEIGHTS");
+        e->prefill_single_f16 = (w && w[0] == 'f') ? 1 : 0;
+    }
 
     cudaError_t err = cudaHostAlloc(reinterpret_cast<void **>(&e->status_host), sizeof(int) * 4, cudaHostAllocMapped);
     if (err == cudaSuccess) {
@@ -164,10 +177,13 @@ int vox_engine_sync_status(vox_engine * e, void * stream) {
     const int word = *reinterpret_cast<volatile int *>(e->status_host);
     if (word != 0) {
         *reinterpret_cast<volatile int *>(e->status_host) = 0;
-        cudaMemset(e->counters_dev, 0, sizeof(int) * kCounterSlots);  // a kernel that gave up may have left tickets behind
-        set_error("device status word 0x%x: %s", word,
-                  (word & kStatusTimeout) ? "a bounded wait on a copy barrier ran out" : "kernel reported bad state");
-        return VOX_ATTN_TIMEOUT;
+        reset_ticket_counters(e, static_cast<cudaStream_t>(stream));  // a kernel that gave up may have left tickets behind
+        if (word & kStatusTimeout) {
+            set_error("device status word 0x%x: a bounded wait on a copy barrier ran out", word);
+            return VOX_ATTN_TIMEOUT;
+        }
+        set_error("device status word 0x%x: a kernel found a stream longer than its cache rows; that row was not stored", word);
+        return VOX_ATTN_DEVICE_STATE;
     }
     return VOX_ATTN_OK;
 }

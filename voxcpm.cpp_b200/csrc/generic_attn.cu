@@ -14,11 +14,11 @@
 using namespace vox;
 
 namespace vox {
-int    launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorMap & map_v, int layer, int max_len,
-                         int n_streams, int n_heads, int n_kv_heads, const int32_t * kv_len, int kv_len_const,
-                         int kv_bound, const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst, float scale,
-                         void * workspace, size_t workspace_bytes, cudaStream_t stream);
+int    launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorMap & map_v, int n_kv, int n_streams,
+                         int n_heads, int n_kv_heads, const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst,
+                         float scale, const vox_tensor * mask, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);
+bool   decode_mask_ok(const vox_attn_args * a);
 // single-token calls over q8_0 K/V in block layout: taken apart into planes in the workspace (decode_attn.cu)
 bool   decode_q8_blocks_route_ok(const vox_attn_args * a);
 size_t decode_q8_blocks_workspace_bytes(const vox_attn_args * a);
@@ -159,10 +159,12 @@ int validate(const vox_attn_args * a, bool need_data) {
     return VOX_ATTN_OK;
 }
 
-// n_q == 1, f16 K/V with 16-byte-aligned strides, no mask, GQA <= 8: the split-KV decode kernel
+// n_q == 1, f16 K/V with 16-byte-aligned strides, no mask or one whose rows can be read two values at a time,
+// GQA <= 8: the split-KV decode kernel
 bool decode_route_ok(const vox_attn_args * a) {
     const vox_tensor &q = a->q, &k = a->k, &v = a->v;
-    if (q.ne[1] != 1 || a->mask.data != nullptr) return false;
+    if (q.ne[1] != 1 || !decode_mask_ok(a)) return false;
+    if (q.ne[3] * k.ne[2] > kCounterSlots) return false;
     if (k.type != VOX_TYPE_F16 || v.type != VOX_TYPE_F16) return false;
     if (k.ne[2] != v.ne[2] || q.ne[2] / k.ne[2] > 8) return false;
     if (k.ne[1] < 1) return false;
@@ -203,7 +205,7 @@ int vox_attn_supported(const vox_attn_args * a) { return validate(a, false) == V
 
 size_t vox_attn_workspace_bytes(const vox_attn_args * a) {
     if (validate(a, false) != VOX_ATTN_OK) return 0;
-    if (a->q.ne[1] == 1 && a->k.type == VOX_TYPE_F16 && a->v.type == VOX_TYPE_F16 && a->mask.data == nullptr)
+    if (decode_route_ok(a))
         return decode_workspace_bytes((int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2], (int) a->k.ne[1]);
     if (decode_q8_blocks_route_ok(a)) return decode_q8_blocks_workspace_bytes(a);
     return a->mask.data ? prefill_mask_workspace_bytes(a) : prefill_full_workspace_bytes(a);
@@ -214,7 +216,8 @@ int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, 
     int rc = validate(a, true);
     if (rc != VOX_ATTN_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (decode_route_ok(a)) {
+    if (decode_route_ok(a) && workspace != nullptr &&
+        workspace_bytes >= decode_workspace_bytes((int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2], (int) a->k.ne[1])) {
         // K/V of the caller described to the copy engine exactly as given: rows beyond n_kv are
         // out of bounds for the descriptor and read as zeros
         CUtensorMap    mk, mv;
@@ -229,9 +232,9 @@ int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, 
                                  CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc != VOX_ATTN_OK) return rc;
         }
-        return launch_decode_f16(e, mk, mv, 0, (int) a->k.ne[1], (int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2],
-                                 nullptr, (int) a->k.ne[1], (int) a->k.ne[1], (const float *) a->q.data, a->q.nb[2],
-                                 a->q.nb[3], (float *) a->dst.data, a->scale, workspace, workspace_bytes, st);
+        return launch_decode_f16(e, mk, mv, (int) a->k.ne[1], (int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2],
+                                 (const float *) a->q.data, a->q.nb[2], a->q.nb[3], (float *) a->dst.data, a->scale,
+                                 a->mask.data ? &a->mask : nullptr, workspace, workspace_bytes, st);
     }
     if (decode_q8_blocks_route_ok(a) && workspace != nullptr && workspace_bytes >= decode_q8_blocks_workspace_bytes(a))
         return launch_decode_q8_blocks(e, a, workspace, workspace_bytes, st);

@@ -103,6 +103,14 @@ CacheView view_of(const vox_kv_cache * c) {
 }  // namespace
 
 namespace vox {
+// after a kernel gave up (status word raised) some of a pair's CTAs may have taken tickets that nobody reset
+void reset_ticket_counters(vox_engine * e, cudaStream_t stream) {
+    cudaMemsetAsync(e->counters_dev, 0, sizeof(int) * kCounterSlots, stream);
+    for (vox_kv_cache * c : e->caches)
+        cudaMemsetAsync(c->counters, 0, sizeof(int) * (size_t) c->cfg.n_layers * c->cfg.n_streams * c->cfg.n_kv_heads, stream);
+    cudaStreamSynchronize(stream);
+}
+
 int kv_fill_synthetic(vox_kv_cache * c, const int32_t * kv_len_dev, uint64_t seed, cudaStream_t stream) {
     const long long rows = (long long) c->cfg.max_len * c->cfg.n_kv_heads * c->cfg.n_layers * c->cfg.n_streams;
     const int blocks     = (int) std::min<long long>((rows + 7) / 8, (long long) c->e->sm_count * 16);
@@ -158,6 +166,11 @@ int vox_kv_create(vox_engine * e, const vox_kv_config * cfg, vox_kv_cache ** out
         c->v_scale = base + 2 * plane + splane;
     }
     err = cudaMemset(base, 0, c->bytes);  // MiniCPMKVCache::init ends with clear()
+    if (err == cudaSuccess) {
+        const size_t n_ctr = (size_t) cfg->n_layers * cfg->n_streams * cfg->n_kv_heads;
+        err = cudaMalloc(reinterpret_cast<void **>(&c->counters), sizeof(int) * n_ctr);
+        if (err == cudaSuccess) err = cudaMemset(c->counters, 0, sizeof(int) * n_ctr);
+    }
     int rc = err == cudaSuccess ? VOX_ATTN_OK : VOX_ATTN_CUDA_ERROR;
     if (rc == VOX_ATTN_OK) {
         const uint64_t dims[5]    = {64, (uint64_t) cfg->max_len, (uint64_t) cfg->n_kv_heads, (uint64_t) cfg->n_streams,
@@ -181,13 +194,15 @@ int vox_kv_create(vox_engine * e, const vox_kv_config * cfg, vox_kv_cache ** out
                                      CU_TENSOR_MAP_SWIZZLE_NONE);
         }
     } else {
-        set_error("clearing the KV cache failed: %s", cudaGetErrorString(err));
+        set_error("clearing the KV cache or allocating its ticket counters failed: %s", cudaGetErrorString(err));
     }
     if (rc != VOX_ATTN_OK) {
         cudaFree(base);
+        if (c->counters) cudaFree(c->counters);
         delete c;
         return rc;
     }
+    e->caches.push_back(c);
     *out = c;
     return VOX_ATTN_OK;
 }
@@ -195,7 +210,11 @@ int vox_kv_create(vox_engine * e, const vox_kv_config * cfg, vox_kv_cache ** out
 void vox_kv_destroy(vox_kv_cache * c) {
     if (!c) return;
     cudaSetDevice(c->e->device);
+    auto & list = c->e->caches;
+    for (size_t i = 0; i < list.size(); ++i)
+        if (list[i] == c) { list.erase(list.begin() + i); break; }
     if (c->k_data) cudaFree(c->k_data);
+    if (c->counters) cudaFree(c->counters);
     delete c;
 }
 

@@ -17,6 +17,9 @@ struct vox_kv_cache {
     uint8_t * v_scale = nullptr;
     size_t    sb_pos = 0, sb_head = 0, sb_stream = 0, sb_layer = 0;
     size_t    bytes  = 0;
+    // split-KV arrival tickets of the decode launches on this cache: one int per (layer, stream, kv head), zero
+    // between launches.  They belong to the cache so that launches on different caches (or layers) never share one.
+    int *     counters = nullptr;
     // bulk-tensor descriptors, box = kKvTile rows
     CUtensorMap map_k, map_v;    // data planes, 5-D (64, pos, head, stream, layer)
     CUtensorMap map_ks, map_vs;  // scale planes, 5-D (2*pos halves, 1, head, stream, layer)

@@ -984,10 +984,10 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
         VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(true)));
         e->attr_mask |= 1u << 12;
     }
-    // Experiment hook: VOX_PREFILL_WEIGHTS=f16 sends the weights as one f16 part (faster; on long sequences of
-    // random data the result then misses the 2e-3 parity bound: 2.6e-3 at 640 keys).  The product path splits them.
-    const char * weights_env = std::getenv("VOX_PREFILL_WEIGHTS");
-    const bool   split_p     = !(weights_env && weights_env[0] == 'f');
+    // Developer setting (VOX_PREFILL_WEIGHTS=f16 when the engine was created): the weights as one f16 part (faster; on
+    // long sequences of random data the result then misses the 2e-3 parity bound: 2.6e-3 at 640 keys).  The product
+    // path splits them.
+    const bool   split_p     = e->prefill_single_f16 == 0;
     PrefillParams p;
     p.q = static_cast<const uint8_t *>(a->q.data);
     p.q_nb1 = a->q.nb[1]; p.q_nb2 = a->q.nb[2]; p.q_nb3 = a->q.nb[3];

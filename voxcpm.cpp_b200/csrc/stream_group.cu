@@ -4,10 +4,10 @@
 // Replaces, for attention, the per-stream loop of VoxCPMRuntime::decode
 // (src/voxcpm.cpp:1027-1128): there each stream rebuilds a ggml graph per position
 // (:485-544), runs 24 + 6 single-token attention nodes and one unrolled CFM solve with
-// 8 attention nodes per evaluation.  Here every LM layer is one append launch plus one decode
-// launch (plus a merge) for ALL streams of the group, and every CFM timestep is one launch.
-// Streams never exchange data, so several GPUs each run their own group with no collective;
-// vox_partition_streams assigns streams to GPUs.
+// 8 attention nodes per evaluation.  Here every LM layer is ONE decode launch for ALL streams of
+// the group (it stores the arriving K/V row and folds the split-KV partials itself), and every CFM
+// timestep that evaluates the network is one launch.  Streams never exchange data, so several GPUs
+// each run their own group with no collective; vox_partition_streams assigns streams to GPUs.
 #include "kv_cache.cuh"
 
 #include <algorithm>
@@ -32,7 +32,6 @@ struct vox_group {
     int              grid_bound = 0;                  // vox_group_set_bound: grids are sized for this length instead (0: exact)
     void *           workspace = nullptr;
     size_t           workspace_bytes = 0;
-    int32_t *        order_dev = nullptr;             // streams by descending length (all grow together: set once)
     // rotary embedding inside the step (vox_group_set_rope): one table per step, applied by every layer's decode
     bool             rope_on = false;
     vox_rope_config  rope{};
@@ -61,8 +60,8 @@ size_t step_bytes(const vox_group_config & c, int which) {
     switch (which) {
         case 0: return lm_layers(c) * S * (c.n_heads + 2 * (size_t) c.n_kv_heads) * D * 4;            // q + k_new + v_new
         case 1: return lm_layers(c) * S * c.n_heads * D * 4;                                            // lm_out
-        case 2: return (size_t) c.cfm_steps * S * c.locdit_layers * 2 * c.locdit_seq * (c.n_heads + 2 * (size_t) c.n_kv_heads) * D * 4;
-        case 3: return (size_t) c.cfm_steps * S * c.locdit_layers * 2 * c.locdit_seq * c.n_heads * D * 4;
+        case 2: return (size_t) (c.cfm_steps - c.cfm_zero_init_steps) * S * c.locdit_layers * 2 * c.locdit_seq * (c.n_heads + 2 * (size_t) c.n_kv_heads) * D * 4;
+        case 3: return (size_t) (c.cfm_steps - c.cfm_zero_init_steps) * S * c.locdit_layers * 2 * c.locdit_seq * c.n_heads * D * 4;
         default: return 0;
     }
 }
@@ -81,6 +80,8 @@ int vox_group_create(vox_engine * e, const vox_group_config * cfg, vox_group ** 
                     cfg->n_heads / cfg->n_kv_heads <= 8,
                 VOX_ATTN_UNSUPPORTED, "head counts %d/%d not supported", cfg->n_heads, cfg->n_kv_heads);
     VOX_REQUIRE(cfg->cfm_steps >= 0 && cfg->cfm_steps <= 16, VOX_ATTN_UNSUPPORTED, "cfm_steps %d not supported (0..16)", cfg->cfm_steps);
+    VOX_REQUIRE(cfg->cfm_zero_init_steps >= 0 && cfg->cfm_zero_init_steps <= cfg->cfm_steps, VOX_ATTN_INVALID_ARGUMENT,
+                "cfm_zero_init_steps %d must lie in [0, cfm_steps]", cfg->cfm_zero_init_steps);
     VOX_REQUIRE(cfg->locdit_seq >= 1 && cfg->locdit_seq <= 16 && cfg->locdit_layers >= 0, VOX_ATTN_UNSUPPORTED, "LocDiT shape not supported");
     VOX_CUDA_TRY(cudaSetDevice(e->device));
 
@@ -97,10 +98,8 @@ int vox_group_create(vox_engine * e, const vox_group_config * cfg, vox_group ** 
         rc = vox_kv_create(e, &kc, &g->cache[s]);
     }
     if (rc == VOX_ATTN_OK) {
-        g->workspace_bytes = vox_attn_decode_workspace_bytes(cfg->n_streams, cfg->n_heads, cfg->n_kv_heads, cfg->max_len);
-        // the plan may pick any chunk for smaller bounds: size for the finest split
-        g->workspace_bytes = std::max(g->workspace_bytes,
-                                      (size_t) cfg->n_streams * cfg->n_heads * ((cfg->max_len + 63) / 64) * 66 * sizeof(float));
+        // the grid of a decode launch, and with it the workspace, only grows with the bound
+        g->workspace_bytes = std::max<size_t>(256, vox_attn_decode_workspace_bytes(cfg->n_streams, cfg->n_heads, cfg->n_kv_heads, cfg->max_len));
         cudaError_t err = cudaMalloc(&g->workspace, g->workspace_bytes);
         if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&g->kv_len_dev), sizeof(int32_t) * cfg->n_streams);
         if (err == cudaSuccess) err = cudaMemset(g->kv_len_dev, 0, sizeof(int32_t) * cfg->n_streams);
@@ -124,7 +123,6 @@ void vox_group_destroy(vox_group * g) {
     for (int s = 0; s < 2; ++s) vox_kv_destroy(g->cache[s]);
     if (g->workspace) cudaFree(g->workspace);
     if (g->kv_len_dev) cudaFree(g->kv_len_dev);
-    if (g->order_dev) cudaFree(g->order_dev);
     if (g->rope_factors) cudaFree(g->rope_factors);
     if (g->rope_table) cudaFree(g->rope_table);
     if (g->dev_buf) cudaFree(g->dev_buf);
@@ -154,13 +152,6 @@ int vox_group_set_kv_len(vox_group * g, const int32_t * kv_len) {
     VOX_CUDA_TRY(cudaMemcpy(g->kv_len_dev, kv_len, sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
     memcpy(g->kv_len_host.data(), kv_len, sizeof(int32_t) * g->cfg.n_streams);
     g->kv_bound = bound;
-    // longest stream first: a decode launch then ends on short streams (every stream grows by one row per step, so
-    // the order holds until the lengths are set again)
-    std::vector<int32_t> order(g->cfg.n_streams);
-    for (int s = 0; s < g->cfg.n_streams; ++s) order[s] = s;
-    std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return kv_len[a] > kv_len[b]; });
-    if (!g->order_dev) VOX_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&g->order_dev), sizeof(int32_t) * g->cfg.n_streams));
-    VOX_CUDA_TRY(cudaMemcpy(g->order_dev, order.data(), sizeof(int32_t) * g->cfg.n_streams, cudaMemcpyHostToDevice));
     return VOX_ATTN_OK;
 }
 
@@ -242,7 +233,9 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
     VOX_CUDA_TRY(cudaStreamIsCapturing(st, &capture));
     const bool capturing = capture != cudaStreamCaptureStatusNone;
     if (advance) {  // the appended row becomes visible to this step's attention
-        launch_pdl(add_scalar_kernel, dim3((c.n_streams + 255) / 256), dim3(256), 0, st, g->kv_len_dev, c.n_streams, 1, c.max_len);
+        // a replayed step may run past the capacity before the host looks again: the length then stops one beyond it,
+        // which the decode launch reports (it stores nothing for such a stream)
+        launch_pdl(add_scalar_kernel, dim3((c.n_streams + 255) / 256), dim3(256), 0, st, g->kv_len_dev, c.n_streams, 1, c.max_len + 1);
         int rc = check_launch(g->e, "add_scalar_kernel");
         if (rc != VOX_ATTN_OK) return rc;
     }
@@ -261,7 +254,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         // neither the lengths nor this layer's rows (layer 0 follows the length update)
         da.flags = l > 0 ? VOX_DECODE_CACHE_STABLE : 0u;
         da.rope_table = g->rope_on ? g->rope_table : nullptr;
-        da.stream_order = g->order_dev;
+        da.stream_order = nullptr;  // every CTA of a decode launch streams an equal share of the rows whatever the order
         if (advance) {  // the token's K/V rows are stored by the decode launch itself (position kv_len-1)
             da.k_new = b->lm_k_new + (size_t) l * S * c.n_kv_heads * D;
             da.v_new = b->lm_v_new + (size_t) l * S * c.n_kv_heads * D;
@@ -284,7 +277,9 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         VOX_REQUIRE(b->dit_k && b->dit_v && b->dit_out, VOX_ATTN_INVALID_ARGUMENT, "LocDiT step buffers are null");
         const size_t q_step  = S * c.locdit_layers * 2 * c.locdit_seq * c.n_heads * D;
         const size_t kv_step = S * c.locdit_layers * 2 * c.locdit_seq * c.n_kv_heads * D;
-        for (int t = 0; t < c.cfm_steps; ++t) {
+        // the first cfm_zero_init_steps timesteps evaluate no network (UnifiedCFM::solve_euler with cfg-zero-star,
+        // src/unified_cfm.cpp:107-116: dphi_dt = 0 there), so they issue nothing and leave their slice of dit_out alone
+        for (int t = c.cfm_zero_init_steps; t < c.cfm_steps; ++t) {
             vox_locdit_args la;
             la.n_streams = c.n_streams; la.n_layers = c.locdit_layers; la.n_heads = c.n_heads; la.n_kv_heads = c.n_kv_heads;
             la.seq = c.locdit_seq; la.head_dim = c.head_dim;
@@ -341,7 +336,8 @@ int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) 
         }
     }
     VOX_CUDA_TRY(cudaEventRecord(g->ev_lm_in, g->st_copy));
-    for (size_t t = 0; t < T; ++t) {
+    const size_t T0 = c.cfm_zero_init_steps;  // timesteps that evaluate no network move no data either
+    for (size_t t = T0; t < T; ++t) {
         VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) dev.dit_q + t * dq_step, (const uint8_t *) h->dit_q + t * dq_step, dq_step, cudaMemcpyHostToDevice, g->st_copy));
         VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) dev.dit_k + t * dkv_step, (const uint8_t *) h->dit_k + t * dkv_step, dkv_step, cudaMemcpyHostToDevice, g->st_copy));
         VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) dev.dit_v + t * dkv_step, (const uint8_t *) h->dit_v + t * dkv_step, dkv_step, cudaMemcpyHostToDevice, g->st_copy));
@@ -357,7 +353,7 @@ int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) 
     if (rc != VOX_ATTN_OK) return rc;
     VOX_CUDA_TRY(cudaEventRecord(g->ev_lm_done, g->st_compute));
     const float scale = 1.0f / sqrtf((float) c.head_dim);
-    for (size_t t = 0; t < T && c.locdit_layers > 0; ++t) {
+    for (size_t t = T0; t < T && c.locdit_layers > 0; ++t) {
         VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_compute, g->ev_dit_in[t], 0));
         vox_locdit_args la;
         la.n_streams = c.n_streams; la.n_layers = c.locdit_layers; la.n_heads = c.n_heads; la.n_kv_heads = c.n_kv_heads;
@@ -375,7 +371,7 @@ int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) 
         VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_back, g->ev_lm_done, 0));
         VOX_CUDA_TRY(cudaMemcpyAsync(h->lm_out, dev.lm_out, lm_q_b, cudaMemcpyDeviceToHost, g->st_back));
     }
-    for (size_t t = 0; t < T && c.locdit_layers > 0; ++t) {
+    for (size_t t = T0; t < T && c.locdit_layers > 0; ++t) {
         VOX_CUDA_TRY(cudaStreamWaitEvent(g->st_back, g->ev_dit_done[t], 0));
         VOX_CUDA_TRY(cudaMemcpyAsync((uint8_t *) h->dit_out + t * dq_step, (const uint8_t *) dev.dit_out + t * dq_step, dq_step, cudaMemcpyDeviceToHost, g->st_back));
     }
