@@ -43,6 +43,21 @@ constexpr int kThreads       = (kConsumerWarps + 1) * 32;
 constexpr int kPartialStride = 66;  // max, sum, acc[64]
 constexpr int kMaxGqa        = 8;   // query heads per kv head (rows 0-7 of the A operand)
 
+// Developer build (-DVOX_ATTN_DEVELOPER): every CTA notes the time (globaltimer, ns) at which it passes a few points
+// of its life; vox_debug_decode_trace copies the notes out.  Compiled out of the product library.
+#ifdef VOX_ATTN_DEVELOPER
+constexpr int kTraceCtas = 1024, kTracePoints = 8;
+__device__ unsigned long long g_decode_trace[kTraceCtas][kTracePoints];
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define DECODE_TRACE(point) do { if (blockIdx.x < kTraceCtas) g_decode_trace[blockIdx.x][point] = global_ns(); } while (0)
+#else
+#define DECODE_TRACE(point)
+#endif
+
 struct DecodeParams {
     const uint8_t * q;
     size_t          q_nb_head, q_nb_stream;
@@ -231,6 +246,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) DECODE_TRACE(0);
 
     // set-up that reads nothing the previous kernel of the stream wrote: done while that kernel drains
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]);
@@ -264,6 +280,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     bool any_empty;
     const int total = cut_work_list(p, lane, run, f0, w, any_empty);
     const int f1    = min(total, f0 + run);
+    if (tid == 0) DECODE_TRACE(1);
     if (f0 >= total && blockIdx.x != 0) return;  // more CTAs than runs: nothing to do
 
     if (warp == kConsumerWarps) {
@@ -329,6 +346,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             }
             good = __shfl_sync(0xffffffffu, good, 0);
             if (!good) break;
+            if (lane == 0 && it == 0) DECODE_TRACE(6);
             issued = it + 1;
             if (++w.t == w.tiles && f + 1 < f1) walk_next_pair(p, w);
         }
@@ -336,6 +354,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             pdl_wait();
             pdl_launch_dependents();
         }
+        if (lane == 0) DECODE_TRACE(7);
         if (lane == 0 && *reinterpret_cast<volatile int *>(&abort_flag)) {
             // consumers gave up: let the copies already issued land before the CTA retires
             for (int i = max(0, issued - kStages); i < issued; ++i)
@@ -350,6 +369,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         pdl_wait();
         pdl_launch_dependents();
     }
+    if (tid == 0) DECODE_TRACE(2);
     if (blockIdx.x == 0 && any_empty) {
         // a stream with no visible rows has no tile in the list: its result is zeros (ops.cpp:8333)
         for (int i = 0; i < p.n_streams; ++i) {
@@ -441,7 +461,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         // overlap them with; max, rescale decision and row sum are then taken once per 32 rows.  Measured per 256-stream
         // launch: at 3 CTAs per SM (115 registers) 48.2 -> 45.4 us; at 4 CTAs per SM (96 registers, the configuration
         // used) 43.9 -> 43.8 us: with that register budget the compiler cannot keep both chains in flight.
-        constexpr int U = Q8 ? 2 : 1;  // f16 with two tiles per pass measured 50.6 against 49.9 us: it holds two stages at a time
+#ifndef VOX_DECODE_U_F16
+#define VOX_DECODE_U_F16 1
+#endif
+        constexpr int U = Q8 ? 2 : VOX_DECODE_U_F16;  // f16 with two tiles per pass measured 50.6 against 49.9 us: it holds two stages at a time
         for (int i = 0; i < seg && ok; i += U) {
             int  st[U], p0[U];
             bool have[U], act[U];
@@ -458,7 +481,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 }
             }
             if (!ok) break;
-#ifdef VOX_DECODE_NOMATH  // developer build: the copy structure alone
+            if (tid == 0 && it == 0 && i == 0) DECODE_TRACE(3);
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_DECODE_NOMATH)  // developer build: the copy structure alone
             if (false) {
 #else
             if (act[0]) {
@@ -617,6 +641,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (tid == 0 && f + seg >= f1) DECODE_TRACE(4);
 
         // ---- merge the four warps through the stage of the last tile (all of them are done with it after the barrier)
         named_bar_sync(1, kConsumerWarps * 32);
@@ -738,6 +763,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         w.t += seg;
         if (w.t == w.tiles && f < f1) walk_next_pair(p, w);
     }
+    if (tid == 0) DECODE_TRACE(5);
 }
 
 }  // namespace
@@ -1022,6 +1048,14 @@ int decode_checked(vox_engine * e, const vox_decode_args * a, void * workspace, 
 }
 
 }  // namespace
+
+#ifdef VOX_ATTN_DEVELOPER
+// out: kTraceCtas x kTracePoints times in ns (0 entry, 1 work list cut, 2 consumers past the dependency wait, 3 first tile
+// in shared memory, 4 last tile consumed, 5 consumers done, 6 first copy issued, 7 producer done)
+extern "C" int vox_debug_decode_trace(unsigned long long * out) {
+    return cudaMemcpyFromSymbol(out, g_decode_trace, sizeof(unsigned long long) * kTraceCtas * kTracePoints) == cudaSuccess ? 0 : 4;
+}
+#endif
 
 extern "C" {
 

@@ -71,9 +71,9 @@ int    launch_prefill_full(vox_engine * e, const vox_attn_args * a, void * works
 
 namespace {
 
-// Developer aid, off unless the file is compiled with -DVOX_PREFILL_PROFILE: per-role cycle counters
-// (SM clock, summed over CTAs with atomics) that vox_debug_prefill_profile copies out.
-#ifdef VOX_PREFILL_PROFILE
+// Developer build only (-DVOX_ATTN_DEVELOPER -DVOX_PREFILL_PROFILE): per-role cycle counters (SM clock, summed over
+// CTAs with atomics) that vox_debug_prefill_profile copies out.  Compiled out of the product library.
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
 __device__ unsigned long long g_prof[32];
 __device__ long long g_trace[4][64];  // CTA 0, first 64 tiles: scores seen, weights signalled, weights seen, MMAs issued
 #define PROF_TRACE(k, T) do { if (blockIdx.x == 0 && (T) < 64) g_trace[k][T] = clock64(); } while (0)
@@ -1061,7 +1061,7 @@ int launch_prefill_full(vox_engine * e, const vox_attn_args * a, void * workspac
 
 extern "C" {
 
-#ifdef VOX_PREFILL_PROFILE
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
 int vox_debug_prefill_trace(long long * out) {
     return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 4 * 64) != cudaSuccess;
 }
