@@ -36,7 +36,28 @@ CASES = {
     "odd_nq3_kv113_f16_mask": dict(B=1, n_q=3, n_kv=113, H=16, HK=2, kv="f16", mask="random", seed=12),
     "odd_nq33_kv75_q8_mask": dict(B=2, n_q=33, n_kv=75, H=8, HK=2, kv="q8_0", mask="random", seed=13),
     "masked_row_f32": dict(B=1, n_q=4, n_kv=40, H=4, HK=4, kv="f32", mask="row_masked", seed=14),
+    # the configured full sizes that the reference's CPU code finishes in seconds: prefill of a 512-token prompt
+    # (fixture keeps a sample of the query rows, see golden_rows) and long-form decode at 4096 / 8192 rows
+    "prefill512_causal_f16": dict(B=1, n_q=512, n_kv=512, H=16, HK=2, kv="f16", mask="causal", seed=15, q_f16=True, sample_rows=True),
+    "decode_kv4096_f16": dict(B=1, n_q=1, n_kv=4096, H=16, HK=2, kv="f16", mask=None, seed=16),
+    "decode_kv8192_f16": dict(B=1, n_q=1, n_kv=8192, H=16, HK=2, kv="f16", mask=None, seed=17),
+    "decode_kv4096_q8": dict(B=1, n_q=1, n_kv=4096, H=16, HK=2, kv="q8_0", mask=None, seed=18),
+    "decode_kv8192_q8": dict(B=1, n_q=1, n_kv=8192, H=16, HK=2, kv="q8_0", mask=None, seed=19),
 }
+
+
+def golden_rows(case):
+    """Query rows of the output a fixture keeps: all of them, or for the large prefill case the first and last eight and
+    every 13th in between (every 128-row tile, its first and last rows and the diagonal tiles are all represented)."""
+    n_q = case["n_q"]
+    if not case.get("sample_rows"):
+        return np.arange(n_q)
+    return np.unique(np.concatenate([np.arange(8), np.arange(8, n_q - 8, 13), np.arange(120, 136), np.arange(n_q - 8, n_q)]))
+
+
+def pick_rows(out, case):
+    """The rows of an operator result [B, n_q, H, D] that the case's fixture holds."""
+    return np.asarray(out)[:, golden_rows(case)]
 
 
 def make_mask(case, oracle):
