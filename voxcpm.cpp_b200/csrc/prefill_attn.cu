@@ -6,41 +6,46 @@
 // On the CPU this is ggml's tiled path (third_party/ggml/src/ggml-cpu/ops.cpp:8347-8633); ggml-cuda
 // would run the mma.sync kernel flash_attn_ext_f16 (fattn-mma-f16.cuh:1459-1628).
 //
-// A work item = 128 query rows of one head of one sequence, walked over 64-key tiles.  CTAs are persistent
-// (two per SM) and take items from a heaviest-first list in snake order; barriers, TMEM and the tile of ones
-// are set up once.  Twelve warps in three warpgroups, which trade registers after launch (setmaxnreg: the launch
-// allots 80 per thread, the softmax group takes 144, the others keep 40 and 56):
-//   warps 0-3  softmax: one thread per query row (row r = TMEM lane r).  Per tile a thread reads its 64 scores
-//              from TMEM (tcgen05.ld), takes their maximum, and writes P = 2^(c*S - m_ref) back into TMEM
-//              (tcgen05.st) over the scores it has just read, as two packed-f16 tiles hi + lo (~21 bits: one f16 per
-//              weight measured 2.3e-3 to 5e-3 of the output RMS on random sequences of 512 to 4096 tokens, outside
-//              the 2e-3 parity bound; hi + lo measures under 6e-5): the tensor core takes the weights from there
-//              as the A operand of P.V, so they never pass through shared memory.  On the
-//              diagonal tile a warp skips the 32-column blocks none of its rows can see.  The output row and the
-//              row sums accumulate in TMEM over all tiles (no per-tile read-back); they are rescaled in place only
-//              when a tile's maximum exceeds the reference m_ref by more than 2^8.  These warps do nothing else:
-//              from the last tile of an item they go straight to the first tile of the next.
-//   warp 4     producer: one lane issues cp.async.bulk.tensor copies of 64-row K and V tiles into four-stage rings.
-//   warp 5     MMA issuer: one lane issues tcgen05.mma (kind::f16, M=128).  S = Q.K^T (N=64, 4 k-steps, both
-//              operands in shared memory) goes to one of two score buffers in TMEM (tile T uses buffer T % 2) and
-//              runs two tiles ahead of P.V, across item boundaries, so the scores of tile T+1 are computed while the
-//              softmax of tile T runs.  O += P.V and the row sums come from ONE instruction per 16 keys and weight
-//              part (N=80, 4 k-steps for hi, 4 for lo): P from TMEM, V read MN-major straight from its row-major tile, and a tile of ones
-//              addressed as columns 64-79 of every V tile, which yields the sums of exactly the rounded weights the
-//              tensor core used.  The tensor pipe executes in issue order, so Q.K^T of tile T+2, issued behind P.V
-//              of tile T, overwrites that tile's weights only once they have been used.  Completion is signalled
-//              with tcgen05.commit (two per tile).  (Warps 6-7 only fill the warpgroup.)
-//   warps 8-11 in/out: one thread per query row again.  They keep the Q tiles of the next two items in shared
+// A work item = 128 rows: 16 consecutive tokens x the 8 query heads that share a kv head (row r = token r / 8, head
+// r % 8; 128 tokens of one head when the GQA ratio is odd), walked over 128-key tiles, so that a K/V tile is fetched
+// once for the whole group (the incumbent packs its GQA heads the same way, fattn-mma-f16.cuh:38-72).  CTAs are
+// persistent, one per SM, and take items from a heaviest-first list in snake order; barriers, TMEM (all 512 columns)
+// and the tile of ones are set up once.  Sixteen warps in four warpgroups, which trade registers after launch
+// (setmaxnreg: the launch allots 128 per thread, the two softmax groups take 168, the others keep 56 and 96):
+//   warps 0-3, 8-11  softmax: two threads per query row (row r = TMEM lane r; warps w and w + 8 share a lane quarter),
+//              64 keys of a tile each.  Per tile a thread reads its 64 scores from TMEM (tcgen05.ld), takes their
+//              maximum, trades it with its partner (shared memory + an mbarrier, which also tells it that the partner
+//              holds its scores in registers), and writes P = 2^(c*S - m_ref) back into TMEM (tcgen05.st) over the
+//              tile's scores as two packed-f16 tiles hi + lo (~21 bits: one f16 per weight measured 2.3e-3 to 5e-3 of
+//              the output RMS on random sequences of 512 to 4096 tokens, outside the 2e-3 parity bound; hi + lo
+//              measures under 6e-5): the tensor core takes the weights from there as the A operand of P.V, so they
+//              never pass through shared memory.  On the diagonal tile a warp skips the 32-column blocks none of its
+//              rows can see.  The output row and the row sums accumulate in TMEM over all tiles (no per-tile
+//              read-back); they are rescaled in place only when a tile's maximum exceeds the reference m_ref by more
+//              than 2^8.  These warps do nothing else: from the last tile of an item they go straight to the first
+//              tile of the next.
+//   warp 4     producer: one lane issues cp.async.bulk.tensor copies of 128-row K and V tiles into three-stage rings.
+//   warp 6     score issuer: one lane issues S = Q.K^T (tcgen05.mma kind::f16, M = 128, N = 128, 4 k-steps, both
+//              operands in shared memory) into one of three score buffers in TMEM (tile T uses buffer T % 3), up to
+//              three tiles ahead of P.V and across item boundaries.
+//   warp 5     output issuer: O += P.V and the row sums come from ONE instruction per 16 keys and weight part
+//              (N = 80, 8 k-steps for hi, 8 for lo): P from TMEM, V read MN-major straight from its row-major tile,
+//              and a tile of ones addressed as columns 64-79 of every 16-key step, which yields the sums of exactly
+//              the rounded weights the tensor core used.  One thread issues both parts, so the order of the f32
+//              accumulation, and with it every bit of the result, is the same in every run (two threads sharing the
+//              parts measured no faster).  Completion is signalled with tcgen05.commit.  (Warp 7 only fills the group.)
+//   warps 12-15 in/out: one thread per query row again.  They keep the Q tiles of the next two items in shared
 //              memory (f32 from memory, rounded to f16 once, exact when it already holds f16 values) and read each
 //              finished output row out of TMEM, normalise and store it, handing the columns back to the issuer.
-// Measured costs that shaped this: a tcgen05.mma costs its issuing thread 45-70 cycles whatever its shape, so
-// instructions are few and wide (the sums ride along with P.V); the per-tile chain scores -> weights -> P.V ->
-// next scores was 2.5x the softmax time until the scores were double-buffered; and a parity wait cannot see
-// two completed phases, so every barrier here completes at most once between two looks of its waiters.
-// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  105 KB of shared memory,
-// 256 TMEM columns and half the register file per CTA.  Every wait on a barrier is bounded; on expiry the status
-// word is set and all roles fall through to the common exit, where the TMEM columns are released.  The register
-// trade cannot block: what the softmax group takes is exactly what the other two give up (static_assert below).
+// What bounds it, measured with cycle counters and with the softmax arithmetic compiled out (developer builds): the
+// special-function unit (16 exponentials per clock: 1024 clocks per 128 x 128 tile; the weights' block of the softmax
+// loop takes 1300, the whole loop 2300 with its waits, the load of the scores and the trade of the maxima), and, close
+// behind, the hand-over chain scores -> weights -> P.V -> buffer free (1900 clocks per tile with no softmax arithmetic
+// at all, whatever the number of issuing threads, ring stages or P.V instructions).  The tensor pipe itself needs 900.
+// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  131 KB of shared memory per CTA (195 KB
+// with remainder tiles).  Every wait on a barrier is bounded; on expiry the status word is set and all roles fall
+// through to the common exit, where the TMEM columns are released.  The register trade cannot block: what the softmax
+// groups take, the other two have given up before (static_assert below).
 //
 // Three forms of the kernel share this code (template parameters):
 //   kSplitP  the weights as hi + lo (the product path; a single f16 is kept for comparison);
@@ -49,7 +54,7 @@
 //            kernel first notes which key tiles the mask leaves anything of, and every role walks only those;
 //   kVLo     K/V that are not f16 (q8_0 blocks, f32) are expanded by a small kernel into an f16 value tile and an f16
 //            remainder tile each, Q is kept as value + remainder too, and the remainders take extra Q.K^T and P.V
-//            passes (24 tcgen05.mma per tile instead of 12; one CTA per SM), so that nothing is lost to f16 rounding.
+//            passes (36 tcgen05.mma per tile instead of 20), so that nothing is lost to f16 rounding.
 #include "common.cuh"
 
 #include <algorithm>
@@ -92,29 +97,35 @@ __device__ long long g_trace[4][64];  // CTA 0, first 64 tiles: scores seen, wei
 #endif
 
 constexpr int kTile      = 128;            // query rows per item
-constexpr int kKeys      = 64;             // keys per tile
+constexpr int kKeys      = 128;            // keys per tile
 constexpr int kQBytes    = kTile * 128;    // the item's [128][64] f16 Q tile
-constexpr int kKvBytes   = kKeys * 128;    // one [64][64] f16 K or V tile
-constexpr int kStages    = 4;              // K ring and V ring
-constexpr int kSoftmaxThreads = 128;
+constexpr int kKvBytes   = kKeys * 128;    // one [128][64] f16 K or V tile
+constexpr int kStages    = 6;              // most stages a K or V ring has (barrier slots)
+constexpr int kSBufs     = 3;              // score buffers in TMEM
+constexpr int kSoftmaxThreads = 256;       // two warpgroups: one thread per query row and half of a tile's keys
 constexpr int kIoThreads = 128;
-constexpr int kThreadsPf = 384;            // softmax warpgroup, control warpgroup (producer, issuer, two idle warps), in/out warpgroup
+constexpr int kThreadsPf = 512;            // softmax A, control (producer, two issuers, one idle warp), softmax B, in/out
 constexpr int kQBufs     = 2;              // Q tiles of two consecutive items
-// Registers per thread after the warpgroups have traded (setmaxnreg).  What one group takes must have been given
-// up by the others of the same CTA: the launch allots 80 x 384 (two CTAs per SM), so the three figures sum to 240.
-constexpr int kRegsSoftmax = 144, kRegsControl = 40, kRegsIo = 56;
-static_assert(kRegsSoftmax + kRegsControl + kRegsIo == 3 * 80, "the CTA's registers are conserved");
-// TMEM columns: two score buffers (tile T uses buffer T % 2; its weights, packed f16, replace the first 32
-// columns of its scores) and the output row with its row sum
-constexpr int kTmemCols  = 256;
-constexpr int kSCol      = 0;              // S: 2 x 64 columns
-constexpr int kOCol      = 128;            // O: 64 columns, row sums: 16 columns behind them
-constexpr int kOnesBytes = kKvBytes;       // a tile of ones, addressed as columns 64-79 of every V tile (any layout: every element is 1)
-// With kVLo (K/V expanded from q8_0) a K or V stage holds two tiles, the f16 values and what their rounding left over, and
-// the rings are two stages deep, so that two CTAs still fit on an SM.
-constexpr int stages_of(bool v_lo) { return v_lo ? 2 : kStages; }
+// Registers per thread after the warpgroups have traded (setmaxnreg).  One CTA per SM: the launch allots 128 x 512;
+// what the softmax groups take beyond that, the other two have given up before (they do so first thing).
+constexpr int kRegsLaunch = 128, kRegsSoftmax = 168, kRegsControl = 56, kRegsIo = 96;
+static_assert(2 * (kRegsSoftmax - kRegsLaunch) <= (kRegsLaunch - kRegsControl) + (kRegsLaunch - kRegsIo), "the trade cannot block");
+static_assert((2 * kRegsSoftmax + kRegsControl + kRegsIo) * 128 <= 65536, "the CTA's registers fit the SM");
+// TMEM columns: three score buffers of 128 columns (tile T uses buffer T % 3; its weights, packed f16, replace its scores:
+// high parts in the first 64 columns, low parts in the last 64) and the output row with its row sum
+constexpr int kTmemCols  = 512;
+constexpr int kSCol      = 0;              // S: 3 x 128 columns
+constexpr int kOCol      = kSBufs * kKeys; // O: 64 columns, row sums: 16 columns behind them
+constexpr int kOnesBytes = 2048;           // 16 keys x 64 ones, addressed as columns 64-79 of every 16-key step of every V tile
+// With kVLo (K/V expanded from q8_0 or f32) a K or V stage holds two tiles, the f16 values and what their rounding left
+// over, and the rings are two stages deep instead of three (five stages measured 5 % slower than three: the rings
+// are not what the kernel waits for) ...
+#ifndef VOX_PREFILL_STAGES
+#define VOX_PREFILL_STAGES 3
+#endif
+constexpr int stages_of(bool v_lo) { return v_lo ? 2 : VOX_PREFILL_STAGES; }
 constexpr int v_stage_bytes(bool v_lo) { return v_lo ? 2 * kKvBytes : kKvBytes; }
-// ... and a Q buffer holds the f16 tile and the remainder tile as well (then one CTA fits per SM)
+// ... and a Q buffer holds the f16 tile and the remainder tile as well
 constexpr int q_buf_bytes(bool v_lo) { return v_lo ? 2 * kQBytes : kQBytes; }
 constexpr int smem_pf(bool v_lo) {  // Q x 2, K ring, V ring, ones
     return kQBufs * q_buf_bytes(v_lo) + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + 1024;
@@ -126,6 +137,10 @@ struct PrefillParams {
     float *         dst;
     int             n_q, n_kv, n_heads, gqa, causal_offset;
     int             n_batch, n_qtiles, n_items;
+    // The 128 rows of an item are `tok` consecutive tokens x `pack` query heads that share a kv head (row r = token
+    // r / pack, head r % pack): K and V tiles are fetched once for the whole group (the incumbent packs its GQA heads
+    // the same way, third_party/ggml/src/ggml-cuda/fattn-mma-f16.cuh:38-72).  pack = 8, 4, 2 or 1, tok = 128 / pack.
+    int             pack, tok, n_hgroups;
     float           scale_log2;
     int *           status;
     // additive f16 mask (kMask kernels): rows of n_kv values, planes broadcast over heads and sequences
@@ -292,11 +307,11 @@ __device__ __noinline__ void rescale_accumulators(uint32_t t_row, float f) {
     tc_fence_before();
 }
 
-// One unit of work: 128 query rows (tile `qtile`) of one head of one sequence.  Items are numbered
+// One unit of work: 128 rows = `tok` tokens (tile `qtile`) x `pack` heads of one sequence.  Items are numbered
 // heaviest first (late query tiles see more keys); CTA c of G takes items c, 2G-1-c, 2G+c, ... so that
 // a heavy first item is followed by a light one.
 struct WorkItem {
-    int                qtile, head, batch, n_tiles, q0;
+    int                qtile, head, batch, n_tiles, q0;  // head: the first of the group; q0: the first token
     unsigned long long live;  // key tiles to walk, as bits (at most 64 when some are left out)
 };
 template <bool kMask>
@@ -304,18 +319,19 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
     const int G = gridDim.x, c = blockIdx.x;
     const int idx = round * G + ((round & 1) ? G - 1 - c : c);
     if (idx >= p.n_items) return false;
-    const int per_tile = p.n_heads * p.n_batch;
+    const int per_tile = p.n_hgroups * p.n_batch;
     const int rest     = idx % per_tile;
     w.qtile = p.n_qtiles - 1 - idx / per_tile;
-    w.head  = rest % p.n_heads;
-    w.batch = rest / p.n_heads;
-    w.q0    = w.qtile * kTile;
-    const int last_row = min(w.q0 + kTile, p.n_q) - 1;
-    w.n_tiles = min((p.n_kv + kKeys - 1) / kKeys, (last_row + p.causal_offset) / kKeys + 1);
+    w.head  = (rest % p.n_hgroups) * p.pack;
+    w.batch = rest / p.n_hgroups;
+    w.q0    = w.qtile * p.tok;
+    const int last_tok = min(w.q0 + p.tok, p.n_q) - 1;
+    w.n_tiles = min((p.n_kv + kKeys - 1) / kKeys, (last_tok + p.causal_offset) / kKeys + 1);
     w.live    = ~0ull;
     if (kMask && p.tile_live != nullptr) {  // only set for n_tiles <= 64; a tile where the mask hides every key from every row is left out
-        const unsigned long long seen =
-            p.tile_live[((size_t) (w.batch % p.m_ne3) * p.m_ne2 + (w.head % p.m_ne2)) * p.n_qtiles + w.qtile];
+        unsigned long long seen = 0ull;
+        for (int h = 0; h < p.pack; ++h)  // the heads of the group may read different planes of the mask
+            seen |= p.tile_live[((size_t) (w.batch % p.m_ne3) * p.m_ne2 + ((w.head + h) % p.m_ne2)) * p.n_qtiles + w.qtile];
         w.live = seen != 0 ? seen : 1ull;  // an item that sees nothing still walks one tile: its rows come out as zeros
     }
     return true;
@@ -337,12 +353,13 @@ __device__ __forceinline__ int next_live(const WorkItem & w, int from) {
 // kMask: an additive f16 mask is read instead of implying the causal one; every key tile is walked, a row may see no
 // key at all (its output is zero, third_party/ggml/src/ggml-cpu/ops.cpp:8333).
 template <bool kSplitP, bool kVLo, bool kMask>
-__global__ void __launch_bounds__(kThreadsPf, kVLo ? 1 : 2)
+__global__ void __launch_bounds__(kThreadsPf, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo, const PrefillParams p) {
     constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo), kQBufBytes = q_buf_bytes(kVLo);
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[4 * kStages + 6];
+    __shared__ uint64_t bars[4 * kStages + 3 * kSBufs + kQBufs + 2 + 2];
+    __shared__ float    row_max[2][2][kTile];  // [tile parity][half of the keys][row]: the two softmax threads of a row trade their maxima
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
 
@@ -352,15 +369,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // per-tile barriers: K/V ring (stage T % 4; "K stage free" is signalled when Q.K^T of the tile has retired and
-    // is also what the softmax warps wait on for the scores; "V stage free" is signalled when P.V has retired and
-    // is also what tells them that the accumulators are at rest), weights ready (buffer T % 2);
-    // the softmax warps may be two tiles ahead of the MMA thread (the scores of tile T+1 exist before it has
-    // looked at the weights of tile T), so "weights ready" is one barrier per buffer: a single one could complete
-    // two phases unobserved, and a parity wait cannot tell that from none;
-    // per-item barriers: Q in place (one per Q buffer, for the same reason), output complete, output read
+    // Barriers.  Per ring stage (tile T uses stage T % kSt): K landed / K stage free, V landed / V stage free; the
+    // producer is the only waiter of the two "free" ones.  Per score buffer (tile T uses buffer T % 3): scores ready
+    // (Q.K^T retired), weights ready (one arrival per softmax warp), buffer free (P.V retired: the weights have been used
+    // and the accumulators are at rest).  A barrier of buffer b completes once per tile of that buffer, and each of the
+    // three events of tile T + 3 needs the one its waiter is looking for in tile T to have been seen, so no barrier can
+    // complete twice between two looks of a waiter (a parity wait cannot tell two completed phases from none).
+    // Per item: Q in place (one per Q buffer), output complete, output read.  Per tile parity: row maxima traded
+    // between the two softmax warpgroups (tile T + 2 cannot be traded before every warp has seen tile T's).
     const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = kfull0 + 8 * kStages, vfull0 = kempty0 + 8 * kStages,
-                   vempty0 = vfull0 + 8 * kStages, bP0 = vempty0 + 8 * kStages, bQ0 = bP0 + 16, bO = bQ0 + 16, bOfree = bO + 8;
+                   vempty0 = vfull0 + 8 * kStages, bS0 = vempty0 + 8 * kStages, bP0 = bS0 + 8 * kSBufs, bF0 = bP0 + 8 * kSBufs,
+                   bQ0 = bF0 + 8 * kSBufs, bO = bQ0 + 8 * kQBufs, bOfree = bO + 8, bX0 = bOfree + 8;
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
@@ -369,14 +388,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             mbar_init(vfull0 + 8 * s, 1);
             mbar_init(vempty0 + 8 * s, 1);
         }
-        for (int s = 0; s < 2; ++s) mbar_init(bP0 + 8 * s, kSoftmaxThreads / 32);  // one arrival per softmax warp
+        for (int s = 0; s < kSBufs; ++s) {
+            mbar_init(bS0 + 8 * s, 1);
+            mbar_init(bP0 + 8 * s, kSoftmaxThreads / 32);  // one arrival per softmax warp
+            mbar_init(bF0 + 8 * s, 1);
+        }
         for (int s = 0; s < kQBufs; ++s) mbar_init(bQ0 + 8 * s, kIoThreads / 32);  // one arrival per in/out warp
         mbar_init(bO, 1);
         mbar_init(bOfree, kIoThreads / 32);
+        for (int s = 0; s < 2; ++s) mbar_init(bX0 + 8 * s, kSoftmaxThreads / 32);  // row maxima of a tile traded (tile T uses T % 2)
         fence_mbar_init();
     }
     if (warp == 5) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
-    if (tid == kSoftmaxThreads) {
+    if (tid == 128) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
         if (kVLo) {
@@ -399,12 +423,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     // The CTA is persistent: every role walks the same item sequence; T counts key tiles over all items
     // and fixes the phase of every per-tile barrier; `round` fixes the phase of the per-item ones.
-    if (warp >= 8) {
+    if (warp >= 12) {
         // ------------------------------------------------------------------ in/out warps: Q tiles in, results out
-        // One thread per query row, as in the softmax warps (warp 8+i may touch TMEM lanes 32i..32i+31).  They keep
+        // One thread per query row, as in the softmax warps (warp 12+i may touch TMEM lanes 32i..32i+31).  They keep
         // the Q tiles of the next two items in shared memory and read each finished output out of TMEM, so that the
         // softmax warps go from the last tile of one item straight to the first tile of the next.
-        if (!kVLo) regs_give<kRegsIo>();  // one CTA per SM with kVLo: the launch allots every thread enough
+        regs_give<kRegsIo>();
         const int      row   = tid - (kThreadsPf - kIoThreads);
         const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);
         {
@@ -415,8 +439,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         // this thread's Q row: f32 from memory, f16 into eight 16-byte chunks at their swizzled places
         auto load_q = [&](const WorkItem & w, int buf) {
             uint8_t * const q_dst = smem_gen + buf * kQBufBytes + row * 128;
-            const int       qpos  = w.q0 + row;
-            const float4 *  src   = reinterpret_cast<const float4 *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) w.head * p.q_nb2 +
+            const int       qpos  = w.q0 + row / p.pack, head = w.head + row % p.pack;
+            const float4 *  src   = reinterpret_cast<const float4 *>(p.q + (size_t) qpos * p.q_nb1 + (size_t) head * p.q_nb2 +
                                                                   (size_t) w.batch * p.q_nb3);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -449,11 +473,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         for (int round = 0; work_item<kMask>(p, round, w) && !aborted(); ++round) {
             if (!mbar_wait_bounded(bO, round & 1)) { give_up(); break; }
             tc_fence_after();
-            const int   qpos = w.q0 + row;
+            const int   qpos = w.q0 + row / p.pack, head = w.head + row % p.pack;
             const bool  live = qpos < p.n_q;
             const float l    = tmem_ld1(t_row + kOCol + kHeadDim);  // sum of exactly the rounded weights the tensor core used
             const float inv  = l > 0.0f ? 1.0f / l : 0.0f;
-            float4 *    out  = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + w.head) * kHeadDim);
+            float4 *    out  = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 uint32_t r[32];
@@ -470,11 +494,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                                                      __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
                 }
             }
-            // every Q.K^T of this item retired before its output was complete: its Q buffer takes the item after next
+            // The item's output is complete only after its last P.V, which needed its last weights, which needed its last
+            // scores: every Q.K^T of this item has retired, and its Q buffer takes the item after next.
             if (work_item<kMask>(p, round + kQBufs, wn)) load_q(wn, round % kQBufs);
         }
-    } else if (warp >= 4) {
-        if (!kVLo) regs_give<kRegsControl>();
+    } else if (warp >= 4 && warp < 8) {
+        regs_give<kRegsControl>();
         if (warp == 4) {
             // -------------------------------------------------------------- producer
             if (lane == 0) {
@@ -506,79 +531,84 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_STOP(0);
                 PROF_FLUSH(0, 3);  // 0 issue, 1 wait K stage free, 2 wait V stage free
             }
-        } else if (warp == 5) {
-            // -------------------------------------------------------------- MMA issuer
+        } else if (warp == 6) {
+            // -------------------------------------------------------------- score issuer: S = Q.K^T
+            // Two threads share the issuing, because issuing is what a CTA runs out of first: a tcgen05.mma costs its
+            // issuing thread 60 cycles or more whatever its shape.  This thread walks the item sequence on its own, up
+            // to three tiles ahead of P.V, across item boundaries.  S of global tile Tq goes into score buffer Tq % 3:
+            // four k-steps of 16 along head_dim (32 bytes each inside the swizzle atom), N = 128 keys.  The buffer last
+            // held the weights of tile Tq-3, which P.V of that tile reads: its retirement is awaited first.
             if (lane == 0) {
-                constexpr uint32_t idesc_qk = idesc_f16(kKeys, false), idesc_pv = idesc_f16(kHeadDim + 16, true);
-                // Descriptors are built once (the thread lives on 40 registers); a k-step, a ring stage or a Q buffer is
-                // selected by adding its distance to the address field (for V, a stage's distance also comes off the
-                // distance to the tile of ones).
-                const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK0), dV = smem_desc_sw128_mn(sV0, sOnes - sV0);
-                constexpr uint64_t kStepQK = 32 >> 4, kStepV = 2048 >> 4;  // 16 of head_dim inside the swizzle atom; 16 keys
-                constexpr uint64_t kVStep  = kVBytes >> 4;
-                constexpr uint64_t kStage  = kVStep;  // K stages are as large as V stages
-                const uint64_t     dKlo    = smem_desc_sw128(sK0 + kKvBytes);
-                constexpr uint64_t kVStage = kVStep - (kVStep << 16);
+                constexpr uint32_t idesc_qk = idesc_f16(kKeys, false);
+                const uint64_t     dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK0), dKlo = smem_desc_sw128(sK0 + kKvBytes);
+                constexpr uint64_t kStepQK = 32 >> 4;          // 16 of head_dim inside the swizzle atom
+                constexpr uint64_t kStage  = kVBytes >> 4;     // K stages are as large as V stages
+                constexpr uint64_t kQBuf   = kQBufBytes >> 4;
+                constexpr uint64_t kQLo    = kQBytes >> 4;     // from a Q tile to its remainder tile
+                WorkItem wq;
+                int      Tq = 0;
+                bool     ok = true;
+                PROF_VARS;
+                PROF_START();
+                for (int rq = 0; ok && work_item<kMask>(p, rq, wq); ++rq) {
+                    PROF_STOP(0);
+                    if (!mbar_wait_bounded(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) { give_up(); break; }  // the item's Q tile is in place
+                    PROF_STOP(2);
+                    const uint64_t dQi = dQ + (rq % kQBufs) * kQBuf;
+                    for (int jq = next_live<kMask>(wq, 0); jq < wq.n_tiles && !aborted(); jq = next_live<kMask>(wq, jq + 1), ++Tq) {
+                        const int st = Tq % kSt, sb = Tq % kSBufs;
+                        PROF_STOP(0);
+                        if (Tq >= kSBufs && !mbar_wait_bounded(bF0 + 8 * sb, ((Tq / kSBufs) - 1) & 1)) { give_up(); ok = false; break; }
+                        PROF_STOP(1);
+                        if (!mbar_wait_bounded(kfull0 + 8 * st, (Tq / kSt) & 1)) { give_up(); ok = false; break; }
+                        PROF_STOP(2);
+                        tc_fence_after();
+                        const uint32_t dS = tmem + kSCol + kKeys * sb;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) tc_mma_f16(dS, dQi + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, k > 0);
+                        if (kVLo) {  // what rounding K to f16 left over
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) tc_mma_f16(dS, dQi + k * kStepQK, dKlo + st * kStage + k * kStepQK, idesc_qk, 1);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)  // and what rounding Q to f16 left over
+                                tc_mma_f16(dS, dQi + kQLo + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, 1);
+                        }
+                        tc_commit(bS0 + 8 * sb);      // Q.K^T has retired: the scores are there ...
+                        tc_commit(kempty0 + 8 * st);  // ... and the K stage may be refilled
+                    }
+                    if (aborted()) break;
+                }
+                PROF_STOP(0);
+                PROF_FLUSH(21, 3);  // 21 issue, 22 wait for the score buffer, 23 wait Q / K tile
+            }
+        } else if (warp == 5) {
+            // -------------------------------------------------------------- output issuer: O += P.V, row sums += P.1
+            if (lane == 0) {
+                constexpr uint32_t idesc_pv = idesc_f16(kHeadDim + 16, true);
+                // Descriptors are built once; a k-step or a ring stage is selected by adding its distance to the address
+                // field, and the same distance comes off the leading byte offset, which then still points at the tile of ones.
+                const uint64_t     dV = smem_desc_sw128_mn(sV0, sOnes - sV0);
+                constexpr uint64_t kStepV   = 2048 >> 4;  // 16 keys
+                constexpr uint64_t kStepVPv = kStepV - (kStepV << 16);
+                constexpr uint64_t kVStep   = kVBytes >> 4;
+                constexpr uint64_t kVStage  = kVStep - (kVStep << 16);
                 // the remainder tile of a V stage: 64 columns, no tile of ones behind it
                 const uint64_t     dVlo     = smem_desc_sw128_mn(sV0 + kKvBytes, 16);
                 constexpr uint32_t idesc_lo = idesc_f16(kHeadDim, true);
-                constexpr uint64_t kQBuf   = kQBufBytes >> 4;
-                constexpr uint64_t kQLo    = kQBytes >> 4;  // from a Q tile to its remainder tile
                 PROF_VARS;
-                // Q.K^T runs two tiles ahead of P.V, across item boundaries: `q` walks the same item sequence as the
-                // P.V loop below.  S of global tile Tq goes into score buffer Tq % 2: four k-steps of 16 along
-                // head_dim, 32 bytes each inside the swizzle atom.  The buffer last held the weights of tile Tq-2; the
-                // tensor pipe executes in issue order, so issuing this behind P.V of tile Tq-2 is all the protection
-                // they need.
-                WorkItem wq;
-                int      rq = 0, jq = 0, Tq = 0;
-                bool     have_q = work_item<kMask>(p, 0, wq), first_q = true;
-                if (have_q) jq = next_live<kMask>(wq, 0);
-                auto issue_qk = [&]() {
-                    if (!have_q) return true;
-                    PROF_STOP(0);
-                    if (first_q && !mbar_wait_bounded(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) return false;  // the item's Q tile is in place
-                    first_q = false;
-                    PROF_STOP(2);
-                    const int st = Tq % kSt, sb = Tq & 1;
-                    if (!mbar_wait_bounded(kfull0 + 8 * st, (Tq / kSt) & 1)) return false;
-                    PROF_STOP(1);
-                    tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, k > 0);
-                    if (kVLo) {  // what rounding K to f16 left over
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + k * kStepQK, dKlo + st * kStage + k * kStepQK, idesc_qk, 1);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)  // and what rounding Q to f16 left over
-                            tc_mma_f16(tmem + kSCol + kKeys * sb, dQ + (rq % kQBufs) * kQBuf + kQLo + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, 1);
-                    }
-                    tc_commit(kempty0 + 8 * st);  // Q.K^T has retired: the scores are there and the K stage may be refilled
-                    ++Tq;
-                    jq = next_live<kMask>(wq, jq + 1);
-                    if (jq >= wq.n_tiles) {
-                        first_q = true;
-                        have_q  = work_item<kMask>(p, ++rq, wq);
-                        if (have_q) jq = next_live<kMask>(wq, 0);
-                    }
-                    return true;
-                };
                 WorkItem w;
                 int      T  = 0;
                 bool     ok = true;
                 PROF_START();
-                if (!issue_qk() || !issue_qk()) { give_up(); ok = false; }
                 for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
                     const int j_first = next_live<kMask>(w, 0);
                     for (int j = j_first; j < w.n_tiles && !aborted(); ++T) {
-                        const int st     = T % kSt;
+                        const int st = T % kSt, sb = T % kSBufs;
                         const int j_next = next_live<kMask>(w, j + 1);
                         PROF_STOP(0);
                         if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kSt) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(3);
-                        if (!mbar_wait_bounded(bP0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
+                        if (!mbar_wait_bounded(bP0 + 8 * sb, (T / kSBufs) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(4);
                         // the previous item's result has been read out of TMEM: its columns may be overwritten
                         if (j == j_first && round > 0 && !mbar_wait_bounded(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
@@ -586,39 +616,45 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         PROF_TRACE(2, T);
                         tc_fence_after();
                         // O += P V and row sums += P 1 in one instruction per 16 keys: N = 80, columns 64-79 of the B
-                        // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, at the start of
-                        // the tile's score buffer.
+                        // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, the high parts in
+                        // the first half of the tile's score buffer, the low parts in the second half.
+                        const uint32_t tP = tmem + kSCol + kKeys * sb;
+                        const uint64_t dVs = dV + st * kVStage;
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, j != j_first || k > 0);
-                        if (kSplitP) {  // the low parts of the same weights, behind the high parts in the score buffer
+                        for (int k = 0; k < kKeys / 16; ++k)
+                            tc_mma_f16_ts(tmem + kOCol, tP + 8 * k, dVs + k * kStepVPv, idesc_pv, j != j_first || k > 0);
+                        if (kSplitP) {
 #pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 32 + 8 * k, dV + st * kVStage + k * kStepV, idesc_pv, 1);
+                            for (int k = 0; k < kKeys / 16; ++k)
+                                tc_mma_f16_ts(tmem + kOCol, tP + kKeys / 2 + 8 * k, dVs + k * kStepVPv, idesc_pv, 1);
                         }
                         if (kVLo) {  // what rounding V to f16 left over, against the high parts of the weights
 #pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                tc_mma_f16_ts(tmem + kOCol, tmem + kSCol + kKeys * (T & 1) + 8 * k, dVlo + st * kVStep + k * kStepV, idesc_lo, 1);
+                            for (int k = 0; k < kKeys / 16; ++k)
+                                tc_mma_f16_ts(tmem + kOCol, tP + 8 * k, dVlo + st * kVStep + k * kStepV, idesc_lo, 1);
                         }
-                        tc_commit(vempty0 + 8 * st);  // P.V has retired: the V stage may be refilled, the accumulators are at rest
+                        tc_commit(bF0 + 8 * sb);      // P.V has retired: the score buffer may take tile T + 3, the accumulators are at rest ...
+                        tc_commit(vempty0 + 8 * st);  // ... and the V stage may be refilled
                         if (j_next >= w.n_tiles) tc_commit(bO);  // the item's output is complete
-                        // scores two tiles ahead, into the buffer whose weights P.V has just been told to read
-                        if (!issue_qk()) { give_up(); ok = false; break; }
                         PROF_TRACE(3, T);
                         j = j_next;
                     }
                     if (aborted()) break;
                 }
                 PROF_STOP(0);
-                PROF_FLUSH(4, 5);  // 4 issue, 5 wait K tile, 6 wait Q / output read, 7 wait V tile, 8 wait P
+                PROF_FLUSH(4, 5);  // 4 issue, 6 wait output read, 7 wait V tile, 8 wait P
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax warps: one thread per query row
-        if (!kVLo) regs_take<kRegsSoftmax>();
-        const int      row   = tid;                                    // == TMEM lane; warp w may only touch lanes 32w..32w+31
-        const uint32_t t_row = tmem + ((uint32_t) (32 * warp) << 16);  // this warp's lane quarter
+        // ------------------------------------------------------------------ softmax warps: two threads per query row
+        // Warps 0-3 take keys 0-63 of every tile, warps 8-11 keys 64-127 (a warp may touch the TMEM lanes of its
+        // quarter, warp % 4, so warps w and w + 8 share rows).  The special-function unit delivers 16 exponentials per
+        // clock: 1024 clocks for a 128 x 128 tile, and only with two warps per scheduler does one warp's arithmetic
+        // overlap the other's exponentials (one warp per scheduler measured 2200 clocks per tile).
+        regs_take<kRegsSoftmax>();
+        const int      half  = warp >> 3;                                    // which 64 keys of a tile
+        const int      row   = 32 * (warp & 3) + lane;                       // == TMEM lane
+        const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);  // this warp's lane quarter
 
         WorkItem w;
         int      T  = 0;
@@ -626,27 +662,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         PROF_VARS;
         PROF_START();
         for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
-            const int  qpos  = w.q0 + row;
+            const int  qpos  = w.q0 + row / p.pack;
             const int  limit = min(qpos + p.causal_offset, p.n_kv - 1);  // last key this row may see
             // last key any row of this warp may see (rows beyond n_q compute on zeros and are not stored)
-            const int  warp_limit = min(w.q0 + 32 * warp + 31 + p.causal_offset, p.n_kv - 1);
+            const int  warp_limit = min(w.q0 + (32 * (warp & 3) + 31) / p.pack + p.causal_offset, p.n_kv - 1);
             // The output row and the row sum accumulate in TMEM across all key tiles, both scaled by
             // 2^(-m_ref): their ratio does not depend on m_ref, so the reference maximum only has to keep
             // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
-            // block's maximum exceeds it by more than 2^8, which after the first tile is rare.
+            // tile's maximum exceeds it by more than 2^8, which after the first tile is rare.  Both threads of a row
+            // follow the same reference: they trade their halves' maxima every tile.
             float m_ref = -INFINITY;
             // this row of the mask (rows past n_q are computed on zeros and not stored: they borrow the last row)
             const uint8_t * mrow = nullptr;
             if (kMask)
-                mrow = p.mask + (size_t) min(qpos, p.n_q - 1) * p.m_nb1 + (size_t) (w.head % p.m_ne2) * p.m_nb2 +
+                mrow = p.mask + (size_t) min(qpos, p.n_q - 1) * p.m_nb1 + (size_t) ((w.head + row % p.pack) % p.m_ne2) * p.m_nb2 +
                        (size_t) (w.batch % p.m_ne3) * p.m_nb3;
             // the scores are multiplied by `mul` on their way into the exponent: with a mask they have been put into
             // natural units (scale * S + mask) first
             const float mul = kMask ? 1.4426950408889634f : p.scale_log2;
             const int j_first = next_live<kMask>(w, 0);
             for (int j = j_first; j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1), ++T) {
-                const int sb = T & 1;
-                const int k0 = j * kKeys;
+                const int sb = T % kSBufs;
+                const int k0 = j * kKeys + 64 * half;  // this thread's first key
                 uint4     mv[8];
                 if (kMask) {  // requested before the wait for the scores; chunks of 8 keys lie wholly inside or outside n_kv
                     const uint4 * mp = reinterpret_cast<const uint4 *>(mrow + (size_t) k0 * 2);
@@ -654,22 +691,29 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     for (int c = 0; c < 8; ++c) mv[c] = k0 + 8 * c < p.n_kv ? __ldg(mp + c) : make_uint4(0u, 0u, 0u, 0u);
                 }
                 PROF_STOP(0);
-                if (!mbar_wait_bounded(kempty0 + 8 * (T % kSt), (T / kSt) & 1)) { give_up(); ok = false; break; }
+                if (!mbar_wait_bounded(bS0 + 8 * sb, (T / kSBufs) & 1)) { give_up(); ok = false; break; }
                 PROF_STOP(1);
                 PROF_COUNT(7, 1);
                 if (tid == 0) PROF_TRACE(0, T);
                 tc_fence_after();
-                const uint32_t t_s    = t_row + kSCol + kKeys * sb;
-                const bool     masked = k0 + kKeys - 1 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // CTA-uniform: the tile may be cut
-                // 32-column blocks with at least one key some row of this warp sees (warp-uniform)
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_NOSOFTMAX)  // developer build: the copy and MMA structure alone
+                if (j == j_first) m_ref = 0.0f;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bP0 + 8 * sb);
+                continue;
+#endif
+                const uint32_t t_s    = t_row + kSCol + kKeys * sb;  // the tile's score buffer; this thread's scores start 64 * half in
+                const bool     masked = k0 + 63 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // uniform over the warpgroup: the half may be cut
+                // 32-column blocks of this half with at least one key some row of this warp sees (warp-uniform)
                 const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
                 uint32_t       r[64];
                 if (n_live == 2) {
-                    tmem_ld64_sync(t_s, r);
+                    tmem_ld64_sync(t_s + 64 * half, r);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) r[i] = 0xff800000u;  // -inf: no weight
-                    if (n_live == 1) tmem_ld32_sync(t_s, r);
+                    if (n_live == 1) tmem_ld32_sync(t_s + 64 * half, r);
                 }
                 PROF_STOP(10);
                 if (kMask) {
@@ -699,10 +743,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     cmax = fmaxf(t0, t1) * mul;
                 }
+                // Trade the maxima of the two halves.  The barrier also tells each thread that its partner holds its
+                // scores in registers: the weights written below overwrite both halves of the buffer.
+                row_max[T & 1][half][row] = cmax;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bX0 + 8 * (T & 1));
+                if (!mbar_wait_bounded(bX0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
+                cmax = fmaxf(cmax, row_max[T & 1][half ^ 1][row]);
                 PROF_STOP(11);
                 // The weights are written only after the whole tile has been looked at, so a raise of the
                 // reference needs no second pass.  tcgen05.ld/st are warp-collective: the decision to rescale is
-                // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.
+                // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.  Both threads
+                // of a row take the same decision; the one of the first half rescales the accumulators.
                 // With a mask a row may have seen no key yet: its reference stays -inf (any finite maximum then
                 // raises it, with a factor of 0 for accumulators that hold 0) and its weights are 2^(-inf - 0) = 0.
                 if (j == j_first) {
@@ -712,18 +764,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     if (__any_sync(0xffffffffu, raise)) {
                         const float f = raise ? ex2_approx(m_ref - cmax) : 1.0f;
                         if (raise) m_ref = cmax;
-                        // the accumulators are at rest once P.V of the previous tile has retired
-                        if (!mbar_wait_bounded(vempty0 + 8 * ((T - 1) % kSt), ((T - 1) / kSt) & 1)) { give_up(); ok = false; break; }
-                        rescale_accumulators(t_row, f);
+                        if (half == 0) {
+                            // the accumulators are at rest once P.V of the previous tile has retired
+                            if (!mbar_wait_bounded(bF0 + 8 * ((T - 1) % kSBufs), ((T - 1) / kSBufs) & 1)) { give_up(); ok = false; break; }
+                            rescale_accumulators(t_row, f);
+                        }
                     }
                 }
                 const float m_sub = kMask && m_ref == -INFINITY ? 0.0f : m_ref;
+                // P = 2^(c*S - m_ref), 16 keys (8 columns of packed f16 pairs) at a time: k-step 4 * half + g of the tile.
                 if (kSplitP) {
-                    // P = 2^(c*S - m_ref) as hi + lo, two packed f16 tiles over the scores just read (hi: columns 0-31,
-                    // lo: columns 32-63).  hi keeps the top 11 bits of the f32 weight (a mask: exact in f16 for every
-                    // weight above 2^-14, and the weights that matter are >= 1 for the row's largest), lo is the
-                    // exact remainder rounded to f16: together ~21 bits, so that the result does not depend on how
-                    // the rounding errors of a few large weights happen to fall against the spread of V.
+                    // hi + lo: two packed f16 tiles (hi: columns 0-63 of the buffer, lo: columns 64-127).  hi keeps the
+                    // top 11 bits of the f32 weight (a mask: exact in f16 for every weight above 2^-14, and the weights
+                    // that matter are >= 1 for the row's largest), lo is the exact remainder rounded to f16: together ~21
+                    // bits, so that the result does not depend on how the rounding errors of a few large weights happen
+                    // to fall against the spread of V.
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         uint32_t hi[8], lo[8];
@@ -736,34 +791,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             hi[i] = pack_half2(h0, h1);
                             lo[i] = pack_half2(p0 - h0, p1 - h1);
                         }
-                        tmem_st8_nowait(t_s + 8 * g, hi);
-                        tmem_st8_nowait(t_s + 32 + 8 * g, lo);
+                        tmem_st8_nowait(t_s + 8 * (4 * half + g), hi);
+                        tmem_st8_nowait(t_s + kKeys / 2 + 8 * (4 * half + g), lo);
                     }
                 } else {
-                    // P = 2^(c*S - m_ref) as packed f16 over the first half of the scores just read
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t h[16];
+                    for (int g = 0; g < 4; ++g) {
+                        uint32_t h[8];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i]), mul, -m_sub)),
-                                              ex2_approx(fmaf(__uint_as_float(r[32 * c + 2 * i + 1]), mul, -m_sub)));
-                        tmem_st16_nowait(t_s + 16 * c, h);
+                        for (int i = 0; i < 8; ++i)
+                            h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), mul, -m_sub)),
+                                              ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), mul, -m_sub)));
+                        tmem_st8_nowait(t_s + 8 * (4 * half + g), h);
                     }
                 }
                 PROF_STOP(2);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bP0 + 8 * sb);  // this warp's rows of P are in TMEM
+                if (lane == 0) mbar_arrive(bP0 + 8 * sb);  // this warp's rows of its half of P are in TMEM
                 if (tid == 0) PROF_TRACE(1, T);
                 PROF_STOP(3);
             }
             if (!ok || aborted()) break;
             PROF_COUNT(9, 1);
         }
-        // 0 other, 1 wait S, 2 softmax blocks, 3 store wait + signal, 7 tiles, 9 items, 10 wait for the scores' load, 11 tile maximum
-        if (lane == 0) PROF_FLUSH(9 + 0, 12);
+        // 0 other, 1 wait S, 2 softmax blocks, 3 store wait + signal, 7 tiles, 9 items, 10 wait for the scores' load, 11 tile maximum + trade
+        if (lane == 0 && half == 0) PROF_FLUSH(9 + 0, 12);
     }
 
     // common exit: every role has left its loop; release TMEM
@@ -873,14 +927,14 @@ bool tc_route_ok(const vox_attn_args * a) {
 // query tiles, planes), one thread per row, into words cleared beforehand (one CTA per query tile walking all its key
 // tiles needs no clearing but measured slower: 95.6 against 73.2 us per layer at 2048 tokens x 2).
 __global__ void __launch_bounds__(kTile) mask_tiles_kernel(const uint8_t * mask, size_t nb1, size_t nb2, size_t nb3, int ne2, int n_q,
-                                                           int n_kv, unsigned long long * live) {
-    const int row = blockIdx.y * kTile + threadIdx.x, k0 = blockIdx.x * kKeys;
+                                                           int n_kv, int tok, unsigned long long * live) {
+    const int row = blockIdx.y * tok + threadIdx.x, k0 = blockIdx.x * kKeys;  // a query tile holds `tok` tokens
     const int i2 = blockIdx.z % ne2, i3 = blockIdx.z / ne2;
     int       any = 0;
-    if (row < n_q) {
+    if (threadIdx.x < tok && row < n_q) {
         const uint4 * m = reinterpret_cast<const uint4 *>(mask + (size_t) row * nb1 + (size_t) i2 * nb2 + (size_t) i3 * nb3 + (size_t) k0 * 2);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < kKeys / 8; ++c) {
             if (k0 + 8 * c < n_kv) {  // n_kv is a multiple of 8: a piece lies wholly inside or outside
                 const uint4    x    = __ldg(m + c);
                 const uint32_t w[4] = {x.x, x.y, x.z, x.w};
@@ -893,9 +947,21 @@ __global__ void __launch_bounds__(kTile) mask_tiles_kernel(const uint8_t * mask,
         atomicOr(live + (size_t) blockIdx.z * gridDim.y + blockIdx.y, 1ull << blockIdx.x);
 }
 
+// query heads of one kv head that share an item's 128 rows: the largest of 8, 4, 2, 1 that divides the GQA ratio
+int pack_of(const vox_attn_args * a) {
+    const long long gqa = a->k.ne[2] > 0 ? a->q.ne[2] / a->k.ne[2] : 1;
+    for (int pk = 8; pk > 1; pk >>= 1)
+        if (gqa % pk == 0) return pk;
+    return 1;
+}
+long long query_tiles_of(const vox_attn_args * a) {
+    const int tok = kTile / pack_of(a);
+    return (a->q.ne[1] + tok - 1) / tok;
+}
+
 // bytes of those words (0 when there are more than 64 key tiles: then every tile is walked)
 size_t mask_tiles_bytes(const vox_attn_args * a) {
-    const long long n_ktiles = (a->k.ne[1] + kKeys - 1) / kKeys, n_qtiles = (a->q.ne[1] + kTile - 1) / kTile;
+    const long long n_ktiles = (a->k.ne[1] + kKeys - 1) / kKeys, n_qtiles = query_tiles_of(a);
     if (a->mask.data == nullptr || n_ktiles > 64) return 0;
     return ((size_t) (a->mask.ne[2] * a->mask.ne[3] * n_qtiles * 8) + 255) & ~(size_t) 255;
 }
@@ -912,14 +978,14 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
         const size_t words = mask_tiles_bytes(a);
         const size_t rest  = q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;
         // worth its launch from a few thousand tiles on (512 tokens x 1 sequence is 512 tiles: not worth it)
-        const long long tiles = ((a->k.ne[1] + kKeys - 1) / kKeys) * ((a->q.ne[1] + kTile - 1) / kTile) * a->q.ne[2] * a->q.ne[3];
+        const long long tiles = ((a->k.ne[1] + kKeys - 1) / kKeys) * query_tiles_of(a) * (a->q.ne[2] / pack_of(a)) * a->q.ne[3];
         if (words > 0 && workspace_bytes >= words + rest && tiles >= 2048) {
             unsigned long long * live = static_cast<unsigned long long *>(workspace);
             VOX_CUDA_TRY(cudaMemsetAsync(live, 0, words, st));
-            const dim3 grid((unsigned) ((a->k.ne[1] + kKeys - 1) / kKeys), (unsigned) ((a->q.ne[1] + kTile - 1) / kTile),
+            const dim3 grid((unsigned) ((a->k.ne[1] + kKeys - 1) / kKeys), (unsigned) query_tiles_of(a),
                             (unsigned) (a->mask.ne[2] * a->mask.ne[3]));
             mask_tiles_kernel<<<grid, kTile, 0, st>>>(static_cast<const uint8_t *>(a->mask.data), a->mask.nb[1], a->mask.nb[2], a->mask.nb[3],
-                                                      (int) a->mask.ne[2], (int) a->q.ne[1], (int) a->k.ne[1], live);
+                                                      (int) a->mask.ne[2], (int) a->q.ne[1], (int) a->k.ne[1], kTile / pack_of(a), live);
             int rc = check_launch(e, "mask_tiles_kernel");
             if (rc != VOX_ATTN_OK) return rc;
             tile_live       = live;
@@ -1002,13 +1068,16 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     p.m_ne2 = with_mask ? (int) a->mask.ne[2] : 1; p.m_ne3 = with_mask ? (int) a->mask.ne[3] : 1;
     p.tile_live = tile_live;
     p.n_batch  = (int) a->q.ne[3];
-    p.n_qtiles = (p.n_q + kTile - 1) / kTile;
-    const long long items = (long long) p.n_qtiles * p.n_heads * p.n_batch;
+    p.pack      = pack_of(a);
+    p.tok       = kTile / p.pack;
+    p.n_hgroups = p.n_heads / p.pack;
+    p.n_qtiles  = (int) query_tiles_of(a);
+    const long long items = (long long) p.n_qtiles * p.n_hgroups * p.n_batch;
     VOX_REQUIRE(items < (1LL << 30), VOX_ATTN_INVALID_ARGUMENT, "too many query tiles");
     p.n_items = (int) items;
-    // persistent CTAs, two per SM (105 KB of shared memory, 256 TMEM columns and half the register file each); one
-    // per SM when K/V were expanded (137 KB: every operand tile comes with its remainder tile)
-    dim3 grid((unsigned) std::min<long long>(items, (v_lo ? 1LL : 2LL) * e->sm_count));
+    // persistent CTAs, one per SM (all 512 TMEM columns, 131 KB of shared memory; 195 KB when K/V were expanded and every
+    // operand tile comes with its remainder tile)
+    dim3 grid((unsigned) std::min<long long>(items, (long long) e->sm_count));
     if (with_mask && v_lo) launch_pdl(prefill_tc_kernel<true, true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
     else if (with_mask) launch_pdl(prefill_tc_kernel<true, false, true>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
     else if (v_lo) launch_pdl(prefill_tc_kernel<true, true, false>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
