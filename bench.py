@@ -63,7 +63,7 @@ def parse():
     p.add_argument("--prefill-kv", default="f16", choices=["f16", "q8_0"], help="K/V operand type for --workload prefill")
     p.add_argument("--prefill-mask", action="store_true",
                    help="--workload prefill through vox_attn_forward with the causal mask as a tensor, as the reference's call site passes it")
-    p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1"],
+    p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1", "decode_profile", "locdit_profile"],
                    help="serving = the headline line; the others time one more configuration each on one GPU")
     return p.parse_args()
 
@@ -442,6 +442,18 @@ def aux_workload(args, pkg, torch):
         out["results"] = time_prefill(pkg, torch, eng, timer, shapes, args.prefill_kv, args.prefill_mask, cpu=not args.no_cpu_baseline)
     elif args.workload == "decode_c1":
         out["results"] = [time_decode_shape(pkg, torch, eng, timer, 256, 1, "f16", BASE_LAYERS, 0, cpu=not args.no_cpu_baseline)]
+    elif args.workload == "decode_profile":
+        # a reduced instance of the serving launch for profiler captures: one layer, 128 streams of 4096 rows (268 MB of
+        # f16 K/V, 142 MB of q8_0: more than the L2 holds, far less than the serving workload's 8 to 17 GB)
+        out["results"] = [time_decode_shape(pkg, torch, eng, timer, 4096, 128, args.kv_type, 1, 0, cpu=False)]
+    elif args.workload == "locdit_profile":
+        # the same for the LocDiT launch: 64 patches x 8 layers, one CFM timestep per launch (85 MB per launch)
+        g = pkg.Group(eng, n_streams=64, max_len=64, kv_type=pkg.F16, base_layers=0, res_layers=0, n_heads=H, n_kv_heads=HK,
+                      locdit_layers=DIT_LAYERS, locdit_seq=DIT_SEQ, cfm_steps=2)
+        bufs = {n: torch.randn(s, device="cuda") for n, s in g.buffer_shapes().items() if n.startswith("dit_")}
+        ms = timer.ms(lambda: g.step(bufs, advance=False), 10)
+        out["results"] = [{"config": "LocDiT 64 patches x 8 layers, 2 CFM timesteps per step", "us_per_launch": ms * 1e3 / 2}]
+        g.close()
     else:
         for t in ("f16", "q8_0"):
             for B in (1, 32):

@@ -469,7 +469,7 @@ def test_decode_rotates_q_and_the_arriving_row(kv, engine, pkg, oracle, vo):
     t_dev = engine.rope_table(dev(np.array(lens, np.int32)), pos_offset=-1, freq_base=1000000.0, attn_factor=1.05, freq_factors=dev(ff))
     out2 = cache2.decode(0, dev(q), dev(np.array(lens, np.int32)), max(lens), k_new=dev(k_new), v_new=dev(v_new), rope_table=t_dev)
     engine.sync_status()
-    assert rel_err(out2.cpu().numpy(), out) < 1e-4
+    assert rel_err(out2.cpu().numpy(), out) < TOL[kv] / 20  # q8_0: an angle off in the last place can move a stored byte
 
 
 def test_decode_refuses_bad_arguments(engine, pkg):

@@ -1,7 +1,7 @@
 // Shared declarations of the attention engine: status handling, the engine object, and
 // thin wrappers over the sm_100a PTX the kernels use (mbarrier, bulk-tensor copies,
 // ldmatrix, mma).  Every device-side wait in this code base goes through mbar_wait_bounded or
-// mbar_wait_spin, which compare the SM clock with a limit every 1024 polls, give up when it is
+// mbar_wait_spin, which compare the SM clock with a limit every few polls, give up when it is
 // exceeded and report through the engine's status word instead of spinning forever.
 #pragma once
 
@@ -138,26 +138,31 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll.  try_wait parks the thread in hardware until the phase completes or a time limit passes; the limit asked for
+// here (the suspend-time hint, in ns) is long, so that a thread whose wait is long (a producer facing a full ring, a
+// consumer ahead of the copies) polls rarely and leaves the issue slots to the warps that have work: with the default
+// limit the waiting warps of the q8_0 decode kernel accounted for about a quarter of all instructions issued.  The
+// thread wakes as soon as the phase completes, whatever the limit.
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
-// Returns false when the phase did not complete in time.  try_wait already parks the thread in
-// hardware for a short while, so the loop polls back to back (waking late costs more than polling);
-// every 1024 failed polls the elapsed clock is checked against kWaitCycles (about two seconds).
+// Returns false when the phase did not complete in time.  The loop polls back to back (each poll parks the thread,
+// see above); every 16 failed polls the elapsed clock is checked against kWaitCycles (about two seconds).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 0 && clock64() - t0 > limit) return false;
+        if ((i & 15u) == 0 && clock64() - t0 > limit) return false;
     }
 }
 

@@ -196,14 +196,14 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 __device__ __forceinline__ float half_lo(uint32_t x) { return __half2float(__ushort_as_half((unsigned short) (x & 0xffffu))); }
 __device__ __forceinline__ float half_hi(uint32_t x) { return __half2float(__ushort_as_half((unsigned short) (x >> 16))); }
 
-// four signed bytes -> two half2 registers holding the exact values.  A byte b is biased to b+128,
-// placed in the mantissa of 1024.0h (0x6400 | b+128 == 1024 + b + 128) and 1152 is subtracted.
-// `sel_a` / `sel_b` pick which two bytes go to each register (PRMT selectors, 4 = the 0x64 byte).
-__device__ __forceinline__ uint32_t s8_pair_to_half2(uint32_t biased, uint32_t selector) {
-    const uint32_t h  = __byte_perm(biased, 0x64646464u, selector);
-    const __half2  r  = __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half((unsigned short) 0x6480)));
-    return *reinterpret_cast<const uint32_t *>(&r);
-}
+// Bytes of a q8_0 plane -> f16 tensor-core operands without arithmetic.  The planes hold u = q + 128 (1..255); a byte
+// in the low half of a 16-bit word whose high half is zero is the (subnormal) f16 number u * 2^-24, which mma.sync
+// takes as it is.  `selector` picks which two bytes of the word go to the two halves (PRMT, 4 = a zero byte).  The
+// products then carry (q + 128) * 2^-24: the factor goes into the step that consumes the accumulator anyway, and the
+// 128 comes out of the accumulator as 128 times the sum of the other operand, taken once (K: the row sums of Q per
+// 32-value block, known when Q is loaded; V: the running sums of the weights).
+constexpr float kTwo24 = 16777216.0f, kTwoM24 = 1.0f / 16777216.0f;
+__device__ __forceinline__ uint32_t u8_pair_to_half2(uint32_t bytes, uint32_t selector) { return __byte_perm(bytes, 0u, selector); }
 
 // The row that arrives with this call, stored by the producer warp (lane l holds elements 2l, 2l+1 of K
 // and of V; converted exactly as kv_append_kernel converts them) before it requests the tile that
@@ -220,8 +220,8 @@ __device__ __forceinline__ void store_arriving_row(float2 kk, float2 vv, uint8_t
         float dk, dv;
         q8_0_quantize_pair(kk.x, kk.y, qk, dk);
         q8_0_quantize_pair(vv.x, vv.y, qv, dv);
-        *reinterpret_cast<char2 *>(k_dst + lane * 2) = qk;
-        *reinterpret_cast<char2 *>(v_dst + lane * 2) = qv;
+        *reinterpret_cast<uchar2 *>(k_dst + lane * 2) = q8_0_biased(qk);
+        *reinterpret_cast<uchar2 *>(v_dst + lane * 2) = q8_0_biased(qv);
         if ((lane & 15) == 0) {
             *reinterpret_cast<__half *>(ks_dst + (lane >> 4) * 2) = __float2half_rn(dk);
             *reinterpret_cast<__half *>(vs_dst + (lane >> 4) * 2) = __float2half_rn(dv);
@@ -401,6 +401,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         //         d = 32*(s/2) + 8t + 4*(s%2) + {0,1,2,3}, so that k-steps 0,1 / 2,3 stay inside one
         //         32-value quantisation block and the block scale can be applied to their accumulator.
         uint32_t qa[4][4];
+        float    q_bias[2] = {0.0f, 0.0f};  // q8_0: what the +128 of the K bytes contributes to a score, per 32-value block
         {
             const int     head = kvh * p.gqa + min(g, p.gqa - 1);
             const float * qrow = reinterpret_cast<const float *>(p.q + (size_t) stream * p.q_nb_stream + (size_t) head * p.q_nb_head);
@@ -441,30 +442,36 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 qa[c][1] = pack_half2(l0, l1);
                 qa[c][2] = pack_half2(h2, h3);
                 qa[c][3] = pack_half2(l2, l3);
+                if constexpr (Q8) q_bias[c >> 1] += ((h0 + l0) + (h1 + l1)) + ((h2 + l2) + (h3 + l3));
+            }
+            if constexpr (Q8) {
+                // k-steps 2b, 2b+1 hold the lane's share of block b: summed over the four lanes of a head, times 128 * 2^-24,
+                // that is what the bias of the K bytes adds to every score of the block
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    q_bias[b] += __shfl_xor_sync(0xffffffffu, q_bias[b], 1);
+                    q_bias[b] += __shfl_xor_sync(0xffffffffu, q_bias[b], 2);
+                    q_bias[b] *= 128.0f * kTwoM24;
+                }
             }
         }
-        // the mask row of this lane's head (rows g and g + 8 of the A operand are the same head)
-        const __half * mrow = nullptr;
-        if (p.mask != nullptr) {
-            const int head = kvh * p.gqa + min(g, p.gqa - 1);
-            mrow = reinterpret_cast<const __half *>(p.mask + (size_t) (head % p.mask_ne2) * p.mask_nb_head +
-                                                    (size_t) (stream % p.mask_ne3) * p.mask_nb_stream);
-        }
-
         float o[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
         float m = -INFINITY, l = 0.0f;
+        float v_bias[2] = {0.0f, 0.0f};  // q8_0: this lane's share of the sums of the V-scaled weights, per 32-column block
 
-        // Tiles per pass of a consumer warp.  q8_0 takes two (its 16 rows of each): the byte unpacking and the per-block
-        // scales make its dependency chains long, and two independent tiles in one pass give the scheduler something to
-        // overlap them with; max, rescale decision and row sum are then taken once per 32 rows.  Measured per 256-stream
-        // launch: at 3 CTAs per SM (115 registers) 48.2 -> 45.4 us; at 4 CTAs per SM (96 registers, the configuration
-        // used) 43.9 -> 43.8 us: with that register budget the compiler cannot keep both chains in flight.
+        // Tiles per pass of a consumer warp: one.  Two (both cache types were tried: two independent tiles in one pass
+        // give the scheduler something to overlap the dependency chains with) measured the same or slower: f16 50.6
+        // against 49.9 us per 256-stream launch (it holds two ring stages at a time), q8_0 43.8 against 43.9 us at four
+        // CTAs per SM, where the 96 registers a thread may have cannot keep both chains in flight.
 #ifndef VOX_DECODE_U_F16
 #define VOX_DECODE_U_F16 1
 #endif
-        constexpr int U = Q8 ? 2 : VOX_DECODE_U_F16;  // f16 with two tiles per pass measured 50.6 against 49.9 us: it holds two stages at a time
+#ifndef VOX_DECODE_U_Q8
+#define VOX_DECODE_U_Q8 1
+#endif
+        constexpr int U = Q8 ? VOX_DECODE_U_Q8 : VOX_DECODE_U_F16;
         for (int i = 0; i < seg && ok; i += U) {
             int  st[U], p0[U];
             bool have[U], act[U];
@@ -514,18 +521,18 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const int row = 16 * warp + 8 * j + g;
-                            float     sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // one accumulator per 32-value block
+                            // one accumulator per 32-value block; the hi rows start at minus the bias of the block
+                            float     sc[2][4] = {{-q_bias[0], -q_bias[0], 0.f, 0.f}, {-q_bias[1], -q_bias[1], 0.f, 0.f}};
 #pragma unroll
                             for (int b = 0; b < 2; ++b) {
                                 const uint2 raw = lds64(kb + row * 64 + (((2 * b + (t >> 1)) ^ ((row >> 1) & 3)) << 4) + ((t & 1) << 3));
-                                const uint32_t x0 = raw.x ^ 0x80808080u, x1 = raw.y ^ 0x80808080u;
-                                mma_16816(sc[b], qa[2 * b], s8_pair_to_half2(x0, 0x4140), s8_pair_to_half2(x0, 0x4342));
-                                mma_16816(sc[b], qa[2 * b + 1], s8_pair_to_half2(x1, 0x4140), s8_pair_to_half2(x1, 0x4342));
+                                mma_16816(sc[b], qa[2 * b], u8_pair_to_half2(raw.x, 0x4140), u8_pair_to_half2(raw.x, 0x4342));
+                                mma_16816(sc[b], qa[2 * b + 1], u8_pair_to_half2(raw.y, 0x4140), u8_pair_to_half2(raw.y, 0x4342));
                             }
                             // scales of positions 8j+2t and 8j+2t+1, both blocks: four consecutive halves
                             const uint2 ds = lds64(ksc + (16 * warp + 8 * j + 2 * t) * 4);
-                            sv[u][j][0] = (sc[0][0] + sc[0][2]) * half_lo(ds.x) + (sc[1][0] + sc[1][2]) * half_hi(ds.x);
-                            sv[u][j][1] = (sc[0][1] + sc[0][3]) * half_lo(ds.y) + (sc[1][1] + sc[1][3]) * half_hi(ds.y);
+                            sv[u][j][0] = ((sc[0][0] + sc[0][2]) * half_lo(ds.x) + (sc[1][0] + sc[1][2]) * half_hi(ds.x)) * kTwo24;
+                            sv[u][j][1] = ((sc[0][1] + sc[0][3]) * half_lo(ds.y) + (sc[1][1] + sc[1][3]) * half_hi(ds.y)) * kTwo24;
                         }
                     }
                 }
@@ -535,8 +542,13 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const int pos = p0[u] + 8 * j + 2 * t;  // this lane's two positions: pos, pos + 1
-                        if (mrow != nullptr && pos < c1) {
-                            // additive mask in natural units; the scores are in units of log2 e
+                        if (p.mask != nullptr && pos < c1) {
+                            // additive mask in natural units (the scores are in units of log2 e): the row of this lane's head
+                            // (rows g and g + 8 of the A operand are the same head); the pointer is rebuilt here rather than
+                            // kept in registers across the tile loop, which the q8_0 form cannot spare
+                            const int      head = kvh * p.gqa + min(g, p.gqa - 1);
+                            const __half * mrow = reinterpret_cast<const __half *>(p.mask + (size_t) (head % p.mask_ne2) * p.mask_nb_head +
+                                                                                   (size_t) (stream % p.mask_ne3) * p.mask_nb_stream);
                             const float2 mv = make_float2(__half2float(mrow[pos]), pos + 1 < c1 ? __half2float(mrow[pos + 1]) : 0.0f);
                             sv[u][j][0] += mv.x * 1.4426950408889634f;
                             sv[u][j][1] += mv.y * 1.4426950408889634f;
@@ -568,6 +580,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                     for (int n = 0; n < 8; ++n) {
                         o[n][0] *= alpha; o[n][1] *= alpha; o[n][2] *= alpha; o[n][3] *= alpha;
                     }
+                    v_bias[0] *= alpha; v_bias[1] *= alpha;
                 }
                 if constexpr (!Q8) {
                     float psum = 0.0f;
@@ -609,10 +622,13 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #pragma unroll
                             for (int b = 0; b < 2; ++b) {
                                 // weights times V scale rounded to f16 once (2^-12 relative, far inside the q8_0
-                                // tolerance): the lo rows of the A operand stay zero
-                                pa[b][2 * j]     = pack_half2(pr[u][j][0] * (b ? half_hi(ds.x) : half_lo(ds.x)),
-                                                              pr[u][j][1] * (b ? half_hi(ds.y) : half_lo(ds.y)));
+                                // tolerance): the lo rows of the A operand stay zero.  Their sum is what the +128 of
+                                // the V bytes multiplies.
+                                const float w0 = pr[u][j][0] * (b ? half_hi(ds.x) : half_lo(ds.x));
+                                const float w1 = pr[u][j][1] * (b ? half_hi(ds.y) : half_lo(ds.y));
+                                pa[b][2 * j]     = pack_half2(w0, w1);
                                 pa[b][2 * j + 1] = 0u;
+                                v_bias[b] += w0 + w1;
                             }
                         }
                         // ldmatrix.trans on 16-bit units keeps byte pairs together: a register holds
@@ -622,11 +638,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                         for (int cp = 0; cp < 2; ++cp) {
                             uint32_t r0, r1, r2, r3;
                             ldmatrix_x4_trans(vb + v_row * 64 + (((2 * cp + v_chk) ^ ((v_row >> 1) & 3)) << 4), r0, r1, r2, r3);
-                            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-                            mma_16816(o[4 * cp + 0], pa[cp], s8_pair_to_half2(r0, 0x4240), s8_pair_to_half2(r1, 0x4240));
-                            mma_16816(o[4 * cp + 1], pa[cp], s8_pair_to_half2(r0, 0x4341), s8_pair_to_half2(r1, 0x4341));
-                            mma_16816(o[4 * cp + 2], pa[cp], s8_pair_to_half2(r2, 0x4240), s8_pair_to_half2(r3, 0x4240));
-                            mma_16816(o[4 * cp + 3], pa[cp], s8_pair_to_half2(r2, 0x4341), s8_pair_to_half2(r3, 0x4341));
+                            mma_16816(o[4 * cp + 0], pa[cp], u8_pair_to_half2(r0, 0x4240), u8_pair_to_half2(r1, 0x4240));
+                            mma_16816(o[4 * cp + 1], pa[cp], u8_pair_to_half2(r0, 0x4341), u8_pair_to_half2(r1, 0x4341));
+                            mma_16816(o[4 * cp + 2], pa[cp], u8_pair_to_half2(r2, 0x4240), u8_pair_to_half2(r3, 0x4240));
+                            mma_16816(o[4 * cp + 3], pa[cp], u8_pair_to_half2(r2, 0x4341), u8_pair_to_half2(r3, 0x4341));
                         }
                     }
                 }
@@ -641,6 +656,19 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if constexpr (Q8) {
+            // the accumulators hold sum(w * (v + 128)) * 2^-24: back to sum(w * v)
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                v_bias[b] += __shfl_xor_sync(0xffffffffu, v_bias[b], 1);
+                v_bias[b] += __shfl_xor_sync(0xffffffffu, v_bias[b], 2);
+            }
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                o[n][0] = fmaf(o[n][0], kTwo24, -128.0f * v_bias[n >> 2]);
+                o[n][1] = fmaf(o[n][1], kTwo24, -128.0f * v_bias[n >> 2]);
+            }
+        }
         if (tid == 0 && f + seg >= f1) DECODE_TRACE(4);
 
         // ---- merge the four warps through the stage of the last tile (all of them are done with it after the barrier)
@@ -913,13 +941,13 @@ __global__ void __launch_bounds__(256) q8_0_blocks_to_planes_kernel(const Repack
         const int       kvh = (int) ((row / p.n_pad) % p.n_kvh);
         const int       b   = (int) (row / ((long long) p.n_pad * p.n_kvh));
         uint32_t        q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        uint16_t        d    = 0;  // rows past n_kv (up to the next multiple of the tile) hold zeros
+        uint16_t        d    = 0;  // rows past n_kv (up to the next multiple of the tile) have a zero scale
         if (pos < p.n_kv) {
             const uint16_t * s = reinterpret_cast<const uint16_t *>(src + (size_t) pos * nb1 + (size_t) kvh * nb2 + (size_t) b * nb3 +
                                                                     (size_t) blk * 34);
             d = s[0];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = (uint32_t) s[1 + 2 * j] | ((uint32_t) s[2 + 2 * j] << 16);
+            for (int j = 0; j < 8; ++j) q[j] = ((uint32_t) s[1 + 2 * j] | ((uint32_t) s[2 + 2 * j] << 16)) ^ 0x80808080u;  // q + 128, as the cache planes hold it
         }
         uint4 * o = reinterpret_cast<uint4 *>(rows + (size_t) row * 64 + (size_t) blk * 32);
         o[0] = make_uint4(q[0], q[1], q[2], q[3]);

@@ -35,7 +35,7 @@ __device__ __forceinline__ void write_row(const CacheView & c, uint8_t * data, u
         char2 q;
         float d;
         q8_0_quantize_pair(x0, x1, q, d);
-        *reinterpret_cast<char2 *>(data + off + lane * 2) = q;
+        *reinterpret_cast<uchar2 *>(data + off + lane * 2) = q8_0_biased(q);
         if ((lane & 15) == 0) {
             const size_t soff = (size_t) layer * c.sb_layer + (size_t) stream * c.sb_stream + (size_t) head * c.sb_head +
                                 (size_t) pos * c.sb_pos;
@@ -165,7 +165,9 @@ int vox_kv_create(vox_engine * e, const vox_kv_config * cfg, vox_kv_cache ** out
         c->k_scale = base + 2 * plane;
         c->v_scale = base + 2 * plane + splane;
     }
-    err = cudaMemset(base, 0, c->bytes);  // MiniCPMKVCache::init ends with clear()
+    // MiniCPMKVCache::init ends with clear(): every stored value is zero (a q8_0 byte plane holds q + 128)
+    err = cudaMemset(base, 0, c->bytes);
+    if (err == cudaSuccess && q8) err = cudaMemset(base, 0x80, 2 * plane);
     if (err == cudaSuccess) {
         const size_t n_ctr = (size_t) cfg->n_layers * cfg->n_streams * cfg->n_kv_heads;
         err = cudaMalloc(reinterpret_cast<void **>(&c->counters), sizeof(int) * n_ctr);
@@ -225,14 +227,16 @@ int vox_kv_clear(vox_kv_cache * c, int stream_id, void * stream) {
     VOX_REQUIRE(stream_id >= -1 && stream_id < c->cfg.n_streams, VOX_ATTN_INVALID_ARGUMENT, "stream_id %d out of range",
                 stream_id);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int zero = c->cfg.type == VOX_TYPE_Q8_0 ? 0x80 : 0;  // a q8_0 byte plane holds q + 128
     if (stream_id < 0) {
         VOX_CUDA_TRY(cudaMemsetAsync(c->k_data, 0, c->bytes, st));
+        if (zero) VOX_CUDA_TRY(cudaMemsetAsync(c->k_data, zero, 2 * c->nb_layer * c->cfg.n_layers, st));
         return VOX_ATTN_OK;
     }
     for (int l = 0; l < c->cfg.n_layers; ++l) {
         const size_t off = (size_t) l * c->nb_layer + (size_t) stream_id * c->nb_stream;
-        VOX_CUDA_TRY(cudaMemsetAsync(c->k_data + off, 0, c->nb_stream, st));
-        VOX_CUDA_TRY(cudaMemsetAsync(c->v_data + off, 0, c->nb_stream, st));
+        VOX_CUDA_TRY(cudaMemsetAsync(c->k_data + off, zero, c->nb_stream, st));
+        VOX_CUDA_TRY(cudaMemsetAsync(c->v_data + off, zero, c->nb_stream, st));
         if (c->k_scale) {
             const size_t soff = (size_t) l * c->sb_layer + (size_t) stream_id * c->sb_stream;
             VOX_CUDA_TRY(cudaMemsetAsync(c->k_scale + soff, 0, c->sb_stream, st));
@@ -308,6 +312,7 @@ static int kv_transfer(const vox_kv_cache * c, int layer, int stream_id, int n_p
             if (to_host) {
                 VOX_CUDA_TRY(cudaMemcpy(qbuf.data(), dev, qbuf.size(), cudaMemcpyDeviceToHost));
                 VOX_CUDA_TRY(cudaMemcpy(sbuf.data(), sdev, sbuf.size(), cudaMemcpyDeviceToHost));
+                for (auto & b : qbuf) b ^= 0x80;  // the plane holds q + 128
                 for (int p = 0; p < n_pos; ++p)
                     for (int b = 0; b < 2; ++b) {
                         memcpy(hp + (size_t) p * 68 + b * 34, sbuf.data() + (size_t) p * 4 + b * 2, 2);
@@ -319,6 +324,7 @@ static int kv_transfer(const vox_kv_cache * c, int layer, int stream_id, int n_p
                         memcpy(sbuf.data() + (size_t) p * 4 + b * 2, hp + (size_t) p * 68 + b * 34, 2);
                         memcpy(qbuf.data() + (size_t) p * 64 + b * 32, hp + (size_t) p * 68 + b * 34 + 2, 32);
                     }
+                for (auto & b : qbuf) b ^= 0x80;  // the plane holds q + 128
                 VOX_CUDA_TRY(cudaMemcpy(dev, qbuf.data(), qbuf.size(), cudaMemcpyHostToDevice));
                 VOX_CUDA_TRY(cudaMemcpy(sdev, sbuf.data(), sbuf.size(), cudaMemcpyHostToDevice));
             }

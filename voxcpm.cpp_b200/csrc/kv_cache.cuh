@@ -8,7 +8,7 @@ constexpr int kKvTile = 64;  // cache rows moved per bulk-tensor copy
 struct vox_kv_cache {
     vox_engine *  e = nullptr;
     vox_kv_config cfg{};
-    // data planes: f16 rows (128 B) or int8 rows (64 B); [layer][stream][kv_head][pos][64]
+    // data planes: f16 rows (128 B) or int8 rows (64 B, each byte q + 128); [layer][stream][kv_head][pos][64]
     uint8_t * k_data = nullptr;
     uint8_t * v_data = nullptr;
     size_t    nb_pos = 0, nb_head = 0, nb_stream = 0, nb_layer = 0;
@@ -56,6 +56,13 @@ __device__ __forceinline__ void q8_0_quantize_pair(float x0, float x1, char2 & q
     const float id = d != 0.0f ? 1.0f / d : 0.0f;
     q.x = (signed char) (int) roundf(x0 * id);
     q.y = (signed char) (int) roundf(x1 * id);
+}
+// The int8 plane of a q8_0 cache holds q + 128 as unsigned bytes (1..255): such a byte, placed in the low byte of a
+// 16-bit word whose high byte is zero, IS the f16 number (q + 128) * 2^-24, so the decode kernel turns bytes into tensor-core
+// operands with one byte permute and takes the 128 out of its accumulators once.  vox_kv_export / vox_kv_import
+// convert to and from the reference's signed bytes.
+__device__ __forceinline__ uchar2 q8_0_biased(char2 q) {
+    return make_uchar2((unsigned char) ((int) q.x + 128), (unsigned char) ((int) q.y + 128));
 }
 #endif
 
