@@ -63,7 +63,7 @@ def parse():
     p.add_argument("--prefill-kv", default="f16", choices=["f16", "q8_0"], help="K/V operand type for --workload prefill")
     p.add_argument("--prefill-mask", action="store_true",
                    help="--workload prefill through vox_attn_forward with the causal mask as a tensor, as the reference's call site passes it")
-    p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1", "decode_profile", "locdit_profile"],
+    p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1", "decode_profile", "locdit_profile", "projection"],
                    help="serving = the headline line; the others time one more configuration each on one GPU")
     return p.parse_args()
 
@@ -394,6 +394,33 @@ def time_prefill(pkg, torch, eng, timer, shapes, kv="f16", with_mask=False, cpu=
     return out
 
 
+def time_projection(pkg, torch, eng, timer, S, hidden=1024, layers=BASE_LAYERS + RES_LAYERS):
+    """The batched Q/K/V projection with the rotary embedding in its epilogue (hidden -> 16 + 2 + 2 heads of 64, f16
+    weights) for S streams, one launch pair per layer with weights of its own, replayed from a CUDA graph: us per layer
+    with the weights where the previous replay left them (79 MB: they fit the L2) and with the L2 scrubbed first;
+    roofline = the weight bytes / time against the measured HBM peak."""
+    hbm, _, _ = measured_peaks()
+    gen = torch.Generator(device="cuda").manual_seed(S)
+    n_out = (H + 2 * HK) * D
+    w = (torch.randn((layers, n_out, hidden), device="cuda", generator=gen) / hidden ** 0.5).half()
+    x = torch.randn((layers, S, hidden), device="cuda", generator=gen)
+    pos = torch.randint(0, 4096, (S,), device="cuda", dtype=torch.int32, generator=gen)
+    table = eng.rope_table(pos)
+    for l in range(layers):
+        eng.qkv_project(x[l], w[l], H, HK, rope_table=table)
+    eng.sync_status()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for l in range(layers):
+            eng.qkv_project(x[l], w[l], H, HK, rope_table=table)
+    warm, cold = timer.ms(graph.replay, 20), timer.ms(graph.replay, 10, cold=True)
+    wbytes = n_out * hidden * 2.0
+    return {"config": f"Q/K/V projection {hidden} -> {n_out}, {S} streams, f16 weights, rotary embedding in the epilogue, x {layers} layers",
+            "warm_us_per_layer": warm * 1e3 / layers, "cold_us_per_layer": cold * 1e3 / layers, "weight_bytes_per_layer": wbytes,
+            "cold_weight_gb_s": wbytes * layers / (cold * 1e-3) / 1e9, "cold_frac_of_measured_hbm": wbytes * layers / (cold * 1e-3) / 1e9 / hbm,
+            "launches_per_layer": 2, "per_stream_in_the_reference": "one ggml_mul_mat + two ggml_rope_ext + two ggml_cpy nodes per stream and layer"}
+
+
 def time_decode_shape(pkg, torch, eng, timer, L, B, kv, n_base, n_res, cpu=False):
     """Single-token attention of `n_base + n_res` layers over B streams of L rows each, issued from C as one step
     (no append): warm and cold (L2 scrubbed) us per layer, GB/s, fraction of the measured HBM peak; for one stream
@@ -442,6 +469,8 @@ def aux_workload(args, pkg, torch):
         out["results"] = time_prefill(pkg, torch, eng, timer, shapes, args.prefill_kv, args.prefill_mask, cpu=not args.no_cpu_baseline)
     elif args.workload == "decode_c1":
         out["results"] = [time_decode_shape(pkg, torch, eng, timer, 256, 1, "f16", BASE_LAYERS, 0, cpu=not args.no_cpu_baseline)]
+    elif args.workload == "projection":
+        out["results"] = [time_projection(pkg, torch, eng, timer, S) for S in (256, 32)]
     elif args.workload == "decode_profile":
         # a reduced instance of the serving launch for profiler captures: one layer, 128 streams of 4096 rows (268 MB of
         # f16 K/V, 142 MB of q8_0: more than the L2 holds, far less than the serving workload's 8 to 17 GB)
@@ -718,6 +747,7 @@ def other_shapes(args, pkg, torch, eng, total_steps):
                 sweep.append(time_decode_shape(pkg, torch, eng, timer, L, B, t, BASE_LAYERS, RES_LAYERS, cpu=cpu and L in (1024, 8192)))
     out["decode_sweep"] = sweep
     out["decode_c1"] = time_decode_shape(pkg, torch, eng, timer, 256, 1, "f16", BASE_LAYERS, 0, cpu=cpu)
+    out["qkv_projection"] = [time_projection(pkg, torch, eng, timer, S) for S in (256, 32)]
     if cpu:
         out["locdit_cpu_baseline"] = cpu_attention_us(2, DIT_SEQ, DIT_SEQ, "f32", False, n_layers=CFM_STEPS * DIT_LAYERS)
     return out

@@ -199,6 +199,46 @@ typedef struct {
 int vox_rope_table(vox_engine * e, const vox_rope_config * cfg, const int32_t * positions, int pos_offset,
                    int n_streams, float * table, void * stream);
 
+/* ---------------------------------------------------------------- Q/K/V projection ------ */
+
+/* The three graph nodes in front of attention in MiniCPMModel::attention_forward (src/minicpm.cpp:644-701), for the
+ * single-token step of n_streams streams in ONE launch (plus a small one that rounds the activations to f16):
+ * ggml_mul_mat(qkv_proj, hidden) (:660-686, or q_proj / k_proj / v_proj stacked into one matrix), apply_rope on q and
+ * k (:688-689, :582-600) and the ggml_cpy of the new K and V rows into the cache views (:684-685).  The reference
+ * runs them per stream, reading the projection weights once per stream and step; here they are read once per step.
+ * Arithmetic as ggml's CPU backend does it for f16 weights (activations rounded to f16, f32 accumulation:
+ * third_party/ggml/src/ggml-cpu/ggml-cpu.c:217, ggml-cpu/vec.cpp:264), on tcgen05 tensor cores.
+ *   x          [hidden, n_streams] f32: the normed hidden state of each stream's token; x_nb_stream bytes apart
+ *   w_qkv      [hidden, (H + 2 HK) * 64] f16 in ggml's layout (a weight row per output feature, hidden contiguous;
+ *              Q rows first, then K, then V, as qkv_proj stores them); w_nb_row bytes between rows; w_type VOX_TYPE_F16
+ *   rope_table optional, from vox_rope_table for these streams' positions: q and k leave rotated (NULL: not rotated)
+ *   q          out [64, H, n_streams] f32 contiguous: what vox_attn_decode reads with q_nb_head = 256, q_nb_stream = H * 256
+ *   cache, layer, positions   the K and V rows go straight into the cache (converted as vox_kv_append converts them),
+ *              stream s's at row positions[s] + pos_offset (device array): the decode call that follows then takes
+ *              kv_len = that row + 1 and no k_new / v_new.  Or, with cache == NULL:
+ *   k_new, v_new   out [64, HK, n_streams] f32 contiguous, for the decode launch's own store (its k_new / v_new;
+ *              with rope_table given here, pass none there).
+ * workspace: vox_qkv_workspace_bytes (the f16 copy of x), 16-byte aligned.  Never allocates. */
+typedef struct {
+    int32_t         n_streams, hidden, n_heads, n_kv_heads, head_dim /* 64 */;
+    const float *   x;
+    size_t          x_nb_stream;
+    const void *    w_qkv;
+    size_t          w_nb_row;
+    int32_t         w_type;
+    const float *   rope_table;
+    float *         q;
+    float *         k_new;
+    float *         v_new;
+    vox_kv_cache *  cache;
+    int32_t         layer;
+    const int32_t * positions;
+    int32_t         pos_offset; /* added to every positions[s] (-1 when positions holds the lengths after the step) */
+} vox_qkv_args;
+
+size_t vox_qkv_workspace_bytes(int n_streams, int hidden);
+int    vox_qkv_project(vox_engine * e, const vox_qkv_args * a, void * workspace, size_t workspace_bytes, void * stream);
+
 /* ---------------------------------------------------------------- decode --------------- */
 
 /* One-token attention for n_streams independent streams in one launch (+ a merge launch when
@@ -316,6 +356,7 @@ typedef struct {
  *   lm_k_new  [D, HK, 1, S, L] f32   rows appended at position kv_len[s] before attending
  *   lm_v_new  same
  *   lm_out    [D, H, 1, S, L] f32
+ *   lm_hidden [hidden, S, L] f32   (only with vox_group_set_qkv_weights, instead of the three inputs above)
  *   dit_q     [D, seq, H,  2, locdit_layers, S, cfm_steps] f32;  dit_k, dit_v with HK
  *   dit_out   [D, H, seq, 2, locdit_layers, S, cfm_steps] f32
  * vox_group_step skips the LM stacks when lm_q is NULL and the LocDiT patch when dit_q is NULL.  */
@@ -328,6 +369,10 @@ typedef struct {
     const float * dit_k;
     const float * dit_v;
     float *       dit_out;
+    /* With projection weights set (vox_group_set_qkv_weights): [hidden, S, L] f32, the normed hidden state of every
+     * stream's token for every LM layer, INSTEAD of lm_q / lm_k_new / lm_v_new (which must then be NULL).  Every layer
+     * becomes projection (with the rotary embedding when the group has it set) + decode attention. */
+    const float * lm_hidden;
 } vox_step_buffers;
 
 int  vox_group_create(vox_engine * e, const vox_group_config * cfg, vox_group ** out);
@@ -345,6 +390,10 @@ size_t vox_group_step_bytes(const vox_group * g, int which /* 0 lm in, 1 lm out,
  * streams' positions (one launch) and every layer's decode launch rotates Q and the arriving K row.
  * freq_factors_host: 32 floats on the host (copied), or NULL.  cfg == NULL switches it off again. */
 int vox_group_set_rope(vox_group * g, const vox_rope_config * cfg, const float * freq_factors_host);
+/* Q/K/V projection inside the step (src/minicpm.cpp:660-686 for every LM layer): w is a device array of
+ * base_layers + res_layers matrices [hidden, (H + 2 HK) * 64] f16 in ggml's layout, nb_layer bytes apart, rows nb_row
+ * bytes apart (they stay the caller's).  vox_group_step then takes lm_hidden of vox_step_buffers.  w == NULL: off. */
+int vox_group_set_qkv_weights(vox_group * g, const void * w, int hidden, size_t nb_row, size_t nb_layer);
 
 /* Position-independent step (the reference rebuilds and re-reserves its step graph at every position,
  * src/voxcpm.cpp:485-513).  Lengths live on the device and are advanced there, so the launch sequence of

@@ -515,3 +515,21 @@ void voxo_rope_neox(float * x, int64_t n_rows, int n_dims, const float * table, 
         }
     }
 }
+
+/* ------------------------------------------------------------------ Q/K/V projection */
+
+/* ggml_mul_mat with f16 weights as the CPU backend computes it (ggml_compute_forward_mul_mat, vec_dot_type F16:
+ * third_party/ggml/src/ggml-cpu/ggml-cpu.c:217; ggml_vec_dot_f16, ggml-cpu/vec.cpp:264): the activations are rounded to
+ * f16 (from_float of the vec_dot_type), every product of two f16 values is exact in f32, and the sum is kept in f32
+ * (the reference sums in SIMD lanes, so the order differs from this loop; the result agrees to f32 rounding).
+ *   x [n_tok][k] f32, w [n_out][k] f16 bits, out [n_tok][n_out] f32 */
+void voxo_mul_mat_f16(const float * x, const uint16_t * w, int64_t n_tok, int64_t k, int64_t n_out, float * out) {
+    for (int64_t t = 0; t < n_tok; ++t) {
+        for (int64_t o = 0; o < n_out; ++o) {
+            float acc = 0.0f;
+            for (int64_t i = 0; i < k; ++i)
+                acc += voxo_fp16_to_fp32(voxo_fp32_to_fp16(x[t * k + i])) * voxo_fp16_to_fp32(w[o * k + i]);
+            out[t * n_out + o] = acc;
+        }
+    }
+}

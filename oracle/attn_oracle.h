@@ -89,4 +89,8 @@ void voxo_rope_neox(float * x, int64_t n_rows, int n_dims, const float * table, 
 #ifdef __cplusplus
 }
 #endif
+/* ggml_mul_mat with f16 weights (ggml-cpu.c:217, vec.cpp:264): activations rounded to f16, f32 accumulation.
+ *   x [n_tok][k] f32, w [n_out][k] f16 bits, out [n_tok][n_out] f32 */
+void voxo_mul_mat_f16(const float * x, const uint16_t * w, int64_t n_tok, int64_t k, int64_t n_out, float * out);
+
 #endif

@@ -155,4 +155,30 @@ int voxref_rope(const float * x, int64_t D, int64_t n_heads, int64_t n_tok, cons
     return rc;
 }
 
+// ggml_mul_mat(w, x) exactly as MiniCPMModel::attention_forward issues it for the Q/K/V projection
+// (src/minicpm.cpp:660): w [k, n_out] f16 (a weight row per output feature), x [k, n_tok] f32, out [n_out, n_tok] f32.
+int voxref_mul_mat_f16(const uint16_t * w, const float * x, int64_t k, int64_t n_out, int64_t n_tok, int n_threads, float * out) {
+    ggml_init_params ip = {
+        /*.mem_size   =*/ ggml_tensor_overhead() * 8 + ggml_graph_overhead_custom(16, false) + 4096,
+        /*.mem_buffer =*/ nullptr,
+        /*.no_alloc   =*/ true,
+    };
+    ggml_context * ctx = ggml_init(ip);
+    if (!ctx) return 2;
+    ggml_tensor * tw = ggml_new_tensor_2d(ctx, GGML_TYPE_F16, k, n_out);
+    ggml_tensor * tx = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, k, n_tok);
+    tw->data = (void *) w;
+    tx->data = (void *) x;
+    ggml_tensor * to = ggml_mul_mat(ctx, tw, tx);
+    to->data = out;
+    ggml_cgraph * gf = ggml_new_graph_custom(ctx, 16, false);
+    ggml_build_forward_expand(gf, to);
+    ggml_cplan plan = ggml_graph_plan(gf, n_threads, nullptr);
+    std::vector<uint8_t> work(plan.work_size + 64);
+    plan.work_data = work.data();
+    const int rc = ggml_graph_compute(gf, &plan) == GGML_STATUS_SUCCESS ? 0 : 3;
+    ggml_free(ctx);
+    return rc;
+}
+
 }  // extern "C"

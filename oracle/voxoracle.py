@@ -129,6 +129,17 @@ class Oracle:
                                 _ptr(pos_index))
         return rows.reshape(x.shape)
 
+    def mul_mat_f16(self, x, w) -> np.ndarray:
+        """ggml_mul_mat with f16 weights: x [n_tok, k] f32, w [n_out, k] f16 -> [n_tok, n_out] f32."""
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float16)
+        n_tok, k = x.shape
+        n_out = w.shape[0]
+        out = np.zeros((n_tok, n_out), np.float32)
+        i64 = ctypes.c_int64
+        self.lib.voxo_mul_mat_f16(_ptr(x), _ptr(w.view(np.uint16)), i64(n_tok), i64(k), i64(n_out), _ptr(out))
+        return out
+
     def causal_mask(self, positions, total_len: int) -> np.ndarray:
         pos = np.ascontiguousarray(positions, np.int32)
         out = np.zeros((len(pos), total_len), np.uint16)
@@ -218,6 +229,19 @@ class RefGgml:
         i64 = ctypes.c_int64
         rc = self.lib.voxref_rope(_ptr(x), i64(D), i64(n_heads), i64(n_tok), _ptr(pos), _ptr(ff), int(n_ctx_orig),
                                   ctypes.c_float(freq_base), ctypes.c_float(attn_factor), int(n_threads), _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"reference harness failed (code {rc})")
+        return out
+
+    def mul_mat_f16(self, x, w, n_threads=1) -> np.ndarray:
+        """The reference's ggml_mul_mat: x [n_tok, k] f32, w [n_out, k] f16 -> [n_tok, n_out] f32."""
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float16)
+        n_tok, k = x.shape
+        n_out = w.shape[0]
+        out = np.zeros((n_tok, n_out), np.float32)
+        i64 = ctypes.c_int64
+        rc = self.lib.voxref_mul_mat_f16(_ptr(w.view(np.uint16)), _ptr(x), i64(k), i64(n_out), i64(n_tok), int(n_threads), _ptr(out))
         if rc != 0:
             raise RuntimeError(f"reference harness failed (code {rc})")
         return out

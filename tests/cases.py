@@ -107,6 +107,26 @@ ROPE_CASES = {
 }
 
 
+# Q/K/V projection of a decode step (src/minicpm.cpp:644-689): tokens at the listed positions, hidden 1024 -> 16 Q, 2 K, 2 V
+# heads of 64, f16 weights in ggml's layout [features][hidden], rotary embedding on q and k.
+QKV_CASE = dict(seed=40, hidden=1024, n_heads=16, n_kv_heads=2, positions=[0, 3, 100, 2047, 4095], freq_base=10000.0, attn_factor=1.0)
+
+
+def qkv_inputs(args=QKV_CASE, n_tok=None):
+    rng = np.random.default_rng(args["seed"])
+    pos = np.array(args["positions"], np.int32) if n_tok is None else rng.integers(0, 4096, n_tok).astype(np.int32)
+    n_out = (args["n_heads"] + 2 * args["n_kv_heads"]) * D
+    w = (rng.standard_normal((n_out, args["hidden"])) / np.sqrt(args["hidden"])).astype(np.float16)
+    x = rng.standard_normal((len(pos), args["hidden"])).astype(np.float32)
+    return x, w, pos
+
+
+def split_qkv(y, args=QKV_CASE):
+    """[n_tok, (H + 2 HK) * 64] -> q [n_tok, H, 64], k, v [n_tok, HK, 64] (the views attention_forward takes of qkv)."""
+    n, H, HK = y.shape[0], args["n_heads"], args["n_kv_heads"]
+    return (y[:, :H * D].reshape(n, H, D), y[:, H * D:(H + HK) * D].reshape(n, HK, D), y[:, (H + HK) * D:].reshape(n, HK, D))
+
+
 def rope_inputs(args):
     rng = np.random.default_rng(args["seed"])
     pos = np.array(args["positions"], np.int32)

@@ -26,7 +26,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(HERE))
 
 from oracle import voxoracle as vo  # noqa: E402
-from cases import CASES, KV_TYPE, ROPE_CASES, digest, make_inputs, pick_rows, rope_inputs  # noqa: E402
+from cases import CASES, KV_TYPE, QKV_CASE, ROPE_CASES, digest, make_inputs, pick_rows, qkv_inputs, rope_inputs, split_qkv  # noqa: E402
 
 
 def main():
@@ -57,6 +57,13 @@ def main():
         out[name + "/out"] = ref.rope(x, pos, freq_base=args["freq_base"], attn_factor=args["attn_factor"], freq_factors=ff,
                                       n_ctx_orig=args["n_ctx_orig"])
         print(f"{name:32s} rope of {x.shape}")
+    # the projection in front of attention (src/minicpm.cpp:660-689): ggml_mul_mat with f16 weights, then ggml_rope_ext on q and k
+    x, w, pos = qkv_inputs()
+    q, k, v = split_qkv(ref.mul_mat_f16(x, w))
+    out["qkv/q"] = ref.rope(q, pos, freq_base=QKV_CASE["freq_base"], attn_factor=QKV_CASE["attn_factor"])
+    out["qkv/k"] = ref.rope(k, pos, freq_base=QKV_CASE["freq_base"], attn_factor=QKV_CASE["attn_factor"])
+    out["qkv/v"] = v
+    print(f"{'qkv':32s} projection of {x.shape} by {w.shape}")
     path = os.path.join(HERE, "attn_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {os.path.getsize(path) / 1024:.0f} KiB")

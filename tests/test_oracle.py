@@ -3,7 +3,7 @@ reference's own ggml CPU backend, and against that backend itself where it is pr
 import numpy as np
 import pytest
 
-from cases import CASES, KV_TYPE, ROPE_CASES, digest, make_inputs, pick_rows, rel_err, rope_inputs
+from cases import CASES, KV_TYPE, QKV_CASE, ROPE_CASES, digest, make_inputs, pick_rows, qkv_inputs, rel_err, rope_inputs, split_qkv
 
 # tolerance of the restatement against the reference's accurate path (both f32; they differ by
 # summation order and libm vs vectorised expf only)
@@ -55,6 +55,18 @@ def test_rope_restatement_matches_the_reference_fixture(name, oracle, golden):
     assert np.allclose(np.linalg.norm(got, axis=-1), np.linalg.norm(x, axis=-1) * args["attn_factor"], rtol=1e-5)
     # position 0 is the identity (times the factor)
     assert np.allclose(got[0], x[0] * np.float32(args["attn_factor"]), rtol=1e-6, atol=1e-7)
+
+
+def test_projection_restatement_matches_the_reference_fixture(oracle, golden):
+    """ggml_mul_mat with f16 weights + ggml_rope_ext on q and k, as attention_forward issues them (src/minicpm.cpp:660-689):
+    the restatement (activations rounded to f16, f32 accumulation; rotation from the cos/sin table) against the
+    reference's output.  They differ by the order of the f32 sums only."""
+    x, w, pos = qkv_inputs()
+    q, k, v = split_qkv(oracle.mul_mat_f16(x, w))
+    table = oracle.rope_table(pos, freq_base=QKV_CASE["freq_base"], attn_factor=QKV_CASE["attn_factor"])
+    assert rel_err(oracle.rope(q, table), golden["qkv/q"]) < GATE_TOL
+    assert rel_err(oracle.rope(k, table), golden["qkv/k"]) < GATE_TOL
+    assert rel_err(v, golden["qkv/v"]) < GATE_TOL
 
 
 def test_storage_formats_bit_exact(oracle, golden):

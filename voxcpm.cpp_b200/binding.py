@@ -77,6 +77,14 @@ class DecodeArgs(C.Structure):
                 ("rope_table", C.c_void_p), ("stream_order", C.c_void_p)]
 
 
+class QkvArgs(C.Structure):
+    _fields_ = [("n_streams", C.c_int32), ("hidden", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("x", C.c_void_p), ("x_nb_stream", C.c_size_t), ("w_qkv", C.c_void_p),
+                ("w_nb_row", C.c_size_t), ("w_type", C.c_int32), ("rope_table", C.c_void_p), ("q", C.c_void_p),
+                ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("cache", C.c_void_p), ("layer", C.c_int32), ("positions", C.c_void_p),
+                ("pos_offset", C.c_int32)]
+
+
 class RopeConfig(C.Structure):
     _fields_ = [("freq_base", C.c_float), ("attn_factor", C.c_float), ("freq_factors", C.c_void_p)]
 
@@ -95,7 +103,7 @@ class GroupConfig(C.Structure):
 
 
 class StepBuffers(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("lm_q", "lm_k_new", "lm_v_new", "lm_out", "dit_q", "dit_k", "dit_v", "dit_out")]
+    _fields_ = [(n, C.c_void_p) for n in ("lm_q", "lm_k_new", "lm_v_new", "lm_out", "dit_q", "dit_k", "dit_v", "dit_out", "lm_hidden")]
 
 
 def library_path() -> str:
@@ -134,6 +142,7 @@ def lib() -> C.CDLL:
         "vox_engine_selftest_wait": (i32, [vp, C.c_longlong, vp]),
         "vox_rope_table": (i32, [vp, C.POINTER(RopeConfig), vp, i32, i32, vp, vp]),
         "vox_group_set_rope": (i32, [vp, C.POINTER(RopeConfig), vp]),
+        "vox_group_set_qkv_weights": (i32, [vp, vp, i32, sz, sz]),
         "vox_group_set_bound": (i32, [vp, i32]),
         "vox_group_advance": (i32, [vp, i32]),
         "vox_attn_supported": (i32, [C.POINTER(AttnArgs)]),
@@ -151,6 +160,8 @@ def lib() -> C.CDLL:
         "vox_kv_export": (i32, [vp, i32, i32, i32, vp, vp]),
         "vox_kv_import": (i32, [vp, i32, i32, i32, vp, vp]),
         "vox_kv_copy_from": (i32, [vp, vp, vp]),
+        "vox_qkv_workspace_bytes": (sz, [i32, i32]),
+        "vox_qkv_project": (i32, [vp, C.POINTER(QkvArgs), vp, sz, vp]),
         "vox_attn_decode_workspace_bytes": (sz, [i32, i32, i32, i32]),
         "vox_attn_decode": (i32, [vp, C.POINTER(DecodeArgs), vp, sz, vp]),
         "vox_attn_decode_static": (i32, [vp, C.POINTER(DecodeArgs), vp]),
@@ -276,6 +287,27 @@ class Engine:
         ws = self.workspace(ws_bytes)
         _check(lib().vox_attn_prefill(self.h, C.byref(a), C.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(stream)))
         return dst
+
+    def qkv_project(self, x, w, n_heads, n_kv_heads, rope_table=None, cache=None, layer=0, positions=None, stream=None):
+        """``vox_qkv_project``: x [n_streams, hidden] f32, w [(H + 2 HK) * 64, hidden] f16 (ggml's layout).  Returns
+        q [n_streams, H, 64] and, without a cache, k_new / v_new [n_streams, HK, 64]; with one, the rows are stored
+        at ``positions`` and (q, None, None) comes back."""
+        import torch
+        S, hidden = x.shape
+        q = torch.empty((S, n_heads, 64), dtype=torch.float32, device=x.device)
+        k_new = v_new = None
+        a = QkvArgs(S, hidden, n_heads, n_kv_heads, 64, x.data_ptr(), x.stride(0) * 4, w.data_ptr(), w.stride(0) * 2, F16)
+        a.rope_table = rope_table.data_ptr() if rope_table is not None else None
+        a.q = q.data_ptr()
+        if cache is None:
+            k_new = torch.empty((S, n_kv_heads, 64), dtype=torch.float32, device=x.device)
+            v_new = torch.empty((S, n_kv_heads, 64), dtype=torch.float32, device=x.device)
+            a.k_new, a.v_new = k_new.data_ptr(), v_new.data_ptr()
+        else:
+            a.cache, a.layer, a.positions = cache.h, layer, positions.data_ptr()
+        ws = self.workspace(lib().vox_qkv_workspace_bytes(S, hidden))
+        _check(lib().vox_qkv_project(self.h, C.byref(a), C.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(stream)))
+        return q, k_new, v_new
 
     def supported(self, a: AttnArgs) -> bool:
         return bool(lib().vox_attn_supported(C.byref(a)))
@@ -442,6 +474,14 @@ class Group:
         ff = None if freq_factors is None else np.ascontiguousarray(freq_factors, np.float32)
         assert ff is None or ff.shape == (32,)
         _check(lib().vox_group_set_rope(self.h, C.byref(cfg), None if ff is None else ff.ctypes.data_as(C.c_void_p)))
+
+    def set_qkv_weights(self, w):
+        """``vox_group_set_qkv_weights``: w [L, (H + 2 HK) * 64, hidden] f16 on the device (kept alive here), or None."""
+        self._qkv_w = w
+        if w is None:
+            _check(lib().vox_group_set_qkv_weights(self.h, None, 0, 0, 0))
+        else:
+            _check(lib().vox_group_set_qkv_weights(self.h, w.data_ptr(), w.shape[2], w.stride(1) * 2, w.stride(0) * 2))
 
     def set_kv_len(self, kv_len):
         import numpy as np

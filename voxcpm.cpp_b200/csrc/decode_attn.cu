@@ -523,6 +523,9 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                             const int row = 16 * warp + 8 * j + g;
                             // one accumulator per 32-value block; the hi rows start at minus the bias of the block
                             float     sc[2][4] = {{-q_bias[0], -q_bias[0], 0.f, 0.f}, {-q_bias[1], -q_bias[1], 0.f, 0.f}};
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_ABL_NOK)
+                            if (false)
+#endif
 #pragma unroll
                             for (int b = 0; b < 2; ++b) {
                                 const uint2 raw = lds64(kb + row * 64 + (((2 * b + (t >> 1)) ^ ((row >> 1) & 3)) << 4) + ((t & 1) << 3));
@@ -634,6 +637,9 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                         // ldmatrix.trans on 16-bit units keeps byte pairs together: a register holds
                         // V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1] of one 16-column chunk, i.e. the B
                         // fragments of an "even columns" tile (bytes 0,2) and an "odd columns" tile (bytes 1,3).
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_ABL_NOV)
+                        if (false)
+#endif
 #pragma unroll
                         for (int cp = 0; cp < 2; ++cp) {
                             uint32_t r0, r1, r2, r3;

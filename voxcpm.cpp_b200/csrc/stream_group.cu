@@ -37,6 +37,14 @@ struct vox_group {
     vox_rope_config  rope{};
     float *          rope_factors = nullptr;          // device copy of the 32 per-frequency factors
     float *          rope_table   = nullptr;          // [n_streams][32][2]
+    // Q/K/V projection inside the step (vox_group_set_qkv_weights): the caller's weights, and the group's own rows for
+    // one layer's q, k, v and the f16 copy of its activations
+    const uint8_t *  qkv_w = nullptr;
+    int              qkv_hidden = 0;
+    size_t           qkv_nb_row = 0, qkv_nb_layer = 0;
+    float *          proj_q = nullptr;                // [S][H][64], then [S][HK][64] x 2
+    void *           proj_ws = nullptr;
+    size_t           proj_ws_bytes = 0;
     // vox_group_step_host: device mirrors of the step buffers, two copy streams, events
     uint8_t *        dev_buf   = nullptr;
     size_t           dev_off[8] = {0};
@@ -125,6 +133,8 @@ void vox_group_destroy(vox_group * g) {
     if (g->kv_len_dev) cudaFree(g->kv_len_dev);
     if (g->rope_factors) cudaFree(g->rope_factors);
     if (g->rope_table) cudaFree(g->rope_table);
+    if (g->proj_q) cudaFree(g->proj_q);
+    if (g->proj_ws) cudaFree(g->proj_ws);
     if (g->dev_buf) cudaFree(g->dev_buf);
     if (g->st_compute) cudaStreamDestroy(g->st_compute);
     if (g->st_copy) cudaStreamDestroy(g->st_copy);
@@ -208,6 +218,35 @@ int vox_group_set_rope(vox_group * g, const vox_rope_config * cfg, const float *
     return VOX_ATTN_OK;
 }
 
+int vox_group_set_qkv_weights(vox_group * g, const void * w, int hidden, size_t nb_row, size_t nb_layer) {
+    VOX_REQUIRE(g != nullptr, VOX_ATTN_INVALID_ARGUMENT, "null group");
+    if (w == nullptr) {
+        g->qkv_w = nullptr;
+        return VOX_ATTN_OK;
+    }
+    const vox_group_config & c = g->cfg;
+    VOX_REQUIRE(hidden > 0 && hidden % 64 == 0, VOX_ATTN_UNSUPPORTED, "hidden size %d is not a multiple of 64", hidden);
+    VOX_REQUIRE((reinterpret_cast<uintptr_t>(w) & 15) == 0 && nb_row % 16 == 0 && nb_row >= (size_t) hidden * 2 && nb_layer % 16 == 0,
+                VOX_ATTN_INVALID_ARGUMENT, "weight rows must be 16-byte aligned and at least hidden halves apart");
+    VOX_CUDA_TRY(cudaSetDevice(g->e->device));
+    if (!g->proj_q) {
+        const size_t rows = (size_t) c.n_streams * (c.n_heads + 2 * (size_t) c.n_kv_heads) * c.head_dim * sizeof(float);
+        cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&g->proj_q), rows);
+        if (err != cudaSuccess) { cudaGetLastError(); set_error("projection rows allocation of %zu bytes failed", rows); return VOX_ATTN_OUT_OF_MEMORY; }
+    }
+    const size_t ws = vox_qkv_workspace_bytes(c.n_streams, hidden);
+    if (ws > g->proj_ws_bytes) {
+        if (g->proj_ws) cudaFree(g->proj_ws);
+        g->proj_ws = nullptr; g->proj_ws_bytes = 0;
+        cudaError_t err = cudaMalloc(&g->proj_ws, ws);
+        if (err != cudaSuccess) { cudaGetLastError(); set_error("projection workspace allocation of %zu bytes failed", ws); return VOX_ATTN_OUT_OF_MEMORY; }
+        g->proj_ws_bytes = ws;
+    }
+    g->qkv_w = static_cast<const uint8_t *>(w);
+    g->qkv_hidden = hidden; g->qkv_nb_row = nb_row; g->qkv_nb_layer = nb_layer;
+    return VOX_ATTN_OK;
+}
+
 size_t vox_group_step_bytes(const vox_group * g, int which) { return g ? step_bytes(g->cfg, which) : 0; }
 
 int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void * stream) {
@@ -217,9 +256,15 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
     const size_t S = c.n_streams, D = c.head_dim;
     const float  scale = 1.0f / sqrtf((float) c.head_dim);  // src/minicpm.cpp:708-710
     // a null lm_q skips the LM stacks, a null dit_q skips the LocDiT patch (partial steps for profiling)
-    const int    L = b->lm_q ? c.base_layers + c.res_layers : 0;
+    const bool   project = b->lm_hidden != nullptr;  // the step starts from hidden states: projection + attention per layer
+    if (project) {
+        VOX_REQUIRE(g->qkv_w != nullptr, VOX_ATTN_INVALID_ARGUMENT, "lm_hidden needs vox_group_set_qkv_weights first");
+        VOX_REQUIRE(!b->lm_q && !b->lm_k_new && !b->lm_v_new, VOX_ATTN_INVALID_ARGUMENT, "give lm_hidden or lm_q / lm_k_new / lm_v_new, not both");
+        VOX_REQUIRE(advance, VOX_ATTN_INVALID_ARGUMENT, "a step from hidden states produces the new K/V rows: it advances");
+    }
+    const int    L = (b->lm_q || project) ? c.base_layers + c.res_layers : 0;
     VOX_REQUIRE(L > 0 || !advance, VOX_ATTN_INVALID_ARGUMENT, "advance needs the LM step buffers");
-    if (L > 0) VOX_REQUIRE(b->lm_out && (!advance || (b->lm_k_new && b->lm_v_new)), VOX_ATTN_INVALID_ARGUMENT, "LM step buffers are null");
+    if (L > 0) VOX_REQUIRE(b->lm_out && (!advance || project || (b->lm_k_new && b->lm_v_new)), VOX_ATTN_INVALID_ARGUMENT, "LM step buffers are null");
     if (advance) {
         VOX_REQUIRE(g->kv_bound + 1 <= c.max_len, VOX_ATTN_INVALID_ARGUMENT, "a stream would outgrow the cache capacity %d", c.max_len);
     }
@@ -255,14 +300,32 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         da.flags = l > 0 ? VOX_DECODE_CACHE_STABLE : 0u;
         da.rope_table = g->rope_on ? g->rope_table : nullptr;
         da.stream_order = nullptr;  // every CTA of a decode launch streams an equal share of the rows whatever the order
-        if (advance) {  // the token's K/V rows are stored by the decode launch itself (position kv_len-1)
+        if (advance && !project) {  // the token's K/V rows are stored by the decode launch itself (position kv_len-1)
             da.k_new = b->lm_k_new + (size_t) l * S * c.n_kv_heads * D;
             da.v_new = b->lm_v_new + (size_t) l * S * c.n_kv_heads * D;
             da.new_nb_head = D * 4; da.new_nb_stream = (size_t) c.n_kv_heads * D * 4;
         }
         da.cache = kc; da.layer = layer; da.n_streams = c.n_streams; da.n_heads = c.n_heads;
         da.kv_len = g->kv_len_dev; da.kv_bound = bound;
-        da.q = b->lm_q + (size_t) l * S * c.n_heads * D;
+        if (project) {
+            // this layer's Q and new K/V rows from the hidden states: one projection launch for all streams (rotated when
+            // the group applies the rotary embedding); the decode launch then stores the rows and attends
+            vox_qkv_args qa;
+            memset(&qa, 0, sizeof(qa));
+            qa.n_streams = c.n_streams; qa.hidden = g->qkv_hidden; qa.n_heads = c.n_heads; qa.n_kv_heads = c.n_kv_heads; qa.head_dim = c.head_dim;
+            qa.x = b->lm_hidden + (size_t) l * S * g->qkv_hidden; qa.x_nb_stream = (size_t) g->qkv_hidden * 4;
+            qa.w_qkv = g->qkv_w + (size_t) l * g->qkv_nb_layer; qa.w_nb_row = g->qkv_nb_row; qa.w_type = VOX_TYPE_F16;
+            qa.rope_table = g->rope_on ? g->rope_table : nullptr;
+            qa.q = g->proj_q;
+            qa.k_new = g->proj_q + S * c.n_heads * D;
+            qa.v_new = qa.k_new + S * c.n_kv_heads * D;
+            int rc = vox_qkv_project(g->e, &qa, g->proj_ws, g->proj_ws_bytes, stream);
+            if (rc != VOX_ATTN_OK) return rc;
+            da.k_new = qa.k_new; da.v_new = qa.v_new;
+            da.new_nb_head = D * 4; da.new_nb_stream = (size_t) c.n_kv_heads * D * 4;
+            da.rope_table = nullptr;  // applied by the projection
+        }
+        da.q = project ? g->proj_q : b->lm_q + (size_t) l * S * c.n_heads * D;
         da.q_nb_head = D * 4; da.q_nb_stream = (size_t) c.n_heads * D * 4;
         da.dst = b->lm_out + (size_t) l * S * c.n_heads * D;
         da.scale = scale;
