@@ -18,6 +18,11 @@
 // tcgen05.mma (kind::f16, M = 128, N = 64, four k-steps per block), the accumulator (64 columns of TMEM) is read
 // by four warps, one thread per token: that thread holds the token's whole head, so the rotary pairs (i, i + 32) and
 // the q8_0 block maxima are all inside one thread.
+// What bounds it: a CTA fills its shared memory at about 45 KB/us and a whole K range is 384 KB per CTA (two thirds of
+// it the activations, which every head's CTA of a token tile fetches again from the L2), so the 40 CTAs of a
+// 256-stream launch take about 10 us on 40 of the 148 SMs.  Tried: a ring of eight stages (no change: the ring is not
+// what it waits for); the K range split over four CTAs with their partial sums folded by the last to finish through
+// the workspace (160 CTAs: 21 us, the fold and a second wave cost more than the split saves).
 #include "kv_cache.cuh"
 #include "tcgen05.cuh"
 
