@@ -292,7 +292,7 @@ int vox_group_step(vox_group * g, const vox_step_buffers * b, int advance, void 
         const int      stack = l < c.base_layers ? 0 : 1;
         const int      layer = stack == 0 ? l : l - c.base_layers;
         vox_kv_cache * kc    = g->cache[stack];
-        vox_decode_args da;
+        vox_decode_args da = {};
         da.k_new = da.v_new = nullptr;
         da.new_nb_head = da.new_nb_stream = 0;
         // from the second layer on, the kernel before this one is the previous layer's decode: it wrote
@@ -384,7 +384,7 @@ int vox_group_step_host(vox_group * g, const vox_step_buffers * h, int advance) 
         }
     }
     uint8_t * d = g->dev_buf;
-    vox_step_buffers dev;
+    vox_step_buffers dev = {};
     dev.lm_q = (const float *) (d + g->dev_off[0]); dev.lm_k_new = (const float *) (d + g->dev_off[1]);
     dev.lm_v_new = (const float *) (d + g->dev_off[2]); dev.lm_out = (float *) (d + g->dev_off[3]);
     dev.dit_q = (const float *) (d + g->dev_off[4]); dev.dit_k = (const float *) (d + g->dev_off[5]);
