@@ -241,8 +241,9 @@ int    vox_qkv_project(vox_engine * e, const vox_qkv_args * a, void * workspace,
 
 /* ---------------------------------------------------------------- decode --------------- */
 
-/* One-token attention for n_streams independent streams in one launch (+ a merge launch when
- * the KV range is split).  Replaces the n_q==1 call made by MiniCPMModel::forward_step
+/* One-token attention for n_streams independent streams in ONE launch (the K/V rows of all
+ * streams are cut into equal runs, one per CTA; the CTA that finishes a stream's last run folds
+ * the partial results).  Replaces the n_q==1 call made by MiniCPMModel::forward_step
  * (src/minicpm.cpp:813-846) once per stream.
  *   q        [D, 1, H, n_streams] f32 (strides q_nb_head, q_nb_stream in bytes)
  *   kv_len   device array [n_streams]: rows of each stream that are visible (after append)
@@ -261,8 +262,9 @@ int    vox_qkv_project(vox_engine * e, const vox_qkv_args * a, void * workspace,
  *            and the launch rotates them (element i with element i + 32) as it reads them;
  *            v_new is stored as it is.  NULL: q and k_new are already rotated.
  *   stream_order  optional device array, a permutation of [0, n_streams): the order in which the
- *            launch takes the streams up.  Longest first lets a launch end on short streams
- *            instead of long ones (vox_group_* keeps such an order); results do not depend on it.
+ *            streams are laid end to end before the rows are cut into runs.  Every CTA gets an equal
+ *            share of the rows whatever the order, so it only decides which streams share a CTA;
+ *            the outputs agree to rounding of the f32 folds (NULL: 0, 1, 2, ...).
  *   flags    VOX_DECODE_CACHE_STABLE: a promise that neither kv_len nor any cache row this call reads
  *            was written by the kernel launched just before it on the same stream (q, k_new and
  *            v_new may have been).  True for the layers of a model, where a projection GEMM
@@ -297,12 +299,14 @@ int    vox_attn_decode(vox_engine * e, const vox_decode_args * a, void * workspa
  * pass: a real-time audio thread that must stay out of the allocator, a host that gave all device
  * memory to its own arena at start-up, a plugin that is handed nothing but its inputs and
  * outputs.  It has no counterpart in the reference.  Same arguments and results as
- * vox_attn_decode; the split-KV partials go to a 16 MiB array built into the library (each GPU
+ * vox_attn_decode; the split-KV partials go to a 4 MiB array built into the library (each GPU
  * that loads the library holds it until the process exits), and the call performs no allocation
- * of any kind.
- *   - A call whose partials would not fit (n_streams * n_heads * chunks * 264 bytes > 16 MiB;
- *     ask vox_attn_decode_workspace_bytes) returns VOX_ATTN_WORKSPACE_TOO_SMALL and launches
- *     nothing.
+ * of any kind.  The arguments are validated exactly as vox_attn_decode validates them, before
+ * anything is derived from them.
+ *   - A launch needs two partial slots per CTA of a grid that never exceeds one wave (2 x CTAs x
+ *     n_heads / n_kv_heads x 264 bytes: 2.4 MiB on a 148-SM device with 8 heads per kv head).  A
+ *     call whose plan needs more than 4 MiB (ask vox_attn_decode_workspace_bytes) returns
+ *     VOX_ATTN_WORKSPACE_TOO_SMALL and launches nothing.
  *   - The engine's device must be the current device.  The first call on a device looks up the
  *     array's device address; make that first call outside any stream capture.
  *   - All calls on a device share the one array.  Nothing in it needs clearing between calls, but

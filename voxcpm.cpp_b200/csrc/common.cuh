@@ -64,6 +64,8 @@ struct vox_engine {
     int *             counters_dev = nullptr;  // kCounterSlots zeroed ints: split-KV arrival tickets
     uint32_t          attr_mask    = 0;      // kernels whose shared-memory attribute was set on this device
     // developer settings, read from the environment once, when the engine is created
+    int               decode_early_tiles = -1;  // VOX_DECODE_EARLY: tiles a decode CTA requests before its dependency wait (-1: a full ring)
+    int               decode_q_first     = 0;   // VOX_DECODE_Q_FIRST: hold the remaining copies back until Q is loaded
     int               decode_wave[2] = {0, 0};  // VOX_DECODE_WAVE / VOX_DECODE_WAVE_Q8: CTAs per SM of a decode grid (0: all that fit)
     int               prefill_single_f16 = 0;   // VOX_PREFILL_WEIGHTS=f16: softmax weights as one f16 (comparison only)
     std::vector<vox_kv_cache *> caches;         // caches created from this engine (their ticket counters are reset after a failure)
@@ -211,8 +213,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t & r0, 
                  : "r"(addr));
 }
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+#ifndef VOX_MMA_ASM
+#define VOX_MMA_ASM asm volatile
+#endif
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
+    VOX_MMA_ASM(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));

@@ -40,20 +40,24 @@ namespace {
 
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads       = (kConsumerWarps + 1) * 32;
+#ifndef VOX_Q_PREFETCH  // developer builds may switch the prefetch of the next pair's Q rows off per cache type
+#define VOX_Q_PREFETCH(q8) true
+#endif
 constexpr int kPartialStride = 66;  // max, sum, acc[64]
 constexpr int kMaxGqa        = 8;   // query heads per kv head (rows 0-7 of the A operand)
 
 // Developer build (-DVOX_ATTN_DEVELOPER): every CTA notes the time (globaltimer, ns) at which it passes a few points
-// of its life; vox_debug_decode_trace copies the notes out.  Compiled out of the product library.
+// of its life, launches of even and odd layers apart (two consecutive launches are then on record together);
+// vox_debug_decode_trace copies the notes out.  Compiled out of the product library.
 #ifdef VOX_ATTN_DEVELOPER
 constexpr int kTraceCtas = 1024, kTracePoints = 8;
-__device__ unsigned long long g_decode_trace[kTraceCtas][kTracePoints];
+__device__ unsigned long long g_decode_trace[2][kTraceCtas][kTracePoints];
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-#define DECODE_TRACE(point) do { if (blockIdx.x < kTraceCtas) g_decode_trace[blockIdx.x][point] = global_ns(); } while (0)
+#define DECODE_TRACE(point) do { if (blockIdx.x < kTraceCtas) g_decode_trace[p.layer & 1][blockIdx.x][point] = global_ns(); } while (0)
 #else
 #define DECODE_TRACE(point)
 #endif
@@ -84,6 +88,8 @@ struct DecodeParams {
     // it on the stream (only Q and the arriving row were), so the first tiles are requested before the
     // programmatic-dependency wait, while that kernel is still draining.
     int             early;
+    int             early_tiles;  // tiles of a run requested before the dependency wait (at most the ring's depth)
+    int             q_first;      // non-zero: after the wait the producer holds its copies back until the consumer warps have their Q rows
     // Non-null: [stream][32] (cos, sin) pairs; Q and the arriving K row are rotated as they are read
     // (element i with element i + 32: the reference's ggml_rope_ext, GGML_ROPE_TYPE_NEOX).
     const float2 *  rope;
@@ -121,17 +127,61 @@ __device__ __forceinline__ void walk_next_pair(const DecodeParams & p, Walk & w)
 }
 
 // The cut of the work list, computed by every warp for itself (32 lanes, each summing a block of the
-// streams; the lengths stay in L1 for the other warps of the CTA).  Returns the number of tiles in the
-// list; `run` = tiles per CTA; `w` = where tile f0 = blockIdx.x * run lies (valid when f0 < total).
-__device__ __forceinline__ int cut_work_list(const DecodeParams & p, int lane, int & run, int & f0, Walk & w, bool & any_empty) {
+// streams; the lengths stay in L1 for the other warps of the CTA).
+//
+// Flat cut: the tiles of all pairs laid end to end, `run` tiles per CTA, CTA b from tile f0 = b * run on.  A run may
+// start in the middle of one pair and end in the middle of another.
+//
+// Aligned cut, taken for launches whose runs are short: a CTA that crosses from one pair into the next loads Q
+// twice, merges its warps twice and usually folds two pairs, one after the other, at the very end of the launch,
+// which costs more than one extra tile.  So when every pair can be split into parts of at most r tiles for some r
+// up to a quarter above the flat run, with no more parts than the grid has CTAs, each pair is split on its own into
+// ceil(tiles / r) nearly equal parts and a CTA works on one part of one pair.
+//
+// Returns the number of tiles of this CTA (0: nothing to do) and where they start (w).  For the bookkeeping of cut
+// pairs: flat cut -> aligned = false, run, f0; aligned cut -> aligned = true and part b0 .. b1 = the CTAs of this
+// CTA's pair.
+constexpr int kAlignedMaxRun = 16;
+struct Cut {
+    int  n_tiles, run, f0, b0, b1;
+    bool aligned, any_empty;
+};
+// ceil(x / r) for 0 <= x, 1 <= r, x < 2^20, without an integer division: (x + r - 0.5) / r lies at least 0.5 / r away
+// from an integer, far more than the error of the approximate quotient
+__device__ __forceinline__ int ceil_div_small(int x, int r) { return __float2int_rd(__fdividef((float) (x + r) - 0.5f, (float) r)); }
+
+__device__ __forceinline__ Cut cut_work_list(const DecodeParams & p, int lane, Walk & w) {
+    constexpr int kKeep = 8;  // a lane keeps the tile counts of its streams in registers up to 8 (256 streams)
     const int n = p.n_streams, per = (n + 31) >> 5;
     const int lo = min(n, lane * per), hi = min(n, lo + per);
+    const int HK = p.n_kv_heads, grid = (int) gridDim.x, b = (int) blockIdx.x;
+    auto load_tiles = [&](int i) {
+        const int s = p.order ? p.order[i] : i;
+        return tiles_of(clamp_len(p, p.kv_len ? p.kv_len[s] : p.kv_len_const));
+    };
+    int kept[kKeep];
+#pragma unroll
+    for (int k = 0; k < kKeep; ++k) kept[k] = lo + k < hi ? load_tiles(lo + k) : 0;
+    auto tiles_at = [&](int i) {  // i in [lo, hi)
+        int v = 0;
+        if (i - lo < kKeep) {
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) v = i - lo == k ? kept[k] : v;
+        } else {
+            v = load_tiles(i);
+        }
+        return v;
+    };
+    Cut  c;
     int  sum   = 0;
     bool empty = false;
-#pragma unroll 4
-    for (int i = lo; i < hi; ++i) {
-        const int s  = p.order ? p.order[i] : i;
-        const int tl = tiles_of(clamp_len(p, p.kv_len ? p.kv_len[s] : p.kv_len_const));
+#pragma unroll
+    for (int k = 0; k < kKeep; ++k) {
+        sum += kept[k];
+        empty |= lo + k < hi && kept[k] == 0;
+    }
+    for (int i = lo + kKeep; i < hi; ++i) {
+        const int tl = load_tiles(i);
         sum += tl;
         empty |= tl == 0;
     }
@@ -141,23 +191,73 @@ __device__ __forceinline__ int cut_work_list(const DecodeParams & p, int lane, i
         const int y = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += y;
     }
-    const int HK    = p.n_kv_heads;
     const int total = __shfl_sync(0xffffffffu, incl, 31) * HK;
-    any_empty       = __any_sync(0xffffffffu, empty);
-    run             = max(p.run_min, (total + (int) gridDim.x - 1) / (int) gridDim.x);
-    f0              = (int) blockIdx.x * run;
+    c.any_empty     = __any_sync(0xffffffffu, empty);
+    c.run           = max(p.run_min, (total + grid - 1) / grid);
+    c.f0            = b * c.run;
+    c.aligned       = false;
+    c.b0 = c.b1 = b;
+    c.n_tiles       = 0;
     w.i = w.kvh = w.t = 0;
-    if (f0 >= total) return total;
+
+    if (c.run <= kAlignedMaxRun && total < (1 << 20)) {
+        const int r_max = c.run + max(1, c.run >> 2);
+        for (int r = c.run; r <= r_max && !c.aligned; ++r) {
+            int parts = 0;
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) parts += ceil_div_small(kept[k], r);
+            for (int i = lo + kKeep; i < hi; ++i) parts += ceil_div_small(load_tiles(i), r);
+            int pincl = parts;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(0xffffffffu, pincl, o);
+                if (lane >= o) pincl += y;
+            }
+            const int all = __shfl_sync(0xffffffffu, pincl, 31) * HK;
+            if (all > grid) continue;
+            c.aligned = true;
+            if (b >= all) return c;  // more CTAs than parts
+            const int      pexcl = pincl - parts;
+            const unsigned owner = __ballot_sync(0xffffffffu, b >= pexcl * HK && b < pincl * HK);
+            const int      src   = __ffs(owner) - 1;
+            int start = 0, count = 0, b0 = 0, b1 = 0;
+            if (lane == src) {
+                int acc = pexcl * HK;
+                for (int i = lo; i < hi; ++i) {
+                    const int tl = tiles_at(i), np = ceil_div_small(tl, r);
+                    if (b < acc + np * HK) {
+                        const int rem = b - acc, kvh = rem / np, j = rem - kvh * np;
+                        w.i = i; w.kvh = kvh;
+                        start = (j * tl) / np;
+                        count = ((j + 1) * tl) / np - start;
+                        b0 = b - j; b1 = b0 + np - 1;
+                        break;
+                    }
+                    acc += np * HK;
+                }
+            }
+            w.i       = __shfl_sync(0xffffffffu, w.i, src);
+            w.kvh     = __shfl_sync(0xffffffffu, w.kvh, src);
+            w.t       = __shfl_sync(0xffffffffu, start, src);
+            c.n_tiles = __shfl_sync(0xffffffffu, count, src);
+            c.b0      = __shfl_sync(0xffffffffu, b0, src);
+            c.b1      = __shfl_sync(0xffffffffu, b1, src);
+            walk_load(p, w);
+            return c;
+        }
+    }
+
+    if (c.f0 >= total) return c;
+    c.n_tiles = min(total, c.f0 + c.run) - c.f0;
     const int      excl  = incl - sum;
-    const unsigned owner = __ballot_sync(0xffffffffu, f0 >= excl * HK && f0 < incl * HK);
+    const unsigned owner = __ballot_sync(0xffffffffu, c.f0 >= excl * HK && c.f0 < incl * HK);
     const int      src   = __ffs(owner) - 1;
     if (lane == src) {
         int acc = excl;
         for (int i = lo; i < hi; ++i) {
-            const int s  = p.order ? p.order[i] : i;
-            const int tl = tiles_of(clamp_len(p, p.kv_len ? p.kv_len[s] : p.kv_len_const));
-            if (f0 < (acc + tl) * HK) {
-                const int rem = f0 - acc * HK;
+            const int tl = tiles_at(i);
+            if (c.f0 < (acc + tl) * HK) {
+                const int rem = c.f0 - acc * HK;
                 w.i = i; w.kvh = rem / tl; w.t = rem % tl;
                 break;
             }
@@ -168,7 +268,7 @@ __device__ __forceinline__ int cut_work_list(const DecodeParams & p, int lane, i
     w.kvh = __shfl_sync(0xffffffffu, w.kvh, src);
     w.t   = __shfl_sync(0xffffffffu, w.t, src);
     walk_load(p, w);
-    return total;
+    return c;
 }
 
 // Shared-memory ring: per stage one 64-row K tile and one 64-row V tile.
@@ -204,6 +304,11 @@ __device__ __forceinline__ float half_hi(uint32_t x) { return __half2float(__ush
 // 32-value block, known when Q is loaded; V: the running sums of the weights).
 constexpr float kTwo24 = 16777216.0f, kTwoM24 = 1.0f / 16777216.0f;
 __device__ __forceinline__ uint32_t u8_pair_to_half2(uint32_t bytes, uint32_t selector) { return __byte_perm(bytes, 0u, selector); }
+// product of two packed pairs of halves, as bits
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2 *>(&a), *reinterpret_cast<const __half2 *>(&b));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
 
 // The row that arrives with this call, stored by the producer warp (lane l holds elements 2l, 2l+1 of K
 // and of V; converted exactly as kv_append_kernel converts them) before it requests the tile that
@@ -239,8 +344,14 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     constexpr int kStages = R::kStages;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * kStages];
+    __shared__ uint64_t q_bar;  // the consumer warps have loaded the Q rows of the run's first pair
     __shared__ int      abort_flag;
     __shared__ int      fold_flag;
+    // pairs this run holds a part of (at most two: one that began in an earlier run, one that goes on in a later
+    // one): stream, kv head, first and last run of the pair.  Their tickets are taken together when the run ends.
+    __shared__ int      pending[2][4];
+    __shared__ int      n_pending;
+    __shared__ int      cut_note[5];  // what thread 0 needs of the cut when it records a cut pair (kept out of the registers)
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -253,10 +364,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     if (tid == 0) {
         abort_flag = 0;
         fold_flag  = 0;
+        n_pending  = 0;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, kConsumerWarps);
         }
+        mbar_init(smem_u32(&q_bar), kConsumerWarps);
         fence_mbar_init();
     }
     if (tid == kConsumerWarps * 32) {
@@ -275,25 +388,35 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         pdl_wait();
         pdl_launch_dependents();
     }
-    int  run, f0;
-    Walk w;
-    bool any_empty;
-    const int total = cut_work_list(p, lane, run, f0, w, any_empty);
-    const int f1    = min(total, f0 + run);
-    if (tid == 0) DECODE_TRACE(1);
-    if (f0 >= total && blockIdx.x != 0) return;  // more CTAs than runs: nothing to do
+    Walk      w;
+    const Cut cut     = cut_work_list(p, lane, w);
+    const int  n_tiles   = cut.n_tiles;
+    const bool any_empty = cut.any_empty;
+    if (tid == 0) {
+        cut_note[0] = cut.aligned; cut_note[1] = cut.f0; cut_note[2] = cut.run; cut_note[3] = cut.b0; cut_note[4] = cut.b1;
+        DECODE_TRACE(1);
+    }
+    if (n_tiles == 0 && blockIdx.x != 0) return;  // more CTAs than runs: nothing to do
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer
         // All lanes walk the run (the arriving row is converted by the whole warp); lane 0 issues the copies.
         bool waited = !p.early;
         int  issued = 0;
-        for (int f = f0, it = 0; f < f1; ++f, ++it) {
+        for (int it = 0; it < n_tiles; ++it) {
             const bool append_here = p.k_new != nullptr && w.t == w.tiles - 1;  // the arriving row lies in the pair's last tile
-            if (!waited && (append_here || it >= kStages)) {  // the ring was filled while the previous kernel drained
+            if (!waited && (append_here || it >= p.early_tiles)) {  // the first tiles were requested while the previous kernel drained
                 pdl_wait();
                 pdl_launch_dependents();
                 waited = true;
+                // The previous kernel's last CTAs may still be folding their partials, and this launch's consumer warps
+                // now fetch their Q rows: both are short chains of dependent round trips to L2 that a burst of bulk
+                // copies from every CTA stretches several times over.  So the rest of the run is requested once Q is here.
+                if (p.q_first && lane == 0 && !mbar_wait_bounded(smem_u32(&q_bar), 0)) {
+                    atomicOr(p.status, kStatusTimeout);
+                    atomicExch(&abort_flag, 1);
+                }
+                __syncwarp();
             }
             if (append_here) {
                 const int raw = p.kv_len[w.stream];
@@ -348,7 +471,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             if (!good) break;
             if (lane == 0 && it == 0) DECODE_TRACE(6);
             issued = it + 1;
-            if (++w.t == w.tiles && f + 1 < f1) walk_next_pair(p, w);
+            if (++w.t == w.tiles && it + 1 < n_tiles) walk_next_pair(p, w);
         }
         if (!waited) {
             pdl_wait();
@@ -384,12 +507,22 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     const int k_row = 16 * warp + ((lane >> 4) << 3) + (lane & 7), k_chk = (lane >> 3) & 1;
     const int v_row = 16 * warp + (((lane >> 3) & 1) << 3) + (lane & 7), v_chk = lane >> 4;
 
+    // q8_0: byte offsets inside a stage that do not change from tile to tile.  Row 16*warp + 8j + g of the K bytes:
+    // 16-byte chunk (2b + t/2) ^ ((row / 2) % 4), where 8j drops out of the swizzle term and b only flips bit 1 of the
+    // chunk, so block 1 is the same offset with bit 5 flipped and j adds 512; likewise the two chunk pairs of V.
+    const uint32_t k_off = (16 * warp + g) * 64 + ((((t >> 1)) ^ ((g >> 1) & 3)) << 4) + ((t & 1) << 3);
+    const uint32_t v_off = v_row * 64 + ((v_chk ^ ((v_row >> 1) & 3)) << 4);
+    const uint32_t s_off = (16 * warp + 2 * t) * 4;  // scales of positions 8j + 2t, 8j + 2t + 1: + 32j
+
     bool ok = true;
-    int  it = 0;  // tiles of the run consumed so far: tile `it` sits in ring stage it % kStages
-    for (int f = f0; f < f1 && ok;) {
-        const int seg    = min(w.tiles - w.t, f1 - f);  // tiles of this pair inside the run
+    int  it = 0;                 // tiles of the run consumed so far
+    int  cstage = 0, cphase = 0; // ring stage and barrier phase of the next tile to consume
+    int  last_stage = 0;         // stage of the tile consumed last
+    while (it < n_tiles && ok) {
+        const int seg    = min(w.tiles - w.t, n_tiles - it);  // tiles of this pair inside the run
         if (seg <= 0) {  // the lengths moved under the launch: the cut no longer matches them
             if (tid == 0) atomicOr(p.status, kStatusBadState);
+            if (it == 0 && lane == 0) mbar_arrive(smem_u32(&q_bar));
             break;
         }
         const int stream = w.stream, kvh = w.kvh, c1 = w.len;
@@ -455,11 +588,28 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 }
             }
         }
+        if (it == 0) {  // the values are in registers (they were used above): the producer may go on
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&q_bar));
+        }
+        if (VOX_Q_PREFETCH(Q8) && warp == 0 && it + seg < n_tiles) {
+            // the run goes on into another pair: its Q rows are asked for now, so that the loads at the top of that
+            // pair's part find them on the SM instead of paying a round trip to L2 between two tiles
+            Walk nx = w;
+            nx.t    = w.tiles;
+            walk_next_pair(p, nx);
+            if (lane < 2 * p.gqa) {
+                const uint8_t * row = p.q + (size_t) nx.stream * p.q_nb_stream + (size_t) (nx.kvh * p.gqa + (lane >> 1)) * p.q_nb_head + (lane & 1) * 128;
+                asm volatile("prefetch.global.L1 [%0];" ::"l"(row));
+            }
+        }
         float o[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
         float m = -INFINITY, l = 0.0f;
-        float v_bias[2] = {0.0f, 0.0f};  // q8_0: this lane's share of the sums of the V-scaled weights, per 32-column block
+        // q8_0: sums of the V-scaled weights (accumulator tile of the product with ones: [0] = [1] = head g with the
+        // scales of block 0, [2] = [3] = with those of block 1)
+        float v_bias[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
         // Tiles per pass of a consumer warp: one.  Two (both cache types were tried: two independent tiles in one pass
         // give the scheduler something to overlap the dependency chains with) measured the same or slower: f16 50.6
@@ -478,10 +628,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 have[u] = i + u < seg;
-                st[u]   = (it + i + u) % kStages;
+                st[u]   = cstage + u < kStages ? cstage + u : cstage + u - kStages;
                 p0[u]   = (w.t + i + u) * kKvTile + 16 * warp;
                 act[u]  = have[u] && p0[u] < c1;
-                if (have[u] && !mbar_wait_bounded(full0 + 8 * st[u], ((it + i + u) / kStages) & 1)) {
+                if (have[u] && !mbar_wait_bounded(full0 + 8 * st[u], cstage + u < kStages ? cphase : cphase ^ 1)) {
                     atomicOr(p.status, kStatusTimeout);
                     atomicExch(&abort_flag, 1);
                     ok = false;
@@ -520,7 +670,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                         const uint32_t ksc = kb + 2 * R::kDataBytes;
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            const int row = 16 * warp + 8 * j + g;
                             // one accumulator per 32-value block; the hi rows start at minus the bias of the block
                             float     sc[2][4] = {{-q_bias[0], -q_bias[0], 0.f, 0.f}, {-q_bias[1], -q_bias[1], 0.f, 0.f}};
 #if defined(VOX_ATTN_DEVELOPER) && defined(VOX_ABL_NOK)
@@ -528,18 +677,29 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #endif
 #pragma unroll
                             for (int b = 0; b < 2; ++b) {
-                                const uint2 raw = lds64(kb + row * 64 + (((2 * b + (t >> 1)) ^ ((row >> 1) & 3)) << 4) + ((t & 1) << 3));
+                                const uint2 raw = lds64(kb + ((k_off ^ (b << 5)) + 512 * j));
                                 mma_16816(sc[b], qa[2 * b], u8_pair_to_half2(raw.x, 0x4140), u8_pair_to_half2(raw.x, 0x4342));
                                 mma_16816(sc[b], qa[2 * b + 1], u8_pair_to_half2(raw.y, 0x4140), u8_pair_to_half2(raw.y, 0x4342));
                             }
                             // scales of positions 8j+2t and 8j+2t+1, both blocks: four consecutive halves
-                            const uint2 ds = lds64(ksc + (16 * warp + 8 * j + 2 * t) * 4);
+                            const uint2 ds = lds64(ksc + s_off + 32 * j);
                             sv[u][j][0] = ((sc[0][0] + sc[0][2]) * half_lo(ds.x) + (sc[1][0] + sc[1][2]) * half_hi(ds.x)) * kTwo24;
                             sv[u][j][1] = ((sc[0][1] + sc[0][3]) * half_lo(ds.y) + (sc[1][1] + sc[1][3]) * half_hi(ds.y)) * kTwo24;
                         }
                     }
                 }
                 float tmax = -INFINITY;
+                // only a pair's last tile can hold positions past its length, and masks are rare: every other tile
+                // takes the short way (the same for all lanes of the warp)
+                bool edge = p.mask != nullptr;
+#pragma unroll
+                for (int u = 0; u < U; ++u) edge |= !act[u] || p0[u] + 16 > c1;
+                if (!edge) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tmax = fmaxf(tmax, fmaxf(sv[u][j][0], sv[u][j][1]));
+                } else {
 #pragma unroll
                 for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -562,6 +722,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                             tmax        = fmaxf(tmax, sv[u][j][e]);
                         }
                     }
+                }
                 tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
                 tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
                 const float m_new = fmaxf(m, tmax);
@@ -583,7 +744,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                     for (int n = 0; n < 8; ++n) {
                         o[n][0] *= alpha; o[n][1] *= alpha; o[n][2] *= alpha; o[n][3] *= alpha;
                     }
-                    v_bias[0] *= alpha; v_bias[1] *= alpha;
+                    v_bias[0] *= alpha; v_bias[2] *= alpha;
                 }
                 if constexpr (!Q8) {
                     float psum = 0.0f;
@@ -616,24 +777,23 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                     for (int u = 0; u < U; ++u) {
                         if (!act[u]) continue;
                         const uint32_t kb = smem_base + st[u] * R::kStageBytes, vb = kb + R::kDataBytes;
-                        // V scales are folded into the weights: one A operand per 32-wide block of output columns
+                        // V scales are folded into the weights.  The two 32-column blocks of a row have different scales:
+                        // rows 0-7 of the A operand carry the weights times the scale of block 0, rows 8-15 times the scale
+                        // of block 1 (products in f16: twice 2^-11 relative, far inside the q8_0 tolerance), so one operand
+                        // serves both chunk pairs; of each accumulator tile the half that belongs to its block is kept.
                         const uint32_t vsc = kb + 2 * R::kDataBytes + kKvTile * 4;
-                        uint32_t       pa[2][4];
+                        uint32_t       pa[4];
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            const uint2 ds = lds64(vsc + (16 * warp + 8 * j + 2 * t) * 4);
-#pragma unroll
-                            for (int b = 0; b < 2; ++b) {
-                                // weights times V scale rounded to f16 once (2^-12 relative, far inside the q8_0
-                                // tolerance): the lo rows of the A operand stay zero.  Their sum is what the +128 of
-                                // the V bytes multiplies.
-                                const float w0 = pr[u][j][0] * (b ? half_hi(ds.x) : half_lo(ds.x));
-                                const float w1 = pr[u][j][1] * (b ? half_hi(ds.y) : half_lo(ds.y));
-                                pa[b][2 * j]     = pack_half2(w0, w1);
-                                pa[b][2 * j + 1] = 0u;
-                                v_bias[b] += w0 + w1;
-                            }
+                            const uint2    ds  = lds64(vsc + s_off + 32 * j);  // halves: (pos: b0, b1), (pos + 1: b0, b1)
+                            const uint32_t ph  = pack_half2(pr[u][j][0], pr[u][j][1]);
+                            const uint32_t sb0 = __byte_perm(ds.x, ds.y, 0x5410), sb1 = __byte_perm(ds.x, ds.y, 0x7632);
+                            pa[2 * j]     = hmul2_bits(ph, sb0);
+                            pa[2 * j + 1] = hmul2_bits(ph, sb1);
                         }
+                        // what the +128 of the V bytes multiplies: the sums of these very operands, from one more MMA
+                        // against a tile of ones (every column of its result is the row sum)
+                        mma_16816(v_bias, pa, 0x3c003c00u, 0x3c003c00u);
                         // ldmatrix.trans on 16-bit units keeps byte pairs together: a register holds
                         // V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1] of one 16-column chunk, i.e. the B
                         // fragments of an "even columns" tile (bytes 0,2) and an "odd columns" tile (bytes 1,3).
@@ -643,11 +803,11 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #pragma unroll
                         for (int cp = 0; cp < 2; ++cp) {
                             uint32_t r0, r1, r2, r3;
-                            ldmatrix_x4_trans(vb + v_row * 64 + (((2 * cp + v_chk) ^ ((v_row >> 1) & 3)) << 4), r0, r1, r2, r3);
-                            mma_16816(o[4 * cp + 0], pa[cp], u8_pair_to_half2(r0, 0x4240), u8_pair_to_half2(r1, 0x4240));
-                            mma_16816(o[4 * cp + 1], pa[cp], u8_pair_to_half2(r0, 0x4341), u8_pair_to_half2(r1, 0x4341));
-                            mma_16816(o[4 * cp + 2], pa[cp], u8_pair_to_half2(r2, 0x4240), u8_pair_to_half2(r3, 0x4240));
-                            mma_16816(o[4 * cp + 3], pa[cp], u8_pair_to_half2(r2, 0x4341), u8_pair_to_half2(r3, 0x4341));
+                            ldmatrix_x4_trans(vb + (v_off ^ (cp << 5)), r0, r1, r2, r3);
+                            mma_16816(o[4 * cp + 0], pa, u8_pair_to_half2(r0, 0x4240), u8_pair_to_half2(r1, 0x4240));
+                            mma_16816(o[4 * cp + 1], pa, u8_pair_to_half2(r0, 0x4341), u8_pair_to_half2(r1, 0x4341));
+                            mma_16816(o[4 * cp + 2], pa, u8_pair_to_half2(r2, 0x4240), u8_pair_to_half2(r3, 0x4240));
+                            mma_16816(o[4 * cp + 3], pa, u8_pair_to_half2(r2, 0x4341), u8_pair_to_half2(r3, 0x4341));
                         }
                     }
                 }
@@ -656,31 +816,33 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             // stages go back to the producer as soon as their tile is consumed, except the last one of the
             // pair's part: the warps are merged through it first
 #pragma unroll
-            for (int u = 0; u < U; ++u)
-                if (have[u] && i + u != seg - 1 && lane == 0) mbar_arrive(empty0 + 8 * st[u]);
+            for (int u = 0; u < U; ++u) {
+                if (!have[u]) continue;
+                if (i + u != seg - 1 && lane == 0) mbar_arrive(empty0 + 8 * st[u]);
+                last_stage = st[u];
+                if (++cstage == kStages) { cstage = 0; cphase ^= 1; }
+            }
         }
 
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         if constexpr (Q8) {
-            // the accumulators hold sum(w * (v + 128)) * 2^-24: back to sum(w * v)
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                v_bias[b] += __shfl_xor_sync(0xffffffffu, v_bias[b], 1);
-                v_bias[b] += __shfl_xor_sync(0xffffffffu, v_bias[b], 2);
-            }
+            // the accumulators hold sum(w * (v + 128)) * 2^-24: back to sum(w * v).  Block 0 (tiles 0-3) is in the rows
+            // of the first half of the operand, block 1 (tiles 4-7) in those of the second; the other half of a tile
+            // (the other block's scales on this block's bytes) is dropped.
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
-                o[n][0] = fmaf(o[n][0], kTwo24, -128.0f * v_bias[n >> 2]);
-                o[n][1] = fmaf(o[n][1], kTwo24, -128.0f * v_bias[n >> 2]);
+                const float b = -128.0f * v_bias[n < 4 ? 0 : 2];
+                o[n][0] = fmaf(n < 4 ? o[n][0] : o[n][2], kTwo24, b);
+                o[n][1] = fmaf(n < 4 ? o[n][1] : o[n][3], kTwo24, b);
+                o[n][2] = o[n][3] = 0.0f;
             }
         }
-        if (tid == 0 && f + seg >= f1) DECODE_TRACE(4);
+        if (tid == 0 && it + seg >= n_tiles) DECODE_TRACE(4);
 
         // ---- merge the four warps through the stage of the last tile (all of them are done with it after the barrier)
         named_bar_sync(1, kConsumerWarps * 32);
         if (!ok || *reinterpret_cast<volatile int *>(&abort_flag)) return;
-        const int last_stage = (it + seg - 1) % kStages;
         float *   scratch    = reinterpret_cast<float *>(smem_gen + last_stage * R::kStageBytes);
         {
             float * mine = scratch + (warp * 8 + g) * kPartialStride;
@@ -731,71 +893,86 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         // the stage is free once every thread has read the scratch; the generic-proxy accesses above are ordered
         // before the bulk copy that refills it
         fence_proxy_async_smem();
+        if (!whole && tid == 0 && n_pending < 2) {  // a cut pair: its ticket is taken when the run ends
+            const volatile int * cn = cut_note;
+            const int f_pair = cn[1] + it - w.t;  // flat cut: the pair's first tile in the list
+            int *     pd     = pending[n_pending];
+            pd[0] = stream; pd[1] = kvh;
+            pd[2] = cn[0] ? cn[3] : f_pair / cn[2];
+            pd[3] = cn[0] ? cn[4] : (f_pair + w.tiles - 1) / cn[2];
+            n_pending += 1;
+        }
         named_bar_sync(1, kConsumerWarps * 32);
         if (lane == 0) mbar_arrive(empty0 + 8 * last_stage);
 
-        if (!whole) {
-            // Second pass without a second launch: every run that holds a part of this pair takes a ticket after
-            // publishing its partials; the one that draws the last ticket folds them all and resets the counter.
-            // One fence by one thread after the barrier above: the barrier orders every thread's partial stores
-            // before it, and the fence is cumulative, so the ticket is taken only once they are visible device-wide.
-            const int f_pair = f - w.t;                           // the pair's first tile in the list
-            const int b0     = f_pair / run, b1 = (f_pair + w.tiles - 1) / run;
-            if (tid == 0) {
-                int * ctr = p.counters + stream * p.n_kv_heads + kvh;
-                __threadfence();
-                const int ticket = atomicAdd(ctr, 1);
-                const int last   = ticket == b1 - b0;
-                if (last) *ctr = 0;
-                fold_flag = last;
-            }
-            named_bar_sync(1, kConsumerWarps * 32);
-            const bool fold = *reinterpret_cast<volatile int *>(&fold_flag) != 0;
-            if (fold) {
-                __threadfence();
-                const int hh = tid >> 4, d0 = (tid & 15) * 4;
-                if (hh < p.gqa) {
-                    // One pass, four partials at a time: their loads are issued together (each is a round trip to L2,
-                    // and a pair may have been cut 17 ways), and the running maximum is raised as they come.
-                    const int head = kvh * p.gqa + hh;
-                    float     M = -INFINITY, L = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    for (int c = b0; c <= b1; c += 4) {
-                        float  mc[4], lc[4];
-                        float2 lo[4], hi[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int     cc = min(c + u, b1);
-                            const float * pc = p.partial + ((size_t) cc * 2 + (cc == b0 ? 1 : 0)) * p.gqa * kPartialStride + hh * kPartialStride;
-                            mc[u] = c + u <= b1 ? __ldcg(pc) : -INFINITY;
-                            lc[u] = __ldcg(pc + 1);
-                            lo[u] = __ldcg(reinterpret_cast<const float2 *>(pc + 2 + d0));
-                            hi[u] = __ldcg(reinterpret_cast<const float2 *>(pc + 4 + d0));
-                        }
-                        const float m4 = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
-                        const float Mn = fmaxf(M, m4);
-                        if (Mn == -INFINITY) continue;  // nothing visible so far
-                        const float fo = exp2f(M - Mn);  // M == -inf: 0
-                        L *= fo; acc[0] *= fo; acc[1] *= fo; acc[2] *= fo; acc[3] *= fo;
-                        M = Mn;
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const float fw = mc[u] == -INFINITY ? 0.0f : exp2f(mc[u] - M);
-                            L += lc[u] * fw;
-                            acc[0] += lo[u].x * fw; acc[1] += lo[u].y * fw; acc[2] += hi[u].x * fw; acc[3] += hi[u].y * fw;
-                        }
-                    }
-                    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-                    *reinterpret_cast<float4 *>(p.dst + ((size_t) stream * p.n_heads + head) * kHeadDim + d0) =
-                        make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
-                }
-            }
-            // fold_flag is rewritten by thread 0 only after the next pair's barriers, which every reader has passed
-        }
-
         it += seg;
-        f += seg;
         w.t += seg;
-        if (w.t == w.tiles && f < f1) walk_next_pair(p, w);
+        if (w.t == w.tiles && it < n_tiles) walk_next_pair(p, w);
+    }
+    const int n_cut = ok ? *reinterpret_cast<volatile int *>(&n_pending) : 0;  // written before the barrier that ends a merge
+    if (n_cut > 0) {
+        // Second pass without a second launch: every run that holds a part of a pair takes a ticket after publishing
+        // its partials; the one that draws the last ticket folds them all and resets the counter.  The tickets of a
+        // run's (at most two) cut pairs are taken together at its end, so a run that crosses from one pair into the
+        // next pays the round trips to L2 once.  One fence by one thread: the barrier that ends every merge orders
+        // all threads' partial stores before it, and the fence is cumulative, so a ticket is taken only once they are
+        // visible device-wide.
+        if (tid == 0) {
+            __threadfence();
+            int * c0 = p.counters + pending[0][0] * p.n_kv_heads + pending[0][1];
+            int * c1 = p.counters + pending[n_cut - 1][0] * p.n_kv_heads + pending[n_cut - 1][1];
+            const int t0 = atomicAdd(c0, 1);
+            const int t1 = n_cut > 1 ? atomicAdd(c1, 1) : -1;
+            int flags = 0;
+            if (t0 == pending[0][3] - pending[0][2]) { *c0 = 0; flags |= 1; }
+            if (n_cut > 1 && t1 == pending[1][3] - pending[1][2]) { *c1 = 0; flags |= 2; }
+            fold_flag = flags;
+        }
+        named_bar_sync(1, kConsumerWarps * 32);
+        const int flags = *reinterpret_cast<volatile int *>(&fold_flag);
+        if (flags != 0) {
+            __threadfence();
+            const int hh = tid >> 4, d0 = (tid & 15) * 4;  // 8 heads x 16 threads x 4 values
+            for (int k = 0; k < n_cut; ++k) {
+                if (!((flags >> k) & 1) || hh >= p.gqa) continue;
+                const int stream = pending[k][0], kvh = pending[k][1], b0 = pending[k][2], b1 = pending[k][3];
+                constexpr int kFoldWidth = Q8 ? 4 : 8;  // the q8_0 form has no registers to spare for eight
+                // One pass, kFoldWidth partials at a time: their loads are issued together (each is a round trip to L2,
+                // and a pair may have been cut 17 ways), and the running maximum is raised as they come.
+                const int head = kvh * p.gqa + hh;
+                float     M = -INFINITY, L = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int c = b0; c <= b1; c += kFoldWidth) {
+                    float  mc[kFoldWidth], lc[kFoldWidth];
+                    float2 lo[kFoldWidth], hi[kFoldWidth];
+#pragma unroll
+                    for (int u = 0; u < kFoldWidth; ++u) {
+                        const int     cc = min(c + u, b1);
+                        const float * pc = p.partial + ((size_t) cc * 2 + (cc == b0 ? 1 : 0)) * p.gqa * kPartialStride + hh * kPartialStride;
+                        mc[u] = c + u <= b1 ? __ldcg(pc) : -INFINITY;
+                        lc[u] = __ldcg(pc + 1);
+                        lo[u] = __ldcg(reinterpret_cast<const float2 *>(pc + 2 + d0));
+                        hi[u] = __ldcg(reinterpret_cast<const float2 *>(pc + 4 + d0));
+                    }
+                    float m8 = mc[0];
+#pragma unroll
+                    for (int u = 1; u < kFoldWidth; ++u) m8 = fmaxf(m8, mc[u]);
+                    const float Mn = fmaxf(M, m8);
+                    if (Mn == -INFINITY) continue;  // nothing visible so far
+                    const float fo = exp2f(M - Mn);  // M == -inf: 0
+                    L *= fo; acc[0] *= fo; acc[1] *= fo; acc[2] *= fo; acc[3] *= fo;
+                    M = Mn;
+#pragma unroll
+                    for (int u = 0; u < kFoldWidth; ++u) {
+                        const float fw = mc[u] == -INFINITY ? 0.0f : exp2f(mc[u] - M);
+                        L += lc[u] * fw;
+                        acc[0] += lo[u].x * fw; acc[1] += lo[u].y * fw; acc[2] += hi[u].x * fw; acc[3] += hi[u].y * fw;
+                    }
+                }
+                const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+                *reinterpret_cast<float4 *>(p.dst + ((size_t) stream * p.n_heads + head) * kHeadDim + d0) =
+                    make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+            }
+        }
     }
     if (tid == 0) DECODE_TRACE(5);
 }
@@ -873,6 +1050,16 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     p.status = e->status_dev;
     p.counters = counters;
     p.early = early ? 1 : 0;
+    {
+        const int depth = q8 ? Ring<true>::kStages : Ring<false>::kStages;
+        const int tuned = e->decode_early_tiles;
+        // Two tiles: enough to start on as soon as Q is here.  A full ring from every CTA of the next launch is a burst
+        // of bulk copies in which the last CTAs of this launch fold their partials, several times slower than in quiet
+        // (measured, 32 streams x 2048 / 4096 rows: 11.6 / 16.7 us per launch with a full ring, 11.2 / 16.2 us with two
+        // tiles, no difference on launches of 128 streams and more).
+        p.early_tiles   = tuned >= 0 ? std::min(tuned, depth) : 2;
+        p.q_first       = e->decode_q_first;
+    }
     p.rope  = reinterpret_cast<const float2 *>(rope_table);
     p.order = order;
     p.k_new = p.v_new = nullptr;
@@ -1087,7 +1274,7 @@ int decode_checked(vox_engine * e, const vox_decode_args * a, void * workspace, 
 // out: kTraceCtas x kTracePoints times in ns (0 entry, 1 work list cut, 2 consumers past the dependency wait, 3 first tile
 // in shared memory, 4 last tile consumed, 5 consumers done, 6 first copy issued, 7 producer done)
 extern "C" int vox_debug_decode_trace(unsigned long long * out) {
-    return cudaMemcpyFromSymbol(out, g_decode_trace, sizeof(unsigned long long) * kTraceCtas * kTracePoints) == cudaSuccess ? 0 : 4;
+    return cudaMemcpyFromSymbol(out, g_decode_trace, sizeof(unsigned long long) * 2 * kTraceCtas * kTracePoints) == cudaSuccess ? 0 : 4;
 }
 #endif
 
