@@ -40,9 +40,6 @@ namespace {
 
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads       = (kConsumerWarps + 1) * 32;
-#ifndef VOX_Q_PREFETCH  // developer builds may switch the prefetch of the next pair's Q rows off per cache type
-#define VOX_Q_PREFETCH(q8) true
-#endif
 constexpr int kPartialStride = 66;  // max, sum, acc[64]
 constexpr int kMaxGqa        = 8;   // query heads per kv head (rows 0-7 of the A operand)
 
@@ -134,14 +131,25 @@ __device__ __forceinline__ void walk_next_pair(const DecodeParams & p, Walk & w)
 //
 // Aligned cut, taken for launches whose runs are short: a CTA that crosses from one pair into the next loads Q
 // twice, merges its warps twice and usually folds two pairs, one after the other, at the very end of the launch,
-// which costs more than one extra tile.  So when every pair can be split into parts of at most r tiles for some r
-// up to a quarter above the flat run, with no more parts than the grid has CTAs, each pair is split on its own into
-// ceil(tiles / r) nearly equal parts and a CTA works on one part of one pair.
+// which costs about as much as three or four more tiles (measured: 32 streams x 2048 rows 14.9 -> 11.6 us per launch,
+// x 4096 rows 19.4 -> 16.7 us).  So when every pair can be split into parts of at most r tiles for some r up to a
+// quarter (and at most `slack` tiles) above the flat run, with no more parts than the grid has CTAs, each pair is split
+// on its own into ceil(tiles / r) nearly equal parts and a CTA works on one part of one pair.  Staging the next pair's
+// Q rows in shared memory ahead of time was tried for the flat cut and changed nothing: the cost is in the second
+// merge and in two folds one after the other, not in the load.
+//
+// What the flat cut leaves on the table: CTAs that are given equal shares do not finish together (per-CTA timelines of
+// a launch of 256 streams x 4096 rows: the last tile of a CTA anywhere between 59 and 82 us after the start, by SM
+// rather than by what the CTA reads; 28 to 41 us on the ragged serving launch).  Dealing out only four fifths of the
+// list as runs and leaving the rest as a pool of 4-tile chunks that CTAs take as they finish (an atomic counter, the
+// chunk announced to the consumer warps through the ring stage of its first tile) was built and measured: 20 % slower
+// (63 against 50 us on the serving launch).  Every chunk pays a Q load, a merge of the warps and a partial of its own,
+// and with the tickets of a CTA taken together at its end all folds of the launch land in its last microseconds.
 //
 // Returns the number of tiles of this CTA (0: nothing to do) and where they start (w).  For the bookkeeping of cut
 // pairs: flat cut -> aligned = false, run, f0; aligned cut -> aligned = true and part b0 .. b1 = the CTAs of this
 // CTA's pair.
-constexpr int kAlignedMaxRun = 16;
+constexpr int kAlignedMaxRun = 64;  // beyond this a second Q load, merge and fold are small against the run itself
 struct Cut {
     int  n_tiles, run, f0, b0, b1;
     bool aligned, any_empty;
@@ -150,7 +158,7 @@ struct Cut {
 // from an integer, far more than the error of the approximate quotient
 __device__ __forceinline__ int ceil_div_small(int x, int r) { return __float2int_rd(__fdividef((float) (x + r) - 0.5f, (float) r)); }
 
-__device__ __forceinline__ Cut cut_work_list(const DecodeParams & p, int lane, Walk & w) {
+__device__ __forceinline__ Cut cut_work_list(const DecodeParams & p, int lane, int slack, Walk & w) {
     constexpr int kKeep = 8;  // a lane keeps the tile counts of its streams in registers up to 8 (256 streams)
     const int n = p.n_streams, per = (n + 31) >> 5;
     const int lo = min(n, lane * per), hi = min(n, lo + per);
@@ -201,7 +209,8 @@ __device__ __forceinline__ Cut cut_work_list(const DecodeParams & p, int lane, W
     w.i = w.kvh = w.t = 0;
 
     if (c.run <= kAlignedMaxRun && total < (1 << 20)) {
-        const int r_max = c.run + max(1, c.run >> 2);
+        // crossing into a second pair costs a CTA about as much as `slack` tiles
+        const int r_max = c.run + max(1, min(slack, c.run >> 2));
         for (int r = c.run; r <= r_max && !c.aligned; ++r) {
             int parts = 0;
 #pragma unroll
@@ -389,7 +398,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         pdl_launch_dependents();
     }
     Walk      w;
-    const Cut cut     = cut_work_list(p, lane, w);
+    const Cut cut     = cut_work_list(p, lane, Q8 ? 3 : 4, w);
     const int  n_tiles   = cut.n_tiles;
     const bool any_empty = cut.any_empty;
     if (tid == 0) {
@@ -477,7 +486,13 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             pdl_wait();
             pdl_launch_dependents();
         }
-        if (lane == 0) DECODE_TRACE(7);
+#ifdef VOX_ATTN_DEVELOPER
+        if (lane == 0 && blockIdx.x < kTraceCtas) {  // which SM the CTA ran on
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            g_decode_trace[p.layer & 1][blockIdx.x][7] = smid + 1;
+        }
+#endif
         if (lane == 0 && *reinterpret_cast<volatile int *>(&abort_flag)) {
             // consumers gave up: let the copies already issued land before the CTA retires
             for (int i = max(0, issued - kStages); i < issued; ++i)
@@ -591,17 +606,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         if (it == 0) {  // the values are in registers (they were used above): the producer may go on
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&q_bar));
-        }
-        if (VOX_Q_PREFETCH(Q8) && warp == 0 && it + seg < n_tiles) {
-            // the run goes on into another pair: its Q rows are asked for now, so that the loads at the top of that
-            // pair's part find them on the SM instead of paying a round trip to L2 between two tiles
-            Walk nx = w;
-            nx.t    = w.tiles;
-            walk_next_pair(p, nx);
-            if (lane < 2 * p.gqa) {
-                const uint8_t * row = p.q + (size_t) nx.stream * p.q_nb_stream + (size_t) (nx.kvh * p.gqa + (lane >> 1)) * p.q_nb_head + (lane & 1) * 128;
-                asm volatile("prefetch.global.L1 [%0];" ::"l"(row));
-            }
         }
         float o[8][4];
 #pragma unroll
