@@ -86,7 +86,6 @@ struct DecodeParams {
     // programmatic-dependency wait, while that kernel is still draining.
     int             early;
     int             early_tiles;  // tiles of a run requested before the dependency wait (at most the ring's depth)
-    int             q_first;      // non-zero: after the wait the producer holds its copies back until the consumer warps have their Q rows
     // Non-null: [stream][32] (cos, sin) pairs; Q and the arriving K row are rotated as they are read
     // (element i with element i + 32: the reference's ggml_rope_ext, GGML_ROPE_TYPE_NEOX).
     const float2 *  rope;
@@ -345,6 +344,64 @@ __device__ __forceinline__ void store_arriving_row(float2 kk, float2 vv, uint8_t
     __syncwarp();
 }
 
+// The fold of NP pairs at once by one thread (head hh of each pair, output columns d0 .. d0+3): the partials of a pair
+// (runs b0 .. b1 of the launch; the run that holds the pair's first tile wrote its slot 1, the others their slot 0) are
+// read W at a time, the loads of a batch issued together (each is a round trip to L2, and a pair may have been cut 17
+// ways).  pend[k] = stream, kv head, b0, b1.
+template <int NP, int W>
+__device__ __forceinline__ void fold_pairs(const DecodeParams & p, const int (*pend)[4], int k0, int hh, int d0) {
+    int   b0[NP], b1[NP];
+    float M[NP], L[NP], acc[NP][4];
+    int   span = 0;
+#pragma unroll
+    for (int k = 0; k < NP; ++k) {
+        b0[k] = pend[k0 + k][2];
+        b1[k] = pend[k0 + k][3];
+        span  = max(span, b1[k] - b0[k] + 1);
+        M[k] = -INFINITY; L[k] = 0.0f;
+        acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.0f;
+    }
+    for (int c = 0; c < span; c += W) {
+        float  mc[NP][W], lc[NP][W];
+        float2 lo[NP][W], hi[NP][W];
+#pragma unroll
+        for (int k = 0; k < NP; ++k)
+#pragma unroll
+            for (int u = 0; u < W; ++u) {
+                const int     cc = min(b0[k] + c + u, b1[k]);
+                const float * pc = p.partial + ((size_t) cc * 2 + (cc == b0[k] ? 1 : 0)) * p.gqa * kPartialStride + hh * kPartialStride;
+                mc[k][u] = b0[k] + c + u <= b1[k] ? __ldcg(pc) : -INFINITY;
+                lc[k][u] = __ldcg(pc + 1);
+                lo[k][u] = __ldcg(reinterpret_cast<const float2 *>(pc + 2 + d0));
+                hi[k][u] = __ldcg(reinterpret_cast<const float2 *>(pc + 4 + d0));
+            }
+        // the running maximum is raised partial by partial, in list order: the arithmetic (and so every bit of the
+        // result) does not depend on W, i.e. not on whether this CTA happened to fold one pair or two
+#pragma unroll
+        for (int k = 0; k < NP; ++k)
+#pragma unroll
+            for (int u = 0; u < W; ++u) {
+                if (mc[k][u] == -INFINITY) continue;  // past the pair's last partial, or a partial that saw nothing
+                const float Mn = fmaxf(M[k], mc[k][u]);
+                const float fo = exp2f(M[k] - Mn);  // M == -inf: 0
+                const float fw = exp2f(mc[k][u] - Mn);
+                M[k]      = Mn;
+                L[k]      = L[k] * fo + lc[k][u] * fw;
+                acc[k][0] = acc[k][0] * fo + lo[k][u].x * fw;
+                acc[k][1] = acc[k][1] * fo + lo[k][u].y * fw;
+                acc[k][2] = acc[k][2] * fo + hi[k][u].x * fw;
+                acc[k][3] = acc[k][3] * fo + hi[k][u].y * fw;
+            }
+    }
+#pragma unroll
+    for (int k = 0; k < NP; ++k) {
+        const int   stream = pend[k0 + k][0], head = pend[k0 + k][1] * p.gqa + hh;
+        const float inv    = L[k] > 0.0f ? 1.0f / L[k] : 0.0f;
+        *reinterpret_cast<float4 *>(p.dst + ((size_t) stream * p.n_heads + head) * kHeadDim + d0) =
+            make_float4(acc[k][0] * inv, acc[k][1] * inv, acc[k][2] * inv, acc[k][3] * inv);
+    }
+}
+
 template <bool Q8>
 __global__ void __launch_bounds__(kThreads, Ring<Q8>::kCtasPerSm)
 decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -353,7 +410,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     constexpr int kStages = R::kStages;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * kStages];
-    __shared__ uint64_t q_bar;  // the consumer warps have loaded the Q rows of the run's first pair
     __shared__ int      abort_flag;
     __shared__ int      fold_flag;
     // pairs this run holds a part of (at most two: one that began in an earlier run, one that goes on in a later
@@ -378,7 +434,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, kConsumerWarps);
         }
-        mbar_init(smem_u32(&q_bar), kConsumerWarps);
         fence_mbar_init();
     }
     if (tid == kConsumerWarps * 32) {
@@ -418,14 +473,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 pdl_wait();
                 pdl_launch_dependents();
                 waited = true;
-                // The previous kernel's last CTAs may still be folding their partials, and this launch's consumer warps
-                // now fetch their Q rows: both are short chains of dependent round trips to L2 that a burst of bulk
-                // copies from every CTA stretches several times over.  So the rest of the run is requested once Q is here.
-                if (p.q_first && lane == 0 && !mbar_wait_bounded(smem_u32(&q_bar), 0)) {
-                    atomicOr(p.status, kStatusTimeout);
-                    atomicExch(&abort_flag, 1);
-                }
-                __syncwarp();
             }
             if (append_here) {
                 const int raw = p.kv_len[w.stream];
@@ -537,7 +584,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int seg    = min(w.tiles - w.t, n_tiles - it);  // tiles of this pair inside the run
         if (seg <= 0) {  // the lengths moved under the launch: the cut no longer matches them
             if (tid == 0) atomicOr(p.status, kStatusBadState);
-            if (it == 0 && lane == 0) mbar_arrive(smem_u32(&q_bar));
             break;
         }
         const int stream = w.stream, kvh = w.kvh, c1 = w.len;
@@ -602,10 +648,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                     q_bias[b] *= 128.0f * kTwoM24;
                 }
             }
-        }
-        if (it == 0) {  // the values are in registers (they were used above): the producer may go on
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&q_bar));
         }
         float o[8][4];
 #pragma unroll
@@ -937,44 +979,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         if (flags != 0) {
             __threadfence();
             const int hh = tid >> 4, d0 = (tid & 15) * 4;  // 8 heads x 16 threads x 4 values
-            for (int k = 0; k < n_cut; ++k) {
-                if (!((flags >> k) & 1) || hh >= p.gqa) continue;
-                const int stream = pending[k][0], kvh = pending[k][1], b0 = pending[k][2], b1 = pending[k][3];
-                constexpr int kFoldWidth = Q8 ? 4 : 8;  // the q8_0 form has no registers to spare for eight
-                // One pass, kFoldWidth partials at a time: their loads are issued together (each is a round trip to L2,
-                // and a pair may have been cut 17 ways), and the running maximum is raised as they come.
-                const int head = kvh * p.gqa + hh;
-                float     M = -INFINITY, L = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int c = b0; c <= b1; c += kFoldWidth) {
-                    float  mc[kFoldWidth], lc[kFoldWidth];
-                    float2 lo[kFoldWidth], hi[kFoldWidth];
-#pragma unroll
-                    for (int u = 0; u < kFoldWidth; ++u) {
-                        const int     cc = min(c + u, b1);
-                        const float * pc = p.partial + ((size_t) cc * 2 + (cc == b0 ? 1 : 0)) * p.gqa * kPartialStride + hh * kPartialStride;
-                        mc[u] = c + u <= b1 ? __ldcg(pc) : -INFINITY;
-                        lc[u] = __ldcg(pc + 1);
-                        lo[u] = __ldcg(reinterpret_cast<const float2 *>(pc + 2 + d0));
-                        hi[u] = __ldcg(reinterpret_cast<const float2 *>(pc + 4 + d0));
-                    }
-                    float m8 = mc[0];
-#pragma unroll
-                    for (int u = 1; u < kFoldWidth; ++u) m8 = fmaxf(m8, mc[u]);
-                    const float Mn = fmaxf(M, m8);
-                    if (Mn == -INFINITY) continue;  // nothing visible so far
-                    const float fo = exp2f(M - Mn);  // M == -inf: 0
-                    L *= fo; acc[0] *= fo; acc[1] *= fo; acc[2] *= fo; acc[3] *= fo;
-                    M = Mn;
-#pragma unroll
-                    for (int u = 0; u < kFoldWidth; ++u) {
-                        const float fw = mc[u] == -INFINITY ? 0.0f : exp2f(mc[u] - M);
-                        L += lc[u] * fw;
-                        acc[0] += lo[u].x * fw; acc[1] += lo[u].y * fw; acc[2] += hi[u].x * fw; acc[3] += hi[u].y * fw;
-                    }
-                }
-                const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-                *reinterpret_cast<float4 *>(p.dst + ((size_t) stream * p.n_heads + head) * kHeadDim + d0) =
-                    make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+            constexpr int kFoldWidth = Q8 ? 4 : 8;  // the q8_0 form has no registers to spare for eight
+            if (hh < p.gqa) {
+                // a CTA that drew the last ticket of both its cut pairs folds them side by side: the loads of both are
+                // in flight together, instead of one fold waiting for its round trips to L2 after the other
+                if (flags == 3) fold_pairs<2, kFoldWidth / 2>(p, pending, 0, hh, d0);
+                else            fold_pairs<1, kFoldWidth>(p, pending, flags == 2 ? 1 : 0, hh, d0);
             }
         }
     }
@@ -1062,7 +1072,6 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
         // (measured, 32 streams x 2048 / 4096 rows: 11.6 / 16.7 us per launch with a full ring, 11.2 / 16.2 us with two
         // tiles, no difference on launches of 128 streams and more).
         p.early_tiles   = tuned >= 0 ? std::min(tuned, depth) : 2;
-        p.q_first       = e->decode_q_first;
     }
     p.rope  = reinterpret_cast<const float2 *>(rope_table);
     p.order = order;

@@ -112,7 +112,6 @@ int vox_engine_create(int device, vox_engine ** out) {
         e->decode_wave[0] = env_int("VOX_DECODE_WAVE");
         e->decode_wave[1] = env_int("VOX_DECODE_WAVE_Q8");
         if (getenv("VOX_DECODE_EARLY") != nullptr) e->decode_early_tiles = env_int("VOX_DECODE_EARLY");
-        e->decode_q_first = env_int("VOX_DECODE_Q_FIRST");
         const char * w = getenv("VOX_PREFILL_WEIGHTS");
         e->prefill_single_f16 = (w && w[0] == 'f') ? 1 : 0;
     }
