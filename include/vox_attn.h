@@ -239,6 +239,44 @@ typedef struct {
 size_t vox_qkv_workspace_bytes(int n_streams, int hidden);
 int    vox_qkv_project(vox_engine * e, const vox_qkv_args * a, void * workspace, size_t workspace_bytes, void * stream);
 
+/* ---------------------------------------------------------------- linear layers of a step - */
+
+/* The other weight matrices of a decoder layer, for the single-token step of n_tokens streams in ONE launch each (plus a
+ * small one that rounds the activations to f16): the reference runs ggml_mul_mat per stream, reading every matrix once
+ * per stream and step.
+ *   VOX_LINEAR_PLAIN     out = W x                          ggml_mul_mat (e.g. o_proj, src/minicpm.cpp:715)
+ *   VOX_LINEAR_RESIDUAL  out = residual + scale * (W x)     + ggml_scale and ggml_add of layer_forward (:765-768, :773-776)
+ *   VOX_LINEAR_SWIGLU    out = silu(W_gate x) * (W_up x)    ggml_mul_mat(gate_up_proj) + ggml_swiglu_split (:718-746);
+ *                        w holds 2 * n_out rows, the gate rows first, as gate_up_proj stores them
+ * With norm_weight given, x is first normalised as MiniCPMModel::rms_norm does (:572-580: ggml_rms_norm with norm_eps,
+ * then ggml_mul with the weight).  Arithmetic as ggml's CPU backend (activations rounded to f16, exact products, f32
+ * sums), on tcgen05 tensor cores; the order of the f32 sums differs, so results agree to about 1e-6 of their RMS.
+ *   x     [k_dim, n_tokens] f32, x_nb_token bytes between tokens
+ *   w     [k_dim, rows] f16 in ggml's layout (a row per output feature, k_dim contiguous), w_nb_row bytes between rows
+ *   out   [n_out, n_tokens] f32, out_nb_token bytes between tokens; residual likewise (may be out itself)
+ * k_dim a multiple of 64; n_out a multiple of 64 (32 for SwiGLU).
+ * workspace: vox_linear_workspace_bytes (the f16 copy of x), 16-byte aligned.  Never allocates. */
+enum vox_linear_mode { VOX_LINEAR_PLAIN = 0, VOX_LINEAR_RESIDUAL = 1, VOX_LINEAR_SWIGLU = 2 };
+typedef struct {
+    int32_t       n_tokens, k_dim, n_out;
+    int32_t       mode;
+    const float * x;
+    size_t        x_nb_token;
+    const void *  w;
+    size_t        w_nb_row;
+    int32_t       w_type; /* VOX_TYPE_F16 */
+    float *       out;
+    size_t        out_nb_token;
+    const float * residual;
+    size_t        res_nb_token;
+    float         scale;
+    const float * norm_weight; /* [k_dim] f32 or NULL */
+    float         norm_eps;
+} vox_linear_args;
+
+size_t vox_linear_workspace_bytes(int n_tokens, int k_dim);
+int    vox_linear(vox_engine * e, const vox_linear_args * a, void * workspace, size_t workspace_bytes, void * stream);
+
 /* ---------------------------------------------------------------- decode --------------- */
 
 /* One-token attention for n_streams independent streams in ONE launch (the K/V rows of all

@@ -533,3 +533,26 @@ void voxo_mul_mat_f16(const float * x, const uint16_t * w, int64_t n_tok, int64_
         }
     }
 }
+
+/* MiniCPMModel::rms_norm (src/minicpm.cpp:572-580): ggml_rms_norm (ggml_compute_forward_rms_norm_f32,
+ * third_party/ggml/src/ggml-cpu/ops.cpp:3725-3755: the sum of squares in double, mean and scale in float, y = x * scale),
+ * then ggml_mul with the weight.   x, out [n_tok][k] f32, w [k] f32 */
+void voxo_rms_norm_mul(const float * x, const float * w, float eps, int64_t n_tok, int64_t k, float * out) {
+    for (int64_t t = 0; t < n_tok; ++t) {
+        double sum = 0.0;
+        for (int64_t i = 0; i < k; ++i) sum += (double) (x[t * k + i] * x[t * k + i]);
+        const float mean  = (float) (sum / (double) k);
+        const float scale = 1.0f / sqrtf(mean + eps);
+        for (int64_t i = 0; i < k; ++i) {
+            const float y = x[t * k + i] * scale;
+            out[t * k + i] = y * w[i];
+        }
+    }
+}
+
+/* ggml_swiglu_split(gate, up) as MiniCPMModel::mlp_forward issues it (src/minicpm.cpp:738-741): silu(gate) * up with
+ * silu(x) = x / (1 + expf(-x)) (ggml_silu_f32, third_party/ggml/src/ggml-cpu/vec.h:1061; ggml_vec_swiglu_f32,
+ * ggml-cpu/vec.cpp:433-469, whose SIMD paths use a polynomial expf that agrees to a few units in the last place). */
+void voxo_swiglu(const float * gate, const float * up, int64_t n, float * out) {
+    for (int64_t i = 0; i < n; ++i) out[i] = gate[i] / (1.0f + expf(-gate[i])) * up[i];
+}

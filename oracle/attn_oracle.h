@@ -92,5 +92,9 @@ void voxo_rope_neox(float * x, int64_t n_rows, int n_dims, const float * table, 
 /* ggml_mul_mat with f16 weights (ggml-cpu.c:217, vec.cpp:264): activations rounded to f16, f32 accumulation.
  *   x [n_tok][k] f32, w [n_out][k] f16 bits, out [n_tok][n_out] f32 */
 void voxo_mul_mat_f16(const float * x, const uint16_t * w, int64_t n_tok, int64_t k, int64_t n_out, float * out);
+/* MiniCPMModel::rms_norm (src/minicpm.cpp:572-580): ggml_rms_norm, then ggml_mul with the weight.  x, out [n_tok][k], w [k] */
+void voxo_rms_norm_mul(const float * x, const float * w, float eps, int64_t n_tok, int64_t k, float * out);
+/* ggml_swiglu_split(gate, up): silu(gate) * up, element by element */
+void voxo_swiglu(const float * gate, const float * up, int64_t n, float * out);
 
 #endif

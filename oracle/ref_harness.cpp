@@ -181,4 +181,58 @@ int voxref_mul_mat_f16(const uint16_t * w, const float * x, int64_t k, int64_t n
     return rc;
 }
 
+// MiniCPMModel::rms_norm (src/minicpm.cpp:572-580): ggml_rms_norm(x, eps), then ggml_mul with the weight.
+//   x, out [k, n_tok] f32, w [k] f32
+int voxref_rms_norm_mul(const float * x, const float * w, float eps, int64_t k, int64_t n_tok, int n_threads, float * out) {
+    ggml_init_params ip = {
+        /*.mem_size   =*/ ggml_tensor_overhead() * 8 + ggml_graph_overhead_custom(16, false) + 4096,
+        /*.mem_buffer =*/ nullptr,
+        /*.no_alloc   =*/ true,
+    };
+    ggml_context * ctx = ggml_init(ip);
+    if (!ctx) return 2;
+    ggml_tensor * tx = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, k, n_tok);
+    ggml_tensor * tw = ggml_new_tensor_1d(ctx, GGML_TYPE_F32, k);
+    tx->data = (void *) x;
+    tw->data = (void *) w;
+    std::vector<float> normed((size_t) k * n_tok);
+    ggml_tensor * tn = ggml_rms_norm(ctx, tx, eps);
+    tn->data = normed.data();
+    ggml_tensor * to = ggml_mul(ctx, tn, tw);
+    to->data = out;
+    ggml_cgraph * gf = ggml_new_graph_custom(ctx, 16, false);
+    ggml_build_forward_expand(gf, to);
+    ggml_cplan plan = ggml_graph_plan(gf, n_threads, nullptr);
+    std::vector<uint8_t> work(plan.work_size + 64);
+    plan.work_data = work.data();
+    const int rc = ggml_graph_compute(gf, &plan) == GGML_STATUS_SUCCESS ? 0 : 3;
+    ggml_free(ctx);
+    return rc;
+}
+
+// ggml_swiglu_split(gate, up) as MiniCPMModel::mlp_forward issues it (src/minicpm.cpp:738-741).  gate, up, out [n, n_tok] f32
+int voxref_swiglu(const float * gate, const float * up, int64_t n, int64_t n_tok, int n_threads, float * out) {
+    ggml_init_params ip = {
+        /*.mem_size   =*/ ggml_tensor_overhead() * 8 + ggml_graph_overhead_custom(16, false) + 4096,
+        /*.mem_buffer =*/ nullptr,
+        /*.no_alloc   =*/ true,
+    };
+    ggml_context * ctx = ggml_init(ip);
+    if (!ctx) return 2;
+    ggml_tensor * tg = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, n, n_tok);
+    ggml_tensor * tu = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, n, n_tok);
+    tg->data = (void *) gate;
+    tu->data = (void *) up;
+    ggml_tensor * to = ggml_swiglu_split(ctx, tg, tu);
+    to->data = out;
+    ggml_cgraph * gf = ggml_new_graph_custom(ctx, 16, false);
+    ggml_build_forward_expand(gf, to);
+    ggml_cplan plan = ggml_graph_plan(gf, n_threads, nullptr);
+    std::vector<uint8_t> work(plan.work_size + 64);
+    plan.work_data = work.data();
+    const int rc = ggml_graph_compute(gf, &plan) == GGML_STATUS_SUCCESS ? 0 : 3;
+    ggml_free(ctx);
+    return rc;
+}
+
 }  // extern "C"

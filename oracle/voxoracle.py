@@ -140,6 +140,30 @@ class Oracle:
         self.lib.voxo_mul_mat_f16(_ptr(x), _ptr(w.view(np.uint16)), i64(n_tok), i64(k), i64(n_out), _ptr(out))
         return out
 
+    @staticmethod
+    def mul_mat_f16_blas(x, w) -> np.ndarray:
+        """The same product for sizes the scalar loop above would take minutes on: the activations rounded to f16, then an
+        f32 matrix product by numpy.  Same exact products, another order of the f32 sums."""
+        x16 = np.ascontiguousarray(x, np.float32).astype(np.float16).astype(np.float32)
+        return x16 @ np.ascontiguousarray(w, np.float16).astype(np.float32).T
+
+    def rms_norm_mul(self, x, w, eps) -> np.ndarray:
+        """MiniCPMModel::rms_norm: x [n_tok, k] f32, w [k] f32 -> [n_tok, k] f32."""
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        out = np.zeros_like(x)
+        i64 = ctypes.c_int64
+        self.lib.voxo_rms_norm_mul(_ptr(x), _ptr(w), ctypes.c_float(eps), i64(x.shape[0]), i64(x.shape[1]), _ptr(out))
+        return out
+
+    def swiglu(self, gate, up) -> np.ndarray:
+        """ggml_swiglu_split: silu(gate) * up, f32, any shape."""
+        gate = np.ascontiguousarray(gate, np.float32)
+        up = np.ascontiguousarray(up, np.float32)
+        out = np.zeros_like(gate)
+        self.lib.voxo_swiglu(_ptr(gate), _ptr(up), ctypes.c_int64(gate.size), _ptr(out))
+        return out
+
     def causal_mask(self, positions, total_len: int) -> np.ndarray:
         pos = np.ascontiguousarray(positions, np.int32)
         out = np.zeros((len(pos), total_len), np.uint16)
@@ -242,6 +266,28 @@ class RefGgml:
         out = np.zeros((n_tok, n_out), np.float32)
         i64 = ctypes.c_int64
         rc = self.lib.voxref_mul_mat_f16(_ptr(w.view(np.uint16)), _ptr(x), i64(k), i64(n_out), i64(n_tok), int(n_threads), _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"reference harness failed (code {rc})")
+        return out
+
+    def rms_norm_mul(self, x, w, eps, n_threads=1) -> np.ndarray:
+        """The reference's ggml_rms_norm + ggml_mul: x [n_tok, k] f32, w [k] f32 -> [n_tok, k] f32."""
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        out = np.zeros_like(x)
+        i64 = ctypes.c_int64
+        rc = self.lib.voxref_rms_norm_mul(_ptr(x), _ptr(w), ctypes.c_float(eps), i64(x.shape[1]), i64(x.shape[0]), int(n_threads), _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"reference harness failed (code {rc})")
+        return out
+
+    def swiglu(self, gate, up, n_threads=1) -> np.ndarray:
+        """The reference's ggml_swiglu_split: gate, up [n_tok, n] f32 -> [n_tok, n] f32."""
+        gate = np.ascontiguousarray(gate, np.float32)
+        up = np.ascontiguousarray(up, np.float32)
+        out = np.zeros_like(gate)
+        i64 = ctypes.c_int64
+        rc = self.lib.voxref_swiglu(_ptr(gate), _ptr(up), i64(gate.shape[1]), i64(gate.shape[0]), int(n_threads), _ptr(out))
         if rc != 0:
             raise RuntimeError(f"reference harness failed (code {rc})")
         return out

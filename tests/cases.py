@@ -127,6 +127,40 @@ def split_qkv(y, args=QKV_CASE):
     return (y[:, :H * D].reshape(n, H, D), y[:, H * D:(H + HK) * D].reshape(n, HK, D), y[:, (H + HK) * D:].reshape(n, HK, D))
 
 
+# The rest of a decoder layer for single-token steps (src/minicpm.cpp:715, 718-747, 762-776): output projection with the
+# scaled residual add, RMS norm, gate_up projection, SwiGLU, down projection with the scaled residual add.  f16 weights in
+# ggml's layout [features][inputs]; scale = scale_depth / sqrt(num_layers) of the 24-layer model.
+LAYER_CASE = dict(seed=41, hidden=1024, inter=4096, n_tok=5, eps=1e-5, scale=1.4 / np.sqrt(24.0))
+
+
+def layer_inputs(args=LAYER_CASE, n_tok=None):
+    rng = np.random.default_rng(args["seed"])
+    n, hid, inter = args["n_tok"] if n_tok is None else n_tok, args["hidden"], args["inter"]
+    return dict(attn=rng.standard_normal((n, hid)).astype(np.float32),
+                hidden=rng.standard_normal((n, hid)).astype(np.float32),
+                w_o=(rng.standard_normal((hid, hid)) / np.sqrt(hid)).astype(np.float16),
+                norm_w=(1.0 + 0.1 * rng.standard_normal(hid)).astype(np.float32),
+                w_gate_up=(rng.standard_normal((2 * inter, hid)) / np.sqrt(hid)).astype(np.float16),
+                w_down=(rng.standard_normal((hid, inter)) / np.sqrt(inter)).astype(np.float16))
+
+
+def layer_tail(ops, inp, args=LAYER_CASE, given=None):
+    """The chain above with `ops` providing mul_mat_f16, rms_norm_mul and swiglu (the oracle, or the reference build).
+    Returns every stage: h1 (hidden state after attention), normed, gate_up, fused (the SwiGLU output), h2 (the layer's
+    output).  With `given` (a mapping stage -> array, e.g. the reference's fixture) each stage is computed from the GIVEN
+    output of the stage before instead of from its own: a rounding that falls the other way in one stage (the
+    activations are rounded to f16 in front of every product) is then not carried into the next."""
+    scale, inter = np.float32(args["scale"]), args["inter"]
+    prev = (lambda name, own: own) if given is None else (lambda name, own: np.asarray(given[name]))
+    h1 = inp["hidden"] + ops.mul_mat_f16(inp["attn"], inp["w_o"]) * scale
+    normed = ops.rms_norm_mul(prev("h1", h1), inp["norm_w"], args["eps"])
+    gate_up = ops.mul_mat_f16(prev("normed", normed), inp["w_gate_up"])
+    gu = prev("gate_up", gate_up)
+    fused = ops.swiglu(np.ascontiguousarray(gu[:, :inter]), np.ascontiguousarray(gu[:, inter:]))
+    h2 = prev("h1", h1) + ops.mul_mat_f16(prev("fused", fused), inp["w_down"]) * scale
+    return dict(h1=h1, normed=normed, gate_up=gate_up, fused=fused, h2=h2)
+
+
 def rope_inputs(args):
     rng = np.random.default_rng(args["seed"])
     pos = np.array(args["positions"], np.int32)

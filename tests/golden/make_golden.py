@@ -26,7 +26,8 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(HERE))
 
 from oracle import voxoracle as vo  # noqa: E402
-from cases import CASES, KV_TYPE, QKV_CASE, ROPE_CASES, digest, make_inputs, pick_rows, qkv_inputs, rope_inputs, split_qkv  # noqa: E402
+from cases import (CASES, KV_TYPE, LAYER_CASE, QKV_CASE, ROPE_CASES, digest, layer_inputs, layer_tail, make_inputs, pick_rows,  # noqa: E402
+                   qkv_inputs, rope_inputs, split_qkv)
 
 
 def main():
@@ -64,6 +65,10 @@ def main():
     out["qkv/k"] = ref.rope(k, pos, freq_base=QKV_CASE["freq_base"], attn_factor=QKV_CASE["attn_factor"])
     out["qkv/v"] = v
     print(f"{'qkv':32s} projection of {x.shape} by {w.shape}")
+    # the rest of the layer (src/minicpm.cpp:715, 718-747, 762-776): o_proj + residual, rms_norm, gate_up, swiglu, down + residual
+    for stage, value in layer_tail(ref, layer_inputs()).items():
+        out["layer/" + stage] = value
+    print(f"{'layer':32s} {LAYER_CASE['n_tok']} tokens, hidden {LAYER_CASE['hidden']}, intermediate {LAYER_CASE['inter']}")
     path = os.path.join(HERE, "attn_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {os.path.getsize(path) / 1024:.0f} KiB")

@@ -3,7 +3,8 @@ reference's own ggml CPU backend, and against that backend itself where it is pr
 import numpy as np
 import pytest
 
-from cases import CASES, KV_TYPE, QKV_CASE, ROPE_CASES, digest, make_inputs, pick_rows, qkv_inputs, rel_err, rope_inputs, split_qkv
+from cases import (CASES, KV_TYPE, QKV_CASE, ROPE_CASES, digest, layer_inputs, layer_tail, make_inputs, pick_rows, qkv_inputs, rel_err,
+                   rope_inputs, split_qkv)
 
 # tolerance of the restatement against the reference's accurate path (both f32; they differ by
 # summation order and libm vs vectorised expf only)
@@ -67,6 +68,21 @@ def test_projection_restatement_matches_the_reference_fixture(oracle, golden):
     assert rel_err(oracle.rope(q, table), golden["qkv/q"]) < GATE_TOL
     assert rel_err(oracle.rope(k, table), golden["qkv/k"]) < GATE_TOL
     assert rel_err(v, golden["qkv/v"]) < GATE_TOL
+
+
+def test_layer_tail_restatement_matches_the_reference_fixture(oracle, golden):
+    """The rest of a decoder layer after attention (src/minicpm.cpp:715, 718-747, 762-776): ggml_mul_mat(o_proj) with the
+    scaled residual add, rms_norm, ggml_mul_mat(gate_up_proj), ggml_swiglu_split, ggml_mul_mat(down_proj) with the scaled
+    residual add; the restatement against the reference's own output of the same chain."""
+    given = {stage: golden["layer/" + stage] for stage in ("h1", "normed", "gate_up", "fused", "h2")}
+    # stage by stage, each from the reference's output of the stage before: sums in another order, nothing else
+    staged = layer_tail(oracle, layer_inputs(), given=given)
+    assert np.array_equal(staged["normed"], given["normed"])
+    for stage in ("h1", "gate_up", "fused", "h2"):
+        assert rel_err(staged[stage], given[stage]) < GATE_TOL, stage
+    # the whole chain on its own: an f16 rounding of an activation that falls the other way moves an output by about 1e-5
+    chain = layer_tail(oracle, layer_inputs())
+    assert rel_err(chain["h2"], given["h2"]) < 2e-4
 
 
 def test_storage_formats_bit_exact(oracle, golden):

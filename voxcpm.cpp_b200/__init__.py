@@ -8,6 +8,7 @@ the library is missing or cannot be loaded, importing ``lib()`` raises.
 from __future__ import annotations
 
 from .binding import (  # noqa: F401
-    F16, F32, Q8_0, AttnArgs, DecodeArgs, Engine, Group, GroupConfig, KVCache, KVConfig, LocditArgs, StepBuffers,
+    F16, F32, LINEAR_PLAIN, LINEAR_RESIDUAL, LINEAR_SWIGLU, Q8_0, AttnArgs, DecodeArgs, Engine, Group, GroupConfig, KVCache, KVConfig,
+    LinearArgs, LocditArgs, StepBuffers,
     Tensor, VoxError, declared_symbols, lib, library_path, partition_streams,
 )
