@@ -63,7 +63,7 @@ def parse():
     p.add_argument("--prefill-kv", default="f16", choices=["f16", "q8_0"], help="K/V operand type for --workload prefill")
     p.add_argument("--prefill-mask", action="store_true",
                    help="--workload prefill through vox_attn_forward with the causal mask as a tensor, as the reference's call site passes it")
-    p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1", "decode_profile", "locdit_profile", "projection"],
+    p.add_argument("--workload", default="serving", choices=["serving", "prefill", "decode_sweep", "decode_c1", "decode_profile", "locdit_profile", "projection", "layer_linears"],
                    help="serving = the headline line; the others time one more configuration each on one GPU")
     return p.parse_args()
 
@@ -421,6 +421,56 @@ def time_projection(pkg, torch, eng, timer, S, hidden=1024, layers=BASE_LAYERS +
             "launches_per_layer": 2, "per_stream_in_the_reference": "one ggml_mul_mat + two ggml_rope_ext + two ggml_cpy nodes per stream and layer"}
 
 
+def time_layer_linears(pkg, torch, eng, timer, S, hidden=1024, inter=4096, layers=BASE_LAYERS):
+    """The other matrices of a decoder layer for S streams (vox_linear): output projection with the residual add, RMS norm +
+    gate_up projection + SwiGLU (f16 out), down projection with the residual add; five launches per layer, every layer with
+    weights of its own (30 MB of f16 per layer: 24 layers do not fit the L2), replayed from a CUDA graph.  us per layer
+    and per matrix; roofline = the weight bytes / time against the measured HBM peak."""
+    hbm, _, _ = measured_peaks()
+    gen = torch.Generator(device="cuda").manual_seed(S + 1)
+    w_o = (torch.randn((layers, hidden, hidden), device="cuda", generator=gen) / hidden ** 0.5).half()
+    w_gu = (torch.randn((layers, 2 * inter, hidden), device="cuda", generator=gen) / hidden ** 0.5).half()
+    w_dn = (torch.randn((layers, hidden, inter), device="cuda", generator=gen) / inter ** 0.5).half()
+    norm = torch.ones((hidden,), device="cuda")
+    attn = torch.randn((S, hidden), device="cuda", generator=gen)
+    h0 = torch.randn((S, hidden), device="cuda", generator=gen)
+    h1, h2 = torch.empty_like(h0), torch.empty_like(h0)
+    fused = torch.empty((S, inter), device="cuda", dtype=torch.float16)  # leaves SwiGLU as f16, enters down_proj as f16
+
+    def o_proj(l):
+        eng.linear(attn, w_o[l], pkg.LINEAR_RESIDUAL, residual=h0, scale=0.3, out=h1)
+
+    def gate_up(l):
+        eng.linear(h1, w_gu[l], pkg.LINEAR_SWIGLU, norm_weight=norm, norm_eps=1e-5, out=fused)
+
+    def down(l):
+        eng.linear(fused, w_dn[l], pkg.LINEAR_RESIDUAL, residual=h1, scale=0.3, out=h2)
+
+    def graph_of(fns):
+        for l in range(layers):
+            for f in fns:
+                f(l)
+        eng.sync_status()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for l in range(layers):
+                for f in fns:
+                    f(l)
+        return g
+
+    out = {"config": f"o_proj {hidden} -> {hidden} + residual; RMS norm + gate_up {hidden} -> 2 x {inter} + SwiGLU; down {inter} -> {hidden} + residual; "
+                     f"{S} streams, f16 weights, x {layers} layers",
+           "launches_per_layer": 5, "per_stream_in_the_reference": "three ggml_mul_mat, ggml_rms_norm, ggml_mul, ggml_swiglu_split, two ggml_scale and two ggml_add nodes per stream and layer"}
+    wbytes = {"o_proj": hidden * hidden * 2.0, "gate_up": 2 * inter * hidden * 2.0, "down": hidden * inter * 2.0}
+    for name, fns in (("o_proj", [o_proj]), ("gate_up", [gate_up]), ("down", [down]), ("layer", [o_proj, gate_up, down])):
+        g = graph_of(fns)
+        cold = timer.ms(g.replay, 10, cold=True)
+        nbytes = sum(wbytes.values()) if name == "layer" else wbytes[name]
+        out[name] = {"cold_us_per_layer": cold * 1e3 / layers, "weight_bytes_per_layer": nbytes,
+                     "cold_weight_gb_s": nbytes * layers / (cold * 1e-3) / 1e9, "cold_frac_of_measured_hbm": nbytes * layers / (cold * 1e-3) / 1e9 / hbm}
+    return out
+
+
 def time_decode_shape(pkg, torch, eng, timer, L, B, kv, n_base, n_res, cpu=False):
     """Single-token attention of `n_base + n_res` layers over B streams of L rows each, issued from C as one step
     (no append): warm and cold (L2 scrubbed) us per layer, GB/s, fraction of the measured HBM peak; for one stream
@@ -471,6 +521,8 @@ def aux_workload(args, pkg, torch):
         out["results"] = [time_decode_shape(pkg, torch, eng, timer, 256, 1, "f16", BASE_LAYERS, 0, cpu=not args.no_cpu_baseline)]
     elif args.workload == "projection":
         out["results"] = [time_projection(pkg, torch, eng, timer, S) for S in (256, 32)]
+    elif args.workload == "layer_linears":
+        out["results"] = [time_layer_linears(pkg, torch, eng, timer, S) for S in (256, 32)]
     elif args.workload == "decode_profile":
         # a reduced instance of the serving launch for profiler captures: one layer, 128 streams of 4096 rows (268 MB of
         # f16 K/V, 142 MB of q8_0: more than the L2 holds, far less than the serving workload's 8 to 17 GB)
@@ -748,6 +800,7 @@ def other_shapes(args, pkg, torch, eng, total_steps):
     out["decode_sweep"] = sweep
     out["decode_c1"] = time_decode_shape(pkg, torch, eng, timer, 256, 1, "f16", BASE_LAYERS, 0, cpu=cpu)
     out["qkv_projection"] = [time_projection(pkg, torch, eng, timer, S) for S in (256, 32)]
+    out["layer_linears"] = [time_layer_linears(pkg, torch, eng, timer, S) for S in (256, 32)]
     if cpu:
         out["locdit_cpu_baseline"] = cpu_attention_us(2, DIT_SEQ, DIT_SEQ, "f32", False, n_layers=CFM_STEPS * DIT_LAYERS)
     return out

@@ -254,24 +254,29 @@ int    vox_qkv_project(vox_engine * e, const vox_qkv_args * a, void * workspace,
  *   x     [k_dim, n_tokens] f32, x_nb_token bytes between tokens
  *   w     [k_dim, rows] f16 in ggml's layout (a row per output feature, k_dim contiguous), w_nb_row bytes between rows
  *   out   [n_out, n_tokens] f32, out_nb_token bytes between tokens; residual likewise (may be out itself)
+ *   x_type, out_type   VOX_TYPE_F32 (0, the default) or VOX_TYPE_F16.  The product rounds its activations to f16 in any
+ *         case, so a layer whose output only feeds another product (the SwiGLU output in front of down_proj) may leave
+ *         as f16 and enter the next call as f16: same values, no conversion launch, half the bytes.  f16 x comes without
+ *         norm_weight; f16 out comes without a residual.
  * k_dim a multiple of 64; n_out a multiple of 64 (32 for SwiGLU).
- * workspace: vox_linear_workspace_bytes (the f16 copy of x), 16-byte aligned.  Never allocates. */
+ * workspace: vox_linear_workspace_bytes (the f16 copy of x; none needed for f16 x), 16-byte aligned.  Never allocates. */
 enum vox_linear_mode { VOX_LINEAR_PLAIN = 0, VOX_LINEAR_RESIDUAL = 1, VOX_LINEAR_SWIGLU = 2 };
 typedef struct {
     int32_t       n_tokens, k_dim, n_out;
     int32_t       mode;
-    const float * x;
+    const void *  x;
     size_t        x_nb_token;
     const void *  w;
     size_t        w_nb_row;
     int32_t       w_type; /* VOX_TYPE_F16 */
-    float *       out;
+    void *        out;
     size_t        out_nb_token;
     const float * residual;
     size_t        res_nb_token;
     float         scale;
     const float * norm_weight; /* [k_dim] f32 or NULL */
     float         norm_eps;
+    int32_t       x_type, out_type;
 } vox_linear_args;
 
 size_t vox_linear_workspace_bytes(int n_tokens, int k_dim);

@@ -80,6 +80,24 @@ def test_plain_product_for_shapes_that_split_k_differently(k, n_out, engine, pkg
     assert rel_err(got, oracle.mul_mat_f16_blas(x, w)) < TOL
 
 
+def test_f16_between_two_products_changes_nothing(engine, pkg):
+    """The SwiGLU output leaves as f16 and enters the down projection as f16: the product rounds its activations to f16
+    anyway, so the layer's output has the same bits as with an f32 tensor (and a conversion launch) in between."""
+    import torch
+    inp = layer_inputs(n_tok=200)
+    h1 = dev(inp["hidden"])
+    kw = dict(norm_weight=dev(inp["norm_w"]), norm_eps=LAYER_CASE["eps"])
+    fused32 = engine.linear(h1, dev(inp["w_gate_up"]), pkg.LINEAR_SWIGLU, **kw)
+    launches = engine.launches
+    fused16 = engine.linear(h1, dev(inp["w_gate_up"]), pkg.LINEAR_SWIGLU, out_f16=True, **kw)
+    via16 = engine.linear(fused16, dev(inp["w_down"]), pkg.LINEAR_RESIDUAL, residual=h1, scale=0.25)
+    assert engine.launches - launches == 3  # conversion + product, then the product alone
+    via32 = engine.linear(fused32, dev(inp["w_down"]), pkg.LINEAR_RESIDUAL, residual=h1, scale=0.25)
+    engine.sync_status()
+    assert torch.equal(fused16, fused32.half())
+    assert torch.equal(via16, via32)
+
+
 def test_results_do_not_depend_on_timing(engine, pkg):
     """The CTAs of a cluster add their partial sums in rank order: two runs give the same bits."""
     import torch

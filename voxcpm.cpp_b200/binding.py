@@ -89,7 +89,7 @@ class LinearArgs(C.Structure):
     _fields_ = [("n_tokens", C.c_int32), ("k_dim", C.c_int32), ("n_out", C.c_int32), ("mode", C.c_int32), ("x", C.c_void_p),
                 ("x_nb_token", C.c_size_t), ("w", C.c_void_p), ("w_nb_row", C.c_size_t), ("w_type", C.c_int32), ("out", C.c_void_p),
                 ("out_nb_token", C.c_size_t), ("residual", C.c_void_p), ("res_nb_token", C.c_size_t), ("scale", C.c_float),
-                ("norm_weight", C.c_void_p), ("norm_eps", C.c_float)]
+                ("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("x_type", C.c_int32), ("out_type", C.c_int32)]
 
 
 LINEAR_PLAIN, LINEAR_RESIDUAL, LINEAR_SWIGLU = 0, 1, 2
@@ -321,22 +321,27 @@ class Engine:
         _check(lib().vox_qkv_project(self.h, C.byref(a), C.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(stream)))
         return q, k_new, v_new
 
-    def linear(self, x, w, mode=LINEAR_PLAIN, residual=None, scale=1.0, norm_weight=None, norm_eps=0.0, out=None, stream=None):
-        """``vox_linear``: x [n_tokens, k] f32, w [rows, k] f16 (ggml's layout) -> [n_tokens, n_out] f32; n_out = rows, or
-        rows / 2 in the SwiGLU mode (gate rows first).  ``residual`` [n_tokens, n_out] for LINEAR_RESIDUAL."""
+    def linear(self, x, w, mode=LINEAR_PLAIN, residual=None, scale=1.0, norm_weight=None, norm_eps=0.0, out=None, out_f16=False,
+               stream=None):
+        """``vox_linear``: x [n_tokens, k] f32 or f16, w [rows, k] f16 (ggml's layout) -> [n_tokens, n_out] f32 (f16 with
+        ``out_f16``); n_out = rows, or rows / 2 in the SwiGLU mode (gate rows first).  ``residual`` [n_tokens, n_out] for
+        LINEAR_RESIDUAL."""
         import torch
         n_tok, k = x.shape
+        x16 = x.dtype == torch.float16
         n_out = w.shape[0] // 2 if mode == LINEAR_SWIGLU else w.shape[0]
         if out is None:
-            out = torch.empty((n_tok, n_out), dtype=torch.float32, device=x.device)
-        a = LinearArgs(n_tok, k, n_out, mode, x.data_ptr(), x.stride(0) * 4, w.data_ptr(), w.stride(0) * 2, F16, out.data_ptr(),
-                       out.stride(0) * 4)
+            out = torch.empty((n_tok, n_out), dtype=torch.float16 if out_f16 else torch.float32, device=x.device)
+        out16 = out.dtype == torch.float16
+        a = LinearArgs(n_tok, k, n_out, mode, x.data_ptr(), x.stride(0) * (2 if x16 else 4), w.data_ptr(), w.stride(0) * 2, F16,
+                       out.data_ptr(), out.stride(0) * (2 if out16 else 4))
         if residual is not None:
             a.residual, a.res_nb_token = residual.data_ptr(), residual.stride(0) * 4
         a.scale = scale
         if norm_weight is not None:
             a.norm_weight, a.norm_eps = norm_weight.data_ptr(), norm_eps
-        ws = self.workspace(lib().vox_linear_workspace_bytes(n_tok, k))
+        a.x_type, a.out_type = (F16 if x16 else F32), (F16 if out16 else F32)
+        ws = self.workspace(max(256, lib().vox_linear_workspace_bytes(n_tok, k)))
         _check(lib().vox_linear(self.h, C.byref(a), C.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(stream)))
         return out
 

@@ -40,7 +40,26 @@ constexpr int kLinStage  = kLinABytes + kLinBBytes;
 constexpr int kLinSmem   = kLinRing * kLinStage + 1024;
 constexpr int kLinThreads = 256;                // producer, issuer, two idle warps, four epilogue warps
 constexpr int kLinMaxSplit = 8;
-static_assert(kLinRing * kLinStage >= kLinTok * kLinCols * 4, "the ring must hold the accumulators the cluster exchanges");
+static_assert(kLinRing * kLinStage >= 3 * kLinTok * kLinCols * 4 && kLinRing * kLinStage >= kLinTok * (kLinCols + 4) * 4,
+              "the idle ring holds what a CTA sends, what it receives and what it writes out");
+
+// Developer build (-DVOX_ATTN_DEVELOPER): the time (globaltimer, ns) at which thread 128 of a CTA passes a few points.
+#ifdef VOX_ATTN_DEVELOPER
+constexpr int kLinTraceCtas = 1024, kLinTracePoints = 8;
+__device__ unsigned long long g_linear_trace[kLinTraceCtas][kLinTracePoints];
+__device__ __forceinline__ unsigned long long lin_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define LIN_TRACE(point)                                                                                                      \
+    do {                                                                                                                      \
+        const int cta__ = (int) (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));                             \
+        if (threadIdx.x == 128 && cta__ < kLinTraceCtas) g_linear_trace[cta__][point] = lin_ns();                            \
+    } while (0)
+#else
+#define LIN_TRACE(point)
+#endif
 
 struct LinearParams {
     int           n_tokens, k_dim, n_out;  // n_out: output features (SwiGLU: of the product gate * up)
@@ -48,8 +67,9 @@ struct LinearParams {
     float         scale;
     const float * residual;
     size_t        res_nb_token;
-    float *       out;
+    uint8_t *     out;
     size_t        out_nb_token;
+    int           out_f16;
     int *         status;
 };
 
@@ -62,10 +82,18 @@ __global__ void __launch_bounds__(256) linear_prepare_kernel(const uint8_t * x, 
     pdl_launch_dependents();
     const int     token = blockIdx.x, tid = threadIdx.x;
     const float * row = reinterpret_cast<const float *>(x + (size_t) token * nb_token);
+    const bool    vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;  // k_dim is a multiple of 64
     float         scale = 1.0f;
     if (norm_w != nullptr) {
         float s = 0.0f;
-        for (int i = tid; i < k_dim; i += 256) s += row[i] * row[i];
+        if (vec) {
+            for (int i = tid; i < k_dim / 4; i += 256) {
+                const float4 v = reinterpret_cast<const float4 *>(row)[i];
+                s += v.x * v.x; s += v.y * v.y; s += v.z * v.z; s += v.w * v.w;
+            }
+        } else {
+            for (int i = tid; i < k_dim; i += 256) s += row[i] * row[i];
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if ((tid & 31) == 0) part[tid >> 5] = s;
@@ -75,10 +103,23 @@ __global__ void __launch_bounds__(256) linear_prepare_kernel(const uint8_t * x, 
         for (int i = 0; i < 8; ++i) total += part[i];
         scale = 1.0f / sqrtf(total / (float) k_dim + eps);
     }
-    for (int i = tid; i < k_dim; i += 256) {
-        float v = row[i];
-        if (norm_w != nullptr) v = __fmul_rn(__fmul_rn(v, scale), norm_w[i]);
-        out[(size_t) token * k_dim + i] = __float2half_rn(v);
+    __half * orow = out + (size_t) token * k_dim;
+    if (vec) {
+        for (int i = tid; i < k_dim / 4; i += 256) {
+            float4 v = reinterpret_cast<const float4 *>(row)[i];
+            if (norm_w != nullptr) {
+                const float4 w = reinterpret_cast<const float4 *>(norm_w)[i];
+                v.x = __fmul_rn(__fmul_rn(v.x, scale), w.x); v.y = __fmul_rn(__fmul_rn(v.y, scale), w.y);
+                v.z = __fmul_rn(__fmul_rn(v.z, scale), w.z); v.w = __fmul_rn(__fmul_rn(v.w, scale), w.w);
+            }
+            *reinterpret_cast<uint2 *>(orow + 4 * i) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+        }
+    } else {
+        for (int i = tid; i < k_dim; i += 256) {
+            float v = row[i];
+            if (norm_w != nullptr) v = __fmul_rn(__fmul_rn(v, scale), norm_w[i]);
+            orow[i] = __float2half_rn(v);
+        }
     }
 }
 
@@ -106,7 +147,7 @@ template <int S>
 __global__ void __launch_bounds__(kLinThreads, 2)
 linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const LinearParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[2 * kLinRing + 1];
+    __shared__ uint64_t bars[2 * kLinRing + 2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -114,7 +155,8 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     const int      tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int      tile = blockIdx.x, tok0 = blockIdx.y * kLinTok;
     const int      rank = S > 1 ? (int) cluster_rank() : 0;
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = full0 + 8 * kLinRing, done = empty0 + 8 * kLinRing;
+    LIN_TRACE(0);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = full0 + 8 * kLinRing, done = empty0 + 8 * kLinRing, xbar = done + 8;
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kLinRing; ++s) {
@@ -122,6 +164,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             mbar_init(empty0 + 8 * s, 1);
         }
         mbar_init(done, 1);
+        mbar_init(xbar, 1);
         fence_mbar_init();
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
@@ -130,7 +173,9 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    pdl_wait();  // the f16 copy of the activations comes from the kernel before
+    LIN_TRACE(1);
+    // The next kernel of the stream may be scheduled from here on; it still waits, in its own dependency wait, for this
+    // grid to complete, and every thread of this grid passes its own wait before it touches what the kernel before wrote.
     pdl_launch_dependents();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&tmem_base_slot);
     const int      n_kb = p.k_dim / kLinKBlock / S, kb0 = rank * n_kb;  // this CTA's share of the K blocks
@@ -145,15 +190,28 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 
     if (warp == 0) {
         if (lane == 0) {  // producer
+            // The weights do not come from the kernel before: the first ring of them is asked for ahead of the dependency
+            // wait, so their way from HBM is covered by that kernel's last microseconds.
+            const int n_early = min(n_kb, kLinRing);
+            for (int i = 0; i < n_early; ++i) {
+                const uint32_t sa = smem_base + i * kLinStage;
+                const int      kx = (kb0 + i) * kLinKBlock;
+                mbar_expect_tx(full0 + 8 * i, kLinStage);
+                tma_load_5d(sa + kLinABytes, &map_w, full0 + 8 * i, kx, row_a, 0, 0, 0);
+                tma_load_5d(sa + kLinABytes + kLinBBytes / 2, &map_w, full0 + 8 * i, kx, row_b, 0, 0, 0);
+            }
+            pdl_wait();  // the f16 copy of the activations comes from the kernel before
             for (int i = 0; i < n_kb && !aborted(); ++i) {
                 const int st = i % kLinRing;
                 if (i >= kLinRing && !mbar_wait_bounded(empty0 + 8 * st, ((i / kLinRing) - 1) & 1)) { give_up(); break; }
                 const uint32_t sa = smem_base + st * kLinStage;
                 const int      kx = (kb0 + i) * kLinKBlock;
-                mbar_expect_tx(full0 + 8 * st, kLinStage);
+                if (i >= n_early) {
+                    mbar_expect_tx(full0 + 8 * st, kLinStage);
+                    tma_load_5d(sa + kLinABytes, &map_w, full0 + 8 * st, kx, row_a, 0, 0, 0);
+                    tma_load_5d(sa + kLinABytes + kLinBBytes / 2, &map_w, full0 + 8 * st, kx, row_b, 0, 0, 0);
+                }
                 tma_load_5d(sa, &map_x, full0 + 8 * st, kx, tok0, 0, 0, 0);
-                tma_load_5d(sa + kLinABytes, &map_w, full0 + 8 * st, kx, row_a, 0, 0, 0);
-                tma_load_5d(sa + kLinABytes + kLinBBytes / 2, &map_w, full0 + 8 * st, kx, row_b, 0, 0, 0);
             }
         }
     } else if (warp == 1) {
@@ -176,6 +234,8 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     }
 
     // ---- epilogue: one thread per token holds the 64 accumulator columns of its row
+    if (!(warp == 0 && lane == 0)) pdl_wait();  // the residual may come from the kernel before as well
+    LIN_TRACE(2);
     const bool epi = warp >= 4;
     const int  row = tid - 128, token = tok0 + row;
     uint32_t   r[kLinCols];
@@ -183,6 +243,7 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     if (epi) {
         if (mbar_wait_bounded(done, 0)) {
             tc_fence_after();
+            LIN_TRACE(3);
             tmem_ld64_sync(tmem + ((uint32_t) (32 * (warp & 3)) << 16), r);
             have = true;
         } else {
@@ -190,89 +251,141 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         }
     }
     // columns this CTA finishes: h of the first 32 and the h that go with them of the second 32
-    constexpr int h = 32 / S;
-    float         a[h], b[h];  // sums of columns rank * h + i and 32 + rank * h + i
+    constexpr int      h = 32 / S;
+    constexpr uint32_t kSendOff = 0, kRecvOff = 32 * 1024, kOutOff = S == 1 ? 0 : 64 * 1024;  // areas of the (idle) ring
+    constexpr int      kOutStride = 2 * h + 4;  // floats per staged row: four more than it holds, against bank conflicts
+    float              a[h], b[h];  // sums of columns rank * h + i and 32 + rank * h + i
     if constexpr (S == 1) {
         if (epi && have) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) { a[i] = __uint_as_float(r[i]); b[i] = __uint_as_float(r[32 + i]); }
         }
     } else {
-        // Every CTA of the cluster is past its MMAs once its epilogue threads are here: the rings are idle and take the
-        // accumulators, [source rank][token][2h columns] f32 (32 KB whatever the split).
+        // The CTAs of the cluster exchange accumulators: every CTA lays its 64 columns out by destination
+        // ([destination rank][token][2h columns] f32, 4 KB per destination at S = 8) and sends each destination its part
+        // with one bulk copy through distributed shared memory, which counts the bytes on the receiver's barrier.
+        // (Storing the pieces one by one with st.shared::cluster took 5 us per launch.)
+        // Every CTA of the cluster is past its MMAs once its epilogue threads have passed the cluster barrier: the rings
+        // are idle from there on and take the copies.
+        if (tid == 128) mbar_expect_tx(xbar, kLinTok * kLinCols * 4);  // what the S senders (this CTA among them) will deliver
         __syncwarp();
         cluster_sync_all();
+        LIN_TRACE(4);
         if (epi && have) {
-            const uint32_t mine = smem_base + ((uint32_t) (rank * kLinTok + row) * 2 * h) * 4;
 #pragma unroll
             for (int d = 0; d < S; ++d) {
-                const uint32_t dst = map_to_rank(mine, (uint32_t) d);
-#pragma unroll
-                for (int j = 0; j < h; j += 4) {
-                    st_cluster_f4(dst + 4 * j, __uint_as_float(r[d * h + j]), __uint_as_float(r[d * h + j + 1]),
-                                  __uint_as_float(r[d * h + j + 2]), __uint_as_float(r[d * h + j + 3]));
-                    st_cluster_f4(dst + 4 * (h + j), __uint_as_float(r[32 + d * h + j]), __uint_as_float(r[32 + d * h + j + 1]),
-                                  __uint_as_float(r[32 + d * h + j + 2]), __uint_as_float(r[32 + d * h + j + 3]));
-                }
-            }
-        }
-        __syncwarp();
-        cluster_sync_all();
-        if (epi) {
-#pragma unroll
-            for (int i = 0; i < h; ++i) a[i] = b[i] = 0.0f;
-#pragma unroll
-            for (int s = 0; s < S; ++s) {  // in rank order: the sum does not depend on which CTA was first
-                const float4 * src = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(smem_gen) + (size_t) (s * kLinTok + row) * 2 * h);
+                float4 * dst = reinterpret_cast<float4 *>(smem_gen + kSendOff) + ((size_t) (d * kLinTok + row) * 2 * h) / 4;
 #pragma unroll
                 for (int j = 0; j < h / 4; ++j) {
-                    const float4 va = src[j], vb = src[h / 4 + j];
-                    a[4 * j] += va.x; a[4 * j + 1] += va.y; a[4 * j + 2] += va.z; a[4 * j + 3] += va.w;
-                    b[4 * j] += vb.x; b[4 * j + 1] += vb.y; b[4 * j + 2] += vb.z; b[4 * j + 3] += vb.w;
+                    dst[j] = make_float4(__uint_as_float(r[d * h + 4 * j]), __uint_as_float(r[d * h + 4 * j + 1]),
+                                         __uint_as_float(r[d * h + 4 * j + 2]), __uint_as_float(r[d * h + 4 * j + 3]));
+                    dst[h / 4 + j] = make_float4(__uint_as_float(r[32 + d * h + 4 * j]), __uint_as_float(r[32 + d * h + 4 * j + 1]),
+                                                 __uint_as_float(r[32 + d * h + 4 * j + 2]), __uint_as_float(r[32 + d * h + 4 * j + 3]));
+                }
+            }
+        }
+        if (epi) {
+            fence_proxy_async_smem();  // the rows above are read by the bulk copies
+            named_bar_sync(1, 128);
+            if (tid == 128 && !aborted()) {
+                constexpr uint32_t part = kLinTok * 2 * h * 4;  // bytes per destination
+#pragma unroll
+                for (int d = 0; d < S; ++d)
+                    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     map_to_rank(smem_base + kRecvOff + (uint32_t) rank * part, (uint32_t) d)),
+                                 "r"(smem_base + kSendOff + (uint32_t) d * part), "r"(part), "r"(map_to_rank(xbar, (uint32_t) d))
+                                 : "memory");
+            }
+            const bool arrived = mbar_wait_bounded(xbar, 0);
+            LIN_TRACE(5);
+            if (!arrived) give_up();
+#pragma unroll
+            for (int i = 0; i < h; ++i) a[i] = b[i] = 0.0f;
+            if (arrived) {
+#pragma unroll
+                for (int s2 = 0; s2 < S; ++s2) {  // in rank order: the sum does not depend on which CTA was first
+                    const float4 * src = reinterpret_cast<const float4 *>(smem_gen + kRecvOff) + ((size_t) (s2 * kLinTok + row) * 2 * h) / 4;
+#pragma unroll
+                    for (int j = 0; j < h / 4; ++j) {
+                        const float4 va = src[j], vb = src[h / 4 + j];
+                        a[4 * j] += va.x; a[4 * j + 1] += va.y; a[4 * j + 2] += va.z; a[4 * j + 3] += va.w;
+                        b[4 * j] += vb.x; b[4 * j + 1] += vb.y; b[4 * j + 2] += vb.z; b[4 * j + 3] += vb.w;
+                    }
                 }
             }
         }
     }
-    if (epi && have && token < p.n_tokens && !aborted()) {
-        float *       out = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(p.out) + (size_t) token * p.out_nb_token);
-        const float * res = p.residual ? reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(p.residual) + (size_t) token * p.res_nb_token) : nullptr;
-        if (p.mode == VOX_LINEAR_SWIGLU) {
-            const int c0 = tile * 32 + rank * h;
+    // The results leave through shared memory, so that neighbouring threads write neighbouring pieces of a token's row
+    // (a thread storing its own row float by float, rows 4 to 32 KB apart, took 15 us for 8 MB of output).
+    if (epi) {
+        const bool swiglu = p.mode == VOX_LINEAR_SWIGLU;
+        float *    stage  = reinterpret_cast<float *>(smem_gen + kOutOff) + (size_t) row * kOutStride;
+        if (swiglu) {
 #pragma unroll
-            for (int i = 0; i < h; ++i) {
-                const float g = a[i];
-                out[c0 + i]   = g / (1.0f + expf(-g)) * b[i];  // ggml_swiglu_split: silu(gate) * up
-            }
+            for (int i = 0; i < h; ++i) stage[i] = a[i] / (1.0f + expf(-a[i])) * b[i];  // ggml_swiglu_split: silu(gate) * up
         } else {
-            const int c0 = tile * kLinCols + rank * h;
 #pragma unroll
-            for (int i = 0; i < h; ++i) {
-                float va = a[i], vb = b[i];
+            for (int i = 0; i < h; ++i) { stage[i] = a[i]; stage[h + i] = b[i]; }
+        }
+        named_bar_sync(1, 128);
+        if (have && !aborted()) {
+            const int per_row = swiglu ? h / 4 : 2 * h / 4;  // 16-byte pieces of a row that this CTA writes
+            const int c0      = swiglu ? tile * 32 + rank * h : tile * kLinCols + rank * h;
+            for (int pc = row; pc < kLinTok * per_row; pc += 128) {
+                const int rr = pc / per_row, q = pc - rr * per_row;
+                if (tok0 + rr >= p.n_tokens) break;  // rows only grow along the loop
+                const int col = c0 + (q < h / 4 ? 4 * q : 32 + 4 * (q - h / 4));
+                float4    v   = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(smem_gen + kOutOff) + (size_t) rr * kOutStride + 4 * q);
+                uint8_t * orow = p.out + (size_t) (tok0 + rr) * p.out_nb_token;
                 if (p.mode == VOX_LINEAR_RESIDUAL) {  // hidden = residual + scale * product (ggml_scale, then ggml_add)
-                    va = __fadd_rn(res[c0 + i], __fmul_rn(va, p.scale));
-                    vb = __fadd_rn(res[c0 + 32 + i], __fmul_rn(vb, p.scale));
+                    const float * res = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(p.residual) + (size_t) (tok0 + rr) * p.res_nb_token) + col;
+                    v.x = __fadd_rn(res[0], __fmul_rn(v.x, p.scale));
+                    v.y = __fadd_rn(res[1], __fmul_rn(v.y, p.scale));
+                    v.z = __fadd_rn(res[2], __fmul_rn(v.z, p.scale));
+                    v.w = __fadd_rn(res[3], __fmul_rn(v.w, p.scale));
                 }
-                out[c0 + i]      = va;
-                out[c0 + 32 + i] = vb;
+                if (p.out_f16) {
+                    *reinterpret_cast<uint2 *>(orow + (size_t) col * 2) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+                } else {
+                    float * o = reinterpret_cast<float *>(orow) + col;
+                    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+                }
             }
         }
     }
+    if constexpr (S > 1) {
+        // no CTA leaves while a copy it sent, or one sent to it, may still be on its way
+        __syncwarp();
+        cluster_sync_all();
+    }
+    LIN_TRACE(6);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, kLinCols);
     }
+    LIN_TRACE(7);
 }
 
-// CTAs along K: as many as keep every CTA at two K blocks or more, without going far past two CTAs per SM in all
+// CTAs along K: as many as keep every CTA at four K blocks or more (a CTA's fixed costs, set-up, the exchange and the
+// barriers of the cluster, are about 6 us: measured on 256 tokens x 1024 -> 1024, 13.3 / 10.6 / 12.4 us per launch pair
+// with 2 / 4 / 8 CTAs along K), without going far past two CTAs per SM in all
 int pick_split(int k_dim, int tiles, int sms) {
     int s = 1;
-    while (s < kLinMaxSplit && (k_dim / kLinKBlock) % (2 * s) == 0 && k_dim / kLinKBlock / (2 * s) >= 2 && tiles * 2 * s <= 2 * sms + sms / 2) s *= 2;
+    while (s < kLinMaxSplit && (k_dim / kLinKBlock) % (2 * s) == 0 && k_dim / kLinKBlock / (2 * s) >= 4 && tiles * 2 * s <= 2 * sms + sms / 2) s *= 2;
     return s;
 }
 
 }  // namespace
+
+#ifdef VOX_ATTN_DEVELOPER
+// out: kLinTraceCtas x kLinTracePoints times in ns of the last launch (0 entry, 1 set-up done, 2 past the dependency wait,
+// 3 accumulator complete, 4 / 5 past the first / second cluster barrier, 6 results stored, 7 tensor memory released)
+extern "C" int vox_debug_linear_trace(unsigned long long * out) {
+    return cudaMemcpyFromSymbol(out, g_linear_trace, sizeof(unsigned long long) * kLinTraceCtas * kLinTracePoints) == cudaSuccess ? 0 : 4;
+}
+#endif
 
 extern "C" {
 
@@ -290,17 +403,31 @@ int vox_linear(vox_engine * e, const vox_linear_args * a, void * workspace, size
     VOX_REQUIRE(a->k_dim > 0 && a->k_dim % kLinKBlock == 0, VOX_ATTN_UNSUPPORTED, "input size %d is not a multiple of 64", a->k_dim);
     const int tile_out = a->mode == VOX_LINEAR_SWIGLU ? 32 : kLinCols;
     VOX_REQUIRE(a->n_out > 0 && a->n_out % tile_out == 0, VOX_ATTN_UNSUPPORTED, "output size %d is not a multiple of %d", a->n_out, tile_out);
-    VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->x) & 3) == 0 && a->x_nb_token % 4 == 0 && a->x_nb_token >= (size_t) a->k_dim * 4,
-                VOX_ATTN_INVALID_ARGUMENT, "x rows must be 4-byte aligned and at least k_dim floats apart");
+    const bool x16 = a->x_type == VOX_TYPE_F16, out16 = a->out_type == VOX_TYPE_F16;
+    VOX_REQUIRE((a->x_type == VOX_TYPE_F32 || x16) && (a->out_type == VOX_TYPE_F32 || out16), VOX_ATTN_UNSUPPORTED,
+                "x and out are f32 or f16 (types %d, %d)", a->x_type, a->out_type);
+    if (x16) {
+        VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->x) & 15) == 0 && a->x_nb_token % 16 == 0 && a->x_nb_token >= (size_t) a->k_dim * 2,
+                    VOX_ATTN_INVALID_ARGUMENT, "f16 x rows must be 16-byte aligned and at least k_dim halves apart");
+        VOX_REQUIRE(a->norm_weight == nullptr, VOX_ATTN_UNSUPPORTED, "the norm needs f32 x");
+    } else {
+        VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->x) & 3) == 0 && a->x_nb_token % 4 == 0 && a->x_nb_token >= (size_t) a->k_dim * 4,
+                    VOX_ATTN_INVALID_ARGUMENT, "x rows must be 4-byte aligned and at least k_dim floats apart");
+        VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->norm_weight) & 15) == 0, VOX_ATTN_INVALID_ARGUMENT, "norm_weight must be 16-byte aligned");
+    }
     VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->w) & 15) == 0 && a->w_nb_row % 16 == 0 && a->w_nb_row >= (size_t) a->k_dim * 2,
                 VOX_ATTN_INVALID_ARGUMENT, "weight rows must be 16-byte aligned and at least k_dim halves apart");
-    VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 3) == 0 && a->out_nb_token % 4 == 0 && a->out_nb_token >= (size_t) a->n_out * 4,
-                VOX_ATTN_INVALID_ARGUMENT, "out rows must be 4-byte aligned and at least n_out floats apart");
-    if (a->mode == VOX_LINEAR_RESIDUAL)
+    const size_t out_elem = out16 ? 2 : 4;
+    VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & (out16 ? 7 : 3)) == 0 && a->out_nb_token % (out16 ? 8 : 4) == 0 &&
+                    a->out_nb_token >= (size_t) a->n_out * out_elem,
+                VOX_ATTN_INVALID_ARGUMENT, "out rows must be aligned (4 bytes for f32, 8 for f16) and at least n_out values apart");
+    if (a->mode == VOX_LINEAR_RESIDUAL) {
+        VOX_REQUIRE(!out16, VOX_ATTN_UNSUPPORTED, "the residual mode writes f32");
         VOX_REQUIRE(a->residual != nullptr && a->res_nb_token % 4 == 0 && a->res_nb_token >= (size_t) a->n_out * 4, VOX_ATTN_INVALID_ARGUMENT,
                     "the residual mode needs residual rows at least n_out floats apart");
-    const size_t need = vox_linear_workspace_bytes(a->n_tokens, a->k_dim);
-    VOX_REQUIRE(workspace != nullptr && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+    }
+    const size_t need = x16 ? 0 : vox_linear_workspace_bytes(a->n_tokens, a->k_dim);
+    VOX_REQUIRE(x16 || (workspace != nullptr && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0),
                 VOX_ATTN_WORKSPACE_TOO_SMALL, "vox_linear needs %zu workspace bytes (16-byte aligned), got %zu", need, workspace_bytes);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!(e->attr_mask & (1u << 15))) {
@@ -310,19 +437,24 @@ int vox_linear(vox_engine * e, const vox_linear_args * a, void * workspace, size
         VOX_CUDA_TRY(cudaFuncSetAttribute(linear_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLinSmem));
         e->attr_mask |= 1u << 15;
     }
-    __half * x16 = static_cast<__half *>(workspace);
-    launch_pdl(linear_prepare_kernel, dim3((unsigned) a->n_tokens), dim3(256), 0, st, reinterpret_cast<const uint8_t *>(a->x), a->x_nb_token,
-               a->k_dim, a->norm_weight, a->norm_eps, x16);
-    int rc = check_launch(e, "linear_prepare_kernel");
-    if (rc != VOX_ATTN_OK) return rc;
+    int rc = VOX_ATTN_OK;
+    const void * xh = a->x;                      // f16 rows the product reads
+    uint64_t     xh_stride = a->x_nb_token;
+    if (!x16) {
+        xh = workspace;
+        xh_stride = (uint64_t) a->k_dim * 2;
+        launch_pdl(linear_prepare_kernel, dim3((unsigned) a->n_tokens), dim3(256), 0, st, reinterpret_cast<const uint8_t *>(a->x), a->x_nb_token,
+                   a->k_dim, a->norm_weight, a->norm_eps, static_cast<__half *>(workspace));
+        rc = check_launch(e, "linear_prepare_kernel");
+        if (rc != VOX_ATTN_OK) return rc;
+    }
 
     const int      w_rows = a->mode == VOX_LINEAR_SWIGLU ? 2 * a->n_out : a->n_out;
     CUtensorMap    mx, mw;
     const uint64_t xd[5] = {(uint64_t) a->k_dim, (uint64_t) a->n_tokens, 1, 1, 1};
-    const uint64_t xs[4] = {(uint64_t) a->k_dim * 2, (uint64_t) a->k_dim * 2 * a->n_tokens, (uint64_t) a->k_dim * 2 * a->n_tokens,
-                            (uint64_t) a->k_dim * 2 * a->n_tokens};
+    const uint64_t xs[4] = {xh_stride, xh_stride * a->n_tokens, xh_stride * a->n_tokens, xh_stride * a->n_tokens};
     const uint32_t xb[5] = {kLinKBlock, kLinTok, 1, 1, 1};
-    rc = make_tensor_map(e, &mx, x16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tensor_map(e, &mx, const_cast<void *>(xh), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != VOX_ATTN_OK) return rc;
     const uint64_t wd[5] = {(uint64_t) a->k_dim, (uint64_t) w_rows, 1, 1, 1};
     const uint64_t ws[4] = {(uint64_t) a->w_nb_row, (uint64_t) a->w_nb_row * w_rows, (uint64_t) a->w_nb_row * w_rows, (uint64_t) a->w_nb_row * w_rows};
@@ -334,10 +466,13 @@ int vox_linear(vox_engine * e, const vox_linear_args * a, void * workspace, size
     p.n_tokens = a->n_tokens; p.k_dim = a->k_dim; p.n_out = a->n_out; p.mode = a->mode;
     p.scale = a->mode == VOX_LINEAR_RESIDUAL ? a->scale : 1.0f;
     p.residual = a->residual; p.res_nb_token = a->res_nb_token;
-    p.out = a->out; p.out_nb_token = a->out_nb_token;
+    p.out = static_cast<uint8_t *>(a->out); p.out_nb_token = a->out_nb_token; p.out_f16 = out16 ? 1 : 0;
     p.status = e->status_dev;
     const int col_tiles = a->n_out / tile_out, tok_tiles = (a->n_tokens + kLinTok - 1) / kLinTok;
-    const int split = pick_split(a->k_dim, col_tiles * tok_tiles, e->sm_count);
+    int split = pick_split(a->k_dim, col_tiles * tok_tiles, e->sm_count);
+    if (e->linear_split > 0 && (a->k_dim / kLinKBlock) % e->linear_split == 0 &&
+        (e->linear_split == 1 || e->linear_split == 2 || e->linear_split == 4 || e->linear_split == 8))
+        split = e->linear_split;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned) col_tiles, (unsigned) tok_tiles, (unsigned) split);
