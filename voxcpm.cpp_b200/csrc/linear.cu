@@ -368,12 +368,16 @@ linear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     LIN_TRACE(7);
 }
 
-// CTAs along K: as many as keep every CTA at four K blocks or more (a CTA's fixed costs, set-up, the exchange and the
-// barriers of the cluster, are about 6 us: measured on 256 tokens x 1024 -> 1024, 13.3 / 10.6 / 12.4 us per launch pair
-// with 2 / 4 / 8 CTAs along K), without going far past two CTAs per SM in all
+// CTAs along K.  A matrix with few tiles (o_proj, down_proj: 32 tiles for 256 tokens) is split as far as every CTA keeps
+// four K blocks or more and the grid stays within two CTAs per SM: a CTA's fixed costs (set-up, the exchange and the
+// barriers of the cluster) are about 6 us (measured on 256 tokens x 1024 -> 1024: 13.3 / 10.6 / 12.4 us per launch pair
+// with 2 / 4 / 8 CTAs along K; x 4096 -> 1024: 21.0 / 15.4 / 13.8 us).  A matrix with a tile for every other SM or more
+// (gate_up: 128 and more) is not split: its CTAs fill the GPU as they are, and clusters only add their costs (32
+// tokens, 1024 -> 2 x 4096: 16.6 / 20.1 / 25.5 us with 1 / 2 / 4 CTAs along K).
 int pick_split(int k_dim, int tiles, int sms) {
+    if (tiles * 2 > sms) return 1;
     int s = 1;
-    while (s < kLinMaxSplit && (k_dim / kLinKBlock) % (2 * s) == 0 && k_dim / kLinKBlock / (2 * s) >= 4 && tiles * 2 * s <= 2 * sms + sms / 2) s *= 2;
+    while (s < kLinMaxSplit && (k_dim / kLinKBlock) % (2 * s) == 0 && k_dim / kLinKBlock / (2 * s) >= 4 && tiles * 2 * s <= 2 * sms) s *= 2;
     return s;
 }
 
