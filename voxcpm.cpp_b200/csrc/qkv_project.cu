@@ -40,6 +40,8 @@ constexpr int kBBytes   = kHeadDim * 128;           // [64 features][64 k] f16
 constexpr int kStageQkv = kABytes + kBBytes;
 constexpr int kSmemQkv  = kRing * kStageQkv + 1024;
 constexpr int kThreadsQkv = 256;                    // producer, issuer, two idle warps, four epilogue warps
+constexpr int kStageRow   = kHeadDim + 4;           // floats per row of the epilogue's staging tile (padded against bank conflicts)
+static_assert(kRing * kStageQkv >= kTokTile * kStageRow * 4, "the idle ring holds the staging tile");
 
 struct QkvParams {
     int             n_streams, k_dim, n_heads, n_kv_heads;
@@ -179,7 +181,9 @@ qkv_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     } else if (warp >= 4) {
         // epilogue: one thread per token
         const int row = tid - 128, token = tok0 + row;
-        if (mbar_wait_bounded(done, 0)) {
+        const bool arrived = mbar_wait_bounded(done, 0);
+        if (!arrived) give_up();
+        if (arrived) {
             tc_fence_after();
             uint32_t r[64];
             tmem_ld64_sync(tmem + ((uint32_t) (32 * (warp & 3)) << 16), r);
@@ -200,27 +204,39 @@ qkv_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         x[i + 32] = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
                     }
                 }
-                if (is_q) {
-                    float4 * out = reinterpret_cast<float4 *>(p.q + ((size_t) token * p.n_heads + head) * kHeadDim);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) out[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
-                } else {
+                if (!is_q && p.k_new == nullptr) {
                     const int kvh = is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
-                    if (p.k_new != nullptr) {
-                        float4 * out = reinterpret_cast<float4 *>((is_k ? p.k_new : p.v_new) + ((size_t) token * p.n_kv_heads + kvh) * kHeadDim);
+                    const int pos = p.positions[token] + p.pos_offset;
+                    if (pos < 0 || pos >= p.max_len) atomicOr(p.status, kStatusBadState);  // never write outside the stream's rows
+                    else store_cache_row(p, is_k ? p.k_rows : p.v_rows, is_k ? p.k_scales : p.v_scales, token, kvh, pos, x);
+                } else {
+                    // f32 rows leave through shared memory (the ring is idle by now), so that neighbouring threads write
+                    // neighbouring 16-byte pieces of a token's row instead of each thread its own row, 4 KB from the next
+                    float4 * stage = reinterpret_cast<float4 *>(smem_raw + (smem_base - smem_u32(smem_raw))) + (size_t) row * (kStageRow / 4);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) out[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
-                    } else {
-                        const int pos = p.positions[token] + p.pos_offset;
-                        if (pos < 0 || pos >= p.max_len) atomicOr(p.status, kStatusBadState);  // never write outside the stream's rows
-                        else store_cache_row(p, is_k ? p.k_rows : p.v_rows, is_k ? p.k_scales : p.v_scales, token, kvh, pos, x);
-                    }
+                    for (int i = 0; i < 16; ++i) stage[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
                 }
             }
-        } else {
-            give_up();
+        }
+        {
+            const bool f32_rows = head < p.n_heads || p.k_new != nullptr;  // the same for every thread of the CTA
+            if (f32_rows) {
+                named_bar_sync(1, 128);  // every epilogue thread gets here, whatever became of its wait
+                if (aborted()) goto epilogue_done;
+                const bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
+                float *    base = is_q ? p.q + (size_t) head * kHeadDim
+                                       : (is_k ? p.k_new + (size_t) (head - p.n_heads) * kHeadDim : p.v_new + (size_t) (head - p.n_heads - p.n_kv_heads) * kHeadDim);
+                const size_t tok_stride = (size_t) (is_q ? p.n_heads : p.n_kv_heads) * kHeadDim;
+                for (int pc = row; pc < kTokTile * 16; pc += 128) {
+                    const int rr = pc >> 4, q4 = pc & 15;
+                    if (tok0 + rr >= p.n_streams) break;
+                    const float4 v = reinterpret_cast<const float4 *>(smem_raw + (smem_base - smem_u32(smem_raw)))[(size_t) rr * (kStageRow / 4) + q4];
+                    reinterpret_cast<float4 *>(base + (size_t) (tok0 + rr) * tok_stride)[q4] = v;
+                }
+            }
         }
     }
+epilogue_done:
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
