@@ -81,6 +81,10 @@ struct DecodeParams {
     uint8_t *       k_scales;  // scale planes of this layer (q8_0)
     uint8_t *       v_scales;
     size_t          nb_pos, nb_head, nb_stream, sb_pos, sb_head, sb_stream;
+    // q8_0: the tiles of this layer (one contiguous span per 64 rows of a pair, see kQ8TileBytes) and the strides of a
+    // pair and of a stream
+    const uint8_t * q8_tiles;
+    size_t          q8_nb_head, q8_nb_stream;
     // Non-zero: the lengths and the cache rows this launch reads were not written by the kernel just before
     // it on the stream (only Q and the arriving row were), so the first tiles are requested before the
     // programmatic-dependency wait, while that kernel is still draining.
@@ -281,7 +285,7 @@ __device__ __forceinline__ Cut cut_work_list(const DecodeParams & p, int lane, i
 
 // Shared-memory ring: per stage one 64-row K tile and one 64-row V tile.
 //   f16 : 2 x 8 KB (128-byte rows, 128-byte swizzle)                       -> 16 KB, 4 stages
-//   q8_0: 2 x 4 KB int8 (64-byte rows, 64-byte swizzle) + 2 x 256 B scales -> 9 KB (1 KB aligned), 6 stages
+//   q8_0: 2 x 4 KB bytes (64-byte rows, 64-byte swizzle) + 2 x 256 B scales, one span of the cache -> 9 KB (1 KB aligned), 6 stages
 template <bool Q8> struct Ring {
     static constexpr int kStages     = Q8 ? 6 : 4;
     // q8_0 tiles are half the bytes and its arithmetic chain is longer: one more CTA hides it.  Measured per 256-stream
@@ -290,7 +294,7 @@ template <bool Q8> struct Ring {
     static constexpr int kCtasPerSm  = Q8 ? 4 : 3;
     static constexpr int kDataBytes  = Q8 ? kKvTile * 64 : kKvTile * 128;
     static constexpr int kStageBytes = Q8 ? 9 * 1024 : 2 * kDataBytes;
-    static constexpr int kTxBytes    = Q8 ? 2 * kDataBytes + 2 * kKvTile * 4 : 2 * kDataBytes;
+    static constexpr int kTxBytes    = Q8 ? kQ8TileBytes : 2 * kDataBytes;
     static constexpr int kSmemBytes  = kStages * kStageBytes + 1024;
     // the warps of a CTA are merged through the stage of the tile they consumed last
     static_assert(kStageBytes >= kConsumerWarps * kMaxGqa * kPartialStride * 4, "a stage must hold the warps' partials");
@@ -323,21 +327,22 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
 // contains the row: the bulk copy then delivers the new row like any other.  The proxy fence orders
 // these generic-proxy stores before the async-proxy read of the copy issued after the warp barrier.
 template <bool Q8>
-__device__ __forceinline__ void store_arriving_row(float2 kk, float2 vv, uint8_t * k_dst, uint8_t * v_dst, uint8_t * ks_dst,
-                                                   uint8_t * vs_dst, int lane) {
+__device__ __forceinline__ void store_arriving_row(float2 kk, float2 vv, uint8_t * k_pair, uint8_t * v_pair, uint8_t * ks_pair,
+                                                   uint8_t * vs_pair, size_t nb_pos, int pos, int lane) {
     if constexpr (!Q8) {
-        *reinterpret_cast<uint32_t *>(k_dst + lane * 4) = pack_half2(kk.x, kk.y);
-        *reinterpret_cast<uint32_t *>(v_dst + lane * 4) = pack_half2(vv.x, vv.y);
+        *reinterpret_cast<uint32_t *>(k_pair + (size_t) pos * nb_pos + lane * 4) = pack_half2(kk.x, kk.y);
+        *reinterpret_cast<uint32_t *>(v_pair + (size_t) pos * nb_pos + lane * 4) = pack_half2(vv.x, vv.y);
     } else {
         char2 qk, qv;
         float dk, dv;
         q8_0_quantize_pair(kk.x, kk.y, qk, dk);
         q8_0_quantize_pair(vv.x, vv.y, qv, dv);
-        *reinterpret_cast<uchar2 *>(k_dst + lane * 2) = q8_0_biased(qk);
-        *reinterpret_cast<uchar2 *>(v_dst + lane * 2) = q8_0_biased(qv);
+        const size_t tile = q8_tile_off(pos);
+        *reinterpret_cast<uchar2 *>(k_pair + tile + q8_byte_off(pos, 2 * lane)) = q8_0_biased(qk);
+        *reinterpret_cast<uchar2 *>(v_pair + tile + q8_byte_off(pos, 2 * lane)) = q8_0_biased(qv);
         if ((lane & 15) == 0) {
-            *reinterpret_cast<__half *>(ks_dst + (lane >> 4) * 2) = __float2half_rn(dk);
-            *reinterpret_cast<__half *>(vs_dst + (lane >> 4) * 2) = __float2half_rn(dv);
+            *reinterpret_cast<__half *>(ks_pair + tile + q8_scale_off(pos, lane >> 4)) = __float2half_rn(dk);
+            *reinterpret_cast<__half *>(vs_pair + tile + q8_scale_off(pos, lane >> 4)) = __float2half_rn(dv);
         }
     }
     asm volatile("fence.proxy.async;" ::: "memory");
@@ -404,8 +409,7 @@ __device__ __forceinline__ void fold_pairs(const DecodeParams & p, const int (*p
 
 template <bool Q8>
 __global__ void __launch_bounds__(kThreads, Ring<Q8>::kCtasPerSm)
-decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-              const __grid_constant__ CUtensorMap map_ks, const __grid_constant__ CUtensorMap map_vs, const DecodeParams p) {
+decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
     using R = Ring<Q8>;
     constexpr int kStages = R::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -436,12 +440,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         }
         fence_mbar_init();
     }
-    if (tid == kConsumerWarps * 32) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
-        if constexpr (Q8) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_ks)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_vs)) : "memory");
+    if constexpr (!Q8) {
+        if (tid == kConsumerWarps * 32) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
         }
     }
     __syncthreads();
@@ -496,9 +498,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                             kk.y = __fadd_rn(__fmul_rn(oy, r1.y), __fmul_rn(kk.y, r1.x));
                         }
                     }
-                    const size_t off  = (size_t) w.stream * p.nb_stream + (size_t) w.kvh * p.nb_head + (size_t) (w.len - 1) * p.nb_pos;
-                    const size_t soff = (size_t) w.stream * p.sb_stream + (size_t) w.kvh * p.sb_head + (size_t) (w.len - 1) * p.sb_pos;
-                    store_arriving_row<Q8>(kk, vv, p.k_rows + off, p.v_rows + off, p.k_scales + soff, p.v_scales + soff, lane);
+                    const size_t pair = (size_t) w.stream * p.nb_stream + (size_t) w.kvh * p.nb_head;
+                    store_arriving_row<Q8>(kk, vv, p.k_rows + pair, p.v_rows + pair, p.k_scales + pair, p.v_scales + pair, p.nb_pos, w.len - 1, lane);
                 }
             }
             int good = 1;
@@ -515,11 +516,14 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                     const uint32_t bar = full0 + 8 * s;
                     const int      pos = w.t * kKvTile;
                     mbar_expect_tx(bar, R::kTxBytes);
-                    tma_load_5d(sb, &map_k, bar, 0, pos, w.kvh, w.stream, p.layer);
-                    tma_load_5d(sb + R::kDataBytes, &map_v, bar, 0, pos, w.kvh, w.stream, p.layer);
-                    if constexpr (Q8) {
-                        tma_load_5d(sb + 2 * R::kDataBytes, &map_ks, bar, 2 * pos, 0, w.kvh, w.stream, p.layer);
-                        tma_load_5d(sb + 2 * R::kDataBytes + kKvTile * 4, &map_vs, bar, 2 * pos, 0, w.kvh, w.stream, p.layer);
+                    if constexpr (Q8) {  // the tile is one span of the cache, already in the layout of the stage
+                        const uint8_t * src = p.q8_tiles + (size_t) w.stream * p.q8_nb_stream + (size_t) w.kvh * p.q8_nb_head + (size_t) w.t * kQ8TileBytes;
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sb),
+                                     "l"(src), "r"((uint32_t) kQ8TileBytes), "r"(bar)
+                                     : "memory");
+                    } else {
+                        tma_load_5d(sb, &map_k, bar, 0, pos, w.kvh, w.stream, p.layer);
+                        tma_load_5d(sb + R::kDataBytes, &map_v, bar, 0, pos, w.kvh, w.stream, p.layer);
                     }
                 }
             }
@@ -1033,11 +1037,12 @@ size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv
     return (size_t) 2 * std::max(g_f16, g_q8) * (n_heads / n_kv_heads) * kPartialStride * sizeof(float);
 }
 
-// K/V described by tensor maps (a cache layer, or caller tensors); q/dst/lengths by pointers.
-// map_ks / map_vs are the scale planes of a q8_0 cache (null for f16).  `counters`: one zeroed int per
-// (stream, kv head) of the launch, owned by whoever owns the K/V (a cache layer, or the engine).
-int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUtensorMap & map_v, const CUtensorMap * map_ks,
-                  const CUtensorMap * map_vs, int layer, int max_len, int n_streams, int n_heads, int n_kv_heads,
+// K/V described by tensor maps (f16: a cache layer, or caller tensors) or, for q8_0, by the start of the layer's tiles
+// and the strides of a pair and a stream (a cache layer, or tiles built in the workspace); q/dst/lengths by pointers.
+// `counters`: one zeroed int per (stream, kv head) of the launch, owned by whoever owns the K/V (a cache layer, or the
+// engine).
+int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUtensorMap & map_v, const uint8_t * q8_tiles,
+                  size_t q8_nb_head, size_t q8_nb_stream, int layer, int max_len, int n_streams, int n_heads, int n_kv_heads,
                   const int32_t * kv_len, int kv_len_const, int kv_bound, const float * q, size_t q_nb_head,
                   size_t q_nb_stream, float * dst, float scale, void * workspace, size_t workspace_bytes, int * counters,
                   cudaStream_t stream, const vox_kv_cache * append_to, const float * k_new, const float * v_new,
@@ -1075,6 +1080,8 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     }
     p.rope  = reinterpret_cast<const float2 *>(rope_table);
     p.order = order;
+    p.q8_tiles = q8_tiles; p.q8_nb_head = q8_nb_head; p.q8_nb_stream = q8_nb_stream;
+    VOX_REQUIRE(!q8 || q8_tiles != nullptr, VOX_ATTN_INVALID_ARGUMENT, "decode: no q8_0 tiles");
     p.k_new = p.v_new = nullptr;
     p.new_nb_head = p.new_nb_stream = 0;
     p.k_rows = p.v_rows = p.k_scales = p.v_scales = nullptr;
@@ -1107,8 +1114,8 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     VOX_REQUIRE(workspace != nullptr && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 7) == 0,
                 VOX_ATTN_WORKSPACE_TOO_SMALL, "decode needs %zu workspace bytes (8-byte aligned), got %zu", need, workspace_bytes);
     p.partial = static_cast<float *>(workspace);
-    if (q8) launch_pdl(decode_kernel<true>, dim3(grid), dim3(kThreads), Ring<true>::kSmemBytes, stream, map_k, map_v, *map_ks, *map_vs, p);
-    else    launch_pdl(decode_kernel<false>, dim3(grid), dim3(kThreads), Ring<false>::kSmemBytes, stream, map_k, map_v, map_k, map_v, p);
+    if (q8) launch_pdl(decode_kernel<true>, dim3(grid), dim3(kThreads), Ring<true>::kSmemBytes, stream, map_k, map_v, p);
+    else    launch_pdl(decode_kernel<false>, dim3(grid), dim3(kThreads), Ring<false>::kSmemBytes, stream, map_k, map_v, p);
     return check_launch(e, q8 ? "decode_kernel<q8_0>" : "decode_kernel<f16>");
 }
 
@@ -1116,49 +1123,49 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
 int launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorMap & map_v, int n_kv, int n_streams,
                       int n_heads, int n_kv_heads, const float * q, size_t q_nb_head, size_t q_nb_stream, float * dst,
                       float scale, const vox_tensor * mask, void * workspace, size_t workspace_bytes, cudaStream_t stream) {
-    return launch_decode(e, false, map_k, map_v, nullptr, nullptr, 0, n_kv, n_streams, n_heads, n_kv_heads, nullptr, n_kv, n_kv, q,
+    return launch_decode(e, false, map_k, map_v, nullptr, 0, 0, 0, n_kv, n_streams, n_heads, n_kv_heads, nullptr, n_kv, n_kv, q,
                          q_nb_head, q_nb_stream, dst, scale, workspace, workspace_bytes, e->counters_dev, stream, nullptr, nullptr,
                          nullptr, 0, 0, false, nullptr, nullptr, mask);
 }
 
 // ---- single-token calls over q8_0 K/V in ggml's block layout (the operator called on a caller's own quantised
 // cache, third_party/ggml/src/ggml-common.h:221-224): the blocks are taken apart into the planes the q8_0 decode
-// kernel reads (int8 rows of 64 bytes, two f16 scales per row), in the workspace, and that kernel runs on them.
+// kernel reads (tiles of 64 rows: bytes and scales of K and V in one span, as the cache object keeps them), in the
+// workspace, and that kernel runs on them.
 // Nothing is re-quantised: the result is what the cache object gives for the same blocks.
 
 struct RepackParams {
     const uint8_t * src[2];
     size_t          nb1[2], nb2[2], nb3[2];
-    uint8_t *       rows[2];    // [B][HK][n_pad][64] int8
-    uint8_t *       scales[2];  // [B][HK][n_pad][2] f16
+    uint8_t *       tiles;  // [B][HK][n_pad / 64] tiles of kQ8TileBytes
     int             n_kv, n_pad, n_kvh, n_batch;
 };
-__global__ void __launch_bounds__(256) q8_0_blocks_to_planes_kernel(const RepackParams p) {
+__global__ void __launch_bounds__(256) q8_0_blocks_to_tiles_kernel(const RepackParams p) {
     const long long n_blocks = 2LL * p.n_pad * p.n_kvh * p.n_batch;
     const bool      is_v     = blockIdx.y != 0;
     const uint8_t * src      = is_v ? p.src[1] : p.src[0];
-    uint8_t *       rows     = is_v ? p.rows[1] : p.rows[0];
-    uint8_t *       scales   = is_v ? p.scales[1] : p.scales[0];
     const size_t    nb1 = is_v ? p.nb1[1] : p.nb1[0], nb2 = is_v ? p.nb2[1] : p.nb2[0], nb3 = is_v ? p.nb3[1] : p.nb3[0];
     for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks; i += (long long) gridDim.x * blockDim.x) {
         const int       blk = (int) (i & 1);
         const long long row = i >> 1;
         const int       pos = (int) (row % p.n_pad);
-        const int       kvh = (int) ((row / p.n_pad) % p.n_kvh);
-        const int       b   = (int) (row / ((long long) p.n_pad * p.n_kvh));
-        uint32_t        q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long pair = row / p.n_pad;  // (batch, kv head) flattened, kv head fastest
+        const int       kvh = (int) (pair % p.n_kvh);
+        const int       b   = (int) (pair / p.n_kvh);
+        uint32_t        q[8] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u};
         uint16_t        d    = 0;  // rows past n_kv (up to the next multiple of the tile) have a zero scale
         if (pos < p.n_kv) {
             const uint16_t * s = reinterpret_cast<const uint16_t *>(src + (size_t) pos * nb1 + (size_t) kvh * nb2 + (size_t) b * nb3 +
                                                                     (size_t) blk * 34);
             d = s[0];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = ((uint32_t) s[1 + 2 * j] | ((uint32_t) s[2 + 2 * j] << 16)) ^ 0x80808080u;  // q + 128, as the cache planes hold it
+            for (int j = 0; j < 8; ++j) q[j] = ((uint32_t) s[1 + 2 * j] | ((uint32_t) s[2 + 2 * j] << 16)) ^ 0x80808080u;  // q + 128, as the cache holds it
         }
-        uint4 * o = reinterpret_cast<uint4 *>(rows + (size_t) row * 64 + (size_t) blk * 32);
-        o[0] = make_uint4(q[0], q[1], q[2], q[3]);
-        o[1] = make_uint4(q[4], q[5], q[6], q[7]);
-        reinterpret_cast<uint16_t *>(scales)[row * 2 + blk] = d;
+        uint8_t * tile = p.tiles + (size_t) pair * (p.n_pad / kKvTile) * kQ8TileBytes + q8_tile_off(pos);
+        uint8_t * bytes = tile + (is_v ? kQ8VBytesOff : 0);
+        *reinterpret_cast<uint4 *>(bytes + q8_byte_off(pos, 32 * blk))      = make_uint4(q[0], q[1], q[2], q[3]);
+        *reinterpret_cast<uint4 *>(bytes + q8_byte_off(pos, 32 * blk + 16)) = make_uint4(q[4], q[5], q[6], q[7]);
+        *reinterpret_cast<uint16_t *>(tile + (is_v ? kQ8VScaleOff : kQ8KScaleOff) + q8_scale_off(pos, blk)) = d;
     }
 }
 
@@ -1172,8 +1179,7 @@ bool decode_mask_ok(const vox_attn_args * a) {
 static size_t q8_planes_bytes(const vox_attn_args * a, int * n_pad_out) {
     const int n_pad = (int) ((a->k.ne[1] + kKvTile - 1) / kKvTile * kKvTile);
     if (n_pad_out) *n_pad_out = n_pad;
-    const size_t rows = (size_t) n_pad * a->k.ne[2] * a->k.ne[3];
-    return 2 * (rows * 64 + rows * 4);  // K and V: int8 rows + scale pairs (both multiples of 256 bytes)
+    return (size_t) (n_pad / kKvTile) * a->k.ne[2] * a->k.ne[3] * kQ8TileBytes;  // K and V bytes and scales, tile by tile
 }
 
 bool decode_q8_blocks_route_ok(const vox_attn_args * a) {
@@ -1201,38 +1207,24 @@ int launch_decode_q8_blocks(vox_engine * e, const vox_attn_args * a, void * work
     VOX_REQUIRE(workspace != nullptr && workspace_bytes >= partials + planes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
                 VOX_ATTN_WORKSPACE_TOO_SMALL, "q8_0 decode needs %zu workspace bytes, got %zu", partials + planes, workspace_bytes);
     uint8_t *    base = static_cast<uint8_t *>(workspace) + partials;
-    const size_t rows = (size_t) n_pad * HK * B;
     RepackParams rp;
     const vox_tensor * ts[2] = {&a->k, &a->v};
     for (int i = 0; i < 2; ++i) {
         rp.src[i] = static_cast<const uint8_t *>(ts[i]->data);
         rp.nb1[i] = ts[i]->nb[1]; rp.nb2[i] = ts[i]->nb[2]; rp.nb3[i] = ts[i]->nb[3];
-        rp.rows[i]   = base + i * rows * 64;
-        rp.scales[i] = base + 2 * rows * 64 + i * rows * 4;
     }
+    rp.tiles = base;
     rp.n_kv = n_kv; rp.n_pad = n_pad; rp.n_kvh = HK; rp.n_batch = B;
-    const long long n_blocks = 2LL * (long long) rows;
+    const long long n_blocks = 2LL * n_pad * HK * B;
     const unsigned  gx = (unsigned) std::min<long long>((n_blocks + 255) / 256, 8LL * e->sm_count);
-    q8_0_blocks_to_planes_kernel<<<dim3(gx, 2), 256, 0, st>>>(rp);
-    int rc = check_launch(e, "q8_0_blocks_to_planes_kernel");
+    q8_0_blocks_to_tiles_kernel<<<dim3(gx, 2), 256, 0, st>>>(rp);
+    int rc = check_launch(e, "q8_0_blocks_to_tiles_kernel");
     if (rc != VOX_ATTN_OK) return rc;
-    // the planes described as one cache layer of n_pad rows (the same descriptors vox_kv_create builds)
-    CUtensorMap    mk, mv, mks, mvs;
-    const uint64_t dims[5]     = {64, (uint64_t) n_pad, (uint64_t) HK, (uint64_t) B, 1};
-    const uint64_t strides[4]  = {64, (uint64_t) 64 * n_pad, (uint64_t) 64 * n_pad * HK, (uint64_t) 64 * n_pad * HK * B};
-    const uint32_t box[5]      = {64, kKvTile, 1, 1, 1};
-    const uint64_t sdims[5]    = {(uint64_t) n_pad * 2, 1, (uint64_t) HK, (uint64_t) B, 1};
-    const uint64_t sstrides[4] = {(uint64_t) 4 * n_pad, (uint64_t) 4 * n_pad, (uint64_t) 4 * n_pad * HK, (uint64_t) 4 * n_pad * HK * B};
-    const uint32_t sbox[5]     = {2 * kKvTile, 1, 1, 1, 1};
-    CUtensorMap * ms[2] = {&mk, &mv};
-    CUtensorMap * ss[2] = {&mks, &mvs};
-    for (int i = 0; i < 2; ++i) {
-        rc = make_tensor_map(e, ms[i], rp.rows[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
-        if (rc == VOX_ATTN_OK)
-            rc = make_tensor_map(e, ss[i], rp.scales[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, sdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
-        if (rc != VOX_ATTN_OK) return rc;
-    }
-    return launch_decode(e, true, mk, mv, &mks, &mvs, 0, n_pad, B, (int) a->q.ne[2], HK, nullptr, n_kv, n_kv,
+    // the tiles as one cache layer of n_pad rows
+    CUtensorMap  none;
+    memset(&none, 0, sizeof(none));
+    const size_t pair_bytes = (size_t) (n_pad / kKvTile) * kQ8TileBytes;
+    return launch_decode(e, true, none, none, base, pair_bytes, pair_bytes * HK, 0, n_pad, B, (int) a->q.ne[2], HK, nullptr, n_kv, n_kv,
                          static_cast<const float *>(a->q.data), a->q.nb[2], a->q.nb[3], static_cast<float *>(a->dst.data), a->scale,
                          workspace, partials, e->counters_dev, st, nullptr, nullptr, nullptr, 0, 0, false, nullptr, nullptr,
                          a->mask.data ? &a->mask : nullptr);
@@ -1274,7 +1266,9 @@ int decode_checked(vox_engine * e, const vox_decode_args * a, void * workspace, 
     const vox_kv_cache * c       = a->cache;
     const bool           appends = a->k_new != nullptr;
     int * counters = c->counters + (size_t) a->layer * c->cfg.n_streams * c->cfg.n_kv_heads;
-    return launch_decode(e, c->cfg.type == VOX_TYPE_Q8_0, c->map_k, c->map_v, &c->map_ks, &c->map_vs, a->layer, c->cfg.max_len,
+    const bool q8 = c->cfg.type == VOX_TYPE_Q8_0;
+    return launch_decode(e, q8, c->map_k, c->map_v, q8 ? c->k_data + (size_t) a->layer * c->nb_layer : nullptr, c->nb_head, c->nb_stream,
+                         a->layer, c->cfg.max_len,
                          a->n_streams, a->n_heads, c->cfg.n_kv_heads, a->kv_len, 0, a->kv_bound, a->q, a->q_nb_head, a->q_nb_stream,
                          a->dst, a->scale, workspace, workspace_bytes, counters, static_cast<cudaStream_t>(stream),
                          appends ? c : nullptr, a->k_new, a->v_new, a->new_nb_head, a->new_nb_stream,

@@ -27,20 +27,16 @@ struct CacheView {
 
 __device__ __forceinline__ void write_row(const CacheView & c, uint8_t * data, uint8_t * scale, int layer, int stream,
                                           int head, int pos, float x0, float x1, int lane) {
-    const size_t off = (size_t) layer * c.nb_layer + (size_t) stream * c.nb_stream + (size_t) head * c.nb_head +
-                       (size_t) pos * c.nb_pos;
+    const size_t pair = (size_t) layer * c.nb_layer + (size_t) stream * c.nb_stream + (size_t) head * c.nb_head;
     if (c.type == VOX_TYPE_F16) {
-        *reinterpret_cast<__half2 *>(data + off + lane * 4) = __floats2half2_rn(x0, x1);
+        *reinterpret_cast<__half2 *>(data + pair + (size_t) pos * c.nb_pos + lane * 4) = __floats2half2_rn(x0, x1);
     } else {
         char2 q;
         float d;
         q8_0_quantize_pair(x0, x1, q, d);
-        *reinterpret_cast<uchar2 *>(data + off + lane * 2) = q8_0_biased(q);
-        if ((lane & 15) == 0) {
-            const size_t soff = (size_t) layer * c.sb_layer + (size_t) stream * c.sb_stream + (size_t) head * c.sb_head +
-                                (size_t) pos * c.sb_pos;
-            *reinterpret_cast<__half *>(scale + soff + (lane >> 4) * 2) = __float2half_rn(d);
-        }
+        const size_t tile = pair + q8_tile_off(pos);
+        *reinterpret_cast<uchar2 *>(data + tile + q8_byte_off(pos, 2 * lane)) = q8_0_biased(q);
+        if ((lane & 15) == 0) *reinterpret_cast<__half *>(scale + tile + q8_scale_off(pos, lane >> 4)) = __float2half_rn(d);
     }
 }
 
@@ -137,20 +133,21 @@ int vox_kv_create(vox_engine * e, const vox_kv_config * cfg, vox_kv_cache ** out
     c->e   = e;
     c->cfg = *cfg;
     const bool q8 = cfg->type == VOX_TYPE_Q8_0;
-    c->nb_pos    = q8 ? 64 : 128;
-    c->nb_head   = c->nb_pos * cfg->max_len;
-    c->nb_stream = c->nb_head * cfg->n_kv_heads;
-    c->nb_layer  = c->nb_stream * cfg->n_streams;
-    const size_t plane = c->nb_layer * cfg->n_layers;
-    size_t splane = 0;
-    if (q8) {
-        c->sb_pos    = 4;
-        c->sb_head   = c->sb_pos * cfg->max_len;
-        c->sb_stream = c->sb_head * cfg->n_kv_heads;
-        c->sb_layer  = c->sb_stream * cfg->n_streams;
-        splane       = c->sb_layer * cfg->n_layers;
+    if (!q8) {
+        c->nb_pos    = 128;
+        c->nb_head   = c->nb_pos * cfg->max_len;
+        c->nb_stream = c->nb_head * cfg->n_kv_heads;
+        c->nb_layer  = c->nb_stream * cfg->n_streams;
+        c->bytes     = 2 * c->nb_layer * cfg->n_layers;
+    } else {
+        const size_t tiles = ((size_t) cfg->max_len + kKvTile - 1) / kKvTile;
+        c->nb_pos    = 0;
+        c->nb_head   = tiles * kQ8TileBytes;
+        c->nb_stream = c->nb_head * cfg->n_kv_heads;
+        c->nb_layer  = c->nb_stream * cfg->n_streams;
+        c->sb_pos = 0; c->sb_head = c->nb_head; c->sb_stream = c->nb_stream; c->sb_layer = c->nb_layer;
+        c->bytes     = c->nb_layer * cfg->n_layers;
     }
-    c->bytes = 2 * (plane + splane);
     uint8_t * base = nullptr;
     cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&base), c->bytes);
     if (err != cudaSuccess) {
@@ -160,41 +157,34 @@ int vox_kv_create(vox_engine * e, const vox_kv_config * cfg, vox_kv_cache ** out
         return VOX_ATTN_OUT_OF_MEMORY;
     }
     c->k_data = base;
-    c->v_data = base + plane;
-    if (q8) {
-        c->k_scale = base + 2 * plane;
-        c->v_scale = base + 2 * plane + splane;
+    if (!q8) {
+        c->v_data = base + c->bytes / 2;
+    } else {
+        c->v_data  = base + kQ8VBytesOff;
+        c->k_scale = base + kQ8KScaleOff;
+        c->v_scale = base + kQ8VScaleOff;
     }
-    // MiniCPMKVCache::init ends with clear(): every stored value is zero (a q8_0 byte plane holds q + 128)
+    // MiniCPMKVCache::init ends with clear(): every stored value is zero (a q8_0 byte holds q + 128)
     err = cudaMemset(base, 0, c->bytes);
-    if (err == cudaSuccess && q8) err = cudaMemset(base, 0x80, 2 * plane);
+    if (err == cudaSuccess && q8)  // the byte blocks of every tile
+        err = cudaMemset2D(base, kQ8TileBytes, 0x80, kQ8KScaleOff, c->bytes / kQ8TileBytes);
     if (err == cudaSuccess) {
         const size_t n_ctr = (size_t) cfg->n_layers * cfg->n_streams * cfg->n_kv_heads;
         err = cudaMalloc(reinterpret_cast<void **>(&c->counters), sizeof(int) * n_ctr);
         if (err == cudaSuccess) err = cudaMemset(c->counters, 0, sizeof(int) * n_ctr);
     }
     int rc = err == cudaSuccess ? VOX_ATTN_OK : VOX_ATTN_CUDA_ERROR;
-    if (rc == VOX_ATTN_OK) {
+    if (rc == VOX_ATTN_OK && !q8) {
         const uint64_t dims[5]    = {64, (uint64_t) cfg->max_len, (uint64_t) cfg->n_kv_heads, (uint64_t) cfg->n_streams,
                                      (uint64_t) cfg->n_layers};
         const uint64_t strides[4] = {c->nb_pos, c->nb_head, c->nb_stream, c->nb_layer};
         const uint32_t box[5]     = {64, kKvTile, 1, 1, 1};
-        const CUtensorMapDataType dt = q8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-        const CUtensorMapSwizzle  sw = q8 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
-        rc = make_tensor_map(e, &c->map_k, c->k_data, dt, dims, strides, box, sw);
-        if (rc == VOX_ATTN_OK) rc = make_tensor_map(e, &c->map_v, c->v_data, dt, dims, strides, box, sw);
-        if (rc == VOX_ATTN_OK && q8) {
-            // scale plane of one head viewed as a flat run of 2*max_len halves
-            const uint64_t sdims[5]    = {(uint64_t) cfg->max_len * 2, 1, (uint64_t) cfg->n_kv_heads,
-                                          (uint64_t) cfg->n_streams, (uint64_t) cfg->n_layers};
-            const uint64_t sstrides[4] = {c->sb_head, c->sb_head, c->sb_stream, c->sb_layer};
-            const uint32_t sbox[5]     = {2 * kKvTile, 1, 1, 1, 1};
-            rc = make_tensor_map(e, &c->map_ks, c->k_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, sdims, sstrides, sbox,
-                                 CU_TENSOR_MAP_SWIZZLE_NONE);
-            if (rc == VOX_ATTN_OK)
-                rc = make_tensor_map(e, &c->map_vs, c->v_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, sdims, sstrides, sbox,
-                                     CU_TENSOR_MAP_SWIZZLE_NONE);
-        }
+        rc = make_tensor_map(e, &c->map_k, c->k_data, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc == VOX_ATTN_OK)
+            rc = make_tensor_map(e, &c->map_v, c->v_data, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    } else if (rc == VOX_ATTN_OK) {
+        memset(&c->map_k, 0, sizeof(c->map_k));
+        memset(&c->map_v, 0, sizeof(c->map_v));
     } else {
         set_error("clearing the KV cache or allocating its ticket counters failed: %s", cudaGetErrorString(err));
     }
@@ -227,21 +217,17 @@ int vox_kv_clear(vox_kv_cache * c, int stream_id, void * stream) {
     VOX_REQUIRE(stream_id >= -1 && stream_id < c->cfg.n_streams, VOX_ATTN_INVALID_ARGUMENT, "stream_id %d out of range",
                 stream_id);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int zero = c->cfg.type == VOX_TYPE_Q8_0 ? 0x80 : 0;  // a q8_0 byte plane holds q + 128
+    const bool q8 = c->cfg.type == VOX_TYPE_Q8_0;  // a q8_0 byte holds q + 128: zero is 0x80 there, and 0 in the scales
     if (stream_id < 0) {
         VOX_CUDA_TRY(cudaMemsetAsync(c->k_data, 0, c->bytes, st));
-        if (zero) VOX_CUDA_TRY(cudaMemsetAsync(c->k_data, zero, 2 * c->nb_layer * c->cfg.n_layers, st));
+        if (q8) VOX_CUDA_TRY(cudaMemset2DAsync(c->k_data, kQ8TileBytes, 0x80, kQ8KScaleOff, c->bytes / kQ8TileBytes, st));
         return VOX_ATTN_OK;
     }
     for (int l = 0; l < c->cfg.n_layers; ++l) {
         const size_t off = (size_t) l * c->nb_layer + (size_t) stream_id * c->nb_stream;
-        VOX_CUDA_TRY(cudaMemsetAsync(c->k_data + off, zero, c->nb_stream, st));
-        VOX_CUDA_TRY(cudaMemsetAsync(c->v_data + off, zero, c->nb_stream, st));
-        if (c->k_scale) {
-            const size_t soff = (size_t) l * c->sb_layer + (size_t) stream_id * c->sb_stream;
-            VOX_CUDA_TRY(cudaMemsetAsync(c->k_scale + soff, 0, c->sb_stream, st));
-            VOX_CUDA_TRY(cudaMemsetAsync(c->v_scale + soff, 0, c->sb_stream, st));
-        }
+        VOX_CUDA_TRY(cudaMemsetAsync(c->k_data + off, 0, c->nb_stream, st));
+        if (q8) VOX_CUDA_TRY(cudaMemset2DAsync(c->k_data + off, kQ8TileBytes, 0x80, kQ8KScaleOff, c->nb_stream / kQ8TileBytes, st));
+        else    VOX_CUDA_TRY(cudaMemsetAsync(c->v_data + off, 0, c->nb_stream, st));
     }
     return VOX_ATTN_OK;
 }
@@ -271,7 +257,7 @@ int vox_kv_view(const vox_kv_cache * c, int layer, int stream_id, int seq_len, v
                 VOX_ATTN_INVALID_ARGUMENT, "layer/stream out of range");
     VOX_REQUIRE(seq_len >= 0 && seq_len <= c->cfg.max_len, VOX_ATTN_INVALID_ARGUMENT, "seq_len %d out of range", seq_len);
     VOX_REQUIRE(c->cfg.type == VOX_TYPE_F16, VOX_ATTN_UNSUPPORTED,
-                "a q8_0 cache is stored as separate int8 and scale planes and has no ggml tensor view");
+                "a q8_0 cache is stored as tiles of bytes and scales and has no ggml tensor view");
     const size_t off = (size_t) layer * c->nb_layer + (size_t) stream_id * c->nb_stream;
     vox_tensor * ts[2]   = {k, v};
     uint8_t *    base[2] = {c->k_data, c->v_data};
@@ -294,41 +280,44 @@ static int kv_transfer(const vox_kv_cache * c, int layer, int stream_id, int n_p
     const int  HK = c->cfg.n_kv_heads;
     const bool q8 = c->cfg.type == VOX_TYPE_Q8_0;
     uint8_t *  hosts[2]  = {static_cast<uint8_t *>(k_host), static_cast<uint8_t *>(v_host)};
-    uint8_t *  datas[2]  = {c->k_data, c->v_data};
-    uint8_t *  scales[2] = {c->k_scale, c->v_scale};
-    std::vector<uint8_t> qbuf, sbuf;
-    if (q8) { qbuf.resize((size_t) n_pos * 64); sbuf.resize((size_t) n_pos * 4); }
-    for (int t = 0; t < 2; ++t) {
-        for (int h = 0; h < HK; ++h) {
-            uint8_t * dev = datas[t] + (size_t) layer * c->nb_layer + (size_t) stream_id * c->nb_stream + (size_t) h * c->nb_head;
-            if (!q8) {
-                uint8_t * hp = hosts[t] + (size_t) h * n_pos * 128;
+    if (!q8) {
+        uint8_t * datas[2] = {c->k_data, c->v_data};
+        for (int t = 0; t < 2; ++t)
+            for (int h = 0; h < HK; ++h) {
+                uint8_t * dev = datas[t] + (size_t) layer * c->nb_layer + (size_t) stream_id * c->nb_stream + (size_t) h * c->nb_head;
+                uint8_t * hp  = hosts[t] + (size_t) h * n_pos * 128;
                 if (to_host) VOX_CUDA_TRY(cudaMemcpy(hp, dev, (size_t) n_pos * 128, cudaMemcpyDeviceToHost));
                 else         VOX_CUDA_TRY(cudaMemcpy(dev, hp, (size_t) n_pos * 128, cudaMemcpyHostToDevice));
-                continue;
             }
-            uint8_t * sdev = scales[t] + (size_t) layer * c->sb_layer + (size_t) stream_id * c->sb_stream + (size_t) h * c->sb_head;
-            uint8_t * hp   = hosts[t] + (size_t) h * n_pos * 68;  // two block_q8_0 per row
-            if (to_host) {
-                VOX_CUDA_TRY(cudaMemcpy(qbuf.data(), dev, qbuf.size(), cudaMemcpyDeviceToHost));
-                VOX_CUDA_TRY(cudaMemcpy(sbuf.data(), sdev, sbuf.size(), cudaMemcpyDeviceToHost));
-                for (auto & b : qbuf) b ^= 0x80;  // the plane holds q + 128
-                for (int p = 0; p < n_pos; ++p)
-                    for (int b = 0; b < 2; ++b) {
-                        memcpy(hp + (size_t) p * 68 + b * 34, sbuf.data() + (size_t) p * 4 + b * 2, 2);
-                        memcpy(hp + (size_t) p * 68 + b * 34 + 2, qbuf.data() + (size_t) p * 64 + b * 32, 32);
+        return VOX_ATTN_OK;
+    }
+    // q8_0: the tiles that hold rows [0, n_pos) of a pair come to the host as they are; rows are taken out of them, or
+    // put into them and the tiles sent back (rows past n_pos in the last tile keep what they held).  Host side: two
+    // block_q8_0 per row (34 bytes each: f16 scale, 32 signed bytes).
+    const size_t         span = (size_t) ((n_pos + kKvTile - 1) / kKvTile) * kQ8TileBytes;
+    std::vector<uint8_t> tiles(span);
+    const uint32_t       byte_block[2] = {0, (uint32_t) kQ8VBytesOff}, scale_block[2] = {(uint32_t) kQ8KScaleOff, (uint32_t) kQ8VScaleOff};
+    for (int h = 0; h < HK && span > 0; ++h) {
+        uint8_t * dev = c->k_data + (size_t) layer * c->nb_layer + (size_t) stream_id * c->nb_stream + (size_t) h * c->nb_head;
+        VOX_CUDA_TRY(cudaMemcpy(tiles.data(), dev, span, cudaMemcpyDeviceToHost));
+        for (int t = 0; t < 2; ++t) {
+            uint8_t * hp = hosts[t] + (size_t) h * n_pos * 68;
+            for (int p = 0; p < n_pos; ++p) {
+                uint8_t * tile = tiles.data() + q8_tile_off(p);
+                for (int b = 0; b < 2; ++b) {
+                    uint8_t * blk = hp + (size_t) p * 68 + b * 34;
+                    uint8_t * sc  = tile + scale_block[t] + q8_scale_off(p, b);
+                    if (to_host) memcpy(blk, sc, 2);
+                    else         memcpy(sc, blk, 2);
+                    for (int i = 0; i < 32; ++i) {
+                        uint8_t * q = tile + byte_block[t] + q8_byte_off(p, 32 * b + i);
+                        if (to_host) blk[2 + i] = (uint8_t) (*q ^ 0x80);  // the cache holds q + 128
+                        else         *q = (uint8_t) (blk[2 + i] ^ 0x80);
                     }
-            } else {
-                for (int p = 0; p < n_pos; ++p)
-                    for (int b = 0; b < 2; ++b) {
-                        memcpy(sbuf.data() + (size_t) p * 4 + b * 2, hp + (size_t) p * 68 + b * 34, 2);
-                        memcpy(qbuf.data() + (size_t) p * 64 + b * 32, hp + (size_t) p * 68 + b * 34 + 2, 32);
-                    }
-                for (auto & b : qbuf) b ^= 0x80;  // the plane holds q + 128
-                VOX_CUDA_TRY(cudaMemcpy(dev, qbuf.data(), qbuf.size(), cudaMemcpyHostToDevice));
-                VOX_CUDA_TRY(cudaMemcpy(sdev, sbuf.data(), sbuf.size(), cudaMemcpyHostToDevice));
+                }
             }
         }
+        if (!to_host) VOX_CUDA_TRY(cudaMemcpy(dev, tiles.data(), span, cudaMemcpyHostToDevice));
     }
     return VOX_ATTN_OK;
 }

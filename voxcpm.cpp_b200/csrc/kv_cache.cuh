@@ -3,16 +3,34 @@
 
 #include "common.cuh"
 
-constexpr int kKvTile = 64;  // cache rows moved per bulk-tensor copy
+constexpr int kKvTile = 64;  // cache rows moved per bulk copy
+
+// A q8_0 cache keeps every 64-row tile of a (layer, stream, kv head) as ONE contiguous span, laid out exactly as the decode
+// kernel wants it in shared memory, so that a tile is one bulk copy (cp.async.bulk) instead of four bulk-tensor copies:
+//   [K bytes: 64 rows x 64, each byte q + 128][V bytes likewise][K scales: 64 rows x 2 halves][V scales]
+// Inside a byte block the 16-byte pieces of row r sit at piece index (d / 16) ^ ((r / 2) % 4): the 64-byte swizzle the
+// kernel's shared-memory reads are written for (what a bulk-tensor copy with CU_TENSOR_MAP_SWIZZLE_64B would produce).
+constexpr int kQ8TileBytes = 2 * kKvTile * 64 + 2 * kKvTile * 4;  // 8704
+constexpr int kQ8VBytesOff = kKvTile * 64, kQ8KScaleOff = 2 * kKvTile * 64, kQ8VScaleOff = 2 * kKvTile * 64 + kKvTile * 4;
+// where row `pos` of a pair starts its tile, and where value d / scale b of that row lie inside the tile's byte / scale block
+__host__ __device__ inline size_t   q8_tile_off(int pos) { return (size_t) (pos >> 6) * kQ8TileBytes; }
+__host__ __device__ inline uint32_t q8_byte_off(int pos, int d) {
+    const int r = pos & 63;
+    return (uint32_t) (r * 64 + ((((d >> 4) ^ ((r >> 1) & 3)) << 4) | (d & 15)));
+}
+__host__ __device__ inline uint32_t q8_scale_off(int pos, int b) { return (uint32_t) ((pos & 63) * 4 + b * 2); }
 
 struct vox_kv_cache {
     vox_engine *  e = nullptr;
     vox_kv_config cfg{};
-    // data planes: f16 rows (128 B) or int8 rows (64 B, each byte q + 128); [layer][stream][kv_head][pos][64]
+    // f16: two planes of 128-byte rows, [layer][stream][kv_head][pos][64], nb_* the strides in bytes.
+    // q8_0: one run of tiles (see kQ8TileBytes), [layer][stream][kv_head][tile]: k_data is its start, v_data / k_scale /
+    // v_scale point at the V bytes / K scales / V scales of the first tile, nb_head / nb_stream / nb_layer (and sb_*,
+    // the same) are the strides of a pair / stream / layer, nb_pos is unused: a row's bytes lie at
+    // pair + q8_tile_off(pos) + q8_byte_off(pos, d), its scales at pair + q8_tile_off(pos) + q8_scale_off(pos, b).
     uint8_t * k_data = nullptr;
     uint8_t * v_data = nullptr;
     size_t    nb_pos = 0, nb_head = 0, nb_stream = 0, nb_layer = 0;
-    // q8_0 only, scale planes: two halves per row; [layer][stream][kv_head][pos][2]
     uint8_t * k_scale = nullptr;
     uint8_t * v_scale = nullptr;
     size_t    sb_pos = 0, sb_head = 0, sb_stream = 0, sb_layer = 0;
@@ -20,9 +38,8 @@ struct vox_kv_cache {
     // split-KV arrival tickets of the decode launches on this cache: one int per (layer, stream, kv head), zero
     // between launches.  They belong to the cache so that launches on different caches (or layers) never share one.
     int *     counters = nullptr;
-    // bulk-tensor descriptors, box = kKvTile rows
-    CUtensorMap map_k, map_v;    // data planes, 5-D (64, pos, head, stream, layer)
-    CUtensorMap map_ks, map_vs;  // scale planes, 5-D (2*pos halves, 1, head, stream, layer)
+    // f16 only: bulk-tensor descriptors of the planes, 5-D (64, pos, head, stream, layer), box = kKvTile rows
+    CUtensorMap map_k, map_v;
 };
 
 namespace vox {

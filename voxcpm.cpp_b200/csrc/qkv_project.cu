@@ -76,15 +76,18 @@ __global__ void __launch_bounds__(256) f32_to_f16_rows_kernel(const uint8_t * x,
 // one cache row (64 values held by one thread) in the cache's type
 __device__ __forceinline__ void store_cache_row(const QkvParams & p, uint8_t * rows, uint8_t * scales, int stream, int kvh, int pos,
                                                 const float (&x)[64]) {
-    uint8_t * dst = rows + (size_t) stream * p.nb_stream + (size_t) kvh * p.nb_head + (size_t) pos * p.nb_pos;
+    uint8_t * pair = rows + (size_t) stream * p.nb_stream + (size_t) kvh * p.nb_head;
     if (p.cache_type == VOX_TYPE_F16) {
+        uint8_t * dst = pair + (size_t) pos * p.nb_pos;
 #pragma unroll
         for (int c = 0; c < 8; ++c)
             *reinterpret_cast<uint4 *>(dst + 16 * c) = make_uint4(pack_half2(x[8 * c], x[8 * c + 1]), pack_half2(x[8 * c + 2], x[8 * c + 3]),
                                                                    pack_half2(x[8 * c + 4], x[8 * c + 5]), pack_half2(x[8 * c + 6], x[8 * c + 7]));
     } else {
-        // quantize_row_q8_0_ref (third_party/ggml/src/ggml-quants.c:199-222) on each 32-value block; bytes stored as q + 128
-        uint8_t * sdst = scales + (size_t) stream * p.sb_stream + (size_t) kvh * p.sb_head + (size_t) pos * p.sb_pos;
+        // quantize_row_q8_0_ref (third_party/ggml/src/ggml-quants.c:199-222) on each 32-value block; bytes stored as q + 128,
+        // in the row's place inside its tile of the cache (16-byte pieces, swizzled: q8_byte_off)
+        uint8_t * dst  = pair + q8_tile_off(pos);
+        uint8_t * sdst = scales + (size_t) stream * p.sb_stream + (size_t) kvh * p.sb_head + q8_tile_off(pos) + q8_scale_off(pos, 0);
         __half    d2[2];
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
@@ -107,7 +110,7 @@ __device__ __forceinline__ void store_cache_row(const QkvParams & p, uint8_t * r
                     }
                     wds[j] = word;
                 }
-                *reinterpret_cast<uint4 *>(dst + 32 * b + 16 * c) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                *reinterpret_cast<uint4 *>(dst + q8_byte_off(pos, 32 * b + 16 * c)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
             }
         }
         *reinterpret_cast<__half2 *>(sdst) = __halves2half2(d2[0], d2[1]);
