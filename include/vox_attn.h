@@ -112,7 +112,7 @@ size_t vox_attn_workspace_bytes(const vox_attn_args * a);
 
 /* Replaces ggml_cuda_flash_attn_ext (fattn.cu:460-478) / ggml_compute_forward_flash_attn_ext
  * (third_party/ggml/src/ggml-cpu/ops.cpp:8838-8853).  Routes by shape: n_q==1 with f16 K/V, or
- * q8_0 K/V and the workspace vox_attn_workspace_bytes names (the blocks are taken apart into planes
+ * q8_0 K/V and the workspace vox_attn_workspace_bytes names (the blocks are taken apart into tiles
  * there) -> split-KV decode kernel; 32 or more keys with a mask (the
  * reference's prefill call, src/minicpm.cpp:708-710, with the tensor create_causal_mask built, or
  * any other additive f16 mask whose rows start on 16-byte boundaries, n_kv a multiple of 8) ->
@@ -142,9 +142,10 @@ size_t vox_attn_prefill_workspace_bytes(const vox_attn_args * a);
 /* Replaces MiniCPMKVCache (src/minicpm.cpp:144-271).  Storage is f16 or q8_0 instead of the
  * reference's F32 and holds many independent streams:
  *   f16 : K and V as [layer][stream][kv_head][pos][64] halves
- *   q8_0: K and V each as an int8 plane [layer][stream][kv_head][pos][64] plus a scale plane
- *         [layer][stream][kv_head][pos][2] halves — the values of block_q8_0, re-packed so
- *         that rows are 16-byte aligned for bulk copies.                                   */
+ *   q8_0: [layer][stream][kv_head][tile], a tile = 64 rows in one span of 8704 bytes: the bytes
+ *         of K (each q + 128), the bytes of V, two f16 scales per row of K, then of V — the
+ *         values of block_q8_0, laid out so that the decode kernel fetches a tile with one
+ *         bulk copy; vox_kv_export / vox_kv_import speak the reference's 34-byte blocks.      */
 typedef struct {
     int32_t n_layers, n_streams, n_kv_heads, head_dim /* 64 */, max_len, type /* F16 | Q8_0 */;
 } vox_kv_config;
