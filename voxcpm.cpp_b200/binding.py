@@ -7,6 +7,7 @@ here computes attention.  Tensors are described the way the reference describes 
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 import os
 import re
 
@@ -229,9 +230,12 @@ class Engine:
         self.h = h
         self.device = device
         self._ws = None
+        self._children = weakref.WeakSet()  # caches and groups created from this engine: they go before it does
 
     def close(self):
         if self.h:
+            for child in list(self._children):
+                child.close()
             lib().vox_engine_destroy(self.h)
             self.h = None
 
@@ -371,11 +375,12 @@ class KVCache:
             h = C.c_void_p()
             _check(lib().vox_kv_create(engine.h, C.byref(self.cfg), C.byref(h)))
             self.h = h
+            engine._children.add(self)
         else:
             self.h = C.c_void_p(handle)
 
     def close(self):
-        if self.h and self.owned:
+        if self.h and self.owned and self.engine.h:  # a cache never outlives its engine (Engine.close closes it first)
             lib().vox_kv_destroy(self.h)
         self.h = None
 
@@ -477,11 +482,12 @@ class Group:
         h = C.c_void_p()
         _check(lib().vox_group_create(engine.h, C.byref(self.cfg), C.byref(h)))
         self.h = h
+        engine._children.add(self)
 
     def close(self):
-        if self.h:
+        if self.h and self.engine.h:  # a group never outlives its engine (Engine.close closes it first)
             lib().vox_group_destroy(self.h)
-            self.h = None
+        self.h = None
 
     def __del__(self):
         try:
