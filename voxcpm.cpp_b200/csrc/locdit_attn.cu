@@ -19,7 +19,9 @@
 // cp.async into a second buffer while the current group is computed, so with many streams the
 // kernel streams Q/K/V from HBM, and with one stream it is a single short launch per timestep.
 // (Three and four buffers per CTA, i.e. two or three groups on their way, were measured: 80 and 118 us
-// per 256-stream launch against 71 us with two, because fewer CTAs then fit an SM.)
+// per 256-stream launch against 71 us with two, because fewer CTAs then fit an SM.  One buffer per CTA,
+// only the warps that have rows and six CTAs per SM, meant for launches of few groups: 13.9 against 14.3
+// us at 32 streams, 84 against 71 us at 256: not kept.)
 #include "common.cuh"
 
 #include <algorithm>
