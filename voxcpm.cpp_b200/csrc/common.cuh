@@ -66,6 +66,7 @@ struct vox_engine {
     // developer settings, read from the environment once, when the engine is created
     int               decode_early_tiles = -1;  // VOX_DECODE_EARLY: tiles a decode CTA requests before its dependency wait (-1: a full ring)
     int               linear_split = 0;         // VOX_LINEAR_SPLIT: CTAs along K of a vox_linear launch (0: chosen by shape)
+    int               decode_cluster = 1;       // VOX_DECODE_CLUSTER=0: no cluster mode in decode launches of few pairs
     int               decode_wave[2] = {0, 0};  // VOX_DECODE_WAVE / VOX_DECODE_WAVE_Q8: CTAs per SM of a decode grid (0: all that fit)
     int               prefill_single_f16 = 0;   // VOX_PREFILL_WEIGHTS=f16: softmax weights as one f16 (comparison only)
     std::vector<vox_kv_cache *> caches;         // caches created from this engine (their ticket counters are reset after a failure)

@@ -90,6 +90,10 @@ struct DecodeParams {
     // programmatic-dependency wait, while that kernel is still draining.
     int             early;
     int             early_tiles;  // tiles of a run requested before the dependency wait (at most the ring's depth)
+    // Cluster mode (cluster > 0): the grid is one thread-block cluster of `cluster` CTAs per pair; the CTAs of a cluster
+    // split the pair's tiles among them and hand their partial results to the first CTA through distributed shared
+    // memory.  The ring then has n_stages stages and the memory of the rest holds the partials.
+    int             cluster, n_stages;
     // Non-null: [stream][32] (cos, sin) pairs; Q and the arriving K row are rotated as they are read
     // (element i with element i + 32: the reference's ggml_rope_ext, GGML_ROPE_TYPE_NEOX).
     const float2 *  rope;
@@ -152,6 +156,7 @@ __device__ __forceinline__ void walk_next_pair(const DecodeParams & p, Walk & w)
 // Returns the number of tiles of this CTA (0: nothing to do) and where they start (w).  For the bookkeeping of cut
 // pairs: flat cut -> aligned = false, run, f0; aligned cut -> aligned = true and part b0 .. b1 = the CTAs of this
 // CTA's pair.
+constexpr int kClusterMaxRun = 24;  // cluster mode: longest part of a pair, in tiles, that the bound may lead to
 constexpr int kAlignedMaxRun = 64;  // beyond this a second Q load, merge and fold are small against the run itself
 struct Cut {
     int  n_tiles, run, f0, b0, b1;
@@ -349,6 +354,37 @@ __device__ __forceinline__ void store_arriving_row(float2 kk, float2 vv, uint8_t
     __syncwarp();
 }
 
+// Cluster mode: distributed shared memory.  The address of `addr` (of this CTA's shared memory) in the CTA of rank
+// `rank`, stores to such an address, an arrival on a barrier of that CTA that publishes this thread's (and, after a
+// CTA barrier, its CTA's) earlier stores, and the bounded wait that goes with it.
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void dsmem_st2(uint32_t addr, float a, float b) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void dsmem_arrive(uint32_t bar) {
+    asm volatile("fence.acq_rel.cluster;" ::: "memory");
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((i & 15u) == 0 && clock64() - t0 > kWaitCycles) return false;
+    }
+}
+
 // The fold of NP pairs at once by one thread (head hh of each pair, output columns d0 .. d0+3): the partials of a pair
 // (runs b0 .. b1 of the launch; the run that holds the pair's first tile wrote its slot 1, the others their slot 0) are
 // read W at a time, the loads of a batch issued together (each is a round trip to L2, and a pair may have been cut 17
@@ -414,6 +450,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     constexpr int kStages = R::kStages;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * kStages];
+    __shared__ uint64_t xbar;  // cluster mode, first CTA of a cluster: the CTAs of the pair have delivered their partials
     __shared__ int      abort_flag;
     __shared__ int      fold_flag;
     // pairs this run holds a part of (at most two: one that began in an earlier run, one that goes on in a later
@@ -446,6 +483,53 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
         }
     }
+    const int n_stages = kStages == 4 ? p.n_stages : kStages;  // only the f16 kernel gives ring stages up (cluster mode)
+    Walk      w;
+    int       n_tiles = 0, parts = 1, rank = 0;
+    bool      any_empty = false;
+    // (q8_0 launches do not use the cluster mode: with two of its six ring stages given up for the partials the kernel
+    // was slower than with tickets, 13.7 against 11.7 us at 32 streams x 2048 rows.)
+    constexpr bool kClusterMode = !Q8;
+    if (kClusterMode && p.cluster > 0) {
+        // One cluster per pair: no list to cut.  The pair's tiles are split into nearly equal parts of four tiles or
+        // more, one per CTA of the cluster as far as they go; the other CTAs of the cluster have nothing to do.
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        const int pair = (int) blockIdx.x / p.cluster;
+        w.i = pair / p.n_kv_heads; w.kvh = pair - w.i * p.n_kv_heads;
+        walk_load(p, w);
+        parts   = max(1, min(p.cluster, w.tiles >> 2));
+        w.t     = rank < parts ? (rank * w.tiles) / parts : 0;
+        n_tiles = rank < parts ? ((rank + 1) * w.tiles) / parts - w.t : 0;
+        if (tid == 0) mbar_init(smem_u32(&xbar), parts);
+        fence_mbar_init();
+        __syncthreads();
+        // every CTA's barrier is initialised before anyone can reach it
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (!p.early) {
+            pdl_wait();
+            pdl_launch_dependents();
+        }
+        if (tid == 0) DECODE_TRACE(1);
+        if (rank >= parts) {
+            if (p.early) {  // every CTA of the grid passes the dependency wait
+                pdl_wait();
+                pdl_launch_dependents();
+            }
+            return;
+        }
+        if (w.tiles == 0) {  // nothing visible: the result is zeros (ops.cpp:8333); rank 0 is the only part
+            if (p.early) {
+                pdl_wait();
+                pdl_launch_dependents();
+            }
+            if (warp < kConsumerWarps) {
+                float4 * out = reinterpret_cast<float4 *>(p.dst + ((size_t) w.stream * p.n_heads + (size_t) w.kvh * p.gqa) * kHeadDim);
+                for (int j = tid; j < p.gqa * kHeadDim / 4; j += kConsumerWarps * 32) out[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            return;
+        }
+    } else {
     __syncthreads();
     // Dependency wait.  Every thread passes it before it triggers the launch of the next kernel, and
     // CTA 0 always passes it, so a kernel that starts early can rely on everything before its
@@ -454,15 +538,15 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         pdl_wait();
         pdl_launch_dependents();
     }
-    Walk      w;
-    const Cut cut     = cut_work_list(p, lane, Q8 ? 3 : 4, w);
-    const int  n_tiles   = cut.n_tiles;
-    const bool any_empty = cut.any_empty;
+    const Cut cut = cut_work_list(p, lane, Q8 ? 3 : 4, w);
+    n_tiles   = cut.n_tiles;
+    any_empty = cut.any_empty;
     if (tid == 0) {
         cut_note[0] = cut.aligned; cut_note[1] = cut.f0; cut_note[2] = cut.run; cut_note[3] = cut.b0; cut_note[4] = cut.b1;
         DECODE_TRACE(1);
     }
     if (n_tiles == 0 && blockIdx.x != 0) return;  // more CTAs than runs: nothing to do
+    }
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer
@@ -504,8 +588,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             }
             int good = 1;
             if (lane == 0) {
-                const int s = it % kStages;
-                if (it >= kStages && !mbar_wait_bounded(empty0 + 8 * s, ((it / kStages) - 1) & 1)) {
+                const int s = it % n_stages;
+                if (it >= n_stages && !mbar_wait_bounded(empty0 + 8 * s, ((it / n_stages) - 1) & 1)) {
                     atomicOr(p.status, kStatusTimeout);
                     atomicExch(&abort_flag, 1);
                     good = 0;
@@ -546,8 +630,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #endif
         if (lane == 0 && *reinterpret_cast<volatile int *>(&abort_flag)) {
             // consumers gave up: let the copies already issued land before the CTA retires
-            for (int i = max(0, issued - kStages); i < issued; ++i)
-                mbar_wait_bounded(full0 + 8 * (i % kStages), (i / kStages) & 1);
+            for (int i = max(0, issued - n_stages); i < issued; ++i)
+                mbar_wait_bounded(full0 + 8 * (i % n_stages), (i / n_stages) & 1);
         }
         return;
     }
@@ -678,10 +762,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 have[u] = i + u < seg;
-                st[u]   = cstage + u < kStages ? cstage + u : cstage + u - kStages;
+                st[u]   = cstage + u < n_stages ? cstage + u : cstage + u - n_stages;
                 p0[u]   = (w.t + i + u) * kKvTile + 16 * warp;
                 act[u]  = have[u] && p0[u] < c1;
-                if (have[u] && !mbar_wait_bounded(full0 + 8 * st[u], cstage + u < kStages ? cphase : cphase ^ 1)) {
+                if (have[u] && !mbar_wait_bounded(full0 + 8 * st[u], cstage + u < n_stages ? cphase : cphase ^ 1)) {
                     atomicOr(p.status, kStatusTimeout);
                     atomicExch(&abort_flag, 1);
                     ok = false;
@@ -870,7 +954,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 if (!have[u]) continue;
                 if (i + u != seg - 1 && lane == 0) mbar_arrive(empty0 + 8 * st[u]);
                 last_stage = st[u];
-                if (++cstage == kStages) { cstage = 0; cphase ^= 1; }
+                if (++cstage == n_stages) { cstage = 0; cphase ^= 1; }
             }
         }
 
@@ -932,6 +1016,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                     const float inv  = L > 0.0f ? 1.0f / L : 0.0f;  // nothing visible -> zeros, as the reference
                     *reinterpret_cast<float4 *>(p.dst + ((size_t) stream * p.n_heads + head) * kHeadDim + d0) =
                         make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+                } else if (kClusterMode && p.cluster > 0) {
+                    // into the first CTA of the cluster: slot `rank`, behind its ring
+                    const uint32_t dstp = dsmem_addr(smem_base + n_stages * R::kStageBytes + (uint32_t) ((rank * kMaxGqa + hh) * kPartialStride) * 4, 0);
+                    if ((tid & 15) == 0) dsmem_st2(dstp, M, L);
+                    dsmem_st2(dstp + (2 + d0) * 4, acc[0], acc[1]);
+                    dsmem_st2(dstp + (4 + d0) * 4, acc[2], acc[3]);
                 } else {
                     float * dstp = slot + hh * kPartialStride;
                     if ((tid & 15) == 0) { dstp[0] = M; dstp[1] = L; }
@@ -943,7 +1033,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         // the stage is free once every thread has read the scratch; the generic-proxy accesses above are ordered
         // before the bulk copy that refills it
         fence_proxy_async_smem();
-        if (!whole && tid == 0 && n_pending < 2) {  // a cut pair: its ticket is taken when the run ends
+        if (!whole && !(kClusterMode && p.cluster > 0) && tid == 0 && n_pending < 2) {  // a cut pair: its ticket is taken when the run ends
             const volatile int * cn = cut_note;
             const int f_pair = cn[1] + it - w.t;  // flat cut: the pair's first tile in the list
             int *     pd     = pending[n_pending];
@@ -959,7 +1049,37 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         w.t += seg;
         if (w.t == w.tiles && it < n_tiles) walk_next_pair(p, w);
     }
-    const int n_cut = ok ? *reinterpret_cast<volatile int *>(&n_pending) : 0;  // written before the barrier that ends a merge
+    if (kClusterMode && p.cluster > 0 && parts > 1 && ok) {
+        // Every thread's piece of the partial is on its way to the first CTA (the barrier that ends the merge has ordered
+        // the stores before thread 0's arrival, which publishes them cluster-wide).  The first CTA folds when all parts
+        // have arrived: no round trip to L2, no ticket.
+        if (tid == 0) dsmem_arrive(dsmem_addr(smem_u32(&xbar), 0));
+        if (rank == 0) {
+            if (!mbar_wait_cluster_bounded(smem_u32(&xbar), 0)) {
+                if (tid == 0) atomicOr(p.status, kStatusTimeout);
+            } else {
+                const int hh = tid >> 4, d0 = (tid & 15) * 4;  // 8 heads x 16 threads x 4 values
+                if (hh < p.gqa) {
+                    const float * slots = reinterpret_cast<const float *>(smem_gen + n_stages * R::kStageBytes);
+                    float         M = -INFINITY, L = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int r = 0; r < parts; ++r) {  // in list order, the running maximum raised part by part
+                        const float * src = slots + (r * kMaxGqa + hh) * kPartialStride;
+                        const float   mc  = src[0];
+                        if (mc == -INFINITY) continue;
+                        const float Mn = fmaxf(M, mc), fo = exp2f(M - Mn), fw = exp2f(mc - Mn);
+                        M = Mn;
+                        L = L * fo + src[1] * fw;
+#pragma unroll
+                        for (int d = 0; d < 4; ++d) acc[d] = acc[d] * fo + src[2 + d0 + d] * fw;
+                    }
+                    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+                    *reinterpret_cast<float4 *>(p.dst + ((size_t) w.stream * p.n_heads + (size_t) w.kvh * p.gqa + hh) * kHeadDim + d0) =
+                        make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+                }
+            }
+        }
+    }
+    const int n_cut = ok && !(kClusterMode && p.cluster > 0) ? *reinterpret_cast<volatile int *>(&n_pending) : 0;  // written before the barrier that ends a merge
     if (n_cut > 0) {
         // Second pass without a second launch: every run that holds a part of a pair takes a ticket after publishing
         // its partials; the one that draws the last ticket folds them all and resets the counter.  The tickets of a
@@ -1114,8 +1234,45 @@ int launch_decode(vox_engine * e, bool q8, const CUtensorMap & map_k, const CUte
     VOX_REQUIRE(workspace != nullptr && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 7) == 0,
                 VOX_ATTN_WORKSPACE_TOO_SMALL, "decode needs %zu workspace bytes (8-byte aligned), got %zu", need, workspace_bytes);
     p.partial = static_cast<float *>(workspace);
-    if (q8) launch_pdl(decode_kernel<true>, dim3(grid), dim3(kThreads), Ring<true>::kSmemBytes, stream, map_k, map_v, p);
-    else    launch_pdl(decode_kernel<false>, dim3(grid), dim3(kThreads), Ring<false>::kSmemBytes, stream, map_k, map_v, p);
+    // Cluster mode for launches of few pairs: with a whole cluster of CTAs per pair inside one wave, the CTAs of a pair
+    // exchange their partial results through distributed shared memory and no CTA pays the round trips of partials,
+    // tickets and fold through L2.  A stream order is not supported there (the cluster's number is the pair's).
+    // Only where a pair gets five CTAs or more: a pair cannot use more CTAs than its cluster has, so with small
+    // clusters the long pairs of a ragged launch run far longer than an equal share (64 ragged streams, clusters of
+    // three: 17.9 against 16.5 us per launch; 32 ragged streams, clusters of six: 11.4 against 12.7 us).
+    const int depth  = q8 ? Ring<true>::kStages : Ring<false>::kStages;
+    const int spare  = q8 ? 2 : 1;  // ring stages whose memory holds the partials instead: 18 KB / 16 KB
+    const int slots  = std::min(kDecodeMaxSms, e->sm_count) * (q8 ? Ring<true>::kCtasPerSm : Ring<false>::kCtasPerSm);
+    const int pairs  = n_streams * n_kv_heads;
+    const int c_fit  = (q8 ? 2 * Ring<true>::kStageBytes : Ring<false>::kStageBytes) / (kMaxGqa * kPartialStride * 4);  // slots of partials that fit
+    const int tiles_bound = std::max(1, (std::max(kv_bound, 1) + kKvTile - 1) / kKvTile);
+    int       cluster = std::min(std::min(8, c_fit), slots / std::max(1, pairs));
+    if (q8 || e->decode_cluster == 0 || order != nullptr || cluster < 5 || tiles_bound < 8 || (tiles_bound + cluster - 1) / cluster > kClusterMaxRun) cluster = 0;
+    p.cluster  = cluster;
+    p.n_stages = cluster > 0 ? depth - spare : depth;
+    p.early_tiles = std::min(p.early_tiles, p.n_stages);
+    if (cluster > 0) grid = pairs * cluster;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned) grid); cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = q8 ? Ring<true>::kSmemBytes : Ring<false>::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (cluster > 0) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = (unsigned) cluster; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    if (q8) cudaLaunchKernelEx(&cfg, decode_kernel<true>, map_k, map_v, p);
+    else    cudaLaunchKernelEx(&cfg, decode_kernel<false>, map_k, map_v, p);
     return check_launch(e, q8 ? "decode_kernel<q8_0>" : "decode_kernel<f16>");
 }
 

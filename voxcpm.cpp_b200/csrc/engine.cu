@@ -112,6 +112,7 @@ int vox_engine_create(int device, vox_engine ** out) {
         e->decode_wave[0] = env_int("VOX_DECODE_WAVE");
         e->decode_wave[1] = env_int("VOX_DECODE_WAVE_Q8");
         e->linear_split   = env_int("VOX_LINEAR_SPLIT");
+        if (getenv("VOX_DECODE_CLUSTER") != nullptr) e->decode_cluster = env_int("VOX_DECODE_CLUSTER");
         if (getenv("VOX_DECODE_EARLY") != nullptr) e->decode_early_tiles = env_int("VOX_DECODE_EARLY");
         const char * w = getenv("VOX_PREFILL_WEIGHTS");
         e->prefill_single_f16 = (w && w[0] == 'f') ? 1 : 0;
