@@ -13,10 +13,14 @@
 //           runs, one per CTA of a one-wave grid, whatever the streams' lengths are: a CTA's run
 //           may start in the middle of one pair and end in the middle of another.  The cut is
 //           computed on the device from the lengths as they are at launch time, so nothing in
-//           the launch depends on the position but its grid size;
-//   copy  = a producer warp streams its run of K and V tiles into a shared-memory ring (4 stages
-//           for f16, 6 for q8_0) with bulk-tensor copies (cp.async.bulk.tensor, 128-byte swizzle)
-//           signalled on mbarriers, straight across pair boundaries;
+//           the launch depends on the position but its grid size.  Launches with short runs
+//           split every pair on its own instead (no CTA crosses from one pair into the next),
+//           and f16 launches of few pairs run one thread-block cluster per pair: see
+//           cut_work_list and the cluster mode in launch_decode;
+//   copy  = a producer warp streams its run of tiles into a shared-memory ring (4 stages for f16,
+//           6 for q8_0) signalled on mbarriers, straight across pair boundaries: f16 K and V tiles
+//           by bulk-tensor copies (cp.async.bulk.tensor, 128-byte swizzle), a q8_0 tile (bytes and
+//           scales of K and V, one span of the cache) by one bulk copy;
 //   math  = four consumer warps, 16 rows of each tile.  Q (pre-scaled by scale*log2 e) is split as
 //           hi + lo in f16 and the two parts occupy rows 0-7 and 8-15 of the m16n8k16 A operand,
 //           so one MMA yields the hi and lo products and their sum carries ~22 bits of Q.  The
@@ -25,10 +29,12 @@
 //           (the ring stage of the tile consumed last).  A pair that lies inside one run is
 //           written out directly; otherwise the (max, sum, acc[64]) partials go to one of the
 //           CTA's two workspace slots and the last CTA of the pair to finish folds them (a ticket
-//           counter per pair decides who is last).
-// q8_0 K/V (int8 plane + scale plane) is dequantised in registers: int8 -> f16 is exact, the
-// per-block scales are applied in f32 to the per-block score accumulators (K) and folded into
-// the softmax weights (V), so Q is never quantised.
+//           counter per pair, taken when the run ends, decides who is last); in cluster mode they
+//           go to the first CTA of the pair's cluster through distributed shared memory.
+// q8_0 K/V: a stored byte is q + 128 and becomes an f16 tensor-core operand with one byte permute
+// (the subnormal (q + 128) * 2^-24); the 128 comes out of the accumulators, the per-block scales are
+// applied in f32 to the per-block score accumulators (K) and folded into the softmax weights (V),
+// so Q is never quantised.
 #include "kv_cache.cuh"
 
 #include <algorithm>
