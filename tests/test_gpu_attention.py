@@ -870,3 +870,52 @@ def test_replay_past_the_capacity_is_reported(engine, pkg):
         g.advance(1)   # and the host bookkeeping refuses to follow
     engine.sync_status()
     g.close()
+
+
+def test_cluster_mode_against_the_ticket_modes(engine, pkg, oracle, vo, monkeypatch):
+    """Launches of few pairs give every (stream, kv head) a thread-block cluster whose CTAs hand their partial results to
+    the first one through distributed shared memory; larger launches (and VOX_DECODE_CLUSTER=0) fold through the
+    workspace with tickets.  The same streams through both: ragged lengths with an empty stream, a one-tile stream and
+    streams that split seven ways, the arriving row stored by the launch, rotary embedding, decode repeated to catch a
+    barrier that is not reusable.  Both agree with the oracle, and with each other to f32 rounding of the folds."""
+    import torch
+    lens = [4096, 1, 64, 0, 700, 2049, 4095, 257, 1024, 3000]
+    S, cap = len(lens), 4096
+    rng = np.random.default_rng(21)
+    k = rng.standard_normal((S, HK, cap, D)).astype(np.float32)
+    v = rng.standard_normal((S, HK, cap, D)).astype(np.float32)
+    q = rng.standard_normal((S, H, D)).astype(np.float32)
+    k_new = rng.standard_normal((S, HK, D)).astype(np.float32)
+    v_new = rng.standard_normal((S, HK, D)).astype(np.float32)
+    pos = np.maximum(np.array(lens, np.int32) - 1, 0)
+    table = oracle.rope_table(pos, freq_base=10000.0, attn_factor=1.0)
+    outs = []
+    for cluster in ("1", "0"):
+        monkeypatch.setenv("VOX_DECODE_CLUSTER", cluster)
+        eng = pkg.Engine(0)
+        cache = pkg.KVCache(eng, 1, S, HK, cap, pkg.F16)
+        for s, n in enumerate(lens):
+            if n > 1:
+                cache.import_(0, s, oracle.kv_store(k[s, :, :n - 1], vo.F16), oracle.kv_store(v[s, :, :n - 1], vo.F16))
+        kv_len = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        qd, kd, vd = (torch.from_numpy(x).cuda() for x in (q, k_new, v_new))
+        for rep in range(3):  # the row is stored again at the same position: same bytes
+            out = cache.decode(0, qd, kv_len, cap, k_new=kd, v_new=vd, rope_table=torch.from_numpy(table).cuda())
+        eng.sync_status()
+        outs.append(out.cpu().numpy())
+        cache.close()
+        eng.close()
+    qr = oracle.rope(q, table)
+    kr = oracle.rope(k_new, table)
+    for s, n in enumerate(lens):
+        if n == 0:
+            assert not outs[0][s].any() and not outs[1][s].any()  # nothing visible: zeros (ops.cpp:8333)
+            continue
+        ks = np.concatenate([k[s, :, :n - 1], kr[s][:, None, :]], axis=1)
+        vs = np.concatenate([v[s, :, :n - 1], v_new[s][:, None, :]], axis=1)
+        ref = oracle.attn(qr[s][None, :, None, :], oracle.kv_store(ks, vo.F16)[None], oracle.kv_store(vs, vo.F16)[None],
+                          kv_type=vo.F16, path=vo.PATH_ROW_F32)[0, 0]
+        for o in outs:
+            assert rel_err(o[s], ref) < TOL["f16"], (s, n)
+    assert rel_err(outs[0], outs[1]) < 1e-5
+
