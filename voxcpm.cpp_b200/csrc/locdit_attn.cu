@@ -21,7 +21,8 @@
 // (Three and four buffers per CTA, i.e. two or three groups on their way, were measured: 80 and 118 us
 // per 256-stream launch against 71 us with two, because fewer CTAs then fit an SM.  One buffer per CTA,
 // only the warps that have rows and six CTAs per SM, meant for launches of few groups: 13.9 against 14.3
-// us at 32 streams, 84 against 71 us at 256: not kept.)
+// us at 32 streams, 84 against 71 us at 256: not kept.  Unpadded, swizzled staging rows, with which four
+// CTAs fit an SM instead of three: 72 against 71 us.  The kernel is not short of copies in flight.)
 #include "common.cuh"
 
 #include <algorithm>
