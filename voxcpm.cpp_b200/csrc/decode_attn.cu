@@ -82,9 +82,9 @@ struct DecodeParams {
     const uint8_t * k_new;
     const uint8_t * v_new;
     size_t          new_nb_head, new_nb_stream;
-    uint8_t *       k_rows;    // data planes of this layer
+    uint8_t *       k_rows;    // this layer's K rows (f16 plane; q8_0: the K bytes of the layer's first tile, see kv_cache.cuh)
     uint8_t *       v_rows;
-    uint8_t *       k_scales;  // scale planes of this layer (q8_0)
+    uint8_t *       k_scales;  // q8_0: the K scales of the layer's first tile
     uint8_t *       v_scales;
     size_t          nb_pos, nb_head, nb_stream, sb_pos, sb_head, sb_stream;
     // q8_0: the tiles of this layer (one contiguous span per 64 rows of a pair, see kQ8TileBytes) and the strides of a
@@ -319,7 +319,7 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 __device__ __forceinline__ float half_lo(uint32_t x) { return __half2float(__ushort_as_half((unsigned short) (x & 0xffffu))); }
 __device__ __forceinline__ float half_hi(uint32_t x) { return __half2float(__ushort_as_half((unsigned short) (x >> 16))); }
 
-// Bytes of a q8_0 plane -> f16 tensor-core operands without arithmetic.  The planes hold u = q + 128 (1..255); a byte
+// Bytes of a q8_0 tile -> f16 tensor-core operands without arithmetic.  The tiles hold u = q + 128 (1..255); a byte
 // in the low half of a 16-bit word whose high half is zero is the (subnormal) f16 number u * 2^-24, which mma.sync
 // takes as it is.  `selector` picks which two bytes of the word go to the two halves (PRMT, 4 = a zero byte).  The
 // products then carry (q + 128) * 2^-24: the factor goes into the step that consumes the accumulator anyway, and the
@@ -1292,7 +1292,7 @@ int launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtensorM
 }
 
 // ---- single-token calls over q8_0 K/V in ggml's block layout (the operator called on a caller's own quantised
-// cache, third_party/ggml/src/ggml-common.h:221-224): the blocks are taken apart into the planes the q8_0 decode
+// cache, third_party/ggml/src/ggml-common.h:221-224): the blocks are taken apart into the layout the q8_0 decode
 // kernel reads (tiles of 64 rows: bytes and scales of K and V in one span, as the cache object keeps them), in the
 // workspace, and that kernel runs on them.
 // Nothing is re-quantised: the result is what the cache object gives for the same blocks.
@@ -1339,7 +1339,7 @@ bool decode_mask_ok(const vox_attn_args * a) {
     return (reinterpret_cast<uintptr_t>(m.data) & 1) == 0 && m.nb[2] % 2 == 0 && m.nb[3] % 2 == 0 && m.ne[2] >= 1 && m.ne[3] >= 1;
 }
 
-static size_t q8_planes_bytes(const vox_attn_args * a, int * n_pad_out) {
+static size_t q8_tiles_bytes(const vox_attn_args * a, int * n_pad_out) {
     const int n_pad = (int) ((a->k.ne[1] + kKvTile - 1) / kKvTile * kKvTile);
     if (n_pad_out) *n_pad_out = n_pad;
     return (size_t) (n_pad / kKvTile) * a->k.ne[2] * a->k.ne[3] * kQ8TileBytes;  // K and V bytes and scales, tile by tile
@@ -1359,16 +1359,16 @@ bool decode_q8_blocks_route_ok(const vox_attn_args * a) {
 size_t decode_q8_blocks_workspace_bytes(const vox_attn_args * a) {
     if (!decode_q8_blocks_route_ok(a)) return 0;
     const size_t partials = decode_workspace_bytes((int) a->q.ne[3], (int) a->q.ne[2], (int) a->k.ne[2], (int) a->k.ne[1]);
-    return ((partials + 255) & ~(size_t) 255) + q8_planes_bytes(a, nullptr);
+    return ((partials + 255) & ~(size_t) 255) + q8_tiles_bytes(a, nullptr);
 }
 
 int launch_decode_q8_blocks(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t st) {
     int          n_pad = 0;
-    const size_t planes = q8_planes_bytes(a, &n_pad);
+    const size_t tiles_bytes = q8_tiles_bytes(a, &n_pad);
     const int    B = (int) a->q.ne[3], HK = (int) a->k.ne[2], n_kv = (int) a->k.ne[1];
     const size_t partials = (decode_workspace_bytes(B, (int) a->q.ne[2], HK, n_kv) + 255) & ~(size_t) 255;
-    VOX_REQUIRE(workspace != nullptr && workspace_bytes >= partials + planes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
-                VOX_ATTN_WORKSPACE_TOO_SMALL, "q8_0 decode needs %zu workspace bytes, got %zu", partials + planes, workspace_bytes);
+    VOX_REQUIRE(workspace != nullptr && workspace_bytes >= partials + tiles_bytes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+                VOX_ATTN_WORKSPACE_TOO_SMALL, "q8_0 decode needs %zu workspace bytes, got %zu", partials + tiles_bytes, workspace_bytes);
     uint8_t *    base = static_cast<uint8_t *>(workspace) + partials;
     RepackParams rp;
     const vox_tensor * ts[2] = {&a->k, &a->v};

@@ -19,7 +19,7 @@ int    launch_decode_f16(vox_engine * e, const CUtensorMap & map_k, const CUtens
                          float scale, const vox_tensor * mask, void * workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t decode_workspace_bytes(int n_streams, int n_heads, int n_kv_heads, int kv_bound);
 bool   decode_mask_ok(const vox_attn_args * a);
-// single-token calls over q8_0 K/V in block layout: taken apart into planes in the workspace (decode_attn.cu)
+// single-token calls over q8_0 K/V in block layout: taken apart into 64-row tiles in the workspace (decode_attn.cu)
 bool   decode_q8_blocks_route_ok(const vox_attn_args * a);
 size_t decode_q8_blocks_workspace_bytes(const vox_attn_args * a);
 int    launch_decode_q8_blocks(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes, cudaStream_t stream);

@@ -49,7 +49,7 @@ struct QkvParams {
     float *         q;          // [stream][H][64]
     float *         k_new;      // [stream][HK][64] or null
     float *         v_new;
-    // cache rows (k_new == null): planes of this layer and their strides
+    // cache rows (k_new == null): this layer's K / V rows (q8_0: bytes and scales of its first tile) and their strides
     uint8_t *       k_rows;
     uint8_t *       v_rows;
     uint8_t *       k_scales;
