@@ -391,6 +391,8 @@ __device__ __forceinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t
     }
 }
 
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
 // The fold of NP pairs at once by one thread (head hh of each pair, output columns d0 .. d0+3): the partials of a pair
 // (runs b0 .. b1 of the launch; the run that holds the pair's first tile wrote its slot 1, the others their slot 0) are
 // read W at a time, the loads of a batch issued together (each is a round trip to L2, and a pair may have been cut 17
@@ -1090,11 +1092,14 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         // Second pass without a second launch: every run that holds a part of a pair takes a ticket after publishing
         // its partials; the one that draws the last ticket folds them all and resets the counter.  The tickets of a
         // run's (at most two) cut pairs are taken together at its end, so a run that crosses from one pair into the
-        // next pays the round trips to L2 once.  One fence by one thread: the barrier that ends every merge orders
-        // all threads' partial stores before it, and the fence is cumulative, so a ticket is taken only once they are
-        // visible device-wide.
+        // next pays the round trips to L2 once.  One release fence by one thread: the barrier that ends every merge
+        // orders all threads' partial stores before it, and the fence is cumulative, so a ticket is taken only once
+        // they are visible device-wide.  The tickets themselves are relaxed (both in flight together); the thread that
+        // drew a last ticket fences once more (acquire), and the barrier below carries that order to the threads that
+        // read the other CTAs' partials from L2.  Acquire-release fences, not the sequentially consistent
+        // __threadfence(): nothing here needs a total order over fences, and the weaker one returns sooner.
         if (tid == 0) {
-            __threadfence();
+            fence_acq_rel_gpu();
             int * c0 = p.counters + pending[0][0] * p.n_kv_heads + pending[0][1];
             int * c1 = p.counters + pending[n_cut - 1][0] * p.n_kv_heads + pending[n_cut - 1][1];
             const int t0 = atomicAdd(c0, 1);
@@ -1102,12 +1107,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             int flags = 0;
             if (t0 == pending[0][3] - pending[0][2]) { *c0 = 0; flags |= 1; }
             if (n_cut > 1 && t1 == pending[1][3] - pending[1][2]) { *c1 = 0; flags |= 2; }
+            if (flags != 0) fence_acq_rel_gpu();
             fold_flag = flags;
         }
         named_bar_sync(1, kConsumerWarps * 32);
         const int flags = *reinterpret_cast<volatile int *>(&fold_flag);
         if (flags != 0) {
-            __threadfence();
             const int hh = tid >> 4, d0 = (tid & 15) * 4;  // 8 heads x 16 threads x 4 values
             constexpr int kFoldWidth = Q8 ? 4 : 8;  // the q8_0 form has no registers to spare for eight
             if (hh < p.gqa) {

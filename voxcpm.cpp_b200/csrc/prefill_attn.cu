@@ -9,43 +9,60 @@
 // A work item = 128 rows: 16 consecutive tokens x the 8 query heads that share a kv head (row r = token r / 8, head
 // r % 8; 128 tokens of one head when the GQA ratio is odd), walked over 128-key tiles, so that a K/V tile is fetched
 // once for the whole group (the incumbent packs its GQA heads the same way, fattn-mma-f16.cuh:38-72).  CTAs are
-// persistent, one per SM, and take items from a heaviest-first list in snake order; barriers, TMEM (all 512 columns)
-// and the tile of ones are set up once.  Sixteen warps in four warpgroups, which trade registers after launch
-// (setmaxnreg: the launch allots 128 per thread, the two softmax groups take 168, the others keep 56 and 96):
-//   warps 0-3, 8-11  softmax: two threads per query row (row r = TMEM lane r; warps w and w + 8 share a lane quarter),
-//              64 keys of a tile each.  Per tile a thread reads its 64 scores from TMEM (tcgen05.ld), takes their
-//              maximum, trades it with its partner (shared memory + an mbarrier, which also tells it that the partner
-//              holds its scores in registers), and writes P = 2^(c*S - m_ref) back into TMEM (tcgen05.st) over the
-//              tile's scores as two packed-f16 tiles hi + lo (~21 bits: one f16 per weight measured 2.3e-3 to 5e-3 of
-//              the output RMS on random sequences of 512 to 4096 tokens, outside the 2e-3 parity bound; hi + lo
+// persistent, one per SM, and take items from a heaviest-first list in snake order; barriers, TMEM (464 of the 512
+// columns) and the tile of ones are set up once.  A key tile is scored and weighted as two SCORE TILES of 64 keys
+// (the second is left out where no row of the item can see it), each in one of six 64-column score buffers in TMEM:
+// a buffer is held from Q.K^T until P.V has retired, several times longer than the softmax works on it, so it is the
+// number of buffers that lets the tensor core, the softmax warps and the issuers run on different tiles at once.
+// Sixteen warps in four warpgroups, which trade registers after launch (setmaxnreg: the launch allots 128 per thread,
+// the two softmax groups take 168, the others keep 56 and 96):
+//   warps 0-3, 8-11  softmax: one thread per query row (row r = TMEM lane r; warps w and w + 8 share a lane quarter).
+//              Warps 0-3 take the even score tiles, warps 8-11 the odd ones.  Per tile a thread reads its 64 scores
+//              from TMEM (tcgen05.ld), takes their maximum, and writes P = 2^(c*S - m_ref) back into TMEM (tcgen05.st)
+//              over the tile's scores as two packed-f16 tiles hi + lo (~21 bits: one f16 per weight measured 2.3e-3 to
+//              5e-3 of the output RMS on random sequences of 512 to 4096 tokens, outside the 2e-3 parity bound; hi + lo
 //              measures under 6e-5): the tensor core takes the weights from there as the A operand of P.V, so they
 //              never pass through shared memory.  On the diagonal tile a warp skips the 32-column blocks none of its
 //              rows can see.  The output row and the row sums accumulate in TMEM over all tiles (no per-tile
 //              read-back); they are rescaled in place only when a tile's maximum exceeds the reference m_ref by more
-//              than 2^8.  These warps do nothing else: from the last tile of an item they go straight to the first
-//              tile of the next.
+//              than 2^8.  The reference of a row passes from the thread of one score tile to the thread of the next
+//              (the other group) through shared memory and an mbarrier; it is handed on half-way through the
+//              exponentials, so the two groups overlap there without starting them together.  These warps do
+//              nothing else: from the last tile of an item they go straight to the first tile of the next.
 //   warp 4     producer: one lane issues cp.async.bulk.tensor copies of 128-row K and V tiles into three-stage rings.
-//   warp 6     score issuer: one lane issues S = Q.K^T (tcgen05.mma kind::f16, M = 128, N = 128, 4 k-steps, both
-//              operands in shared memory) into one of three score buffers in TMEM (tile T uses buffer T % 3), up to
-//              three tiles ahead of P.V and across item boundaries.
+//   warp 6     score issuer: S = Q.K^T (tcgen05.mma kind::f16, M = 128, N = 64, 4 k-steps, both operands in shared
+//              memory) into score buffer U % 6, up to six score tiles ahead of P.V and across item boundaries.
 //   warp 5     output issuer: O += P.V and the row sums come from ONE instruction per 16 keys and weight part
-//              (N = 80, 8 k-steps for hi, 8 for lo): P from TMEM, V read MN-major straight from its row-major tile,
+//              (N = 80, 4 k-steps for hi, 4 for lo): P from TMEM, V read MN-major straight from its row-major tile,
 //              and a tile of ones addressed as columns 64-79 of every 16-key step, which yields the sums of exactly
 //              the rounded weights the tensor core used.  One thread issues both parts, so the order of the f32
-//              accumulation, and with it every bit of the result, is the same in every run (two threads sharing the
-//              parts measured no faster).  Completion is signalled with tcgen05.commit.  (Warp 7 only fills the group.)
+//              accumulation, and with it every bit of the result, is the same in every run.  Completion is signalled
+//              with tcgen05.commit.  (Warp 7 only fills the group.)
+//              Both issuer warps run their loops with all 32 lanes (waits and votes by the warp, the instructions by
+//              one elected lane): in warp-uniform control flow the descriptors live in uniform registers, where
+//              tcgen05.mma takes them from.  Issued from inside a one-lane branch an instruction cost its thread about
+//              80 clocks, now about 40 (a commit costs 46, a satisfied barrier wait 47: measured alone).
 //   warps 12-15 in/out: one thread per query row again.  They keep the Q tiles of the next two items in shared
-//              memory (f32 from memory, rounded to f16 once, exact when it already holds f16 values) and read each
+//              memory (f32 from memory, rounded to f16 once, exact when it already holds f16 values; the raw rows of
+//              the item after those wait in a staging area, copied there by cp.async a whole item ahead) and read each
 //              finished output row out of TMEM, normalise and store it, handing the columns back to the issuer.
-// What bounds it, measured with cycle counters and with the softmax arithmetic compiled out (developer builds): the
-// special-function unit (16 exponentials per clock: 1024 clocks per 128 x 128 tile; the weights' block of the softmax
-// loop takes 1300, the whole loop 2300 with its waits, the load of the scores and the trade of the maxima), and, close
-// behind, the hand-over chain scores -> weights -> P.V -> buffer free (1900 clocks per tile with no softmax arithmetic
-// at all, whatever the number of issuing threads, ring stages or P.V instructions).  The tensor pipe itself needs 900.
-// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  131 KB of shared memory per CTA (195 KB
-// with remainder tiles).  Every wait on a barrier is bounded; on expiry the status word is set and all roles fall
-// through to the common exit, where the TMEM columns are released.  The register trade cannot block: what the softmax
-// groups take, the other two have given up before (static_assert below).
+// What bounds it, measured by leaving parts out (developer builds, 2048 tokens x 2 sequences, 29.4 key tiles per CTA,
+// one layer 43 us): barriers, commits and waits alone, with no copy, no MMA, no softmax arithmetic and no global
+// traffic, 16.5 us (about 450 clocks per score tile although six are in flight and no single wait, arrive or commit
+// costs more than 50 clocks to issue); with the MMAs 26 us; with Q in and results out as well 33 us; the softmax
+// arithmetic adds the last 10.  The exponentials (16 per clock and SM) and the two conversions to packed f16 per pair of
+// weights (32 per clock and SM, on the same unit) bound the arithmetic itself at 1175-1300 clocks per 128 x 128 tile
+// with two or three warps per scheduler at work (measured alone; integer forms of the split, with shifts and byte
+// permutes instead of conversions, measured slower: 1400-1900), against 2100 for the whole tile period.  Arrangements
+// tried on this skeleton, none of which moved the 2048-token figure by more than 3 %: both softmax groups on the same
+// tile with 64 keys per thread and a trade of maxima (the first form of this kernel); 128-key score tiles with
+// three buffers; three softmax groups (640 threads, 120 registers each); handing the reference on before, during or
+// after the exponentials; polling instead of parked waits in the issuers; two output accumulators so that an item's
+// first P.V need not wait for the read-out of the item before.
+// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  163 KB of shared memory per CTA (195 KB
+// with remainder tiles, which leave no room for the staging area).  Every wait on a barrier is bounded; on expiry the
+// status word is set and all roles fall through to the common exit, where the TMEM columns are released.  The
+// register trade cannot block: what the softmax groups take, the other two have given up before (static_assert below).
 //
 // Three forms of the kernel share this code (template parameters):
 //   kSplitP  the weights as hi + lo (the product path; a single f16 is kept for comparison);
@@ -96,26 +113,49 @@ __device__ long long g_trace[4][64];  // CTA 0, first 64 tiles: scores seen, wei
 #define PROF_TRACE(k, T)
 #endif
 
+// Developer builds only (-DVOX_ATTN_DEVELOPER): VOX_PREFILL_NOSOFTMAX, VOX_PF_SKIP_QK, VOX_PF_SKIP_PV, VOX_PF_SKIP_LOAD and
+// VOX_PF_SKIP_IO leave out the softmax arithmetic, the two kinds of MMA, the K/V copies and the global traffic of the
+// in/out warps, one by one; the barrier protocol stays whole, the results are meaningless, the timings are the
+// decomposition quoted in the header.  Compiled out of the product library.
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_PV)
+#define VOX_PF_SKIP_PV_LO 1
+#else
+#define VOX_PF_SKIP_PV_LO 0
+#endif
 constexpr int kTile      = 128;            // query rows per item
 constexpr int kKeys      = 128;            // keys per tile
 constexpr int kQBytes    = kTile * 128;    // the item's [128][64] f16 Q tile
 constexpr int kKvBytes   = kKeys * 128;    // one [128][64] f16 K or V tile
 constexpr int kStages    = 6;              // most stages a K or V ring has (barrier slots)
-constexpr int kSBufs     = 3;              // score buffers in TMEM
-constexpr int kSoftmaxThreads = 256;       // two warpgroups: one thread per query row and half of a tile's keys
+constexpr int kSub       = 64;             // keys per score tile: a key tile is scored and weighted in two halves
+constexpr int kSBufs     = 6;              // score buffers in TMEM
+#ifndef VOX_PREFILL_GROUPS
+#define VOX_PREFILL_GROUPS 2
+#endif
+#ifndef VOX_PREFILL_PUBLISH_AT
+#define VOX_PREFILL_PUBLISH_AT 2
+#endif
+// After how many of its four blocks of 16 weights the thread of a score tile passes the row's reference on to the thread
+// of the next tile, which waits for it before its own exponentials: 0 lets all groups run their exponentials at the same
+// time (and then wait and load at the same time), 4 lets one group at a time run them; in between the groups overlap.
+constexpr int kPublishAt = VOX_PREFILL_PUBLISH_AT;
+constexpr int kGroups    = VOX_PREFILL_GROUPS;  // softmax warpgroups: score tile U is taken by group U % kGroups
+constexpr int kSoftmaxThreads = 128 * kGroups;  // one thread per query row in each group
 constexpr int kIoThreads = 128;
-constexpr int kThreadsPf = 512;            // softmax A, control (producer, two issuers, one idle warp), softmax B, in/out
+constexpr int kThreadsPf = 256 + kSoftmaxThreads;  // softmax 0, control (producer, two issuers, one idle warp), softmax 1, in/out, softmax 2
 constexpr int kQBufs     = 2;              // Q tiles of two consecutive items
 // Registers per thread after the warpgroups have traded (setmaxnreg).  One CTA per SM: the launch allots 128 x 512;
 // what the softmax groups take beyond that, the other two have given up before (they do so first thing).
-constexpr int kRegsLaunch = 128, kRegsSoftmax = 168, kRegsControl = 56, kRegsIo = 96;
-static_assert(2 * (kRegsSoftmax - kRegsLaunch) <= (kRegsLaunch - kRegsControl) + (kRegsLaunch - kRegsIo), "the trade cannot block");
-static_assert((2 * kRegsSoftmax + kRegsControl + kRegsIo) * 128 <= 65536, "the CTA's registers fit the SM");
+constexpr int kRegsLaunch = kGroups == 3 ? 96 : 128, kRegsSoftmax = kGroups == 3 ? 120 : 168, kRegsControl = kGroups == 3 ? 48 : 56,
+              kRegsIo = kGroups == 3 ? 72 : 96;
+static_assert(kRegsLaunch == 65536 / kThreadsPf / 8 * 8, "what a thread holds at launch");
+static_assert(kGroups * (kRegsSoftmax - kRegsLaunch) <= (kRegsLaunch - kRegsControl) + (kRegsLaunch - kRegsIo), "the trade cannot block");
+static_assert((kGroups * kRegsSoftmax + kRegsControl + kRegsIo) * 128 <= 65536, "the CTA's registers fit the SM");
 // TMEM columns: three score buffers of 128 columns (tile T uses buffer T % 3; its weights, packed f16, replace its scores:
 // high parts in the first 64 columns, low parts in the last 64) and the output row with its row sum
 constexpr int kTmemCols  = 512;
 constexpr int kSCol      = 0;              // S: 3 x 128 columns
-constexpr int kOCol      = kSBufs * kKeys; // O: 64 columns, row sums: 16 columns behind them
+constexpr int kOCol      = kSBufs * kSub;  // O: 64 columns, row sums: 16 columns behind them
 constexpr int kOnesBytes = 2048;           // 16 keys x 64 ones, addressed as columns 64-79 of every 16-key step of every V tile
 // With kVLo (K/V expanded from q8_0 or f32) a K or V stage holds two tiles, the f16 values and what their rounding left
 // over, and the rings are two stages deep instead of three (five stages measured 5 % slower than three: the rings
@@ -127,8 +167,11 @@ constexpr int stages_of(bool v_lo) { return v_lo ? 2 : VOX_PREFILL_STAGES; }
 constexpr int v_stage_bytes(bool v_lo) { return v_lo ? 2 * kKvBytes : kKvBytes; }
 // ... and a Q buffer holds the f16 tile and the remainder tile as well
 constexpr int q_buf_bytes(bool v_lo) { return v_lo ? 2 * kQBytes : kQBytes; }
-constexpr int smem_pf(bool v_lo) {  // Q x 2, K ring, V ring, ones
-    return kQBufs * q_buf_bytes(v_lo) + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + 1024;
+// Without remainder tiles there is room for a staging area the size of a raw Q tile (128 rows of 64 floats): the rows of
+// the item after the two whose Q tiles are in place are copied there asynchronously (cp.async) a whole item ahead
+constexpr int kQStageBytes = kTile * kHeadDim * 4;
+constexpr int smem_pf(bool v_lo) {  // Q x 2, K ring, V ring, ones, Q staging
+    return kQBufs * q_buf_bytes(v_lo) + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + (v_lo ? 0 : kQStageBytes) + 1024;
 }
 
 struct PrefillParams {
@@ -207,6 +250,13 @@ __device__ __forceinline__ int next_live(const WorkItem & w, int from) {
     return rest ? from + __ffsll((long long) rest) - 1 : w.n_tiles;
 }
 
+// Score tiles (64 keys) of key tile j that an item walks: the second is left out when no row of the item can see a key
+// of it (the diagonal tile of a causal item; the last tile of a key sequence that ends in its first half).
+__device__ __forceinline__ int sub_tiles(const PrefillParams & p, const WorkItem & w, int j) {
+    const int last_key = min(min(w.q0 + p.tok, p.n_q) - 1 + p.causal_offset, p.n_kv - 1);
+    return last_key - j * kKeys >= kSub ? 2 : 1;
+}
+
 // kSplitP: the weights go to the tensor core as hi + lo (two f16 parts, ~21 bits) instead of one f16 (11 bits).
 // kVLo: K and V come as two f16 tiles each, value + remainder (q8_0 blocks expanded exactly), and Q is kept as value +
 // remainder too (the reference's accurate path for such operands keeps Q in f32); the remainders take a second and
@@ -219,14 +269,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                   const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo, const PrefillParams p) {
     constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo), kQBufBytes = q_buf_bytes(kVLo);
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[4 * kStages + 3 * kSBufs + kQBufs + 2 + 2];
-    __shared__ float    row_max[2][2][kTile];  // [tile parity][half of the keys][row]: the two softmax threads of a row trade their maxima
+    __shared__ uint64_t bars[4 * kStages + 3 * kSBufs + kQBufs + 2 + kGroups];
+    __shared__ float    row_ref[kGroups][kTile];  // [score tile % groups][row]: the row's reference maximum after that tile, for the thread that takes the next one
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBufBytes, sV0 = sK0 + kSt * kVBytes, sOnes = sV0 + kSt * kVBytes;
+    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBufBytes, sV0 = sK0 + kSt * kVBytes, sOnes = sV0 + kSt * kVBytes, sStage = sOnes + kOnesBytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -236,11 +286,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     // and the accumulators are at rest).  A barrier of buffer b completes once per tile of that buffer, and each of the
     // three events of tile T + 3 needs the one its waiter is looking for in tile T to have been seen, so no barrier can
     // complete twice between two looks of a waiter (a parity wait cannot tell two completed phases from none).
-    // Per item: Q in place (one per Q buffer), output complete, output read.  Per tile parity: row maxima traded
-    // between the two softmax warpgroups (tile T + 2 cannot be traded before every warp has seen tile T's).
+    // Per item: Q in place (one per Q buffer), output complete, output read.  Per tile parity: the rows'
+    // reference maxima after the tile, published by the softmax group that took it for the group that takes the next.
     const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = kfull0 + 8 * kStages, vfull0 = kempty0 + 8 * kStages,
                    vempty0 = vfull0 + 8 * kStages, bS0 = vempty0 + 8 * kStages, bP0 = bS0 + 8 * kSBufs, bF0 = bP0 + 8 * kSBufs,
-                   bQ0 = bF0 + 8 * kSBufs, bO = bQ0 + 8 * kQBufs, bOfree = bO + 8, bX0 = bOfree + 8;
+                   bQ0 = bF0 + 8 * kSBufs, bO = bQ0 + 8 * kQBufs, bOfree = bO + 8, bM0 = bOfree + 8;
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
@@ -251,13 +301,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         }
         for (int s = 0; s < kSBufs; ++s) {
             mbar_init(bS0 + 8 * s, 1);
-            mbar_init(bP0 + 8 * s, kSoftmaxThreads / 32);  // one arrival per softmax warp
+            mbar_init(bP0 + 8 * s, 4);  // one arrival per softmax warp of the group that took the tile
             mbar_init(bF0 + 8 * s, 1);
         }
         for (int s = 0; s < kQBufs; ++s) mbar_init(bQ0 + 8 * s, kIoThreads / 32);  // one arrival per in/out warp
         mbar_init(bO, 1);
         mbar_init(bOfree, kIoThreads / 32);
-        for (int s = 0; s < 2; ++s) mbar_init(bX0 + 8 * s, kSoftmaxThreads / 32);  // row maxima of a tile traded (tile T uses T % 2)
+        for (int s = 0; s < kGroups; ++s) mbar_init(bM0 + 8 * s, 4);  // the rows' references after a score tile published (tile U uses U % kGroups)
         fence_mbar_init();
     }
     if (warp == 5) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -281,16 +331,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         atomicExch(&abort_flag, 1);
     };
     auto aborted = [&]() { return *reinterpret_cast<volatile int *>(&abort_flag) != 0; };
+    // the same for a whole warp that must stay together: every lane takes the same way out
+    auto warp_aborted = [&]() { return __any_sync(0xffffffffu, aborted()) != 0; };
+    auto warp_wait    = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity)) != 0; };
 
     // The CTA is persistent: every role walks the same item sequence; T counts key tiles over all items
     // and fixes the phase of every per-tile barrier; `round` fixes the phase of the per-item ones.
-    if (warp >= 12) {
+    if (warp >= 12 && warp < 16) {
         // ------------------------------------------------------------------ in/out warps: Q tiles in, results out
         // One thread per query row, as in the softmax warps (warp 12+i may touch TMEM lanes 32i..32i+31).  They keep
         // the Q tiles of the next two items in shared memory and read each finished output out of TMEM, so that the
         // softmax warps go from the last tile of one item straight to the first tile of the next.
         regs_give<kRegsIo>();
-        const int      row   = tid - (kThreadsPf - kIoThreads);
+        const int      row   = tid - 12 * 32;
         const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);
         {
             const uint32_t one2 = 0x3C003C00u;
@@ -307,7 +360,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             for (int h = 0; h < 2; ++h) {
                 float4 qv[8];
 #pragma unroll
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_IO)
+                for (int i = 0; i < 8; ++i) qv[i] = make_float4(0.f, 0.f, 0.f, (float) (size_t) src * 0.f);
+#else
                 for (int i = 0; i < 8; ++i) qv[i] = qpos < p.n_q ? src[8 * h + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#endif
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const float    x[8] = {qv[2 * c].x, qv[2 * c].y, qv[2 * c].z, qv[2 * c].w, qv[2 * c + 1].x, qv[2 * c + 1].y, qv[2 * c + 1].z, qv[2 * c + 1].w};
@@ -328,14 +385,56 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(bQ0 + 8 * buf);
         };
+        // Without remainder tiles (kVLo) the raw rows travel through a staging area: sixteen 16-byte asynchronous copies per
+        // thread, all in flight together and issued a whole item before the rows are needed, so that a new Q tile costs
+        // the in/out warps a pass over shared memory instead of two round trips to global memory between one item's
+        // output and the next.  A thread copies, waits for and reads only its own row, so no barrier is involved; chunk c
+        // of row r sits at (c ^ (r & 15)), which spreads the rows of a quarter-warp over the banks.
+        constexpr bool  kStageQ   = !kVLo;
+        uint8_t * const stage_row = smem_gen + (sStage - smem_base) + row * 256;
+        auto fetch_q = [&](const WorkItem & w) {
+            const int qpos = w.q0 + row / p.pack, head = w.head + row % p.pack;
+            if (qpos < p.n_q) {
+                const uint8_t * src = p.q + (size_t) qpos * p.q_nb1 + (size_t) head * p.q_nb2 + (size_t) w.batch * p.q_nb3;
+#pragma unroll
+                for (int c = 0; c < 16; ++c) cp_async_16(smem_u32(stage_row) + ((c ^ (row & 15)) << 4), src + 16 * c);
+            }
+            cp_async_commit();
+        };
+        auto convert_q = [&](const WorkItem & w, int buf) {
+            cp_async_wait_all();
+            uint8_t * const q_dst = smem_gen + buf * kQBufBytes + row * 128;
+            const bool      in    = w.q0 + row / p.pack < p.n_q;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float4 a = in ? *reinterpret_cast<const float4 *>(stage_row + (((8 * h + 2 * c) ^ (row & 15)) << 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 b = in ? *reinterpret_cast<const float4 *>(stage_row + (((8 * h + 2 * c + 1) ^ (row & 15)) << 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const int at = ((4 * h + c) ^ (row & 7)) << 4;
+                    *reinterpret_cast<uint4 *>(q_dst + at) = make_uint4(pack_half2(a.x, a.y), pack_half2(a.z, a.w), pack_half2(b.x, b.y), pack_half2(b.z, b.w));
+                }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bQ0 + 8 * buf);
+        };
         WorkItem w, wn;
         for (int r = 0; r < kQBufs; ++r)
-            if (work_item<kMask>(p, r, wn)) load_q(wn, r);
+            if (work_item<kMask>(p, r, wn)) {
+                if (kStageQ) { fetch_q(wn); convert_q(wn, r); }
+                else load_q(wn, r);
+            }
+        if (kStageQ && work_item<kMask>(p, kQBufs, wn)) fetch_q(wn);
         for (int round = 0; work_item<kMask>(p, round, w) && !aborted(); ++round) {
             if (!mbar_wait_bounded(bO, round & 1)) { give_up(); break; }
             tc_fence_after();
             const int   qpos = w.q0 + row / p.pack, head = w.head + row % p.pack;
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_IO)
+            const bool  live = qpos < 0;
+#else
             const bool  live = qpos < p.n_q;
+#endif
             const float l    = tmem_ld1(t_row + kOCol + kHeadDim);  // sum of exactly the rounded weights the tensor core used
             const float inv  = l > 0.0f ? 1.0f / l : 0.0f;
             float4 *    out  = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim);
@@ -357,7 +456,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
             // The item's output is complete only after its last P.V, which needed its last weights, which needed its last
             // scores: every Q.K^T of this item has retired, and its Q buffer takes the item after next.
-            if (work_item<kMask>(p, round + kQBufs, wn)) load_q(wn, round % kQBufs);
+            if (work_item<kMask>(p, round + kQBufs, wn)) {
+                if (kStageQ) {
+                    convert_q(wn, round % kQBufs);  // its rows were asked for an item ago
+                    if (work_item<kMask>(p, round + kQBufs + 1, wn)) fetch_q(wn);
+                } else {
+                    load_q(wn, round % kQBufs);
+                }
+            }
         }
     } else if (warp >= 4 && warp < 8) {
         regs_give<kRegsControl>();
@@ -377,6 +483,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         PROF_STOP(0);
                         if (T >= kSt && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
                         PROF_STOP(1);
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_LOAD)
+                        if (T >= kSt && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        mbar_arrive(kfull0 + 8 * st);
+                        mbar_arrive(vfull0 + 8 * st);
+                        continue;
+#endif
                         mbar_expect_tx(kfull0 + 8 * st, kVBytes);
                         tma_load_5d(sK0 + st * kVBytes, &map_k, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
                         if (kVLo) tma_load_5d(sK0 + st * kVBytes + kKvBytes, &map_klo, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
@@ -394,57 +506,73 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
         } else if (warp == 6) {
             // -------------------------------------------------------------- score issuer: S = Q.K^T
-            // Two threads share the issuing, because issuing is what a CTA runs out of first: a tcgen05.mma costs its
-            // issuing thread 60 cycles or more whatever its shape.  This thread walks the item sequence on its own, up
-            // to three tiles ahead of P.V, across item boundaries.  S of global tile Tq goes into score buffer Tq % 3:
-            // four k-steps of 16 along head_dim (32 bytes each inside the swizzle atom), N = 128 keys.  The buffer last
-            // held the weights of tile Tq-3, which P.V of that tile reads: its retirement is awaited first.
-            if (lane == 0) {
-                constexpr uint32_t idesc_qk = idesc_f16(kKeys, false);
+            // The whole warp walks the item sequence and waits on the barriers; one elected lane issues.  With the loop
+            // in warp-uniform control flow the descriptors and TMEM addresses live in uniform registers, which is where
+            // tcgen05.mma takes them from: issued from inside a one-lane branch every instruction first had its operands
+            // moved over, and cost its thread some 80 clocks.  Every exit from the loops is taken by all lanes together
+            // (votes on the waits' results and on the abort flag).  The warp runs up to three tiles ahead of P.V, across
+            // item boundaries.  S of global tile Tq goes into score buffer Tq % 3: four k-steps of 16 along head_dim
+            // (32 bytes each inside the swizzle atom), N = 128 keys.  The buffer last held the weights of tile Tq-3,
+            // which P.V of that tile reads: its retirement is awaited first.
+            {
+                constexpr uint32_t idesc_qk = idesc_f16(kSub, false);
                 const uint64_t     dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK0), dKlo = smem_desc_sw128(sK0 + kKvBytes);
                 constexpr uint64_t kStepQK = 32 >> 4;          // 16 of head_dim inside the swizzle atom
                 constexpr uint64_t kStage  = kVBytes >> 4;     // K stages are as large as V stages
                 constexpr uint64_t kQBuf   = kQBufBytes >> 4;
                 constexpr uint64_t kQLo    = kQBytes >> 4;     // from a Q tile to its remainder tile
+                const bool leader = elect_one();
+                constexpr uint64_t kSubK   = (kSub * 128) >> 4;  // from the first 64 keys of a K tile to the last
                 WorkItem wq;
-                int      Tq = 0;
+                int      Tk = 0, U = 0;  // key tiles and score tiles so far, over all items
                 bool     ok = true;
                 PROF_VARS;
                 PROF_START();
                 for (int rq = 0; ok && work_item<kMask>(p, rq, wq); ++rq) {
                     PROF_STOP(0);
-                    if (!mbar_wait_bounded(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) { give_up(); break; }  // the item's Q tile is in place
+                    if (!warp_wait(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) { give_up(); break; }  // the item's Q tile is in place
                     PROF_STOP(2);
                     const uint64_t dQi = dQ + (rq % kQBufs) * kQBuf;
-                    for (int jq = next_live<kMask>(wq, 0); jq < wq.n_tiles && !aborted(); jq = next_live<kMask>(wq, jq + 1), ++Tq) {
-                        const int st = Tq % kSt, sb = Tq % kSBufs;
+                    for (int jq = next_live<kMask>(wq, 0); ok && jq < wq.n_tiles && !warp_aborted(); jq = next_live<kMask>(wq, jq + 1), ++Tk) {
+                        const int st = Tk % kSt, n_sub = sub_tiles(p, wq, jq);
                         PROF_STOP(0);
-                        if (Tq >= kSBufs && !mbar_wait_bounded(bF0 + 8 * sb, ((Tq / kSBufs) - 1) & 1)) { give_up(); ok = false; break; }
-                        PROF_STOP(1);
-                        if (!mbar_wait_bounded(kfull0 + 8 * st, (Tq / kSt) & 1)) { give_up(); ok = false; break; }
+                        if (!warp_wait(kfull0 + 8 * st, (Tk / kSt) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(2);
-                        tc_fence_after();
-                        const uint32_t dS = tmem + kSCol + kKeys * sb;
+                        for (int u = 0; u < n_sub; ++u, ++U) {
+                            const int sb = U % kSBufs;
+                            if (U >= kSBufs && !warp_wait(bF0 + 8 * sb, ((U / kSBufs) - 1) & 1)) { give_up(); ok = false; break; }
+                            PROF_STOP(1);
+                            tc_fence_after();
+                            const uint32_t dS  = tmem + kSCol + kSub * sb;
+                            const uint64_t dKs = st * kStage + u * kSubK;
+                            if (leader) {
+#if !(defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_QK))
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) tc_mma_f16(dS, dQi + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, k > 0);
-                        if (kVLo) {  // what rounding K to f16 left over
+                                for (int k = 0; k < 4; ++k) tc_mma_f16(dS, dQi + k * kStepQK, dK + dKs + k * kStepQK, idesc_qk, k > 0);
+#endif
+                                if (kVLo) {  // what rounding K to f16 left over
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) tc_mma_f16(dS, dQi + k * kStepQK, dKlo + st * kStage + k * kStepQK, idesc_qk, 1);
+                                    for (int k = 0; k < 4; ++k) tc_mma_f16(dS, dQi + k * kStepQK, dKlo + dKs + k * kStepQK, idesc_qk, 1);
 #pragma unroll
-                            for (int k = 0; k < 4; ++k)  // and what rounding Q to f16 left over
-                                tc_mma_f16(dS, dQi + kQLo + k * kStepQK, dK + st * kStage + k * kStepQK, idesc_qk, 1);
+                                    for (int k = 0; k < 4; ++k)  // and what rounding Q to f16 left over
+                                        tc_mma_f16(dS, dQi + kQLo + k * kStepQK, dK + dKs + k * kStepQK, idesc_qk, 1);
+                                }
+                                tc_commit(bS0 + 8 * sb);                          // Q.K^T has retired: the scores are there ...
+                                if (u == n_sub - 1) tc_commit(kempty0 + 8 * st);  // ... and the K stage may be refilled
+                            }
+                            __syncwarp();
+                            PROF_STOP(0);
                         }
-                        tc_commit(bS0 + 8 * sb);      // Q.K^T has retired: the scores are there ...
-                        tc_commit(kempty0 + 8 * st);  // ... and the K stage may be refilled
                     }
-                    if (aborted()) break;
+                    if (!ok || warp_aborted()) break;
                 }
                 PROF_STOP(0);
-                PROF_FLUSH(21, 3);  // 21 issue, 22 wait for the score buffer, 23 wait Q / K tile
+                if (lane == 0) PROF_FLUSH(21, 3);  // 21 issue, 22 wait for the score buffer, 23 wait Q / K tile
             }
         } else if (warp == 5) {
             // -------------------------------------------------------------- output issuer: O += P.V, row sums += P.1
-            if (lane == 0) {
+            // (whole warp in the loop, one elected lane issues: see the score issuer)
+            {
                 constexpr uint32_t idesc_pv = idesc_f16(kHeadDim + 16, true);
                 // Descriptors are built once; a k-step or a ring stage is selected by adding its distance to the address
                 // field, and the same distance comes off the leading byte offset, which then still points at the tile of ones.
@@ -456,69 +584,86 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // the remainder tile of a V stage: 64 columns, no tile of ones behind it
                 const uint64_t     dVlo     = smem_desc_sw128_mn(sV0 + kKvBytes, 16);
                 constexpr uint32_t idesc_lo = idesc_f16(kHeadDim, true);
+                const bool leader = elect_one();
                 PROF_VARS;
                 WorkItem w;
-                int      T  = 0;
+                int      Tk = 0, U = 0;
                 bool     ok = true;
                 PROF_START();
                 for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
                     const int j_first = next_live<kMask>(w, 0);
-                    for (int j = j_first; j < w.n_tiles && !aborted(); ++T) {
-                        const int st = T % kSt, sb = T % kSBufs;
+                    bool      first   = true;  // the item's first score tile: O is overwritten, not added to
+                    for (int j = j_first; ok && j < w.n_tiles && !warp_aborted(); ++Tk) {
+                        const int st = Tk % kSt, n_sub = sub_tiles(p, w, j);
                         const int j_next = next_live<kMask>(w, j + 1);
                         PROF_STOP(0);
-                        if (!mbar_wait_bounded(vfull0 + 8 * st, (T / kSt) & 1)) { give_up(); ok = false; break; }
+                        if (!warp_wait(vfull0 + 8 * st, (Tk / kSt) & 1)) { give_up(); ok = false; break; }
                         PROF_STOP(3);
-                        if (!mbar_wait_bounded(bP0 + 8 * sb, (T / kSBufs) & 1)) { give_up(); ok = false; break; }
-                        PROF_STOP(4);
-                        // the previous item's result has been read out of TMEM: its columns may be overwritten
-                        if (j == j_first && round > 0 && !mbar_wait_bounded(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
-                        PROF_STOP(2);
-                        PROF_TRACE(2, T);
-                        tc_fence_after();
-                        // O += P V and row sums += P 1 in one instruction per 16 keys: N = 80, columns 64-79 of the B
-                        // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, the high parts in
-                        // the first half of the tile's score buffer, the low parts in the second half.
-                        const uint32_t tP = tmem + kSCol + kKeys * sb;
                         const uint64_t dVs = dV + st * kVStage;
+                        for (int u = 0; u < n_sub; ++u, ++U) {
+                            const int sb = U % kSBufs;
+                            if (!warp_wait(bP0 + 8 * sb, (U / kSBufs) & 1)) { give_up(); ok = false; break; }
+                            PROF_STOP(4);
+                            // the previous item's result has been read out of TMEM: its columns may be overwritten
+                            if (first && round > 0 && !warp_wait(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
+                            PROF_STOP(2);
+                            if (lane == 0) PROF_TRACE(2, U);
+                            tc_fence_after();
+                            // O += P V and row sums += P 1 in one instruction per 16 keys: N = 80, columns 64-79 of the B
+                            // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, the high parts
+                            // in the first half of the score buffer, the low parts in the second half.
+                            const uint32_t tP = tmem + kSCol + kSub * sb;
+                            if (leader) {
+#if !(defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_PV))
 #pragma unroll
-                        for (int k = 0; k < kKeys / 16; ++k)
-                            tc_mma_f16_ts(tmem + kOCol, tP + 8 * k, dVs + k * kStepVPv, idesc_pv, j != j_first || k > 0);
-                        if (kSplitP) {
+                                for (int k = 0; k < kSub / 16; ++k)
+                                    tc_mma_f16_ts(tmem + kOCol, tP + 8 * k, dVs + (4 * u + k) * kStepVPv, idesc_pv, !first || k > 0);
+#endif
+                                if (kSplitP && !(VOX_PF_SKIP_PV_LO)) {
 #pragma unroll
-                            for (int k = 0; k < kKeys / 16; ++k)
-                                tc_mma_f16_ts(tmem + kOCol, tP + kKeys / 2 + 8 * k, dVs + k * kStepVPv, idesc_pv, 1);
+                                    for (int k = 0; k < kSub / 16; ++k)
+                                        tc_mma_f16_ts(tmem + kOCol, tP + kSub / 2 + 8 * k, dVs + (4 * u + k) * kStepVPv, idesc_pv, 1);
+                                }
+                                if (kVLo) {  // what rounding V to f16 left over, against the high parts of the weights
+#pragma unroll
+                                    for (int k = 0; k < kSub / 16; ++k)
+                                        tc_mma_f16_ts(tmem + kOCol, tP + 8 * k, dVlo + st * kVStep + (4 * u + k) * kStepV, idesc_lo, 1);
+                                }
+                                tc_commit(bF0 + 8 * sb);  // P.V has retired: the score buffer may be reused, the accumulators are at rest ...
+                                if (u == n_sub - 1) {
+                                    tc_commit(vempty0 + 8 * st);                // ... the V stage may be refilled ...
+                                    if (j_next >= w.n_tiles) tc_commit(bO);     // ... and the item's output is complete
+                                }
+                            }
+                            __syncwarp();
+                            if (lane == 0) PROF_TRACE(3, U);
+                            first = false;
+                            PROF_STOP(0);
                         }
-                        if (kVLo) {  // what rounding V to f16 left over, against the high parts of the weights
-#pragma unroll
-                            for (int k = 0; k < kKeys / 16; ++k)
-                                tc_mma_f16_ts(tmem + kOCol, tP + 8 * k, dVlo + st * kVStep + k * kStepV, idesc_lo, 1);
-                        }
-                        tc_commit(bF0 + 8 * sb);      // P.V has retired: the score buffer may take tile T + 3, the accumulators are at rest ...
-                        tc_commit(vempty0 + 8 * st);  // ... and the V stage may be refilled
-                        if (j_next >= w.n_tiles) tc_commit(bO);  // the item's output is complete
-                        PROF_TRACE(3, T);
                         j = j_next;
                     }
-                    if (aborted()) break;
+                    if (!ok || warp_aborted()) break;
                 }
                 PROF_STOP(0);
-                PROF_FLUSH(4, 5);  // 4 issue, 6 wait output read, 7 wait V tile, 8 wait P
+                if (lane == 0) PROF_FLUSH(4, 5);  // 4 issue, 6 wait output read, 7 wait V tile, 8 wait P
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax warps: two threads per query row
-        // Warps 0-3 take keys 0-63 of every tile, warps 8-11 keys 64-127 (a warp may touch the TMEM lanes of its
-        // quarter, warp % 4, so warps w and w + 8 share rows).  The special-function unit delivers 16 exponentials per
-        // clock: 1024 clocks for a 128 x 128 tile, and only with two warps per scheduler does one warp's arithmetic
-        // overlap the other's exponentials (one warp per scheduler measured 2200 clocks per tile).
+        // ------------------------------------------------------------------ softmax warps: one thread per query row
+        // A key tile is scored and weighted as two score tiles of 64 keys; warps 0-3 take the even score tiles (global
+        // count U), warps 8-11 the odd ones (a warp may touch the TMEM lanes of its quarter, warp % 4, so warps w and
+        // w + 8 share rows).  The two groups are half a step apart, so each scheduler has one warp in its exponentials
+        // (the special-function unit delivers 16 per clock: 1024 clocks for 128 x 128 weights) while the other waits
+        // for scores, loads them or stores weights.  Six score buffers of 64 columns instead of three of 128: a buffer
+        // is held from Q.K^T until P.V has retired, several times longer than the softmax works on it, and the number
+        // of buffers over that time is what bounds the rate of tiles.
         regs_take<kRegsSoftmax>();
-        const int      half  = warp >> 3;                                    // which 64 keys of a tile
+        const int      mine  = warp < 4 ? 0 : warp < 12 ? 1 : 2;             // this warpgroup takes the score tiles U % kGroups == mine
         const int      row   = 32 * (warp & 3) + lane;                       // == TMEM lane
         const uint32_t t_row = tmem + ((uint32_t) (32 * (warp & 3)) << 16);  // this warp's lane quarter
 
         WorkItem w;
-        int      T  = 0;
+        int      U  = 0;
         bool     ok = true;
         PROF_VARS;
         PROF_START();
@@ -530,9 +675,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             // The output row and the row sum accumulate in TMEM across all key tiles, both scaled by
             // 2^(-m_ref): their ratio does not depend on m_ref, so the reference maximum only has to keep
             // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
-            // tile's maximum exceeds it by more than 2^8, which after the first tile is rare.  Both threads of a row
-            // follow the same reference: they trade their halves' maxima every tile.
-            float m_ref = -INFINITY;
+            // tile's maximum exceeds it by more than 2^8, which after the first tile is rare.  The reference of a
+            // row passes from the thread of score tile U to the thread of tile U + 1 through shared memory (row_ref).
             // this row of the mask (rows past n_q are computed on zeros and not stored: they borrow the last row)
             const uint8_t * mrow = nullptr;
             if (kMask)
@@ -541,144 +685,158 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             // the scores are multiplied by `mul` on their way into the exponent: with a mask they have been put into
             // natural units (scale * S + mask) first
             const float mul = kMask ? 1.4426950408889634f : p.scale_log2;
-            const int j_first = next_live<kMask>(w, 0);
-            for (int j = j_first; j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1), ++T) {
-                const int sb = T % kSBufs;
-                const int k0 = j * kKeys + 64 * half;  // this thread's first key
-                uint4     mv[8];
-                if (kMask) {  // requested before the wait for the scores; chunks of 8 keys lie wholly inside or outside n_kv
-                    const uint4 * mp = reinterpret_cast<const uint4 *>(mrow + (size_t) k0 * 2);
+            bool  first = true;  // the item's first score tile sets the reference
+            for (int j = next_live<kMask>(w, 0); ok && j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1)) {
+                const int n_sub = sub_tiles(p, w, j);
+                for (int u = 0; u < n_sub; ++u, ++U) {
+                    const bool is_first = first;
+                    first = false;
+                    if (U % kGroups != mine) continue;  // another group's tile
+                    const int sb = U % kSBufs;
+                    const int k0 = j * kKeys + kSub * u;  // the score tile's first key
+                    uint4     mv[8];
+                    if (kMask) {  // requested before the wait for the scores; chunks of 8 keys lie wholly inside or outside n_kv
+                        const uint4 * mp = reinterpret_cast<const uint4 *>(mrow + (size_t) k0 * 2);
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) mv[c] = k0 + 8 * c < p.n_kv ? __ldg(mp + c) : make_uint4(0u, 0u, 0u, 0u);
-                }
-                PROF_STOP(0);
-                if (!mbar_wait_bounded(bS0 + 8 * sb, (T / kSBufs) & 1)) { give_up(); ok = false; break; }
-                PROF_STOP(1);
-                PROF_COUNT(7, 1);
-                if (tid == 0) PROF_TRACE(0, T);
-                tc_fence_after();
+                        for (int c = 0; c < 8; ++c) mv[c] = k0 + 8 * c < p.n_kv ? __ldg(mp + c) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    PROF_STOP(0);
+                    if (!mbar_wait_bounded(bS0 + 8 * sb, (U / kSBufs) & 1)) { give_up(); ok = false; break; }
+                    PROF_STOP(1);
+                    PROF_COUNT(7, 1);
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(0, U);
+                    tc_fence_after();
 #if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_NOSOFTMAX)  // developer build: the copy and MMA structure alone
-                if (j == j_first) m_ref = 0.0f;
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bP0 + 8 * sb);
-                continue;
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bP0 + 8 * sb);
+                    continue;
 #endif
-                const uint32_t t_s    = t_row + kSCol + kKeys * sb;  // the tile's score buffer; this thread's scores start 64 * half in
-                const bool     masked = k0 + 63 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // uniform over the warpgroup: the half may be cut
-                // 32-column blocks of this half with at least one key some row of this warp sees (warp-uniform)
-                const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
-                uint32_t       r[64];
-                if (n_live == 2) {
-                    tmem_ld64_sync(t_s + 64 * half, r);
-                } else {
+                    const uint32_t t_s    = t_row + kSCol + kSub * sb;  // the tile's score buffer
+                    const bool     masked = k0 + kSub - 1 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // uniform over the group: the tile may be cut
+                    // 32-column blocks of the tile with at least one key some row of this warp sees (warp-uniform)
+                    const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
+                    uint32_t       r[kSub];
+                    if (n_live == 2) {
+                        tmem_ld64_sync(t_s, r);
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) r[i] = 0xff800000u;  // -inf: no weight
-                    if (n_live == 1) tmem_ld32_sync(t_s + 64 * half, r);
-                }
-                PROF_STOP(10);
-                if (kMask) {
+                        for (int i = 0; i < kSub; ++i) r[i] = 0xff800000u;  // -inf: no weight
+                        if (n_live == 1) tmem_ld32_sync(t_s, r);
+                    }
+                    PROF_STOP(10);
+                    if (kMask) {
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const uint32_t w4[4] = {mv[c].x, mv[c].y, mv[c].z, mv[c].w};
+                        for (int c = 0; c < 8; ++c) {
+                            const uint32_t w4[4] = {mv[c].x, mv[c].y, mv[c].z, mv[c].w};
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 m2 = __half22float2(*reinterpret_cast<const __half2 *>(&w4[i]));
-                            r[8 * c + 2 * i]     = __float_as_uint(fmaf(__uint_as_float(r[8 * c + 2 * i]), p.scale, m2.x));
-                            r[8 * c + 2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(r[8 * c + 2 * i + 1]), p.scale, m2.y));
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 m2 = __half22float2(*reinterpret_cast<const __half2 *>(&w4[i]));
+                                r[8 * c + 2 * i]     = __float_as_uint(fmaf(__uint_as_float(r[8 * c + 2 * i]), p.scale, m2.x));
+                                r[8 * c + 2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(r[8 * c + 2 * i + 1]), p.scale, m2.y));
+                            }
                         }
                     }
-                }
-                if (masked) {  // only the tiles the causal diagonal or the end of the keys cuts through
+                    if (masked) {  // only the tiles the causal diagonal or the end of the keys cuts through
 #pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (k0 + i > limit) r[i] = 0xff800000u;
-                }
-                float cmax;
-                {
-                    float t0 = -INFINITY, t1 = -INFINITY;
-#pragma unroll
-                    for (int i = 0; i < 64; i += 4) {
-                        t0 = max3(t0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                        t1 = max3(t1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                        for (int i = 0; i < kSub; ++i)
+                            if (k0 + i > limit) r[i] = 0xff800000u;
                     }
-                    cmax = fmaxf(t0, t1) * mul;
-                }
-                // Trade the maxima of the two halves.  The barrier also tells each thread that its partner holds its
-                // scores in registers: the weights written below overwrite both halves of the buffer.
-                row_max[T & 1][half][row] = cmax;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bX0 + 8 * (T & 1));
-                if (!mbar_wait_bounded(bX0 + 8 * (T & 1), (T >> 1) & 1)) { give_up(); ok = false; break; }
-                cmax = fmaxf(cmax, row_max[T & 1][half ^ 1][row]);
-                PROF_STOP(11);
-                // The weights are written only after the whole tile has been looked at, so a raise of the
-                // reference needs no second pass.  tcgen05.ld/st are warp-collective: the decision to rescale is
-                // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.  Both threads
-                // of a row take the same decision; the one of the first half rescales the accumulators.
-                // With a mask a row may have seen no key yet: its reference stays -inf (any finite maximum then
-                // raises it, with a factor of 0 for accumulators that hold 0) and its weights are 2^(-inf - 0) = 0.
-                if (j == j_first) {
-                    m_ref = cmax;  // without a mask key 0 is visible to every row: finite
-                } else {
-                    const bool raise = cmax > m_ref + 8.0f;
-                    if (__any_sync(0xffffffffu, raise)) {
-                        const float f = raise ? ex2_approx(m_ref - cmax) : 1.0f;
-                        if (raise) m_ref = cmax;
-                        if (half == 0) {
-                            // the accumulators are at rest once P.V of the previous tile has retired
-                            if (!mbar_wait_bounded(bF0 + 8 * ((T - 1) % kSBufs), ((T - 1) / kSBufs) & 1)) { give_up(); ok = false; break; }
+                    float cmax;
+                    {
+                        float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < kSub; i += 4) {
+                            t0 = max3(t0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                            t1 = max3(t1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                        }
+                        cmax = fmaxf(t0, t1) * mul;
+                    }
+                    // The row's reference after score tile U - 1, from the thread of the other group that took that
+                    // tile.  The wait is made for every tile but the very first, also where the value is not used (first
+                    // tile of an item): it keeps the two groups within one tile of each other, so that neither barrier
+                    // can complete twice between two looks of its waiter, and a slot of row_ref is rewritten (tile U + 2)
+                    // only after its reader (tile U + 1) has published in turn, which it does after reading.
+                    if (U > 0 && !mbar_wait_bounded(bM0 + 8 * ((U - 1) % kGroups), ((U - 1) / kGroups) & 1)) { give_up(); ok = false; break; }
+                    PROF_STOP(11);
+                    // The weights are written only after the whole tile has been looked at, so a raise of the
+                    // reference needs no second pass.  tcgen05.ld/st are warp-collective: the decision to rescale is
+                    // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.
+                    // With a mask a row may have seen no key yet: its reference stays -inf (any finite maximum then
+                    // raises it, with a factor of 0 for accumulators that hold 0) and its weights are 2^(-inf - 0) = 0.
+                    float m_ref;
+                    if (is_first) {
+                        m_ref = cmax;  // without a mask key 0 is visible to every row: finite
+                    } else {
+                        m_ref = row_ref[(U - 1) % kGroups][row];
+                        const bool raise = cmax > m_ref + 8.0f;
+                        if (__any_sync(0xffffffffu, raise)) {
+                            const float f = raise ? ex2_approx(m_ref - cmax) : 1.0f;
+                            if (raise) m_ref = cmax;
+                            // the accumulators are at rest once P.V of the previous score tile has retired
+                            if (!mbar_wait_bounded(bF0 + 8 * ((U - 1) % kSBufs), ((U - 1) / kSBufs) & 1)) { give_up(); ok = false; break; }
                             rescale_accumulators(t_row, f);
                         }
                     }
-                }
-                const float m_sub = kMask && m_ref == -INFINITY ? 0.0f : m_ref;
-                // P = 2^(c*S - m_ref), 16 keys (8 columns of packed f16 pairs) at a time: k-step 4 * half + g of the tile.
-                if (kSplitP) {
-                    // hi + lo: two packed f16 tiles (hi: columns 0-63 of the buffer, lo: columns 64-127).  hi keeps the
-                    // top 11 bits of the f32 weight (a mask: exact in f16 for every weight above 2^-14, and the weights
-                    // that matter are >= 1 for the row's largest), lo is the exact remainder rounded to f16: together ~21
-                    // bits, so that the result does not depend on how the rounding errors of a few large weights happen
-                    // to fall against the spread of V.
+                    if (kPublishAt == 0 || !kSplitP) {
+                        row_ref[U % kGroups][row] = m_ref;
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bM0 + 8 * (U % kGroups));
+                    }
+                    const float m_sub = kMask && m_ref == -INFINITY ? 0.0f : m_ref;
+                    // P = 2^(c*S - m_ref), 16 keys (8 columns of packed f16 pairs) at a time: k-step g of the score tile.
+                    if (kSplitP) {
+                        // hi + lo: two packed f16 tiles (hi: columns 0-31 of the buffer, lo: columns 32-63).  hi keeps the
+                        // top 11 bits of the f32 weight (a mask: exact in f16 for every weight above 2^-14, and the weights
+                        // that matter are >= 1 for the row's largest), lo is the exact remainder rounded to f16: together
+                        // ~21 bits, so that the result does not depend on how the rounding errors of a few large weights
+                        // happen to fall against the spread of V.  The thread holds every score of its row in registers,
+                        // so the weights may overwrite the buffer in any order.
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint32_t hi[8], lo[8];
+                        for (int g = 0; g < kSub / 16; ++g) {
+                            uint32_t hi[8], lo[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float p0 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), mul, -m_sub));
-                            const float p1 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), mul, -m_sub));
-                            const float h0 = __uint_as_float(__float_as_uint(p0) & 0xFFFFE000u);
-                            const float h1 = __uint_as_float(__float_as_uint(p1) & 0xFFFFE000u);
-                            hi[i] = pack_half2(h0, h1);
-                            lo[i] = pack_half2(p0 - h0, p1 - h1);
+                            for (int i = 0; i < 8; ++i) {
+                                const float p0 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), mul, -m_sub));
+                                const float p1 = ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), mul, -m_sub));
+                                const float h0 = __uint_as_float(__float_as_uint(p0) & 0xFFFFE000u);
+                                const float h1 = __uint_as_float(__float_as_uint(p1) & 0xFFFFE000u);
+                                hi[i] = pack_half2(h0, h1);
+                                lo[i] = pack_half2(p0 - h0, p1 - h1);
+                            }
+                            tmem_st8_nowait(t_s + 8 * g, hi);
+                            tmem_st8_nowait(t_s + kSub / 2 + 8 * g, lo);
+                            if (g + 1 == kPublishAt) {  // see kPublishAt
+                                row_ref[U % kGroups][row] = m_ref;
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(bM0 + 8 * (U % kGroups));
+                            }
                         }
-                        tmem_st8_nowait(t_s + 8 * (4 * half + g), hi);
-                        tmem_st8_nowait(t_s + kKeys / 2 + 8 * (4 * half + g), lo);
-                    }
-                } else {
+                    } else {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint32_t h[8];
+                        for (int g = 0; g < kSub / 16; ++g) {
+                            uint32_t h[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), mul, -m_sub)),
-                                              ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), mul, -m_sub)));
-                        tmem_st8_nowait(t_s + 8 * (4 * half + g), h);
+                            for (int i = 0; i < 8; ++i)
+                                h[i] = pack_half2(ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i]), mul, -m_sub)),
+                                                  ex2_approx(fmaf(__uint_as_float(r[16 * g + 2 * i + 1]), mul, -m_sub)));
+                            tmem_st8_nowait(t_s + 8 * g, h);
+                        }
                     }
+                    PROF_STOP(2);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bP0 + 8 * sb);  // this warp's rows of P are in TMEM
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(1, U);
+                    PROF_STOP(3);
                 }
-                PROF_STOP(2);
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bP0 + 8 * sb);  // this warp's rows of its half of P are in TMEM
-                if (tid == 0) PROF_TRACE(1, T);
-                PROF_STOP(3);
             }
             if (!ok || aborted()) break;
             PROF_COUNT(9, 1);
         }
-        // 0 other, 1 wait S, 2 softmax blocks, 3 store wait + signal, 7 tiles, 9 items, 10 wait for the scores' load, 11 tile maximum + trade
-        if (lane == 0 && half == 0) PROF_FLUSH(9 + 0, 12);
+        // 0 other, 1 wait S, 2 softmax blocks, 3 store wait + signal, 7 tiles, 9 items, 10 wait for the scores' load, 11 tile maximum + reference
+        if (lane == 0 && mine == 0) PROF_FLUSH(9 + 0, 12);
     }
 
     // common exit: every role has left its loop; release TMEM

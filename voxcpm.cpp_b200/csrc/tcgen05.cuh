@@ -36,6 +36,12 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One lane of a converged warp (the same one every time): the lane that issues for the warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t is_leader;
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\tselp.u32 %0, 1, 0, e;\n\t}" : "=r"(is_leader));
+    return is_leader != 0;
+}
 // Warpgroups trade registers after launch: every warp of a group of four executes the same one.
 template <int N>
 __device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -143,6 +149,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr, uint32_t n
 constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
     return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
 }
+// (The format fields of A and B, bits 7-9 and 10-12, must agree: a bf16 A operand against an f16 B operand was
+// answered with "an illegal instruction was encountered".)
 
 
 }  // namespace vox
