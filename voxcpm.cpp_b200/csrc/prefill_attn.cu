@@ -95,10 +95,17 @@ namespace {
 
 // Developer build only (-DVOX_ATTN_DEVELOPER -DVOX_PREFILL_PROFILE): per-role cycle counters (SM clock, summed over
 // CTAs with atomics) that vox_debug_prefill_profile copies out.  Compiled out of the product library.
-#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
+// With -DVOX_PREFILL_TRACE alone only the time stamps of CTA 0 are taken (one store per event: the counters cost the
+// roles a hundred clocks per tile).
+#if defined(VOX_ATTN_DEVELOPER) && (defined(VOX_PREFILL_PROFILE) || defined(VOX_PREFILL_TRACE))
 __device__ unsigned long long g_prof[32];
-__device__ long long g_trace[4][64];  // CTA 0, first 64 tiles: scores seen, weights signalled, weights seen, MMAs issued
+// CTA 0, first 64 score tiles.  0 scores seen, 1 weights signalled, 2 weights seen by the output issuer, 3 its MMAs issued
+// and committed, 4 buffer seen free by the score issuer, 5 its MMAs issued and committed; softmax thread: 11 before the
+// wait for the scores, 6 scores loaded, 7 maximum taken, 8 reference seen, 9 weights computed, 10 their stores complete
+__device__ long long g_trace[12][64];
 #define PROF_TRACE(k, T) do { if (blockIdx.x == 0 && (T) < 64) g_trace[k][T] = clock64(); } while (0)
+#endif
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
 #define PROF_VARS long long pf_t = 0, pf_acc[12] = {0}
 #define PROF_START() pf_t = clock64()
 #define PROF_STOP(i) do { const long long pf_n = clock64(); pf_acc[i] += pf_n - pf_t; pf_t = pf_n; } while (0)
@@ -110,7 +117,9 @@ __device__ long long g_trace[4][64];  // CTA 0, first 64 tiles: scores seen, wei
 #define PROF_STOP(i)
 #define PROF_COUNT(i, n)
 #define PROF_FLUSH(base, n)
+#if !(defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_TRACE))
 #define PROF_TRACE(k, T)
+#endif
 #endif
 
 // Developer builds only (-DVOX_ATTN_DEVELOPER): VOX_PREFILL_NOSOFTMAX, VOX_PF_SKIP_QK, VOX_PF_SKIP_PV, VOX_PF_SKIP_LOAD and
@@ -542,6 +551,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             const int sb = U % kSBufs;
                             if (U >= kSBufs && !warp_wait(bF0 + 8 * sb, ((U / kSBufs) - 1) & 1)) { give_up(); ok = false; break; }
                             PROF_STOP(1);
+                            if (lane == 0) PROF_TRACE(4, U);
                             tc_fence_after();
                             const uint32_t dS  = tmem + kSCol + kSub * sb;
                             const uint64_t dKs = st * kStage + u * kSubK;
@@ -561,6 +571,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                                 if (u == n_sub - 1) tc_commit(kempty0 + 8 * st);  // ... and the K stage may be refilled
                             }
                             __syncwarp();
+                            if (lane == 0) PROF_TRACE(5, U);
                             PROF_STOP(0);
                         }
                     }
@@ -701,6 +712,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         for (int c = 0; c < 8; ++c) mv[c] = k0 + 8 * c < p.n_kv ? __ldg(mp + c) : make_uint4(0u, 0u, 0u, 0u);
                     }
                     PROF_STOP(0);
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(11, U);
                     if (!mbar_wait_bounded(bS0 + 8 * sb, (U / kSBufs) & 1)) { give_up(); ok = false; break; }
                     PROF_STOP(1);
                     PROF_COUNT(7, 1);
@@ -710,6 +722,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bP0 + 8 * sb);
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(1, U);
                     continue;
 #endif
                     const uint32_t t_s    = t_row + kSCol + kSub * sb;  // the tile's score buffer
@@ -725,6 +738,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         if (n_live == 1) tmem_ld32_sync(t_s, r);
                     }
                     PROF_STOP(10);
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(6, U);
                     if (kMask) {
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
@@ -757,8 +771,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     // tile of an item): it keeps the two groups within one tile of each other, so that neither barrier
                     // can complete twice between two looks of its waiter, and a slot of row_ref is rewritten (tile U + 2)
                     // only after its reader (tile U + 1) has published in turn, which it does after reading.
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(7, U);
                     if (U > 0 && !mbar_wait_bounded(bM0 + 8 * ((U - 1) % kGroups), ((U - 1) / kGroups) & 1)) { give_up(); ok = false; break; }
                     PROF_STOP(11);
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(8, U);
                     // The weights are written only after the whole tile has been looked at, so a raise of the
                     // reference needs no second pass.  tcgen05.ld/st are warp-collective: the decision to rescale is
                     // taken per warp (any lane), and lanes that do not need it take part with a factor of 1.
@@ -824,7 +840,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         }
                     }
                     PROF_STOP(2);
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(9, U);
                     tmem_wait_st();
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(10, U);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bP0 + 8 * sb);  // this warp's rows of P are in TMEM
@@ -1149,9 +1167,9 @@ int launch_prefill_full(vox_engine * e, const vox_attn_args * a, void * workspac
 
 extern "C" {
 
-#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
+#if defined(VOX_ATTN_DEVELOPER) && (defined(VOX_PREFILL_PROFILE) || defined(VOX_PREFILL_TRACE))
 int vox_debug_prefill_trace(long long * out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 4 * 64) != cudaSuccess;
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 12 * 64) != cudaSuccess;
 }
 int vox_debug_prefill_profile(unsigned long long * out, int reset) {
     if (out && cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
