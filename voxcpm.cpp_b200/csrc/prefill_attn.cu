@@ -259,6 +259,17 @@ __device__ __forceinline__ int next_live(const WorkItem & w, int from) {
     return rest ? from + __ffsll((long long) rest) - 1 : w.n_tiles;
 }
 
+// A counter modulo n with the parity of its turns: the slot and the barrier phase of tile number t are t % n and
+// (t / n) & 1, kept by stepping instead of dividing (the roles' loop control is one dependent chain per tile, and a
+// warp that runs it shares its scheduler with warps in their arithmetic).
+struct Wheel {
+    int      slot  = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void step(int n) {
+        if (++slot == n) { slot = 0; phase ^= 1u; }
+    }
+};
+
 // Score tiles (64 keys) of key tile j that an item walks: the second is left out when no row of the item can see a key
 // of it (the diagonal tile of a causal item; the last tile of a key sequence that ends in its first half).
 __device__ __forceinline__ int sub_tiles(const PrefillParams & p, const WorkItem & w, int j) {
@@ -481,14 +492,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (lane == 0) {
                 WorkItem w;
                 int      T  = 0;
+                Wheel    tw;
                 bool     ok = true;
                 PROF_VARS;
                 PROF_START();
                 for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
                     const int kvh = w.head / p.gqa;
-                    for (int j = next_live<kMask>(w, 0); j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1), ++T) {
-                        const int      st = T % kSt;
-                        const uint32_t ph = ((T / kSt) - 1) & 1;
+                    for (int j = next_live<kMask>(w, 0); j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1), ++T, tw.step(kSt)) {
+                        const int      st = tw.slot;
+                        const uint32_t ph = tw.phase ^ 1u;  // the stage's previous turn
                         PROF_STOP(0);
                         if (T >= kSt && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
                         PROF_STOP(1);
@@ -534,6 +546,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 constexpr uint64_t kSubK   = (kSub * 128) >> 4;  // from the first 64 keys of a K tile to the last
                 WorkItem wq;
                 int      Tk = 0, U = 0;  // key tiles and score tiles so far, over all items
+                Wheel    tw, uw;         // their ring stage and score buffer
                 bool     ok = true;
                 PROF_VARS;
                 PROF_START();
@@ -542,14 +555,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     if (!warp_wait(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) { give_up(); break; }  // the item's Q tile is in place
                     PROF_STOP(2);
                     const uint64_t dQi = dQ + (rq % kQBufs) * kQBuf;
-                    for (int jq = next_live<kMask>(wq, 0); ok && jq < wq.n_tiles && !warp_aborted(); jq = next_live<kMask>(wq, jq + 1), ++Tk) {
-                        const int st = Tk % kSt, n_sub = sub_tiles(p, wq, jq);
+                    for (int jq = next_live<kMask>(wq, 0); ok && jq < wq.n_tiles && !warp_aborted(); jq = next_live<kMask>(wq, jq + 1), ++Tk, tw.step(kSt)) {
+                        const int st = tw.slot, n_sub = sub_tiles(p, wq, jq);
                         PROF_STOP(0);
-                        if (!warp_wait(kfull0 + 8 * st, (Tk / kSt) & 1)) { give_up(); ok = false; break; }
+                        if (!warp_wait(kfull0 + 8 * st, tw.phase)) { give_up(); ok = false; break; }
                         PROF_STOP(2);
-                        for (int u = 0; u < n_sub; ++u, ++U) {
-                            const int sb = U % kSBufs;
-                            if (U >= kSBufs && !warp_wait(bF0 + 8 * sb, ((U / kSBufs) - 1) & 1)) { give_up(); ok = false; break; }
+                        for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
+                            const int sb = uw.slot;
+                            if (U >= kSBufs && !warp_wait(bF0 + 8 * sb, uw.phase ^ 1u)) { give_up(); ok = false; break; }
                             PROF_STOP(1);
                             if (lane == 0) PROF_TRACE(4, U);
                             tc_fence_after();
@@ -599,21 +612,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_VARS;
                 WorkItem w;
                 int      Tk = 0, U = 0;
+                Wheel    tw, uw;
                 bool     ok = true;
                 PROF_START();
                 for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
                     const int j_first = next_live<kMask>(w, 0);
                     bool      first   = true;  // the item's first score tile: O is overwritten, not added to
-                    for (int j = j_first; ok && j < w.n_tiles && !warp_aborted(); ++Tk) {
-                        const int st = Tk % kSt, n_sub = sub_tiles(p, w, j);
+                    for (int j = j_first; ok && j < w.n_tiles && !warp_aborted(); ++Tk, tw.step(kSt)) {
+                        const int st = tw.slot, n_sub = sub_tiles(p, w, j);
                         const int j_next = next_live<kMask>(w, j + 1);
                         PROF_STOP(0);
-                        if (!warp_wait(vfull0 + 8 * st, (Tk / kSt) & 1)) { give_up(); ok = false; break; }
+                        if (!warp_wait(vfull0 + 8 * st, tw.phase)) { give_up(); ok = false; break; }
                         PROF_STOP(3);
                         const uint64_t dVs = dV + st * kVStage;
-                        for (int u = 0; u < n_sub; ++u, ++U) {
-                            const int sb = U % kSBufs;
-                            if (!warp_wait(bP0 + 8 * sb, (U / kSBufs) & 1)) { give_up(); ok = false; break; }
+                        for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
+                            const int sb = uw.slot;
+                            if (!warp_wait(bP0 + 8 * sb, uw.phase)) { give_up(); ok = false; break; }
                             PROF_STOP(4);
                             // the previous item's result has been read out of TMEM: its columns may be overwritten
                             if (first && round > 0 && !warp_wait(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
@@ -675,6 +689,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
         WorkItem w;
         int      U  = 0;
+        Wheel    uw;  // the score buffer of tile U and the phase of its barriers
         bool     ok = true;
         PROF_VARS;
         PROF_START();
@@ -697,13 +712,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             // natural units (scale * S + mask) first
             const float mul = kMask ? 1.4426950408889634f : p.scale_log2;
             bool  first = true;  // the item's first score tile sets the reference
+            // last key every row of the item sees, and the key tile that holds it
+            const int uncut = min(w.q0 + p.causal_offset, p.n_kv - 1), cut_from = uncut / kKeys;
             for (int j = next_live<kMask>(w, 0); ok && j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1)) {
                 const int n_sub = sub_tiles(p, w, j);
-                for (int u = 0; u < n_sub; ++u, ++U) {
+                for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
                     const bool is_first = first;
                     first = false;
                     if (U % kGroups != mine) continue;  // another group's tile
-                    const int sb = U % kSBufs;
+                    const int sb = uw.slot;
                     const int k0 = j * kKeys + kSub * u;  // the score tile's first key
                     uint4     mv[8];
                     if (kMask) {  // requested before the wait for the scores; chunks of 8 keys lie wholly inside or outside n_kv
@@ -713,7 +730,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     PROF_STOP(0);
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(11, U);
-                    if (!mbar_wait_bounded(bS0 + 8 * sb, (U / kSBufs) & 1)) { give_up(); ok = false; break; }
+                    if (!mbar_wait_bounded(bS0 + 8 * sb, uw.phase)) { give_up(); ok = false; break; }
                     PROF_STOP(1);
                     PROF_COUNT(7, 1);
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(0, U);
@@ -726,7 +743,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     continue;
 #endif
                     const uint32_t t_s    = t_row + kSCol + kSub * sb;  // the tile's score buffer
-                    const bool     masked = k0 + kSub - 1 > min(w.q0 + p.causal_offset, p.n_kv - 1);  // uniform over the group: the tile may be cut
+                    // uniform over the group: the tile may be cut (no key tile before the one that holds `uncut` can be)
+                    const bool     masked = j >= cut_from && k0 + kSub - 1 > uncut;
                     // 32-column blocks of the tile with at least one key some row of this warp sees (warp-uniform)
                     const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
                     uint32_t       r[kSub];
