@@ -102,7 +102,7 @@ __device__ unsigned long long g_prof[32];
 // CTA 0, first 64 score tiles.  0 scores seen, 1 weights signalled, 2 weights seen by the output issuer, 3 its MMAs issued
 // and committed, 4 buffer seen free by the score issuer, 5 its MMAs issued and committed; softmax thread: 11 before the
 // wait for the scores, 6 scores loaded, 7 maximum taken, 8 reference seen, 9 weights computed, 10 their stores complete
-__device__ long long g_trace[12][64];
+__device__ long long g_trace[14][64];
 #define PROF_TRACE(k, T) do { if (blockIdx.x == 0 && (T) < 64) g_trace[k][T] = clock64(); } while (0)
 #endif
 #if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
@@ -719,7 +719,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
                     const bool is_first = first;
                     first = false;
+                    if (U % kGroups != mine && (warp & 3) == 0 && lane == 0) PROF_TRACE(12, U);  // loop top at the other group's tile
                     if (U % kGroups != mine) continue;  // another group's tile
+                    if ((warp & 3) == 0 && lane == 0) PROF_TRACE(13, U);
                     const int sb = uw.slot;
                     const int k0 = j * kKeys + kSub * u;  // the score tile's first key
                     uint4     mv[8];
@@ -1187,7 +1189,7 @@ extern "C" {
 
 #if defined(VOX_ATTN_DEVELOPER) && (defined(VOX_PREFILL_PROFILE) || defined(VOX_PREFILL_TRACE))
 int vox_debug_prefill_trace(long long * out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 12 * 64) != cudaSuccess;
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 14 * 64) != cudaSuccess;
 }
 int vox_debug_prefill_profile(unsigned long long * out, int reset) {
     if (out && cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
