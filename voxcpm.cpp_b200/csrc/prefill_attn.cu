@@ -350,6 +350,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         atomicOr(p.status, kStatusTimeout);
         atomicExch(&abort_flag, 1);
     };
+    // Looked at once per item, not per tile (a shared-memory load in a role's loop control waits behind the role's own
+    // TMEM stores and barrier operations: it measured 380 clocks per tile in the softmax warps).  A role that another
+    // role's give-up leaves waiting inside an item runs into its own bounded wait.
     auto aborted = [&]() { return *reinterpret_cast<volatile int *>(&abort_flag) != 0; };
     // the same for a whole warp that must stay together: every lane takes the same way out
     auto warp_aborted = [&]() { return __any_sync(0xffffffffu, aborted()) != 0; };
@@ -498,7 +501,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_START();
                 for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
                     const int kvh = w.head / p.gqa;
-                    for (int j = next_live<kMask>(w, 0); j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1), ++T, tw.step(kSt)) {
+                    for (int j = next_live<kMask>(w, 0); j < w.n_tiles; j = next_live<kMask>(w, j + 1), ++T, tw.step(kSt)) {
                         const int      st = tw.slot;
                         const uint32_t ph = tw.phase ^ 1u;  // the stage's previous turn
                         PROF_STOP(0);
@@ -555,7 +558,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     if (!warp_wait(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) { give_up(); break; }  // the item's Q tile is in place
                     PROF_STOP(2);
                     const uint64_t dQi = dQ + (rq % kQBufs) * kQBuf;
-                    for (int jq = next_live<kMask>(wq, 0); ok && jq < wq.n_tiles && !warp_aborted(); jq = next_live<kMask>(wq, jq + 1), ++Tk, tw.step(kSt)) {
+                    for (int jq = next_live<kMask>(wq, 0); ok && jq < wq.n_tiles; jq = next_live<kMask>(wq, jq + 1), ++Tk, tw.step(kSt)) {
                         const int st = tw.slot, n_sub = sub_tiles(p, wq, jq);
                         PROF_STOP(0);
                         if (!warp_wait(kfull0 + 8 * st, tw.phase)) { give_up(); ok = false; break; }
@@ -618,7 +621,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
                     const int j_first = next_live<kMask>(w, 0);
                     bool      first   = true;  // the item's first score tile: O is overwritten, not added to
-                    for (int j = j_first; ok && j < w.n_tiles && !warp_aborted(); ++Tk, tw.step(kSt)) {
+                    for (int j = j_first; ok && j < w.n_tiles; ++Tk, tw.step(kSt)) {
                         const int st = tw.slot, n_sub = sub_tiles(p, w, j);
                         const int j_next = next_live<kMask>(w, j + 1);
                         PROF_STOP(0);
@@ -714,7 +717,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             bool  first = true;  // the item's first score tile sets the reference
             // last key every row of the item sees, and the key tile that holds it
             const int uncut = min(w.q0 + p.causal_offset, p.n_kv - 1), cut_from = uncut / kKeys;
-            for (int j = next_live<kMask>(w, 0); ok && j < w.n_tiles && !aborted(); j = next_live<kMask>(w, j + 1)) {
+            for (int j = next_live<kMask>(w, 0); ok && j < w.n_tiles; j = next_live<kMask>(w, j + 1)) {
                 const int n_sub = sub_tiles(p, w, j);
                 for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
                     const bool is_first = first;
