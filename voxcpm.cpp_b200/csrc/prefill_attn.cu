@@ -160,10 +160,10 @@ constexpr int kRegsLaunch = kGroups == 3 ? 96 : 128, kRegsSoftmax = kGroups == 3
 static_assert(kRegsLaunch == 65536 / kThreadsPf / 8 * 8, "what a thread holds at launch");
 static_assert(kGroups * (kRegsSoftmax - kRegsLaunch) <= (kRegsLaunch - kRegsControl) + (kRegsLaunch - kRegsIo), "the trade cannot block");
 static_assert((kGroups * kRegsSoftmax + kRegsControl + kRegsIo) * 128 <= 65536, "the CTA's registers fit the SM");
-// TMEM columns: three score buffers of 128 columns (tile T uses buffer T % 3; its weights, packed f16, replace its scores:
-// high parts in the first 64 columns, low parts in the last 64) and the output row with its row sum
+// TMEM columns: six score buffers of 64 columns (score tile U uses buffer U % 6; its weights, packed f16, replace its
+// scores: high parts in the first 32 columns, low parts in the last 32) and the output row with its row sum
 constexpr int kTmemCols  = 512;
-constexpr int kSCol      = 0;              // S: 3 x 128 columns
+constexpr int kSCol      = 0;              // S: 6 x 64 columns
 constexpr int kOCol      = kSBufs * kSub;  // O: 64 columns, row sums: 16 columns behind them
 constexpr int kOnesBytes = 2048;           // 16 keys x 64 ones, addressed as columns 64-79 of every 16-key step of every V tile
 // With kVLo (K/V expanded from q8_0 or f32) a K or V stage holds two tiles, the f16 values and what their rounding left
@@ -300,14 +300,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // Barriers.  Per ring stage (tile T uses stage T % kSt): K landed / K stage free, V landed / V stage free; the
-    // producer is the only waiter of the two "free" ones.  Per score buffer (tile T uses buffer T % 3): scores ready
-    // (Q.K^T retired), weights ready (one arrival per softmax warp), buffer free (P.V retired: the weights have been used
-    // and the accumulators are at rest).  A barrier of buffer b completes once per tile of that buffer, and each of the
-    // three events of tile T + 3 needs the one its waiter is looking for in tile T to have been seen, so no barrier can
-    // complete twice between two looks of a waiter (a parity wait cannot tell two completed phases from none).
-    // Per item: Q in place (one per Q buffer), output complete, output read.  Per tile parity: the rows'
-    // reference maxima after the tile, published by the softmax group that took it for the group that takes the next.
+    // Barriers.  Per ring stage (key tile T uses stage T % kSt): K landed / K stage free, V landed / V stage free; the
+    // producer is the only waiter of the two "free" ones.  Per score buffer (score tile U uses buffer U % 6): scores ready
+    // (Q.K^T retired), weights ready (one arrival per warp of the softmax group that took the tile), buffer free (P.V
+    // retired: the weights have been used and the accumulators are at rest).  A barrier of buffer b completes once per
+    // score tile of that buffer, and each of the three events of tile U + 6 needs the one its waiter is looking for in
+    // tile U to have been seen, so no barrier can complete twice between two looks of a waiter (a parity wait cannot
+    // tell two completed phases from none).  Per item: Q in place (one per Q buffer), output complete, output read.
+    // Per score tile parity: the rows' reference maxima after the tile, published by the softmax group that took it for
+    // the group that takes the next.
     const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = kfull0 + 8 * kStages, vfull0 = kempty0 + 8 * kStages,
                    vempty0 = vfull0 + 8 * kStages, bS0 = vempty0 + 8 * kStages, bP0 = bS0 + 8 * kSBufs, bF0 = bP0 + 8 * kSBufs,
                    bQ0 = bF0 + 8 * kSBufs, bO = bQ0 + 8 * kQBufs, bOfree = bO + 8, bM0 = bOfree + 8;
