@@ -560,9 +560,12 @@ def test_prefill_rising_logits_move_the_reference_maximum(engine, oracle, vo):
     assert rel_err(out.cpu().numpy(), ref) < TOL["f16"]
 
 
-@pytest.mark.parametrize("n_q, n_kv", [(200, 328), (130, 207), (64, 512), (1, 300)])
+@pytest.mark.parametrize("n_q, n_kv", [(200, 328), (130, 207), (64, 512), (1, 300), (300, 503), (600, 640)])
 def test_prefill_with_past(n_q, n_kv, engine, oracle, vo):
-    """A chunk of n_q new tokens attending over n_kv - n_q cached ones and, causally, itself."""
+    """A chunk of n_q new tokens attending over n_kv - n_q cached ones and, causally, itself.  Offsets that are no
+    multiple of 16 put the 16 tokens of a work item on both sides of a 128-key boundary: the causal cut then reaches
+    into the item's last two key tiles, and the second 64-key half of the last one is walked or left out row block by
+    row block."""
     rng = np.random.default_rng(n_q * 7 + n_kv)
     B = 2
     q = rng.standard_normal((B, H, n_q, D)).astype(np.float16).astype(np.float32)
