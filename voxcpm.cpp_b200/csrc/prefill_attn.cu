@@ -200,8 +200,11 @@ struct PrefillParams {
     size_t          m_nb1, m_nb2, m_nb3;
     int             m_ne2, m_ne3;
     float           scale;
-    // per (mask plane, query tile): bit j set when key tile j holds a finite mask value for some row (NULL: not known)
-    const unsigned long long * tile_live;
+    // per (mask plane, query tile): 64 bytes, byte j set when key tile j holds a finite mask value for some row (NULL: not
+    // known)
+    const uint8_t * tile_live;
+    // the same shape: byte j set when the mask adds 0 to every score of key tile j (the kernel then does not read it there)
+    const uint8_t * tile_zero;
 };
 
 // Rare path of the softmax warps, kept out of line so that its registers do not weigh on the tile loop:
@@ -226,7 +229,22 @@ __device__ __noinline__ void rescale_accumulators(uint32_t t_row, float f) {
 struct WorkItem {
     int                qtile, head, batch, n_tiles, q0;  // head: the first of the group; q0: the first token
     unsigned long long live;  // key tiles to walk, as bits (at most 64 when some are left out)
+    unsigned long long zero;  // key tiles where the mask adds nothing for any row (known only together with `live`)
 };
+// 64 flag bytes (0 or 1, 16-byte aligned) -> a word with bit j = byte j: the multiplier gathers the low bits of eight bytes
+// into the top byte of the product.
+__device__ __forceinline__ unsigned long long bytes_to_bits(const uint8_t * flags) {
+    const ulonglong2 * f = reinterpret_cast<const ulonglong2 *>(flags);
+    unsigned long long bits = 0ull;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const ulonglong2 x = __ldg(f + i);
+        bits |= ((x.x * 0x0102040810204080ull) >> 56) << (16 * i);
+        bits |= ((x.y * 0x0102040810204080ull) >> 56) << (16 * i + 8);
+    }
+    return bits;
+}
+
 template <bool kMask>
 __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, WorkItem & w) {
     const int G = gridDim.x, c = blockIdx.x;
@@ -241,11 +259,20 @@ __device__ __forceinline__ bool work_item(const PrefillParams & p, int round, Wo
     const int last_tok = min(w.q0 + p.tok, p.n_q) - 1;
     w.n_tiles = min((p.n_kv + kKeys - 1) / kKeys, (last_tok + p.causal_offset) / kKeys + 1);
     w.live    = ~0ull;
+    w.zero    = 0ull;
     if (kMask && p.tile_live != nullptr) {  // only set for n_tiles <= 64; a tile where the mask hides every key from every row is left out
-        unsigned long long seen = 0ull;
-        for (int h = 0; h < p.pack; ++h)  // the heads of the group may read different planes of the mask
-            seen |= p.tile_live[((size_t) (w.batch % p.m_ne3) * p.m_ne2 + ((w.head + h) % p.m_ne2)) * p.n_qtiles + w.qtile];
+        unsigned long long seen = 0ull, zero = ~0ull;
+        const int n_planes = min(p.pack, p.m_ne2);  // the heads of the group may read different planes of the mask
+        for (int h = 0; h < n_planes; ++h) {
+            const size_t at = (((size_t) (w.batch % p.m_ne3) * p.m_ne2 + ((w.head + h) % p.m_ne2)) * p.n_qtiles + w.qtile) * 64;
+            seen |= bytes_to_bits(p.tile_live + at);
+            zero &= bytes_to_bits(p.tile_zero + at);
+        }
+        const int n_kt = (p.n_kv + kKeys - 1) / kKeys;  // bytes of key tiles that do not exist were never written
+        const unsigned long long valid = n_kt >= 64 ? ~0ull : (1ull << n_kt) - 1ull;
+        seen &= valid;
         w.live = seen != 0 ? seen : 1ull;  // an item that sees nothing still walks one tile: its rows come out as zeros
+        w.zero = zero & valid;
     }
     return true;
 }
@@ -712,9 +739,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (kMask)
                 mrow = p.mask + (size_t) min(qpos, p.n_q - 1) * p.m_nb1 + (size_t) ((w.head + row % p.pack) % p.m_ne2) * p.m_nb2 +
                        (size_t) (w.batch % p.m_ne3) * p.m_nb3;
-            // the scores are multiplied by `mul` on their way into the exponent: with a mask they have been put into
-            // natural units (scale * S + mask) first
-            const float mul = kMask ? 1.4426950408889634f : p.scale_log2;
             bool  first = true;  // the item's first score tile sets the reference
             // last key every row of the item sees, and the key tile that holds it
             const int uncut = min(w.q0 + p.causal_offset, p.n_kv - 1), cut_from = uncut / kKeys;
@@ -728,8 +752,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(13, U);
                     const int sb = uw.slot;
                     const int k0 = j * kKeys + kSub * u;  // the score tile's first key
+                    // a key tile to which the mask adds nothing for any row of the item (most tiles of a causal mask) is not read
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_FORCE_MREAD)
+                    const bool m_read = kMask;
+#else
+                    const bool m_read = kMask && !(j < 64 && ((w.zero >> j) & 1ull));
+#endif
+                    // the scores are multiplied by `mul` on their way into the exponent: where the mask is read they have
+                    // been put into natural units (scale * S + mask) first
+                    const float mul = m_read ? 1.4426950408889634f : p.scale_log2;
                     uint4     mv[8];
-                    if (kMask) {  // requested before the wait for the scores; chunks of 8 keys lie wholly inside or outside n_kv
+                    if (kMask && m_read) {  // requested before the wait for the scores; chunks of 8 keys lie wholly inside or outside n_kv
                         const uint4 * mp = reinterpret_cast<const uint4 *>(mrow + (size_t) k0 * 2);
 #pragma unroll
                         for (int c = 0; c < 8; ++c) mv[c] = k0 + 8 * c < p.n_kv ? __ldg(mp + c) : make_uint4(0u, 0u, 0u, 0u);
@@ -763,7 +796,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     PROF_STOP(10);
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(6, U);
-                    if (kMask) {
+                    if (kMask && m_read) {
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
                             const uint32_t w4[4] = {mv[c].x, mv[c].y, mv[c].z, mv[c].w};
@@ -982,16 +1015,21 @@ bool tc_route_ok(const vox_attn_args * a) {
     return true;
 }
 
-// Which key tiles of which query tiles the mask leaves anything of: one 64-bit word per (mask plane, query tile), bit j
-// set when some row of the tile has a mask value other than -inf among keys 64j..64j+63.  The tensor-core kernel
-// leaves the other tiles out (with the reference's causal mask tensor that is half of them).  Grid: (key tiles,
-// query tiles, planes), one thread per row, into words cleared beforehand (one CTA per query tile walking all its key
-// tiles needs no clearing but measured slower: 95.6 against 73.2 us per layer at 2048 tokens x 2).
+// Which key tiles of which query tiles the mask leaves anything of, and to which it adds nothing: per (mask plane, query
+// tile) 64 flag bytes of each kind, byte j for keys 128j..128j+127.  The tensor-core kernel leaves the first kind's
+// empty tiles out (with the reference's causal mask tensor that is half of them) and does not read the mask in the
+// second kind's (all tiles below the diagonal).  Grid: (key tiles, query tiles, planes), one thread per row; every CTA
+// writes its own two bytes, so nothing has to be cleared beforehand (words of bits set with atomics needed a memset
+// node in front, and the two extra nodes per call cost a captured graph as much as the tiles they saved: 40 us per
+// layer at 512 tokens x 8 with or without them).  Launched with programmatic dependency: it starts while the kernel
+// before drains, reads the mask after that kernel has completed, and lets the tensor-core kernel's prologue start.
 __global__ void __launch_bounds__(kTile) mask_tiles_kernel(const uint8_t * mask, size_t nb1, size_t nb2, size_t nb3, int ne2, int n_q,
-                                                           int n_kv, int tok, unsigned long long * live) {
+                                                           int n_kv, int tok, uint8_t * live, uint8_t * zero) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.y * tok + threadIdx.x, k0 = blockIdx.x * kKeys;  // a query tile holds `tok` tokens
     const int i2 = blockIdx.z % ne2, i3 = blockIdx.z / ne2;
-    int       any = 0;
+    int       any = 0, nonzero = 0;
     if (threadIdx.x < tok && row < n_q) {
         const uint4 * m = reinterpret_cast<const uint4 *>(mask + (size_t) row * nb1 + (size_t) i2 * nb2 + (size_t) i3 * nb3 + (size_t) k0 * 2);
 #pragma unroll
@@ -1001,11 +1039,17 @@ __global__ void __launch_bounds__(kTile) mask_tiles_kernel(const uint8_t * mask,
                 const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) any |= (w[i] & 0xffffu) != 0xfc00u || (w[i] >> 16) != 0xfc00u;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) nonzero |= (w[i] & 0x7fff7fffu) != 0u;  // anything but +0 or -0
             }
         }
     }
-    if (__syncthreads_or(any) && threadIdx.x == 0)
-        atomicOr(live + (size_t) blockIdx.z * gridDim.y + blockIdx.y, 1ull << blockIdx.x);
+    const int any_all = __syncthreads_or(any), nonzero_all = __syncthreads_or(nonzero);
+    if (threadIdx.x == 0) {
+        const size_t at = ((size_t) blockIdx.z * gridDim.y + blockIdx.y) * 64 + blockIdx.x;
+        live[at] = any_all ? 1 : 0;
+        zero[at] = nonzero_all ? 0 : 1;
+    }
 }
 
 // query heads of one kv head that share an item's 128 rows: the largest of 8, 4, 2, 1 that divides the GQA ratio
@@ -1020,11 +1064,17 @@ long long query_tiles_of(const vox_attn_args * a) {
     return (a->q.ne[1] + tok - 1) / tok;
 }
 
-// bytes of those words (0 when there are more than 64 key tiles: then every tile is walked)
+#ifndef VOX_PREFILL_MASK_PREPASS_TILES
+#define VOX_PREFILL_MASK_PREPASS_TILES 2048
+#endif
+constexpr long long kMaskPrepassTiles = VOX_PREFILL_MASK_PREPASS_TILES;  // see run_tc
+
+// bytes of those flags, the "something visible" array and the "adds nothing" array behind it (0 when there are more
+// than 64 key tiles: then every tile is walked and read)
 size_t mask_tiles_bytes(const vox_attn_args * a) {
     const long long n_ktiles = (a->k.ne[1] + kKeys - 1) / kKeys, n_qtiles = query_tiles_of(a);
     if (a->mask.data == nullptr || n_ktiles > 64) return 0;
-    return ((size_t) (a->mask.ne[2] * a->mask.ne[3] * n_qtiles * 8) + 255) & ~(size_t) 255;
+    return 2 * (((size_t) (a->mask.ne[2] * a->mask.ne[3] * n_qtiles * 64) + 255) & ~(size_t) 255);
 }
 
 // Host side of the tensor-core kernel: `with_mask` false implies the causal mask at `offset` (n_kv - n_q) or, with
@@ -1034,22 +1084,22 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     // every key visible (before the mask, if there is one) is a causal offset of n_kv
     const int offset = with_mask || !causal ? (int) a->k.ne[1] : (int) (a->k.ne[1] - a->q.ne[1]);
     // workspace: the live-tile words of the mask first (when it has room for them), then the expanded K/V
-    const unsigned long long * tile_live = nullptr;
+    const uint8_t * tile_live = nullptr, * tile_zero = nullptr;
     if (with_mask && workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) {
         const size_t words = mask_tiles_bytes(a);
         const size_t rest  = q8_route_ok(a) ? 4 * q8_scratch_bytes(a) : 0;
         // worth its launch from a few thousand tiles on (512 tokens x 1 sequence is 512 tiles: not worth it)
         const long long tiles = ((a->k.ne[1] + kKeys - 1) / kKeys) * query_tiles_of(a) * (a->q.ne[2] / pack_of(a)) * a->q.ne[3];
-        if (words > 0 && workspace_bytes >= words + rest && tiles >= 2048) {
-            unsigned long long * live = static_cast<unsigned long long *>(workspace);
-            VOX_CUDA_TRY(cudaMemsetAsync(live, 0, words, st));
+        if (words > 0 && workspace_bytes >= words + rest && tiles >= kMaskPrepassTiles) {
+            uint8_t * live = static_cast<uint8_t *>(workspace);
             const dim3 grid((unsigned) ((a->k.ne[1] + kKeys - 1) / kKeys), (unsigned) query_tiles_of(a),
                             (unsigned) (a->mask.ne[2] * a->mask.ne[3]));
-            mask_tiles_kernel<<<grid, kTile, 0, st>>>(static_cast<const uint8_t *>(a->mask.data), a->mask.nb[1], a->mask.nb[2], a->mask.nb[3],
-                                                      (int) a->mask.ne[2], (int) a->q.ne[1], (int) a->k.ne[1], kTile / pack_of(a), live);
+            launch_pdl(mask_tiles_kernel, grid, dim3(kTile), 0, st, static_cast<const uint8_t *>(a->mask.data), a->mask.nb[1], a->mask.nb[2],
+                       a->mask.nb[3], (int) a->mask.ne[2], (int) a->q.ne[1], (int) a->k.ne[1], kTile / pack_of(a), live, live + words / 2);
             int rc = check_launch(e, "mask_tiles_kernel");
             if (rc != VOX_ATTN_OK) return rc;
             tile_live       = live;
+            tile_zero       = live + words / 2;
             workspace       = static_cast<uint8_t *>(workspace) + words;
             workspace_bytes -= words;
         }
@@ -1128,6 +1178,7 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     p.m_nb1 = a->mask.nb[1]; p.m_nb2 = a->mask.nb[2]; p.m_nb3 = a->mask.nb[3];
     p.m_ne2 = with_mask ? (int) a->mask.ne[2] : 1; p.m_ne3 = with_mask ? (int) a->mask.ne[3] : 1;
     p.tile_live = tile_live;
+    p.tile_zero = tile_zero;
     p.n_batch  = (int) a->q.ne[3];
     p.pack      = pack_of(a);
     p.tok       = kTile / p.pack;
