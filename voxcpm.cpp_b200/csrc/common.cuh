@@ -141,6 +141,33 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Bulk-tensor store shared -> global of one box of a tensor map (the innermost coordinate times the element size must be
+// a multiple of 16 bytes, no coordinate may be negative; what lies beyond the tensor's extents is not written).  The
+// writes to shared memory that fill the tile are made visible to the copy by fence_proxy_async_smem before the barrier
+// that precedes the issue.  Stores are tracked in bulk groups of the issuing thread: bulk_wait_read returns once the
+// committed groups have read their shared memory (it may be rewritten), bulk_wait_all once they have been performed.
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap * map, uint32_t src, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// A named barrier of n_threads that also votes: true when `mine` is true for every one of them.
+__device__ __forceinline__ bool named_bar_all(int id, int n_threads, bool mine) {
+    uint32_t all;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.and.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(all)
+        : "r"(id), "r"(n_threads), "r"((uint32_t) mine)
+        : "memory");
+    return all != 0;
+}
+
 // Asynchronous 16-byte copies global -> shared by the issuing thread (both addresses 16-byte aligned); a thread sees the
 // bytes of its own copies after cp_async_wait_all.
 __device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void * src) {

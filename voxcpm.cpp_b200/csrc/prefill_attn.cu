@@ -45,7 +45,9 @@
 //   warps 12-15 in/out: one thread per query row again.  They keep the Q tiles of the next two items in shared
 //              memory (f32 from memory, rounded to f16 once, exact when it already holds f16 values; the raw rows of
 //              the item after those wait in a staging area, copied there by cp.async a whole item ahead) and read each
-//              finished output row out of TMEM, normalise and store it, handing the columns back to the issuer.
+//              finished output row out of TMEM, normalise it and put it into an output staging tile, which two
+//              bulk-tensor stores carry to its place (rows past n_q clipped by the copy), handing the columns back to
+//              the issuer.
 // What bounds it, measured by leaving parts out (developer builds, 2048 tokens x 2 sequences, 29.4 key tiles per CTA,
 // one layer 43 us): barriers, commits and waits alone, with no copy, no MMA, no softmax arithmetic and no global
 // traffic, 16.5 us (about 450 clocks per score tile although six are in flight and no single wait, arrive or commit
@@ -59,8 +61,8 @@
 // three buffers; three softmax groups (640 threads, 120 registers each); handing the reference on before, during or
 // after the exponentials; polling instead of parked waits in the issuers; two output accumulators so that an item's
 // first P.V need not wait for the read-out of the item before.
-// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  163 KB of shared memory per CTA (195 KB
-// with remainder tiles, which leave no room for the staging area).  Every wait on a barrier is bounded; on expiry the
+// scale*log2(e) is applied to S in f32.  Accumulation is f32 everywhere.  195 KB of shared memory per CTA (as much
+// with remainder tiles, which leave no room for the two staging areas: rows are then fetched and stored by their threads).  Every wait on a barrier is bounded; on expiry the
 // status word is set and all roles fall through to the common exit, where the TMEM columns are released.  The
 // register trade cannot block: what the softmax groups take, the other two have given up before (static_assert below).
 //
@@ -179,8 +181,11 @@ constexpr int q_buf_bytes(bool v_lo) { return v_lo ? 2 * kQBytes : kQBytes; }
 // Without remainder tiles there is room for a staging area the size of a raw Q tile (128 rows of 64 floats): the rows of
 // the item after the two whose Q tiles are in place are copied there asynchronously (cp.async) a whole item ahead
 constexpr int kQStageBytes = kTile * kHeadDim * 4;
-constexpr int smem_pf(bool v_lo) {  // Q x 2, K ring, V ring, ones, Q staging
-    return kQBufs * q_buf_bytes(v_lo) + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + (v_lo ? 0 : kQStageBytes) + 1024;
+// ... and for an output tile of the same size, from which finished rows leave by bulk-tensor stores (two 128-row halves of
+// 128 bytes per row, in the 128-byte swizzle of the tensor map)
+constexpr int kOutStageBytes = kTile * kHeadDim * 4;
+constexpr int smem_pf(bool v_lo) {  // Q x 2, K ring, V ring, ones, Q staging, output staging
+    return kQBufs * q_buf_bytes(v_lo) + stages_of(v_lo) * 2 * v_stage_bytes(v_lo) + kOnesBytes + (v_lo ? 0 : kQStageBytes + kOutStageBytes) + 1024;
 }
 
 struct PrefillParams {
@@ -195,6 +200,7 @@ struct PrefillParams {
     int             pack, tok, n_hgroups;
     float           scale_log2;
     int *           status;
+    int             tma_out;  // the output leaves through map_o (dst 16-byte aligned, no remainder tiles in shared memory)
     // additive f16 mask (kMask kernels): rows of n_kv values, planes broadcast over heads and sequences
     const uint8_t * mask;
     size_t          m_nb1, m_nb2, m_nb3;
@@ -313,7 +319,8 @@ __device__ __forceinline__ int sub_tiles(const PrefillParams & p, const WorkItem
 template <bool kSplitP, bool kVLo, bool kMask>
 __global__ void __launch_bounds__(kThreadsPf, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                  const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo, const PrefillParams p) {
+                  const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo,
+                  const __grid_constant__ CUtensorMap map_o, const PrefillParams p) {
     constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo), kQBufBytes = q_buf_bytes(kVLo);
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[4 * kStages + 3 * kSBufs + kQBufs + 2 + kGroups];
@@ -323,7 +330,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *      smem_gen  = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBufBytes, sV0 = sK0 + kSt * kVBytes, sOnes = sV0 + kSt * kVBytes, sStage = sOnes + kOnesBytes;
+    const uint32_t sQ = smem_base, sK0 = sQ + kQBufs * kQBufBytes, sV0 = sK0 + kSt * kVBytes, sOnes = sV0 + kSt * kVBytes, sStage = sOnes + kOnesBytes,
+                   sOut = sStage + kQStageBytes;  // 1024-byte aligned: every area before it is a multiple of 1024 bytes but the ones (2048)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -362,6 +370,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     if (tid == 128) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+        if (!kVLo) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_o)) : "memory");
         if (kVLo) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_klo)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_vlo)) : "memory");
@@ -442,6 +451,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         // output and the next.  A thread copies, waits for and reads only its own row, so no barrier is involved; chunk c
         // of row r sits at (c ^ (r & 15)), which spreads the rows of a quarter-warp over the banks.
         constexpr bool  kStageQ   = !kVLo;
+        constexpr bool  kTmaOut   = !kVLo;  // the same room holds the output staging tile
         uint8_t * const stage_row = smem_gen + (sStage - smem_base) + row * 256;
         auto fetch_q = [&](const WorkItem & w) {
             const int qpos = w.q0 + row / p.pack, head = w.head + row % p.pack;
@@ -477,32 +487,70 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 else load_q(wn, r);
             }
         if (kStageQ && work_item<kMask>(p, kQBufs, wn)) fetch_q(wn);
-        for (int round = 0; work_item<kMask>(p, round, w) && !aborted(); ++round) {
-            if (!mbar_wait_bounded(bO, round & 1)) { give_up(); break; }
+        for (int round = 0; work_item<kMask>(p, round, w); ++round) {
+            // one decision for the 128 threads (they meet at barriers below): go on only if nobody has given up and
+            // every thread has seen the item's output complete
+            const bool seen = !aborted() && mbar_wait_bounded(bO, round & 1);
+            if (!named_bar_all(1, kIoThreads, seen)) { give_up(); break; }
             tc_fence_after();
             const int   qpos = w.q0 + row / p.pack, head = w.head + row % p.pack;
-#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_IO)
+#if defined(VOX_ATTN_DEVELOPER) && (defined(VOX_PF_SKIP_IO) || defined(VOX_PF_SKIP_STORE))
             const bool  live = qpos < 0;
 #else
             const bool  live = qpos < p.n_q;
 #endif
             const float l    = tmem_ld1(t_row + kOCol + kHeadDim);  // sum of exactly the rounded weights the tensor core used
             const float inv  = l > 0.0f ? 1.0f / l : 0.0f;
-            float4 *    out  = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim);
+            if (kTmaOut && p.tma_out) {
+                // The row goes into the output staging tile, and two bulk-tensor stores (one per 128-byte half of the
+                // rows) carry the tile to its place: box = 32 floats x the group's heads x the item's tokens, so rows
+                // past n_q are clipped by the copy.  A thread per row writing 256 contiguous bytes of global memory
+                // touched 32 lines per store instruction; measured with the stores left out, they cost 2 us per layer
+                // at 512 tokens x 8 and 1.1 us at 512 x 1.
+                uint8_t * const out_row = smem_gen + (sOut - smem_base) + row * 128;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t r[32];
-                tmem_ld32_sync(t_row + kOCol + 32 * h, r);
-                if (h == 1) {  // both halves are in registers: the columns go back to the tensor core
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bOfree);
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t r[32];
+                    tmem_ld32_sync(t_row + kOCol + 32 * h, r);
+                    if (h == 0) {
+                        // the stores of the item before have read the staging tile
+                        if (row == 0 && round > 0) bulk_wait_read();
+                        named_bar_sync(1, kIoThreads);
+                    } else {  // both halves are in registers: the columns go back to the tensor core
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bOfree);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<float4 *>(out_row + h * (kOutStageBytes / 2) + ((c ^ (row & 7)) << 4)) =
+                            make_float4(__uint_as_float(r[4 * c]) * inv, __uint_as_float(r[4 * c + 1]) * inv,
+                                        __uint_as_float(r[4 * c + 2]) * inv, __uint_as_float(r[4 * c + 3]) * inv);
                 }
-                if (live) {
+                fence_proxy_async_smem();
+                named_bar_sync(1, kIoThreads);
+                if (row == 0) {
+                    tma_store_5d(&map_o, sOut, 0, w.head, w.q0, w.batch, 0);
+                    tma_store_5d(&map_o, sOut + kOutStageBytes / 2, 32, w.head, w.q0, w.batch, 0);
+                    bulk_commit();
+                }
+            } else {
+                float4 * out = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        out[8 * h + i] = make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
-                                                     __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t r[32];
+                    tmem_ld32_sync(t_row + kOCol + 32 * h, r);
+                    if (h == 1) {  // both halves are in registers: the columns go back to the tensor core
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bOfree);
+                    }
+                    if (live) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            out[8 * h + i] = make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
+                                                         __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+                    }
                 }
             }
             // The item's output is complete only after its last P.V, which needed its last weights, which needed its last
@@ -516,6 +564,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
             }
         }
+        if (kTmaOut && p.tma_out && row == 0) bulk_wait_all();  // the last stores have been performed
     } else if (warp >= 4 && warp < 8) {
         regs_give<kRegsControl>();
         if (warp == 4) {
@@ -1153,6 +1202,19 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
         if (rc != VOX_ATTN_OK) return rc;
     }
     if (!v_lo) { mklo = mk; mvlo = mv; }  // not read
+    // the output's tensor map: [batch][n_q][n_heads][64] f32, stored in boxes of 32 floats x the heads of a group x the tokens
+    // of an item (without it, or when remainder tiles fill the shared memory, the rows are stored by their threads)
+    CUtensorMap mo = mk;
+    int         tma_out = 0;
+    if (!v_lo && (reinterpret_cast<uintptr_t>(a->dst.data) & 15) == 0) {
+        const uint64_t row_b = kHeadDim * 4, n_h = (uint64_t) a->q.ne[2], n_q = (uint64_t) a->q.ne[1], n_b = (uint64_t) a->q.ne[3];
+        const uint64_t od[5] = {kHeadDim, n_h, n_q, n_b, 1};
+        const uint64_t os[4] = {row_b, n_h * row_b, n_q * n_h * row_b, n_b * n_q * n_h * row_b};
+        const uint32_t ob[5] = {32, (uint32_t) pack_of(a), (uint32_t) (kTile / pack_of(a)), 1, 1};
+        int rc = make_tensor_map(e, &mo, a->dst.data, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, od, os, ob, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != VOX_ATTN_OK) return rc;
+        tma_out = 1;
+    }
     if (!(e->attr_mask & (1u << 12))) {
         VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
         VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
@@ -1174,6 +1236,7 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.scale  = a->scale;
     p.status = e->status_dev;
+    p.tma_out = tma_out;
     p.mask   = with_mask ? static_cast<const uint8_t *>(a->mask.data) : nullptr;
     p.m_nb1 = a->mask.nb[1]; p.m_nb2 = a->mask.nb[2]; p.m_nb3 = a->mask.nb[3];
     p.m_ne2 = with_mask ? (int) a->mask.ne[2] : 1; p.m_ne3 = with_mask ? (int) a->mask.ne[3] : 1;
@@ -1190,11 +1253,11 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     // persistent CTAs, one per SM (all 512 TMEM columns, 131 KB of shared memory; 195 KB when K/V were expanded and every
     // operand tile comes with its remainder tile)
     dim3 grid((unsigned) std::min<long long>(items, (long long) e->sm_count));
-    if (with_mask && v_lo) launch_pdl(prefill_tc_kernel<true, true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
-    else if (with_mask) launch_pdl(prefill_tc_kernel<true, false, true>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
-    else if (v_lo) launch_pdl(prefill_tc_kernel<true, true, false>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, p);
-    else if (split_p) launch_pdl(prefill_tc_kernel<true, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
-    else launch_pdl(prefill_tc_kernel<false, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, p);
+    if (with_mask && v_lo) launch_pdl(prefill_tc_kernel<true, true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, mo, p);
+    else if (with_mask) launch_pdl(prefill_tc_kernel<true, false, true>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, p);
+    else if (v_lo) launch_pdl(prefill_tc_kernel<true, true, false>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, mo, p);
+    else if (split_p) launch_pdl(prefill_tc_kernel<true, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, p);
+    else launch_pdl(prefill_tc_kernel<false, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, p);
     return check_launch(e, "prefill_tc_kernel");
 }
 
