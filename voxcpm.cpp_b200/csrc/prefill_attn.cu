@@ -44,7 +44,7 @@
 //              80 clocks, now about 40 (a commit costs 46, a satisfied barrier wait 47: measured alone).
 //   warps 12-15 in/out: one thread per query row again.  They keep the Q tiles of the next two items in shared
 //              memory (f32 from memory, rounded to f16 once, exact when it already holds f16 values; the raw rows of
-//              the item after those wait in a staging area, copied there by cp.async a whole item ahead) and read each
+//              the item after those wait in a staging area, brought there by two bulk-tensor loads a whole item ahead) and read each
 //              finished output row out of TMEM, normalise it and put it into an output staging tile, which two
 //              bulk-tensor stores carry to its place (rows past n_q clipped by the copy), handing the columns back to
 //              the issuer.
@@ -200,6 +200,7 @@ struct PrefillParams {
     int             pack, tok, n_hgroups;
     float           scale_log2;
     int *           status;
+    int             tma_q;    // the raw Q rows arrive through map_q (16-byte aligned rows and strides)
     int             tma_out;  // the output leaves through map_o (dst 16-byte aligned, no remainder tiles in shared memory)
     // additive f16 mask (kMask kernels): rows of n_kv values, planes broadcast over heads and sequences
     const uint8_t * mask;
@@ -320,10 +321,10 @@ template <bool kSplitP, bool kVLo, bool kMask>
 __global__ void __launch_bounds__(kThreadsPf, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_klo, const __grid_constant__ CUtensorMap map_vlo,
-                  const __grid_constant__ CUtensorMap map_o, const PrefillParams p) {
+                  const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_q, const PrefillParams p) {
     constexpr int kSt = stages_of(kVLo), kVBytes = v_stage_bytes(kVLo), kQBufBytes = q_buf_bytes(kVLo);
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[4 * kStages + 3 * kSBufs + kQBufs + 2 + kGroups];
+    __shared__ uint64_t bars[4 * kStages + 3 * kSBufs + kQBufs + 2 + kGroups + 1];
     __shared__ float    row_ref[kGroups][kTile];  // [score tile % groups][row]: the row's reference maximum after that tile, for the thread that takes the next one
     __shared__ uint32_t tmem_base_slot;
     __shared__ int      abort_flag;
@@ -346,7 +347,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     // the group that takes the next.
     const uint32_t kfull0 = smem_u32(&bars[0]), kempty0 = kfull0 + 8 * kStages, vfull0 = kempty0 + 8 * kStages,
                    vempty0 = vfull0 + 8 * kStages, bS0 = vempty0 + 8 * kStages, bP0 = bS0 + 8 * kSBufs, bF0 = bP0 + 8 * kSBufs,
-                   bQ0 = bF0 + 8 * kSBufs, bO = bQ0 + 8 * kQBufs, bOfree = bO + 8, bM0 = bOfree + 8;
+                   bQ0 = bF0 + 8 * kSBufs, bO = bQ0 + 8 * kQBufs, bOfree = bO + 8, bM0 = bOfree + 8,
+                   bQS = bM0 + 8 * kGroups;  // the raw rows of a Q tile have landed in the staging area
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
@@ -364,6 +366,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         mbar_init(bO, 1);
         mbar_init(bOfree, kIoThreads / 32);
         for (int s = 0; s < kGroups; ++s) mbar_init(bM0 + 8 * s, 4);  // the rows' references after a score tile published (tile U uses U % kGroups)
+        mbar_init(bQS, 1);
         fence_mbar_init();
     }
     if (warp == 5) tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -371,6 +374,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
         if (!kVLo) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_o)) : "memory");
+        if (!kVLo) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
         if (kVLo) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_klo)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_vlo)) : "memory");
@@ -445,15 +449,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(bQ0 + 8 * buf);
         };
-        // Without remainder tiles (kVLo) the raw rows travel through a staging area: sixteen 16-byte asynchronous copies per
-        // thread, all in flight together and issued a whole item before the rows are needed, so that a new Q tile costs
-        // the in/out warps a pass over shared memory instead of two round trips to global memory between one item's
-        // output and the next.  A thread copies, waits for and reads only its own row, so no barrier is involved; chunk c
-        // of row r sits at (c ^ (r & 15)), which spreads the rows of a quarter-warp over the banks.
+        // Without remainder tiles (kVLo) the raw rows travel through a staging area, asked for a whole item before they
+        // are needed, so that a new Q tile costs the in/out warps a pass over shared memory instead of two round trips
+        // to global memory between one item's output and the next.  Two bulk-tensor loads by one thread fill it (box =
+        // 32 floats x the group's heads x the item's tokens: 128 rows of 128 bytes per half, in the 128-byte swizzle;
+        // rows past n_q arrive as zeros); where the rows or strides of Q are not 16-byte aligned every thread copies
+        // its own row with sixteen cp.async instead (chunk c of row r at c ^ (r & 15), no barrier involved).
         constexpr bool  kStageQ   = !kVLo;
         constexpr bool  kTmaOut   = !kVLo;  // the same room holds the output staging tile
         uint8_t * const stage_row = smem_gen + (sStage - smem_base) + row * 256;
+        uint8_t * const stage_tma = smem_gen + (sStage - smem_base) + row * 128;  // + half * 16 KB + swizzled chunk
+        uint32_t        qs_phase  = 0;      // of the staging barrier
+        bool            io_failed = false;  // set by all 128 threads together
         auto fetch_q = [&](const WorkItem & w) {
+            if (p.tma_q) {
+                named_bar_sync(1, kIoThreads);  // every thread has read the rows that were there
+                if (row == 0) {
+                    mbar_expect_tx(bQS, kQStageBytes);
+                    tma_load_5d(sStage, &map_q, bQS, 0, w.head, w.q0, w.batch, 0);
+                    tma_load_5d(sStage + kQStageBytes / 2, &map_q, bQS, 32, w.head, w.q0, w.batch, 0);
+                }
+                return;
+            }
             const int qpos = w.q0 + row / p.pack, head = w.head + row % p.pack;
             if (qpos < p.n_q) {
                 const uint8_t * src = p.q + (size_t) qpos * p.q_nb1 + (size_t) head * p.q_nb2 + (size_t) w.batch * p.q_nb3;
@@ -463,15 +480,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             cp_async_commit();
         };
         auto convert_q = [&](const WorkItem & w, int buf) {
-            cp_async_wait_all();
+            if (p.tma_q) {
+                const bool got = mbar_wait_bounded(bQS, qs_phase);
+                qs_phase ^= 1u;
+                if (!named_bar_all(1, kIoThreads, got)) { give_up(); io_failed = true; return; }
+            } else {
+                cp_async_wait_all();
+            }
             uint8_t * const q_dst = smem_gen + buf * kQBufBytes + row * 128;
             const bool      in    = w.q0 + row / p.pack < p.n_q;
+            // chunk k (of 16) of this thread's raw row
+            auto raw = [&](int k) {
+                if (p.tma_q) return *reinterpret_cast<const float4 *>(stage_tma + (k >> 3) * (kQStageBytes / 2) + (((k & 7) ^ (row & 7)) << 4));
+                return in ? *reinterpret_cast<const float4 *>(stage_row + ((k ^ (row & 15)) << 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            };
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const float4 a = in ? *reinterpret_cast<const float4 *>(stage_row + (((8 * h + 2 * c) ^ (row & 15)) << 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    const float4 b = in ? *reinterpret_cast<const float4 *>(stage_row + (((8 * h + 2 * c + 1) ^ (row & 15)) << 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 a = raw(8 * h + 2 * c), b = raw(8 * h + 2 * c + 1);
                     const int at = ((4 * h + c) ^ (row & 7)) << 4;
                     *reinterpret_cast<uint4 *>(q_dst + at) = make_uint4(pack_half2(a.x, a.y), pack_half2(a.z, a.w), pack_half2(b.x, b.y), pack_half2(b.z, b.w));
                 }
@@ -481,13 +508,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (lane == 0) mbar_arrive(bQ0 + 8 * buf);
         };
         WorkItem w, wn;
-        for (int r = 0; r < kQBufs; ++r)
+        for (int r = 0; r < kQBufs && !io_failed; ++r)
             if (work_item<kMask>(p, r, wn)) {
                 if (kStageQ) { fetch_q(wn); convert_q(wn, r); }
                 else load_q(wn, r);
             }
-        if (kStageQ && work_item<kMask>(p, kQBufs, wn)) fetch_q(wn);
-        for (int round = 0; work_item<kMask>(p, round, w); ++round) {
+        if (kStageQ && !io_failed && work_item<kMask>(p, kQBufs, wn)) fetch_q(wn);
+        for (int round = 0; !io_failed && work_item<kMask>(p, round, w); ++round) {
             // one decision for the 128 threads (they meet at barriers below): go on only if nobody has given up and
             // every thread has seen the item's output complete
             const bool seen = !aborted() && mbar_wait_bounded(bO, round & 1);
@@ -558,7 +585,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (work_item<kMask>(p, round + kQBufs, wn)) {
                 if (kStageQ) {
                     convert_q(wn, round % kQBufs);  // its rows were asked for an item ago
-                    if (work_item<kMask>(p, round + kQBufs + 1, wn)) fetch_q(wn);
+                    if (!io_failed && work_item<kMask>(p, round + kQBufs + 1, wn)) fetch_q(wn);
                 } else {
                     load_q(wn, round % kQBufs);
                 }
@@ -1202,6 +1229,17 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
         if (rc != VOX_ATTN_OK) return rc;
     }
     if (!v_lo) { mklo = mk; mvlo = mv; }  // not read
+    // the raw Q rows as a tensor map over (64 floats, heads, tokens, sequences), in whatever strides the caller's Q has
+    CUtensorMap mq = mk;
+    int         tma_q = 0;
+    if (!v_lo && (reinterpret_cast<uintptr_t>(a->q.data) & 15) == 0 && a->q.nb[1] % 16 == 0 && a->q.nb[2] % 16 == 0 && a->q.nb[3] % 16 == 0) {
+        const uint64_t qd[5] = {kHeadDim, (uint64_t) a->q.ne[2], (uint64_t) a->q.ne[1], (uint64_t) a->q.ne[3], 1};
+        const uint64_t qs[4] = {a->q.nb[2], a->q.nb[1], a->q.nb[3], std::max<uint64_t>(a->q.nb[3] * (uint64_t) a->q.ne[3], 16)};
+        const uint32_t qb[5] = {32, (uint32_t) pack_of(a), (uint32_t) (kTile / pack_of(a)), 1, 1};
+        int rc = make_tensor_map(e, &mq, const_cast<void *>(a->q.data), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, qd, qs, qb, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != VOX_ATTN_OK) return rc;
+        tma_q = 1;
+    }
     // the output's tensor map: [batch][n_q][n_heads][64] f32, stored in boxes of 32 floats x the heads of a group x the tokens
     // of an item (without it, or when remainder tiles fill the shared memory, the rows are stored by their threads)
     CUtensorMap mo = mk;
@@ -1237,6 +1275,7 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     p.scale  = a->scale;
     p.status = e->status_dev;
     p.tma_out = tma_out;
+    p.tma_q   = tma_q;
     p.mask   = with_mask ? static_cast<const uint8_t *>(a->mask.data) : nullptr;
     p.m_nb1 = a->mask.nb[1]; p.m_nb2 = a->mask.nb[2]; p.m_nb3 = a->mask.nb[3];
     p.m_ne2 = with_mask ? (int) a->mask.ne[2] : 1; p.m_ne3 = with_mask ? (int) a->mask.ne[3] : 1;
@@ -1253,11 +1292,11 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     // persistent CTAs, one per SM (all 512 TMEM columns, 131 KB of shared memory; 195 KB when K/V were expanded and every
     // operand tile comes with its remainder tile)
     dim3 grid((unsigned) std::min<long long>(items, (long long) e->sm_count));
-    if (with_mask && v_lo) launch_pdl(prefill_tc_kernel<true, true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, mo, p);
-    else if (with_mask) launch_pdl(prefill_tc_kernel<true, false, true>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, p);
-    else if (v_lo) launch_pdl(prefill_tc_kernel<true, true, false>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, mo, p);
-    else if (split_p) launch_pdl(prefill_tc_kernel<true, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, p);
-    else launch_pdl(prefill_tc_kernel<false, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, p);
+    if (with_mask && v_lo) launch_pdl(prefill_tc_kernel<true, true, true>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, mo, mq, p);
+    else if (with_mask) launch_pdl(prefill_tc_kernel<true, false, true>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, mq, p);
+    else if (v_lo) launch_pdl(prefill_tc_kernel<true, true, false>, grid, dim3(kThreadsPf), smem_pf(true), st, mk, mv, mklo, mvlo, mo, mq, p);
+    else if (split_p) launch_pdl(prefill_tc_kernel<true, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, mq, p);
+    else launch_pdl(prefill_tc_kernel<false, false, false>, grid, dim3(kThreadsPf), smem_pf(false), st, mk, mv, mklo, mvlo, mo, mq, p);
     return check_launch(e, "prefill_tc_kernel");
 }
 
