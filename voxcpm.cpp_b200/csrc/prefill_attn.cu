@@ -465,9 +465,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (p.tma_q) {
                 named_bar_sync(1, kIoThreads);  // every thread has read the rows that were there
                 if (row == 0) {
+#if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_IO)
+                    mbar_arrive(bQS);
+#else
                     mbar_expect_tx(bQS, kQStageBytes);
                     tma_load_5d(sStage, &map_q, bQS, 0, w.head, w.q0, w.batch, 0);
                     tma_load_5d(sStage + kQStageBytes / 2, &map_q, bQS, 32, w.head, w.q0, w.batch, 0);
+#endif
                 }
                 return;
             }
@@ -556,11 +560,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
                 fence_proxy_async_smem();
                 named_bar_sync(1, kIoThreads);
+#if !(defined(VOX_ATTN_DEVELOPER) && (defined(VOX_PF_SKIP_IO) || defined(VOX_PF_SKIP_STORE)))
                 if (row == 0) {
                     tma_store_5d(&map_o, sOut, 0, w.head, w.q0, w.batch, 0);
                     tma_store_5d(&map_o, sOut + kOutStageBytes / 2, 32, w.head, w.q0, w.batch, 0);
                     bulk_commit();
                 }
+#endif
             } else {
                 float4 * out = reinterpret_cast<float4 *>(p.dst + (((size_t) w.batch * p.n_q + qpos) * p.n_heads + head) * kHeadDim);
 #pragma unroll
@@ -591,7 +597,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
             }
         }
-        if (kTmaOut && p.tma_out && row == 0) bulk_wait_all();  // the last stores have been performed
+        // the last stores have been performed (waiting only until they have read the staging tile measured the same)
+        if (kTmaOut && p.tma_out && row == 0) bulk_wait_all();
     } else if (warp >= 4 && warp < 8) {
         regs_give<kRegsControl>();
         if (warp == 4) {
