@@ -49,13 +49,13 @@
 //              bulk-tensor stores carry to its place (rows past n_q clipped by the copy), handing the columns back to
 //              the issuer.
 // What bounds it, measured by leaving parts out (developer builds, 2048 tokens x 2 sequences, 29.4 key tiles per CTA,
-// one layer 43 us): barriers, commits and waits alone, with no copy, no MMA, no softmax arithmetic and no global
+// one layer 41 us): barriers, commits and waits alone, with no copy, no MMA, no softmax arithmetic and no global
 // traffic, 16.5 us (about 450 clocks per score tile although six are in flight and no single wait, arrive or commit
-// costs more than 50 clocks to issue); with the MMAs 26 us; with Q in and results out as well 33 us; the softmax
-// arithmetic adds the last 10.  The exponentials (16 per clock and SM) and the two conversions to packed f16 per pair of
+// costs more than 50 clocks to issue); with the MMAs 27 us; with Q in and results out as well 29 us (33 while a thread
+// per row fetched and stored its 256 bytes itself); the softmax arithmetic adds the last 12.  The exponentials (16 per clock and SM) and the two conversions to packed f16 per pair of
 // weights (32 per clock and SM, on the same unit) bound the arithmetic itself at 1175-1300 clocks per 128 x 128 tile
 // with two or three warps per scheduler at work (measured alone; integer forms of the split, with shifts and byte
-// permutes instead of conversions, measured slower: 1400-1900), against 2100 for the whole tile period.  Arrangements
+// permutes instead of conversions, measured slower: 1400-1900), against 2000 for the whole tile period.  Arrangements
 // tried on this skeleton, none of which moved the 2048-token figure by more than 3 %: both softmax groups on the same
 // tile with 64 keys per thread and a trade of maxima (the first form of this kernel); 128-key score tiles with
 // three buffers; three softmax groups (640 threads, 120 registers each); handing the reference on before, during or
