@@ -104,7 +104,9 @@ __device__ unsigned long long g_prof[32];
 // CTA 0, first 64 score tiles.  0 scores seen, 1 weights signalled, 2 weights seen by the output issuer, 3 its MMAs issued
 // and committed, 4 buffer seen free by the score issuer, 5 its MMAs issued and committed; softmax thread: 11 before the
 // wait for the scores, 6 scores loaded, 7 maximum taken, 8 reference seen, 9 weights computed, 10 their stores complete
-__device__ long long g_trace[14][64];
+// (12, 13: loop top at the other group's tile, own tile entered); output issuer: 14 loop top, 15 fenced, 16 MMAs issued,
+// 17 commits issued
+__device__ long long g_trace[18][64];
 #define PROF_TRACE(k, T) do { if (blockIdx.x == 0 && (T) < 64) g_trace[k][T] = clock64(); } while (0)
 #endif
 #if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
@@ -741,6 +743,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         const uint64_t dVs = dV + st * kVStage;
                         for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
                             const int sb = uw.slot;
+                            if (lane == 0) PROF_TRACE(14, U);
                             if (!warp_wait(bP0 + 8 * sb, uw.phase)) { give_up(); ok = false; break; }
                             PROF_STOP(4);
                             // the previous item's result has been read out of TMEM: its columns may be overwritten
@@ -748,6 +751,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             PROF_STOP(2);
                             if (lane == 0) PROF_TRACE(2, U);
                             tc_fence_after();
+                            if (lane == 0) PROF_TRACE(15, U);
                             // O += P V and row sums += P 1 in one instruction per 16 keys: N = 80, columns 64-79 of the B
                             // operand are the tile of ones.  P: 8 TMEM columns of packed weights per k-step, the high parts
                             // in the first half of the score buffer, the low parts in the second half.
@@ -768,11 +772,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                                     for (int k = 0; k < kSub / 16; ++k)
                                         tc_mma_f16_ts(tmem + kOCol, tP + 8 * k, dVlo + st * kVStep + (4 * u + k) * kStepV, idesc_lo, 1);
                                 }
+                                PROF_TRACE(16, U);
                                 tc_commit(bF0 + 8 * sb);  // P.V has retired: the score buffer may be reused, the accumulators are at rest ...
                                 if (u == n_sub - 1) {
                                     tc_commit(vempty0 + 8 * st);                // ... the V stage may be refilled ...
                                     if (j_next >= w.n_tiles) tc_commit(bO);     // ... and the item's output is complete
                                 }
+                                PROF_TRACE(17, U);
                             }
                             __syncwarp();
                             if (lane == 0) PROF_TRACE(3, U);
@@ -1353,7 +1359,7 @@ extern "C" {
 
 #if defined(VOX_ATTN_DEVELOPER) && (defined(VOX_PREFILL_PROFILE) || defined(VOX_PREFILL_TRACE))
 int vox_debug_prefill_trace(long long * out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 14 * 64) != cudaSuccess;
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 18 * 64) != cudaSuccess;
 }
 int vox_debug_prefill_profile(unsigned long long * out, int reset) {
     if (out && cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
