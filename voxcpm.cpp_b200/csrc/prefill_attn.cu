@@ -105,8 +105,8 @@ __device__ unsigned long long g_prof[32];
 // and committed, 4 buffer seen free by the score issuer, 5 its MMAs issued and committed; softmax thread: 11 before the
 // wait for the scores, 6 scores loaded, 7 maximum taken, 8 reference seen, 9 weights computed, 10 their stores complete
 // (12, 13: loop top at the other group's tile, own tile entered); output issuer: 14 loop top, 15 fenced, 16 MMAs issued,
-// 17 commits issued
-__device__ long long g_trace[18][64];
+// 17 commits issued; 18-21: weights signalled by each of the four warps of the tile's group
+__device__ long long g_trace[22][64];
 #define PROF_TRACE(k, T) do { if (blockIdx.x == 0 && (T) < 64) g_trace[k][T] = clock64(); } while (0)
 #endif
 #if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PREFILL_PROFILE)
@@ -993,6 +993,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bP0 + 8 * sb);  // this warp's rows of P are in TMEM
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(1, U);
+                    if (lane == 0) PROF_TRACE(18 + (warp & 3), U);  // every warp of the group
                     PROF_STOP(3);
                 }
             }
@@ -1359,7 +1360,7 @@ extern "C" {
 
 #if defined(VOX_ATTN_DEVELOPER) && (defined(VOX_PREFILL_PROFILE) || defined(VOX_PREFILL_TRACE))
 int vox_debug_prefill_trace(long long * out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 18 * 64) != cudaSuccess;
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 22 * 64) != cudaSuccess;
 }
 int vox_debug_prefill_profile(unsigned long long * out, int reset) {
     if (out && cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
