@@ -168,14 +168,6 @@ __device__ __forceinline__ bool named_bar_all(int id, int n_threads, bool mine) 
     return all != 0;
 }
 
-// Asynchronous 16-byte copies global -> shared by the issuing thread (both addresses 16-byte aligned); a thread sees the
-// bytes of its own copies after cp_async_wait_all.
-__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void * src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
 // One poll.  try_wait parks the thread in hardware until the phase completes or a time limit passes; the limit asked for
 // here (the suspend-time hint, in ns) is long, so that a thread whose wait is long (a producer facing a full ring, a
 // consumer ahead of the copies) polls rarely and leaves the issue slots to the warps that have work: with the default

@@ -202,8 +202,6 @@ struct PrefillParams {
     int             pack, tok, n_hgroups;
     float           scale_log2;
     int *           status;
-    int             tma_q;    // the raw Q rows arrive through map_q (16-byte aligned rows and strides)
-    int             tma_out;  // the output leaves through map_o (dst 16-byte aligned, no remainder tiles in shared memory)
     // additive f16 mask (kMask kernels): rows of n_kv values, planes broadcast over heads and sequences
     const uint8_t * mask;
     size_t          m_nb1, m_nb2, m_nb3;
@@ -455,50 +453,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         // are needed, so that a new Q tile costs the in/out warps a pass over shared memory instead of two round trips
         // to global memory between one item's output and the next.  Two bulk-tensor loads by one thread fill it (box =
         // 32 floats x the group's heads x the item's tokens: 128 rows of 128 bytes per half, in the 128-byte swizzle;
-        // rows past n_q arrive as zeros); where the rows or strides of Q are not 16-byte aligned every thread copies
-        // its own row with sixteen cp.async instead (chunk c of row r at c ^ (r & 15), no barrier involved).
+        // rows past n_q arrive as zeros).  The route to this kernel asks for 16-byte aligned Q rows and strides and a
+        // 16-byte aligned output, which is all the two tensor maps need.
         constexpr bool  kStageQ   = !kVLo;
         constexpr bool  kTmaOut   = !kVLo;  // the same room holds the output staging tile
-        uint8_t * const stage_row = smem_gen + (sStage - smem_base) + row * 256;
         uint8_t * const stage_tma = smem_gen + (sStage - smem_base) + row * 128;  // + half * 16 KB + swizzled chunk
         uint32_t        qs_phase  = 0;      // of the staging barrier
         bool            io_failed = false;  // set by all 128 threads together
         auto fetch_q = [&](const WorkItem & w) {
-            if (p.tma_q) {
-                named_bar_sync(1, kIoThreads);  // every thread has read the rows that were there
-                if (row == 0) {
+            named_bar_sync(1, kIoThreads);  // every thread has read the rows that were there
+            if (row == 0) {
 #if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_IO)
-                    mbar_arrive(bQS);
+                mbar_arrive(bQS);
 #else
-                    mbar_expect_tx(bQS, kQStageBytes);
-                    tma_load_5d(sStage, &map_q, bQS, 0, w.head, w.q0, w.batch, 0);
-                    tma_load_5d(sStage + kQStageBytes / 2, &map_q, bQS, 32, w.head, w.q0, w.batch, 0);
+                mbar_expect_tx(bQS, kQStageBytes);
+                tma_load_5d(sStage, &map_q, bQS, 0, w.head, w.q0, w.batch, 0);
+                tma_load_5d(sStage + kQStageBytes / 2, &map_q, bQS, 32, w.head, w.q0, w.batch, 0);
 #endif
-                }
-                return;
             }
-            const int qpos = w.q0 + row / p.pack, head = w.head + row % p.pack;
-            if (qpos < p.n_q) {
-                const uint8_t * src = p.q + (size_t) qpos * p.q_nb1 + (size_t) head * p.q_nb2 + (size_t) w.batch * p.q_nb3;
-#pragma unroll
-                for (int c = 0; c < 16; ++c) cp_async_16(smem_u32(stage_row) + ((c ^ (row & 15)) << 4), src + 16 * c);
-            }
-            cp_async_commit();
         };
-        auto convert_q = [&](const WorkItem & w, int buf) {
-            if (p.tma_q) {
-                const bool got = mbar_wait_bounded(bQS, qs_phase);
-                qs_phase ^= 1u;
-                if (!named_bar_all(1, kIoThreads, got)) { give_up(); io_failed = true; return; }
-            } else {
-                cp_async_wait_all();
-            }
+        auto convert_q = [&](const WorkItem &, int buf) {
+            const bool got = mbar_wait_bounded(bQS, qs_phase);
+            qs_phase ^= 1u;
+            if (!named_bar_all(1, kIoThreads, got)) { give_up(); io_failed = true; return; }
             uint8_t * const q_dst = smem_gen + buf * kQBufBytes + row * 128;
-            const bool      in    = w.q0 + row / p.pack < p.n_q;
             // chunk k (of 16) of this thread's raw row
             auto raw = [&](int k) {
-                if (p.tma_q) return *reinterpret_cast<const float4 *>(stage_tma + (k >> 3) * (kQStageBytes / 2) + (((k & 7) ^ (row & 7)) << 4));
-                return in ? *reinterpret_cast<const float4 *>(stage_row + ((k ^ (row & 15)) << 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                return *reinterpret_cast<const float4 *>(stage_tma + (k >> 3) * (kQStageBytes / 2) + (((k & 7) ^ (row & 7)) << 4));
             };
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -534,7 +515,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #endif
             const float l    = tmem_ld1(t_row + kOCol + kHeadDim);  // sum of exactly the rounded weights the tensor core used
             const float inv  = l > 0.0f ? 1.0f / l : 0.0f;
-            if (kTmaOut && p.tma_out) {
+            if (kTmaOut) {
                 // The row goes into the output staging tile, and two bulk-tensor stores (one per 128-byte half of the
                 // rows) carry the tile to its place: box = 32 floats x the group's heads x the item's tokens, so rows
                 // past n_q are clipped by the copy.  A thread per row writing 256 contiguous bytes of global memory
@@ -600,7 +581,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
         }
         // the last stores have been performed (waiting only until they have read the staging tile measured the same)
-        if (kTmaOut && p.tma_out && row == 0) bulk_wait_all();
+        if (kTmaOut && row == 0) bulk_wait_all();
     } else if (warp >= 4 && warp < 8) {
         regs_give<kRegsControl>();
         if (warp == 4) {
@@ -1243,29 +1224,22 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
         if (rc != VOX_ATTN_OK) return rc;
     }
     if (!v_lo) { mklo = mk; mvlo = mv; }  // not read
-    // the raw Q rows as a tensor map over (64 floats, heads, tokens, sequences), in whatever strides the caller's Q has
-    CUtensorMap mq = mk;
-    int         tma_q = 0;
-    if (!v_lo && (reinterpret_cast<uintptr_t>(a->q.data) & 15) == 0 && a->q.nb[1] % 16 == 0 && a->q.nb[2] % 16 == 0 && a->q.nb[3] % 16 == 0) {
-        const uint64_t qd[5] = {kHeadDim, (uint64_t) a->q.ne[2], (uint64_t) a->q.ne[1], (uint64_t) a->q.ne[3], 1};
-        const uint64_t qs[4] = {a->q.nb[2], a->q.nb[1], a->q.nb[3], std::max<uint64_t>(a->q.nb[3] * (uint64_t) a->q.ne[3], 16)};
-        const uint32_t qb[5] = {32, (uint32_t) pack_of(a), (uint32_t) (kTile / pack_of(a)), 1, 1};
-        int rc = make_tensor_map(e, &mq, const_cast<void *>(a->q.data), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, qd, qs, qb, CU_TENSOR_MAP_SWIZZLE_128B);
+    // Without remainder tiles in shared memory the raw Q rows come in and the results go out by bulk-tensor copies: Q as a
+    // tensor map over (64 floats, heads, tokens, sequences) in whatever strides the caller's Q has, the output as
+    // [batch][n_q][n_heads][64] f32; boxes of 32 floats x the heads of a group x the tokens of an item.  (With remainder
+    // tiles the rows are fetched and stored by their threads and the two maps are not read.)
+    CUtensorMap mq = mk, mo = mk;
+    if (!v_lo) {
+        VOX_REQUIRE((reinterpret_cast<uintptr_t>(a->dst.data) & 15) == 0, VOX_ATTN_INVALID_ARGUMENT, "dst must be 16-byte aligned");
+        const uint32_t box[5] = {32, (uint32_t) pack_of(a), (uint32_t) (kTile / pack_of(a)), 1, 1};
+        const uint64_t n_h = (uint64_t) a->q.ne[2], n_q = (uint64_t) a->q.ne[1], n_b = (uint64_t) a->q.ne[3], row_b = kHeadDim * 4;
+        const uint64_t qd[5] = {kHeadDim, n_h, n_q, n_b, 1};
+        const uint64_t qs[4] = {a->q.nb[2], a->q.nb[1], a->q.nb[3], std::max<uint64_t>(a->q.nb[3] * n_b, 16)};
+        int rc = make_tensor_map(e, &mq, const_cast<void *>(a->q.data), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, qd, qs, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != VOX_ATTN_OK) return rc;
-        tma_q = 1;
-    }
-    // the output's tensor map: [batch][n_q][n_heads][64] f32, stored in boxes of 32 floats x the heads of a group x the tokens
-    // of an item (without it, or when remainder tiles fill the shared memory, the rows are stored by their threads)
-    CUtensorMap mo = mk;
-    int         tma_out = 0;
-    if (!v_lo && (reinterpret_cast<uintptr_t>(a->dst.data) & 15) == 0) {
-        const uint64_t row_b = kHeadDim * 4, n_h = (uint64_t) a->q.ne[2], n_q = (uint64_t) a->q.ne[1], n_b = (uint64_t) a->q.ne[3];
-        const uint64_t od[5] = {kHeadDim, n_h, n_q, n_b, 1};
         const uint64_t os[4] = {row_b, n_h * row_b, n_q * n_h * row_b, n_b * n_q * n_h * row_b};
-        const uint32_t ob[5] = {32, (uint32_t) pack_of(a), (uint32_t) (kTile / pack_of(a)), 1, 1};
-        int rc = make_tensor_map(e, &mo, a->dst.data, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, od, os, ob, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = make_tensor_map(e, &mo, a->dst.data, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, qd, os, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != VOX_ATTN_OK) return rc;
-        tma_out = 1;
     }
     if (!(e->attr_mask & (1u << 12))) {
         VOX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pf(false)));
@@ -1288,8 +1262,6 @@ int run_tc(vox_engine * e, const vox_attn_args * a, void * workspace, size_t wor
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.scale  = a->scale;
     p.status = e->status_dev;
-    p.tma_out = tma_out;
-    p.tma_q   = tma_q;
     p.mask   = with_mask ? static_cast<const uint8_t *>(a->mask.data) : nullptr;
     p.m_nb1 = a->mask.nb[1]; p.m_nb2 = a->mask.nb[2]; p.m_nb3 = a->mask.nb[3];
     p.m_ne2 = with_mask ? (int) a->mask.ne[2] : 1; p.m_ne3 = with_mask ? (int) a->mask.ne[3] : 1;
