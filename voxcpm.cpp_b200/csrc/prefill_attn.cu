@@ -22,8 +22,7 @@
 //              over the tile's scores as two packed-f16 tiles hi + lo (~21 bits: one f16 per weight measured 2.3e-3 to
 //              5e-3 of the output RMS on random sequences of 512 to 4096 tokens, outside the 2e-3 parity bound; hi + lo
 //              measures under 6e-5): the tensor core takes the weights from there as the A operand of P.V, so they
-//              never pass through shared memory.  On the diagonal tile a warp skips the 32-column blocks none of its
-//              rows can see.  The output row and the row sums accumulate in TMEM over all tiles (no per-tile
+//              never pass through shared memory.  The output row and the row sums accumulate in TMEM over all tiles (no per-tile
 //              read-back); they are rescaled in place only when a tile's maximum exceeds the reference m_ref by more
 //              than 2^8.  The reference of a row passes from the thread of one score tile to the thread of the next
 //              (the other group) through shared memory and an mbarrier; it is handed on half-way through the
@@ -797,8 +796,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         for (int round = 0; ok && work_item<kMask>(p, round, w); ++round) {
             const int  qpos  = w.q0 + row / p.pack;
             const int  limit = min(qpos + p.causal_offset, p.n_kv - 1);  // last key this row may see
-            // last key any row of this warp may see (rows beyond n_q compute on zeros and are not stored)
-            const int  warp_limit = min(w.q0 + (32 * (warp & 3) + 31) / p.pack + p.causal_offset, p.n_kv - 1);
             // The output row and the row sum accumulate in TMEM across all key tiles, both scaled by
             // 2^(-m_ref): their ratio does not depend on m_ref, so the reference maximum only has to keep
             // the weights inside f16 range.  It is raised (and the accumulated columns rescaled) only when a
@@ -854,16 +851,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     const uint32_t t_s    = t_row + kSCol + kSub * sb;  // the tile's score buffer
                     // uniform over the group: the tile may be cut (no key tile before the one that holds `uncut` can be)
                     const bool     masked = j >= cut_from && k0 + kSub - 1 > uncut;
-                    // 32-column blocks of the tile with at least one key some row of this warp sees (warp-uniform)
-                    const int      n_live = !masked ? 2 : warp_limit < k0 ? 0 : min(2, (warp_limit - k0) / 32 + 1);
+                    // (Loading only the 32-column blocks some row of the warp can see, on the tiles the diagonal cuts, was
+                    // measured against always loading all 64 columns: the extra code in the loop cost more than the
+                    // loads it saved.)
                     uint32_t       r[kSub];
-                    if (n_live == 2) {
-                        tmem_ld64_sync(t_s, r);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < kSub; ++i) r[i] = 0xff800000u;  // -inf: no weight
-                        if (n_live == 1) tmem_ld32_sync(t_s, r);
-                    }
+                    tmem_ld64_sync(t_s, r);
                     PROF_STOP(10);
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(6, U);
                     if (kMask && m_read) {
