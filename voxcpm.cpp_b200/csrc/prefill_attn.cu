@@ -598,10 +598,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         const int      st = tw.slot;
                         const uint32_t ph = tw.phase ^ 1u;  // the stage's previous turn
                         PROF_STOP(0);
-                        if (T >= kSt && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        if (T >= kSt && !mbar_wait_bounded(kempty0 + 8 * st, ph)) { ok = false; break; }
                         PROF_STOP(1);
 #if defined(VOX_ATTN_DEVELOPER) && defined(VOX_PF_SKIP_LOAD)
-                        if (T >= kSt && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        if (T >= kSt && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { ok = false; break; }
                         mbar_arrive(kfull0 + 8 * st);
                         mbar_arrive(vfull0 + 8 * st);
                         continue;
@@ -610,7 +610,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         tma_load_5d(sK0 + st * kVBytes, &map_k, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
                         if (kVLo) tma_load_5d(sK0 + st * kVBytes + kKvBytes, &map_klo, kfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
                         PROF_STOP(0);
-                        if (T >= kSt && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { give_up(); ok = false; break; }
+                        if (T >= kSt && !mbar_wait_bounded(vempty0 + 8 * st, ph)) { ok = false; break; }
                         PROF_STOP(2);
                         mbar_expect_tx(vfull0 + 8 * st, kVBytes);
                         tma_load_5d(sV0 + st * kVBytes, &map_v, vfull0 + 8 * st, 0, j * kKeys, kvh, w.batch, 0);
@@ -618,6 +618,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     if (aborted()) break;
                 }
+                if (!ok) give_up();
                 PROF_STOP(0);
                 PROF_FLUSH(0, 3);  // 0 issue, 1 wait K stage free, 2 wait V stage free
             }
@@ -648,17 +649,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 PROF_START();
                 for (int rq = 0; ok && work_item<kMask>(p, rq, wq); ++rq) {
                     PROF_STOP(0);
-                    if (!warp_wait(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) { give_up(); break; }  // the item's Q tile is in place
+                    if (!warp_wait(bQ0 + 8 * (rq % kQBufs), (rq / kQBufs) & 1)) { ok = false; break; }  // the item's Q tile is in place
                     PROF_STOP(2);
                     const uint64_t dQi = dQ + (rq % kQBufs) * kQBuf;
                     for (int jq = next_live<kMask>(wq, 0); ok && jq < wq.n_tiles; jq = next_live<kMask>(wq, jq + 1), ++Tk, tw.step(kSt)) {
                         const int st = tw.slot, n_sub = sub_tiles(p, wq, jq);
                         PROF_STOP(0);
-                        if (!warp_wait(kfull0 + 8 * st, tw.phase)) { give_up(); ok = false; break; }
+                        if (!warp_wait(kfull0 + 8 * st, tw.phase)) { ok = false; break; }
                         PROF_STOP(2);
                         for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
                             const int sb = uw.slot;
-                            if (U >= kSBufs && !warp_wait(bF0 + 8 * sb, uw.phase ^ 1u)) { give_up(); ok = false; break; }
+                            if (U >= kSBufs && !warp_wait(bF0 + 8 * sb, uw.phase ^ 1u)) { ok = false; break; }
                             PROF_STOP(1);
                             if (lane == 0) PROF_TRACE(4, U);
                             tc_fence_after();
@@ -686,6 +687,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     if (!ok || warp_aborted()) break;
                 }
+                if (!ok) give_up();
                 PROF_STOP(0);
                 if (lane == 0) PROF_FLUSH(21, 3);  // 21 issue, 22 wait for the score buffer, 23 wait Q / K tile
             }
@@ -718,16 +720,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         const int st = tw.slot, n_sub = sub_tiles(p, w, j);
                         const int j_next = next_live<kMask>(w, j + 1);
                         PROF_STOP(0);
-                        if (!warp_wait(vfull0 + 8 * st, tw.phase)) { give_up(); ok = false; break; }
+                        if (!warp_wait(vfull0 + 8 * st, tw.phase)) { ok = false; break; }
                         PROF_STOP(3);
                         const uint64_t dVs = dV + st * kVStage;
                         for (int u = 0; u < n_sub; ++u, ++U, uw.step(kSBufs)) {
                             const int sb = uw.slot;
                             if (lane == 0) PROF_TRACE(14, U);
-                            if (!warp_wait(bP0 + 8 * sb, uw.phase)) { give_up(); ok = false; break; }
+                            if (!warp_wait(bP0 + 8 * sb, uw.phase)) { ok = false; break; }
                             PROF_STOP(4);
                             // the previous item's result has been read out of TMEM: its columns may be overwritten
-                            if (first && round > 0 && !warp_wait(bOfree, (round - 1) & 1)) { give_up(); ok = false; break; }
+                            if (first && round > 0 && !warp_wait(bOfree, (round - 1) & 1)) { ok = false; break; }
                             PROF_STOP(2);
                             if (lane == 0) PROF_TRACE(2, U);
                             tc_fence_after();
@@ -769,6 +771,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     if (!ok || warp_aborted()) break;
                 }
+                if (!ok) give_up();
                 PROF_STOP(0);
                 if (lane == 0) PROF_FLUSH(4, 5);  // 4 issue, 6 wait output read, 7 wait V tile, 8 wait P
             }
@@ -836,7 +839,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     }
                     PROF_STOP(0);
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(11, U);
-                    if (!mbar_wait_bounded(bS0 + 8 * sb, uw.phase)) { give_up(); ok = false; break; }
+                    if (!mbar_wait_bounded(bS0 + 8 * sb, uw.phase)) { ok = false; break; }
                     PROF_STOP(1);
                     PROF_COUNT(7, 1);
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(0, U);
@@ -891,7 +894,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     // can complete twice between two looks of its waiter, and a slot of row_ref is rewritten (tile U + 2)
                     // only after its reader (tile U + 1) has published in turn, which it does after reading.
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(7, U);
-                    if (U > 0 && !mbar_wait_bounded(bM0 + 8 * ((U - 1) % kGroups), ((U - 1) / kGroups) & 1)) { give_up(); ok = false; break; }
+                    if (U > 0 && !mbar_wait_bounded(bM0 + 8 * ((U - 1) % kGroups), ((U - 1) / kGroups) & 1)) { ok = false; break; }
                     PROF_STOP(11);
                     if ((warp & 3) == 0 && lane == 0) PROF_TRACE(8, U);
                     // The weights are written only after the whole tile has been looked at, so a raise of the
@@ -909,7 +912,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             const float f = raise ? ex2_approx(m_ref - cmax) : 1.0f;
                             if (raise) m_ref = cmax;
                             // the accumulators are at rest once P.V of the previous score tile has retired
-                            if (!mbar_wait_bounded(bF0 + 8 * ((U - 1) % kSBufs), ((U - 1) / kSBufs) & 1)) { give_up(); ok = false; break; }
+                            if (!mbar_wait_bounded(bF0 + 8 * ((U - 1) % kSBufs), ((U - 1) / kSBufs) & 1)) { ok = false; break; }
                             rescale_accumulators(t_row, f);
                         }
                     }
@@ -970,6 +973,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     PROF_STOP(3);
                 }
             }
+            if (!ok) give_up();  // a wait of this thread ran out: raised once, here, to keep the tile loop short
             if (!ok || aborted()) break;
             PROF_COUNT(9, 1);
         }
