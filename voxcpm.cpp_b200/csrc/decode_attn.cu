@@ -773,7 +773,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                 st[u]   = cstage + u < n_stages ? cstage + u : cstage + u - n_stages;
                 p0[u]   = (w.t + i + u) * kKvTile + 16 * warp;
                 act[u]  = have[u] && p0[u] < c1;
-                if (have[u] && !mbar_wait_bounded(full0 + 8 * st[u], cstage + u < n_stages ? cphase : cphase ^ 1)) ok = false;
+                if (have[u] && !mbar_wait_bounded(full0 + 8 * st[u], cstage + u < n_stages ? cphase : cphase ^ 1)) {
+                    *reinterpret_cast<volatile int *>(&abort_flag) = 1;
+                    ok = false;
+                }
             }
             if (!ok) break;
             if (tid == 0 && it == 0 && i == 0) DECODE_TRACE(3);
@@ -978,10 +981,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         }
         if (tid == 0 && it + seg >= n_tiles) DECODE_TRACE(4);
 
-        if (!ok) {  // a copy never arrived: raised here, once, so that the tile loop stays short
-            atomicOr(p.status, kStatusTimeout);
-            atomicExch(&abort_flag, 1);
-        }
+        if (*reinterpret_cast<volatile int *>(&abort_flag)) atomicOr(p.status, kStatusTimeout);  // raised here, once: the tile loop stays short
         // ---- merge the four warps through the stage of the last tile (all of them are done with it after the barrier)
         named_bar_sync(1, kConsumerWarps * 32);
         if (!ok || *reinterpret_cast<volatile int *>(&abort_flag)) return;
