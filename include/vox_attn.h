@@ -117,7 +117,9 @@ size_t vox_attn_workspace_bytes(const vox_attn_args * a);
  * reference's prefill call, src/minicpm.cpp:708-710, with the tensor create_causal_mask built, or
  * any other additive f16 mask whose rows start on 16-byte boundaries, n_kv a multiple of 8) ->
  * tcgen05 kernel, which reads the mask (see vox_attn_prefill for the form that implies it; q8_0
- * and f32 K/V need the workspace vox_attn_workspace_bytes names), and so do two or more queries
+ * and f32 K/V need the workspace vox_attn_workspace_bytes names; with that workspace a small kernel
+ * first marks the key tiles the mask hides altogether, which are then not walked, and those it adds
+ * nothing to, which are then not read), and so do two or more queries
  * over 32 or more keys without a mask; anything else the contract allows (any
  * n_q/n_kv, f32/f16/q8_0 K/V, arbitrary f16 mask, strides) -> general kernel.  Never allocates. */
 int vox_attn_forward(vox_engine * e, const vox_attn_args * a, void * workspace, size_t workspace_bytes,
